@@ -1,0 +1,111 @@
+"""ctypes mirrors of the C records of include/anemone_b200_records.h and include/anemone_b200_backend.h.
+
+Field order and sizes follow the C headers exactly; sizes are asserted at import.
+"""
+import ctypes as C
+
+LINEAR_MAXIMUM_ROWS = 8
+LAUNCH_ARGUMENT_BYTES = 192
+EXL3_WIDTH_PER_EXPERT = 0xFFFF
+BACKEND_NO_KERNEL = 0xFFFFFFFF
+
+STATUS_NAMES = ["OK", "INVALID_ARGUMENT", "OUT_OF_MEMORY", "INPUT_OUTPUT_ERROR", "CORRUPT_PACK", "DEVICE_ERROR",
+                "TIMED_OUT", "UNSUPPORTED", "BUSY_VALUE", "INJECTED_FAULT"]
+STATUS_OK, STATUS_INVALID_ARGUMENT, STATUS_OUT_OF_MEMORY = 0, 1, 2
+STATUS_DEVICE_ERROR, STATUS_TIMED_OUT, STATUS_UNSUPPORTED, STATUS_BUSY_VALUE = 5, 6, 7, 8
+
+
+class Exl3Reconstruct(C.Structure):
+    _fields_ = [("matrix_offset", C.c_uint64), ("output_offset", C.c_uint64), ("input_size", C.c_uint32),
+                ("output_size", C.c_uint32), ("bits_per_weight", C.c_uint32), ("reserved_zero", C.c_uint32)]
+
+
+class Exl3Expert(C.Structure):
+    _fields_ = [("jobs_offset", C.c_uint64), ("input_offset", C.c_uint64), ("operands_offset", C.c_uint64),
+                ("products_offset", C.c_uint64), ("hidden_offset", C.c_uint64), ("output_offset", C.c_uint64),
+                ("input_size", C.c_uint32), ("inner_size", C.c_uint32), ("pair_count", C.c_uint32),
+                ("pairs_per_row", C.c_uint32), ("job_count", C.c_uint32), ("bits_per_weight", C.c_uint32),
+                ("activation_limit", C.c_float), ("reserved_zero", C.c_uint32)]
+
+
+class ExpertJob(C.Structure):
+    _fields_ = [("gate_offset", C.c_uint64), ("up_offset", C.c_uint64), ("down_offset", C.c_uint64),
+                ("row_count", C.c_uint32), ("expert", C.c_uint32), ("pair_index", C.c_uint32 * LINEAR_MAXIMUM_ROWS),
+                ("route_weight", C.c_float * LINEAR_MAXIMUM_ROWS)]
+
+
+class ExpertRowSum(C.Structure):
+    _fields_ = [("pair_output_offset", C.c_uint64), ("row_output_offset", C.c_uint64), ("width", C.c_uint32),
+                ("pairs_per_row", C.c_uint32)]
+
+
+class Exl3ShardActivation(C.Structure):
+    _fields_ = [("base", Exl3Expert), ("down_input_size", C.c_uint32), ("down_output_size", C.c_uint32),
+                ("down_input_begin", C.c_uint32), ("reserved_zero", C.c_uint32)]
+
+
+class Exl3Moe(C.Structure):
+    _fields_ = [("base", Exl3Expert), ("widths_offset", C.c_uint64), ("row_output_offset", C.c_uint64),
+                ("expert_count", C.c_uint32), ("reserved_zero", C.c_uint32)]
+
+
+class StepBlock(C.Structure):
+    _fields_ = [("sequence", C.c_uint64), ("row_count", C.c_uint32), ("flags", C.c_uint32)]
+
+
+class OrderedPeer(C.Structure):
+    _fields_ = [("arena_address", C.c_uint64), ("region_offset", C.c_uint64), ("host_address", C.c_uint64),
+                ("route", C.c_uint32), ("reserved_zero", C.c_uint32)]
+
+
+class OrderedCollective(C.Structure):
+    _fields_ = [("peer_table_offset", C.c_uint64), ("region_offset", C.c_uint64), ("input_offset", C.c_uint64),
+                ("output_offset", C.c_uint64), ("scratch_offset", C.c_uint64), ("step_offset", C.c_uint64),
+                ("parity_stride", C.c_uint64), ("deadline_cycles", C.c_uint64), ("element_count", C.c_uint32),
+                ("rank_count", C.c_uint32), ("rank", C.c_uint32), ("reserved_zero", C.c_uint32)]
+
+
+class OrderedReduceBf16(C.Structure):
+    _fields_ = [("collective", OrderedCollective), ("status_offset", C.c_uint64), ("width", C.c_uint32),
+                ("reserved_zero", C.c_uint32)]
+
+
+class OrderedRowSumPublish(C.Structure):
+    _fields_ = [("collective", OrderedCollective), ("pair_output_offset", C.c_uint64), ("width", C.c_uint32),
+                ("pairs_per_row", C.c_uint32)]
+
+
+class RouterSelectB200(C.Structure):
+    _fields_ = [("scores_offset", C.c_uint64), ("expert_table_offset", C.c_uint64), ("picks_offset", C.c_uint64),
+                ("weights_offset", C.c_uint64), ("jobs_offset", C.c_uint64), ("step_offset", C.c_uint64),
+                ("expert_count", C.c_uint32), ("shared_count", C.c_uint32), ("picks", C.c_uint32),
+                ("row_capacity", C.c_uint32), ("job_capacity", C.c_uint32), ("scoring", C.c_uint32),
+                ("route_scale", C.c_float), ("reserved_zero", C.c_uint32)]
+
+
+class KernelLaunch(C.Structure):
+    _fields_ = [("kernel", C.c_uint32), ("grid", C.c_uint32 * 3), ("block", C.c_uint32 * 3),
+                ("dynamic_shared_byte_count", C.c_uint32), ("argument_byte_count", C.c_uint32),
+                ("branch", C.c_uint32), ("argument", C.c_ubyte * LAUNCH_ARGUMENT_BYTES)]
+
+
+class CardDescription(C.Structure):
+    _fields_ = [("name", C.c_char * 96), ("bus_address", C.c_char * 32), ("arithmetic_class", C.c_uint32),
+                ("link_generation", C.c_uint32), ("link_lane_count", C.c_uint32), ("reserved_zero", C.c_uint32),
+                ("memory_total_bytes", C.c_uint64), ("memory_free_bytes", C.c_uint64),
+                ("memory_reserved_bytes", C.c_uint64)]
+
+
+class OrderedCollectiveDescription(C.Structure):
+    _fields_ = [("arguments", OrderedCollective), ("arena_byte_count", C.c_uint64), ("operation", C.c_int)]
+
+
+class OrderedCollectiveKernels(C.Structure):
+    _fields_ = [("handles", C.c_uint32 * 4)]
+
+
+for _record, _bytes in ((Exl3Reconstruct, 32), (Exl3Expert, 80), (ExpertJob, 96), (ExpertRowSum, 24),
+                        (Exl3ShardActivation, 96), (Exl3Moe, 104), (StepBlock, 16), (OrderedPeer, 32),
+                        (OrderedCollective, 80), (OrderedReduceBf16, 96), (OrderedRowSumPublish, 96),
+                        (RouterSelectB200, 80), (KernelLaunch, 232), (CardDescription, 168)):
+    assert C.sizeof(_record) == _bytes, (_record.__name__, C.sizeof(_record), _bytes)

@@ -1,0 +1,350 @@
+/*
+ * anemone_b200_records.h: the by-value records the kernels of this library take, and the layout of every
+ * array a record names. Compiles as C11 (host preparers, oracle, tests) and as CUDA C++ (kernel files).
+ *
+ * The universal kernel contract (reference: include/anemone/backend_seam.h:60-79,
+ * include/anemone/linear_records.h:9-15): a kernel is
+ *     extern "C" __global__ void name(struct <record> record, unsigned char *arena);
+ * a record names memory only by byte offsets into the card's arena, never by address, so a prepared launch is
+ * the same bytes on every card. Kernels validate nothing; the host preparer has checked every range.
+ *
+ * Every struct below whose comment names a reference header is ABI-identical to that header's struct (same
+ * field order, sizes and offsets, asserted at the end of this file), so launch tables and job tables written
+ * by reference-side code are read unchanged. Structs marked "B200 extension" have no reference counterpart.
+ */
+#ifndef ANEMONE_B200_RECORDS_H
+#define ANEMONE_B200_RECORDS_H
+
+#include <stdbool.h>
+#include <stdint.h>
+
+#ifdef __CUDACC__
+#define AB_INLINE __host__ __device__ static inline
+#else
+#define AB_INLINE static inline
+#endif
+
+/* ------------------------------------------------------------------------------------------------------------
+ * EXL3 "mul1" trellis format (reference: include/anemone/exl3_records.h:2-9, 45-119).
+ *
+ * A matrix of `inputs` x `outputs` weights is stored as
+ *     codes  [inputs/16][outputs/16] tiles, each tile 16 x 16 weights = 128 * bits_x2 bits
+ *            (little-endian uint32 words, bit stream MSB-first inside each word, cyclic),
+ *     suh    FP16 [inputs]   (sign/scale applied to the input side before the 128-wide Hadamard transform),
+ *     svh    FP16 [outputs]  (sign/scale applied to the output side after it).
+ * bits_x2 is twice the bits per weight, so that half widths (2.5 bits) are whole numbers. The weight at stream
+ * position p of a tile has the 16-bit state whose window ENDS at ring bit S(p) = floor((p + 1) * bits_x2 / 2);
+ * its value is the codebook below. Stream position <-> (input, output) inside a tile follows the A-fragment
+ * order of the m16n8k16 tensor-core instruction: see exl3_tile_position.
+ * A "stored width" is K for whole K bits per weight and 16 K for a half width (K = 2.5 is stored as 40).
+ * ---------------------------------------------------------------------------------------------------------- */
+#define EXL3_TILE 16u
+#define EXL3_TILE_VALUES 256u
+#define EXL3_TRANSFORM 128u
+#define EXL3_STATE_BITS 16u
+#define EXL3_WORD_BITS 32u
+#define EXL3_HALF_BYTES 2u
+#define EXL3_K2 2u
+#define EXL3_K2_5 40u
+#define EXL3_K3 3u
+#define EXL3_K4 4u
+#define EXL3_BITS_X2_K2 4u
+#define EXL3_BITS_X2_K2_5 5u
+#define EXL3_BITS_X2_K3 6u
+#define EXL3_BITS_X2_K4 8u
+#define EXL3_MUL1_MULTIPLIER 0x83DCD12Du
+#define EXL3_MUL1_BASE 0x6400u /* FP16 1024.0: adding a byte sum b < 1024 gives FP16 (1024 + b) exactly */
+#define EXL3_MUL1_SCALE 0x1EEEu /* FP16 1774 / 2^18 */
+#define EXL3_MUL1_BIAS 0xC931u /* FP16 -10.3828125 */
+#define EXL3_NORMALIZATION 0.08838834764831845f /* 1 / sqrt(128), the Hadamard scale */
+#define EXL3_PROJECTIONS 2u /* gate and up */
+#define EXL3_EXPERT_LAUNCHES 5u
+#define EXL3_KERNEL_FILE "kernel_exl3"
+#define EXL3_RECONSTRUCT "exl3_reconstruct"
+#define EXL3_ROW_SUM "exl3_row_sum"
+/* B200 extension: a record's bits_per_weight that means "read each expert's stored width from the table at
+ * widths_offset" (struct exl3_moe_record). No stored width has this value. */
+#define EXL3_WIDTH_PER_EXPERT 0xFFFFu
+
+/* bits_x2 of a stored width, 0 if the value is no width of the format (whole 1..8, half 1.5..7.5). */
+AB_INLINE uint32_t exl3_bits_x2(uint32_t stored_width)
+{
+	if (stored_width >= 1u && stored_width <= 8u)
+		return 2u * stored_width;
+	if ((stored_width & 15u) == 8u && stored_width < 128u)
+		return stored_width >> 3;
+	return 0u;
+}
+
+/* The widths this library decodes: K2, K2.5, K3, K4 (the reference's EXL3_SUPPORTED_BITS_X2). */
+AB_INLINE bool exl3_width_supported(uint32_t stored_width)
+{
+	const uint32_t b = exl3_bits_x2(stored_width);
+	return b == EXL3_BITS_X2_K2 || b == EXL3_BITS_X2_K2_5 || b == EXL3_BITS_X2_K3 || b == EXL3_BITS_X2_K4;
+}
+
+/* S(p): the ring bit at which the 16-bit window of stream position p ends. */
+AB_INLINE uint32_t exl3_window_end(uint32_t position, uint32_t bits_x2)
+{
+	return ((position + 1u) * bits_x2) >> 1;
+}
+
+/* Bytes of the codes of an inputs x outputs matrix (both whole tiles). Divides first: no 64-bit overflow. */
+AB_INLINE uint64_t exl3_code_bytes(uint64_t inputs, uint64_t outputs, uint32_t bits_x2)
+{
+	return inputs * outputs / 16u * bits_x2;
+}
+
+/* Stored bytes of a matrix: codes, then suh[inputs], then svh[outputs]. */
+AB_INLINE uint64_t exl3_matrix_bytes(uint64_t inputs, uint64_t outputs, uint32_t bits_x2)
+{
+	return exl3_code_bytes(inputs, outputs, bits_x2) + (inputs + outputs) * EXL3_HALF_BYTES;
+}
+
+/* Stream position of weight (input, output), both 0..15, inside its tile: lane l = 4 (output % 8) +
+ * (input % 8) / 2 of a warp holds positions 8 l .. 8 l + 7, in the register order of the instruction's A operand. */
+AB_INLINE uint32_t exl3_tile_position(uint32_t input, uint32_t output)
+{
+	const uint32_t lane = ((output & 7u) << 2) | ((input & 7u) >> 1);
+	const uint32_t element = (input & 1u) | ((input >> 3) << 1) | ((output >> 3) << 2);
+	return (lane << 3) | element;
+}
+
+/* kernel_exl3 / exl3_reconstruct (reference: include/anemone/exl3_records.h:123-130): decode a whole matrix to
+ * FP16 [input][output], before either transform or scale. Bit-exact diagnostic. */
+struct exl3_reconstruct_record {
+	uint64_t matrix_offset;
+	uint64_t output_offset;
+	uint32_t input_size;
+	uint32_t output_size;
+	uint32_t bits_per_weight; /* stored width */
+	uint32_t reserved_zero;
+};
+
+/* One expert layer's chain (reference: include/anemone/exl3_records.h:144-159).
+ *   jobs      struct expert_job_record [job_count]
+ *   input     bfloat16 [rows][input_size], rows = pair_count / pairs_per_row
+ *   operands  FP16 [2][pair_count][input_size] for gate/up; reused as FP16 [pair_count][inner_size] for down
+ *   products  FP32 [2][pair_count][inner_size] for gate/up; reused as FP32 [pair_count][input_size] for down
+ *   hidden    bfloat16 [pair_count][inner_size] (side output of the activation)
+ *   output    FP32 [pair_count][input_size]; equals products_offset (finish works in place) */
+struct exl3_expert_record {
+	uint64_t jobs_offset;
+	uint64_t input_offset;
+	uint64_t operands_offset;
+	uint64_t products_offset;
+	uint64_t hidden_offset;
+	uint64_t output_offset;
+	uint32_t input_size; /* hidden width H of the model */
+	uint32_t inner_size; /* this rank's intermediate width */
+	uint32_t pair_count;
+	uint32_t pairs_per_row;
+	uint32_t job_count;
+	uint32_t bits_per_weight; /* stored width of every matrix of the launch */
+	float activation_limit;
+	uint32_t reserved_zero;
+};
+
+/* One routed expert with the rows routed to it (reference: include/anemone/linear_records.h:245-253). Written by
+ * the router, read by every expert kernel. row_count 0 = empty job, nothing else of it is read. Column c < row_count
+ * carries pair pair_index[c] = row * pairs_per_row + slot and that pair's route weight. */
+#define LINEAR_MAXIMUM_ROWS 8u
+#define LINEAR_OFFSET_ALIGNMENT_BYTES 16u
+#define WEIGHT_FORMAT_MATRIX_ALIGNMENT_BYTES 64u
+struct expert_job_record {
+	uint64_t gate_offset;
+	uint64_t up_offset;
+	uint64_t down_offset;
+	uint32_t row_count;
+	uint32_t expert;
+	uint32_t pair_index[LINEAR_MAXIMUM_ROWS];
+	float route_weight[LINEAR_MAXIMUM_ROWS];
+};
+
+/* exl3_row_sum (reference: include/anemone/linear_records.h:209-216): row = sum of its pairs_per_row pair outputs,
+ * from +0 in ascending slot order. FP32 [rows * pairs_per_row][width] -> FP32 [rows][width], rows = grid[1]. */
+struct expert_row_sum_arguments {
+	uint64_t pair_output_offset;
+	uint64_t row_output_offset;
+	uint32_t width;
+	uint32_t pairs_per_row;
+};
+
+/* bb_exl3_activate_output_shard (reference: include/anemone/exl3_tp_records.h:17-23): the activation of a rank whose
+ * gate/up are an output slice [down_input_begin, +base.inner_size) of the full intermediate and whose resident down
+ * matrix has the stated full shape; it reads down's suh at down_input_begin. */
+struct bb_exl3_shard_activation_record {
+	struct exl3_expert_record base;
+	uint32_t down_input_size;
+	uint32_t down_output_size;
+	uint32_t down_input_begin;
+	uint32_t reserved_zero;
+};
+
+/* B200 extension, kernel file "kernel_exl3_b200": the whole routed-expert layer of one rank in four launches
+ * (input transform; gate/up products fused with the SwiGLU activation and the down-side input transform; down
+ * products fused with the output transform and route weight; ordered row sum), with a stored width per expert.
+ * base is read exactly as the five-pass chain reads it, except that base.bits_per_weight may be
+ * EXL3_WIDTH_PER_EXPERT, in which case expert e's three matrices have stored width widths[e]
+ * (uint32 [expert_count] at widths_offset). row_output: FP32 [rows][input_size]. */
+#define EXL3_MOE_KERNEL_FILE "kernel_exl3_b200"
+#define EXL3_MOE_LAUNCHES 4u
+struct exl3_moe_record {
+	struct exl3_expert_record base;
+	uint64_t widths_offset;
+	uint64_t row_output_offset;
+	uint32_t expert_count;
+	uint32_t reserved_zero;
+};
+
+/* The block every step-dependent kernel reads on the device, so that one prepared launch (or one captured graph)
+ * serves every step (reference: include/anemone/step_records.h:111-115). */
+struct step_block {
+	uint64_t sequence; /* of the step, from 1, strictly increasing */
+	uint32_t row_count; /* live rows of this step */
+	uint32_t flags;
+};
+
+/* ------------------------------------------------------------------------------------------------------------
+ * Fixed-order reduction over ranks (reference: include/anemone/ordered_collective_records.h:45-98).
+ *
+ * Each rank owns a region of two parity slots (slot = sequence & 1) of parity_stride bytes. A slot begins with three
+ * 128-byte signal lines (READY, REDUCED, DONE), each written only by its owner: a 32-bit commit generation at byte 0
+ * and the 64-bit step sequence at byte 8; then the input, output and scratch arrays at the record's offsets (relative
+ * to the slot). The peer table holds, per rank, the device address under which THIS card reaches that rank's arena
+ * and that rank's region offset. Sum order: ((+0 + rank 0) + rank 1) + ..., one rounded FP32 add per rank.
+ * ---------------------------------------------------------------------------------------------------------- */
+#define KERNEL_FILE_ORDERED_COLLECTIVE "kernel_ordered_collective"
+#define KERNEL_ORDERED_ALL_REDUCE "ordered_all_reduce"
+#define KERNEL_ORDERED_TWO_SHOT "ordered_two_shot"
+#define KERNEL_ORDERED_REDUCE_SCATTER "ordered_reduce_scatter"
+#define KERNEL_ORDERED_GATHER "ordered_gather"
+#define ORDERED_COLLECTIVE_MAXIMUM_RANKS 16u
+#define ORDERED_COLLECTIVE_THREADS 256u
+#define ORDERED_COLLECTIVE_LINE_BYTES 128ull
+#define ORDERED_COLLECTIVE_PHASES 3u
+#define ORDERED_COLLECTIVE_SIGNAL_BYTES (ORDERED_COLLECTIVE_PHASES * ORDERED_COLLECTIVE_LINE_BYTES)
+#define ORDERED_COLLECTIVE_SLOTS 2u
+#define ORDERED_COLLECTIVE_MAXIMUM_ELEMENTS 262144u
+#define ORDERED_COLLECTIVE_SEQUENCE_OFFSET 8u
+#define ORDERED_COLLECTIVE_DIRECT_ROUTE 0u
+#define ORDERED_COLLECTIVE_HOST_ROUTE 1u /* PCIe host mirrors of the reference's cards: refused by this library */
+
+enum ordered_collective_operation {
+	ORDERED_ALL_REDUCE,
+	ORDERED_TWO_SHOT,
+	ORDERED_REDUCE_SCATTER,
+	ORDERED_GATHER,
+	ORDERED_COLLECTIVE_OPERATIONS
+};
+
+struct ordered_collective_peer {
+	uint64_t arena_address;
+	uint64_t region_offset;
+	uint64_t host_address;
+	uint32_t route;
+	uint32_t reserved_zero;
+};
+
+struct ordered_collective_arguments {
+	uint64_t peer_table_offset;
+	uint64_t region_offset;
+	uint64_t input_offset; /* the three arrays: offsets inside a parity slot, behind the signal lines */
+	uint64_t output_offset;
+	uint64_t scratch_offset;
+	uint64_t step_offset; /* struct step_block in the arena */
+	uint64_t parity_stride;
+	uint64_t deadline_cycles; /* of the device clock; a wait that runs out sets the status word, never traps */
+	uint32_t element_count;
+	uint32_t rank_count;
+	uint32_t rank;
+	uint32_t reserved_zero;
+};
+
+/* B200 extension, kernel file "kernel_ordered_b200": the production reduction of expert partial sums. Many CTAs;
+ * every rank pulls every rank's FP32 partial rows by peer loads over NVLink, adds them in rank order from +0 in FP32,
+ * rounds ONCE to bfloat16 (to nearest even, a not-a-number to 0x7FC0: the arithmetic of the reference's
+ * tp_exchange_owner_sum, source/kernel_tp_exchange.cu:190-247) and stores bfloat16 [rows][width] locally.
+ * `collective` is read as the FP32 collective reads it, except: output_offset is an ARENA offset of the bfloat16
+ * result (not inside the slot); scratch_offset is unused; element_count is the capacity rows * width and the live
+ * element count is step.row_count * width. status_offset names a 16-byte status block in the arena:
+ * {uint32 code (0 ok, 1 timed out, 2 bad sequence), uint32 phase, uint32 rank waited for, uint32 reserved},
+ * written only on failure. */
+#define KERNEL_FILE_ORDERED_B200 "kernel_ordered_b200"
+#define KERNEL_ORDERED_REDUCE_BF16 "ordered_reduce_bf16"
+#define KERNEL_ORDERED_ROW_SUM_PUBLISH "ordered_row_sum_publish"
+#define ORDERED_B200_MAXIMUM_BLOCKS 64u
+#define ORDERED_B200_STATUS_BYTES 16u
+#define ORDERED_STATUS_OK 0u
+#define ORDERED_STATUS_TIMED_OUT 1u
+#define ORDERED_STATUS_BAD_SEQUENCE 2u
+struct ordered_reduce_bf16_arguments {
+	struct ordered_collective_arguments collective;
+	uint64_t status_offset;
+	uint32_t width; /* elements of a row */
+	uint32_t reserved_zero;
+};
+
+/* B200 extension: the row sum of a rank written straight into its collective input slot of this step's parity
+ * (FP32 [rows][width] at collective.input_offset of the slot), so that no copy stands between the experts and the
+ * reduction. Rows at or beyond step.row_count are not written. grid (width / 128 rounded up, rows). */
+struct ordered_row_sum_publish_arguments {
+	struct ordered_collective_arguments collective;
+	uint64_t pair_output_offset; /* FP32 [rows * pairs_per_row][width] */
+	uint32_t width;
+	uint32_t pairs_per_row;
+};
+
+/* ------------------------------------------------------------------------------------------------------------
+ * Router (B200 extension of the reference's router_select_entry, include/anemone/router_records.h:7-52): scores
+ * FP32 [rows][expert_count] -> for each live row the `picks` experts of largest score (a not-a-number above every
+ * number, -0 below +0, the lower expert first among equals), slots in ascending expert order, affinity
+ * a = 1 / (1 + exp(-s)) (scoring 0) or sqrt(softplus(s)) (scoring 1, the reference's), weights a / (t + 1e-20) *
+ * route_scale with t the sum of the picked a from +0 in ascending expert order; then the whole job table: one job per
+ * chosen expert in ascending expert order, split in jobs of at most 8 rows in ascending row order, then the
+ * always-on experts (shared experts: ids expert_count .. expert_count + shared_count - 1, weight 1, pair slot
+ * picks + s), then empty jobs to job_capacity. One block of 1024 threads. */
+#define KERNEL_FILE_ROUTER_B200 "kernel_router_b200"
+#define KERNEL_ROUTER_SELECT_B200 "router_select_b200"
+#define ROUTER_B200_THREADS 1024u
+#define ROUTER_B200_MAXIMUM_EXPERTS 512u
+#define ROUTER_B200_MAXIMUM_PICKS 16u
+#define ROUTER_B200_MAXIMUM_ROWS 64u
+#define ROUTER_SCORING_SIGMOID 0u
+#define ROUTER_SCORING_SQRT_SOFTPLUS 1u
+struct router_select_b200_arguments {
+	uint64_t scores_offset; /* FP32 [row_capacity][expert_count] */
+	uint64_t expert_table_offset; /* uint64 [expert_count + shared_count][3]: gate, up, down matrix offsets */
+	uint64_t picks_offset; /* written: uint32 [row_capacity][picks] experts by slot */
+	uint64_t weights_offset; /* written: FP32 [row_capacity][picks] */
+	uint64_t jobs_offset; /* written: struct expert_job_record [job_capacity] */
+	uint64_t step_offset; /* struct step_block: row_count live rows */
+	uint32_t expert_count;
+	uint32_t shared_count;
+	uint32_t picks;
+	uint32_t row_capacity;
+	uint32_t job_capacity;
+	uint32_t scoring;
+	float route_scale;
+	uint32_t reserved_zero;
+};
+
+#ifdef __cplusplus
+#define AB_RECORD_HAS(record, bytes) static_assert(sizeof(struct record) == (bytes), #record " ABI")
+#else
+#define AB_RECORD_HAS(record, bytes) _Static_assert(sizeof(struct record) == (bytes), #record " ABI")
+#endif
+AB_RECORD_HAS(exl3_reconstruct_record, 32);
+AB_RECORD_HAS(exl3_expert_record, 80);
+AB_RECORD_HAS(expert_job_record, 96);
+AB_RECORD_HAS(expert_row_sum_arguments, 24);
+AB_RECORD_HAS(bb_exl3_shard_activation_record, 96);
+AB_RECORD_HAS(exl3_moe_record, 104);
+AB_RECORD_HAS(step_block, 16);
+AB_RECORD_HAS(ordered_collective_peer, 32);
+AB_RECORD_HAS(ordered_collective_arguments, 80);
+AB_RECORD_HAS(ordered_reduce_bf16_arguments, 96);
+AB_RECORD_HAS(ordered_row_sum_publish_arguments, 96);
+AB_RECORD_HAS(router_select_b200_arguments, 80);
+
+#endif

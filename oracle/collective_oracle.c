@@ -1,0 +1,149 @@
+/*
+ * collective_oracle.c: CPU restatement of the reference's fixed-order reduction and of the router's conventions.
+ * TEST INFRASTRUCTURE ONLY (see anemone_oracle.h): never linked into or called by the shipped library.
+ */
+#include "anemone_oracle.h"
+
+#include <math.h>
+#include <string.h>
+
+/* source/ordered_collective.c:187-196: sum = +0; for each rank ascending: sum = sum + input[rank][element] */
+void orc_ordered_sum(const float *const *inputs, uint32_t rank_count, uint32_t element_count, float *output)
+{
+	for (uint32_t element = 0; element < element_count; element++) {
+		float sum = 0.0f;
+		for (uint32_t rank = 0; rank < rank_count; rank++)
+			sum = sum + inputs[rank][element];
+		output[element] = sum;
+	}
+}
+
+/* source/kernel_tp_exchange.cu:223-237: the same sum, then one rounding to bfloat16 */
+void orc_ordered_reduce_bf16(const float *const *inputs, uint32_t rank_count, uint32_t element_count,
+			     uint16_t *output)
+{
+	for (uint32_t element = 0; element < element_count; element++) {
+		float sum = 0.0f;
+		for (uint32_t rank = 0; rank < rank_count; rank++)
+			sum = sum + inputs[rank][element];
+		output[element] = orc_bfloat16_bits(sum);
+	}
+}
+
+/* source/ordered_collective.c:144-206. Slices are ceil(n / ranks) elements; reduce-scatter writes only the owner's
+ * output at full-array indices; gather copies slice owner's input. Returns 0, or 1 for arguments it refuses. */
+int orc_ordered_collective(const float *const *inputs, float *const *outputs, uint32_t rank_count,
+			   uint32_t element_count, int operation)
+{
+	if (inputs == NULL || outputs == NULL || rank_count == 0 || rank_count > ORDERED_COLLECTIVE_MAXIMUM_RANKS ||
+	    element_count == 0 || element_count > ORDERED_COLLECTIVE_MAXIMUM_ELEMENTS || operation < 0 ||
+	    operation >= (int)ORDERED_COLLECTIVE_OPERATIONS)
+		return 1;
+	const uint32_t slice = (element_count + rank_count - 1u) / rank_count;
+	for (uint32_t element = 0; element < element_count; element++) {
+		float sum = 0.0f;
+		if (operation == ORDERED_GATHER) {
+			sum = inputs[element / slice][element];
+		} else {
+			for (uint32_t rank = 0; rank < rank_count; rank++)
+				sum = sum + inputs[rank][element];
+		}
+		if (operation == ORDERED_REDUCE_SCATTER) {
+			outputs[element / slice][element] = sum;
+		} else {
+			for (uint32_t rank = 0; rank < rank_count; rank++)
+				outputs[rank][element] = sum;
+		}
+	}
+	return 0;
+}
+
+/* ---------------------------------------------------------------- router */
+
+/* source/kernel_router.cuh:36-46: a float's bits mapped so that unsigned order is numeric order, -0 below +0, a
+ * not-a-number above everything; ties go to the lower expert (its complement is larger). */
+static uint64_t router_key(float score, uint32_t expert)
+{
+	uint32_t bits;
+	memcpy(&bits, &score, sizeof(bits));
+	const uint32_t ordered = score != score ? 0xFFFFFFFFu : (bits & 0x80000000u) ? ~bits : bits | 0x80000000u;
+	return (uint64_t)ordered << 32 | (uint32_t)~expert;
+}
+
+static float router_affinity(float score, uint32_t scoring)
+{
+	if (scoring == ROUTER_SCORING_SQRT_SOFTPLUS) /* include/anemone/router_records.h:10-12 */
+		return sqrtf(score > 20.0f ? score : log1pf(expf(score)));
+	return 1.0f / (1.0f + expf(-score));
+}
+
+void orc_router_row(const float *scores, uint32_t expert_count, uint32_t picks, uint32_t scoring, float route_scale,
+		    uint32_t *experts_out, float *weights_out)
+{
+	uint64_t keys[ROUTER_B200_MAXIMUM_EXPERTS];
+	uint32_t chosen[ROUTER_B200_MAXIMUM_PICKS];
+	for (uint32_t expert = 0; expert < expert_count; expert++)
+		keys[expert] = router_key(scores[expert], expert);
+	for (uint32_t pick = 0; pick < picks; pick++) {
+		uint32_t best = 0;
+		for (uint32_t expert = 1; expert < expert_count; expert++)
+			if (keys[expert] > keys[best])
+				best = expert;
+		chosen[pick] = best;
+		keys[best] = 0; /* below every live key */
+	}
+	/* slots in ascending expert order */
+	for (uint32_t pick = 0; pick < picks; pick++) {
+		uint32_t slot = 0;
+		for (uint32_t other = 0; other < picks; other++)
+			slot += chosen[other] < chosen[pick] ? 1u : 0u;
+		experts_out[slot] = chosen[pick];
+	}
+	float sum = 0.0f;
+	for (uint32_t slot = 0; slot < picks; slot++) {
+		weights_out[slot] = router_affinity(scores[experts_out[slot]], scoring);
+		sum += weights_out[slot];
+	}
+	for (uint32_t slot = 0; slot < picks; slot++)
+		weights_out[slot] = weights_out[slot] / (sum + 1e-20f) * route_scale;
+}
+
+uint32_t orc_router_jobs(const uint32_t *experts, const float *weights, uint32_t live_rows, uint32_t picks,
+			 uint32_t expert_count, uint32_t shared_count, const uint64_t *expert_table,
+			 uint32_t job_capacity, struct expert_job_record *jobs_out)
+{
+	const uint32_t pairs_per_row = picks + shared_count;
+	uint32_t job_count = 0;
+	memset(jobs_out, 0, (size_t)job_capacity * sizeof(*jobs_out));
+	for (uint32_t expert = 0; expert < expert_count + shared_count; expert++) {
+		struct expert_job_record *job = NULL;
+		for (uint32_t row = 0; row < live_rows; row++) {
+			uint32_t slot = UINT32_MAX;
+			float weight = 1.0f;
+			if (expert >= expert_count) {
+				slot = picks + (expert - expert_count);
+			} else {
+				for (uint32_t pick = 0; pick < picks; pick++)
+					if (experts[row * picks + pick] == expert) {
+						slot = pick;
+						weight = weights[row * picks + pick];
+					}
+			}
+			if (slot == UINT32_MAX)
+				continue;
+			if (job == NULL || job->row_count == LINEAR_MAXIMUM_ROWS) {
+				if (job_count == job_capacity)
+					return UINT32_MAX;
+				job = &jobs_out[job_count++];
+				job->gate_offset = expert_table[3u * expert];
+				job->up_offset = expert_table[3u * expert + 1u];
+				job->down_offset = expert_table[3u * expert + 2u];
+				job->expert = expert;
+			}
+			job->pair_index[job->row_count] = row * pairs_per_row + slot;
+			job->route_weight[job->row_count] = weight;
+			job->row_count++;
+		}
+	}
+	return job_count;
+}

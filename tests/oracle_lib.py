@@ -1,0 +1,108 @@
+"""ctypes bindings of the CPU oracle (oracle/liboracle.so) and of the reference's own host code (oracle/_ref).
+
+Test infrastructure: only tests, the smoke check and the benchmark's CPU-baseline legs import this module.
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ORACLE_DIR = os.path.join(ROOT, "oracle")
+ORACLE_SO = os.path.join(ORACLE_DIR, "liboracle.so")
+REFERENCE_SO = os.path.join(ORACLE_DIR, "_ref", "libanemone_ref.so")
+
+u8p = C.POINTER(C.c_ubyte)
+u16p = C.POINTER(C.c_uint16)
+u32p = C.POINTER(C.c_uint32)
+u64p = C.POINTER(C.c_uint64)
+f32p = C.POINTER(C.c_float)
+
+
+def ptr(array, kind):
+    return array.ctypes.data_as(kind)
+
+
+def build_oracle():
+    subprocess.run(["make", "-C", ORACLE_DIR, "all"], check=True, capture_output=True)
+
+
+def load_oracle():
+    if not os.path.exists(ORACLE_SO):
+        build_oracle()
+    lib = C.CDLL(ORACLE_SO)
+    lib.orc_half_value.restype = C.c_float
+    lib.orc_half_value.argtypes = [C.c_uint16]
+    lib.orc_half_nearest.restype = C.c_uint16
+    lib.orc_half_nearest.argtypes = [C.c_double]
+    lib.orc_bfloat16_bits.restype = C.c_uint16
+    lib.orc_bfloat16_bits.argtypes = [C.c_float]
+    lib.orc_exl3_codebook.restype = C.c_uint16
+    lib.orc_exl3_codebook.argtypes = [C.c_uint32]
+    lib.orc_exl3_state.restype = C.c_uint16
+    lib.orc_exl3_state.argtypes = [u8p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32]
+    for name in ("orc_exl3_states", "orc_exl3_decode"):
+        getattr(lib, name).restype = None
+        getattr(lib, name).argtypes = [u8p, C.c_uint32, C.c_uint32, C.c_uint32, u16p]
+    lib.orc_exl3_states_digest.restype = C.c_uint64
+    lib.orc_exl3_states_digest.argtypes = [u8p, C.c_uint32, C.c_uint32, C.c_uint32]
+    lib.orc_exl3_slice.restype = C.c_uint64
+    lib.orc_exl3_slice.argtypes = [u8p] + [C.c_uint32] * 7 + [u8p]
+    lib.orc_hadamard128.restype = None
+    lib.orc_hadamard128.argtypes = [f32p]
+    lib.orc_exl3_experts.restype = None
+    lib.orc_exl3_experts.argtypes = [C.c_void_p, u8p, u32p, C.c_uint32]
+    lib.orc_exl3_row_sum.restype = None
+    lib.orc_exl3_row_sum.argtypes = [C.c_void_p, C.c_uint32, u8p]
+    lib.orc_ordered_sum.restype = None
+    lib.orc_ordered_sum.argtypes = [C.POINTER(f32p), C.c_uint32, C.c_uint32, f32p]
+    lib.orc_ordered_reduce_bf16.restype = None
+    lib.orc_ordered_reduce_bf16.argtypes = [C.POINTER(f32p), C.c_uint32, C.c_uint32, u16p]
+    lib.orc_ordered_collective.restype = C.c_int
+    lib.orc_ordered_collective.argtypes = [C.POINTER(f32p), C.POINTER(f32p), C.c_uint32, C.c_uint32, C.c_int]
+    lib.orc_router_row.restype = None
+    lib.orc_router_row.argtypes = [f32p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_float, u32p, f32p]
+    lib.orc_router_jobs.restype = C.c_uint32
+    lib.orc_router_jobs.argtypes = [u32p, f32p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, u64p, C.c_uint32,
+                                    C.c_void_p]
+    return lib
+
+
+def load_reference():
+    if not os.path.exists(REFERENCE_SO):
+        return None
+    lib = C.CDLL(REFERENCE_SO)
+    lib.test_exl3_codebook.restype = C.c_uint16
+    lib.test_exl3_codebook.argtypes = [C.c_uint32]
+    lib.test_exl3_position.restype = C.c_uint32
+    lib.test_exl3_position.argtypes = [C.c_uint32, C.c_uint32]
+    lib.test_exl3_state.restype = C.c_uint16
+    lib.test_exl3_state.argtypes = [u8p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32]
+    lib.test_exl3_reconstruct.restype = C.c_uint16
+    lib.test_exl3_reconstruct.argtypes = [u8p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32]
+    lib.ordered_collective_host.restype = C.c_int
+    lib.ordered_collective_host.argtypes = [C.POINTER(f32p), C.POINTER(f32p), C.c_uint32, C.c_uint32, C.c_int]
+    return lib
+
+
+def pointer_array(arrays, kind=f32p):
+    """A C array of pointers to the rows of `arrays` (numpy arrays kept alive by the caller)."""
+    holder = (kind * len(arrays))()
+    for index, array in enumerate(arrays):
+        holder[index] = ptr(array, kind)
+    return holder
+
+
+def splitmix_words(seed, count):
+    """The 32-bit words of the splitmix64 stream the reference's known-answer test draws its tiles from."""
+    mask = (1 << 64) - 1
+    state = seed & mask
+    out = np.empty(count, dtype=np.uint32)
+    for index in range(count):
+        state = (state + 0x9E3779B97F4A7C15) & mask
+        mixed = state
+        mixed = ((mixed ^ (mixed >> 30)) * 0xBF58476D1CE4E5B9) & mask
+        mixed = ((mixed ^ (mixed >> 27)) * 0x94D049BB133111EB) & mask
+        out[index] = (mixed ^ (mixed >> 31)) & 0xFFFFFFFF
+    return out
