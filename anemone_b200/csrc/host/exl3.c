@@ -1,0 +1,250 @@
+/*
+ * exl3.c: EXL3 format sizes and the load-time preparation of the expert launches (anemone_b200_exl3.h).
+ * Takes the place of the reference's source/exl3.c: same entry points, same validation and refusals, same records;
+ * the kernels behind the names and therefore the launch shapes are this library's.
+ */
+#include "anemone_b200_exl3.h"
+
+#include <math.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "../kernels/exl3_geometry.h"
+#include "prepare_common.h"
+
+#define EXL3_MAXIMUM_GRID_ROWS 65535u
+#define EXL3_OPERAND_BYTES_PER_INPUT 4u /* FP16, gate and up */
+#define EXL3_PRODUCT_BYTES_PER_INPUT 8u /* FP32, gate and up (inner <= input) */
+
+static result_status exl3_stored_byte_count(const struct matrix_shape_record *shape, uint64_t *byte_count_out)
+{
+	if (shape == NULL || byte_count_out == NULL || shape->reserved_must_be_zero != 0 || shape->input_size == 0 ||
+	    shape->output_size == 0 || shape->input_size % EXL3_TRANSFORM != 0 ||
+	    shape->output_size % EXL3_TRANSFORM != 0 || exl3_bits_x2(shape->bits_per_weight) == 0)
+		return STATUS_INVALID_ARGUMENT;
+	if (!exl3_width_supported(shape->bits_per_weight))
+		return STATUS_UNSUPPORTED;
+	*byte_count_out = exl3_matrix_bytes(shape->input_size, shape->output_size, exl3_bits_x2(shape->bits_per_weight));
+	return STATUS_OK;
+}
+
+const struct weight_format_operations exl3_weight_operations = { .name = "exl3_mul1",
+								  .stored_byte_count = exl3_stored_byte_count };
+
+const char *exl3_width_name(uint32_t bits_x2)
+{
+	switch (bits_x2) {
+	case EXL3_BITS_X2_K2:
+		return "k2";
+	case EXL3_BITS_X2_K2_5:
+		return "k2_5";
+	case EXL3_BITS_X2_K3:
+		return "k3";
+	case EXL3_BITS_X2_K4:
+		return "k4";
+	default:
+		return NULL;
+	}
+}
+
+static bool range_inside(uint64_t offset, uint64_t bytes, uint64_t capacity)
+{
+	return offset <= capacity && bytes <= capacity - offset;
+}
+
+result_status exl3_reconstruct_prepare(const struct exl3_reconstruct_record *record, uint64_t arena_byte_count,
+				       uint32_t kernel, struct kernel_launch *launch_out)
+{
+	if (record == NULL || launch_out == NULL || kernel == BACKEND_NO_KERNEL || record->reserved_zero != 0)
+		return STATUS_INVALID_ARGUMENT;
+	const struct matrix_shape_record shape = { record->output_size, record->input_size, record->bits_per_weight, 0 };
+	uint64_t matrix_bytes = 0;
+	if (exl3_stored_byte_count(&shape, &matrix_bytes) != STATUS_OK)
+		return STATUS_INVALID_ARGUMENT;
+	const uint64_t values = (uint64_t)record->input_size * record->output_size;
+	const uint64_t output_bytes = values * EXL3_HALF_BYTES;
+	if (record->matrix_offset % WEIGHT_FORMAT_MATRIX_ALIGNMENT_BYTES != 0 ||
+	    record->output_offset % WEIGHT_FORMAT_MATRIX_ALIGNMENT_BYTES != 0 ||
+	    !range_inside(record->matrix_offset, matrix_bytes, arena_byte_count) ||
+	    !range_inside(record->output_offset, output_bytes, arena_byte_count) ||
+	    (record->matrix_offset < record->output_offset + output_bytes &&
+	     record->output_offset < record->matrix_offset + matrix_bytes) ||
+	    values / EXL3_RECONSTRUCT_THREADS > UINT32_MAX)
+		return STATUS_INVALID_ARGUMENT;
+	prepare_launch_fill(launch_out, kernel,
+			    (uint32_t)((values + EXL3_RECONSTRUCT_THREADS - 1u) / EXL3_RECONSTRUCT_THREADS), 1, 1,
+			    EXL3_RECONSTRUCT_THREADS, 0, record, sizeof(*record));
+	return STATUS_OK;
+}
+
+uint64_t exl3_scratch_byte_count(uint32_t pair_count, uint32_t input_size)
+{
+	const uint64_t values = (uint64_t)pair_count * input_size;
+	const uint64_t per_input = EXL3_OPERAND_BYTES_PER_INPUT + EXL3_PRODUCT_BYTES_PER_INPUT;
+	return values > UINT64_MAX / per_input ? UINT64_MAX : values * per_input;
+}
+
+/* What every chain shares: the record's own consistency and its five ranges. width_known: the record carries one
+ * stored width (else widths come from a table and the widest supported shape is assumed for nothing: matrices are
+ * placed by the router's table, which this function does not see). */
+static result_status chain_validate(const char *what, const struct exl3_expert_record *record,
+				    uint64_t arena_byte_count, bool width_known, const struct checked_range *extra,
+				    uint32_t extra_count)
+{
+	if (record->reserved_zero != 0 || record->pair_count == 0 || record->pairs_per_row == 0 ||
+	    record->pair_count % record->pairs_per_row != 0 || record->output_offset != record->products_offset ||
+	    record->job_count == 0 || record->job_count > EXL3_MAXIMUM_GRID_ROWS ||
+	    record->inner_size > record->input_size || !isfinite(record->activation_limit) ||
+	    record->activation_limit <= 0)
+		return STATUS_INVALID_ARGUMENT;
+	const struct matrix_shape_record shape = { record->inner_size, record->input_size,
+						   width_known ? record->bits_per_weight : EXL3_K4, 0 };
+	uint64_t bytes = 0;
+	if (exl3_stored_byte_count(&shape, &bytes) != STATUS_OK)
+		return STATUS_INVALID_ARGUMENT;
+	const uint64_t inputs = (uint64_t)record->pair_count * record->input_size;
+	if (inputs > UINT64_MAX / (EXL3_OPERAND_BYTES_PER_INPUT + EXL3_PRODUCT_BYTES_PER_INPUT))
+		return STATUS_INVALID_ARGUMENT;
+	struct checked_range ranges[8] = {
+		{ "jobs", record->jobs_offset, (uint64_t)record->job_count * sizeof(struct expert_job_record) },
+		{ "input", record->input_offset, inputs / record->pairs_per_row * EXL3_HALF_BYTES },
+		{ "operands", record->operands_offset, inputs * EXL3_OPERAND_BYTES_PER_INPUT },
+		{ "products", record->products_offset, inputs * EXL3_PRODUCT_BYTES_PER_INPUT },
+		{ "hidden", record->hidden_offset, (uint64_t)record->pair_count * record->inner_size * EXL3_HALF_BYTES }
+	};
+	uint32_t count = 5;
+	for (uint32_t index = 0; index < extra_count; index++)
+		ranges[count++] = extra[index];
+	return prepare_ranges_are_valid(what, ranges, count, arena_byte_count) ? STATUS_OK : STATUS_INVALID_ARGUMENT;
+}
+
+static uint32_t transform_grid(uint32_t width)
+{
+	return (width / EXL3_TRANSFORM + EXL3_TRANSFORM_WARPS - 1u) / EXL3_TRANSFORM_WARPS;
+}
+
+static result_status class_check(uint32_t arithmetic_class)
+{
+	if (arithmetic_class == ARITHMETIC_CLASS_SM_100)
+		return STATUS_OK;
+	if (arithmetic_class == ARITHMETIC_CLASS_SM_80 || arithmetic_class == ARITHMETIC_CLASS_SM_120 ||
+	    arithmetic_class == ARITHMETIC_CLASS_SM_120_NATIVE)
+		return STATUS_UNSUPPORTED; /* the reference's classes: this library has no build for them */
+	return STATUS_INVALID_ARGUMENT;
+}
+
+result_status exl3_experts_prepare(const struct exl3_expert_record *record, uint64_t arena_byte_count,
+				   const struct backend_operations *backend, struct device_card *card,
+				   uint32_t arithmetic_class, struct kernel_launch *launches_out)
+{
+	if (record == NULL || backend == NULL || card == NULL || launches_out == NULL ||
+	    backend->kernel_prepare == NULL)
+		return STATUS_INVALID_ARGUMENT;
+	result_status status = class_check(arithmetic_class);
+	if (status == STATUS_INVALID_ARGUMENT)
+		return status;
+	const result_status valid = chain_validate("EXL3 experts", record, arena_byte_count, true, NULL, 0);
+	if (valid != STATUS_OK)
+		return valid;
+	if (status != STATUS_OK)
+		return status;
+	const uint32_t bits_x2 = exl3_bits_x2(record->bits_per_weight);
+	const char *const width = exl3_width_name(bits_x2);
+	char gate_up[64], down[64];
+	if (width == NULL || snprintf(gate_up, sizeof(gate_up), "exl3_gate_up_%s", width) <= 0 ||
+	    snprintf(down, sizeof(down), "exl3_down_%s", width) <= 0)
+		return STATUS_INVALID_ARGUMENT;
+	const char *const names[EXL3_EXPERT_LAUNCHES] = { "exl3_input", gate_up, "exl3_activate", down, "exl3_finish" };
+	const uint32_t H = record->input_size, I = record->inner_size, jobs = record->job_count;
+	const uint32_t shared = exl3_product_dynamic_bytes(bits_x2);
+	const struct {
+		uint32_t x, z, threads, shared;
+	} shapes[EXL3_EXPERT_LAUNCHES] = { { transform_grid(H), EXL3_PROJECTIONS, EXL3_TRANSFORM_THREADS, 0 },
+					   { I / EXL3_TRANSFORM, EXL3_PROJECTIONS, EXL3_PRODUCT_THREADS, shared },
+					   { transform_grid(I), 1, EXL3_TRANSFORM_THREADS, 0 },
+					   { H / EXL3_TRANSFORM, 1, EXL3_PRODUCT_THREADS, shared },
+					   { transform_grid(H), 1, EXL3_TRANSFORM_THREADS, 0 } };
+	struct kernel_launch launches[EXL3_EXPERT_LAUNCHES];
+	for (uint32_t index = 0; index < EXL3_EXPERT_LAUNCHES; index++) {
+		uint32_t kernel = BACKEND_NO_KERNEL;
+		status = backend->kernel_prepare(card, EXL3_KERNEL_FILE, names[index], sizeof(*record), &kernel);
+		if (status != STATUS_OK)
+			return status;
+		if (kernel == BACKEND_NO_KERNEL)
+			return STATUS_UNSUPPORTED;
+		prepare_launch_fill(&launches[index], kernel, shapes[index].x, jobs, shapes[index].z,
+				    shapes[index].threads, shapes[index].shared, record, sizeof(*record));
+	}
+	memcpy(launches_out, launches, sizeof(launches));
+	return STATUS_OK;
+}
+
+result_status exl3_experts_fast_prepare(const struct exl3_expert_record *record, uint64_t arena_byte_count,
+					const struct backend_operations *backend, struct device_card *card,
+					uint32_t arithmetic_class, struct kernel_launch *launches_out)
+{
+	return exl3_experts_prepare(record, arena_byte_count, backend, card, arithmetic_class, launches_out);
+}
+
+result_status exl3_experts_relaxed_prepare(const struct exl3_expert_record *record, uint64_t arena_byte_count,
+					   const struct backend_operations *backend, struct device_card *card,
+					   uint32_t arithmetic_class, struct kernel_launch *launches_out)
+{
+	if (record == NULL || backend == NULL || card == NULL || launches_out == NULL ||
+	    backend->kernel_prepare == NULL || class_check(arithmetic_class) == STATUS_INVALID_ARGUMENT)
+		return STATUS_INVALID_ARGUMENT;
+	const result_status valid = chain_validate("EXL3 experts", record, arena_byte_count, true, NULL, 0);
+	return valid != STATUS_OK ? valid : STATUS_UNSUPPORTED;
+}
+
+result_status exl3_moe_prepare(const struct exl3_moe_record *record, uint64_t arena_byte_count,
+			       const struct backend_operations *backend, struct device_card *card,
+			       struct kernel_launch *launches_out)
+{
+	if (record == NULL || backend == NULL || card == NULL || launches_out == NULL ||
+	    backend->kernel_prepare == NULL || record->reserved_zero != 0 || record->expert_count == 0)
+		return STATUS_INVALID_ARGUMENT;
+	const struct exl3_expert_record *const base = &record->base;
+	const bool per_expert = base->bits_per_weight == EXL3_WIDTH_PER_EXPERT;
+	const uint64_t rows = base->pairs_per_row == 0 ? 0 : base->pair_count / base->pairs_per_row;
+	/* the fused gate/up launch writes the down operands while other CTAs still read the gate/up operands, so they
+	 * live behind them: FP16 [pair][inner] at operands_offset + 4 pair_count input_size */
+	const uint64_t gate_up_operand_bytes = (uint64_t)base->pair_count * base->input_size * EXL3_OPERAND_BYTES_PER_INPUT;
+	const struct checked_range extra[3] = {
+		{ "row output", record->row_output_offset, rows * base->input_size * 4u },
+		{ "width table", record->widths_offset, per_expert ? (uint64_t)record->expert_count * 4u : 0u },
+		{ "down operands", base->operands_offset + gate_up_operand_bytes,
+		  (uint64_t)base->pair_count * base->inner_size * EXL3_HALF_BYTES }
+	};
+	if (base->operands_offset > UINT64_MAX - gate_up_operand_bytes)
+		return STATUS_INVALID_ARGUMENT;
+	const result_status valid = chain_validate("EXL3 MoE", base, arena_byte_count, !per_expert, extra, 3);
+	if (valid != STATUS_OK)
+		return valid;
+	static const char *const names[EXL3_MOE_LAUNCHES] = { "exl3_moe_input", "exl3_moe_gate_up", "exl3_moe_down",
+							      "exl3_moe_row_sum" };
+	const uint32_t H = base->input_size, I = base->inner_size, jobs = base->job_count;
+	const uint32_t shared =
+		exl3_product_dynamic_bytes(per_expert ? EXL3_BITS_X2_K4 : exl3_bits_x2(base->bits_per_weight));
+	const struct {
+		uint32_t x, y, z, threads, shared;
+	} shapes[EXL3_MOE_LAUNCHES] = { { transform_grid(H), jobs, EXL3_PROJECTIONS, EXL3_TRANSFORM_THREADS, 0 },
+					{ I / EXL3_TRANSFORM, jobs, 1, EXL3_PRODUCT_THREADS, shared },
+					{ H / EXL3_TRANSFORM, jobs, 1, EXL3_PRODUCT_THREADS, shared },
+					{ (H + EXL3_ROW_SUM_THREADS - 1u) / EXL3_ROW_SUM_THREADS, (uint32_t)rows, 1,
+					  EXL3_ROW_SUM_THREADS, 0 } };
+	struct kernel_launch launches[EXL3_MOE_LAUNCHES];
+	for (uint32_t index = 0; index < EXL3_MOE_LAUNCHES; index++) {
+		uint32_t kernel = BACKEND_NO_KERNEL;
+		const result_status status =
+			backend->kernel_prepare(card, EXL3_MOE_KERNEL_FILE, names[index], sizeof(*record), &kernel);
+		if (status != STATUS_OK)
+			return status;
+		if (kernel == BACKEND_NO_KERNEL)
+			return STATUS_UNSUPPORTED;
+		prepare_launch_fill(&launches[index], kernel, shapes[index].x, shapes[index].y, shapes[index].z,
+				    shapes[index].threads, shapes[index].shared, record, sizeof(*record));
+	}
+	memcpy(launches_out, launches, sizeof(launches));
+	return STATUS_OK;
+}

@@ -1,0 +1,313 @@
+/*
+ * exl3_device.cuh: device building blocks of the EXL3 expert kernels for sm_100a.
+ *
+ *   - trellis decode of a lane's eight weights of a 16 x 16 tile straight into the A-fragment registers of
+ *     mma.sync.m16n8k16 (the stream order of the format IS that fragment order);
+ *   - the 128-point Hadamard butterfly on one warp, four values a lane, in the stage order of the reference's
+ *     transform (source/kernel_exl3.cu:104-124), so the FP32 bits are the same;
+ *   - a product core: one CTA computes 128 outputs of one job for up to eight rows. The CTA's trellis rows arrive
+ *     through a ring of shared-memory stages filled by bulk asynchronous copies (cp.async.bulk, completion on an
+ *     mbarrier); four warps take interleaved K steps, decode in registers and accumulate in FP32 on the tensor cores;
+ *     the four partial sums are added in warp order from +0.
+ *
+ * Every mbarrier wait is bounded: a wait that runs out raises exl3_wait_expired (a module global the host can read)
+ * and the CTA leaves without touching its outputs; nothing traps.
+ */
+#ifndef AB_EXL3_DEVICE_CUH
+#define AB_EXL3_DEVICE_CUH
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+#include "exl3_geometry.h"
+
+#define EXL3_WAIT_POLLS (1u << 22) /* of ~100 ns each with the back-off below: well under a second */
+
+__device__ unsigned int exl3_wait_expired;
+
+/* ------------------------------------------------------------------ mbarrier and bulk copy (PTX) */
+
+__device__ __forceinline__ uint32_t smem_address(const void *pointer)
+{
+	return (uint32_t)__cvta_generic_to_shared(pointer);
+}
+
+__device__ __forceinline__ void barrier_init(uint64_t *barrier, uint32_t arrivals)
+{
+	asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_address(barrier)), "r"(arrivals) : "memory");
+}
+
+__device__ __forceinline__ void barrier_invalidate(uint64_t *barrier)
+{
+	asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(smem_address(barrier)) : "memory");
+}
+
+__device__ __forceinline__ void barrier_expect(uint64_t *barrier, uint32_t bytes)
+{
+	asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_address(barrier)), "r"(bytes)
+		     : "memory");
+}
+
+__device__ __forceinline__ void barrier_arrive(uint64_t *barrier)
+{
+	asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_address(barrier)) : "memory");
+}
+
+/* true once the phase of the given parity has completed; false if the bounded wait ran out */
+__device__ __forceinline__ bool barrier_wait(uint64_t *barrier, uint32_t parity)
+{
+	const uint32_t address = smem_address(barrier);
+	for (uint32_t poll = 0; poll < EXL3_WAIT_POLLS; poll++) {
+		uint32_t complete;
+		asm volatile("{\n\t.reg .pred p;\n\t"
+			     "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+			     "selp.u32 %0, 1, 0, p;\n\t}"
+			     : "=r"(complete)
+			     : "r"(address), "r"(parity)
+			     : "memory");
+		if (complete != 0)
+			return true;
+		if (poll > 64)
+			__nanosleep(64);
+	}
+	atomicExch(&exl3_wait_expired, 1u);
+	return false;
+}
+
+/* bytes a multiple of 16, both addresses 16-byte aligned; completes `bytes` of the barrier's transaction count */
+__device__ __forceinline__ void bulk_load(void *shared_destination, const void *global_source, uint32_t bytes,
+					  uint64_t *barrier)
+{
+	asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+			     smem_address(shared_destination)),
+		     "l"(global_source), "r"(bytes), "r"(smem_address(barrier))
+		     : "memory");
+}
+
+/* ------------------------------------------------------------------ decode */
+
+template <uint32_t BX2> struct exl3_ring {
+	static constexpr uint32_t ring_bits = 128u * BX2;
+	static constexpr uint32_t words = ring_bits / 32u;
+	static constexpr uint32_t tile_bytes = ring_bits / 8u;
+	/* bits from the start of the lane's first window to the start of the window of its symbol e */
+	__host__ __device__ static constexpr uint32_t offset(uint32_t e)
+	{
+		return (((e + 1u) * BX2) >> 1) - (BX2 >> 1);
+	}
+	/* ring bit where lane l's first window starts */
+	__host__ __device__ static constexpr uint32_t begin(uint32_t lane)
+	{
+		return ((((8u * lane + 1u) * BX2) >> 1) + ring_bits - 16u) % ring_bits;
+	}
+};
+
+/* FP16 bits (in the low half) of a state: dp4a sums the four bytes of state * multiplier onto 0x6400 */
+__device__ __forceinline__ uint32_t exl3_value_bits(uint32_t state)
+{
+	return __dp4a(state * EXL3_MUL1_MULTIPLIER, 0x01010101u, EXL3_MUL1_BASE);
+}
+
+__device__ __forceinline__ uint32_t exl3_pair(uint32_t low_state, uint32_t high_state)
+{
+	const uint32_t packed = __byte_perm(exl3_value_bits(low_state), exl3_value_bits(high_state), 0x5410);
+	const __half2 scale = __halves2half2(__ushort_as_half(EXL3_MUL1_SCALE), __ushort_as_half(EXL3_MUL1_SCALE));
+	const __half2 bias = __halves2half2(__ushort_as_half(EXL3_MUL1_BIAS), __ushort_as_half(EXL3_MUL1_BIAS));
+	const __half2 value = __hfma2(*reinterpret_cast<const __half2 *>(&packed), scale, bias);
+	return *reinterpret_cast<const uint32_t *>(&value);
+}
+
+/* state of the lane's symbol e from its two ring words, already shifted so that its first window starts at the top */
+template <uint32_t BX2>
+__device__ __forceinline__ uint32_t exl3_state_of(uint32_t high, uint32_t low, uint32_t e)
+{
+	const uint32_t offset = exl3_ring<BX2>::offset(e);
+	if (offset == 0u)
+		return high >> 16;
+	if (offset <= 16u)
+		return (high >> (16u - offset)) & 0xFFFFu;
+	return __funnelshift_r(low, high, 48u - offset) & 0xFFFFu;
+}
+
+/* The four A registers of m16n8k16 for one tile: symbols {0,1}, {4,5}, {2,3}, {6,7} of the lane. */
+template <uint32_t BX2>
+__device__ __forceinline__ void exl3_decode_fragment(uint32_t word0, uint32_t word1, uint32_t shift,
+						      uint32_t fragment[4])
+{
+	const uint32_t high = __funnelshift_l(word1, word0, shift);
+	const uint32_t low = word1 << shift;
+	fragment[0] = exl3_pair(exl3_state_of<BX2>(high, low, 0), exl3_state_of<BX2>(high, low, 1));
+	fragment[1] = exl3_pair(exl3_state_of<BX2>(high, low, 4), exl3_state_of<BX2>(high, low, 5));
+	fragment[2] = exl3_pair(exl3_state_of<BX2>(high, low, 2), exl3_state_of<BX2>(high, low, 3));
+	fragment[3] = exl3_pair(exl3_state_of<BX2>(high, low, 6), exl3_state_of<BX2>(high, low, 7));
+}
+
+__device__ __forceinline__ void mma_f16(float accumulator[4], const uint32_t a[4], uint32_t b0, uint32_t b1)
+{
+	asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+		     "{%0,%1,%2,%3};"
+		     : "+f"(accumulator[0]), "+f"(accumulator[1]), "+f"(accumulator[2]), "+f"(accumulator[3])
+		     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+/* ------------------------------------------------------------------ Hadamard, one warp, values 4 lane + i */
+
+__device__ __forceinline__ void hadamard128_warp(float v[4], uint32_t lane)
+{
+	/* strides 1 and 2 inside the lane */
+	float a = __fadd_rn(v[0], v[1]), b = __fsub_rn(v[0], v[1]);
+	float c = __fadd_rn(v[2], v[3]), d = __fsub_rn(v[2], v[3]);
+	v[0] = __fadd_rn(a, c);
+	v[1] = __fadd_rn(b, d);
+	v[2] = __fsub_rn(a, c);
+	v[3] = __fsub_rn(b, d);
+	/* strides 4 .. 64 across lanes: the lower partner takes a + b, the upper one (lower - upper) */
+#pragma unroll
+	for (uint32_t distance = 1; distance < EXL3_WARP; distance <<= 1) {
+		const bool upper = (lane & distance) != 0;
+#pragma unroll
+		for (uint32_t i = 0; i < 4; i++) {
+			const float other = __shfl_xor_sync(0xFFFFFFFFu, v[i], distance);
+			v[i] = upper ? __fsub_rn(other, v[i]) : __fadd_rn(v[i], other);
+		}
+	}
+}
+
+/* ------------------------------------------------------------------ the product core */
+
+struct exl3_product_shared {
+	uint64_t full[EXL3_STAGES];
+	uint64_t empty[EXL3_STAGES];
+	uint32_t failed;
+};
+
+/* Dynamic shared memory of a product CTA (exl3_geometry.h): the stage ring, then (aliased onto it after the K loop)
+ * the warps' partial sums; the barriers live in static shared memory. */
+
+/* sums[tile][c]: this thread's share of the CTA's 128 outputs x 8 columns after the cross-warp reduction: thread
+ * (warp w, lane (g, t)) returns, for tiles j = 2 w and 2 w + 1, the m16n8 accumulator layout
+ *   c0: (output 16 j + g, column 2 t)   c1: (16 j + g, 2 t + 1)   c2: (16 j + g + 8, 2 t)   c3: (16 j + g + 8, 2 t + 1).
+ * matrix: the codes of an inputs x outputs matrix; group: which 128 outputs; operands[column]: FP16 [inputs] of the
+ * column's pair (columns beyond row_count repeat column 0 and are ignored by the caller).
+ * Returns false if a bounded wait expired (the caller then stores nothing). All 128 threads call it. */
+template <uint32_t BX2>
+__device__ __forceinline__ bool exl3_product_core(const unsigned char *matrix, uint32_t inputs, uint32_t outputs,
+						  uint32_t group, const __half *const operand_row,
+						  unsigned char *dynamic_shared, exl3_product_shared *shared,
+						  float sums[2][4])
+{
+	typedef exl3_ring<BX2> ring;
+	constexpr uint32_t row_bytes = EXL3_GROUP_TILES * ring::tile_bytes; /* the CTA's part of one tile row */
+	constexpr uint32_t stage_bytes = EXL3_STAGE_STEPS * row_bytes;
+	const uint32_t lane = threadIdx.x % EXL3_WARP, warp = threadIdx.x / EXL3_WARP;
+	const uint32_t steps = inputs / EXL3_TILE, rounds = steps / EXL3_STAGE_STEPS;
+	const uint64_t matrix_row_bytes = (uint64_t)(outputs / EXL3_TILE) * ring::tile_bytes;
+	const unsigned char *const source = matrix + (uint64_t)group * row_bytes;
+
+	if (threadIdx.x == 0) {
+		for (uint32_t stage = 0; stage < EXL3_STAGES; stage++) {
+			barrier_init(&shared->full[stage], 1);
+			barrier_init(&shared->empty[stage], EXL3_PRODUCT_WARPS);
+		}
+		shared->failed = 0;
+		asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+	}
+	__syncthreads();
+
+	/* warp 0 fills: lane s < 8 copies tile row s of a stage */
+	auto fill = [&](uint32_t round) {
+		const uint32_t stage = round % EXL3_STAGES;
+		if (lane == 0)
+			barrier_expect(&shared->full[stage], stage_bytes);
+		__syncwarp();
+		if (lane < EXL3_STAGE_STEPS)
+			bulk_load(dynamic_shared + stage * stage_bytes + lane * row_bytes,
+				  source + (uint64_t)(round * EXL3_STAGE_STEPS + lane) * matrix_row_bytes, row_bytes,
+				  &shared->full[stage]);
+	};
+	if (warp == 0)
+		for (uint32_t round = 0; round < EXL3_STAGES && round < rounds; round++)
+			fill(round);
+
+	const uint32_t begin = ring::begin(lane);
+	const uint32_t word_index = begin / 32u, shift = begin % 32u, next_index = (word_index + 1u) % ring::words;
+	const uint32_t place = lane % 4u;
+	float accumulators[EXL3_GROUP_TILES][4];
+#pragma unroll
+	for (uint32_t tile = 0; tile < EXL3_GROUP_TILES; tile++)
+#pragma unroll
+		for (uint32_t c = 0; c < 4; c++)
+			accumulators[tile][c] = 0.0f;
+
+	bool alive = true;
+	for (uint32_t round = 0; round < rounds && alive; round++) {
+		const uint32_t stage = round % EXL3_STAGES, use = round / EXL3_STAGES;
+		if (warp == 0 && round >= 1 && round - 1u + EXL3_STAGES < rounds) {
+			/* the slot of the previous round is free once all four warps have read it */
+			if (barrier_wait(&shared->empty[(round - 1u) % EXL3_STAGES], ((round - 1u) / EXL3_STAGES) & 1u))
+				fill(round - 1u + EXL3_STAGES);
+			else
+				shared->failed = 1;
+		}
+		if (!barrier_wait(&shared->full[stage], use & 1u)) {
+			shared->failed = 1;
+			alive = false;
+			break;
+		}
+		const unsigned char *const rows = dynamic_shared + stage * stage_bytes;
+#pragma unroll
+		for (uint32_t turn = 0; turn < EXL3_STAGE_STEPS / EXL3_PRODUCT_WARPS; turn++) {
+			const uint32_t row = warp * (EXL3_STAGE_STEPS / EXL3_PRODUCT_WARPS) + turn;
+			const uint32_t step = round * EXL3_STAGE_STEPS + row;
+			const uint32_t *const fed =
+				reinterpret_cast<const uint32_t *>(operand_row + step * EXL3_TILE + place * 2u);
+			const uint32_t b0 = __ldg(fed), b1 = __ldg(fed + 4);
+			const uint32_t *const words = reinterpret_cast<const uint32_t *>(rows + row * row_bytes);
+#pragma unroll
+			for (uint32_t tile = 0; tile < EXL3_GROUP_TILES; tile++) {
+				uint32_t fragment[4];
+				exl3_decode_fragment<BX2>(words[tile * ring::words + word_index],
+							  words[tile * ring::words + next_index], shift, fragment);
+				mma_f16(accumulators[tile], fragment, b0, b1);
+			}
+		}
+		__syncwarp();
+		if (lane == 0)
+			barrier_arrive(&shared->empty[stage]);
+	}
+	__syncthreads(); /* every read of the ring is done: its memory now holds the partial sums */
+	if (shared->failed != 0)
+		return false;
+	float4 *const partial = reinterpret_cast<float4 *>(dynamic_shared); /* [warp][tile][lane] */
+#pragma unroll
+	for (uint32_t tile = 0; tile < EXL3_GROUP_TILES; tile++)
+		partial[(warp * EXL3_GROUP_TILES + tile) * EXL3_WARP + lane] = make_float4(
+			accumulators[tile][0], accumulators[tile][1], accumulators[tile][2], accumulators[tile][3]);
+	__syncthreads();
+#pragma unroll
+	for (uint32_t mine = 0; mine < 2; mine++) {
+		const uint32_t tile = warp * 2u + mine;
+		float total[4] = { 0.0f, 0.0f, 0.0f, 0.0f };
+#pragma unroll
+		for (uint32_t slice = 0; slice < EXL3_PRODUCT_WARPS; slice++) {
+			const float4 part = partial[(slice * EXL3_GROUP_TILES + tile) * EXL3_WARP + lane];
+			total[0] = __fadd_rn(total[0], part.x);
+			total[1] = __fadd_rn(total[1], part.y);
+			total[2] = __fadd_rn(total[2], part.z);
+			total[3] = __fadd_rn(total[3], part.w);
+		}
+#pragma unroll
+		for (uint32_t c = 0; c < 4; c++)
+			sums[mine][c] = total[c];
+	}
+	__syncthreads(); /* the partial sums are consumed: the caller may reuse the dynamic shared memory */
+	if (threadIdx.x == 0) /* a CTA may run the core again (gate, then up): leave no live barrier behind */
+		for (uint32_t stage = 0; stage < EXL3_STAGES; stage++) {
+			barrier_invalidate(&shared->full[stage]);
+			barrier_invalidate(&shared->empty[stage]);
+		}
+	return true;
+}
+
+#endif

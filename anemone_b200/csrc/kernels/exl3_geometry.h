@@ -1,0 +1,36 @@
+/*
+ * exl3_geometry.h: launch geometry the EXL3 kernels and the host preparers must agree on. C11 and CUDA.
+ */
+#ifndef AB_EXL3_GEOMETRY_H
+#define AB_EXL3_GEOMETRY_H
+
+#include "anemone_b200_records.h"
+
+#define EXL3_WARP 32u
+#define EXL3_PRODUCT_WARPS 4u
+#define EXL3_PRODUCT_THREADS (EXL3_PRODUCT_WARPS * EXL3_WARP)
+#define EXL3_GROUP_TILES 8u /* adjacent output tiles of a product CTA: 128 outputs, one Hadamard block */
+#define EXL3_STAGE_STEPS 8u /* K steps (tile rows) of one pipeline stage: two a warp */
+#define EXL3_STAGES 6u
+#define EXL3_TRANSFORM_WARPS 4u /* a transform CTA: one warp per 128-channel block */
+#define EXL3_TRANSFORM_THREADS (EXL3_TRANSFORM_WARPS * EXL3_WARP)
+#define EXL3_RECONSTRUCT_THREADS 256u
+#define EXL3_ROW_SUM_THREADS 128u
+
+/* bytes of one pipeline stage: EXL3_STAGE_STEPS tile rows of EXL3_GROUP_TILES tiles of 16 bits_x2 bytes */
+AB_INLINE uint32_t exl3_product_stage_bytes(uint32_t bits_x2)
+{
+	return EXL3_STAGE_STEPS * EXL3_GROUP_TILES * 16u * bits_x2;
+}
+
+/* bytes of the cross-warp partial sums that reuse the ring after the K loop: [warp][tile][lane] float4 */
+#define EXL3_PRODUCT_PARTIAL_BYTES (EXL3_PRODUCT_WARPS * EXL3_GROUP_TILES * EXL3_WARP * 16u)
+
+/* Dynamic shared memory of a product CTA for one width; a launch of mixed widths takes the widest (K4). */
+AB_INLINE uint32_t exl3_product_dynamic_bytes(uint32_t bits_x2)
+{
+	const uint32_t ring = EXL3_STAGES * exl3_product_stage_bytes(bits_x2);
+	return ring > EXL3_PRODUCT_PARTIAL_BYTES ? ring : EXL3_PRODUCT_PARTIAL_BYTES;
+}
+
+#endif

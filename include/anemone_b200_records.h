@@ -186,7 +186,10 @@ struct bb_exl3_shard_activation_record {
  * products fused with the output transform and route weight; ordered row sum), with a stored width per expert.
  * base is read exactly as the five-pass chain reads it, except that base.bits_per_weight may be
  * EXL3_WIDTH_PER_EXPERT, in which case expert e's three matrices have stored width widths[e]
- * (uint32 [expert_count] at widths_offset). row_output: FP32 [rows][input_size]. */
+ * (uint32 [expert_count] at widths_offset). row_output: FP32 [rows][input_size]. One layout differs: the FP16 down
+ * operands [pair_count][inner_size] are written BEHIND the gate/up operands, at operands_offset +
+ * 4 pair_count input_size (the fused launch writes them while the gate/up operands are still being read), so the
+ * operands range of this record is 4 pair_count input_size + 2 pair_count inner_size bytes. */
 #define EXL3_MOE_KERNEL_FILE "kernel_exl3_b200"
 #define EXL3_MOE_LAUNCHES 4u
 struct exl3_moe_record {

