@@ -1,0 +1,48 @@
+/* router.c: preparation of router_select_b200 (anemone_b200_router.h). */
+#include "anemone_b200_router.h"
+
+#include <math.h>
+#include <stddef.h>
+
+#include "prepare_common.h"
+
+uint32_t router_b200_job_capacity(uint32_t rows, uint32_t picks, uint32_t shared_count)
+{
+	return rows * picks + shared_count * ((rows + LINEAR_MAXIMUM_ROWS - 1u) / LINEAR_MAXIMUM_ROWS);
+}
+
+result_status router_select_b200_prepare(const struct router_select_b200_arguments *arguments,
+					 uint64_t arena_byte_count, const struct backend_operations *backend,
+					 struct device_card *card, struct kernel_launch *launch_out)
+{
+	if (arguments == NULL || backend == NULL || backend->kernel_prepare == NULL || card == NULL ||
+	    launch_out == NULL || arguments->reserved_zero != 0 || arguments->expert_count == 0 ||
+	    arguments->expert_count + arguments->shared_count > ROUTER_B200_MAXIMUM_EXPERTS ||
+	    arguments->expert_count + arguments->shared_count < arguments->expert_count || arguments->picks == 0 ||
+	    arguments->picks > ROUTER_B200_MAXIMUM_PICKS || arguments->picks > arguments->expert_count ||
+	    arguments->row_capacity == 0 || arguments->row_capacity > ROUTER_B200_MAXIMUM_ROWS ||
+	    arguments->scoring > ROUTER_SCORING_SQRT_SOFTPLUS || !isfinite(arguments->route_scale) ||
+	    arguments->route_scale <= 0 ||
+	    arguments->job_capacity <
+		    router_b200_job_capacity(arguments->row_capacity, arguments->picks, arguments->shared_count))
+		return STATUS_INVALID_ARGUMENT;
+	const uint64_t rows = arguments->row_capacity;
+	const struct checked_range ranges[6] = {
+		{ "scores", arguments->scores_offset, rows * arguments->expert_count * 4u },
+		{ "expert table", arguments->expert_table_offset,
+		  (uint64_t)(arguments->expert_count + arguments->shared_count) * 24u },
+		{ "picks", arguments->picks_offset, rows * arguments->picks * 4u },
+		{ "weights", arguments->weights_offset, rows * arguments->picks * 4u },
+		{ "jobs", arguments->jobs_offset, (uint64_t)arguments->job_capacity * sizeof(struct expert_job_record) },
+		{ "step block", arguments->step_offset, sizeof(struct step_block) }
+	};
+	if (!prepare_ranges_are_valid("router select", ranges, 6, arena_byte_count))
+		return STATUS_INVALID_ARGUMENT;
+	uint32_t kernel = BACKEND_NO_KERNEL;
+	const result_status status = backend->kernel_prepare(card, KERNEL_FILE_ROUTER_B200, KERNEL_ROUTER_SELECT_B200,
+							     sizeof(*arguments), &kernel);
+	if (status != STATUS_OK)
+		return status;
+	prepare_launch_fill(launch_out, kernel, 1, 1, 1, ROUTER_B200_THREADS, 0, arguments, sizeof(*arguments));
+	return STATUS_OK;
+}

@@ -1,0 +1,123 @@
+/*
+ * kernel_ordered_b200.cu: the production reduction of expert partial sums on NVLink (no counterpart file in the
+ * reference; the arithmetic is its owner sums', source/kernel_tp_exchange.cu:190-247: FP32 adds in ascending rank
+ * order from +0, ONE rounding to bfloat16).
+ *
+ *   ordered_row_sum_publish  grid (ceil(width / 512), row capacity) x 128: waits until every rank has finished
+ *       reading this slot's previous use (their DONE lines), writes this rank's FP32 row sums (slots added from +0 in
+ *       ascending order) straight into its input array of the slot, and the last block to finish publishes READY.
+ *   ordered_reduce_bf16      grid (up to 64 blocks) x 256: waits for every rank's READY, pulls every rank's rows by
+ *       128-bit peer loads, adds them in rank order, rounds once, stores bfloat16 [rows][width] at the arena offset
+ *       output_offset; the last block to finish publishes DONE.
+ * Both read the live row count and the sequence from the step block. The read-complete barrier of the FP32
+ * collectives is moved from the end of a step to the next refill of the same slot (two steps later), where it costs
+ * nothing; the slot's input must therefore only ever be written by ordered_row_sum_publish.
+ */
+#include "ordered_device.cuh"
+
+/* true for exactly one block: the last of the grid to arrive. The counter is the owner's own, at `line` + 64. */
+__device__ __forceinline__ bool last_block_of_grid(unsigned char *line, uint32_t *shared_flag)
+{
+	__threadfence_system();
+	__syncthreads();
+	if (threadIdx.x == 0) {
+		unsigned int *const counter = reinterpret_cast<unsigned int *>(line + ORDERED_LOCAL_COUNTER_OFFSET);
+		const unsigned int blocks = gridDim.x * gridDim.y * gridDim.z;
+		const unsigned int arrived = atomicAdd(counter, 1u) + 1u;
+		*shared_flag = arrived == blocks ? 1u : 0u;
+		if (arrived == blocks)
+			*counter = 0u; /* ready for the slot's next use */
+	}
+	__syncthreads();
+	return *shared_flag != 0;
+}
+
+extern "C" __global__ void __launch_bounds__(128)
+	ordered_row_sum_publish(struct ordered_row_sum_publish_arguments arguments, unsigned char *arena)
+{
+	__shared__ uint32_t verdict, last;
+	const struct ordered_collective_arguments &collective = arguments.collective;
+	const struct step_block step = *reinterpret_cast<const struct step_block *>(arena + collective.step_offset);
+	const uint64_t sequence = step.sequence;
+	if (sequence == 0)
+		return;
+	unsigned char *const mine = ordered_slot(collective, arena, collective.rank, sequence);
+	unsigned char *const ready_line = mine + ORDERED_READY_PHASE * ORDERED_COLLECTIVE_LINE_BYTES;
+	/* the slot's previous use must have been read by everyone before it is overwritten */
+	const uint64_t previous = *reinterpret_cast<const uint64_t *>(ready_line + ORDERED_LOCAL_PREVIOUS_OFFSET);
+	bool alive = true;
+	if (previous != 0 && previous < sequence)
+		alive = ordered_wait_all(collective, arena, ORDERED_DONE_PHASE, sequence, previous, false, nullptr, &verdict);
+	const uint32_t row = blockIdx.y;
+	if (alive && row < step.row_count) {
+		const float4 *const pairs = reinterpret_cast<const float4 *>(arena + arguments.pair_output_offset);
+		float4 *const out = reinterpret_cast<float4 *>(mine + collective.input_offset);
+		const uint32_t vectors = arguments.width / 4u;
+		const uint32_t vector = blockIdx.x * blockDim.x + threadIdx.x;
+		if (vector < vectors) {
+			float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+			for (uint32_t slot = 0; slot < arguments.pairs_per_row; slot++) {
+				const float4 value = pairs[((uint64_t)row * arguments.pairs_per_row + slot) * vectors + vector];
+				sum.x = __fadd_rn(sum.x, value.x);
+				sum.y = __fadd_rn(sum.y, value.y);
+				sum.z = __fadd_rn(sum.z, value.z);
+				sum.w = __fadd_rn(sum.w, value.w);
+			}
+			out[(uint64_t)row * vectors + vector] = sum;
+		}
+	}
+	if (last_block_of_grid(ready_line, &last) && threadIdx.x == 0) {
+		*reinterpret_cast<uint64_t *>(ready_line + ORDERED_LOCAL_PREVIOUS_OFFSET) = sequence;
+		__threadfence_system();
+		signal_store(ready_line, sequence);
+	}
+}
+
+extern "C" __global__ void __launch_bounds__(ORDERED_COLLECTIVE_THREADS)
+	ordered_reduce_bf16(struct ordered_reduce_bf16_arguments arguments, unsigned char *arena)
+{
+	__shared__ uint32_t verdict, last;
+	const struct ordered_collective_arguments &collective = arguments.collective;
+	const struct step_block step = *reinterpret_cast<const struct step_block *>(arena + collective.step_offset);
+	const uint64_t sequence = step.sequence;
+	if (sequence == 0 || collective.rank_count == 0 || collective.rank_count > ORDERED_COLLECTIVE_MAXIMUM_RANKS)
+		return;
+	unsigned char *const status = arena + arguments.status_offset;
+	unsigned char *const mine = ordered_slot(collective, arena, collective.rank, sequence);
+	const bool alive = ordered_wait_all(collective, arena, ORDERED_READY_PHASE, sequence, sequence, true, status, &verdict);
+	if (alive) {
+		const uint32_t live = min(step.row_count * arguments.width, collective.element_count);
+		const uint32_t vectors = live / 4u;
+		const float *inputs[ORDERED_COLLECTIVE_MAXIMUM_RANKS];
+#pragma unroll
+		for (uint32_t rank = 0; rank < ORDERED_COLLECTIVE_MAXIMUM_RANKS; rank++)
+			inputs[rank] = rank < collective.rank_count ?
+					       reinterpret_cast<const float *>(ordered_slot(collective, arena, rank, sequence) +
+									       collective.input_offset) :
+					       nullptr;
+		uint2 *const output = reinterpret_cast<uint2 *>(arena + collective.output_offset);
+		for (uint32_t vector = blockIdx.x * blockDim.x + threadIdx.x; vector < vectors;
+		     vector += gridDim.x * blockDim.x) {
+			float4 values[ORDERED_COLLECTIVE_MAXIMUM_RANKS];
+#pragma unroll
+			for (uint32_t rank = 0; rank < ORDERED_COLLECTIVE_MAXIMUM_RANKS; rank++)
+				if (rank < collective.rank_count)
+					values[rank] = ordered_load4(inputs[rank] + 4u * (uint64_t)vector);
+			float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+			for (uint32_t rank = 0; rank < ORDERED_COLLECTIVE_MAXIMUM_RANKS; rank++)
+				if (rank < collective.rank_count) {
+					sum.x = __fadd_rn(sum.x, values[rank].x);
+					sum.y = __fadd_rn(sum.y, values[rank].y);
+					sum.z = __fadd_rn(sum.z, values[rank].z);
+					sum.w = __fadd_rn(sum.w, values[rank].w);
+				}
+			output[vector] = make_uint2(bfloat16_bits(sum.x) | bfloat16_bits(sum.y) << 16,
+						    bfloat16_bits(sum.z) | bfloat16_bits(sum.w) << 16);
+		}
+	}
+	/* this rank has read (or given up on) every peer's slot: say so, whatever happened */
+	unsigned char *const done_line = mine + ORDERED_DONE_PHASE * ORDERED_COLLECTIVE_LINE_BYTES;
+	if (last_block_of_grid(done_line, &last) && threadIdx.x == 0)
+		signal_store(done_line, sequence);
+}

@@ -1,0 +1,158 @@
+/*
+ * kernel_router_b200.cu: router select and job-table builder for up to 64 live rows (struct
+ * router_select_b200_arguments). One block of 1024 threads, no atomics on data, a row's picks depend on that row alone.
+ * Conventions are the reference's router_select_entry (source/kernel_router.cuh:36-119, include/anemone/
+ * router_records.h:7-30): keys order scores as the reference's top-k orders float32 (a not-a-number above every
+ * number, -0 below +0), the lower expert first among equals; slots in ascending expert order; the weight sum from +0
+ * in ascending expert order, every operation one FP32 rounding; jobs in ascending expert order, rows ascending, at
+ * most eight rows a job. Differences: expert count, picks and scoring are record fields instead of the reference
+ * model's constants; the picks are the largest SCORES (the affinity is monotone in the score), so that the chosen
+ * experts do not depend on the last bit of expf; always-on shared experts get jobs behind the routed ones.
+ */
+#include <stdint.h>
+
+#include "anemone_b200_records.h"
+
+#define WARP 32u
+#define EXPERTS_PER_LANE (ROUTER_B200_MAXIMUM_EXPERTS / WARP)
+
+__device__ __forceinline__ uint64_t router_key(float score, uint32_t expert)
+{
+	const uint32_t bits = __float_as_uint(score);
+	const uint32_t ordered = score != score ? 0xFFFFFFFFu : (bits & 0x80000000u) != 0 ? ~bits : bits | 0x80000000u;
+	return (uint64_t)ordered << 32 | (uint64_t)(uint32_t)~expert;
+}
+
+__device__ __forceinline__ float router_affinity(float score, uint32_t scoring)
+{
+	if (scoring == ROUTER_SCORING_SQRT_SOFTPLUS)
+		return __fsqrt_rn(score > 20.0f ? score : log1pf(expf(score)));
+	return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-score)));
+}
+
+extern "C" __global__ void __launch_bounds__(ROUTER_B200_THREADS)
+	router_select_b200(struct router_select_b200_arguments arguments, unsigned char *arena)
+{
+	__shared__ uint32_t chosen[ROUTER_B200_MAXIMUM_ROWS][ROUTER_B200_MAXIMUM_PICKS]; /* by slot */
+	__shared__ float weight[ROUTER_B200_MAXIMUM_ROWS][ROUTER_B200_MAXIMUM_PICKS];
+	__shared__ uint32_t rows_of[ROUTER_B200_MAXIMUM_EXPERTS]; /* rows that chose the expert */
+	__shared__ uint32_t first_job[ROUTER_B200_MAXIMUM_EXPERTS + 1u];
+	const struct step_block step = *reinterpret_cast<const struct step_block *>(arena + arguments.step_offset);
+	const uint32_t live = min(step.row_count, arguments.row_capacity);
+	const uint32_t experts = arguments.expert_count, picks = arguments.picks, shared = arguments.shared_count;
+	const uint32_t lane = threadIdx.x % WARP, warp = threadIdx.x / WARP;
+	const float *const scores = reinterpret_cast<const float *>(arena + arguments.scores_offset);
+
+	/* every byte of the job table starts zero */
+	uint4 *const table = reinterpret_cast<uint4 *>(arena + arguments.jobs_offset);
+	for (uint32_t index = threadIdx.x; index < arguments.job_capacity * (uint32_t)(sizeof(struct expert_job_record) / 16u);
+	     index += blockDim.x)
+		table[index] = make_uint4(0, 0, 0, 0);
+	for (uint32_t expert = threadIdx.x; expert < ROUTER_B200_MAXIMUM_EXPERTS; expert += blockDim.x)
+		rows_of[expert] = 0;
+
+	/* one warp a row: `picks` rounds of a warp-wide maximum over 64-bit keys */
+	for (uint32_t row = warp; row < live; row += blockDim.x / WARP) {
+		uint64_t keys[EXPERTS_PER_LANE];
+#pragma unroll
+		for (uint32_t place = 0; place < EXPERTS_PER_LANE; place++) {
+			const uint32_t expert = place * WARP + lane;
+			keys[place] = expert < experts ? router_key(scores[(uint64_t)row * experts + expert], expert) : 0ull;
+		}
+		uint32_t mine = 0; /* lane p keeps pick p */
+		for (uint32_t pick = 0; pick < picks; pick++) {
+			uint64_t best = 0;
+#pragma unroll
+			for (uint32_t place = 0; place < EXPERTS_PER_LANE; place++)
+				best = keys[place] > best ? keys[place] : best;
+			for (uint32_t distance = WARP / 2u; distance != 0; distance >>= 1) {
+				const uint64_t other = __shfl_xor_sync(0xFFFFFFFFu, best, distance);
+				best = other > best ? other : best;
+			}
+#pragma unroll
+			for (uint32_t place = 0; place < EXPERTS_PER_LANE; place++)
+				keys[place] = keys[place] == best ? 0ull : keys[place];
+			if (lane == pick)
+				mine = ~(uint32_t)best;
+		}
+		/* slot = the number of picked experts below mine */
+		uint32_t slot = 0;
+		for (uint32_t pick = 0; pick < picks; pick++) {
+			const uint32_t other = __shfl_sync(0xFFFFFFFFu, mine, pick);
+			slot += lane < picks && other < mine ? 1u : 0u;
+		}
+		if (lane < picks) {
+			chosen[row][slot] = mine;
+			weight[row][slot] = router_affinity(scores[(uint64_t)row * experts + mine], arguments.scoring);
+		}
+		__syncwarp();
+		float sum = 0.0f;
+		for (uint32_t place = 0; place < picks; place++)
+			sum = __fadd_rn(sum, weight[row][place]);
+		__syncwarp();
+		if (lane < picks) {
+			const float value =
+				__fmul_rn(__fdiv_rn(weight[row][lane], __fadd_rn(sum, 1e-20f)), arguments.route_scale);
+			weight[row][lane] = value;
+			reinterpret_cast<uint32_t *>(arena + arguments.picks_offset)[(uint64_t)row * picks + lane] =
+				chosen[row][lane];
+			reinterpret_cast<float *>(arena + arguments.weights_offset)[(uint64_t)row * picks + lane] = value;
+		}
+	}
+	__syncthreads();
+
+	/* rows per expert (a thread an expert: no atomics), then the first job of every expert */
+	for (uint32_t expert = threadIdx.x; expert < experts + shared; expert += blockDim.x) {
+		uint32_t count = 0;
+		if (expert >= experts) {
+			count = live;
+		} else {
+			for (uint32_t row = 0; row < live; row++)
+				for (uint32_t place = 0; place < picks; place++)
+					count += chosen[row][place] == expert ? 1u : 0u;
+		}
+		rows_of[expert] = count;
+	}
+	__syncthreads();
+	if (threadIdx.x == 0) {
+		uint32_t jobs = 0;
+		for (uint32_t expert = 0; expert < experts + shared; expert++) {
+			first_job[expert] = jobs;
+			jobs += (rows_of[expert] + LINEAR_MAXIMUM_ROWS - 1u) / LINEAR_MAXIMUM_ROWS;
+		}
+		first_job[experts + shared] = jobs;
+	}
+	__syncthreads();
+
+	/* a thread a pair: its place among its expert's rows decides its job and column */
+	const uint32_t pairs_per_row = picks + shared;
+	struct expert_job_record *const jobs = reinterpret_cast<struct expert_job_record *>(arena + arguments.jobs_offset);
+	const uint64_t *const offsets = reinterpret_cast<const uint64_t *>(arena + arguments.expert_table_offset);
+	for (uint32_t pair = threadIdx.x; pair < live * pairs_per_row; pair += blockDim.x) {
+		const uint32_t row = pair / pairs_per_row, slot = pair % pairs_per_row;
+		const uint32_t expert = slot < picks ? chosen[row][slot] : experts + (slot - picks);
+		uint32_t place = 0; /* rows below mine that stand in the same expert */
+		if (slot >= picks) {
+			place = row;
+		} else {
+			for (uint32_t other = 0; other < row; other++)
+				for (uint32_t pick = 0; pick < picks; pick++)
+					place += chosen[other][pick] == expert ? 1u : 0u;
+		}
+		const uint32_t job_index = first_job[expert] + place / LINEAR_MAXIMUM_ROWS;
+		if (job_index >= arguments.job_capacity)
+			continue;
+		struct expert_job_record *const job = &jobs[job_index];
+		const uint32_t column = place % LINEAR_MAXIMUM_ROWS;
+		job->pair_index[column] = pair;
+		job->route_weight[column] = slot < picks ? weight[row][slot] : 1.0f;
+		if (column == 0) {
+			const uint32_t remaining = rows_of[expert] - place;
+			job->gate_offset = offsets[3u * expert];
+			job->up_offset = offsets[3u * expert + 1u];
+			job->down_offset = offsets[3u * expert + 2u];
+			job->expert = expert;
+			job->row_count = remaining < LINEAR_MAXIMUM_ROWS ? remaining : LINEAR_MAXIMUM_ROWS;
+		}
+	}
+}

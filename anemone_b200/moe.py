@@ -1,0 +1,225 @@
+"""One rank's quantized MoE expert layer, prepared once and run per step through the C-ABI library.
+
+Host-side mirror of how the reference's model program uses the path (source/model_v41_program.c:4227-4531, 2618-2770):
+at load, matrices are placed in the arena, every launch is prepared by the library's preparers and captured into one
+graph; per step the caller writes the step block, the tokens and the router scores, runs the graph and reads the
+bfloat16 result. Launches of one step, all from libanemone_b200.so:
+    router_select_b200 -> exl3_moe_input -> exl3_moe_gate_up -> exl3_moe_down -> ordered_row_sum_publish
+    -> ordered_reduce_bf16
+Tensor parallelism is by intermediate columns: this rank holds columns [begin, begin + inner_local) of every expert's
+gate and up and the matching input rows of down; the ranks' FP32 partial rows are summed in rank order by peer loads
+and rounded once to bfloat16. Nothing here computes on the host.
+"""
+import ctypes as C
+from dataclasses import dataclass
+
+import numpy as np
+
+from . import api
+from . import records as R
+from . import synthetic
+
+LINE = 128
+SIGNAL_BYTES = 3 * LINE
+
+
+@dataclass
+class MoeConfig:
+    hidden: int = 4096
+    inner: int = 2048  # full intermediate width of an expert
+    experts: int = 256  # routed
+    shared: int = 1  # always-on experts, weight 1
+    picks: int = 8
+    row_capacity: int = 8
+    activation_limit: float = 10.0
+    scoring: int = 0  # ROUTER_SCORING_SIGMOID
+    route_scale: float = 1.0
+    deadline_cycles: int = 2_000_000_000  # about a second of device clock
+
+    @property
+    def pairs_per_row(self):
+        return self.picks + self.shared
+
+    @property
+    def total_experts(self):
+        return self.experts + self.shared
+
+
+def rank_columns(inner, rank_count, rank):
+    """The 128-column blocks of a rank: [blocks r / R, blocks (r + 1) / R), as bb_exl3_inner_shard_prepare cuts them."""
+    blocks = inner // 128
+    begin = blocks * rank // rank_count * 128
+    return begin, blocks * (rank + 1) // rank_count * 128 - begin
+
+
+def local_matrices(gate, up, down, config, width, rank_count, rank):
+    """This rank's slices of one expert's three stored matrices."""
+    begin, count = rank_columns(config.inner, rank_count, rank)
+    if rank_count == 1:
+        return gate, up, down
+    H, I = config.hidden, config.inner
+    return (synthetic.slice_matrix(gate, H, I, width, 0, H, begin, count),
+            synthetic.slice_matrix(up, H, I, width, 0, H, begin, count),
+            synthetic.slice_matrix(down, I, H, width, begin, count, 0, H))
+
+
+class MoeLayout:
+    """Byte offsets of everything one rank keeps in its arena. Identical on every rank of a group."""
+
+    def __init__(self, config, widths, rank_count, rank):
+        self.config, self.rank_count, self.rank = config, rank_count, rank
+        self.inner_local = rank_columns(config.inner, rank_count, rank)[1]
+        c, H, I = config, config.hidden, self.inner_local
+        rows, pairs = c.row_capacity, c.row_capacity * c.pairs_per_row
+        self.pairs = pairs
+        self.job_capacity = rows * c.picks + c.shared * ((rows + 7) // 8)
+        layout = api.Layout()
+        self.peer_table = layout.take(16 * 32)
+        self.status = layout.take(16)
+        # per-step inputs, contiguous so that one copy brings a whole step: step block, tokens, scores
+        self.step = layout.take(256)
+        self.tokens = layout.take(rows * H * 2)
+        self.scores = layout.take(rows * c.experts * 4)
+        self.step_input_bytes = layout.cursor - self.step
+        self.result = layout.take(rows * H * 2)
+        # the reduction's region: two parity slots of signal lines and this rank's FP32 partial rows
+        self.slot_input = SIGNAL_BYTES
+        self.parity_stride = api.align(SIGNAL_BYTES + rows * H * 4, LINE)
+        self.region = layout.take(2 * self.parity_stride, LINE)
+        self.picks = layout.take(rows * c.picks * 4)
+        self.weights = layout.take(rows * c.picks * 4)
+        self.jobs = layout.take(self.job_capacity * 96)
+        self.expert_table = layout.take(c.total_experts * 24)
+        self.widths = layout.take(c.total_experts * 4)
+        self.operands = layout.take(pairs * H * 4 + pairs * I * 2)
+        self.products = layout.take(pairs * H * 8)
+        self.hidden = layout.take(pairs * I * 2)
+        self.row_output = layout.take(rows * H * 4)
+        self.matrices = []
+        for expert in range(c.total_experts):
+            width = int(widths[expert])
+            sizes = (synthetic.matrix_bytes(H, I, width), synthetic.matrix_bytes(H, I, width),
+                     synthetic.matrix_bytes(I, H, width))
+            self.matrices.append(tuple(layout.take(size, 64) for size in sizes))
+        self.arena_bytes = api.align(layout.cursor, 4096) + 4096
+
+
+class MoeLayer:
+    def __init__(self, card, config, widths, matrices, rank=0, rank_count=1):
+        """matrices: iterable over experts (routed, then shared) of this rank's (gate, up, down) stored bytes."""
+        self.card, self.config = card, config
+        self.widths = np.asarray(widths, dtype=np.uint32)
+        self.layout = L = MoeLayout(config, self.widths, rank_count, rank)
+        assert card.arena_bytes >= L.arena_bytes
+        self.rank, self.rank_count = rank, rank_count
+        self.weight_bytes = 0
+        table = np.zeros((config.total_experts, 3), dtype=np.uint64)
+        for expert, triple in enumerate(matrices):
+            for which, data in enumerate(triple):
+                offset = L.matrices[expert][which]
+                card.upload(offset, data)
+                table[expert, which] = offset
+                self.weight_bytes += data.size
+        card.upload(L.expert_table, table)
+        card.upload(L.widths, self.widths)
+        card.fill(L.peer_table, 0, 16 * 32)
+        card.fill(L.status, 0, 16)
+        card.fill(L.step, 0, 256)
+        card.fill(L.region, 0, 2 * L.parity_stride)
+        peers = (R.OrderedPeer * rank_count)()
+        for peer in range(rank_count):
+            peers[peer].region_offset = L.region
+        card.upload(L.peer_table, np.frombuffer(bytes(peers), dtype=np.uint8))
+        self._prepare()
+        self.sequence = 0
+
+    # ---- load time ----
+    def connect_local(self, layers):
+        """All ranks in this process (the reference's arrangement): peer_connect every card to every card."""
+        for peer, other in enumerate(layers):
+            self.card.peer_connect(other.card, 0, self.layout.peer_table + 32 * peer)
+
+    def connect_handles(self, handles):
+        """One process per GPU: handles[r] is rank r's exported arena handle (all-gathered by the caller)."""
+        for peer, handle in enumerate(handles):
+            if peer == self.rank:
+                self.card.peer_connect(self.card, 0, self.layout.peer_table + 32 * peer)
+            else:
+                self.card.ipc_connect(handle, 0, self.layout.peer_table + 32 * peer)
+
+    def _prepare(self):
+        c, L, card, lib = self.config, self.layout, self.card, api.library()
+        router = R.RouterSelectB200(L.scores, L.expert_table, L.picks, L.weights, L.jobs, L.step, c.experts, c.shared,
+                                    c.picks, c.row_capacity, L.job_capacity, c.scoring, c.route_scale, 0)
+        lib.router_select_b200_prepare.argtypes = [C.POINTER(R.RouterSelectB200), C.c_uint64,
+                                                   C.POINTER(api.BackendOperations), C.c_void_p,
+                                                   C.POINTER(R.KernelLaunch)]
+        router_launch = R.KernelLaunch()
+        api.check(lib.router_select_b200_prepare(C.byref(router), card.arena_bytes, card.ops_pointer, card.handle,
+                                                 C.byref(router_launch)), "router_select_b200_prepare")
+        moe = R.Exl3Moe()
+        moe.base = R.Exl3Expert(L.jobs, L.tokens, L.operands, L.products, L.hidden, L.products, c.hidden,
+                                L.inner_local, L.pairs, c.pairs_per_row, L.job_capacity, R.EXL3_WIDTH_PER_EXPERT,
+                                c.activation_limit, 0)
+        moe.widths_offset, moe.row_output_offset, moe.expert_count = L.widths, L.row_output, c.total_experts
+        moe_launches = (R.KernelLaunch * 4)()
+        api.check(lib.exl3_moe_prepare(C.byref(moe), card.arena_bytes, card.ops_pointer, card.handle, moe_launches),
+                  "exl3_moe_prepare")
+        reduce = R.OrderedReduceBf16Description()
+        reduce.reduce.collective = R.OrderedCollective(L.peer_table, L.region, L.slot_input, L.result, 0, L.step,
+                                                       L.parity_stride, c.deadline_cycles,
+                                                       c.row_capacity * c.hidden, self.rank_count, self.rank, 0)
+        reduce.reduce.status_offset, reduce.reduce.width = L.status, c.hidden
+        reduce.pair_output_offset, reduce.arena_byte_count = L.products, card.arena_bytes
+        reduce.pairs_per_row, reduce.row_capacity = c.pairs_per_row, c.row_capacity
+        lib.ordered_reduce_bf16_prepare.argtypes = [C.POINTER(R.OrderedReduceBf16Description),
+                                                    C.POINTER(api.BackendOperations), C.c_void_p,
+                                                    C.POINTER(R.KernelLaunch)]
+        reduce_launches = (R.KernelLaunch * 2)()
+        api.check(lib.ordered_reduce_bf16_prepare(C.byref(reduce), card.ops_pointer, card.handle, reduce_launches),
+                  "ordered_reduce_bf16_prepare")
+        # the fused chain's own row sum is replaced by the reduction's, which sums straight into the exchange slot
+        self.launches = [router_launch, moe_launches[0], moe_launches[1], moe_launches[2], reduce_launches[0],
+                         reduce_launches[1]]
+        self.graph = card.graph(self.launches)
+
+    # ---- per step ----
+    def stage_step(self, staging_offset, sequence, tokens, scores):
+        """Write one step's inputs into the card's staging block at staging_offset (layout of the step input area)."""
+        L, view = self.layout, self.card.staging_view
+        rows = tokens.shape[0]
+        block = R.StepBlock(sequence, rows, 0)
+        base = staging_offset
+        view[base:base + 16] = np.frombuffer(bytes(block), dtype=np.uint8)
+        at = base + (L.tokens - L.step)
+        view[at:at + tokens.nbytes] = tokens.reshape(-1).view(np.uint8)
+        at = base + (L.scores - L.step)
+        view[at:at + scores.nbytes] = np.ascontiguousarray(scores, dtype=np.float32).reshape(-1).view(np.uint8)
+
+    def submit(self, staging_offset, result_staging_offset, rows):
+        """Queue: copy the staged step in, run the layer's graph, copy the bfloat16 result out. Returns the ticket of
+        the result copy; nothing waits."""
+        L, card = self.layout, self.card
+        card.upload_async(L.step, staging_offset, L.step_input_bytes)
+        card.graph_run(self.graph)
+        return card.download_async(L.result, result_staging_offset, rows * self.config.hidden * 2)
+
+    def step(self, tokens, scores):
+        """One layer call on host arrays: tokens bfloat16 bits [rows][hidden], scores FP32 [rows][experts].
+        Returns bfloat16 bits [rows][hidden]. Raises if the reduction reported a failed wait."""
+        L, card = self.layout, self.card
+        rows = tokens.shape[0]
+        self.sequence += 1
+        result_at = api.align(L.step_input_bytes, 4096)
+        self.stage_step(0, self.sequence, tokens, scores)
+        ticket = self.submit(0, result_at, rows)
+        card.transfer_wait(ticket)
+        self.check_status()
+        nbytes = rows * self.config.hidden * 2
+        return card.staging_view[result_at:result_at + nbytes].view(np.uint16).reshape(rows, self.config.hidden).copy()
+
+    def check_status(self):
+        status = self.card.download(self.layout.status, 16, np.uint32)
+        if status[0] != 0:
+            raise RuntimeError("ordered reduction failed: code %d (1 timed out, 2 bad sequence), phase %d, rank %d"
+                               % (status[0], status[1], status[2]))

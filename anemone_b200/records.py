@@ -100,6 +100,11 @@ class OrderedCollectiveDescription(C.Structure):
     _fields_ = [("arguments", OrderedCollective), ("arena_byte_count", C.c_uint64), ("operation", C.c_int)]
 
 
+class OrderedReduceBf16Description(C.Structure):
+    _fields_ = [("reduce", OrderedReduceBf16), ("pair_output_offset", C.c_uint64), ("arena_byte_count", C.c_uint64),
+                ("pairs_per_row", C.c_uint32), ("row_capacity", C.c_uint32)]
+
+
 class OrderedCollectiveKernels(C.Structure):
     _fields_ = [("handles", C.c_uint32 * 4)]
 

@@ -1,0 +1,91 @@
+/*
+ * anemone_b200_collective.h: load-time preparation of the fixed-order reductions over ranks, and the host function that
+ * defines their order. Host C11. A refusal leaves every output unchanged.
+ *
+ * Protocol kept from the reference (include/anemone/ordered_collective_records.h:5-38): every rank launches the same
+ * kernel with the same strictly increasing 64-bit sequence, read on the device from the step block, so one prepared
+ * launch (or captured graph) serves every step; two parity slots per rank; a signal line is written only by its owner,
+ * after its payload, with a system-scope release, and read with a system-scope acquire; sums are
+ * ((+0 + rank 0) + rank 1) + ... in FP32 with one rounded add per rank; no atomics on data.
+ * Changed for NVLink/NVSwitch: all routes are direct peer loads (no host mirrors); a line holds the owner's step
+ * sequence itself instead of a generation counter plus sequence words; a wait that runs out reports through a status
+ * block (B200 entries) and never traps.
+ */
+#ifndef ANEMONE_B200_COLLECTIVE_H
+#define ANEMONE_B200_COLLECTIVE_H
+
+#include "anemone_b200_backend.h"
+#include "anemone_b200_records.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* include/anemone/ordered_collective.h:25-33 */
+struct ordered_collective_kernels {
+	uint32_t handles[ORDERED_COLLECTIVE_OPERATIONS];
+};
+
+struct ordered_collective_description {
+	struct ordered_collective_arguments arguments;
+	uint64_t arena_byte_count;
+	enum ordered_collective_operation operation;
+};
+
+/* include/anemone/ordered_collective.h:57-68 */
+struct ordered_collective_route_description {
+	const struct card_description_record *cards;
+	const uint32_t *direct_reader_masks;
+	uint32_t rank_count, element_count;
+	enum ordered_collective_operation operation;
+	bool common_numa_root;
+	bool paired_scatter_gather;
+};
+
+/* include/anemone/ordered_collective.h:67-69. host_reader_masks_out[source] = the readers of `source` that lack
+ * direct access (they would need a host mirror). The reference's PCIe preferences for its CMP cards do not apply to
+ * NVLink: a reader with direct access is always direct. This library's kernels refuse host routes, so a caller must
+ * see all-zero masks before it prepares a launch. */
+MUST_CHECK result_status ordered_collective_routes_prepare(
+	const struct ordered_collective_route_description *description, uint32_t *host_reader_masks_out);
+
+/* include/anemone/ordered_collective.h:101-103 (source/ordered_collective.c:117-142): the four FP32 kernels. */
+MUST_CHECK result_status ordered_collective_kernels_prepare(const struct backend_operations *backend,
+							    struct device_card *card,
+							    struct ordered_collective_kernels *kernels_out);
+
+/* include/anemone/ordered_collective.h:104-107 (source/ordered_collective.c:208-282): one block of 256 threads. */
+MUST_CHECK result_status ordered_collective_prepare(const struct ordered_collective_description *description,
+						    const struct ordered_collective_kernels *kernels,
+						    struct kernel_launch *launch_out);
+
+/* include/anemone/ordered_collective.h:108-110 (source/ordered_collective.c:144-206): the same four operations on host
+ * arrays, which DEFINE the order the kernels must reproduce bit for bit. A staging utility for callers and tests;
+ * nothing in this library calls it. Refuses overlapping buffers and a rounding mode other than to-nearest. */
+MUST_CHECK result_status ordered_collective_host(const float *const *inputs, float *const *outputs,
+						 uint32_t rank_count, uint32_t element_count,
+						 enum ordered_collective_operation operation);
+
+/* ---- B200 extension: the expert layer's reduction, FP32 partial rows -> one bfloat16 result ---- */
+
+struct ordered_reduce_bf16_description {
+	struct ordered_reduce_bf16_arguments reduce; /* .collective as above; output_offset an ARENA offset */
+	uint64_t pair_output_offset; /* FP32 [row_capacity * pairs_per_row][width]: the finished pair outputs */
+	uint64_t arena_byte_count;
+	uint32_t pairs_per_row;
+	uint32_t row_capacity; /* collective.element_count = row_capacity * width */
+};
+
+/* No reference counterpart as one call; the arithmetic is tp_exchange_owner_sum's (source/kernel_tp_exchange.cu:
+ * 190-247). Writes two launches: ordered_row_sum_publish, ordered_reduce_bf16 (kernel file "kernel_ordered_b200").
+ * Validates what ordered_collective_prepare validates (region, slots, table, step block, disjointness), that width is a
+ * multiple of 4, the result and status ranges, and that no peer entry will be a host route. */
+#define ORDERED_REDUCE_BF16_LAUNCHES 2u
+MUST_CHECK result_status ordered_reduce_bf16_prepare(const struct ordered_reduce_bf16_description *description,
+						     const struct backend_operations *backend,
+						     struct device_card *card, struct kernel_launch *launches_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

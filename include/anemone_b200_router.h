@@ -1,0 +1,31 @@
+/*
+ * anemone_b200_router.h: load-time preparation of the router select that feeds the expert launches their job table.
+ * Host C11. A refusal leaves the launch unchanged.
+ */
+#ifndef ANEMONE_B200_ROUTER_H
+#define ANEMONE_B200_ROUTER_H
+
+#include "anemone_b200_backend.h"
+#include "anemone_b200_records.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Worst-case jobs of `rows` live rows: every pick its own job, plus the shared experts' jobs of eight rows. */
+uint32_t router_b200_job_capacity(uint32_t rows, uint32_t picks, uint32_t shared_count);
+
+/* Takes the place of router_select_prepare for this path (include/anemone/router.h; the reference's record is fixed
+ * to its model's 384 experts and 6 picks, this one carries them). Checks counts against the kernel's limits
+ * (ROUTER_B200_MAXIMUM_*), that job_capacity covers the worst case of row_capacity rows, the scoring code, a finite
+ * positive route scale, and that the six ranges lie inside the arena, 16-byte aligned and disjoint. One launch:
+ * ("kernel_router_b200", "router_select_b200"), one block of ROUTER_B200_THREADS threads. */
+MUST_CHECK result_status router_select_b200_prepare(const struct router_select_b200_arguments *arguments,
+						    uint64_t arena_byte_count,
+						    const struct backend_operations *backend, struct device_card *card,
+						    struct kernel_launch *launch_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
