@@ -46,3 +46,28 @@ result_status router_select_b200_prepare(const struct router_select_b200_argumen
 	prepare_launch_fill(launch_out, kernel, 1, 1, 1, ROUTER_B200_THREADS, 0, arguments, sizeof(*arguments));
 	return STATUS_OK;
 }
+
+result_status step_input_select_prepare(const struct step_input_select_arguments *arguments, uint64_t arena_byte_count,
+					const struct backend_operations *backend, struct device_card *card,
+					struct kernel_launch *launch_out)
+{
+	if (arguments == NULL || backend == NULL || backend->kernel_prepare == NULL || card == NULL ||
+	    launch_out == NULL || arguments->pool_count == 0 || arguments->byte_count == 0 ||
+	    arguments->byte_count % 16u != 0 || arguments->byte_count > arguments->pool_stride ||
+	    arguments->pool_stride % 16u != 0 || arguments->pool_stride > UINT64_MAX / arguments->pool_count)
+		return STATUS_INVALID_ARGUMENT;
+	const struct checked_range ranges[3] = {
+		{ "step pool", arguments->pool_offset, arguments->pool_stride * arguments->pool_count },
+		{ "step input area", arguments->destination_offset, arguments->byte_count },
+		{ "cursor", arguments->cursor_offset, 16u }
+	};
+	if (!prepare_ranges_are_valid("step input select", ranges, 3, arena_byte_count))
+		return STATUS_INVALID_ARGUMENT;
+	uint32_t kernel = BACKEND_NO_KERNEL;
+	const result_status status = backend->kernel_prepare(card, KERNEL_FILE_ROUTER_B200, KERNEL_STEP_INPUT_SELECT,
+							     sizeof(*arguments), &kernel);
+	if (status != STATUS_OK)
+		return status;
+	prepare_launch_fill(launch_out, kernel, 1, 1, 1, ROUTER_B200_THREADS, 0, arguments, sizeof(*arguments));
+	return STATUS_OK;
+}

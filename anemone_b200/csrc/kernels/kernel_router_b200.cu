@@ -156,3 +156,18 @@ extern "C" __global__ void __launch_bounds__(ROUTER_B200_THREADS)
 		}
 	}
 }
+
+/* One block: copy the pool entry the cursor names into the step input area, then advance the cursor. */
+extern "C" __global__ void __launch_bounds__(ROUTER_B200_THREADS)
+	step_input_select(struct step_input_select_arguments arguments, unsigned char *arena)
+{
+	uint64_t *const cursor = reinterpret_cast<uint64_t *>(arena + arguments.cursor_offset);
+	const uint64_t entry = *cursor % arguments.pool_count;
+	const uint4 *const source = reinterpret_cast<const uint4 *>(arena + arguments.pool_offset + entry * arguments.pool_stride);
+	uint4 *const destination = reinterpret_cast<uint4 *>(arena + arguments.destination_offset);
+	for (uint32_t index = threadIdx.x; index < arguments.byte_count / 16u; index += blockDim.x)
+		destination[index] = source[index];
+	__syncthreads();
+	if (threadIdx.x == 0)
+		*cursor = *cursor + 1u;
+}

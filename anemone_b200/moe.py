@@ -66,8 +66,9 @@ def local_matrices(gate, up, down, config, width, rank_count, rank):
 class MoeLayout:
     """Byte offsets of everything one rank keeps in its arena. Identical on every rank of a group."""
 
-    def __init__(self, config, widths, rank_count, rank):
+    def __init__(self, config, widths, rank_count, rank, pool_entries=0):
         self.config, self.rank_count, self.rank = config, rank_count, rank
+        self.pool_entries = pool_entries
         self.inner_local = rank_columns(config.inner, rank_count, rank)[1]
         c, H, I = config, config.hidden, self.inner_local
         rows, pairs = c.row_capacity, c.row_capacity * c.pairs_per_row
@@ -82,6 +83,10 @@ class MoeLayout:
         self.scores = layout.take(rows * c.experts * 4)
         self.step_input_bytes = layout.cursor - self.step
         self.result = layout.take(rows * H * 2)
+        # optional: a pool of prepared step inputs resident on the card (step_input_select walks it)
+        self.pool_stride = api.align(self.step_input_bytes, 256)
+        self.cursor = layout.take(16)
+        self.pool = layout.take(self.pool_stride * pool_entries) if pool_entries else 0
         # the reduction's region: two parity slots of signal lines and this rank's FP32 partial rows
         self.slot_input = SIGNAL_BYTES
         self.parity_stride = api.align(SIGNAL_BYTES + rows * H * 4, LINE)
@@ -105,11 +110,11 @@ class MoeLayout:
 
 
 class MoeLayer:
-    def __init__(self, card, config, widths, matrices, rank=0, rank_count=1):
+    def __init__(self, card, config, widths, matrices, rank=0, rank_count=1, pool_entries=0):
         """matrices: iterable over experts (routed, then shared) of this rank's (gate, up, down) stored bytes."""
         self.card, self.config = card, config
         self.widths = np.asarray(widths, dtype=np.uint32)
-        self.layout = L = MoeLayout(config, self.widths, rank_count, rank)
+        self.layout = L = MoeLayout(config, self.widths, rank_count, rank, pool_entries)
         assert card.arena_bytes >= L.arena_bytes
         self.rank, self.rank_count = rank, rank_count
         self.weight_bytes = 0
@@ -182,6 +187,30 @@ class MoeLayer:
         self.launches = [router_launch, moe_launches[0], moe_launches[1], moe_launches[2], reduce_launches[0],
                          reduce_launches[1]]
         self.graph = card.graph(self.launches)
+        self.resident_graph = None
+        if L.pool_entries:
+            select = R.StepInputSelect(L.pool, L.pool_stride, L.step, L.cursor, L.pool_entries, L.step_input_bytes)
+            lib.step_input_select_prepare.argtypes = [C.POINTER(R.StepInputSelect), C.c_uint64,
+                                                      C.POINTER(api.BackendOperations), C.c_void_p,
+                                                      C.POINTER(R.KernelLaunch)]
+            select_launch = R.KernelLaunch()
+            api.check(lib.step_input_select_prepare(C.byref(select), card.arena_bytes, card.ops_pointer, card.handle,
+                                                    C.byref(select_launch)), "step_input_select_prepare")
+            self.resident_graph = card.graph([select_launch] + self.launches)
+
+    def load_pool(self, steps):
+        """steps: pool_entries tuples (sequence, tokens, scores), sequences strictly increasing. Their input areas go
+        to the card's pool; run_resident() then takes them one after the other without touching the host."""
+        L, card = self.layout, self.card
+        assert len(steps) == L.pool_entries
+        for index, (sequence, tokens, scores) in enumerate(steps):
+            self.stage_step(0, sequence, tokens, scores)
+            card.transfer_wait(card.upload_async(L.pool + index * L.pool_stride, 0, L.step_input_bytes))
+        card.fill(L.cursor, 0, 16)
+        card.wait()
+
+    def run_resident(self):
+        self.card.graph_run(self.resident_graph)
 
     # ---- per step ----
     def stage_step(self, staging_offset, sequence, tokens, scores):

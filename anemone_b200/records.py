@@ -83,6 +83,11 @@ class RouterSelectB200(C.Structure):
                 ("route_scale", C.c_float), ("reserved_zero", C.c_uint32)]
 
 
+class StepInputSelect(C.Structure):
+    _fields_ = [("pool_offset", C.c_uint64), ("pool_stride", C.c_uint64), ("destination_offset", C.c_uint64),
+                ("cursor_offset", C.c_uint64), ("pool_count", C.c_uint32), ("byte_count", C.c_uint32)]
+
+
 class KernelLaunch(C.Structure):
     _fields_ = [("kernel", C.c_uint32), ("grid", C.c_uint32 * 3), ("block", C.c_uint32 * 3),
                 ("dynamic_shared_byte_count", C.c_uint32), ("argument_byte_count", C.c_uint32),
@@ -112,5 +117,5 @@ class OrderedCollectiveKernels(C.Structure):
 for _record, _bytes in ((Exl3Reconstruct, 32), (Exl3Expert, 80), (ExpertJob, 96), (ExpertRowSum, 24),
                         (Exl3ShardActivation, 96), (Exl3Moe, 104), (StepBlock, 16), (OrderedPeer, 32),
                         (OrderedCollective, 80), (OrderedReduceBf16, 96), (OrderedRowSumPublish, 96),
-                        (RouterSelectB200, 80), (KernelLaunch, 232), (CardDescription, 168)):
+                        (RouterSelectB200, 80), (StepInputSelect, 40), (KernelLaunch, 232), (CardDescription, 168)):
     assert C.sizeof(_record) == _bytes, (_record.__name__, C.sizeof(_record), _bytes)

@@ -1,0 +1,353 @@
+"""Benchmark of the quantized MoE expert-layer hot path: one step = one layer call over one batch of M tokens.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--rows M] [--impl reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        bench.py --gpus N --steps K --warmup W
+
+Workload (synthetic, seeded; no checkpoint is available offline): the EXL3 MoE layer of the headline metric, 256 routed
++ 1 shared experts, top-8 sigmoid routing, hidden 4096, intermediate 2048, a stored width per expert drawn from
+{2, 3, 4} bits with probabilities {0.2, 0.5, 0.3}, M = 8 decode tokens, sharded over N GPUs by intermediate columns
+with the fixed-order FP32 -> bfloat16 reduction at the end. Every step draws its own tokens and router scores, so each
+step streams a different set of about 58 experts (about 0.55 GB at N = 1, more than the 126 MB L2).
+
+One JSON line on rank 0:
+  value     tokens/s with every step's inputs already resident in HBM (a device-side step_input_select hands them over),
+            timed with CUDA events on the card's stream, max over ranks;
+  e2e       the same through the public call with host buffers: per step the host -> device copy of the step's inputs
+            from pinned memory, the layer's graph, the device -> host copy of the bfloat16 result, and the wait for it;
+  roofline  the dominant kernel (exl3_moe_gate_up) timed alone, launch by launch, with CUDA events, against the
+            measured HBM copy bandwidth of MEASURED_PEAKS.json;
+  cpu_baseline  the CPU oracle (OpenMP, all host cores) on a bounded sample of the same step, scaled to the step.
+--impl reference times that CPU restatement of the reference's arithmetic alone (the reference has no engine CPU path
+for this layer and its GPU code has no sm_100 build), on the same metric and config.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "MoE expert-layer tok/s (decode M=8, prefill M=4096) at 1/2/4/8 B200"
+SEED = 20261125
+# dram bytes moved per algorithmic byte by exl3_moe_gate_up, from the ncu capture summarised in
+# profiles/exl3_moe_gate_up_k3_64experts_m8.md (dram__bytes_read.sum + dram__bytes_write.sum over the launch's bytes)
+GATE_UP_TRAFFIC_RATIO = 1.02
+
+
+def parse():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--rows", type=int, default=8)
+    parser.add_argument("--impl", default="ours")
+    parser.add_argument("--experts", type=int, default=256)
+    parser.add_argument("--hidden", type=int, default=4096)
+    parser.add_argument("--inner", type=int, default=2048)
+    return parser.parse_args()
+
+
+def expert_matrices(config, widths):
+    """expert -> its three FULL stored matrices, drawn from a stream of its own so that every rank draws the same."""
+    from anemone_b200 import synthetic
+
+    def draw(expert):
+        rng = np.random.default_rng([SEED, 1000 + expert])
+        width = int(widths[expert])
+        return (synthetic.exl3_matrix(rng, config.hidden, config.inner, width),
+                synthetic.exl3_matrix(rng, config.hidden, config.inner, width),
+                synthetic.exl3_matrix(rng, config.inner, config.hidden, width))
+    return draw
+
+
+def step_inputs(config, rows, count):
+    from anemone_b200 import synthetic
+    steps = []
+    for index in range(count):
+        rng = np.random.default_rng([SEED, 7, index])
+        steps.append((synthetic.tokens(rng, rows, config.hidden),
+                      rng.normal(0.0, 1.0, size=(rows, config.experts)).astype(np.float32)))
+    return steps
+
+
+def layer_widths(config):
+    from anemone_b200 import synthetic
+    rng = np.random.default_rng([SEED, 3])
+    return np.concatenate([synthetic.expert_widths(rng, config.experts), [3] * config.shared]).astype(np.uint32)
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons every 200 ms while a timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device):
+        self.samples, self.process = [], None
+        try:
+            self.process = subprocess.Popen(["nvidia-smi", "-i", str(device), "--query-gpu=" + self.QUERY,
+                                             "--format=csv,noheader,nounits", "-lms", "200"],
+                                            stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.process = None
+
+    def _read(self):
+        for line in self.process.stdout:
+            self.samples.append([field.strip() for field in line.split(",")])
+
+    def stop(self):
+        if self.process is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.process.terminate()
+        self.thread.join(timeout=2)
+        clocks = [float(s[0]) for s in self.samples if s and s[0].replace(".", "").isdigit()]
+        maxima = [float(s[1]) for s in self.samples if len(s) > 1 and s[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({names[i] for s in self.samples if len(s) >= 8 for i in range(4) if s[4 + i] == "Active"})
+        return {"sm_mhz": float(np.median(clocks)) if clocks else None,
+                "sm_max_mhz": max(maxima) if maxima else None, "reasons": reasons, "samples": len(clocks)}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as handle:
+            return float(json.load(handle)["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
+    return 6650.0, "fallback (6.65 TB/s, an earlier measurement on this pool)"
+
+
+def cpu_sample(config, widths, draw, tokens, scores, rank_count, job_limit):
+    """The CPU oracle on the first job_limit jobs of a step, scaled by weight bytes to the whole step."""
+    from oracle import binding, moe_reference
+    from anemone_b200 import synthetic
+    from anemone_b200.moe import rank_columns
+    oracle = binding.load_oracle()
+    experts, weights = moe_reference.route(oracle, config, scores)
+    cores = os.cpu_count() or 1
+    inner_local = rank_columns(config.inner, rank_count, 0)[1]
+
+    def job_bytes(jobs, count):
+        return sum(3 * config.hidden * inner_local // 16 * synthetic.bits_x2(int(widths[jobs[i].expert]))
+                   for i in range(count))
+    # the timed call: matrices are drawn before the clock starts
+    cache = {}
+
+    def cached(expert):
+        if expert not in cache:
+            cache[expert] = draw(expert)
+        return cache[expert]
+    _, jobs, kept = moe_reference.rank_partial(oracle, config, widths, cached, tokens, experts, weights, rank_count, 0,
+                                               0, job_limit)  # also the warm-up
+    begin = time.perf_counter()
+    _, jobs, kept = moe_reference.rank_partial(oracle, config, widths, cached, tokens, experts, weights, rank_count, 0,
+                                               0, job_limit)
+    seconds = time.perf_counter() - begin
+    import ctypes as C
+    from anemone_b200 import records as R
+    from oracle.binding import f32p, ptr, u32p, u64p
+    capacity = tokens.shape[0] * config.picks + config.shared * ((tokens.shape[0] + 7) // 8)
+    every = (R.ExpertJob * capacity)()
+    table = np.zeros((config.total_experts, 3), dtype=np.uint64)
+    total = oracle.orc_router_jobs(ptr(np.ascontiguousarray(experts), u32p), ptr(np.ascontiguousarray(weights), f32p),
+                                   tokens.shape[0], config.picks, config.experts, config.shared, ptr(table, u64p),
+                                   capacity, C.byref(every))
+    scale = job_bytes(every, total) / max(1, job_bytes(jobs, kept))
+    step_seconds = seconds * scale
+    return {"value": tokens.shape[0] / step_seconds, "unit": "tok/s", "cores": cores, "kind": "port",
+            "sample": "%d of the step's %d expert jobs (rank 0 of %d) on the OpenMP CPU oracle, %.2f s, scaled by "
+                      "weight bytes x%.2f" % (kept, total, rank_count, seconds, scale)}, step_seconds
+
+
+def run_reference(args, config, widths, draw, rank, world):
+    """--impl reference: the CPU restatement of the reference's arithmetic, all host threads, bounded samples."""
+    if rank != 0:
+        return
+    steps = step_inputs(config, args.rows, args.warmup + args.steps)
+    times = []
+    info = None
+    for index, (tokens, scores) in enumerate(steps):
+        info, seconds = cpu_sample(config, widths, draw, tokens, scores, world, job_limit=6)
+        if index >= args.warmup:
+            times.append(seconds)
+    ms = 1000.0 * float(np.mean(times))
+    value = args.rows * 1000.0 / ms
+    info["value"] = value
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f16xf16->f32", "data": "synthetic",
+        "config": workload_config(args, config, world), "cpu_baseline": info,
+        "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "the reference has no engine CPU path for this layer and no sm_100 kernel build; this arm times the "
+                "CPU restatement of its arithmetic (oracle/, pinned to its known-answer vectors) on the host cores"}))
+
+
+def workload_config(args, config, world):
+    return {"workload": "cfg3 EXL3 MoE layer decode: %d routed + %d shared experts, top-%d, hidden %d, intermediate %d, "
+                        "per-expert widths {2,3,4} p={0.2,0.5,0.3}, M=%d" % (config.experts, config.shared,
+                                                                                 config.picks, config.hidden,
+                                                                                 config.inner, args.rows),
+            "rows": args.rows, "parallelism": "tp%d by intermediate columns, ordered FP32->bf16 reduce" % world,
+            "l2": "inputs larger than L2: every step routes to a different expert set (~58 experts of 257)"}
+
+
+def main():
+    args = parse()
+    from anemone_b200.moe import MoeConfig
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    config = MoeConfig(hidden=args.hidden, inner=args.inner, experts=args.experts, shared=1, picks=8,
+                       row_capacity=args.rows)
+    widths = layer_widths(config)
+    draw = expert_matrices(config, widths)
+    if args.impl == "reference":
+        run_reference(args, config, widths, draw, rank, world)
+        return
+
+    from anemone_b200 import api, synthetic
+    from anemone_b200 import records as R
+    from anemone_b200.moe import MoeLayer, MoeLayout, local_matrices
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local_rank))
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+
+    def maximum(value):
+        if dist is None:
+            return value
+        import torch
+        tensor = torch.tensor([value], dtype=torch.float64, device="cuda")
+        dist.all_reduce(tensor, op=dist.ReduceOp.MAX)
+        return float(tensor.item())
+
+    if api.card_count() <= local_rank:
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    total_steps = args.warmup + args.steps
+    layout = MoeLayout(config, widths, world, rank, pool_entries=total_steps)
+    card = api.Card(local_rank, layout.arena_bytes)
+    matrices = (local_matrices(*draw(expert), config, int(widths[expert]), world, rank)
+                for expert in range(config.total_experts))
+    layer = MoeLayer(card, config, widths, matrices, rank=rank, rank_count=world, pool_entries=total_steps)
+    if dist is None:
+        layer.connect_local([layer])
+    else:
+        handles = [None] * world
+        dist.all_gather_object(handles, card.ipc_export())
+        layer.connect_handles(handles)
+    card.wait()
+    barrier()
+    steps = step_inputs(config, args.rows, total_steps)
+
+    # ---- value: inputs resident on the card ----
+    layer.load_pool([(index + 1, tokens, scores) for index, (tokens, scores) in enumerate(steps)])
+    barrier()
+    for _ in range(args.warmup):
+        layer.run_resident()
+    card.wait()
+    barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    launches_before = card.launch_count()
+    card.measure_begin()
+    for _ in range(args.steps):
+        layer.run_resident()
+    card.measure_end()
+    device_ms = maximum(card.measure_elapsed_us() / 1000.0)
+    card.wait()
+    launches = card.launch_count() - launches_before
+    barrier()
+    layer.check_status()
+    ms_per_step = device_ms / args.steps
+
+    # ---- e2e: host buffers in, host buffer out, every step ----
+    layer.sequence = total_steps
+    result_at = api.align(layout.step_input_bytes, 4096)
+    for tokens, scores in steps[:args.warmup]:
+        layer.step(tokens, scores)
+    barrier()
+    card.measure_begin()
+    wall_begin = time.perf_counter()
+    for tokens, scores in steps[args.warmup:]:
+        layer.sequence += 1
+        layer.stage_step(0, layer.sequence, tokens, scores)
+        card.transfer_wait(layer.submit(0, result_at, args.rows))
+    wall_ms = 1000.0 * (time.perf_counter() - wall_begin)
+    card.measure_end()
+    e2e_ms = maximum(max(card.measure_elapsed_us() / 1000.0, wall_ms)) / args.steps
+    clocks = sampler.stop() if sampler is not None else None
+    layer.check_status()
+    barrier()
+
+    # ---- roofline: the dominant kernel alone, launch by launch ----
+    roofline = None
+    if rank == 0:
+        peak, peak_source = measured_peaks()
+        gate_up = layer.launches[2:3]
+        prologue = layer.launches[0:2]
+        elapsed_us, byte_total = 0.0, 0
+        inner_local = layout.inner_local
+        for index, (tokens, scores) in enumerate(steps[args.warmup:]):
+            layer.sequence += 1
+            layer.stage_step(0, layer.sequence, tokens, scores)
+            card.transfer_wait(card.upload_async(layout.step, 0, layout.step_input_bytes))
+            card.run(prologue)
+            card.wait()
+            card.measure_begin()
+            card.run(gate_up)
+            card.measure_end()
+            elapsed_us += card.measure_elapsed_us()
+            picks = card.download(layout.picks, args.rows * config.picks * 4, np.uint32)
+            active = sorted(set(picks.tolist())) + list(range(config.experts, config.total_experts))
+            pairs = args.rows * config.pairs_per_row
+            byte_total += sum(2 * synthetic.matrix_bytes(config.hidden, inner_local, int(widths[e])) for e in active)
+            byte_total += 2 * pairs * config.hidden * 2 + pairs * inner_local * 4  # operands in, hidden + operands out
+        achieved = byte_total / elapsed_us / 1000.0  # GB/s
+        roofline = {"kernel": "exl3_moe_gate_up", "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                    "frac": achieved / peak, "peak_source": peak_source,
+                    "traffic": GATE_UP_TRAFFIC_RATIO * byte_total / args.steps,
+                    "algorithmic_bytes_per_launch": byte_total / args.steps,
+                    "us_per_launch": elapsed_us / args.steps}
+    card.wait()
+    barrier()
+
+    # ---- the CPU oracle beside it (rank 0 at N = 1 only) ----
+    cpu = None
+    if rank == 0 and world == 1:
+        tokens, scores = steps[args.warmup]
+        cpu, _ = cpu_sample(config, widths, draw, tokens, scores, 1, job_limit=12)
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": args.rows * 1000.0 / ms_per_step, "unit": "tok/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f16xf16->f32", "data": "synthetic",
+            "config": workload_config(args, config, world),
+            "e2e": {"value": args.rows * 1000.0 / e2e_ms, "unit": "tok/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": layout.step_input_bytes, "d2h_bytes_per_step": args.rows * config.hidden * 2},
+            "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline,
+        }
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line))
+    card.close()
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -332,6 +332,23 @@ struct router_select_b200_arguments {
 	uint32_t reserved_zero;
 };
 
+/* B200 extension, kernel file "kernel_router_b200", entry "step_input_select": the step driver's hand-over of one
+ * step's inputs that already lie in device memory. A pool holds `pool_count` prepared step input areas of `byte_count`
+ * bytes at `pool_stride` apart (each beginning with its struct step_block, sequences strictly increasing); the kernel
+ * copies entry (cursor mod pool_count) to destination_offset and advances the 64-bit cursor at cursor_offset. One
+ * block of 1024 threads; byte_count a multiple of 16. (The reference's step driver uploads each step block from the
+ * host, source/step.c:1421-1497; this keeps a run of steps on the device, for captured graphs and for timing with
+ * resident inputs.) */
+#define KERNEL_STEP_INPUT_SELECT "step_input_select"
+struct step_input_select_arguments {
+	uint64_t pool_offset;
+	uint64_t pool_stride;
+	uint64_t destination_offset;
+	uint64_t cursor_offset;
+	uint32_t pool_count;
+	uint32_t byte_count;
+};
+
 #ifdef __cplusplus
 #define AB_RECORD_HAS(record, bytes) static_assert(sizeof(struct record) == (bytes), #record " ABI")
 #else
@@ -349,5 +366,6 @@ AB_RECORD_HAS(ordered_collective_arguments, 80);
 AB_RECORD_HAS(ordered_reduce_bf16_arguments, 96);
 AB_RECORD_HAS(ordered_row_sum_publish_arguments, 96);
 AB_RECORD_HAS(router_select_b200_arguments, 80);
+AB_RECORD_HAS(step_input_select_arguments, 40);
 
 #endif

@@ -25,6 +25,14 @@ MUST_CHECK result_status router_select_b200_prepare(const struct router_select_b
 						    const struct backend_operations *backend, struct device_card *card,
 						    struct kernel_launch *launch_out);
 
+/* No reference counterpart (its step driver uploads every step block from the host). Checks the pool, the destination
+ * and the cursor ranges (16-byte aligned, inside the arena, disjoint), pool_count >= 1, byte_count a positive multiple
+ * of 16 not above pool_stride. One launch: ("kernel_router_b200", "step_input_select"), one block. */
+MUST_CHECK result_status step_input_select_prepare(const struct step_input_select_arguments *arguments,
+						   uint64_t arena_byte_count,
+						   const struct backend_operations *backend, struct device_card *card,
+						   struct kernel_launch *launch_out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,6 +1,7 @@
 """ctypes bindings of the CPU oracle (oracle/liboracle.so) and of the reference's own host code (oracle/_ref).
 
-Test infrastructure: only tests, the smoke check and the benchmark's CPU-baseline legs import this module.
+TEST INFRASTRUCTURE: only tests, the smoke check and the benchmark's CPU-baseline legs import this module; the
+product package (anemone_b200/) never does.
 """
 import ctypes as C
 import os
@@ -8,8 +9,8 @@ import subprocess
 
 import numpy as np
 
-ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-ORACLE_DIR = os.path.join(ROOT, "oracle")
+ORACLE_DIR = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(ORACLE_DIR)
 ORACLE_SO = os.path.join(ORACLE_DIR, "liboracle.so")
 REFERENCE_SO = os.path.join(ORACLE_DIR, "_ref", "libanemone_ref.so")
 

@@ -15,14 +15,14 @@ def pytest_configure(config):
 
 @pytest.fixture(scope="session")
 def oracle():
-    from tests import oracle_lib
+    from oracle import binding as oracle_lib
     return oracle_lib.load_oracle()
 
 
 @pytest.fixture(scope="session")
 def reference():
     """The reference's own host code compiled from its sources (oracle/_ref), or skip where it was never built."""
-    from tests import oracle_lib
+    from oracle import binding as oracle_lib
     lib = oracle_lib.load_reference()
     if lib is None:
         pytest.skip("oracle/_ref/libanemone_ref.so not built (reference tree absent)")

@@ -8,7 +8,7 @@ import numpy as np
 from anemone_b200 import records as R
 from anemone_b200 import synthetic
 from anemone_b200.api import Layout
-from tests.oracle_lib import f32p, ptr, u32p, u64p, u8p
+from oracle.binding import f32p, ptr, u32p, u64p, u8p
 
 GUARD = 64
 GUARD_BYTE = 0xC3

@@ -14,7 +14,7 @@ import numpy as np
 
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 sys.path.insert(0, ROOT)
-from tests.oracle_lib import load_reference, pointer_array, ptr, u8p  # noqa: E402
+from oracle.binding import load_reference, pointer_array, ptr, u8p  # noqa: E402
 
 
 def fnv64(values):

@@ -13,7 +13,7 @@ import pytest
 
 from anemone_b200 import records as R
 from tests import golden_util
-from tests.oracle_lib import f32p, pointer_array, ptr, u16p
+from oracle.binding import f32p, pointer_array, ptr, u16p
 
 pytestmark = pytest.mark.gpu
 

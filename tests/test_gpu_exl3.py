@@ -12,7 +12,7 @@ from anemone_b200 import records as R
 from anemone_b200 import synthetic
 from tests import golden_util
 from tests.exl3_cases import ChainCase
-from tests.oracle_lib import ptr, u16p, u8p
+from oracle.binding import ptr, u16p, u8p
 
 pytestmark = pytest.mark.gpu
 

@@ -8,7 +8,7 @@ import pytest
 from anemone_b200 import records as R
 from anemone_b200 import synthetic
 from anemone_b200.moe import MoeConfig, MoeLayer, MoeLayout, local_matrices
-from tests import moe_reference
+from oracle import moe_reference
 
 pytestmark = pytest.mark.gpu
 
@@ -91,8 +91,8 @@ def test_router_job_table_matches_oracle(api, oracle):
     experts, want_weights = moe_reference.route(oracle, config, scores)
     assert np.array_equal(picks[:rows], experts)
     assert 10 in picks[3] and 200 in picks[3] and 77 in picks[5]
-    assert np.allclose(weights[:rows], want_weights, rtol=2e-6, atol=0)
-    from tests.oracle_lib import f32p, ptr, u32p, u64p
+    assert np.allclose(weights[:rows], want_weights, rtol=2e-6, atol=0, equal_nan=True)
+    from oracle.binding import f32p, ptr, u32p, u64p
     want_jobs = (R.ExpertJob * L.job_capacity)()
     count = oracle.orc_router_jobs(ptr(experts, u32p), ptr(want_weights, f32p), rows, config.picks, config.experts,
                                    config.shared, ptr(table, u64p), L.job_capacity, C.byref(want_jobs))
@@ -102,5 +102,5 @@ def test_router_job_table_matches_oracle(api, oracle):
         assert (g.gate_offset, g.up_offset, g.down_offset, g.row_count, g.expert) == \
                (w.gate_offset, w.up_offset, w.down_offset, w.row_count, w.expert), index
         assert list(g.pair_index) == list(w.pair_index)
-        assert np.allclose(list(g.route_weight), list(w.route_weight), rtol=2e-6, atol=0)
+        assert np.allclose(list(g.route_weight), list(w.route_weight), rtol=2e-6, atol=0, equal_nan=True)
     assert count > rows

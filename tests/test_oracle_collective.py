@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 
 from tests import golden_util
-from tests.oracle_lib import f32p, pointer_array, ptr, u16p, u32p, u64p, u8p
+from oracle.binding import f32p, pointer_array, ptr, u16p, u32p, u64p, u8p
 
 RANKS, ELEMENTS, BIG = 5, 7, 16777216.0
 

@@ -9,7 +9,7 @@ import os
 import numpy as np
 import pytest
 
-from tests.oracle_lib import ptr, splitmix_words, u8p, u16p, f32p
+from oracle.binding import ptr, splitmix_words, u8p, u16p, f32p
 
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
 WIDTHS = [2, 40, 3, 4]
