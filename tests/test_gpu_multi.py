@@ -1,0 +1,140 @@
+"""Real multi-GPU runs of the reduction and of the tensor-parallel layer: one process driving R cards (the reference's
+arrangement), peer loads over NVLink. Skipped on a machine with fewer than two GPUs; every rank's kernels are queued
+before the host waits for any, and every device wait is bounded."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from anemone_b200 import records as R
+from anemone_b200 import synthetic
+from anemone_b200.moe import MoeConfig, MoeLayer, MoeLayout, local_matrices
+from oracle import moe_reference
+from oracle.binding import f32p, pointer_array, ptr, u16p
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def api():
+    from anemone_b200 import api as module
+    if module.card_count() < 2:
+        pytest.skip("needs at least two GPUs")
+    return module
+
+
+def world_sizes(api):
+    return [size for size in (2, 4, 8) if size <= api.card_count()]
+
+
+def test_layer_tensor_parallel(api, oracle):
+    for ranks in world_sizes(api):
+        config = MoeConfig(hidden=512, inner=128 * ranks * 2, experts=24, shared=1, picks=4, row_capacity=8)
+        rng = np.random.default_rng(300 + ranks)
+        widths = np.concatenate([synthetic.expert_widths(rng, config.experts), [3]]).astype(np.uint32)
+        matrices = [(synthetic.exl3_matrix(rng, config.hidden, config.inner, int(w)),
+                     synthetic.exl3_matrix(rng, config.hidden, config.inner, int(w)),
+                     synthetic.exl3_matrix(rng, config.inner, config.hidden, int(w))) for w in widths]
+        cards, layers = [], []
+        try:
+            for rank in range(ranks):
+                card = api.Card(rank, MoeLayout(config, widths, ranks, rank).arena_bytes)
+                cards.append(card)
+                local = [local_matrices(*matrices[e], config, int(widths[e]), ranks, rank)
+                         for e in range(config.total_experts)]
+                layers.append(MoeLayer(card, config, widths, local, rank=rank, rank_count=ranks))
+            for layer in layers:
+                layer.connect_local(layers)
+            for card in cards:
+                card.wait()
+            for step in range(4):
+                rows = [8, 3, 8, 1][step]
+                tokens = synthetic.tokens(rng, rows, config.hidden)
+                scores = rng.normal(0, 1, size=(rows, config.experts)).astype(np.float32)
+                expected, partials, _, _ = moe_reference.layer(oracle, config, widths, matrices, tokens, scores, ranks)
+                result_at = api.align(layers[0].layout.step_input_bytes, 4096)
+                tickets = []
+                for layer in layers:  # queue every rank before waiting for any
+                    layer.sequence += 1
+                    layer.stage_step(0, layer.sequence, tokens, scores)
+                    tickets.append(layer.submit(0, result_at, rows))
+                outputs = []
+                for layer, ticket in zip(layers, tickets):
+                    layer.card.transfer_wait(ticket)
+                    layer.check_status()
+                    nbytes = rows * config.hidden * 2
+                    outputs.append(layer.card.staging_view[result_at:result_at + nbytes].view(np.uint16).copy())
+                for rank in range(1, ranks):  # every rank holds the same bits
+                    assert np.array_equal(outputs[rank], outputs[0])
+                a = synthetic.from_bfloat16(outputs[0])
+                b = synthetic.from_bfloat16(expected.reshape(-1))
+                assert np.abs(a - b).max() <= 2e-2
+                assert float(a.astype(np.float64) @ b.astype(np.float64)) / (np.linalg.norm(a) * np.linalg.norm(b)) >= 0.9999
+                # bit-exact ordered reduction: re-reduce the FP32 rows the ranks actually published, on the CPU oracle
+                published = []
+                for layer in layers:
+                    L = layer.layout
+                    slot = L.region + (layer.sequence & 1) * L.parity_stride + L.slot_input
+                    published.append(layer.card.download(slot, rows * config.hidden * 4, np.float32))
+                want = np.zeros(rows * config.hidden, dtype=np.uint16)
+                oracle.orc_ordered_reduce_bf16(pointer_array(published), ranks, want.size, ptr(want, u16p))
+                assert np.array_equal(outputs[0], want)
+        finally:
+            for card in cards:
+                card.close()
+
+
+def test_fp32_all_reduce_across_cards(api, oracle):
+    lib = api.library()
+    lib.ordered_collective_kernels_prepare.argtypes = [C.POINTER(api.BackendOperations), C.c_void_p,
+                                                       C.POINTER(R.OrderedCollectiveKernels)]
+    lib.ordered_collective_prepare.argtypes = [C.POINTER(R.OrderedCollectiveDescription),
+                                               C.POINTER(R.OrderedCollectiveKernels), C.POINTER(R.KernelLaunch)]
+    for ranks in world_sizes(api):
+        elements = 8 * 4096
+        rng = np.random.default_rng(500 + ranks)
+        inputs = [rng.normal(0, 0.05, elements).astype(np.float32) for _ in range(ranks)]
+        inputs[0][0], inputs[1][0] = 16777216.0, 1.0
+        layout = api.Layout()
+        peer_table, step = layout.take(16 * 32), layout.take(16)
+        stride = api.align(384 + 12 * elements, 128)
+        region = layout.take(2 * stride, 128)
+        arena_bytes = layout.take(4096, 4096)
+        cards = [api.Card(rank, arena_bytes) for rank in range(ranks)]
+        try:
+            launches = {}
+            for rank, card in enumerate(cards):
+                card.fill(0, 0, arena_bytes)
+                peers = (R.OrderedPeer * ranks)()
+                for peer in range(ranks):
+                    peers[peer].region_offset = region
+                card.upload(peer_table, np.frombuffer(bytes(peers), dtype=np.uint8))
+                for peer, other in enumerate(cards):
+                    card.peer_connect(other, 0, peer_table + 32 * peer)
+                kernels = R.OrderedCollectiveKernels()
+                api.check(lib.ordered_collective_kernels_prepare(card.ops_pointer, card.handle, C.byref(kernels)), "k")
+                for operation in (0, 1):
+                    arguments = R.OrderedCollective(peer_table, region, 384, 384 + 4 * elements, 384 + 8 * elements,
+                                                    step, stride, 2_000_000_000, elements, ranks, rank, 0)
+                    description = R.OrderedCollectiveDescription(arguments, arena_bytes, operation)
+                    launch = R.KernelLaunch()
+                    api.check(lib.ordered_collective_prepare(C.byref(description), C.byref(kernels), C.byref(launch)),
+                              "prepare")
+                    launches[(rank, operation)] = launch
+            expected = np.zeros(elements, dtype=np.float32)
+            oracle.orc_ordered_sum(pointer_array(inputs), ranks, elements, ptr(expected, f32p))
+            sequence = 0
+            for operation in (0, 1, 0, 1):
+                sequence += 1
+                for rank, card in enumerate(cards):
+                    card.upload(step, np.frombuffer(bytes(R.StepBlock(sequence, 1, 0)), dtype=np.uint8))
+                    card.upload(region + (sequence & 1) * stride + 384, inputs[rank])
+                for rank, card in enumerate(cards):
+                    card.run([launches[(rank, operation)]])
+                for rank, card in enumerate(cards):
+                    card.wait()
+                    got = card.download(region + (sequence & 1) * stride + 384 + 4 * elements, 4 * elements, np.float32)
+                    assert np.array_equal(got.view(np.uint32), expected.view(np.uint32)), (ranks, operation, rank)
+        finally:
+            for card in cards:
+                card.close()
