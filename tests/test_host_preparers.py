@@ -1,0 +1,290 @@
+"""The load-time preparers on the host, with a fake backend whose only member is kernel_prepare (the way the
+reference's own host tests drive them: tests/exl3_tp_test.c:23-48, tests/exl3_fast_prepare_test.c) and, where the
+reference's host code was compiled (oracle/_ref), byte for byte against its preparers."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from anemone_b200 import api, synthetic
+from anemone_b200 import records as R
+
+U32P = C.POINTER(C.c_uint32)
+
+
+class Slice(C.Structure):
+    _fields_ = [(name, C.c_uint32) for name in ("input_size", "output_size", "input_begin", "input_count",
+                                                "output_begin", "output_count", "bits_per_weight", "reserved_zero")]
+
+
+class SliceSizes(C.Structure):
+    _fields_ = [("source_bytes", C.c_uint64), ("packed_bytes", C.c_uint64)]
+
+
+class ShardPlan(C.Structure):
+    _fields_ = [("gate_up", Slice), ("down", Slice), ("rank_count", C.c_uint32), ("rank", C.c_uint32),
+                ("product_slices", C.c_uint32), ("order", C.c_int)]
+
+
+class PassDescription(C.Structure):
+    _fields_ = [("plan", C.POINTER(ShardPlan)), ("record", R.Exl3Expert), ("arena_bytes", C.c_uint64),
+                ("weight_offset", C.c_uint64), ("weight_bytes", C.c_uint64), ("pass_", C.c_int),
+                ("product_tiles", C.c_uint32)]
+
+
+class FakeBackend:
+    """kernel_prepare hands out dense handles and remembers what was asked."""
+
+    def __init__(self):
+        self.asked = []
+        self.table = api.BackendOperations()
+        prototype = dict(api.BackendOperations._fields_)["kernel_prepare"]
+
+        def prepare(card, file_name, function_name, argument_bytes, kernel_out):
+            key = (file_name.decode(), function_name.decode(), argument_bytes)
+            if key not in self.asked:
+                self.asked.append(key)
+            kernel_out[0] = self.asked.index(key)
+            return 0
+        self.callback = prototype(prepare)
+        self.table.kernel_prepare = self.callback
+        self.card = C.c_void_p(0x1000)  # opaque to every preparer: never dereferenced
+
+
+def chain_record(pairs=12, ppr=3, hidden=512, inner=256, jobs=7, width=3):
+    layout = api.Layout()
+    record = R.Exl3Expert()
+    record.jobs_offset = layout.take(jobs * 96)
+    record.input_offset = layout.take(pairs // ppr * hidden * 2)
+    record.operands_offset = layout.take(pairs * hidden * 4)
+    record.products_offset = record.output_offset = layout.take(pairs * hidden * 8)
+    record.hidden_offset = layout.take(pairs * inner * 2)
+    record.input_size, record.inner_size, record.pair_count, record.pairs_per_row = hidden, inner, pairs, ppr
+    record.job_count, record.bits_per_weight, record.activation_limit = jobs, width, 10.0
+    return record, layout.take(0, 4096) + 4096
+
+
+def test_experts_prepare_launches_and_refusals():
+    lib, fake = api.library(), FakeBackend()
+    record, arena = chain_record()
+    launches = (R.KernelLaunch * 5)()
+    assert lib.exl3_experts_prepare(C.byref(record), arena, C.byref(fake.table), fake.card, 100, launches) == 0
+    assert [key[1] for key in fake.asked] == ["exl3_input", "exl3_gate_up_k3", "exl3_activate", "exl3_down_k3",
+                                              "exl3_finish"]
+    assert all(key[0] == "kernel_exl3" and key[2] == 80 for key in fake.asked)
+    grids = [tuple(l.grid) for l in launches]
+    assert grids == [(1, 7, 2), (2, 7, 2), (1, 7, 1), (4, 7, 1), (1, 7, 1)]
+    assert [l.block[0] for l in launches] == [128] * 5
+    assert launches[1].dynamic_shared_byte_count == 6 * 8 * 8 * 16 * 6 and launches[0].dynamic_shared_byte_count == 0
+    for launch in launches:
+        assert bytes(launch.argument[:80]) == bytes(record) and not any(launch.argument[80:])
+    # refusals leave the whole table untouched
+    untouched = bytes(launches)
+    bad = []
+    for field, value in (("reserved_zero", 1), ("pair_count", 0), ("pairs_per_row", 5), ("job_count", 0),
+                         ("job_count", 70000), ("inner_size", 1024), ("activation_limit", 0.0),
+                         ("activation_limit", float("inf")), ("bits_per_weight", 9), ("input_size", 500),
+                         ("output_offset", 64), ("hidden_offset", record.products_offset + 16),
+                         ("jobs_offset", 8), ("operands_offset", arena)):
+        broken = R.Exl3Expert.from_buffer_copy(bytes(record))
+        setattr(broken, field, value)
+        bad.append(lib.exl3_experts_prepare(C.byref(broken), arena, C.byref(fake.table), fake.card, 100, launches))
+    assert all(status == R.STATUS_INVALID_ARGUMENT for status in bad), bad
+    assert lib.exl3_experts_prepare(C.byref(record), arena, C.byref(fake.table), fake.card, 80, launches) == \
+        R.STATUS_UNSUPPORTED
+    assert lib.exl3_experts_prepare(C.byref(record), arena, C.byref(fake.table), fake.card, 7, launches) == \
+        R.STATUS_INVALID_ARGUMENT
+    assert lib.exl3_experts_relaxed_prepare(C.byref(record), arena, C.byref(fake.table), fake.card, 100, launches) == \
+        R.STATUS_UNSUPPORTED
+    assert lib.exl3_experts_prepare(None, arena, C.byref(fake.table), fake.card, 100, launches) == 1
+    assert bytes(launches) == untouched
+    assert lib.exl3_scratch_byte_count(12, 512) == 12 * 512 * 12
+    assert [lib.exl3_width_name(b) for b in (4, 5, 6, 8, 7)] == [b"k2", b"k2_5", b"k3", b"k4", None]
+
+
+def test_moe_prepare():
+    lib, fake = api.library(), FakeBackend()
+    base, arena = chain_record()
+    layout = api.Layout(arena)
+    record = R.Exl3Moe()
+    record.base = base
+    record.base.bits_per_weight = R.EXL3_WIDTH_PER_EXPERT
+    record.base.operands_offset = layout.take(12 * 512 * 4 + 12 * 256 * 2)
+    record.widths_offset, record.row_output_offset, record.expert_count = layout.take(64), layout.take(4 * 512 * 4), 9
+    arena = layout.take(0, 4096) + 4096
+    launches = (R.KernelLaunch * 4)()
+    assert lib.exl3_moe_prepare(C.byref(record), arena, C.byref(fake.table), fake.card, launches) == 0
+    assert [key[1] for key in fake.asked] == ["exl3_moe_input", "exl3_moe_gate_up", "exl3_moe_down", "exl3_moe_row_sum"]
+    assert all(key[0] == "kernel_exl3_b200" and key[2] == 104 for key in fake.asked)
+    untouched = bytes(launches)
+    record.row_output_offset = record.base.products_offset  # overlaps the products
+    assert lib.exl3_moe_prepare(C.byref(record), arena, C.byref(fake.table), fake.card, launches) == 1
+    assert bytes(launches) == untouched
+
+
+def test_slices_and_plans_against_numpy():
+    lib = api.library()
+    lib.bb_exl3_matrix_slice_prepare.argtypes = [C.POINTER(Slice), C.POINTER(SliceSizes)]
+    lib.bb_exl3_matrix_slice_copy.argtypes = [C.POINTER(Slice), C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t]
+    lib.bb_exl3_inner_shard_prepare.argtypes = [C.c_uint32] * 5 + [C.POINTER(ShardPlan)]
+    rng = np.random.default_rng(4)
+    for stored in (2, 40, 3, 4):
+        matrix = synthetic.exl3_matrix(rng, 512, 768, stored)
+        for ranks in (1, 2, 4):
+            covered = 0
+            for rank in range(ranks):
+                plan = ShardPlan()
+                assert lib.bb_exl3_inner_shard_prepare(512, 768, stored, ranks, rank, C.byref(plan)) == 0
+                assert plan.gate_up.output_begin == covered and plan.down.input_begin == covered
+                covered += plan.gate_up.output_count
+                sizes = SliceSizes()
+                assert lib.bb_exl3_matrix_slice_prepare(C.byref(plan.gate_up), C.byref(sizes)) == 0
+                assert sizes.source_bytes == matrix.size
+                packed = np.zeros(sizes.packed_bytes, dtype=np.uint8)
+                assert lib.bb_exl3_matrix_slice_copy(C.byref(plan.gate_up), matrix.ctypes.data, matrix.size,
+                                                     packed.ctypes.data, packed.size) == 0
+                want = synthetic.slice_matrix(matrix, 512, 768, stored, 0, 512, plan.gate_up.output_begin,
+                                              plan.gate_up.output_count)
+                assert np.array_equal(packed, want)
+            assert covered == 768
+    plan = ShardPlan()
+    assert lib.bb_exl3_inner_shard_prepare(512, 768, 3, 3, 0, C.byref(plan)) == 1  # ranks 1, 2, 4, 8 only
+    assert lib.bb_exl3_inner_shard_prepare(512, 256, 3, 4, 0, C.byref(plan)) == 1  # fewer blocks than ranks
+
+
+def test_slice_keeps_every_state(oracle):
+    from oracle.binding import ptr, u16p, u8p
+    rng = np.random.default_rng(9)
+    for stored in (2, 40, 3, 4):
+        matrix = synthetic.exl3_matrix(rng, 256, 256, stored)
+        full = np.zeros((256, 256), dtype=np.uint16)
+        oracle.orc_exl3_states(ptr(matrix, u8p), 256, 256, stored, ptr(full, u16p))
+        for (ib, ic, ob, oc) in ((0, 256, 128, 128), (128, 128, 0, 256)):
+            piece = synthetic.slice_matrix(matrix, 256, 256, stored, ib, ic, ob, oc)
+            states = np.zeros((ic, oc), dtype=np.uint16)
+            oracle.orc_exl3_states(ptr(piece, u8p), ic, oc, stored, ptr(states, u16p))
+            assert np.array_equal(states, full[ib:ib + ic, ob:ob + oc])
+
+
+def test_router_and_reduce_prepare():
+    lib, fake = api.library(), FakeBackend()
+    from anemone_b200.moe import MoeConfig, MoeLayout
+    config = MoeConfig(hidden=512, inner=256, experts=32, shared=1, picks=4, row_capacity=8)
+    L = MoeLayout(config, np.full(33, 3, dtype=np.uint32), 2, 1)
+    lib.router_select_b200_prepare.argtypes = [C.POINTER(R.RouterSelectB200), C.c_uint64,
+                                               C.POINTER(api.BackendOperations), C.c_void_p, C.POINTER(R.KernelLaunch)]
+    lib.router_b200_job_capacity.restype = C.c_uint32
+    assert lib.router_b200_job_capacity(8, 4, 1) == 33 == L.job_capacity
+    router = R.RouterSelectB200(L.scores, L.expert_table, L.picks, L.weights, L.jobs, L.step, 32, 1, 4, 8,
+                                L.job_capacity, 0, 1.0, 0)
+    launch = R.KernelLaunch()
+    assert lib.router_select_b200_prepare(C.byref(router), L.arena_bytes, C.byref(fake.table), fake.card,
+                                          C.byref(launch)) == 0
+    assert tuple(launch.grid) == (1, 1, 1) and launch.block[0] == 1024
+    untouched = bytes(launch)
+    for field, value in (("picks", 0), ("picks", 17), ("expert_count", 600), ("row_capacity", 65),
+                         ("job_capacity", 32), ("scoring", 2), ("route_scale", 0.0), ("jobs_offset", L.step)):
+        broken = R.RouterSelectB200.from_buffer_copy(bytes(router))
+        setattr(broken, field, value)
+        assert lib.router_select_b200_prepare(C.byref(broken), L.arena_bytes, C.byref(fake.table), fake.card,
+                                              C.byref(launch)) == 1, field
+    assert bytes(launch) == untouched
+    lib.ordered_reduce_bf16_prepare.argtypes = [C.POINTER(R.OrderedReduceBf16Description),
+                                                C.POINTER(api.BackendOperations), C.c_void_p, C.POINTER(R.KernelLaunch)]
+    description = R.OrderedReduceBf16Description()
+    description.reduce.collective = R.OrderedCollective(L.peer_table, L.region, L.slot_input, L.result, 0, L.step,
+                                                        L.parity_stride, 1000, 8 * 512, 2, 1, 0)
+    description.reduce.status_offset, description.reduce.width = L.status, 512
+    description.pair_output_offset, description.arena_byte_count = L.products, L.arena_bytes
+    description.pairs_per_row, description.row_capacity = 5, 8
+    launches = (R.KernelLaunch * 2)()
+    assert lib.ordered_reduce_bf16_prepare(C.byref(description), C.byref(fake.table), fake.card, launches) == 0
+    assert tuple(launches[0].grid) == (1, 8, 1) and tuple(launches[1].grid) == (4, 1, 1)
+    untouched = bytes(launches)
+    for path, value in (("rank", 2), ("rank_count", 17), ("deadline_cycles", 0), ("region_offset", L.region + 64),
+                        ("input_offset", 128), ("parity_stride", L.parity_stride - 128)):
+        broken = R.OrderedReduceBf16Description.from_buffer_copy(bytes(description))
+        setattr(broken.reduce.collective, path, value)
+        assert lib.ordered_reduce_bf16_prepare(C.byref(broken), C.byref(fake.table), fake.card, launches) == 1, path
+    description.reduce.width = 510
+    assert lib.ordered_reduce_bf16_prepare(C.byref(description), C.byref(fake.table), fake.card, launches) == 1
+    assert bytes(launches) == untouched
+
+
+# ---- byte for byte against the reference's own preparers (oracle/_ref) ----
+
+def test_reconstruct_and_collective_launches_equal_reference(reference):
+    lib = api.library()
+    record = R.Exl3Reconstruct(0, 1 << 20, 256, 384, 3, 0)
+    ours, theirs = R.KernelLaunch(), R.KernelLaunch()
+    reference.exl3_reconstruct_prepare.argtypes = lib.exl3_reconstruct_prepare.argtypes
+    assert lib.exl3_reconstruct_prepare(C.byref(record), 1 << 22, 5, C.byref(ours)) == 0
+    assert reference.exl3_reconstruct_prepare(C.byref(record), 1 << 22, 5, C.byref(theirs)) == 0
+    assert bytes(ours) == bytes(theirs)
+    for field, value in (("matrix_offset", 32), ("output_offset", 1 << 22), ("bits_per_weight", 5), ("input_size", 100)):
+        broken = R.Exl3Reconstruct.from_buffer_copy(bytes(record))
+        setattr(broken, field, value)
+        assert lib.exl3_reconstruct_prepare(C.byref(broken), 1 << 22, 5, C.byref(ours)) == \
+            reference.exl3_reconstruct_prepare(C.byref(broken), 1 << 22, 5, C.byref(theirs)) != 0
+    kernels = R.OrderedCollectiveKernels((C.c_uint32 * 4)(3, 4, 5, 6))
+    prototype = [C.POINTER(R.OrderedCollectiveDescription), C.POINTER(R.OrderedCollectiveKernels),
+                 C.POINTER(R.KernelLaunch)]
+    lib.ordered_collective_prepare.argtypes = reference.ordered_collective_prepare.argtypes = prototype
+    good = R.OrderedCollective(0, 4096, 384, 384 + 4096, 384 + 8192, 1024, 16384, 1000, 1000, 4, 2, 0)
+    cases = [good]
+    for field, value in (("rank", 4), ("element_count", 0), ("element_count", 300000), ("region_offset", 4100),
+                         ("input_offset", 100), ("scratch_offset", 384 + 4096), ("deadline_cycles", 0),
+                         ("step_offset", 4096), ("peer_table_offset", 4), ("parity_stride", 8192)):
+        broken = R.OrderedCollective.from_buffer_copy(bytes(good))
+        setattr(broken, field, value)
+        cases.append(broken)
+    for arguments in cases:
+        for operation in range(4):
+            description = R.OrderedCollectiveDescription(arguments, 1 << 20, operation)
+            ours, theirs = R.KernelLaunch(), R.KernelLaunch()
+            a = lib.ordered_collective_prepare(C.byref(description), C.byref(kernels), C.byref(ours))
+            b = reference.ordered_collective_prepare(C.byref(description), C.byref(kernels), C.byref(theirs))
+            assert a == b and bytes(ours) == bytes(theirs)
+
+
+def test_output_shard_plan_and_slice_copy_equal_reference(reference):
+    lib = api.library()
+    prototype = [C.c_uint32] * 5 + [C.c_int, C.POINTER(ShardPlan)]
+    lib.bb_exl3_output_shard_prepare.argtypes = reference.bb_exl3_output_shard_prepare.argtypes = prototype
+    copy_prototype = [C.POINTER(Slice), C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t]
+    lib.bb_exl3_matrix_slice_copy.argtypes = reference.bb_exl3_matrix_slice_copy.argtypes = copy_prototype
+    rng = np.random.default_rng(12)
+    for stored in (2, 40, 3, 4):
+        for ranks in (1, 4):
+            for rank in range(ranks):
+                ours, theirs = ShardPlan(), ShardPlan()
+                assert lib.bb_exl3_output_shard_prepare(5120, 2304, stored, ranks, rank, 0, C.byref(ours)) == 0
+                assert reference.bb_exl3_output_shard_prepare(5120, 2304, stored, ranks, rank, 0, C.byref(theirs)) == 0
+                assert bytes(ours) == bytes(theirs)
+        matrix = synthetic.exl3_matrix(rng, 256, 384, stored)
+        piece = Slice(256, 384, 128, 128, 128, 256, stored, 0)
+        size = synthetic.matrix_bytes(128, 256, stored)
+        a, b = np.zeros(size, dtype=np.uint8), np.ones(size, dtype=np.uint8)
+        assert lib.bb_exl3_matrix_slice_copy(C.byref(piece), matrix.ctypes.data, matrix.size, a.ctypes.data, size) == 0
+        assert reference.bb_exl3_matrix_slice_copy(C.byref(piece), matrix.ctypes.data, matrix.size, b.ctypes.data,
+                                                   size) == 0
+        assert np.array_equal(a, b)
+        assert lib.bb_exl3_matrix_slice_copy(C.byref(piece), matrix.ctypes.data, matrix.size, a.ctypes.data,
+                                             size - 1) == 1
+
+
+def test_collective_host_equals_reference(reference):
+    from oracle.binding import f32p, pointer_array
+    lib = api.library()
+    lib.ordered_collective_host.argtypes = [C.POINTER(f32p), C.POINTER(f32p), C.c_uint32, C.c_uint32, C.c_int]
+    rng = np.random.default_rng(2)
+    inputs = [rng.normal(0, 0.05, 999).astype(np.float32) for _ in range(5)]
+    inputs[0][0], inputs[2][0] = 16777216.0, -16777216.0
+    for operation in range(4):
+        ours = [np.full(999, -99, dtype=np.float32) for _ in range(5)]
+        theirs = [np.full(999, -99, dtype=np.float32) for _ in range(5)]
+        assert lib.ordered_collective_host(pointer_array(inputs), pointer_array(ours), 5, 999, operation) == 0
+        assert reference.ordered_collective_host(pointer_array(inputs), pointer_array(theirs), 5, 999, operation) == 0
+        for a, b in zip(ours, theirs):
+            assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+    assert lib.ordered_collective_host(pointer_array(inputs), pointer_array(inputs), 5, 999, 0) == 1  # overlap
