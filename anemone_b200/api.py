@@ -95,6 +95,8 @@ def library():
                                            C.c_uint32, C.POINTER(R.KernelLaunch)]
         lib.exl3_moe_prepare.argtypes = [C.POINTER(R.Exl3Moe), C.c_uint64, C.POINTER(BackendOperations), _card,
                                          C.POINTER(R.KernelLaunch)]
+        lib.exl3_moe_sizes.restype = None
+        lib.exl3_moe_sizes.argtypes = [C.c_uint32] * 4 + [C.POINTER(R.Exl3MoeSizes)]
         lib.bb_exl3_row_sum_prepare.argtypes = [C.POINTER(R.ExpertRowSum), C.c_uint32, C.c_uint64,
                                                 C.POINTER(BackendOperations), _card, C.POINTER(R.KernelLaunch)]
         _library = lib
@@ -109,6 +111,13 @@ def card_count():
     count = C.c_uint32(0)
     check(operations().contents.card_count(C.byref(count)), "card_count")
     return count.value
+
+
+def moe_sizes(pair_count, job_count, input_size, inner_size):
+    """Scratch sizes of the fused launches for these shapes (exl3_moe_sizes)."""
+    sizes = R.Exl3MoeSizes()
+    library().exl3_moe_sizes(pair_count, job_count, input_size, inner_size, C.byref(sizes))
+    return sizes
 
 
 def align(value, alignment):

@@ -105,7 +105,7 @@ static result_status chain_validate(const char *what, const struct exl3_expert_r
 	const uint64_t inputs = (uint64_t)record->pair_count * record->input_size;
 	if (inputs > UINT64_MAX / (EXL3_OPERAND_BYTES_PER_INPUT + EXL3_PRODUCT_BYTES_PER_INPUT))
 		return STATUS_INVALID_ARGUMENT;
-	struct checked_range ranges[8] = {
+	struct checked_range ranges[16] = {
 		{ "jobs", record->jobs_offset, (uint64_t)record->job_count * sizeof(struct expert_job_record) },
 		{ "input", record->input_offset, inputs / record->pairs_per_row * EXL3_HALF_BYTES },
 		{ "operands", record->operands_offset, inputs * EXL3_OPERAND_BYTES_PER_INPUT },
@@ -197,6 +197,25 @@ result_status exl3_experts_relaxed_prepare(const struct exl3_expert_record *reco
 	return valid != STATUS_OK ? valid : STATUS_UNSUPPORTED;
 }
 
+void exl3_moe_sizes(uint32_t pair_count, uint32_t job_count, uint32_t input_size, uint32_t inner_size,
+		    struct exl3_moe_sizes *sizes_out)
+{
+	struct exl3_moe_sizes sizes = { 0, 0, 0, 0, 0 };
+	if (sizes_out == NULL)
+		return;
+	if (input_size != 0 && inner_size != 0 && input_size % EXL3_TRANSFORM == 0 && inner_size % EXL3_TRANSFORM == 0) {
+		sizes.gate_up_splits = exl3_moe_splits(input_size);
+		sizes.down_splits = exl3_moe_splits(inner_size);
+		const uint64_t gate_up = (uint64_t)EXL3_PROJECTIONS * sizes.gate_up_splits * pair_count * inner_size * 4u;
+		const uint64_t down = (uint64_t)sizes.down_splits * pair_count * input_size * 4u;
+		sizes.product_bytes = gate_up > down ? gate_up : down;
+		sizes.operand_bytes = (uint64_t)pair_count * input_size * EXL3_OPERAND_BYTES_PER_INPUT +
+				      (uint64_t)pair_count * inner_size * EXL3_HALF_BYTES;
+		sizes.counter_bytes = (uint64_t)job_count * (inner_size / EXL3_TRANSFORM + input_size / EXL3_TRANSFORM) * 4u;
+	}
+	*sizes_out = sizes;
+}
+
 result_status exl3_moe_prepare(const struct exl3_moe_record *record, uint64_t arena_byte_count,
 			       const struct backend_operations *backend, struct device_card *card,
 			       struct kernel_launch *launches_out)
@@ -207,18 +226,25 @@ result_status exl3_moe_prepare(const struct exl3_moe_record *record, uint64_t ar
 	const struct exl3_expert_record *const base = &record->base;
 	const bool per_expert = base->bits_per_weight == EXL3_WIDTH_PER_EXPERT;
 	const uint64_t rows = base->pairs_per_row == 0 ? 0 : base->pair_count / base->pairs_per_row;
-	/* the fused gate/up launch writes the down operands while other CTAs still read the gate/up operands, so they
-	 * live behind them: FP16 [pair][inner] at operands_offset + 4 pair_count input_size */
-	const uint64_t gate_up_operand_bytes = (uint64_t)base->pair_count * base->input_size * EXL3_OPERAND_BYTES_PER_INPUT;
-	const struct checked_range extra[3] = {
+	struct exl3_moe_sizes sizes;
+	exl3_moe_sizes(base->pair_count, base->job_count, base->input_size, base->inner_size, &sizes);
+	if (sizes.gate_up_splits == 0 || base->pair_count == 0 || base->input_size == 0)
+		return STATUS_INVALID_ARGUMENT;
+	/* the chain's own checks cover 4 pair_count input_size bytes of operands and 8 pair_count input_size bytes of
+	 * products from the same offsets; what the fused launches use beyond that is checked as further ranges */
+	const uint64_t chain_operands = (uint64_t)base->pair_count * base->input_size * EXL3_OPERAND_BYTES_PER_INPUT;
+	const uint64_t chain_products = (uint64_t)base->pair_count * base->input_size * EXL3_PRODUCT_BYTES_PER_INPUT;
+	if (base->operands_offset > UINT64_MAX - chain_operands || base->products_offset > UINT64_MAX - chain_products)
+		return STATUS_INVALID_ARGUMENT;
+	const struct checked_range extra[5] = {
 		{ "row output", record->row_output_offset, rows * base->input_size * 4u },
 		{ "width table", record->widths_offset, per_expert ? (uint64_t)record->expert_count * 4u : 0u },
-		{ "down operands", base->operands_offset + gate_up_operand_bytes,
-		  (uint64_t)base->pair_count * base->inner_size * EXL3_HALF_BYTES }
+		{ "down operands", base->operands_offset + chain_operands, sizes.operand_bytes - chain_operands },
+		{ "split products", base->products_offset + chain_products,
+		  sizes.product_bytes > chain_products ? sizes.product_bytes - chain_products : 0u },
+		{ "counters", record->counters_offset, sizes.counter_bytes }
 	};
-	if (base->operands_offset > UINT64_MAX - gate_up_operand_bytes)
-		return STATUS_INVALID_ARGUMENT;
-	const result_status valid = chain_validate("EXL3 MoE", base, arena_byte_count, !per_expert, extra, 3);
+	const result_status valid = chain_validate("EXL3 MoE", base, arena_byte_count, !per_expert, extra, 5);
 	if (valid != STATUS_OK)
 		return valid;
 	static const char *const names[EXL3_MOE_LAUNCHES] = { "exl3_moe_input", "exl3_moe_gate_up", "exl3_moe_down",
@@ -229,8 +255,9 @@ result_status exl3_moe_prepare(const struct exl3_moe_record *record, uint64_t ar
 	const struct {
 		uint32_t x, y, z, threads, shared;
 	} shapes[EXL3_MOE_LAUNCHES] = { { transform_grid(H), jobs, EXL3_PROJECTIONS, EXL3_TRANSFORM_THREADS, 0 },
-					{ I / EXL3_TRANSFORM, jobs, 1, EXL3_PRODUCT_THREADS, shared },
-					{ H / EXL3_TRANSFORM, jobs, 1, EXL3_PRODUCT_THREADS, shared },
+					{ I / EXL3_TRANSFORM * sizes.gate_up_splits, jobs, EXL3_PROJECTIONS,
+					  EXL3_PRODUCT_THREADS, shared },
+					{ H / EXL3_TRANSFORM * sizes.down_splits, jobs, 1, EXL3_PRODUCT_THREADS, shared },
 					{ (H + EXL3_ROW_SUM_THREADS - 1u) / EXL3_ROW_SUM_THREADS, (uint32_t)rows, 1,
 					  EXL3_ROW_SUM_THREADS, 0 } };
 	struct kernel_launch launches[EXL3_MOE_LAUNCHES];

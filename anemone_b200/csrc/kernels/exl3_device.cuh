@@ -8,7 +8,8 @@
  *   - a product core: one CTA computes 128 outputs of one job for up to eight rows. The CTA's trellis rows arrive
  *     through a ring of shared-memory stages filled by bulk asynchronous copies (cp.async.bulk, completion on an
  *     mbarrier); four warps take interleaved K steps, decode in registers and accumulate in FP32 on the tensor cores;
- *     the four partial sums are added in warp order from +0.
+ *     the four partial sums are added in warp order from +0. A CTA may take a part of K only (split K): the caller then
+ *     adds the parts in a fixed order.
  *
  * Every mbarrier wait is bounded: a wait that runs out raises exl3_wait_expired (a module global the host can read)
  * and the CTA leaves without touching its outputs; nothing traps.
@@ -111,7 +112,9 @@ __device__ __forceinline__ uint32_t exl3_value_bits(uint32_t state)
 
 __device__ __forceinline__ uint32_t exl3_pair(uint32_t low_state, uint32_t high_state)
 {
-	const uint32_t packed = __byte_perm(exl3_value_bits(low_state), exl3_value_bits(high_state), 0x5410);
+	/* low | high << 16 as a multiply-add: the integer multiplier's pipe instead of the ALU's, which the window
+	 * shifts and masks keep busy */
+	const uint32_t packed = exl3_value_bits(high_state) * 65536u + exl3_value_bits(low_state);
 	const __half2 scale = __halves2half2(__ushort_as_half(EXL3_MUL1_SCALE), __ushort_as_half(EXL3_MUL1_SCALE));
 	const __half2 bias = __halves2half2(__ushort_as_half(EXL3_MUL1_BIAS), __ushort_as_half(EXL3_MUL1_BIAS));
 	const __half2 value = __hfma2(*reinterpret_cast<const __half2 *>(&packed), scale, bias);
@@ -188,22 +191,24 @@ struct exl3_product_shared {
 /* sums[tile][c]: this thread's share of the CTA's 128 outputs x 8 columns after the cross-warp reduction: thread
  * (warp w, lane (g, t)) returns, for tiles j = 2 w and 2 w + 1, the m16n8 accumulator layout
  *   c0: (output 16 j + g, column 2 t)   c1: (16 j + g, 2 t + 1)   c2: (16 j + g + 8, 2 t)   c3: (16 j + g + 8, 2 t + 1).
- * matrix: the codes of an inputs x outputs matrix; group: which 128 outputs; operands[column]: FP16 [inputs] of the
- * column's pair (columns beyond row_count repeat column 0 and are ignored by the caller).
+ * matrix: the codes of a matrix of `outputs` outputs; group: which 128 outputs; the K steps (tile rows)
+ * [step_begin, step_begin + step_count), a multiple of EXL3_STAGE_STEPS; operand_row: FP16 [inputs] of the pair that
+ * stands in this lane's column (lane / 4; columns beyond the job's rows repeat column 0 and are ignored by the caller).
+ * Warp w takes step 4 r + w of round r; the next round's operands are fetched while this round decodes.
  * Returns false if a bounded wait expired (the caller then stores nothing). All 128 threads call it. */
 template <uint32_t BX2>
-__device__ __forceinline__ bool exl3_product_core(const unsigned char *matrix, uint32_t inputs, uint32_t outputs,
-						  uint32_t group, const __half *const operand_row,
-						  unsigned char *dynamic_shared, exl3_product_shared *shared,
-						  float sums[2][4])
+__device__ __forceinline__ bool exl3_product_core(const unsigned char *matrix, uint32_t outputs, uint32_t group,
+						  uint32_t step_begin, uint32_t step_count,
+						  const __half *const operand_row, unsigned char *dynamic_shared,
+						  exl3_product_shared *shared, float sums[2][4])
 {
 	typedef exl3_ring<BX2> ring;
 	constexpr uint32_t row_bytes = EXL3_GROUP_TILES * ring::tile_bytes; /* the CTA's part of one tile row */
 	constexpr uint32_t stage_bytes = EXL3_STAGE_STEPS * row_bytes;
 	const uint32_t lane = threadIdx.x % EXL3_WARP, warp = threadIdx.x / EXL3_WARP;
-	const uint32_t steps = inputs / EXL3_TILE, rounds = steps / EXL3_STAGE_STEPS;
+	const uint32_t rounds = step_count / EXL3_STAGE_STEPS;
 	const uint64_t matrix_row_bytes = (uint64_t)(outputs / EXL3_TILE) * ring::tile_bytes;
-	const unsigned char *const source = matrix + (uint64_t)group * row_bytes;
+	const unsigned char *const source = matrix + (uint64_t)step_begin * matrix_row_bytes + (uint64_t)group * row_bytes;
 
 	if (threadIdx.x == 0) {
 		for (uint32_t stage = 0; stage < EXL3_STAGES; stage++) {
@@ -215,7 +220,7 @@ __device__ __forceinline__ bool exl3_product_core(const unsigned char *matrix, u
 	}
 	__syncthreads();
 
-	/* warp 0 fills: lane s < 8 copies tile row s of a stage */
+	/* warp 0 fills: lane s < 4 copies tile row s of a stage */
 	auto fill = [&](uint32_t round) {
 		const uint32_t stage = round % EXL3_STAGES;
 		if (lane == 0)
@@ -232,7 +237,11 @@ __device__ __forceinline__ bool exl3_product_core(const unsigned char *matrix, u
 
 	const uint32_t begin = ring::begin(lane);
 	const uint32_t word_index = begin / 32u, shift = begin % 32u, next_index = (word_index + 1u) % ring::words;
-	const uint32_t place = lane % 4u;
+	/* this lane's B operand of round r: inputs 2 t, 2 t + 1 and 2 t + 8, 2 t + 9 of step 4 r + warp */
+	const uint32_t *const fed = reinterpret_cast<const uint32_t *>(operand_row + (step_begin + warp) * EXL3_TILE +
+								      (lane % 4u) * 2u);
+	constexpr uint32_t fed_round_words = EXL3_STAGE_STEPS * EXL3_TILE / 2u;
+	uint32_t next0 = __ldg(fed), next1 = __ldg(fed + 4);
 	float accumulators[EXL3_GROUP_TILES][4];
 #pragma unroll
 	for (uint32_t tile = 0; tile < EXL3_GROUP_TILES; tile++)
@@ -240,8 +249,7 @@ __device__ __forceinline__ bool exl3_product_core(const unsigned char *matrix, u
 		for (uint32_t c = 0; c < 4; c++)
 			accumulators[tile][c] = 0.0f;
 
-	bool alive = true;
-	for (uint32_t round = 0; round < rounds && alive; round++) {
+	for (uint32_t round = 0; round < rounds; round++) {
 		const uint32_t stage = round % EXL3_STAGES, use = round / EXL3_STAGES;
 		if (warp == 0 && round >= 1 && round - 1u + EXL3_STAGES < rounds) {
 			/* the slot of the previous round is free once all four warps have read it */
@@ -250,27 +258,23 @@ __device__ __forceinline__ bool exl3_product_core(const unsigned char *matrix, u
 			else
 				shared->failed = 1;
 		}
+		const uint32_t b0 = next0, b1 = next1;
+		if (round + 1u < rounds) {
+			next0 = __ldg(fed + (round + 1u) * fed_round_words);
+			next1 = __ldg(fed + (round + 1u) * fed_round_words + 4);
+		}
 		if (!barrier_wait(&shared->full[stage], use & 1u)) {
 			shared->failed = 1;
-			alive = false;
 			break;
 		}
-		const unsigned char *const rows = dynamic_shared + stage * stage_bytes;
+		const uint32_t *const words =
+			reinterpret_cast<const uint32_t *>(dynamic_shared + stage * stage_bytes + warp * row_bytes);
 #pragma unroll
-		for (uint32_t turn = 0; turn < EXL3_STAGE_STEPS / EXL3_PRODUCT_WARPS; turn++) {
-			const uint32_t row = warp * (EXL3_STAGE_STEPS / EXL3_PRODUCT_WARPS) + turn;
-			const uint32_t step = round * EXL3_STAGE_STEPS + row;
-			const uint32_t *const fed =
-				reinterpret_cast<const uint32_t *>(operand_row + step * EXL3_TILE + place * 2u);
-			const uint32_t b0 = __ldg(fed), b1 = __ldg(fed + 4);
-			const uint32_t *const words = reinterpret_cast<const uint32_t *>(rows + row * row_bytes);
-#pragma unroll
-			for (uint32_t tile = 0; tile < EXL3_GROUP_TILES; tile++) {
-				uint32_t fragment[4];
-				exl3_decode_fragment<BX2>(words[tile * ring::words + word_index],
-							  words[tile * ring::words + next_index], shift, fragment);
-				mma_f16(accumulators[tile], fragment, b0, b1);
-			}
+		for (uint32_t tile = 0; tile < EXL3_GROUP_TILES; tile++) {
+			uint32_t fragment[4];
+			exl3_decode_fragment<BX2>(words[tile * ring::words + word_index],
+						  words[tile * ring::words + next_index], shift, fragment);
+			mma_f16(accumulators[tile], fragment, b0, b1);
 		}
 		__syncwarp();
 		if (lane == 0)
@@ -302,7 +306,7 @@ __device__ __forceinline__ bool exl3_product_core(const unsigned char *matrix, u
 			sums[mine][c] = total[c];
 	}
 	__syncthreads(); /* the partial sums are consumed: the caller may reuse the dynamic shared memory */
-	if (threadIdx.x == 0) /* a CTA may run the core again (gate, then up): leave no live barrier behind */
+	if (threadIdx.x == 0) /* a CTA may run the core again: leave no live barrier behind */
 		for (uint32_t stage = 0; stage < EXL3_STAGES; stage++) {
 			barrier_invalidate(&shared->full[stage]);
 			barrier_invalidate(&shared->empty[stage]);

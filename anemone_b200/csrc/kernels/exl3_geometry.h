@@ -10,8 +10,8 @@
 #define EXL3_PRODUCT_WARPS 4u
 #define EXL3_PRODUCT_THREADS (EXL3_PRODUCT_WARPS * EXL3_WARP)
 #define EXL3_GROUP_TILES 8u /* adjacent output tiles of a product CTA: 128 outputs, one Hadamard block */
-#define EXL3_STAGE_STEPS 8u /* K steps (tile rows) of one pipeline stage: two a warp */
-#define EXL3_STAGES 6u
+#define EXL3_STAGE_STEPS 4u /* K steps (tile rows) of one pipeline stage: one a warp */
+#define EXL3_STAGES 8u
 #define EXL3_TRANSFORM_WARPS 4u /* a transform CTA: one warp per 128-channel block */
 #define EXL3_TRANSFORM_THREADS (EXL3_TRANSFORM_WARPS * EXL3_WARP)
 #define EXL3_RECONSTRUCT_THREADS 256u
@@ -31,6 +31,19 @@ AB_INLINE uint32_t exl3_product_dynamic_bytes(uint32_t bits_x2)
 {
 	const uint32_t ring = EXL3_STAGES * exl3_product_stage_bytes(bits_x2);
 	return ring > EXL3_PRODUCT_PARTIAL_BYTES ? ring : EXL3_PRODUCT_PARTIAL_BYTES;
+}
+
+/* Split K of the fused B200 launches: a product over `inputs` is cut in this many equal runs of whole 128-input
+ * blocks, each its own CTA, so that a decode step has several waves of short work items instead of one wave of long
+ * ones; the last CTA to finish a (job, 128 outputs) adds the runs in ascending order from +0. The largest power of two
+ * up to 8 that divides inputs / 128 and leaves at least 8 blocks (64 K steps) a run. */
+AB_INLINE uint32_t exl3_moe_splits(uint32_t inputs)
+{
+	const uint32_t blocks = inputs / EXL3_TRANSFORM;
+	uint32_t splits = 1u;
+	while (splits < 8u && blocks % (2u * splits) == 0u && blocks / (2u * splits) >= 8u)
+		splits *= 2u;
+	return splits;
 }
 
 #endif

@@ -196,8 +196,8 @@ __device__ __forceinline__ void exl3_product_pass(const struct exl3_expert_recor
 		reinterpret_cast<const __half *>(arena + record.operands_offset) +
 		((uint64_t)projection * record.pair_count + job->pair_index[fed_column]) * inputs;
 	float sums[2][4];
-	if (!exl3_product_core<BX2>(arena + matrix, inputs, outputs, blockIdx.x, operand_row, dynamic_shared, shared,
-				    sums))
+	if (!exl3_product_core<BX2>(arena + matrix, outputs, blockIdx.x, 0u, inputs / EXL3_TILE, operand_row,
+				    dynamic_shared, shared, sums))
 		return;
 	float *const products = reinterpret_cast<float *>(arena + record.products_offset);
 #pragma unroll

@@ -96,8 +96,11 @@ class MoeLayout:
         self.jobs = layout.take(self.job_capacity * 96)
         self.expert_table = layout.take(c.total_experts * 24)
         self.widths = layout.take(c.total_experts * 4)
-        self.operands = layout.take(pairs * H * 4 + pairs * I * 2)
-        self.products = layout.take(pairs * H * 8)
+        sizes = api.moe_sizes(pairs, self.job_capacity, H, I)
+        self.operands = layout.take(sizes.operand_bytes)
+        self.products = layout.take(max(sizes.product_bytes, pairs * H * 8))
+        self.counters = layout.take(sizes.counter_bytes)
+        self.counter_bytes = sizes.counter_bytes
         self.hidden = layout.take(pairs * I * 2)
         self.row_output = layout.take(rows * H * 4)
         self.matrices = []
@@ -131,6 +134,7 @@ class MoeLayer:
         card.fill(L.status, 0, 16)
         card.fill(L.step, 0, 256)
         card.fill(L.region, 0, 2 * L.parity_stride)
+        card.fill(L.counters, 0, L.counter_bytes)
         peers = (R.OrderedPeer * rank_count)()
         for peer in range(rank_count):
             peers[peer].region_offset = L.region
@@ -167,6 +171,7 @@ class MoeLayer:
                                 L.inner_local, L.pairs, c.pairs_per_row, L.job_capacity, R.EXL3_WIDTH_PER_EXPERT,
                                 c.activation_limit, 0)
         moe.widths_offset, moe.row_output_offset, moe.expert_count = L.widths, L.row_output, c.total_experts
+        moe.counters_offset = L.counters
         moe_launches = (R.KernelLaunch * 4)()
         api.check(lib.exl3_moe_prepare(C.byref(moe), card.arena_bytes, card.ops_pointer, card.handle, moe_launches),
                   "exl3_moe_prepare")

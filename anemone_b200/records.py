@@ -46,7 +46,12 @@ class Exl3ShardActivation(C.Structure):
 
 class Exl3Moe(C.Structure):
     _fields_ = [("base", Exl3Expert), ("widths_offset", C.c_uint64), ("row_output_offset", C.c_uint64),
-                ("expert_count", C.c_uint32), ("reserved_zero", C.c_uint32)]
+                ("counters_offset", C.c_uint64), ("expert_count", C.c_uint32), ("reserved_zero", C.c_uint32)]
+
+
+class Exl3MoeSizes(C.Structure):
+    _fields_ = [("operand_bytes", C.c_uint64), ("product_bytes", C.c_uint64), ("counter_bytes", C.c_uint64),
+                ("gate_up_splits", C.c_uint32), ("down_splits", C.c_uint32)]
 
 
 class StepBlock(C.Structure):
@@ -115,7 +120,7 @@ class OrderedCollectiveKernels(C.Structure):
 
 
 for _record, _bytes in ((Exl3Reconstruct, 32), (Exl3Expert, 80), (ExpertJob, 96), (ExpertRowSum, 24),
-                        (Exl3ShardActivation, 96), (Exl3Moe, 104), (StepBlock, 16), (OrderedPeer, 32),
+                        (Exl3ShardActivation, 96), (Exl3Moe, 112), (StepBlock, 16), (OrderedPeer, 32),
                         (OrderedCollective, 80), (OrderedReduceBf16, 96), (OrderedRowSumPublish, 96),
                         (RouterSelectB200, 80), (StepInputSelect, 40), (KernelLaunch, 232), (CardDescription, 168)):
     assert C.sizeof(_record) == _bytes, (_record.__name__, C.sizeof(_record), _bytes)

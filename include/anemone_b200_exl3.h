@@ -55,6 +55,18 @@ MUST_CHECK result_status exl3_experts_relaxed_prepare(const struct exl3_expert_r
 						      struct device_card *card, uint32_t arithmetic_class,
 						      struct kernel_launch *launches_out);
 
+/* B200 extension: bytes of the scratch ranges of struct exl3_moe_record, which depend on how the fused launches cut
+ * their products (see the record). Zero sizes for shapes the chain refuses. */
+struct exl3_moe_sizes {
+	uint64_t operand_bytes; /* at base.operands_offset */
+	uint64_t product_bytes; /* at base.products_offset */
+	uint64_t counter_bytes; /* at counters_offset */
+	uint32_t gate_up_splits;
+	uint32_t down_splits;
+};
+void exl3_moe_sizes(uint32_t pair_count, uint32_t job_count, uint32_t input_size, uint32_t inner_size,
+		    struct exl3_moe_sizes *sizes_out);
+
 /* B200 extension (no reference counterpart): the four fused launches of kernel file "kernel_exl3_b200" for
  * struct exl3_moe_record: per-expert stored widths, row sums written to row_output_offset. launches_out has
  * EXL3_MOE_LAUNCHES entries. Validates what exl3_experts_prepare validates, plus the width table and the row output. */

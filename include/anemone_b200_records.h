@@ -184,18 +184,26 @@ struct bb_exl3_shard_activation_record {
 /* B200 extension, kernel file "kernel_exl3_b200": the whole routed-expert layer of one rank in four launches
  * (input transform; gate/up products fused with the SwiGLU activation and the down-side input transform; down
  * products fused with the output transform and route weight; ordered row sum), with a stored width per expert.
- * base is read exactly as the five-pass chain reads it, except that base.bits_per_weight may be
- * EXL3_WIDTH_PER_EXPERT, in which case expert e's three matrices have stored width widths[e]
- * (uint32 [expert_count] at widths_offset). row_output: FP32 [rows][input_size]. One layout differs: the FP16 down
- * operands [pair_count][inner_size] are written BEHIND the gate/up operands, at operands_offset +
- * 4 pair_count input_size (the fused launch writes them while the gate/up operands are still being read), so the
- * operands range of this record is 4 pair_count input_size + 2 pair_count inner_size bytes. */
+ * base is read as the five-pass chain reads it, except:
+ *   - base.bits_per_weight may be EXL3_WIDTH_PER_EXPERT: expert e's three matrices then have stored width widths[e]
+ *     (uint32 [expert_count] at widths_offset);
+ *   - a product over K inputs is cut in S = exl3_moe_splits(K) runs (exl3_geometry.h of the kernel sources; the host
+ *     preparer reports the sizes that follow through exl3_moe_sizes). products: FP32 partial sums
+ *     [2][S(input_size)][pair_count][inner_size] for gate/up, then reused as [S(inner_size)][pair_count][input_size]
+ *     for down; the pair outputs FP32 [pair_count][input_size] are run 0 of the latter (output_offset ==
+ *     products_offset, as in the chain);
+ *   - operands: FP16 [2][pair_count][input_size] for gate/up and, BEHIND them, FP16 [pair_count][inner_size] for
+ *     down (the fused launch writes them while the gate/up operands are still being read);
+ *   - counters: uint32 [job_count][inner_size / 128 + input_size / 128] at counters_offset, zero at load; every launch
+ *     leaves them zero.
+ * row_output: FP32 [rows][input_size]. */
 #define EXL3_MOE_KERNEL_FILE "kernel_exl3_b200"
 #define EXL3_MOE_LAUNCHES 4u
 struct exl3_moe_record {
 	struct exl3_expert_record base;
 	uint64_t widths_offset;
 	uint64_t row_output_offset;
+	uint64_t counters_offset;
 	uint32_t expert_count;
 	uint32_t reserved_zero;
 };
@@ -359,7 +367,7 @@ AB_RECORD_HAS(exl3_expert_record, 80);
 AB_RECORD_HAS(expert_job_record, 96);
 AB_RECORD_HAS(expert_row_sum_arguments, 24);
 AB_RECORD_HAS(bb_exl3_shard_activation_record, 96);
-AB_RECORD_HAS(exl3_moe_record, 104);
+AB_RECORD_HAS(exl3_moe_record, 112);
 AB_RECORD_HAS(step_block, 16);
 AB_RECORD_HAS(ordered_collective_peer, 32);
 AB_RECORD_HAS(ordered_collective_arguments, 80);

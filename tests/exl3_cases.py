@@ -54,8 +54,11 @@ class ChainCase:
         record = R.Exl3Expert()
         record.jobs_offset = take("jobs", C.sizeof(jobs))
         record.input_offset = take("input", rows * hidden * 2)
-        record.operands_offset = take("operands", self.pairs * hidden * 4 + self.pairs * inner * 2)
-        record.products_offset = take("products", self.pairs * hidden * 8)
+        from anemone_b200 import api
+        sizes = api.moe_sizes(self.pairs, self.job_capacity, hidden, inner)
+        record.operands_offset = take("operands", sizes.operand_bytes)
+        record.products_offset = take("products", max(sizes.product_bytes, self.pairs * hidden * 8))
+        self.counters_offset = take("counters", sizes.counter_bytes)
         record.output_offset = record.products_offset
         record.hidden_offset = take("hidden", self.pairs * inner * 2)
         self.row_output_offset = take("row_output", rows * hidden * 4)
@@ -74,6 +77,7 @@ class ChainCase:
         tokens = synthetic.tokens(rng, rows, hidden)
         image[record.input_offset:record.input_offset + tokens.nbytes] = tokens.view(np.uint8).reshape(-1)
         image[self.widths_offset:self.widths_offset + total * 4] = self.widths.view(np.uint8)
+        image[self.counters_offset:self.counters_offset + sizes.counter_bytes] = 0
         self.image = image
         self.expected = None
 

@@ -12,7 +12,7 @@ def declared_symbols():
     for path in glob.glob(os.path.join(ROOT, "include", "*.h")):
         text = re.sub(r"/\*.*?\*/", "", open(path).read(), flags=re.S)
         text = re.sub(r"AB_INLINE[^{;]*\{", "{", text)  # inline helpers are not exports
-        for match in re.finditer(r"(?:result_status|const char \*|uint64_t|uint32_t|const struct backend_operations \*)\s*"
+        for match in re.finditer(r"(?:result_status|const char \*|uint64_t|uint32_t|void|const struct backend_operations \*)\s*"
                                  r"([a-z_0-9]+)\s*\(", text):
             names.add(match.group(1))
         for match in re.finditer(r"extern const struct [a-z_]+ ([a-z_0-9]+);", text):

@@ -94,6 +94,7 @@ def run_chain(api, case, moe):
             record.widths_offset = case.widths_offset
             record.row_output_offset = case.row_output_offset
             record.expert_count = case.widths.size
+            record.counters_offset = case.counters_offset
             launches = (R.KernelLaunch * 4)()
             api.check(lib.exl3_moe_prepare(C.byref(record), case.arena_bytes, card.ops_pointer, card.handle, launches),
                       "exl3_moe_prepare")
@@ -116,7 +117,7 @@ def run_chain(api, case, moe):
 def check_chain(case, received, expected, moe):
     assert case.guards_intact(received) is None
     for name, (offset, size) in case.ranges.items():
-        if name.startswith("matrix_") or name in ("jobs", "input", "widths"):
+        if name.startswith("matrix_") or name in ("jobs", "input", "widths", "counters"):
             assert np.array_equal(received[offset:offset + size], case.image[offset:offset + size]), name
     live = case.live_pairs()
     H, I, pairs = case.H, case.I, case.pairs

@@ -75,7 +75,7 @@ def test_experts_prepare_launches_and_refusals():
     grids = [tuple(l.grid) for l in launches]
     assert grids == [(1, 7, 2), (2, 7, 2), (1, 7, 1), (4, 7, 1), (1, 7, 1)]
     assert [l.block[0] for l in launches] == [128] * 5
-    assert launches[1].dynamic_shared_byte_count == 6 * 8 * 8 * 16 * 6 and launches[0].dynamic_shared_byte_count == 0
+    assert launches[1].dynamic_shared_byte_count == 8 * 4 * 8 * 16 * 6 and launches[0].dynamic_shared_byte_count == 0
     for launch in launches:
         assert bytes(launch.argument[:80]) == bytes(record) and not any(launch.argument[80:])
     # refusals leave the whole table untouched
@@ -109,13 +109,19 @@ def test_moe_prepare():
     record = R.Exl3Moe()
     record.base = base
     record.base.bits_per_weight = R.EXL3_WIDTH_PER_EXPERT
-    record.base.operands_offset = layout.take(12 * 512 * 4 + 12 * 256 * 2)
+    sizes = api.moe_sizes(12, 7, 512, 256)
+    assert (sizes.gate_up_splits, sizes.down_splits) == (1, 1) and sizes.counter_bytes == 7 * 6 * 4
+    big = api.moe_sizes(72, 65, 4096, 2048)
+    assert (big.gate_up_splits, big.down_splits) == (4, 2) and big.product_bytes == 2 * 4 * 72 * 2048 * 4
+    record.base.operands_offset = layout.take(sizes.operand_bytes)
+    record.base.products_offset = record.base.output_offset = layout.take(max(sizes.product_bytes, 12 * 512 * 8))
     record.widths_offset, record.row_output_offset, record.expert_count = layout.take(64), layout.take(4 * 512 * 4), 9
+    record.counters_offset = layout.take(sizes.counter_bytes)
     arena = layout.take(0, 4096) + 4096
     launches = (R.KernelLaunch * 4)()
     assert lib.exl3_moe_prepare(C.byref(record), arena, C.byref(fake.table), fake.card, launches) == 0
     assert [key[1] for key in fake.asked] == ["exl3_moe_input", "exl3_moe_gate_up", "exl3_moe_down", "exl3_moe_row_sum"]
-    assert all(key[0] == "kernel_exl3_b200" and key[2] == 104 for key in fake.asked)
+    assert all(key[0] == "kernel_exl3_b200" and key[2] == 112 for key in fake.asked)
     untouched = bytes(launches)
     record.row_output_offset = record.base.products_offset  # overlaps the products
     assert lib.exl3_moe_prepare(C.byref(record), arena, C.byref(fake.table), fake.card, launches) == 1
