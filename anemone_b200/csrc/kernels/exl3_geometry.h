@@ -11,7 +11,7 @@
 #define EXL3_PRODUCT_THREADS (EXL3_PRODUCT_WARPS * EXL3_WARP)
 #define EXL3_GROUP_TILES 8u /* adjacent output tiles of a product CTA: 128 outputs, one Hadamard block */
 #define EXL3_STAGE_STEPS 4u /* K steps (tile rows) of one pipeline stage: one a warp */
-#define EXL3_STAGES 8u
+#define EXL3_STAGES 4u
 #define EXL3_TRANSFORM_WARPS 4u /* a transform CTA: one warp per 128-channel block */
 #define EXL3_TRANSFORM_THREADS (EXL3_TRANSFORM_WARPS * EXL3_WARP)
 #define EXL3_RECONSTRUCT_THREADS 256u
