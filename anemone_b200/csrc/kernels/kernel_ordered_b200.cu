@@ -15,18 +15,22 @@
  */
 #include "ordered_device.cuh"
 
-/* true for exactly one block: the last of the grid to arrive. The counter is the owner's own, at `line` + 64. */
+/* true for exactly one block: the last of the grid to arrive. The counter is the owner's own, at `line` + 64. Every
+ * block orders its stores at device scope before it counts itself; the block that sees the count complete then
+ * publishes with a system-scope release, which is cumulative over the stores it has observed that way. */
 __device__ __forceinline__ bool last_block_of_grid(unsigned char *line, uint32_t *shared_flag)
 {
-	__threadfence_system();
+	__threadfence();
 	__syncthreads();
 	if (threadIdx.x == 0) {
 		unsigned int *const counter = reinterpret_cast<unsigned int *>(line + ORDERED_LOCAL_COUNTER_OFFSET);
 		const unsigned int blocks = gridDim.x * gridDim.y * gridDim.z;
 		const unsigned int arrived = atomicAdd(counter, 1u) + 1u;
 		*shared_flag = arrived == blocks ? 1u : 0u;
-		if (arrived == blocks)
+		if (arrived == blocks) {
 			*counter = 0u; /* ready for the slot's next use */
+			__threadfence();
+		}
 	}
 	__syncthreads();
 	return *shared_flag != 0;

@@ -1,6 +1,7 @@
 /*
  * kernel_router_b200.cu: router select and job-table builder for up to 64 live rows (struct
- * router_select_b200_arguments). One block of 1024 threads, no atomics on data, a row's picks depend on that row alone.
+ * router_select_b200_arguments). One block of 1024 threads, a row's picks depend on that row alone.
+ * (The only atomic is an OR into a shared-memory bit mask, whose result does not depend on order.)
  * Conventions are the reference's router_select_entry (source/kernel_router.cuh:36-119, include/anemone/
  * router_records.h:7-30): keys order scores as the reference's top-k orders float32 (a not-a-number above every
  * number, -0 below +0), the lower expert first among equals; slots in ascending expert order; the weight sum from +0
@@ -35,8 +36,8 @@ extern "C" __global__ void __launch_bounds__(ROUTER_B200_THREADS)
 {
 	__shared__ uint32_t chosen[ROUTER_B200_MAXIMUM_ROWS][ROUTER_B200_MAXIMUM_PICKS]; /* by slot */
 	__shared__ float weight[ROUTER_B200_MAXIMUM_ROWS][ROUTER_B200_MAXIMUM_PICKS];
-	__shared__ uint32_t rows_of[ROUTER_B200_MAXIMUM_EXPERTS]; /* rows that chose the expert */
-	__shared__ uint32_t first_job[ROUTER_B200_MAXIMUM_EXPERTS + 1u];
+	__shared__ unsigned long long row_mask[ROUTER_B200_MAXIMUM_EXPERTS]; /* bit r: row r stands in the expert */
+	__shared__ uint32_t first_job[ROUTER_B200_MAXIMUM_EXPERTS];
 	const struct step_block step = *reinterpret_cast<const struct step_block *>(arena + arguments.step_offset);
 	const uint32_t live = min(step.row_count, arguments.row_capacity);
 	const uint32_t experts = arguments.expert_count, picks = arguments.picks, shared = arguments.shared_count;
@@ -49,7 +50,7 @@ extern "C" __global__ void __launch_bounds__(ROUTER_B200_THREADS)
 	     index += blockDim.x)
 		table[index] = make_uint4(0, 0, 0, 0);
 	for (uint32_t expert = threadIdx.x; expert < ROUTER_B200_MAXIMUM_EXPERTS; expert += blockDim.x)
-		rows_of[expert] = 0;
+		row_mask[expert] = 0ull;
 
 	/* one warp a row: `picks` rounds of a warp-wide maximum over 64-bit keys */
 	for (uint32_t row = warp; row < live; row += blockDim.x / WARP) {
@@ -101,26 +102,35 @@ extern "C" __global__ void __launch_bounds__(ROUTER_B200_THREADS)
 	}
 	__syncthreads();
 
-	/* rows per expert (a thread an expert: no atomics), then the first job of every expert */
-	for (uint32_t expert = threadIdx.x; expert < experts + shared; expert += blockDim.x) {
-		uint32_t count = 0;
-		if (expert >= experts) {
-			count = live;
-		} else {
-			for (uint32_t row = 0; row < live; row++)
-				for (uint32_t place = 0; place < picks; place++)
-					count += chosen[row][place] == expert ? 1u : 0u;
-		}
-		rows_of[expert] = count;
-	}
+	/* which rows chose each expert: a 64-bit mask per expert (an OR is the same in any order), then the first job of
+	 * every expert by a warp-wide prefix sum over the experts' job counts */
+	for (uint32_t pair = threadIdx.x; pair < live * picks; pair += blockDim.x)
+		atomicOr(&row_mask[chosen[pair / picks][pair % picks]], 1ull << (pair / picks));
 	__syncthreads();
-	if (threadIdx.x == 0) {
-		uint32_t jobs = 0;
-		for (uint32_t expert = 0; expert < experts + shared; expert++) {
-			first_job[expert] = jobs;
-			jobs += (rows_of[expert] + LINEAR_MAXIMUM_ROWS - 1u) / LINEAR_MAXIMUM_ROWS;
+	if (warp == 0) {
+		const unsigned long long everyone = live >= 64u ? ~0ull : (1ull << live) - 1ull;
+		uint32_t local[EXPERTS_PER_LANE], total = 0;
+#pragma unroll
+		for (uint32_t place = 0; place < EXPERTS_PER_LANE; place++) {
+			const uint32_t expert = lane * EXPERTS_PER_LANE + place;
+			const uint32_t rows = expert < experts	       ? (uint32_t)__popcll(row_mask[expert]) :
+					      expert < experts + shared ? live :
+									  0u;
+			if (expert >= experts && expert < experts + shared)
+				row_mask[expert] = everyone;
+			local[place] = total;
+			total += (rows + LINEAR_MAXIMUM_ROWS - 1u) / LINEAR_MAXIMUM_ROWS;
 		}
-		first_job[experts + shared] = jobs;
+		uint32_t before = total; /* inclusive scan over the lanes, then made exclusive */
+		for (uint32_t distance = 1; distance < WARP; distance <<= 1) {
+			const uint32_t other = __shfl_up_sync(0xFFFFFFFFu, before, distance);
+			if (lane >= distance)
+				before += other;
+		}
+		before -= total;
+#pragma unroll
+		for (uint32_t place = 0; place < EXPERTS_PER_LANE; place++)
+			first_job[lane * EXPERTS_PER_LANE + place] = before + local[place];
 	}
 	__syncthreads();
 
@@ -131,14 +141,8 @@ extern "C" __global__ void __launch_bounds__(ROUTER_B200_THREADS)
 	for (uint32_t pair = threadIdx.x; pair < live * pairs_per_row; pair += blockDim.x) {
 		const uint32_t row = pair / pairs_per_row, slot = pair % pairs_per_row;
 		const uint32_t expert = slot < picks ? chosen[row][slot] : experts + (slot - picks);
-		uint32_t place = 0; /* rows below mine that stand in the same expert */
-		if (slot >= picks) {
-			place = row;
-		} else {
-			for (uint32_t other = 0; other < row; other++)
-				for (uint32_t pick = 0; pick < picks; pick++)
-					place += chosen[other][pick] == expert ? 1u : 0u;
-		}
+		const unsigned long long mask = row_mask[expert];
+		const uint32_t place = (uint32_t)__popcll(mask & ((1ull << row) - 1ull)); /* rows below mine in the expert */
 		const uint32_t job_index = first_job[expert] + place / LINEAR_MAXIMUM_ROWS;
 		if (job_index >= arguments.job_capacity)
 			continue;
@@ -147,7 +151,7 @@ extern "C" __global__ void __launch_bounds__(ROUTER_B200_THREADS)
 		job->pair_index[column] = pair;
 		job->route_weight[column] = slot < picks ? weight[row][slot] : 1.0f;
 		if (column == 0) {
-			const uint32_t remaining = rows_of[expert] - place;
+			const uint32_t remaining = (uint32_t)__popcll(mask) - place;
 			job->gate_offset = offsets[3u * expert];
 			job->up_offset = offsets[3u * expert + 1u];
 			job->down_offset = offsets[3u * expert + 2u];
