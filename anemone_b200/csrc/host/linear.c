@@ -1,0 +1,225 @@
+/*
+ * linear.c: preparation of the original-weights routed experts (anemone_b200_linear.h). Takes the place of the part of
+ * the reference's source/linear.c that prepares activation_quantize_entry, expert_gate_up_<S>, expert_down_<S> and
+ * expert_row_sum_entry.
+ */
+#include "anemone_b200_linear.h"
+
+#include <math.h>
+#include <stddef.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "prepare_common.h"
+
+static const uint32_t slice_counts[LINEAR_SLICE_INSTANCES] = { 1, 2, 4, 8, 16 };
+
+static result_status e2m1_stored_byte_count(const struct matrix_shape_record *shape, uint64_t *byte_count_out)
+{
+	if (shape == NULL || byte_count_out == NULL || shape->reserved_must_be_zero != 0 || shape->output_size == 0 ||
+	    shape->input_size == 0 || shape->output_size % LINEAR_OUTPUTS_PER_TILE != 0 ||
+	    shape->input_size % LINEAR_VALUES_PER_LOAD != 0 || shape->bits_per_weight != 4)
+		return STATUS_INVALID_ARGUMENT;
+	const uint64_t weights = (uint64_t)shape->output_size * shape->input_size;
+	*byte_count_out = weights / 2u + weights / LINEAR_VALUES_PER_BLOCK;
+	return STATUS_OK;
+}
+
+const struct weight_format_operations e2m1_scaled_weight_operations = { .name = "e2m1_scaled",
+									 .stored_byte_count = e2m1_stored_byte_count };
+
+uint64_t linear_values_byte_count(uint64_t vector_count, uint32_t width)
+{
+	return vector_count > UINT64_MAX / 2u / (width ? width : 1u) ? UINT64_MAX : vector_count * width * 2u;
+}
+
+uint64_t linear_codes_byte_count(uint64_t vector_count, uint32_t width)
+{
+	return vector_count > UINT64_MAX / (width ? width : 1u) ? UINT64_MAX : vector_count * width;
+}
+
+uint64_t linear_exponents_byte_count(uint64_t vector_count, uint32_t width)
+{
+	return linear_codes_byte_count(vector_count, width / LINEAR_VALUES_PER_BLOCK);
+}
+
+uint64_t linear_sums_byte_count(uint64_t row_count, uint32_t width)
+{
+	return row_count > UINT64_MAX / 4u / (width ? width : 1u) ? UINT64_MAX : row_count * width * 4u;
+}
+
+uint64_t linear_jobs_byte_count(uint64_t job_count)
+{
+	return job_count > UINT64_MAX / sizeof(struct expert_job_record) ? UINT64_MAX :
+									   job_count * sizeof(struct expert_job_record);
+}
+
+result_status linear_kernels_prepare(const struct backend_operations *backend, struct device_card *card,
+				     uint32_t arithmetic_class, struct linear_kernels_record *kernels_out)
+{
+	if (backend == NULL || backend->kernel_prepare == NULL || card == NULL || kernels_out == NULL)
+		return STATUS_INVALID_ARGUMENT;
+	if (arithmetic_class == ARITHMETIC_CLASS_SM_80 || arithmetic_class == ARITHMETIC_CLASS_SM_120 ||
+	    arithmetic_class == ARITHMETIC_CLASS_SM_120_NATIVE)
+		return STATUS_UNSUPPORTED;
+	if (arithmetic_class != ARITHMETIC_CLASS_SM_100)
+		return STATUS_INVALID_ARGUMENT;
+	struct linear_kernels_record kernels;
+	memset(&kernels, 0xFF, sizeof(kernels)); /* every member BACKEND_NO_KERNEL */
+	result_status status = backend->kernel_prepare(card, KERNEL_FILE_ACTIVATION_QUANTIZE, KERNEL_ACTIVATION_QUANTIZE,
+						       sizeof(struct activation_quantize_arguments),
+						       &kernels.activation_quantize);
+	for (uint32_t instance = 0; status == STATUS_OK && instance < LINEAR_SLICE_INSTANCES; instance++) {
+		char name[48];
+		(void)snprintf(name, sizeof(name), KERNEL_EXPERT_GATE_UP_STEM "%u", slice_counts[instance]);
+		status = backend->kernel_prepare(card, KERNEL_FILE_EXPERT_LINEAR, name,
+						 sizeof(struct expert_gate_up_arguments), &kernels.expert_gate_up[instance]);
+		if (status != STATUS_OK)
+			break;
+		(void)snprintf(name, sizeof(name), KERNEL_EXPERT_DOWN_STEM "%u", slice_counts[instance]);
+		status = backend->kernel_prepare(card, KERNEL_FILE_EXPERT_LINEAR, name, sizeof(struct expert_down_arguments),
+						 &kernels.expert_down[instance]);
+	}
+	if (status == STATUS_OK)
+		status = backend->kernel_prepare(card, KERNEL_FILE_EXPERT_LINEAR, KERNEL_EXPERT_ROW_SUM,
+						 sizeof(struct expert_row_sum_arguments), &kernels.expert_row_sum);
+	if (status != STATUS_OK) {
+		(void)fprintf(stderr, "linear kernels: a kernel could not be prepared (%s)\n", status_text(status));
+		return status;
+	}
+	*kernels_out = kernels;
+	return STATUS_OK;
+}
+
+static bool range_holds(const struct linear_range *range, uint64_t needed)
+{
+	return needed != UINT64_MAX && range->byte_count >= needed;
+}
+
+result_status linear_quantize_prepare(const struct linear_quantize_description *description, uint64_t arena_byte_count,
+				      const struct linear_kernels_record *kernels, struct kernel_launch *launch_out)
+{
+	if (description == NULL || kernels == NULL || launch_out == NULL ||
+	    kernels->activation_quantize == BACKEND_NO_KERNEL || description->width == 0 ||
+	    description->width % LINEAR_VALUES_PER_LOAD != 0 || description->row_count == 0 ||
+	    description->row_count > 65535u ||
+	    !range_holds(&description->values, linear_values_byte_count(description->row_count, description->width)) ||
+	    !range_holds(&description->codes, linear_codes_byte_count(description->row_count, description->width)) ||
+	    !range_holds(&description->exponents, linear_exponents_byte_count(description->row_count, description->width)) ||
+	    !range_holds(&description->operands, linear_values_byte_count(description->row_count, description->width)))
+		return STATUS_INVALID_ARGUMENT;
+	const struct checked_range ranges[4] = {
+		{ "values", description->values.byte_offset, description->values.byte_count },
+		{ "codes", description->codes.byte_offset, description->codes.byte_count },
+		{ "exponents", description->exponents.byte_offset, description->exponents.byte_count },
+		{ "operands", description->operands.byte_offset, description->operands.byte_count }
+	};
+	if (!prepare_ranges_are_valid("activation quantize", ranges, 4, arena_byte_count))
+		return STATUS_INVALID_ARGUMENT;
+	const struct activation_quantize_arguments arguments = { description->values.byte_offset,
+								  description->codes.byte_offset,
+								  description->exponents.byte_offset,
+								  description->operands.byte_offset, description->width, 0 };
+	prepare_launch_fill(launch_out, kernels->activation_quantize, description->width / LINEAR_VALUES_PER_LOAD,
+			    description->row_count, 1, 32, 0, &arguments, sizeof(arguments));
+	return STATUS_OK;
+}
+
+/* the instance of a slice count, or LINEAR_SLICE_INSTANCES */
+static uint32_t slice_instance(uint32_t slice_count, uint32_t input_size)
+{
+	for (uint32_t instance = 0; instance < LINEAR_SLICE_INSTANCES; instance++)
+		if (slice_counts[instance] == slice_count && slice_count <= input_size / LINEAR_VALUES_PER_LOAD)
+			return instance;
+	return LINEAR_SLICE_INSTANCES;
+}
+
+result_status linear_routed_experts_prepare(const struct linear_routed_experts_description *description,
+					    uint64_t arena_byte_count, const struct linear_kernels_record *kernels,
+					    struct kernel_launch *launches_out)
+{
+	if (description == NULL || kernels == NULL || launches_out == NULL || description->reserved_zero != 0 ||
+	    description->weight_format != WEIGHT_FORMAT_E2M1_SCALED || description->job_count == 0 ||
+	    description->job_count > 65535u || description->row_count == 0 || description->pairs_per_row == 0 ||
+	    !isfinite(description->activation_limit) || description->activation_limit <= 0)
+		return STATUS_INVALID_ARGUMENT;
+	uint64_t gate_up_bytes = 0, down_bytes = 0;
+	const struct matrix_shape_record *const gate_up = &description->gate_up_shape, *const down = &description->down_shape;
+	if (e2m1_stored_byte_count(gate_up, &gate_up_bytes) != STATUS_OK ||
+	    e2m1_stored_byte_count(down, &down_bytes) != STATUS_OK || down->input_size != gate_up->output_size ||
+	    down->output_size != gate_up->input_size)
+		return STATUS_INVALID_ARGUMENT;
+	const uint32_t gate_up_instance = slice_instance(description->gate_up_slice_count, gate_up->input_size);
+	const uint32_t down_instance = slice_instance(description->down_slice_count, down->input_size);
+	if (gate_up_instance == LINEAR_SLICE_INSTANCES || down_instance == LINEAR_SLICE_INSTANCES ||
+	    kernels->expert_gate_up[gate_up_instance] == BACKEND_NO_KERNEL ||
+	    kernels->expert_down[down_instance] == BACKEND_NO_KERNEL || kernels->activation_quantize == BACKEND_NO_KERNEL ||
+	    kernels->expert_row_sum == BACKEND_NO_KERNEL)
+		return STATUS_INVALID_ARGUMENT;
+	const uint64_t rows = description->row_count, pairs = rows * description->pairs_per_row;
+	const uint32_t H = gate_up->input_size, I = gate_up->output_size;
+	if (pairs > UINT32_MAX || pairs > 65535u * 64u ||
+	    !range_holds(&description->jobs, linear_jobs_byte_count(description->job_count)) ||
+	    !range_holds(&description->expert_weights, gate_up_bytes > down_bytes ? gate_up_bytes : down_bytes) ||
+	    !range_holds(&description->codes, linear_codes_byte_count(rows, H)) ||
+	    !range_holds(&description->exponents, linear_exponents_byte_count(rows, H)) ||
+	    !range_holds(&description->operands, linear_values_byte_count(rows, H)) ||
+	    !range_holds(&description->hidden, linear_values_byte_count(pairs, I)) ||
+	    !range_holds(&description->hidden_codes, linear_codes_byte_count(pairs, I)) ||
+	    !range_holds(&description->hidden_exponents, linear_exponents_byte_count(pairs, I)) ||
+	    !range_holds(&description->hidden_operands, linear_values_byte_count(pairs, I)) ||
+	    !range_holds(&description->pair_output, linear_values_byte_count(pairs, H)) ||
+	    !range_holds(&description->row_output, linear_sums_byte_count(rows, H)))
+		return STATUS_INVALID_ARGUMENT;
+	const struct linear_range *const all[11] = { &description->jobs, &description->expert_weights,
+						     &description->codes, &description->exponents,
+						     &description->operands, &description->hidden,
+						     &description->hidden_codes, &description->hidden_exponents,
+						     &description->hidden_operands, &description->pair_output,
+						     &description->row_output };
+	static const char *const names[11] = { "jobs", "expert weights", "codes", "exponents", "operands", "hidden",
+					       "hidden codes", "hidden exponents", "hidden operands", "pair output",
+					       "row output" };
+	struct checked_range ranges[11];
+	for (uint32_t index = 0; index < 11; index++)
+		ranges[index] = (struct checked_range){ names[index], all[index]->byte_offset, all[index]->byte_count };
+	if (!prepare_ranges_are_valid("routed experts", ranges, 11, arena_byte_count))
+		return STATUS_INVALID_ARGUMENT;
+	const struct expert_gate_up_arguments gate_up_arguments = { description->jobs.byte_offset,
+								    description->codes.byte_offset,
+								    description->exponents.byte_offset,
+								    description->operands.byte_offset,
+								    description->hidden.byte_offset, I, H, (uint32_t)pairs,
+								    description->pairs_per_row,
+								    description->activation_limit, 0 };
+	const struct activation_quantize_arguments quantize_arguments = { description->hidden.byte_offset,
+									   description->hidden_codes.byte_offset,
+									   description->hidden_exponents.byte_offset,
+									   description->hidden_operands.byte_offset, I, 0 };
+	const struct expert_down_arguments down_arguments = { description->jobs.byte_offset,
+							      description->hidden_codes.byte_offset,
+							      description->hidden_exponents.byte_offset,
+							      description->hidden_operands.byte_offset,
+							      description->pair_output.byte_offset, H, I, (uint32_t)pairs, 0 };
+	const struct expert_row_sum_arguments sum_arguments = { description->pair_output.byte_offset,
+								description->row_output.byte_offset, H,
+								description->pairs_per_row };
+	struct kernel_launch launches[LINEAR_ROUTED_EXPERTS_LAUNCH_COUNT];
+	prepare_launch_fill(&launches[LINEAR_ROUTED_EXPERTS_GATE_UP], kernels->expert_gate_up[gate_up_instance],
+			    I / LINEAR_OUTPUTS_PER_TILE, description->job_count, 1, 64u * description->gate_up_slice_count, 0,
+			    &gate_up_arguments, sizeof(gate_up_arguments));
+	/* pairs can exceed a grid's second dimension only beyond 65 535: the quantizer takes them in its second dimension */
+	prepare_launch_fill(&launches[LINEAR_ROUTED_EXPERTS_QUANTIZE], kernels->activation_quantize,
+			    I / LINEAR_VALUES_PER_LOAD, (uint32_t)(pairs > 65535u ? 65535u : pairs), 1, 32, 0,
+			    &quantize_arguments, sizeof(quantize_arguments));
+	if (pairs > 65535u)
+		return STATUS_INVALID_ARGUMENT;
+	prepare_launch_fill(&launches[LINEAR_ROUTED_EXPERTS_DOWN], kernels->expert_down[down_instance],
+			    H / LINEAR_OUTPUTS_PER_TILE, description->job_count, 1, 32u * description->down_slice_count, 0,
+			    &down_arguments, sizeof(down_arguments));
+	prepare_launch_fill(&launches[LINEAR_ROUTED_EXPERTS_ROW_SUM], kernels->expert_row_sum,
+			    (H + LINEAR_ELEMENT_THREADS - 1u) / LINEAR_ELEMENT_THREADS, description->row_count, 1,
+			    LINEAR_ELEMENT_THREADS, 0, &sum_arguments, sizeof(sum_arguments));
+	memcpy(launches_out, launches, sizeof(launches));
+	return STATUS_OK;
+}

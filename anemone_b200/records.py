@@ -93,6 +93,56 @@ class StepInputSelect(C.Structure):
                 ("cursor_offset", C.c_uint64), ("pool_count", C.c_uint32), ("byte_count", C.c_uint32)]
 
 
+class ActivationQuantize(C.Structure):
+    _fields_ = [("values_offset", C.c_uint64), ("codes_offset", C.c_uint64), ("exponents_offset", C.c_uint64),
+                ("operands_offset", C.c_uint64), ("width", C.c_uint32), ("reserved_zero", C.c_uint32)]
+
+
+class ExpertGateUp(C.Structure):
+    _fields_ = [("jobs_offset", C.c_uint64), ("codes_offset", C.c_uint64), ("exponents_offset", C.c_uint64),
+                ("operands_offset", C.c_uint64), ("hidden_offset", C.c_uint64), ("output_size", C.c_uint32),
+                ("input_size", C.c_uint32), ("pair_count", C.c_uint32), ("pairs_per_row", C.c_uint32),
+                ("activation_limit", C.c_float), ("reserved_zero", C.c_uint32)]
+
+
+class ExpertDown(C.Structure):
+    _fields_ = [("jobs_offset", C.c_uint64), ("codes_offset", C.c_uint64), ("exponents_offset", C.c_uint64),
+                ("operands_offset", C.c_uint64), ("output_offset", C.c_uint64), ("output_size", C.c_uint32),
+                ("input_size", C.c_uint32), ("pair_count", C.c_uint32), ("reserved_zero", C.c_uint32)]
+
+
+class LinearRange(C.Structure):
+    _fields_ = [("byte_offset", C.c_uint64), ("byte_count", C.c_uint64)]
+
+
+class MatrixShape(C.Structure):
+    _fields_ = [("output_size", C.c_uint32), ("input_size", C.c_uint32), ("bits_per_weight", C.c_uint32),
+                ("reserved_must_be_zero", C.c_uint32)]
+
+
+class LinearKernels(C.Structure):
+    _fields_ = [("activation_quantize", C.c_uint32), ("expert_gate_up", C.c_uint32 * 5),
+                ("expert_down", C.c_uint32 * 5), ("expert_row_sum", C.c_uint32),
+                ("trunk_linear_quantized", C.c_uint32 * 5), ("trunk_linear_bfloat16", C.c_uint32 * 5),
+                ("trunk_hidden", C.c_uint32), ("trunk_linear_quantized_wide", C.c_uint32 * 5),
+                ("trunk_linear_bfloat16_wide", C.c_uint32 * 5), ("trunk_linear_quantized_interleaved", C.c_uint32)]
+
+
+class LinearQuantizeDescription(C.Structure):
+    _fields_ = [("values", LinearRange), ("codes", LinearRange), ("exponents", LinearRange),
+                ("operands", LinearRange), ("width", C.c_uint32), ("row_count", C.c_uint32)]
+
+
+class LinearRoutedExpertsDescription(C.Structure):
+    _fields_ = [(name, LinearRange) for name in ("jobs", "expert_weights", "codes", "exponents", "operands", "hidden",
+                                                 "hidden_codes", "hidden_exponents", "hidden_operands", "pair_output",
+                                                 "row_output")] + \
+               [("gate_up_shape", MatrixShape), ("down_shape", MatrixShape), ("weight_format", C.c_int),
+                ("job_count", C.c_uint32), ("row_count", C.c_uint32), ("pairs_per_row", C.c_uint32),
+                ("gate_up_slice_count", C.c_uint32), ("down_slice_count", C.c_uint32),
+                ("activation_limit", C.c_float), ("reserved_zero", C.c_uint32)]
+
+
 class KernelLaunch(C.Structure):
     _fields_ = [("kernel", C.c_uint32), ("grid", C.c_uint32 * 3), ("block", C.c_uint32 * 3),
                 ("dynamic_shared_byte_count", C.c_uint32), ("argument_byte_count", C.c_uint32),
@@ -122,5 +172,6 @@ class OrderedCollectiveKernels(C.Structure):
 for _record, _bytes in ((Exl3Reconstruct, 32), (Exl3Expert, 80), (ExpertJob, 96), (ExpertRowSum, 24),
                         (Exl3ShardActivation, 96), (Exl3Moe, 112), (StepBlock, 16), (OrderedPeer, 32),
                         (OrderedCollective, 80), (OrderedReduceBf16, 96), (OrderedRowSumPublish, 96),
-                        (RouterSelectB200, 80), (StepInputSelect, 40), (KernelLaunch, 232), (CardDescription, 168)):
+                        (RouterSelectB200, 80), (StepInputSelect, 40), (ActivationQuantize, 40), (ExpertGateUp, 64), (ExpertDown, 56),
+                        (KernelLaunch, 232), (CardDescription, 168)):
     assert C.sizeof(_record) == _bytes, (_record.__name__, C.sizeof(_record), _bytes)

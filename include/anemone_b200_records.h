@@ -340,6 +340,84 @@ struct router_select_b200_arguments {
 	uint32_t reserved_zero;
 };
 
+/* ------------------------------------------------------------------------------------------------------------
+ * Original-weights experts: MXFP4 (E2M1 weights, one E8M0 scale per 32 inputs) by E4M3 block-quantized activations
+ * (reference: include/anemone/linear_records.h:36-99, 222-299; include/anemone/weight_format_seam.h:23-46).
+ *
+ * Arrays (a vector v is a row of the batch, or a pair):
+ *   values     bfloat16 [v][width]
+ *   codes      uint8 [v][width], E4M3 bytes in LANE ORDER: byte ((4 l + t) 4 + s) 4 + j of a vector is the code of its
+ *              value 64 l + 16 s + 2 t + j / 2 + 8 (j % 2)
+ *   exponents  uint8 [v][width / 32]: E8M0 code c of a block of 32 values; a value is its code's value times 2^(c-127)
+ *   operands   uint16 [v][width] in OPERAND ORDER (half ((4 l + t) 4 + s) 4 + 2 r + h is the operand of value
+ *              64 l + 16 s + 2 t + h + 8 r). On this library's arithmetic class the operand is the E4M3 code PLACED as
+ *              an FP16 (sign to bit 15, the other seven bits to bits 7..13: the code's value times 2^-8, exact), which
+ *              is what its products feed the tensor cores; the reference's class 80 stores a bfloat16 carry there.
+ *   a matrix   WEIGHT_FORMAT_E2M1_SCALED: words uint32 [output / 16][input / 64][lane][step 0..3], the nibble at bit
+ *              4 r + 16 h of a word is W[16 tile + g + 8 (r % 2)][64 load + 16 step + 2 t + 8 (r / 2) + h], lane =
+ *              4 g + t; then scales uint32 [tile][load][g]: byte 2 q + r is the E8M0 scale of inputs 64 load + 32 q ..
+ *              + 31 of output 16 tile + g + 8 r. output_size * input_size / 2 + output_size * input_size / 32 bytes.
+ * Quantization: per block of 32 values, in FP32: m = max(largest magnitude, 1e-4f) * (1 / 448.0f); c - 127 is the
+ * exponent of the smallest power of two not below m; each magnitude is divided by 2^(c-127), limited to 448 and
+ * rounded to the nearest E4M3 number, a tie to the even code; the sign is kept, also of a zero.
+ * A product: the L = input_size / 64 loads are cut in S slices (slice i: loads floor(i L / S) .. floor((i + 1) L / S)
+ * - 1), a slice is one FP32 chain from +0: per block of 32 inputs ascending, chain = fma(p, 2^e, chain), p the tensor
+ * cores' FP32 sum of the block's 32 products (two instructions of 16, the second accumulating on the first) and 2^e
+ * the exact power of two that applies both scales and undoes the placements; the S chains are added from +0 in
+ * ascending order and the sum is rounded once to bfloat16 (nearest even; a not-a-number to 0x7FC0).
+ * Hidden step: gate and up rounded to bfloat16 first; g = min(gate, limit); u = up limited to -limit .. limit;
+ * h = bfloat16(((g / (1 + exp(-g))) * u) * route weight).
+ * ---------------------------------------------------------------------------------------------------------- */
+#define KERNEL_FILE_ACTIVATION_QUANTIZE "kernel_activation_quantize"
+#define KERNEL_FILE_EXPERT_LINEAR "kernel_expert_linear"
+#define KERNEL_ACTIVATION_QUANTIZE "activation_quantize_entry"
+#define KERNEL_EXPERT_GATE_UP_STEM "expert_gate_up_"
+#define KERNEL_EXPERT_DOWN_STEM "expert_down_"
+#define KERNEL_EXPERT_ROW_SUM "expert_row_sum_entry"
+#define LINEAR_SLICE_INSTANCES 5u /* slice counts 1, 2, 4, 8, 16 */
+#define LINEAR_VALUES_PER_LOAD 64u
+#define LINEAR_OUTPUTS_PER_TILE 16u
+#define LINEAR_VALUES_PER_BLOCK 32u
+#define LINEAR_ELEMENT_THREADS 256u
+
+/* activation_quantize_entry: grid (width / 64, vectors), block 32 (a warp a load of 64 values) */
+struct activation_quantize_arguments {
+	uint64_t values_offset;
+	uint64_t codes_offset;
+	uint64_t exponents_offset;
+	uint64_t operands_offset;
+	uint32_t width;
+	uint32_t reserved_zero;
+};
+
+/* expert_gate_up_<S>: grid (output_size / 16, jobs), block 64 S; writes hidden bfloat16 [pair][output_size] */
+struct expert_gate_up_arguments {
+	uint64_t jobs_offset;
+	uint64_t codes_offset;
+	uint64_t exponents_offset;
+	uint64_t operands_offset;
+	uint64_t hidden_offset;
+	uint32_t output_size;
+	uint32_t input_size;
+	uint32_t pair_count;
+	uint32_t pairs_per_row;
+	float activation_limit;
+	uint32_t reserved_zero;
+};
+
+/* expert_down_<S>: grid (output_size / 16, jobs), block 32 S; writes bfloat16 [pair][output_size] */
+struct expert_down_arguments {
+	uint64_t jobs_offset;
+	uint64_t codes_offset;
+	uint64_t exponents_offset;
+	uint64_t operands_offset;
+	uint64_t output_offset;
+	uint32_t output_size;
+	uint32_t input_size;
+	uint32_t pair_count;
+	uint32_t reserved_zero;
+};
+
 /* B200 extension, kernel file "kernel_router_b200", entry "step_input_select": the step driver's hand-over of one
  * step's inputs that already lie in device memory. A pool holds `pool_count` prepared step input areas of `byte_count`
  * bytes at `pool_stride` apart (each beginning with its struct step_block, sequences strictly increasing); the kernel
@@ -375,5 +453,8 @@ AB_RECORD_HAS(ordered_reduce_bf16_arguments, 96);
 AB_RECORD_HAS(ordered_row_sum_publish_arguments, 96);
 AB_RECORD_HAS(router_select_b200_arguments, 80);
 AB_RECORD_HAS(step_input_select_arguments, 40);
+AB_RECORD_HAS(activation_quantize_arguments, 40);
+AB_RECORD_HAS(expert_gate_up_arguments, 64);
+AB_RECORD_HAS(expert_down_arguments, 56);
 
 #endif

@@ -80,4 +80,23 @@ uint32_t orc_router_jobs(const uint32_t *experts, const float *weights, uint32_t
 			 uint32_t expert_count, uint32_t shared_count, const uint64_t *expert_table,
 			 uint32_t job_capacity, struct expert_job_record *jobs_out);
 
+/* ---- original-weights experts: MXFP4 weights by E4M3 block-quantized activations (mx_oracle.c) ---- */
+double orc_e2m1_value(uint32_t code);
+double orc_e4m3_value(uint32_t code);
+double orc_e8m0_value(uint32_t code);
+/* bfloat16 values -> natural-order E4M3 codes and block exponents (tests/linear_reference.c:249-288) */
+void orc_mx_quantize(const uint16_t *values, uint32_t width, uint8_t *codes_out, uint8_t *exponents_out);
+void orc_mx_codes_lay_out(const uint8_t *codes, uint32_t width, uint8_t *stored_out);
+void orc_mx_operands_lay_out(const uint8_t *codes, uint32_t width, uint16_t *operands_out);
+/* 4-bit codes [output][input] and E8M0 scales [output][input / 32] -> the stored matrix */
+void orc_mx_weights_lay_out(const uint8_t *codes, const uint8_t *scales, uint32_t outputs, uint32_t inputs,
+			    uint8_t *stored_out);
+uint16_t orc_mx_output(const uint8_t *stored, uint32_t outputs, uint32_t inputs, uint32_t output, const uint8_t *codes,
+		       const uint8_t *exponents, uint32_t slices);
+uint16_t orc_mx_hidden(uint16_t gate_bits, uint16_t up_bits, float limit, float route_weight);
+void orc_mx_experts(const struct expert_gate_up_arguments *gate_up, const struct expert_down_arguments *down,
+		    uint32_t job_count, uint32_t slices_gate_up, uint32_t slices_down, uint64_t hidden_codes_offset,
+		    uint64_t hidden_exponents_offset, uint64_t hidden_operands_offset, unsigned char *arena);
+void orc_mx_row_sum(const struct expert_row_sum_arguments *record, uint32_t rows, unsigned char *arena);
+
 #endif

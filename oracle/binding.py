@@ -67,6 +67,26 @@ def load_oracle():
     lib.orc_router_jobs.restype = C.c_uint32
     lib.orc_router_jobs.argtypes = [u32p, f32p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, u64p, C.c_uint32,
                                     C.c_void_p]
+    u8 = u8p
+    lib.orc_e2m1_value.restype = lib.orc_e4m3_value.restype = lib.orc_e8m0_value.restype = C.c_double
+    lib.orc_e2m1_value.argtypes = lib.orc_e4m3_value.argtypes = lib.orc_e8m0_value.argtypes = [C.c_uint32]
+    lib.orc_mx_quantize.restype = None
+    lib.orc_mx_quantize.argtypes = [u16p, C.c_uint32, u8, u8]
+    lib.orc_mx_codes_lay_out.restype = None
+    lib.orc_mx_codes_lay_out.argtypes = [u8, C.c_uint32, u8]
+    lib.orc_mx_operands_lay_out.restype = None
+    lib.orc_mx_operands_lay_out.argtypes = [u8, C.c_uint32, u16p]
+    lib.orc_mx_weights_lay_out.restype = None
+    lib.orc_mx_weights_lay_out.argtypes = [u8, u8, C.c_uint32, C.c_uint32, u8]
+    lib.orc_mx_output.restype = C.c_uint16
+    lib.orc_mx_output.argtypes = [u8, C.c_uint32, C.c_uint32, C.c_uint32, u8, u8, C.c_uint32]
+    lib.orc_mx_hidden.restype = C.c_uint16
+    lib.orc_mx_hidden.argtypes = [C.c_uint16, C.c_uint16, C.c_float, C.c_float]
+    lib.orc_mx_experts.restype = None
+    lib.orc_mx_experts.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint64,
+                                   C.c_uint64, C.c_uint64, u8]
+    lib.orc_mx_row_sum.restype = None
+    lib.orc_mx_row_sum.argtypes = [C.c_void_p, C.c_uint32, u8]
     return lib
 
 
@@ -82,6 +102,18 @@ def load_reference():
     lib.test_exl3_state.argtypes = [u8p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32]
     lib.test_exl3_reconstruct.restype = C.c_uint16
     lib.test_exl3_reconstruct.argtypes = [u8p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32]
+    for name in ("test_weight_format_e2m1_value", "test_weight_format_e4m3_value", "test_weight_format_e8m0_value"):
+        getattr(lib, name).restype = C.c_double
+        getattr(lib, name).argtypes = [C.c_uint32]
+    lib.test_linear_quantize.argtypes = [u16p, C.c_uint32, u8p, u8p]
+    lib.test_linear_codes_lay_out.argtypes = [u8p, C.c_uint32, u8p]
+    lib.test_weight_format_lay_out.argtypes = [C.c_int, C.c_void_p, u8p, C.c_uint64, u8p, C.c_uint64, u8p, C.c_uint64]
+    lib.test_linear_bfloat16_nearest.restype = C.c_uint16
+    lib.test_linear_bfloat16_nearest.argtypes = [C.c_double]
+    lib.test_linear_hidden_value.restype = C.c_double
+    lib.test_linear_hidden_value.argtypes = [C.c_double] * 4
+    lib.test_linear_fed_values_of_codes.argtypes = [u8p, C.c_uint32, C.POINTER(C.c_double)]
+    lib.test_linear_output_is_within_tolerance.restype = C.c_bool
     lib.ordered_collective_host.restype = C.c_int
     lib.ordered_collective_host.argtypes = [C.POINTER(f32p), C.POINTER(f32p), C.c_uint32, C.c_uint32, C.c_int]
     return lib

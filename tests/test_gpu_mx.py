@@ -1,0 +1,184 @@
+"""The original-weights routed experts (MXFP4 weights by E4M3 block-quantized activations) on a CUDA device through the
+C-ABI library, against the CPU oracle (itself pinned to the reference's test references). Mirrors the reference's
+expert card tests (tests/linear_expert_card_test.c): quantization bit for bit, products within the tolerance of a
+bfloat16 result, row sums bit for bit given the pair outputs."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from anemone_b200 import records as R
+from anemone_b200 import synthetic
+from oracle.binding import f32p, ptr, u16p, u32p, u64p, u8p
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def api():
+    from anemone_b200 import api as module
+    assert module.card_count() >= 1, "no CUDA device: the CUDA path cannot run and there is no fallback"
+    return module
+
+
+def mx_matrix(oracle, rng, outputs, inputs):
+    """Stored MXFP4 matrix of the original-weights profile: uniform E2M1 nibbles, E8M0 codes 127 + e, e in [-8, -4]."""
+    codes = rng.integers(0, 16, size=outputs * inputs, dtype=np.uint8)
+    scales = (127 + rng.integers(-8, -3, size=outputs * inputs // 32)).astype(np.uint8)
+    stored = np.zeros(outputs * inputs // 2 + outputs * inputs // 32, dtype=np.uint8)
+    oracle.orc_mx_weights_lay_out(ptr(codes, u8p), ptr(scales, u8p), outputs, inputs, ptr(stored, u8p))
+    return stored
+
+
+def prepare_kernels(api, card):
+    lib = api.library()
+    kernels = R.LinearKernels()
+    lib.linear_kernels_prepare.argtypes = [C.POINTER(api.BackendOperations), C.c_void_p, C.c_uint32,
+                                           C.POINTER(R.LinearKernels)]
+    api.check(lib.linear_kernels_prepare(card.ops_pointer, card.handle, 100, C.byref(kernels)), "linear_kernels_prepare")
+    return kernels
+
+
+def test_activation_quantize_is_bit_exact(api, oracle):
+    rng = np.random.default_rng(31)
+    width, rows = 512, 6
+    values = synthetic.to_bfloat16((rng.normal(0, 1, (rows, width)) * np.array([1, 1e-3, 300, 1e-6, 1, 30])[:, None])
+                                   .astype(np.float32))
+    values[4, :40] = 0
+    values[4, 5] = 0x8000
+    values[4, 64:96] = synthetic.to_bfloat16(np.full(32, 0.4375, dtype=np.float32))
+    layout = api.Layout()
+    at = {name: layout.take(size) for name, size in (("values", rows * width * 2), ("codes", rows * width),
+                                                     ("exponents", rows * width // 32), ("operands", rows * width * 2))}
+    card = api.Card(0, layout.take(4096, 4096))
+    try:
+        kernels = prepare_kernels(api, card)
+        card.upload(at["values"], values)
+        description = R.LinearQuantizeDescription(
+            R.LinearRange(at["values"], rows * width * 2), R.LinearRange(at["codes"], rows * width),
+            R.LinearRange(at["exponents"], rows * width // 32), R.LinearRange(at["operands"], rows * width * 2), width, rows)
+        launch = R.KernelLaunch()
+        lib = api.library()
+        lib.linear_quantize_prepare.argtypes = [C.POINTER(R.LinearQuantizeDescription), C.c_uint64,
+                                                C.POINTER(R.LinearKernels), C.POINTER(R.KernelLaunch)]
+        api.check(lib.linear_quantize_prepare(C.byref(description), card.arena_bytes, C.byref(kernels), C.byref(launch)),
+                  "linear_quantize_prepare")
+        card.run([launch])
+        card.wait()
+        codes = card.download(at["codes"], rows * width).reshape(rows, width)
+        exponents = card.download(at["exponents"], rows * width // 32).reshape(rows, width // 32)
+        operands = card.download(at["operands"], rows * width * 2, np.uint16).reshape(rows, width)
+    finally:
+        card.close()
+    for row in range(rows):
+        natural, want_exponents = np.zeros(width, np.uint8), np.zeros(width // 32, np.uint8)
+        line = np.ascontiguousarray(values[row])
+        oracle.orc_mx_quantize(ptr(line, u16p), width, ptr(natural, u8p), ptr(want_exponents, u8p))
+        want_codes, want_operands = np.zeros(width, np.uint8), np.zeros(width, np.uint16)
+        oracle.orc_mx_codes_lay_out(ptr(natural, u8p), width, ptr(want_codes, u8p))
+        oracle.orc_mx_operands_lay_out(ptr(natural, u8p), width, ptr(want_operands, u16p))
+        assert np.array_equal(exponents[row], want_exponents), row
+        assert np.array_equal(codes[row], want_codes), row
+        assert np.array_equal(operands[row], want_operands), row
+
+
+@pytest.mark.parametrize("slices", [(1, 1), (4, 4), (8, 2), (16, 8)])
+def test_routed_experts_match_oracle(api, oracle, slices):
+    rng = np.random.default_rng(32 + slices[0])
+    H, I, experts, rows, picks = 1024, 512, 6, 11, 2
+    pairs = rows * picks
+    layout = api.Layout()
+    table = np.zeros((experts, 3), dtype=np.uint64)
+    matrices = []
+    for expert in range(experts):
+        for which, (outputs, inputs) in enumerate(((I, H), (I, H), (H, I))):
+            data = mx_matrix(oracle, rng, outputs, inputs)
+            table[expert, which] = layout.take(data.size, 64)
+            matrices.append((int(table[expert, which]), data))
+    weights_end = layout.cursor
+    chosen = np.stack([np.sort(rng.choice(experts, size=picks, replace=False)) for _ in range(rows)]).astype(np.uint32)
+    route = rng.uniform(0.3, 1.0, size=(rows, picks)).astype(np.float32)
+    job_capacity = rows * picks + 1
+    jobs = (R.ExpertJob * job_capacity)()
+    oracle.orc_router_jobs(ptr(chosen, u32p), ptr(route, f32p), rows, picks, experts, 0, ptr(table, u64p),
+                           job_capacity, C.byref(jobs))
+    sizes = {"jobs": job_capacity * 96, "values": rows * H * 2, "codes": rows * H, "exponents": rows * H // 32,
+             "operands": rows * H * 2, "hidden": pairs * I * 2, "hidden_codes": pairs * I,
+             "hidden_exponents": pairs * I // 32, "hidden_operands": pairs * I * 2, "pair_output": pairs * H * 2,
+             "row_output": rows * H * 4}
+    at = {name: layout.take(size) for name, size in sizes.items()}
+    arena_bytes = layout.take(4096, 4096)
+    image = np.zeros(arena_bytes, dtype=np.uint8)
+    for offset, data in matrices:
+        image[offset:offset + data.size] = data
+    image[at["jobs"]:at["jobs"] + sizes["jobs"]] = np.frombuffer(bytes(jobs), dtype=np.uint8)
+    tokens = synthetic.tokens(rng, rows, H)
+    image[at["values"]:at["values"] + sizes["values"]] = tokens.view(np.uint8).reshape(-1)
+    description = R.LinearRoutedExpertsDescription()
+    description.jobs = R.LinearRange(at["jobs"], sizes["jobs"])
+    description.expert_weights = R.LinearRange(0, weights_end)
+    for name in ("codes", "exponents", "operands", "hidden", "hidden_codes", "hidden_exponents", "hidden_operands",
+                 "pair_output", "row_output"):
+        setattr(description, name, R.LinearRange(at[name], sizes[name]))
+    description.gate_up_shape, description.down_shape = R.MatrixShape(I, H, 4, 0), R.MatrixShape(H, I, 4, 0)
+    description.weight_format, description.job_count, description.row_count = 3, job_capacity, rows
+    description.pairs_per_row, description.activation_limit = picks, 7.0
+    description.gate_up_slice_count, description.down_slice_count = slices
+    lib = api.library()
+    lib.linear_quantize_prepare.argtypes = [C.POINTER(R.LinearQuantizeDescription), C.c_uint64,
+                                            C.POINTER(R.LinearKernels), C.POINTER(R.KernelLaunch)]
+    lib.linear_routed_experts_prepare.argtypes = [C.POINTER(R.LinearRoutedExpertsDescription), C.c_uint64,
+                                                  C.POINTER(R.LinearKernels), C.POINTER(R.KernelLaunch)]
+    card = api.Card(0, arena_bytes)
+    try:
+        kernels = prepare_kernels(api, card)
+        card.upload(0, image)
+        quantize = R.LinearQuantizeDescription(R.LinearRange(at["values"], sizes["values"]), description.codes,
+                                               description.exponents, description.operands, H, rows)
+        first = R.KernelLaunch()
+        api.check(lib.linear_quantize_prepare(C.byref(quantize), arena_bytes, C.byref(kernels), C.byref(first)), "quantize")
+        launches = (R.KernelLaunch * 4)()
+        api.check(lib.linear_routed_experts_prepare(C.byref(description), arena_bytes, C.byref(kernels), launches),
+                  "linear_routed_experts_prepare")
+        card.run([first] + list(launches))
+        card.wait()
+        received = card.download(0, arena_bytes)
+    finally:
+        card.close()
+    # the oracle on the same image, from the card's own (bit-exact, checked above) quantized rows
+    expected = image.copy()
+    for name in ("codes", "exponents", "operands"):
+        expected[at[name]:at[name] + sizes[name]] = received[at[name]:at[name] + sizes[name]]
+    gate_up = R.ExpertGateUp(at["jobs"], at["codes"], at["exponents"], at["operands"], at["hidden"], I, H, pairs, picks,
+                             7.0, 0)
+    down = R.ExpertDown(at["jobs"], at["hidden_codes"], at["hidden_exponents"], at["hidden_operands"], at["pair_output"],
+                        H, I, pairs, 0)
+    oracle.orc_mx_experts(C.byref(gate_up), C.byref(down), job_capacity, slices[0], slices[1], at["hidden_codes"],
+                          at["hidden_exponents"], at["hidden_operands"], ptr(expected, u8p))
+    row_sum = R.ExpertRowSum(at["pair_output"], at["row_output"], H, picks)
+    oracle.orc_mx_row_sum(C.byref(row_sum), rows, ptr(expected, u8p))
+
+    def ordinals(bits):
+        bits = bits.astype(np.int32)
+        return np.where(bits & 0x8000, -(bits & 0x7FFF), bits & 0x7FFF)
+
+    def region(data, name, dtype):
+        return data[at[name]:at[name] + sizes[name]].view(dtype)
+    hidden_got, hidden_want = region(received, "hidden", np.uint16), region(expected, "hidden", np.uint16)
+    distance = np.abs(ordinals(hidden_got) - ordinals(hidden_want))
+    assert distance.max() <= 2 and (distance == 0).mean() > 0.98  # the tensor cores' sum of a block may round otherwise
+    out_got = synthetic.from_bfloat16(region(received, "pair_output", np.uint16))
+    out_want = synthetic.from_bfloat16(region(expected, "pair_output", np.uint16))
+    assert np.isfinite(out_got).all() and np.abs(out_want).max() > 0
+    assert np.abs(out_got - out_want).max() <= max(2e-2, 2.0 ** -6 * np.abs(out_want).max())
+    cosine = float(out_got.astype(np.float64) @ out_want.astype(np.float64) /
+                   (np.linalg.norm(out_got) * np.linalg.norm(out_want)))
+    assert cosine >= 0.9999
+    # the row sum is bit-exact given the pair outputs the card wrote
+    pair_values = out_got.reshape(rows, picks, H)
+    resummed = np.zeros((rows, H), dtype=np.float32)
+    for slot in range(picks):
+        resummed = (resummed + pair_values[:, slot, :]).astype(np.float32)
+    assert np.array_equal(resummed.view(np.uint32), region(received, "row_output", np.uint32).reshape(rows, H))
+    # weights and inputs untouched
+    assert np.array_equal(received[:weights_end], image[:weights_end])

@@ -75,7 +75,7 @@ def test_experts_prepare_launches_and_refusals():
     grids = [tuple(l.grid) for l in launches]
     assert grids == [(1, 7, 2), (2, 7, 2), (1, 7, 1), (4, 7, 1), (1, 7, 1)]
     assert [l.block[0] for l in launches] == [128] * 5
-    assert launches[1].dynamic_shared_byte_count == 8 * 4 * 8 * 16 * 6 and launches[0].dynamic_shared_byte_count == 0
+    assert launches[1].dynamic_shared_byte_count == max(4 * 4 * 8 * 16 * 6, 16384) and launches[0].dynamic_shared_byte_count == 0
     for launch in launches:
         assert bytes(launch.argument[:80]) == bytes(record) and not any(launch.argument[80:])
     # refusals leave the whole table untouched
