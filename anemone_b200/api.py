@@ -85,6 +85,7 @@ def library():
         lib.backend_b200_launch_count.argtypes = [_card]
         lib.backend_b200_arena_address.restype = C.c_uint64
         lib.backend_b200_arena_address.argtypes = [_card]
+        lib.backend_b200_waits_expired.argtypes = [_card, C.POINTER(C.c_uint32)]
         lib.backend_b200_fill.argtypes = [_card, C.c_uint64, C.c_ubyte, C.c_uint64]
         lib.backend_b200_ipc_export.argtypes = [_card, C.c_char_p]
         lib.backend_b200_ipc_connect.argtypes = [_card, C.c_char_p, C.c_uint64, C.c_uint64]
@@ -95,6 +96,10 @@ def library():
                                            C.c_uint32, C.POINTER(R.KernelLaunch)]
         lib.exl3_moe_prepare.argtypes = [C.POINTER(R.Exl3Moe), C.c_uint64, C.POINTER(BackendOperations), _card,
                                          C.POINTER(R.KernelLaunch)]
+        lib.exl3_prefill_prepare.argtypes = [C.POINTER(R.Exl3Prefill), C.c_uint64, C.POINTER(BackendOperations),
+                                             _card, C.POINTER(R.KernelLaunch)]
+        lib.exl3_prefill_sizes.restype = None
+        lib.exl3_prefill_sizes.argtypes = [C.c_uint32] * 6 + [C.POINTER(R.Exl3PrefillParts)]
         lib.exl3_moe_sizes.restype = None
         lib.exl3_moe_sizes.argtypes = [C.c_uint32] * 4 + [C.POINTER(R.Exl3MoeSizes)]
         lib.bb_exl3_row_sum_prepare.argtypes = [C.POINTER(R.ExpertRowSum), C.c_uint32, C.c_uint64,
@@ -118,6 +123,14 @@ def moe_sizes(pair_count, job_count, input_size, inner_size):
     sizes = R.Exl3MoeSizes()
     library().exl3_moe_sizes(pair_count, job_count, input_size, inner_size, C.byref(sizes))
     return sizes
+
+
+def prefill_parts(row_capacity, picks, shared_count, expert_count, input_size, inner_size):
+    """Workspace layout of the prefill launches for these shapes (exl3_prefill_sizes)."""
+    parts = R.Exl3PrefillParts()
+    library().exl3_prefill_sizes(row_capacity, picks, shared_count, expert_count, input_size, inner_size,
+                                 C.byref(parts))
+    return parts
 
 
 def align(value, alignment):
@@ -230,6 +243,12 @@ class Card:
         value = C.c_double()
         check(self.ops.measure_elapsed_us(self.handle, WAIT_NANOSECONDS, C.byref(value)), "measure_elapsed_us")
         return value.value
+
+    def waits_expired(self):
+        """Waits for the queue; True if a kernel gave up a bounded barrier wait (its CTA then stored nothing)."""
+        expired = C.c_uint32()
+        check(library().backend_b200_waits_expired(self.handle, C.byref(expired)), "waits_expired")
+        return expired.value != 0
 
     def launch_count(self):
         return library().backend_b200_launch_count(self.handle)

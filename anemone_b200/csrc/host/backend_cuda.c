@@ -987,6 +987,33 @@ done:
 	CARD_LEAVE(card);
 }
 
+result_status backend_b200_waits_expired(struct device_card *card, uint32_t *expired_out)
+{
+	if (card == NULL || expired_out == NULL)
+		return STATUS_INVALID_ARGUMENT;
+	uint32_t expired = 0;
+	CARD_ENTER(card);
+	if (card->failed) {
+		status = STATUS_DEVICE_ERROR;
+		goto done;
+	}
+	DRIVER(card, cuStreamSynchronize(card->stream));
+	for (uint32_t module = 0; module < CARD_MODULES_MOST; module++) {
+		CUdeviceptr address = 0;
+		size_t bytes = 0;
+		uint32_t word = 0;
+		if (card->modules[module] == NULL ||
+		    cu->cuModuleGetGlobal(&address, &bytes, card->modules[module], "exl3_wait_expired") != CUDA_SUCCESS ||
+		    bytes != sizeof(word))
+			continue; /* a kernel file without bounded barrier waits */
+		DRIVER(card, cuMemcpyDtoH(&word, address, sizeof(word)));
+		expired |= word;
+	}
+	*expired_out = expired;
+done:
+	CARD_LEAVE(card);
+}
+
 uint64_t backend_b200_launch_count(const struct device_card *card)
 {
 	return card != NULL ? card->launches_queued : 0;

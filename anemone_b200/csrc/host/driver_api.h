@@ -44,6 +44,8 @@
 	X(cuModuleLoadData)       \
 	X(cuModuleUnload)         \
 	X(cuModuleGetFunction)    \
+	X(cuModuleGetGlobal)      \
+	X(cuMemcpyDtoH)           \
 	X(cuFuncGetParamInfo)     \
 	X(cuFuncGetAttribute)     \
 	X(cuFuncSetAttribute)     \

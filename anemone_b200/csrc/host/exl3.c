@@ -275,3 +275,80 @@ result_status exl3_moe_prepare(const struct exl3_moe_record *record, uint64_t ar
 	memcpy(launches_out, launches, sizeof(launches));
 	return STATUS_OK;
 }
+
+result_status exl3_prefill_prepare(const struct exl3_prefill_record *record, uint64_t arena_byte_count,
+				   const struct backend_operations *backend, struct device_card *card,
+				   struct kernel_launch *launches_out)
+{
+	if (record == NULL || backend == NULL || card == NULL || launches_out == NULL ||
+	    backend->kernel_prepare == NULL || record->reserved_zero != 0)
+		return STATUS_INVALID_ARGUMENT;
+	const uint32_t H = record->input_size, I = record->inner_size;
+	const uint32_t experts = record->expert_count + record->shared_count;
+	if (record->expert_count == 0 || record->expert_count > ROUTER_B200_MAXIMUM_EXPERTS ||
+	    record->shared_count > ROUTER_B200_THREADS - ROUTER_B200_MAXIMUM_EXPERTS || record->picks == 0 ||
+	    record->picks > ROUTER_B200_MAXIMUM_PICKS || record->picks > record->expert_count ||
+	    record->row_capacity == 0 || record->row_capacity > EXL3_MAXIMUM_GRID_ROWS || H == 0 || I == 0 ||
+	    H % EXL3_TRANSFORM != 0 || I % EXL3_TRANSFORM != 0 || I > H || record->scoring > ROUTER_SCORING_SQRT_SOFTPLUS ||
+	    !isfinite(record->route_scale) || !isfinite(record->activation_limit) || record->activation_limit <= 0)
+		return STATUS_INVALID_ARGUMENT;
+	const struct exl3_prefill_parts parts = exl3_prefill_parts_of(record->row_capacity, record->picks,
+								      record->shared_count, record->expert_count, H, I);
+	if (parts.tile_capacity > EXL3_MAXIMUM_GRID_ROWS)
+		return STATUS_INVALID_ARGUMENT;
+	const uint64_t rows = record->row_capacity, slots = record->picks + record->shared_count;
+	const struct checked_range ranges[10] = {
+		{ "scores", record->scores_offset, rows * record->expert_count * 4u },
+		{ "input", record->input_offset, rows * H * EXL3_HALF_BYTES },
+		{ "expert table", record->expert_table_offset, (uint64_t)experts * 24u },
+		{ "width table", record->widths_offset, (uint64_t)experts * 4u },
+		{ "picks", record->picks_offset, rows * record->picks * 4u },
+		{ "weights", record->weights_offset, rows * record->picks * 4u },
+		{ "workspace", record->workspace_offset, parts.total },
+		{ "pair outputs", record->pair_output_offset, rows * slots * H * 4u },
+		{ "row outputs", record->row_output_offset, rows * H * 4u },
+		{ "step", record->step_offset, sizeof(struct step_block) }
+	};
+	if (record->workspace_offset % 1024u != 0 ||
+	    !prepare_ranges_are_valid("EXL3 prefill", ranges, 10, arena_byte_count))
+		return STATUS_INVALID_ARGUMENT;
+	static const char *const names[EXL3_PREFILL_LAUNCHES] = { "exl3_prefill_picks",	   "exl3_prefill_group",
+								  "exl3_prefill_tiles",	   "exl3_prefill_operands",
+								  "exl3_prefill_gate_up",  "exl3_prefill_down",
+								  "exl3_prefill_row_sum" };
+	const uint32_t row_warps = ROUTER_B200_THREADS / EXL3_WARP;
+	const struct {
+		uint32_t x, y, z, threads, shared;
+	} shapes[EXL3_PREFILL_LAUNCHES] = {
+		{ (record->row_capacity + row_warps - 1u) / row_warps, 1, 1, ROUTER_B200_THREADS, 0 },
+		{ experts, 1, 1, 256u, 0 },
+		{ 1, 1, 1, ROUTER_B200_THREADS, 0 },
+		{ parts.tile_capacity, transform_grid(H), EXL3_PROJECTIONS, EXL3_TRANSFORM_THREADS, 0 },
+		{ I / EXL3_TRANSFORM, parts.tile_capacity, 1, EXL3_PREFILL_GEMM_THREADS,
+		  EXL3_PREFILL_GATE_UP_STAGES * EXL3_PROJECTIONS * EXL3_PREFILL_STAGE_BYTES },
+		{ H / EXL3_TRANSFORM, parts.tile_capacity, 1, EXL3_PREFILL_GEMM_THREADS,
+		  EXL3_PREFILL_DOWN_STAGES * EXL3_PREFILL_STAGE_BYTES },
+		{ (H + EXL3_ROW_SUM_THREADS - 1u) / EXL3_ROW_SUM_THREADS, record->row_capacity, 1, EXL3_ROW_SUM_THREADS, 0 }
+	};
+	struct kernel_launch launches[EXL3_PREFILL_LAUNCHES];
+	for (uint32_t index = 0; index < EXL3_PREFILL_LAUNCHES; index++) {
+		uint32_t kernel = BACKEND_NO_KERNEL;
+		const result_status status =
+			backend->kernel_prepare(card, EXL3_PREFILL_KERNEL_FILE, names[index], sizeof(*record), &kernel);
+		if (status != STATUS_OK)
+			return status;
+		if (kernel == BACKEND_NO_KERNEL)
+			return STATUS_UNSUPPORTED;
+		prepare_launch_fill(&launches[index], kernel, shapes[index].x, shapes[index].y, shapes[index].z,
+				    shapes[index].threads, shapes[index].shared, record, sizeof(*record));
+	}
+	memcpy(launches_out, launches, sizeof(launches));
+	return STATUS_OK;
+}
+
+void exl3_prefill_sizes(uint32_t row_capacity, uint32_t picks, uint32_t shared_count, uint32_t expert_count,
+			uint32_t input_size, uint32_t inner_size, struct exl3_prefill_parts *parts_out)
+{
+	if (parts_out != NULL)
+		*parts_out = exl3_prefill_parts_of(row_capacity, picks, shared_count, expert_count, input_size, inner_size);
+}

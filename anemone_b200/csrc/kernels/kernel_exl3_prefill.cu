@@ -1,0 +1,660 @@
+/*
+ * kernel_exl3_prefill.cu: the routed-expert layer for many rows (struct exl3_prefill_record): rows are grouped per
+ * expert into tiles of 128 and every (row tile, 128 outputs) is one dense contraction on the fifth-generation tensor
+ * cores. The reference's counterpart is its tensor-core prefill family (source/kernel_exl3_tcp.cuh), fixed to its
+ * model's shapes and to mma.sync; here a CTA
+ *   - streams the row tile's FP16 operand blocks (pre-tiled in the tensor cores' no-swizzle K-major layout) and the
+ *     trellis rows of its 128 outputs into a ring of shared-memory stages by bulk asynchronous copies (one thread),
+ *   - decodes the trellis tiles in registers into FP16 and stores them as the B operand block of the stage (eight
+ *     warps; the decode's fragment order makes every store a contiguous 128 bytes of the block),
+ *   - multiplies with tcgen05.mma (one thread), FP32 accumulators in tensor memory, the stage released by
+ *     tcgen05.commit,
+ *   - reads the accumulators back with tcgen05.ld and applies the chain's FP32 epilogue (exl3_passes.cuh: Hadamard,
+ *     scales, SwiGLU, down-side transform / route weight) a warp a row.
+ * Arithmetic per value is the retained chain's; only the association of the FP32 sums over K is the tensor cores'.
+ * Every wait is bounded: one that runs out raises exl3_wait_expired, the CTA stores nothing, waits (bounded) for what
+ * it has in flight, frees its tensor memory and returns.
+ */
+#include "exl3_passes.cuh"
+#include "router_device.cuh"
+
+#define PREFILL_MOST_STAGES 4u
+#define PREFILL_DECODE_WARPS 8u
+#define PREFILL_DECODE_THREADS (PREFILL_DECODE_WARPS * EXL3_WARP)
+#define PREFILL_COLUMNS 128u /* tensor-memory columns of one accumulator tile */
+#define PREFILL_GROUP_THREADS 256u
+
+struct prefill_shared {
+	uint64_t full[PREFILL_MOST_STAGES]; /* the stage's copies have landed */
+	uint64_t decoded[PREFILL_MOST_STAGES]; /* the stage's B blocks are written */
+	uint64_t consumed[PREFILL_MOST_STAGES]; /* the stage's products are done */
+	uint64_t done; /* every product of the CTA is done */
+	uint32_t tensor_memory;
+	volatile uint32_t failed;
+	uint32_t armed; /* K blocks whose copies were started */
+	uint32_t issued; /* 1: products were issued and `done` will complete */
+};
+
+struct prefill_view {
+	const struct exl3_prefill_parts parts;
+	unsigned char *workspace;
+	uint32_t experts; /* routed + shared */
+	uint32_t pairs_per_row;
+	uint32_t live;
+};
+
+__device__ __forceinline__ prefill_view prefill_view_of(const struct exl3_prefill_record &record, unsigned char *arena)
+{
+	const struct step_block step = *reinterpret_cast<const struct step_block *>(arena + record.step_offset);
+	prefill_view view = { exl3_prefill_parts_of(record.row_capacity, record.picks, record.shared_count,
+						    record.expert_count, record.input_size, record.inner_size),
+			      arena + record.workspace_offset, record.expert_count + record.shared_count,
+			      record.picks + record.shared_count, min(step.row_count, record.row_capacity) };
+	return view;
+}
+
+/* ------------------------------------------------------------------ routing */
+
+extern "C" __global__ void __launch_bounds__(ROUTER_B200_THREADS)
+	exl3_prefill_picks(struct exl3_prefill_record record, unsigned char *arena)
+{
+	__shared__ uint32_t chosen[ROUTER_B200_THREADS / WARP][ROUTER_B200_MAXIMUM_PICKS];
+	__shared__ float weight[ROUTER_B200_THREADS / WARP][ROUTER_B200_MAXIMUM_PICKS];
+	const struct step_block step = *reinterpret_cast<const struct step_block *>(arena + record.step_offset);
+	const uint32_t live = min(step.row_count, record.row_capacity);
+	const uint32_t warp = threadIdx.x / WARP, lane = threadIdx.x % WARP;
+	const uint32_t row = blockIdx.x * (ROUTER_B200_THREADS / WARP) + warp;
+	if (row >= live)
+		return;
+	router_row(reinterpret_cast<const float *>(arena + record.scores_offset) + (uint64_t)row * record.expert_count,
+		   record.expert_count, record.picks, record.scoring, record.route_scale, lane, chosen[warp], weight[warp],
+		   reinterpret_cast<uint32_t *>(arena + record.picks_offset) + (uint64_t)row * record.picks,
+		   reinterpret_cast<float *>(arena + record.weights_offset) + (uint64_t)row * record.picks);
+}
+
+/* A block an expert: its entries in ascending row order (a row holds an expert at most once) and their count. */
+extern "C" __global__ void __launch_bounds__(PREFILL_GROUP_THREADS)
+	exl3_prefill_group(struct exl3_prefill_record record, unsigned char *arena)
+{
+	__shared__ uint32_t warp_total[PREFILL_GROUP_THREADS / WARP];
+	const prefill_view view = prefill_view_of(record, arena);
+	const uint32_t expert = blockIdx.x, lane = threadIdx.x % WARP, warp = threadIdx.x / WARP;
+	const uint32_t *const picked = reinterpret_cast<const uint32_t *>(arena + record.picks_offset);
+	const float *const weights = reinterpret_cast<const float *>(arena + record.weights_offset);
+	struct exl3_prefill_entry *const entries =
+		reinterpret_cast<struct exl3_prefill_entry *>(view.workspace + view.parts.entries) +
+		(uint64_t)expert * record.row_capacity;
+	uint32_t base = 0;
+	for (uint32_t first = 0; first < view.live; first += PREFILL_GROUP_THREADS) {
+		const uint32_t row = first + threadIdx.x;
+		bool found = false;
+		uint32_t slot = 0;
+		float route_weight = 1.0f;
+		if (row < view.live) {
+			if (expert >= record.expert_count) {
+				found = true;
+				slot = record.picks + (expert - record.expert_count);
+			} else {
+				for (uint32_t place = 0; place < record.picks; place++)
+					if (picked[(uint64_t)row * record.picks + place] == expert) {
+						found = true;
+						slot = place;
+						route_weight = weights[(uint64_t)row * record.picks + place];
+					}
+			}
+		}
+		const uint32_t ballot = __ballot_sync(0xFFFFFFFFu, found);
+		if (lane == 0)
+			warp_total[warp] = (uint32_t)__popc(ballot);
+		__syncthreads();
+		uint32_t before = 0, total = 0;
+		for (uint32_t other = 0; other < PREFILL_GROUP_THREADS / WARP; other++) {
+			before += other < warp ? warp_total[other] : 0u;
+			total += warp_total[other];
+		}
+		if (found) {
+			struct exl3_prefill_entry entry;
+			entry.pair = row * view.pairs_per_row + slot;
+			entry.route_weight = route_weight;
+			entries[base + before + (uint32_t)__popc(ballot & ((1u << lane) - 1u))] = entry;
+		}
+		base += total;
+		__syncthreads();
+	}
+	if (threadIdx.x == 0)
+		reinterpret_cast<uint32_t *>(view.workspace + view.parts.counts)[expert] = base;
+}
+
+/* One block: the tile table in ascending expert order and the tile count. */
+extern "C" __global__ void __launch_bounds__(ROUTER_B200_THREADS)
+	exl3_prefill_tiles(struct exl3_prefill_record record, unsigned char *arena)
+{
+	__shared__ uint32_t warp_total[ROUTER_B200_THREADS / WARP];
+	const prefill_view view = prefill_view_of(record, arena);
+	uint32_t *const counts = reinterpret_cast<uint32_t *>(view.workspace + view.parts.counts);
+	struct exl3_prefill_tile *const tiles =
+		reinterpret_cast<struct exl3_prefill_tile *>(view.workspace + view.parts.tiles);
+	const uint32_t expert = threadIdx.x, lane = threadIdx.x % WARP, warp = threadIdx.x / WARP;
+	const uint32_t rows = expert < view.experts ? counts[expert] : 0u;
+	const uint32_t mine = (rows + EXL3_PREFILL_TILE_ROWS - 1u) / EXL3_PREFILL_TILE_ROWS;
+	uint32_t inclusive = mine;
+	for (uint32_t distance = 1; distance < WARP; distance <<= 1) {
+		const uint32_t other = __shfl_up_sync(0xFFFFFFFFu, inclusive, distance);
+		if (lane >= distance)
+			inclusive += other;
+	}
+	if (lane == WARP - 1u)
+		warp_total[warp] = inclusive;
+	__syncthreads();
+	uint32_t before = 0, total = 0;
+	for (uint32_t other = 0; other < ROUTER_B200_THREADS / WARP; other++) {
+		before += other < warp ? warp_total[other] : 0u;
+		total += warp_total[other];
+	}
+	const uint32_t first_tile = before + inclusive - mine;
+	for (uint32_t index = 0; index < mine; index++) {
+		struct exl3_prefill_tile tile;
+		tile.expert = expert;
+		tile.first_entry = index * EXL3_PREFILL_TILE_ROWS;
+		tile.row_count = min(rows - tile.first_entry, EXL3_PREFILL_TILE_ROWS);
+		tile.reserved_zero = 0;
+		if (first_tile + index < view.parts.tile_capacity)
+			tiles[first_tile + index] = tile;
+	}
+	if (threadIdx.x == 0)
+		counts[view.experts] = min(total, view.parts.tile_capacity);
+}
+
+/* byte of (row, input) inside an operand block of 128 rows x 64 inputs: 16-byte pieces of eight inputs, the pieces of
+ * eight rows adjacent, the 16 row groups adjacent, then the next eight inputs */
+__device__ __forceinline__ uint32_t prefill_block_byte(uint32_t row, uint32_t input)
+{
+	return (input / 8u) * 2048u + (row / 8u) * 128u + (row % 8u) * 16u + (input % 8u) * 2u;
+}
+
+/* grid (tile capacity, ceil(H / 128 / 4), 2) x 128: x . suh, Hadamard, FP16 operands of gate (z = 0) and up (z = 1) */
+extern "C" __global__ void __launch_bounds__(EXL3_TRANSFORM_THREADS)
+	exl3_prefill_operands(struct exl3_prefill_record record, unsigned char *arena)
+{
+	const prefill_view view = prefill_view_of(record, arena);
+	const uint32_t tile_index = blockIdx.x;
+	if (tile_index >= reinterpret_cast<const uint32_t *>(view.workspace + view.parts.counts)[view.experts])
+		return;
+	const struct exl3_prefill_tile tile =
+		reinterpret_cast<const struct exl3_prefill_tile *>(view.workspace + view.parts.tiles)[tile_index];
+	const uint32_t lane = threadIdx.x % EXL3_WARP;
+	const uint32_t block = blockIdx.y * EXL3_TRANSFORM_WARPS + threadIdx.x / EXL3_WARP;
+	const uint32_t H = record.input_size;
+	if (block >= H / EXL3_TRANSFORM)
+		return;
+	const uint32_t channel = block * EXL3_TRANSFORM + lane * 4u;
+	const uint32_t bits_x2 = exl3_bits_x2(reinterpret_cast<const uint32_t *>(arena + record.widths_offset)[tile.expert]);
+	const uint64_t matrix =
+		reinterpret_cast<const uint64_t *>(arena + record.expert_table_offset)[3u * tile.expert + blockIdx.z];
+	float scale[4];
+	load_half4(reinterpret_cast<const __half *>(arena + matrix + exl3_code_bytes(H, record.inner_size, bits_x2)) + channel,
+		   scale);
+	const struct exl3_prefill_entry *const entries =
+		reinterpret_cast<const struct exl3_prefill_entry *>(view.workspace + view.parts.entries) +
+		(uint64_t)tile.expert * record.row_capacity + tile.first_entry;
+	const __nv_bfloat16 *const input = reinterpret_cast<const __nv_bfloat16 *>(arena + record.input_offset);
+	unsigned char *const blocks = view.workspace + view.parts.gate_up_operands +
+				      (((uint64_t)blockIdx.z * view.parts.tile_capacity + tile_index) *
+					       (H / EXL3_PREFILL_BLOCK_INPUTS) +
+				       channel / EXL3_PREFILL_BLOCK_INPUTS) *
+					      EXL3_PREFILL_BLOCK_BYTES;
+	for (uint32_t row = 0; row < tile.row_count; row++) {
+		const uint32_t source_row = entries[row].pair / view.pairs_per_row;
+		const uint2 raw = *reinterpret_cast<const uint2 *>(input + (uint64_t)source_row * H + channel);
+		float v[4] = { __uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xFFFF0000u),
+			       __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xFFFF0000u) };
+#pragma unroll
+		for (uint32_t i = 0; i < 4; i++)
+			v[i] = __fmul_rn(v[i], scale[i]);
+		hadamard128_warp(v, lane);
+#pragma unroll
+		for (uint32_t i = 0; i < 4; i++)
+			v[i] = __fmul_rn(v[i], EXL3_NORMALIZATION);
+		store_half4(reinterpret_cast<__half *>(blocks + prefill_block_byte(row, channel % EXL3_PREFILL_BLOCK_INPUTS)), v);
+	}
+}
+
+/* ------------------------------------------------------------------ tensor-core products */
+
+/* shared-memory matrix descriptor of an operand block at a 16-byte aligned address: no swizzle, K-major; 2048 bytes
+ * between the two 16-byte K pieces of a K = 16 step, 128 bytes between groups of eight rows */
+__device__ __forceinline__ uint64_t prefill_descriptor(uint32_t shared_address)
+{
+	return (uint64_t)((shared_address >> 4) & 0x3FFFu) | (uint64_t)(2048u >> 4) << 16 | (uint64_t)(128u >> 4) << 32 |
+	       (uint64_t)1 << 46;
+}
+
+/* FP16 A and B, both K-major, FP32 accumulators, M = 128, N = 128 */
+#define PREFILL_INSTRUCTION ((1u << 4) | ((128u >> 3) << 17) | ((128u >> 4) << 24))
+
+__device__ __forceinline__ void tensor_fence_before()
+{
+	asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ void tensor_fence_after()
+{
+	asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ void tensor_commit(uint64_t *barrier)
+{
+	asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+			     smem_address(barrier))
+		     : "memory");
+}
+
+__device__ __forceinline__ void decode_sync()
+{
+	asm volatile("bar.sync 1, %0;" ::"n"(PREFILL_DECODE_THREADS) : "memory");
+}
+
+/* The K loop of one CTA. matrices[m]: the codes of matrix m (`outputs` outputs), of which the CTA takes outputs
+ * 128 group .. + 127; operand_blocks[m]: the row tile's first operand block for matrix m, `blocks` blocks of 64 inputs.
+ * On return the decode warps (2 .. 9) know whether the accumulators (tensor-memory columns 128 m .. 128 m + 127 from
+ * shared->tensor_memory) are complete; warps 0 and 1 return false. All threads call. */
+template <uint32_t BX2, uint32_t MATRICES, uint32_t STAGES>
+__device__ __forceinline__ bool prefill_products(const unsigned char *const (&matrices)[MATRICES], uint32_t outputs,
+						 uint32_t group, const unsigned char *const (&operand_blocks)[MATRICES],
+						 uint32_t blocks, unsigned char *dynamic_shared, prefill_shared *shared)
+{
+	typedef exl3_ring<BX2> ring;
+	constexpr uint32_t row_bytes = EXL3_GROUP_TILES * ring::tile_bytes;
+	constexpr uint32_t stage_bytes = MATRICES * EXL3_PREFILL_STAGE_BYTES;
+	constexpr uint32_t trellis_at = 2u * EXL3_PREFILL_BLOCK_BYTES;
+	const uint32_t lane = threadIdx.x % EXL3_WARP, warp = threadIdx.x / EXL3_WARP;
+
+	if (threadIdx.x == 0) {
+		for (uint32_t stage = 0; stage < STAGES; stage++) {
+			barrier_init(&shared->full[stage], 1);
+			barrier_init(&shared->decoded[stage], PREFILL_DECODE_WARPS);
+			barrier_init(&shared->consumed[stage], 1);
+		}
+		barrier_init(&shared->done, 1);
+		shared->failed = 0;
+		shared->armed = 0;
+		shared->issued = 0;
+		asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+	}
+	if (warp == 1) {
+		asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+				     smem_address(&shared->tensor_memory)),
+			     "r"(MATRICES * PREFILL_COLUMNS)
+			     : "memory");
+		asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+	}
+	tensor_fence_before();
+	__syncthreads();
+	tensor_fence_after();
+	const uint32_t accumulators = shared->tensor_memory;
+
+	if (warp == 0) {
+		/* copies: one thread */
+		if (lane == 0) {
+			const uint64_t matrix_row_bytes = (uint64_t)(outputs / EXL3_TILE) * ring::tile_bytes;
+			uint32_t block = 0;
+			for (; block < blocks; block++) {
+				const uint32_t stage = block % STAGES, use = block / STAGES;
+				if (use > 0 && !barrier_wait(&shared->consumed[stage], (use - 1u) & 1u)) {
+					shared->failed = 1;
+					break;
+				}
+				unsigned char *const at = dynamic_shared + stage * stage_bytes;
+				barrier_expect(&shared->full[stage],
+					       MATRICES * (EXL3_PREFILL_BLOCK_BYTES + EXL3_STAGE_STEPS * row_bytes));
+#pragma unroll
+				for (uint32_t m = 0; m < MATRICES; m++) {
+					bulk_load(at + m * EXL3_PREFILL_STAGE_BYTES,
+						  operand_blocks[m] + (uint64_t)block * EXL3_PREFILL_BLOCK_BYTES,
+						  EXL3_PREFILL_BLOCK_BYTES, &shared->full[stage]);
+#pragma unroll
+					for (uint32_t step = 0; step < EXL3_STAGE_STEPS; step++)
+						bulk_load(at + m * EXL3_PREFILL_STAGE_BYTES + trellis_at + step * row_bytes,
+							  matrices[m] +
+								  (uint64_t)(block * EXL3_STAGE_STEPS + step) * matrix_row_bytes +
+								  (uint64_t)group * row_bytes,
+							  row_bytes, &shared->full[stage]);
+				}
+			}
+			shared->armed = block;
+		}
+		return false;
+	}
+	if (warp == 1) {
+		/* products: one thread */
+		if (lane == 0) {
+			bool good = true;
+			for (uint32_t block = 0; block < blocks && good; block++) {
+				const uint32_t stage = block % STAGES, use = block / STAGES;
+				good = barrier_wait(&shared->full[stage], use & 1u) &&
+				       barrier_wait(&shared->decoded[stage], use & 1u);
+				if (!good)
+					break;
+				tensor_fence_after();
+				const uint32_t at = smem_address(dynamic_shared + stage * stage_bytes);
+#pragma unroll
+				for (uint32_t m = 0; m < MATRICES; m++)
+#pragma unroll
+					for (uint32_t step = 0; step < EXL3_STAGE_STEPS; step++) {
+						const uint64_t a = prefill_descriptor(at + m * EXL3_PREFILL_STAGE_BYTES +
+										      step * 2u * 2048u);
+						const uint64_t b =
+							prefill_descriptor(at + m * EXL3_PREFILL_STAGE_BYTES +
+									   EXL3_PREFILL_BLOCK_BYTES + step * 2u * 2048u);
+						const uint32_t accumulate = block > 0 || step > 0 ? 1u : 0u;
+						asm volatile("{\n\t.reg .pred p;\n\t"
+							     "setp.ne.b32 p, %4, 0;\n\t"
+							     "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(
+								     accumulators + m * PREFILL_COLUMNS),
+							     "l"(a), "l"(b), "r"(PREFILL_INSTRUCTION), "r"(accumulate)
+							     : "memory");
+					}
+				tensor_commit(&shared->consumed[stage]);
+				shared->issued = 1;
+			}
+			if (!good) {
+				shared->failed = 1;
+				__threadfence_block();
+			}
+			if (shared->issued != 0) /* the decode warps and the release wait on this */
+				tensor_commit(&shared->done);
+		}
+		return false;
+	}
+
+	/* decode: warp w takes K step w % 4 of the stage and the output tiles 4 (w / 4) .. + 3, of every matrix */
+	{
+		const uint32_t decoder = warp - 2u, step = decoder % EXL3_STAGE_STEPS;
+		const uint32_t first_tile = decoder / EXL3_STAGE_STEPS * 4u;
+		const uint32_t begin = ring::begin(lane);
+		const uint32_t word_index = begin / 32u, shift = begin % 32u, next_index = (word_index + 1u) % ring::words;
+		bool good = true;
+		for (uint32_t block = 0; block < blocks && good; block++) {
+			const uint32_t stage = block % STAGES, use = block / STAGES;
+			if (use > 0)
+				good = barrier_wait(&shared->consumed[stage], (use - 1u) & 1u);
+			good = good && barrier_wait(&shared->full[stage], use & 1u);
+			if (!good)
+				break;
+			unsigned char *const at = dynamic_shared + stage * stage_bytes;
+#pragma unroll
+			for (uint32_t m = 0; m < MATRICES; m++) {
+				const uint32_t *const words = reinterpret_cast<const uint32_t *>(
+					at + m * EXL3_PREFILL_STAGE_BYTES + trellis_at + step * row_bytes);
+				unsigned char *const b_block = at + m * EXL3_PREFILL_STAGE_BYTES + EXL3_PREFILL_BLOCK_BYTES;
+#pragma unroll
+				for (uint32_t mine = 0; mine < 4; mine++) {
+					const uint32_t tile = first_tile + mine;
+					uint32_t fragment[4];
+					exl3_decode_fragment<BX2>(words[tile * ring::words + word_index],
+								  words[tile * ring::words + next_index], shift, fragment);
+					/* fragment f: outputs 16 tile + g + 8 (f % 2), inputs 16 step + 2 t + 8 (f / 2), lane 4 g + t:
+					 * the warp's 32 words are the 128 bytes of one K piece of one group of eight outputs */
+					uint32_t *const to = reinterpret_cast<uint32_t *>(b_block + step * 2u * 2048u +
+											  tile * 2u * 128u + lane * 4u);
+					to[0] = fragment[0];
+					to[128u / 4u] = fragment[1];
+					to[2048u / 4u] = fragment[2];
+					to[(2048u + 128u) / 4u] = fragment[3];
+				}
+			}
+			asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+			__syncwarp();
+			if (lane == 0)
+				barrier_arrive(&shared->decoded[stage]);
+		}
+		if (good)
+			good = barrier_wait(&shared->done, 0u);
+		if (!good)
+			shared->failed = 1;
+		tensor_fence_after();
+		decode_sync(); /* every decode warp has its verdict in */
+		return shared->failed == 0;
+	}
+}
+
+/* The accumulator tile of matrix m into shared memory, FP32 [128 rows][EXL3_PREFILL_STAGING_ROW]. A warp reads the 32
+ * tensor-memory lanes of its quarter (warp % 4) and one half of the columns. Decode warps only; ends with their
+ * barrier. */
+__device__ __forceinline__ void prefill_stage_out(uint32_t accumulators, uint32_t matrices, float *staging)
+{
+	const uint32_t lane = threadIdx.x % EXL3_WARP, warp = threadIdx.x / EXL3_WARP;
+	const uint32_t quarter = warp % 4u, half = (warp - 2u) / 4u;
+	__syncwarp();
+	for (uint32_t m = 0; m < matrices; m++)
+#pragma unroll
+		for (uint32_t piece = 0; piece < 2; piece++) {
+			const uint32_t column = half * 64u + piece * 32u;
+			uint32_t r[32];
+			asm volatile(
+				"tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+				"{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,"
+				"%26,%27,%28,%29,%30,%31}, [%32];"
+				: "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+				  "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+				  "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
+				  "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
+				  "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+				: "r"(accumulators + ((quarter * 32u) << 16) + m * PREFILL_COLUMNS + column)
+				: "memory");
+			asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+			uint4 *const to = reinterpret_cast<uint4 *>(
+				staging + ((uint64_t)m * EXL3_PREFILL_TILE_ROWS + quarter * 32u + lane) * EXL3_PREFILL_STAGING_ROW +
+				column);
+#pragma unroll
+			for (uint32_t index = 0; index < 8; index++)
+				to[index] = make_uint4(r[4 * index], r[4 * index + 1], r[4 * index + 2], r[4 * index + 3]);
+		}
+	tensor_fence_before();
+	decode_sync();
+}
+
+/* All threads, at the end of a product CTA: wait (bounded) for what a failed CTA still has in flight, then free the
+ * tensor memory. */
+template <uint32_t MATRICES, uint32_t STAGES> __device__ __forceinline__ void prefill_release(prefill_shared *shared)
+{
+	tensor_fence_before();
+	__syncthreads();
+	if (shared->failed != 0 && threadIdx.x == 0) {
+		const uint32_t armed = shared->armed;
+		for (uint32_t back = 0; back < STAGES && back < armed; back++) {
+			const uint32_t block = armed - 1u - back;
+			(void)barrier_wait(&shared->full[block % STAGES], (block / STAGES) & 1u);
+		}
+		if (shared->issued != 0)
+			(void)barrier_wait(&shared->done, 0u);
+	}
+	__syncthreads();
+	if (threadIdx.x / EXL3_WARP == 1u) {
+		tensor_fence_after();
+		__syncwarp();
+		asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(shared->tensor_memory),
+			     "r"(MATRICES * PREFILL_COLUMNS)
+			     : "memory");
+	}
+}
+
+struct prefill_tile_view {
+	struct exl3_prefill_tile tile;
+	const struct exl3_prefill_entry *entries; /* of the tile's rows */
+	uint64_t gate, up, down; /* matrix offsets */
+};
+
+__device__ __forceinline__ prefill_tile_view prefill_tile_of(const struct exl3_prefill_record &record,
+							     const unsigned char *arena, const prefill_view &view,
+							     uint32_t tile_index)
+{
+	prefill_tile_view out;
+	out.tile = reinterpret_cast<const struct exl3_prefill_tile *>(view.workspace + view.parts.tiles)[tile_index];
+	out.entries = reinterpret_cast<const struct exl3_prefill_entry *>(view.workspace + view.parts.entries) +
+		      (uint64_t)out.tile.expert * record.row_capacity + out.tile.first_entry;
+	const uint64_t *const table = reinterpret_cast<const uint64_t *>(arena + record.expert_table_offset);
+	out.gate = table[3u * out.tile.expert];
+	out.up = table[3u * out.tile.expert + 1u];
+	out.down = table[3u * out.tile.expert + 2u];
+	return out;
+}
+
+template <uint32_t BX2>
+__device__ __forceinline__ void prefill_gate_up(const struct exl3_prefill_record &record, unsigned char *arena,
+						const prefill_view &view, const prefill_tile_view &tile,
+						unsigned char *dynamic_shared, prefill_shared *shared)
+{
+	const uint32_t H = record.input_size, I = record.inner_size, group = blockIdx.x, tile_index = blockIdx.y;
+	const uint32_t lane = threadIdx.x % EXL3_WARP, warp = threadIdx.x / EXL3_WARP;
+	const unsigned char *const matrices[2] = { arena + tile.gate, arena + tile.up };
+	const uint64_t tile_bytes = (uint64_t)(H / EXL3_PREFILL_BLOCK_INPUTS) * EXL3_PREFILL_BLOCK_BYTES;
+	const unsigned char *const operands[2] = {
+		view.workspace + view.parts.gate_up_operands + tile_index * tile_bytes,
+		view.workspace + view.parts.gate_up_operands + ((uint64_t)view.parts.tile_capacity + tile_index) * tile_bytes
+	};
+	const bool complete = prefill_products<BX2, 2, EXL3_PREFILL_GATE_UP_STAGES>(
+		matrices, I, group, operands, H / EXL3_PREFILL_BLOCK_INPUTS, dynamic_shared, shared);
+	if (warp >= 2u && complete) {
+		float *const staging = reinterpret_cast<float *>(dynamic_shared);
+		prefill_stage_out(shared->tensor_memory, 2, staging);
+		const uint32_t channel = group * EXL3_TRANSFORM + lane * 4u;
+		const uint64_t codes = exl3_code_bytes(H, I, BX2);
+		float gate_scale[4], up_scale[4], down_scale[4];
+		load_half4(reinterpret_cast<const __half *>(arena + tile.gate + codes) + H + channel, gate_scale);
+		load_half4(reinterpret_cast<const __half *>(arena + tile.up + codes) + H + channel, up_scale);
+		load_half4(reinterpret_cast<const __half *>(arena + tile.down + exl3_code_bytes(I, H, BX2)) + channel,
+			   down_scale);
+		unsigned char *const blocks =
+			view.workspace + view.parts.down_operands +
+			((uint64_t)tile_index * (I / EXL3_PREFILL_BLOCK_INPUTS) + channel / EXL3_PREFILL_BLOCK_INPUTS) *
+				EXL3_PREFILL_BLOCK_BYTES;
+		for (uint32_t row = warp - 2u; row < tile.tile.row_count; row += PREFILL_DECODE_WARPS) {
+			const float4 gate_raw =
+				*reinterpret_cast<const float4 *>(staging + row * EXL3_PREFILL_STAGING_ROW + lane * 4u);
+			const float4 up_raw = *reinterpret_cast<const float4 *>(
+				staging + (EXL3_PREFILL_TILE_ROWS + row) * EXL3_PREFILL_STAGING_ROW + lane * 4u);
+			float gate[4] = { gate_raw.x, gate_raw.y, gate_raw.z, gate_raw.w };
+			float up[4] = { up_raw.x, up_raw.y, up_raw.z, up_raw.w };
+			hadamard128_warp(gate, lane);
+			hadamard128_warp(up, lane);
+			float hidden[4], fed[4];
+			exl3_swiglu4(gate, up, gate_scale, up_scale, record.activation_limit, hidden);
+#pragma unroll
+			for (uint32_t i = 0; i < 4; i++)
+				fed[i] = __fmul_rn(hidden[i], down_scale[i]);
+			hadamard128_warp(fed, lane);
+#pragma unroll
+			for (uint32_t i = 0; i < 4; i++)
+				fed[i] = __fmul_rn(fed[i], EXL3_NORMALIZATION);
+			store_half4(reinterpret_cast<__half *>(blocks +
+							       prefill_block_byte(row, channel % EXL3_PREFILL_BLOCK_INPUTS)),
+				    fed);
+		}
+	}
+	prefill_release<2, EXL3_PREFILL_GATE_UP_STAGES>(shared);
+}
+
+template <uint32_t BX2>
+__device__ __forceinline__ void prefill_down(const struct exl3_prefill_record &record, unsigned char *arena,
+					     const prefill_view &view, const prefill_tile_view &tile,
+					     unsigned char *dynamic_shared, prefill_shared *shared)
+{
+	const uint32_t H = record.input_size, I = record.inner_size, group = blockIdx.x, tile_index = blockIdx.y;
+	const uint32_t lane = threadIdx.x % EXL3_WARP, warp = threadIdx.x / EXL3_WARP;
+	const unsigned char *const matrices[1] = { arena + tile.down };
+	const unsigned char *const operands[1] = { view.workspace + view.parts.down_operands +
+						   (uint64_t)tile_index * (I / EXL3_PREFILL_BLOCK_INPUTS) *
+							   EXL3_PREFILL_BLOCK_BYTES };
+	const bool complete = prefill_products<BX2, 1, EXL3_PREFILL_DOWN_STAGES>(
+		matrices, H, group, operands, I / EXL3_PREFILL_BLOCK_INPUTS, dynamic_shared, shared);
+	if (warp >= 2u && complete) {
+		float *const staging = reinterpret_cast<float *>(dynamic_shared);
+		prefill_stage_out(shared->tensor_memory, 1, staging);
+		const uint32_t channel = group * EXL3_TRANSFORM + lane * 4u;
+		float scale[4];
+		load_half4(reinterpret_cast<const __half *>(arena + tile.down + exl3_code_bytes(I, H, BX2)) + I + channel,
+			   scale);
+		float *const outputs = reinterpret_cast<float *>(arena + record.pair_output_offset);
+		for (uint32_t row = warp - 2u; row < tile.tile.row_count; row += PREFILL_DECODE_WARPS) {
+			const struct exl3_prefill_entry entry = tile.entries[row];
+			const float4 raw =
+				*reinterpret_cast<const float4 *>(staging + row * EXL3_PREFILL_STAGING_ROW + lane * 4u);
+			float v[4] = { raw.x, raw.y, raw.z, raw.w };
+			hadamard128_warp(v, lane);
+#pragma unroll
+			for (uint32_t i = 0; i < 4; i++)
+				v[i] = __fmul_rn(__fmul_rn(__fmul_rn(v[i], EXL3_NORMALIZATION), scale[i]), entry.route_weight);
+			*reinterpret_cast<float4 *>(outputs + (uint64_t)entry.pair * H + channel) =
+				make_float4(v[0], v[1], v[2], v[3]);
+		}
+	}
+	prefill_release<1, EXL3_PREFILL_DOWN_STAGES>(shared);
+}
+
+#define PREFILL_WIDTH_SWITCH(function)                                                     \
+	switch (exl3_bits_x2(reinterpret_cast<const uint32_t *>(arena + record.widths_offset)[tile.tile.expert])) { \
+	case EXL3_BITS_X2_K2:                                                              \
+		function<EXL3_BITS_X2_K2>(record, arena, view, tile, dynamic_shared, &shared);   \
+		break;                                                                     \
+	case EXL3_BITS_X2_K2_5:                                                            \
+		function<EXL3_BITS_X2_K2_5>(record, arena, view, tile, dynamic_shared, &shared); \
+		break;                                                                     \
+	case EXL3_BITS_X2_K3:                                                              \
+		function<EXL3_BITS_X2_K3>(record, arena, view, tile, dynamic_shared, &shared);   \
+		break;                                                                     \
+	case EXL3_BITS_X2_K4:                                                              \
+		function<EXL3_BITS_X2_K4>(record, arena, view, tile, dynamic_shared, &shared);   \
+		break;                                                                     \
+	default:                                                                           \
+		break;                                                                     \
+	}
+
+/* grid (I / 128, tile capacity) x 320 */
+extern "C" __global__ void __launch_bounds__(EXL3_PREFILL_GEMM_THREADS, 1)
+	exl3_prefill_gate_up(struct exl3_prefill_record record, unsigned char *arena)
+{
+	extern __shared__ __align__(1024) unsigned char dynamic_shared[];
+	__shared__ prefill_shared shared;
+	const prefill_view view = prefill_view_of(record, arena);
+	/* once a wait has run out (the flag is never cleared while the kernel file stays loaded), later CTAs do not
+	 * queue up behind the same fault: the host reads the flag and rejects the result */
+	if (*reinterpret_cast<volatile unsigned int *>(&exl3_wait_expired) != 0u ||
+	    blockIdx.y >= reinterpret_cast<const uint32_t *>(view.workspace + view.parts.counts)[view.experts])
+		return;
+	const prefill_tile_view tile = prefill_tile_of(record, arena, view, blockIdx.y);
+	PREFILL_WIDTH_SWITCH(prefill_gate_up)
+}
+
+/* grid (H / 128, tile capacity) x 320 */
+extern "C" __global__ void __launch_bounds__(EXL3_PREFILL_GEMM_THREADS, 1)
+	exl3_prefill_down(struct exl3_prefill_record record, unsigned char *arena)
+{
+	extern __shared__ __align__(1024) unsigned char dynamic_shared[];
+	__shared__ prefill_shared shared;
+	const prefill_view view = prefill_view_of(record, arena);
+	/* once a wait has run out (the flag is never cleared while the kernel file stays loaded), later CTAs do not
+	 * queue up behind the same fault: the host reads the flag and rejects the result */
+	if (*reinterpret_cast<volatile unsigned int *>(&exl3_wait_expired) != 0u ||
+	    blockIdx.y >= reinterpret_cast<const uint32_t *>(view.workspace + view.parts.counts)[view.experts])
+		return;
+	const prefill_tile_view tile = prefill_tile_of(record, arena, view, blockIdx.y);
+	PREFILL_WIDTH_SWITCH(prefill_down)
+}
+
+/* grid (ceil(H / 128), row capacity) x 128: FP32 row sums from +0 in ascending slot order */
+extern "C" __global__ void __launch_bounds__(EXL3_ROW_SUM_THREADS)
+	exl3_prefill_row_sum(struct exl3_prefill_record record, unsigned char *arena)
+{
+	const struct step_block step = *reinterpret_cast<const struct step_block *>(arena + record.step_offset);
+	const uint32_t channel = blockIdx.x * blockDim.x + threadIdx.x;
+	const uint64_t row = blockIdx.y;
+	if (channel >= record.input_size || row >= min(step.row_count, record.row_capacity))
+		return;
+	const uint32_t width = record.input_size, slots = record.picks + record.shared_count;
+	const float *const pairs = reinterpret_cast<const float *>(arena + record.pair_output_offset);
+	float sum = 0.0f;
+	for (uint32_t slot = 0; slot < slots; slot++)
+		sum = __fadd_rn(sum, pairs[(row * slots + slot) * width + channel]);
+	reinterpret_cast<float *>(arena + record.row_output_offset)[row * width + channel] = sum;
+}

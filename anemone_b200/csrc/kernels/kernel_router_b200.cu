@@ -10,26 +10,7 @@
  * model's constants; the picks are the largest SCORES (the affinity is monotone in the score), so that the chosen
  * experts do not depend on the last bit of expf; always-on shared experts get jobs behind the routed ones.
  */
-#include <stdint.h>
-
-#include "anemone_b200_records.h"
-
-#define WARP 32u
-#define EXPERTS_PER_LANE (ROUTER_B200_MAXIMUM_EXPERTS / WARP)
-
-__device__ __forceinline__ uint64_t router_key(float score, uint32_t expert)
-{
-	const uint32_t bits = __float_as_uint(score);
-	const uint32_t ordered = score != score ? 0xFFFFFFFFu : (bits & 0x80000000u) != 0 ? ~bits : bits | 0x80000000u;
-	return (uint64_t)ordered << 32 | (uint64_t)(uint32_t)~expert;
-}
-
-__device__ __forceinline__ float router_affinity(float score, uint32_t scoring)
-{
-	if (scoring == ROUTER_SCORING_SQRT_SOFTPLUS)
-		return __fsqrt_rn(score > 20.0f ? score : log1pf(expf(score)));
-	return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-score)));
-}
+#include "router_device.cuh"
 
 extern "C" __global__ void __launch_bounds__(ROUTER_B200_THREADS)
 	router_select_b200(struct router_select_b200_arguments arguments, unsigned char *arena)
@@ -52,54 +33,12 @@ extern "C" __global__ void __launch_bounds__(ROUTER_B200_THREADS)
 	for (uint32_t expert = threadIdx.x; expert < ROUTER_B200_MAXIMUM_EXPERTS; expert += blockDim.x)
 		row_mask[expert] = 0ull;
 
-	/* one warp a row: `picks` rounds of a warp-wide maximum over 64-bit keys */
-	for (uint32_t row = warp; row < live; row += blockDim.x / WARP) {
-		uint64_t keys[EXPERTS_PER_LANE];
-#pragma unroll
-		for (uint32_t place = 0; place < EXPERTS_PER_LANE; place++) {
-			const uint32_t expert = place * WARP + lane;
-			keys[place] = expert < experts ? router_key(scores[(uint64_t)row * experts + expert], expert) : 0ull;
-		}
-		uint32_t mine = 0; /* lane p keeps pick p */
-		for (uint32_t pick = 0; pick < picks; pick++) {
-			uint64_t best = 0;
-#pragma unroll
-			for (uint32_t place = 0; place < EXPERTS_PER_LANE; place++)
-				best = keys[place] > best ? keys[place] : best;
-			for (uint32_t distance = WARP / 2u; distance != 0; distance >>= 1) {
-				const uint64_t other = __shfl_xor_sync(0xFFFFFFFFu, best, distance);
-				best = other > best ? other : best;
-			}
-#pragma unroll
-			for (uint32_t place = 0; place < EXPERTS_PER_LANE; place++)
-				keys[place] = keys[place] == best ? 0ull : keys[place];
-			if (lane == pick)
-				mine = ~(uint32_t)best;
-		}
-		/* slot = the number of picked experts below mine */
-		uint32_t slot = 0;
-		for (uint32_t pick = 0; pick < picks; pick++) {
-			const uint32_t other = __shfl_sync(0xFFFFFFFFu, mine, pick);
-			slot += lane < picks && other < mine ? 1u : 0u;
-		}
-		if (lane < picks) {
-			chosen[row][slot] = mine;
-			weight[row][slot] = router_affinity(scores[(uint64_t)row * experts + mine], arguments.scoring);
-		}
-		__syncwarp();
-		float sum = 0.0f;
-		for (uint32_t place = 0; place < picks; place++)
-			sum = __fadd_rn(sum, weight[row][place]);
-		__syncwarp();
-		if (lane < picks) {
-			const float value =
-				__fmul_rn(__fdiv_rn(weight[row][lane], __fadd_rn(sum, 1e-20f)), arguments.route_scale);
-			weight[row][lane] = value;
-			reinterpret_cast<uint32_t *>(arena + arguments.picks_offset)[(uint64_t)row * picks + lane] =
-				chosen[row][lane];
-			reinterpret_cast<float *>(arena + arguments.weights_offset)[(uint64_t)row * picks + lane] = value;
-		}
-	}
+	/* one warp a row */
+	for (uint32_t row = warp; row < live; row += blockDim.x / WARP)
+		router_row(scores + (uint64_t)row * experts, experts, picks, arguments.scoring, arguments.route_scale, lane,
+			   chosen[row], weight[row],
+			   reinterpret_cast<uint32_t *>(arena + arguments.picks_offset) + (uint64_t)row * picks,
+			   reinterpret_cast<float *>(arena + arguments.weights_offset) + (uint64_t)row * picks);
 	__syncthreads();
 
 	/* which rows chose each expert: a 64-bit mask per expert (an OR is the same in any order), then the first job of

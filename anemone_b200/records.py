@@ -54,6 +54,31 @@ class Exl3MoeSizes(C.Structure):
                 ("gate_up_splits", C.c_uint32), ("down_splits", C.c_uint32)]
 
 
+class Exl3Prefill(C.Structure):
+    _fields_ = [("scores_offset", C.c_uint64), ("input_offset", C.c_uint64), ("expert_table_offset", C.c_uint64),
+                ("widths_offset", C.c_uint64), ("picks_offset", C.c_uint64), ("weights_offset", C.c_uint64),
+                ("workspace_offset", C.c_uint64), ("pair_output_offset", C.c_uint64),
+                ("row_output_offset", C.c_uint64), ("step_offset", C.c_uint64), ("input_size", C.c_uint32),
+                ("inner_size", C.c_uint32), ("expert_count", C.c_uint32), ("shared_count", C.c_uint32),
+                ("picks", C.c_uint32), ("row_capacity", C.c_uint32), ("scoring", C.c_uint32),
+                ("route_scale", C.c_float), ("activation_limit", C.c_float), ("reserved_zero", C.c_uint32)]
+
+
+class Exl3PrefillTile(C.Structure):
+    _fields_ = [("expert", C.c_uint32), ("first_entry", C.c_uint32), ("row_count", C.c_uint32),
+                ("reserved_zero", C.c_uint32)]
+
+
+class Exl3PrefillEntry(C.Structure):
+    _fields_ = [("pair", C.c_uint32), ("route_weight", C.c_float)]
+
+
+class Exl3PrefillParts(C.Structure):
+    _fields_ = [("counts", C.c_uint64), ("tiles", C.c_uint64), ("entries", C.c_uint64),
+                ("gate_up_operands", C.c_uint64), ("down_operands", C.c_uint64), ("total", C.c_uint64),
+                ("tile_capacity", C.c_uint32), ("reserved_zero", C.c_uint32)]
+
+
 class StepBlock(C.Structure):
     _fields_ = [("sequence", C.c_uint64), ("row_count", C.c_uint32), ("flags", C.c_uint32)]
 
@@ -170,7 +195,7 @@ class OrderedCollectiveKernels(C.Structure):
 
 
 for _record, _bytes in ((Exl3Reconstruct, 32), (Exl3Expert, 80), (ExpertJob, 96), (ExpertRowSum, 24),
-                        (Exl3ShardActivation, 96), (Exl3Moe, 112), (StepBlock, 16), (OrderedPeer, 32),
+                        (Exl3ShardActivation, 96), (Exl3Moe, 112), (Exl3Prefill, 120), (Exl3PrefillTile, 16), (Exl3PrefillEntry, 8), (Exl3PrefillParts, 56), (StepBlock, 16), (OrderedPeer, 32),
                         (OrderedCollective, 80), (OrderedReduceBf16, 96), (OrderedRowSumPublish, 96),
                         (RouterSelectB200, 80), (StepInputSelect, 40), (ActivationQuantize, 40), (ExpertGateUp, 64), (ExpertDown, 56),
                         (KernelLaunch, 232), (CardDescription, 168)):

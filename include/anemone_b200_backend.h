@@ -177,6 +177,10 @@ MUST_CHECK result_status backend_b200_ipc_connect(struct device_card *accessor,
 /* Queue a fill of arena bytes (zeroing signal lines and scratch at load), behind everything queued before. */
 MUST_CHECK result_status backend_b200_fill(struct device_card *card, uint64_t arena_byte_offset, unsigned char value,
 					   uint64_t byte_count);
+/* Waits for the card's queue, then reports whether any kernel of the EXL3 kernel files gave up a bounded wait on a
+ * shared-memory barrier since the files were loaded (such a CTA stores nothing and returns; nothing traps):
+ * *expired_out is 0 or 1. */
+MUST_CHECK result_status backend_b200_waits_expired(struct device_card *card, uint32_t *expired_out);
 /* Kernel launches this card has queued since it was opened, graph launches counted by their kernel nodes. */
 uint64_t backend_b200_launch_count(const struct device_card *card);
 /* The device address of the arena (diagnostics and interoperation with other libraries of the same process). */

@@ -74,6 +74,20 @@ MUST_CHECK result_status exl3_moe_prepare(const struct exl3_moe_record *record, 
 					  const struct backend_operations *backend, struct device_card *card,
 					  struct kernel_launch *launches_out);
 
+/* B200 extension (the reference's counterpart: its tensor-core prefill family, include/anemone/exl3_tc.h:42-45): the seven
+ * launches of kernel file "kernel_exl3_prefill" for struct exl3_prefill_record: router, grouping of rows per expert in
+ * tiles of 128, operands, the grouped tensor-core products with their epilogues, row sums. launches_out has
+ * EXL3_PREFILL_LAUNCHES entries. The workspace (exl3_prefill_parts_of(...).total bytes) begins on a multiple of 1024
+ * bytes and needs no initial contents. */
+MUST_CHECK result_status exl3_prefill_prepare(const struct exl3_prefill_record *record, uint64_t arena_byte_count,
+					      const struct backend_operations *backend, struct device_card *card,
+					      struct kernel_launch *launches_out);
+
+/* The workspace layout of exl3_prefill_prepare for these shapes: exl3_prefill_parts_of as an export, for callers that
+ * cannot use the inline function. */
+void exl3_prefill_sizes(uint32_t row_capacity, uint32_t picks, uint32_t shared_count, uint32_t expert_count,
+			uint32_t input_size, uint32_t inner_size, struct exl3_prefill_parts *parts_out);
+
 /* ---- load-time slices for tensor parallelism (include/anemone/exl3_layout.h) ---- */
 
 struct bb_exl3_matrix_slice {

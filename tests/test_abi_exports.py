@@ -47,6 +47,8 @@ def test_record_sizes_match_the_headers():
     mirror = {"exl3_reconstruct_record": R.Exl3Reconstruct, "exl3_expert_record": R.Exl3Expert,
               "expert_job_record": R.ExpertJob, "expert_row_sum_arguments": R.ExpertRowSum,
               "bb_exl3_shard_activation_record": R.Exl3ShardActivation, "exl3_moe_record": R.Exl3Moe,
+              "exl3_prefill_record": R.Exl3Prefill, "exl3_prefill_tile": R.Exl3PrefillTile,
+              "exl3_prefill_entry": R.Exl3PrefillEntry,
               "step_block": R.StepBlock, "ordered_collective_peer": R.OrderedPeer,
               "ordered_collective_arguments": R.OrderedCollective, "ordered_reduce_bf16_arguments": R.OrderedReduceBf16,
               "ordered_row_sum_publish_arguments": R.OrderedRowSumPublish,

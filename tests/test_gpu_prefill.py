@@ -1,0 +1,172 @@
+"""The prefill launches (router -> grouping in row tiles -> operands -> tensor-core products -> row sums) on a CUDA
+device against the CPU oracle, through the C-ABI preparer: picks bit-exact, FP32 row sums within the path's tolerance,
+grouping tables checked for their invariants, and the decode launches on the same rows for consistency."""
+import numpy as np
+import pytest
+
+from anemone_b200 import records as R
+from anemone_b200 import synthetic
+from anemone_b200.moe import MoeConfig, MoeLayer, MoeLayout
+from anemone_b200.prefill import PrefillLayer, PrefillLayout
+from oracle import moe_reference
+
+pytestmark = pytest.mark.gpu
+
+MAX_ABS, COSINE = 2e-2, 0.9999  # the path's stated tolerance for layer outputs
+
+
+@pytest.fixture(scope="module")
+def api():
+    from anemone_b200 import api as module
+    assert module.card_count() >= 1, "no CUDA device: the CUDA path cannot run and there is no fallback"
+    return module
+
+
+def make_inputs(seed, config, rows, width=None):
+    rng = np.random.default_rng(seed)
+    if width is None:
+        widths = np.concatenate([synthetic.expert_widths(rng, config.experts), [3] * config.shared])
+    else:
+        widths = np.full(config.total_experts, width)
+    widths = widths.astype(np.uint32)
+    matrices = [(synthetic.exl3_matrix(rng, config.hidden, config.inner, int(w)),
+                 synthetic.exl3_matrix(rng, config.hidden, config.inner, int(w)),
+                 synthetic.exl3_matrix(rng, config.inner, config.hidden, int(w))) for w in widths]
+    tokens = synthetic.tokens(rng, rows, config.hidden)
+    scores = rng.normal(0, 1, size=(rows, config.experts)).astype(np.float32)
+    return widths, matrices, tokens, scores
+
+
+def cosine(a, b):
+    a, b = a.astype(np.float64).reshape(-1), b.astype(np.float64).reshape(-1)
+    return float(a @ b / (np.linalg.norm(a) * np.linalg.norm(b) + 1e-300))
+
+
+def check_tables(card, layer, config, rows, experts):
+    """The grouping the products ran on: every pair once, rows ascending inside an expert, tiles cover the entries."""
+    L = layer.layout
+    total = config.total_experts
+    counts = card.download(L.workspace + L.parts.counts, (total + 1) * 4, np.uint32)
+    want = np.bincount(experts.reshape(-1), minlength=total).astype(np.uint32)
+    want[config.experts:] = rows
+    assert np.array_equal(counts[:total], want)
+    assert counts[total] == sum((int(c) + 127) // 128 for c in want)
+    tiles = card.download(L.workspace + L.parts.tiles, int(counts[total]) * 16, np.uint32).reshape(-1, 4)
+    seen = set()
+    at = 0
+    for expert in range(total):
+        entries = card.download(L.workspace + L.parts.entries + expert * config.row_capacity * 8,
+                                max(int(want[expert]), 1) * 8, np.uint32).reshape(-1, 2)[:want[expert]]
+        pairs = entries[:, 0].astype(np.int64)
+        assert np.all(np.diff(pairs // config.pairs_per_row) > 0)
+        for pair in pairs:
+            row, slot = divmod(int(pair), config.pairs_per_row)
+            assert (experts[row, slot] if slot < config.picks else config.experts + slot - config.picks) == expert
+            seen.add(int(pair))
+        for first in range(0, int(want[expert]), 128):
+            assert list(tiles[at]) == [expert, first, min(128, int(want[expert]) - first), 0]
+            at += 1
+    assert at == counts[total] and len(seen) == rows * config.pairs_per_row
+
+
+@pytest.mark.parametrize("rows,capacity", [(1, 1), (37, 64), (300, 300), (129, 512)])
+def test_prefill_rows_match_oracle(api, oracle, rows, capacity):
+    config = MoeConfig(hidden=512, inner=256, experts=32, shared=1, picks=4, row_capacity=capacity)
+    widths, matrices, tokens, scores = make_inputs(100 + rows, config, rows)
+    experts, weights = moe_reference.route(oracle, config, scores)
+    expected = moe_reference.rank_partial(oracle, config, widths, matrices, tokens, experts, weights, 1, 0)[0]
+    layout = PrefillLayout(config, widths)
+    card = api.Card(0, layout.arena_bytes)
+    try:
+        layer = PrefillLayer(card, config, widths, matrices)
+        for repeat in range(2):  # the workspace needs no clearing between calls
+            got = layer.step(tokens, scores)
+            picks = card.download(layer.layout.picks, rows * config.picks * 4, np.uint32).reshape(rows, config.picks)
+            assert np.array_equal(picks, experts)  # router indices: bit-exact
+            assert np.isfinite(got).all()
+            assert np.abs(got - expected).max() <= MAX_ABS and cosine(got, expected) >= COSINE
+        check_tables(card, layer, config, rows, experts)
+        # fewer live rows than before: stale entries and tiles of the longer call must not be used
+        fewer = max(1, rows // 3)
+        got = layer.step(tokens[:fewer], scores[:fewer])
+        assert np.abs(got - expected[:fewer]).max() <= MAX_ABS and cosine(got, expected[:fewer]) >= COSINE
+    finally:
+        card.close()
+
+
+@pytest.mark.parametrize("width", [2, 40, 3, 4])
+def test_prefill_every_width(api, oracle, width):
+    config = MoeConfig(hidden=256, inner=128, experts=4, shared=0, picks=2, row_capacity=140)
+    rows = 140
+    widths, matrices, tokens, scores = make_inputs(width, config, rows, width)
+    experts, weights = moe_reference.route(oracle, config, scores)
+    expected = moe_reference.rank_partial(oracle, config, widths, matrices, tokens, experts, weights, 1, 0)[0]
+    card = api.Card(0, PrefillLayout(config, widths).arena_bytes)
+    try:
+        got = PrefillLayer(card, config, widths, matrices).step(tokens, scores)
+        assert np.abs(got - expected).max() <= MAX_ABS and cosine(got, expected) >= COSINE
+    finally:
+        card.close()
+
+
+def test_prefill_agrees_with_decode_launches(api):
+    """The same 64 rows through the decode launches and through the prefill launches: same picks, and row sums that
+    differ only by the association of the FP32 products."""
+    config = MoeConfig(hidden=1024, inner=512, experts=16, shared=1, picks=2, row_capacity=64)
+    rows = 64
+    widths, matrices, tokens, scores = make_inputs(7, config, rows)
+    card = api.Card(0, MoeLayout(config, widths, 1, 0).arena_bytes)
+    try:
+        decode = MoeLayer(card, config, widths, matrices)
+        decode.connect_local([decode])
+        decode.step(tokens, scores)
+        slot = decode.layout.region + (decode.sequence & 1) * decode.layout.parity_stride + decode.layout.slot_input
+        decode_rows = card.download(slot, rows * config.hidden * 4, np.float32).reshape(rows, config.hidden)
+        decode_picks = card.download(decode.layout.picks, rows * config.picks * 4, np.uint32)
+    finally:
+        card.close()
+    card = api.Card(0, PrefillLayout(config, widths).arena_bytes)
+    try:
+        prefill = PrefillLayer(card, config, widths, matrices)
+        prefill_rows = prefill.step(tokens, scores)
+        prefill_picks = card.download(prefill.layout.picks, rows * config.picks * 4, np.uint32)
+    finally:
+        card.close()
+    assert np.array_equal(decode_picks, prefill_picks)
+    scale = np.abs(decode_rows).max()
+    assert np.abs(prefill_rows - decode_rows).max() <= 2e-3 * max(scale, 1.0)
+    assert cosine(prefill_rows, decode_rows) >= 0.99999
+
+
+def test_prefill_preparer_refusals(api):
+    config = MoeConfig(hidden=256, inner=128, experts=4, shared=0, picks=2, row_capacity=16)
+    widths = np.full(4, 3, dtype=np.uint32)
+    layout = PrefillLayout(config, widths)
+    card = api.Card(0, layout.arena_bytes)
+    try:
+        import ctypes as C
+        good = R.Exl3Prefill(layout.scores, layout.tokens, layout.expert_table, layout.widths, layout.picks,
+                             layout.weights, layout.workspace, layout.pair_outputs, layout.row_output, layout.step,
+                             256, 128, 4, 0, 2, 16, 0, 1.0, 10.0, 0)
+        launches = (R.KernelLaunch * 7)()
+        lib = api.library()
+
+        def status(**changes):
+            record = R.Exl3Prefill.from_buffer_copy(bytes(good))
+            for name, value in changes.items():
+                setattr(record, name, value)
+            before = bytes(launches)
+            code = lib.exl3_prefill_prepare(C.byref(record), card.arena_bytes, card.ops_pointer, card.handle, launches)
+            if code != 0:
+                assert bytes(launches) == before  # a refusal leaves the launch table unchanged
+            return code
+
+        assert status() == 0
+        assert launches[4].grid[0] == 1 and launches[4].block[0] == 320 and launches[5].grid[0] == 2
+        for changes in ({"input_size": 192}, {"inner_size": 64}, {"picks": 0}, {"picks": 5}, {"expert_count": 0},
+                        {"reserved_zero": 1}, {"workspace_offset": layout.workspace + 512},
+                        {"row_output_offset": layout.pair_outputs}, {"activation_limit": 0.0},
+                        {"row_capacity": 0}, {"scores_offset": card.arena_bytes}):
+            assert status(**changes) == 1, changes  # STATUS_INVALID_ARGUMENT
+    finally:
+        card.close()
