@@ -281,19 +281,23 @@ result_status exl3_prefill_prepare(const struct exl3_prefill_record *record, uin
 				   struct kernel_launch *launches_out)
 {
 	if (record == NULL || backend == NULL || card == NULL || launches_out == NULL ||
-	    backend->kernel_prepare == NULL || record->reserved_zero != 0)
+	    backend->kernel_prepare == NULL || record->reserved_zero[0] != 0 || record->reserved_zero[1] != 0)
 		return STATUS_INVALID_ARGUMENT;
-	const uint32_t H = record->input_size, I = record->inner_size;
-	const uint32_t experts = record->expert_count + record->shared_count;
+	const uint32_t H = record->input_size, I = record->inner_size, shared_I = record->shared_inner_size;
+	const uint32_t experts = record->local_count + record->shared_count;
 	if (record->expert_count == 0 || record->expert_count > ROUTER_B200_MAXIMUM_EXPERTS ||
-	    record->shared_count > ROUTER_B200_THREADS - ROUTER_B200_MAXIMUM_EXPERTS || record->picks == 0 ||
-	    record->picks > ROUTER_B200_MAXIMUM_PICKS || record->picks > record->expert_count ||
-	    record->row_capacity == 0 || record->row_capacity > EXL3_MAXIMUM_GRID_ROWS || H == 0 || I == 0 ||
-	    H % EXL3_TRANSFORM != 0 || I % EXL3_TRANSFORM != 0 || I > H || record->scoring > ROUTER_SCORING_SQRT_SOFTPLUS ||
-	    !isfinite(record->route_scale) || !isfinite(record->activation_limit) || record->activation_limit <= 0)
+	    record->local_first > record->expert_count || record->local_count > record->expert_count - record->local_first ||
+	    experts == 0 || record->shared_count > ROUTER_B200_THREADS - ROUTER_B200_MAXIMUM_EXPERTS ||
+	    record->picks == 0 || record->picks > ROUTER_B200_MAXIMUM_PICKS || record->picks > record->expert_count ||
+	    record->row_capacity == 0 || record->row_capacity > EXL3_MAXIMUM_GRID_ROWS || H == 0 ||
+	    H % EXL3_TRANSFORM != 0 || I % EXL3_TRANSFORM != 0 || shared_I % EXL3_TRANSFORM != 0 || I > H || shared_I > H ||
+	    (record->local_count != 0) != (I != 0) || (record->shared_count != 0) != (shared_I != 0) ||
+	    record->scoring > ROUTER_SCORING_SQRT_SOFTPLUS || !isfinite(record->route_scale) ||
+	    !isfinite(record->activation_limit) || record->activation_limit <= 0)
 		return STATUS_INVALID_ARGUMENT;
+	const uint32_t widest = I > shared_I ? I : shared_I;
 	const struct exl3_prefill_parts parts = exl3_prefill_parts_of(record->row_capacity, record->picks,
-								      record->shared_count, record->expert_count, H, I);
+								      record->shared_count, record->local_count, H, widest);
 	if (parts.tile_capacity > EXL3_MAXIMUM_GRID_ROWS)
 		return STATUS_INVALID_ARGUMENT;
 	const uint64_t rows = record->row_capacity, slots = record->picks + record->shared_count;
@@ -324,7 +328,7 @@ result_status exl3_prefill_prepare(const struct exl3_prefill_record *record, uin
 		{ experts, 1, 1, 256u, 0 },
 		{ 1, 1, 1, ROUTER_B200_THREADS, 0 },
 		{ parts.tile_capacity, transform_grid(H), EXL3_PROJECTIONS, EXL3_TRANSFORM_THREADS, 0 },
-		{ I / EXL3_TRANSFORM, parts.tile_capacity, 1, EXL3_PREFILL_GEMM_THREADS,
+		{ widest / EXL3_TRANSFORM, parts.tile_capacity, 1, EXL3_PREFILL_GEMM_THREADS,
 		  EXL3_PREFILL_GATE_UP_STAGES * EXL3_PROJECTIONS * EXL3_PREFILL_STAGE_BYTES },
 		{ H / EXL3_TRANSFORM, parts.tile_capacity, 1, EXL3_PREFILL_GEMM_THREADS,
 		  EXL3_PREFILL_DOWN_STAGES * EXL3_PREFILL_STAGE_BYTES },
@@ -346,9 +350,10 @@ result_status exl3_prefill_prepare(const struct exl3_prefill_record *record, uin
 	return STATUS_OK;
 }
 
-void exl3_prefill_sizes(uint32_t row_capacity, uint32_t picks, uint32_t shared_count, uint32_t expert_count,
-			uint32_t input_size, uint32_t inner_size, struct exl3_prefill_parts *parts_out)
+void exl3_prefill_sizes(uint32_t row_capacity, uint32_t picks, uint32_t shared_count, uint32_t local_count,
+			uint32_t input_size, uint32_t widest_inner_size, struct exl3_prefill_parts *parts_out)
 {
 	if (parts_out != NULL)
-		*parts_out = exl3_prefill_parts_of(row_capacity, picks, shared_count, expert_count, input_size, inner_size);
+		*parts_out = exl3_prefill_parts_of(row_capacity, picks, shared_count, local_count, input_size,
+						   widest_inner_size);
 }

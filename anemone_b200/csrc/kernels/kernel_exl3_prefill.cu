@@ -38,18 +38,20 @@ struct prefill_shared {
 struct prefill_view {
 	const struct exl3_prefill_parts parts;
 	unsigned char *workspace;
-	uint32_t experts; /* routed + shared */
+	uint32_t experts; /* held here: routed + always-on */
 	uint32_t pairs_per_row;
 	uint32_t live;
+	uint32_t widest; /* the larger intermediate width */
 };
 
 __device__ __forceinline__ prefill_view prefill_view_of(const struct exl3_prefill_record &record, unsigned char *arena)
 {
 	const struct step_block step = *reinterpret_cast<const struct step_block *>(arena + record.step_offset);
+	const uint32_t widest = max(record.inner_size, record.shared_inner_size);
 	prefill_view view = { exl3_prefill_parts_of(record.row_capacity, record.picks, record.shared_count,
-						    record.expert_count, record.input_size, record.inner_size),
-			      arena + record.workspace_offset, record.expert_count + record.shared_count,
-			      record.picks + record.shared_count, min(step.row_count, record.row_capacity) };
+						    record.local_count, record.input_size, widest),
+			      arena + record.workspace_offset, record.local_count + record.shared_count,
+			      record.picks + record.shared_count, min(step.row_count, record.row_capacity), widest };
 	return view;
 }
 
@@ -91,12 +93,12 @@ extern "C" __global__ void __launch_bounds__(PREFILL_GROUP_THREADS)
 		uint32_t slot = 0;
 		float route_weight = 1.0f;
 		if (row < view.live) {
-			if (expert >= record.expert_count) {
+			if (expert >= record.local_count) {
 				found = true;
-				slot = record.picks + (expert - record.expert_count);
+				slot = record.picks + (expert - record.local_count);
 			} else {
 				for (uint32_t place = 0; place < record.picks; place++)
-					if (picked[(uint64_t)row * record.picks + place] == expert) {
+					if (picked[(uint64_t)row * record.picks + place] == record.local_first + expert) {
 						found = true;
 						slot = place;
 						route_weight = weights[(uint64_t)row * record.picks + place];
@@ -165,6 +167,12 @@ extern "C" __global__ void __launch_bounds__(ROUTER_B200_THREADS)
 		counts[view.experts] = min(total, view.parts.tile_capacity);
 }
 
+/* the intermediate width of a local expert's matrices */
+__device__ __forceinline__ uint32_t prefill_inner_of(const struct exl3_prefill_record &record, uint32_t expert)
+{
+	return expert < record.local_count ? record.inner_size : record.shared_inner_size;
+}
+
 /* byte of (row, input) inside an operand block of 128 rows x 64 inputs: 16-byte pieces of eight inputs, the pieces of
  * eight rows adjacent, the 16 row groups adjacent, then the next eight inputs */
 __device__ __forceinline__ uint32_t prefill_block_byte(uint32_t row, uint32_t input)
@@ -192,7 +200,9 @@ extern "C" __global__ void __launch_bounds__(EXL3_TRANSFORM_THREADS)
 	const uint64_t matrix =
 		reinterpret_cast<const uint64_t *>(arena + record.expert_table_offset)[3u * tile.expert + blockIdx.z];
 	float scale[4];
-	load_half4(reinterpret_cast<const __half *>(arena + matrix + exl3_code_bytes(H, record.inner_size, bits_x2)) + channel,
+	load_half4(reinterpret_cast<const __half *>(arena + matrix +
+						    exl3_code_bytes(H, prefill_inner_of(record, tile.expert), bits_x2)) +
+			   channel,
 		   scale);
 	const struct exl3_prefill_entry *const entries =
 		reinterpret_cast<const struct exl3_prefill_entry *>(view.workspace + view.parts.entries) +
@@ -505,7 +515,8 @@ __device__ __forceinline__ void prefill_gate_up(const struct exl3_prefill_record
 						const prefill_view &view, const prefill_tile_view &tile,
 						unsigned char *dynamic_shared, prefill_shared *shared)
 {
-	const uint32_t H = record.input_size, I = record.inner_size, group = blockIdx.x, tile_index = blockIdx.y;
+	const uint32_t H = record.input_size, I = prefill_inner_of(record, tile.tile.expert);
+	const uint32_t group = blockIdx.x, tile_index = blockIdx.y;
 	const uint32_t lane = threadIdx.x % EXL3_WARP, warp = threadIdx.x / EXL3_WARP;
 	const unsigned char *const matrices[2] = { arena + tile.gate, arena + tile.up };
 	const uint64_t tile_bytes = (uint64_t)(H / EXL3_PREFILL_BLOCK_INPUTS) * EXL3_PREFILL_BLOCK_BYTES;
@@ -527,7 +538,8 @@ __device__ __forceinline__ void prefill_gate_up(const struct exl3_prefill_record
 			   down_scale);
 		unsigned char *const blocks =
 			view.workspace + view.parts.down_operands +
-			((uint64_t)tile_index * (I / EXL3_PREFILL_BLOCK_INPUTS) + channel / EXL3_PREFILL_BLOCK_INPUTS) *
+			((uint64_t)tile_index * (view.widest / EXL3_PREFILL_BLOCK_INPUTS) +
+			 channel / EXL3_PREFILL_BLOCK_INPUTS) *
 				EXL3_PREFILL_BLOCK_BYTES;
 		for (uint32_t row = warp - 2u; row < tile.tile.row_count; row += PREFILL_DECODE_WARPS) {
 			const float4 gate_raw =
@@ -560,11 +572,12 @@ __device__ __forceinline__ void prefill_down(const struct exl3_prefill_record &r
 					     const prefill_view &view, const prefill_tile_view &tile,
 					     unsigned char *dynamic_shared, prefill_shared *shared)
 {
-	const uint32_t H = record.input_size, I = record.inner_size, group = blockIdx.x, tile_index = blockIdx.y;
+	const uint32_t H = record.input_size, I = prefill_inner_of(record, tile.tile.expert);
+	const uint32_t group = blockIdx.x, tile_index = blockIdx.y;
 	const uint32_t lane = threadIdx.x % EXL3_WARP, warp = threadIdx.x / EXL3_WARP;
 	const unsigned char *const matrices[1] = { arena + tile.down };
 	const unsigned char *const operands[1] = { view.workspace + view.parts.down_operands +
-						   (uint64_t)tile_index * (I / EXL3_PREFILL_BLOCK_INPUTS) *
+						   (uint64_t)tile_index * (view.widest / EXL3_PREFILL_BLOCK_INPUTS) *
 							   EXL3_PREFILL_BLOCK_BYTES };
 	const bool complete = prefill_products<BX2, 1, EXL3_PREFILL_DOWN_STAGES>(
 		matrices, H, group, operands, I / EXL3_PREFILL_BLOCK_INPUTS, dynamic_shared, shared);
@@ -610,7 +623,7 @@ __device__ __forceinline__ void prefill_down(const struct exl3_prefill_record &r
 		break;                                                                     \
 	}
 
-/* grid (I / 128, tile capacity) x 320 */
+/* grid (widest I / 128, tile capacity) x 320 */
 extern "C" __global__ void __launch_bounds__(EXL3_PREFILL_GEMM_THREADS, 1)
 	exl3_prefill_gate_up(struct exl3_prefill_record record, unsigned char *arena)
 {
@@ -623,6 +636,8 @@ extern "C" __global__ void __launch_bounds__(EXL3_PREFILL_GEMM_THREADS, 1)
 	    blockIdx.y >= reinterpret_cast<const uint32_t *>(view.workspace + view.parts.counts)[view.experts])
 		return;
 	const prefill_tile_view tile = prefill_tile_of(record, arena, view, blockIdx.y);
+	if (blockIdx.x >= prefill_inner_of(record, tile.tile.expert) / EXL3_TRANSFORM)
+		return; /* the grid is as wide as the widest expert */
 	PREFILL_WIDTH_SWITCH(prefill_gate_up)
 }
 
@@ -642,7 +657,7 @@ extern "C" __global__ void __launch_bounds__(EXL3_PREFILL_GEMM_THREADS, 1)
 	PREFILL_WIDTH_SWITCH(prefill_down)
 }
 
-/* grid (ceil(H / 128), row capacity) x 128: FP32 row sums from +0 in ascending slot order */
+/* grid (ceil(H / 128), row capacity) x 128: FP32 row sums over the row's local pairs from +0 in ascending slot order */
 extern "C" __global__ void __launch_bounds__(EXL3_ROW_SUM_THREADS)
 	exl3_prefill_row_sum(struct exl3_prefill_record record, unsigned char *arena)
 {
@@ -653,8 +668,13 @@ extern "C" __global__ void __launch_bounds__(EXL3_ROW_SUM_THREADS)
 		return;
 	const uint32_t width = record.input_size, slots = record.picks + record.shared_count;
 	const float *const pairs = reinterpret_cast<const float *>(arena + record.pair_output_offset);
+	const uint32_t *const picked = reinterpret_cast<const uint32_t *>(arena + record.picks_offset) + row * record.picks;
 	float sum = 0.0f;
-	for (uint32_t slot = 0; slot < slots; slot++)
+	for (uint32_t slot = 0; slot < slots; slot++) {
+		/* a routed pair counts where its expert is held; an always-on pair everywhere it exists */
+		if (slot < record.picks && picked[slot] - record.local_first >= record.local_count)
+			continue;
 		sum = __fadd_rn(sum, pairs[(row * slots + slot) * width + channel]);
+	}
 	reinterpret_cast<float *>(arena + record.row_output_offset)[row * width + channel] = sum;
 }

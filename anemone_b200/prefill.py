@@ -4,11 +4,13 @@ Launches of one call, all from libanemone_b200.so (kernel file kernel_exl3_prefi
     exl3_prefill_picks -> exl3_prefill_group -> exl3_prefill_tiles -> exl3_prefill_operands
     -> exl3_prefill_gate_up -> exl3_prefill_down -> exl3_prefill_row_sum
 Rows are grouped per expert into tiles of 128; each (row tile, 128 outputs) is a tensor-core contraction with the
-expert's trellis tiles decoded on the way. The result is this rank's FP32 [rows][hidden] row sums (a rank of a
-tensor-parallel group holds a slice of the intermediate columns; the ranks' rows are then reduced in rank order as in
-the decode layer). Nothing here computes on the host.
+expert's trellis tiles decoded on the way. The result is this rank's FP32 [rows][hidden] row sums over the pairs whose
+experts it holds. A rank holds a run of the routed experts with their full intermediate width (expert parallelism) or
+all of them with a slice of the intermediate columns (tensor parallelism), and a column slice of the always-on experts;
+the ranks' rows are then summed in rank order. Nothing here computes on the host.
 """
 import ctypes as C
+from dataclasses import dataclass
 
 import numpy as np
 
@@ -18,29 +20,81 @@ from . import synthetic
 from .moe import rank_columns
 
 
-class PrefillLayout:
-    """Byte offsets of everything the prefill launches use in the arena."""
+@dataclass
+class Share:
+    """What one rank holds of the layer's experts."""
+    local_first: int
+    local_count: int
+    inner: int  # intermediate width of the routed experts' matrices held here (0 if local_count is 0)
+    inner_begin: int  # first intermediate column of those matrices (tensor parallelism), else 0
+    shared_inner: int  # the same for the always-on experts
+    shared_begin: int
 
-    def __init__(self, config, widths, rank_count=1, rank=0):
+    @staticmethod
+    def whole(config):
+        return Share(0, config.experts, config.inner, 0, config.inner if config.shared else 0, 0)
+
+    @staticmethod
+    def tensor_parallel(config, rank_count, rank):
+        begin, count = rank_columns(config.inner, rank_count, rank)
+        return Share(0, config.experts, count, begin, count if config.shared else 0, begin)
+
+    @staticmethod
+    def expert_parallel(config, rank_count, rank):
+        first = config.experts * rank // rank_count
+        begin, count = rank_columns(config.inner, rank_count, rank)
+        return Share(first, config.experts * (rank + 1) // rank_count - first, config.inner, 0,
+                     count if config.shared else 0, begin)
+
+    def shared_count(self, config):
+        return config.shared if self.shared_inner else 0
+
+    def experts(self, config):
+        """Global numbers of the experts held, in local order: routed run, then the always-on ones."""
+        return list(range(self.local_first, self.local_first + self.local_count)) + \
+            [config.experts + s for s in range(self.shared_count(config))]
+
+    def matrices(self, config, expert, width, gate, up, down):
+        """This rank's part of one expert's three FULL stored matrices."""
+        H, I = config.hidden, config.inner
+        begin, count = (self.inner_begin, self.inner) if expert < config.experts else \
+            (self.shared_begin, self.shared_inner)
+        if count == I:
+            return gate, up, down
+        return (synthetic.slice_matrix(gate, H, I, width, 0, H, begin, count),
+                synthetic.slice_matrix(up, H, I, width, 0, H, begin, count),
+                synthetic.slice_matrix(down, I, H, width, begin, count, 0, H))
+
+
+class PrefillLayout:
+    """Byte offsets of everything the prefill launches use in the arena. widths: by local expert."""
+
+    def __init__(self, config, widths, share=None):
         self.config = config
-        self.inner_local = rank_columns(config.inner, rank_count, rank)[1]
-        c, H, I = config, config.hidden, self.inner_local
+        self.share = share = share or Share.whole(config)
+        c, H = config, config.hidden
         rows = c.row_capacity
+        self.shared_count = share.shared_count(c)
+        self.local_experts = share.local_count + self.shared_count
+        self.pairs_per_row = c.picks + self.shared_count
+        assert len(widths) == self.local_experts
         layout = api.Layout()
         self.step = layout.take(256)
         self.tokens = layout.take(rows * H * 2)
         self.scores = layout.take(rows * c.experts * 4)
         self.picks = layout.take(rows * c.picks * 4)
         self.weights = layout.take(rows * c.picks * 4)
-        self.expert_table = layout.take(c.total_experts * 24)
-        self.widths = layout.take(c.total_experts * 4)
-        self.parts = api.prefill_parts(rows, c.picks, c.shared, c.experts, H, I)
+        self.expert_table = layout.take(self.local_experts * 24)
+        self.widths = layout.take(self.local_experts * 4)
+        self.parts = api.prefill_parts(rows, c.picks, self.shared_count, share.local_count, H,
+                                       max(share.inner, share.shared_inner))
         self.workspace = layout.take(self.parts.total, 1024)
-        self.pair_outputs = layout.take(rows * c.pairs_per_row * H * 4)
+        self.pair_outputs = layout.take(rows * self.pairs_per_row * H * 4)
         self.row_output = layout.take(rows * H * 4)
         self.matrices = []
-        for expert in range(c.total_experts):
-            width = int(widths[expert])
+        for local in range(self.local_experts):
+            width = int(widths[local])
+            I = share.inner if local < share.local_count else share.shared_inner
             sizes = (synthetic.matrix_bytes(H, I, width), synthetic.matrix_bytes(H, I, width),
                      synthetic.matrix_bytes(I, H, width))
             self.matrices.append(tuple(layout.take(size, 64) for size in sizes))
@@ -48,27 +102,30 @@ class PrefillLayout:
 
 
 class PrefillLayer:
-    def __init__(self, card, config, widths, matrices, rank=0, rank_count=1):
-        """matrices: iterable over experts (routed, then shared) of this rank's (gate, up, down) stored bytes."""
+    def __init__(self, card, config, widths, matrices, share=None):
+        """widths, matrices: by LOCAL expert (the rank's routed run, then its always-on experts): stored widths and
+        this rank's (gate, up, down) stored bytes."""
         self.card, self.config = card, config
         self.widths = np.asarray(widths, dtype=np.uint32)
-        self.layout = L = PrefillLayout(config, self.widths, rank_count, rank)
+        self.layout = L = PrefillLayout(config, self.widths, share)
+        share = L.share
         assert card.arena_bytes >= L.arena_bytes
         self.weight_bytes = 0
-        table = np.zeros((config.total_experts, 3), dtype=np.uint64)
-        for expert, triple in enumerate(matrices):
+        table = np.zeros((L.local_experts, 3), dtype=np.uint64)
+        for local, triple in enumerate(matrices):
             for which, data in enumerate(triple):
-                offset = L.matrices[expert][which]
+                offset = L.matrices[local][which]
                 card.upload(offset, data)
-                table[expert, which] = offset
+                table[local, which] = offset
                 self.weight_bytes += data.size
         card.upload(L.expert_table, table)
         card.upload(L.widths, self.widths)
         card.fill(L.step, 0, 256)
         c = config
         self.record = R.Exl3Prefill(L.scores, L.tokens, L.expert_table, L.widths, L.picks, L.weights, L.workspace,
-                                    L.pair_outputs, L.row_output, L.step, c.hidden, L.inner_local, c.experts, c.shared,
-                                    c.picks, c.row_capacity, c.scoring, c.route_scale, c.activation_limit, 0)
+                                    L.pair_outputs, L.row_output, L.step, c.hidden, share.inner, share.shared_inner,
+                                    c.experts, share.local_first, share.local_count, L.shared_count, c.picks,
+                                    c.row_capacity, c.scoring, c.route_scale, c.activation_limit)
         self.launches = (R.KernelLaunch * 7)()
         api.check(api.library().exl3_prefill_prepare(C.byref(self.record), card.arena_bytes, card.ops_pointer,
                                                      card.handle, self.launches), "exl3_prefill_prepare")

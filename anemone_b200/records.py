@@ -59,9 +59,10 @@ class Exl3Prefill(C.Structure):
                 ("widths_offset", C.c_uint64), ("picks_offset", C.c_uint64), ("weights_offset", C.c_uint64),
                 ("workspace_offset", C.c_uint64), ("pair_output_offset", C.c_uint64),
                 ("row_output_offset", C.c_uint64), ("step_offset", C.c_uint64), ("input_size", C.c_uint32),
-                ("inner_size", C.c_uint32), ("expert_count", C.c_uint32), ("shared_count", C.c_uint32),
+                ("inner_size", C.c_uint32), ("shared_inner_size", C.c_uint32), ("expert_count", C.c_uint32),
+                ("local_first", C.c_uint32), ("local_count", C.c_uint32), ("shared_count", C.c_uint32),
                 ("picks", C.c_uint32), ("row_capacity", C.c_uint32), ("scoring", C.c_uint32),
-                ("route_scale", C.c_float), ("activation_limit", C.c_float), ("reserved_zero", C.c_uint32)]
+                ("route_scale", C.c_float), ("activation_limit", C.c_float), ("reserved_zero", C.c_uint32 * 2)]
 
 
 class Exl3PrefillTile(C.Structure):
@@ -195,7 +196,7 @@ class OrderedCollectiveKernels(C.Structure):
 
 
 for _record, _bytes in ((Exl3Reconstruct, 32), (Exl3Expert, 80), (ExpertJob, 96), (ExpertRowSum, 24),
-                        (Exl3ShardActivation, 96), (Exl3Moe, 112), (Exl3Prefill, 120), (Exl3PrefillTile, 16), (Exl3PrefillEntry, 8), (Exl3PrefillParts, 56), (StepBlock, 16), (OrderedPeer, 32),
+                        (Exl3ShardActivation, 96), (Exl3Moe, 112), (Exl3Prefill, 136), (Exl3PrefillTile, 16), (Exl3PrefillEntry, 8), (Exl3PrefillParts, 56), (StepBlock, 16), (OrderedPeer, 32),
                         (OrderedCollective, 80), (OrderedReduceBf16, 96), (OrderedRowSumPublish, 96),
                         (RouterSelectB200, 80), (StepInputSelect, 40), (ActivationQuantize, 40), (ExpertGateUp, 64), (ExpertDown, 56),
                         (KernelLaunch, 232), (CardDescription, 168)):

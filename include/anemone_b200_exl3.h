@@ -85,8 +85,8 @@ MUST_CHECK result_status exl3_prefill_prepare(const struct exl3_prefill_record *
 
 /* The workspace layout of exl3_prefill_prepare for these shapes: exl3_prefill_parts_of as an export, for callers that
  * cannot use the inline function. */
-void exl3_prefill_sizes(uint32_t row_capacity, uint32_t picks, uint32_t shared_count, uint32_t expert_count,
-			uint32_t input_size, uint32_t inner_size, struct exl3_prefill_parts *parts_out);
+void exl3_prefill_sizes(uint32_t row_capacity, uint32_t picks, uint32_t shared_count, uint32_t local_count,
+			uint32_t input_size, uint32_t widest_inner_size, struct exl3_prefill_parts *parts_out);
 
 /* ---- load-time slices for tensor parallelism (include/anemone/exl3_layout.h) ---- */
 

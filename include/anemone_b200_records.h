@@ -346,26 +346,30 @@ struct router_select_b200_arguments {
  * decoded once per row tile into shared memory as FP16 and multiplied on the fifth-generation tensor cores
  * (tcgen05.mma, FP32 accumulators in tensor memory). The reference's counterpart is its tensor-core prefill family
  * (source/kernel_exl3_tcp.cuh: route, operands, grouped GEMM, combine), fixed to its own model's shapes; this one takes
- * shapes, expert count, picks and a stored width per expert from the record. Arithmetic per value is the retained
+ * shapes, expert count, picks and a stored width per expert from the record, and a rank may hold any run of the routed
+ * experts (expert parallelism) and its own slice of the always-on experts' columns. Arithmetic per value is the retained
  * chain's (FP16 operands from the FP32 Hadamard transform, exactly decoded FP16 weights, FP32 accumulation, FP32
  * transforms, SwiGLU, route weight last); only the association of the FP32 sums over K is the tensor cores'.
  * Seven launches, one record:
  *   exl3_prefill_picks     grid (ceil(rows / 32)) x 1024: each live row's picks and weights (router_select_b200's
  *                          conventions), from scores
- *   exl3_prefill_group     grid (experts + shared) x 256: entries[expert][...]: the pairs routed to the expert in
+ *   exl3_prefill_group     grid (local + shared) x 256: entries[local expert][...]: the pairs routed to the expert in
  *                          ascending row order, and their count
  *   exl3_prefill_tiles     grid 1 x 1024: the tile table: (expert, first entry, rows) per 128-row tile, tile count
  *   exl3_prefill_operands  grid (tile capacity, H / 128, 2) x 128: FP16 gate and up operands of every tile row
- *   exl3_prefill_gate_up   grid (I / 128, tile capacity) x 320: both products, SwiGLU, FP16 down operands
+ *   exl3_prefill_gate_up   grid (max(I, shared I) / 128, tile capacity) x 320: both products, SwiGLU, FP16 down operands
  *   exl3_prefill_down      grid (H / 128, tile capacity) x 320: down product, output transform: FP32 pair outputs
- *   exl3_prefill_row_sum   grid (ceil(H / 128), rows) x 128: FP32 row sums, ascending slots from +0
+ *   exl3_prefill_row_sum   grid (ceil(H / 128), rows) x 128: FP32 row sums over the row's LOCAL pairs, ascending slots
+ *                          from +0
  * Workspace at workspace_offset, parts in this order, each aligned to 1024 bytes (exl3_prefill_sizes gives them):
- *   counts uint32 [experts + shared + 1] (the last: tile count) | tiles struct exl3_prefill_tile [tile capacity] |
- *   entries struct exl3_prefill_entry [experts + shared][row_capacity] |
- *   gate/up operands FP16 [2][tile capacity][H / 64][128 x 64 block] | down operands FP16 [tile capacity][I / 64][block]
+ *   counts uint32 [local + shared + 1] (the last: tile count) | tiles struct exl3_prefill_tile [tile capacity] |
+ *   entries struct exl3_prefill_entry [local + shared][row_capacity] |
+ *   gate/up operands FP16 [2][tile capacity][H / 64][128 x 64 block] |
+ *   down operands FP16 [tile capacity][max(I, shared I) / 64][block]
  * where a 128 x 64 block is stored as the tensor cores read it without swizzling: the 16 bytes of row r, inputs
  * 8 c .. 8 c + 7 lie at byte 2048 c + 128 (r / 8) + 16 (r % 8).
- * tile capacity = ceil(row_capacity * (picks + shared) / 128) + experts + shared.
+ * tile capacity = ceil(row_capacity * (picks + shared) / 128) + local + shared; exl3_prefill_parts_of takes the local
+ * expert count and the larger of the two intermediate widths.
  * Rows at or beyond step.row_count are not read and nothing is written for them; a pair output is written only for
  * live rows. expert_count <= 512, experts + shared <= 1024, picks <= 16, H and I multiples of 128. */
 #define EXL3_PREFILL_KERNEL_FILE "kernel_exl3_prefill"
@@ -374,7 +378,7 @@ struct router_select_b200_arguments {
 #define EXL3_PREFILL_BLOCK_INPUTS 64u
 #define EXL3_PREFILL_BLOCK_BYTES 16384u
 struct exl3_prefill_tile {
-	uint32_t expert;
+	uint32_t expert; /* local numbering: the rank's routed experts, then its always-on experts */
 	uint32_t first_entry; /* into the expert's entries */
 	uint32_t row_count; /* 1 .. 128 */
 	uint32_t reserved_zero;
@@ -386,24 +390,27 @@ struct exl3_prefill_entry {
 struct exl3_prefill_record {
 	uint64_t scores_offset; /* FP32 [row_capacity][expert_count] */
 	uint64_t input_offset; /* bfloat16 [row_capacity][input_size] */
-	uint64_t expert_table_offset; /* uint64 [expert_count + shared_count][3] */
-	uint64_t widths_offset; /* uint32 [expert_count + shared_count] stored widths */
-	uint64_t picks_offset; /* written: uint32 [row_capacity][picks] */
+	uint64_t expert_table_offset; /* uint64 [local_count + shared_count][3], by LOCAL expert */
+	uint64_t widths_offset; /* uint32 [local_count + shared_count] stored widths, by local expert */
+	uint64_t picks_offset; /* written: uint32 [row_capacity][picks], global expert numbers */
 	uint64_t weights_offset; /* written: FP32 [row_capacity][picks] */
 	uint64_t workspace_offset;
-	uint64_t pair_output_offset; /* written: FP32 [row_capacity * (picks + shared)][input_size] */
+	uint64_t pair_output_offset; /* written: FP32 [row_capacity * (picks + shared)][input_size], local pairs only */
 	uint64_t row_output_offset; /* written: FP32 [row_capacity][input_size] */
 	uint64_t step_offset; /* struct step_block: row_count live rows */
 	uint32_t input_size; /* H */
-	uint32_t inner_size; /* this rank's intermediate width */
-	uint32_t expert_count;
-	uint32_t shared_count;
+	uint32_t inner_size; /* intermediate width of the routed experts' matrices held here */
+	uint32_t shared_inner_size; /* the same of the always-on experts' matrices (0 if shared_count is 0) */
+	uint32_t expert_count; /* routed experts the router chooses among */
+	uint32_t local_first; /* this rank holds the routed experts local_first .. local_first + local_count - 1 */
+	uint32_t local_count; /* may be 0: a rank that only holds always-on experts */
+	uint32_t shared_count; /* always-on experts held here (slot picks + s of every row, weight 1) */
 	uint32_t picks;
 	uint32_t row_capacity;
 	uint32_t scoring;
 	float route_scale;
 	float activation_limit;
-	uint32_t reserved_zero;
+	uint32_t reserved_zero[2];
 };
 
 /* Offsets of the workspace parts from workspace_offset, the workspace's bytes and the tile capacity. */
@@ -419,10 +426,10 @@ AB_INLINE uint64_t exl3_prefill_aligned(uint64_t bytes)
 }
 
 AB_INLINE struct exl3_prefill_parts exl3_prefill_parts_of(uint32_t row_capacity, uint32_t picks, uint32_t shared_count,
-							    uint32_t expert_count, uint32_t input_size, uint32_t inner_size)
+							    uint32_t local_count, uint32_t input_size, uint32_t inner_size)
 {
 	struct exl3_prefill_parts parts;
-	const uint32_t experts = expert_count + shared_count;
+	const uint32_t experts = local_count + shared_count;
 	const uint64_t pairs = (uint64_t)row_capacity * (picks + shared_count);
 	parts.tile_capacity = (uint32_t)((pairs + EXL3_PREFILL_TILE_ROWS - 1u) / EXL3_PREFILL_TILE_ROWS) + experts;
 	parts.reserved_zero = 0;
@@ -552,7 +559,7 @@ AB_RECORD_HAS(router_select_b200_arguments, 80);
 AB_RECORD_HAS(step_input_select_arguments, 40);
 AB_RECORD_HAS(exl3_prefill_tile, 16);
 AB_RECORD_HAS(exl3_prefill_entry, 8);
-AB_RECORD_HAS(exl3_prefill_record, 120);
+AB_RECORD_HAS(exl3_prefill_record, 136);
 AB_RECORD_HAS(activation_quantize_arguments, 40);
 AB_RECORD_HAS(expert_gate_up_arguments, 64);
 AB_RECORD_HAS(expert_down_arguments, 56);

@@ -7,7 +7,7 @@ import pytest
 from anemone_b200 import records as R
 from anemone_b200 import synthetic
 from anemone_b200.moe import MoeConfig, MoeLayer, MoeLayout
-from anemone_b200.prefill import PrefillLayer, PrefillLayout
+from anemone_b200.prefill import PrefillLayer, PrefillLayout, Share
 from oracle import moe_reference
 
 pytestmark = pytest.mark.gpu
@@ -138,6 +138,36 @@ def test_prefill_agrees_with_decode_launches(api):
     assert cosine(prefill_rows, decode_rows) >= 0.99999
 
 
+@pytest.mark.parametrize("kind,ranks", [("expert_parallel", 2), ("expert_parallel", 4), ("tensor_parallel", 2)])
+def test_prefill_shares_add_up(api, oracle, kind, ranks):
+    """Every rank of a group in turn on one card: each holds its share of the experts; the ranks' FP32 rows, added in
+    rank order, are the whole layer's rows (the oracle's, which computes all experts in one place)."""
+    config = MoeConfig(hidden=512, inner=512, experts=16, shared=1, picks=4, row_capacity=200)
+    rows = 200
+    widths, matrices, tokens, scores = make_inputs(31, config, rows)
+    scores[:, :4] += 2.0  # skewed routing: the first rank of an expert-parallel group gets most pairs
+    experts, weights = moe_reference.route(oracle, config, scores)
+    expected = moe_reference.rank_partial(oracle, config, widths, matrices, tokens, experts, weights, 1, 0)[0]
+    total = np.zeros_like(expected)
+    for rank in range(ranks):
+        share = getattr(Share, kind)(config, ranks, rank)
+        held = share.experts(config)
+        local_widths = widths[held]
+        local_matrices = [share.matrices(config, e, int(widths[e]), *matrices[e]) for e in held]
+        card = api.Card(0, PrefillLayout(config, local_widths, share).arena_bytes)
+        try:
+            layer = PrefillLayer(card, config, local_widths, local_matrices, share)
+            total = total + layer.step(tokens, scores)
+            picks = card.download(layer.layout.picks, rows * config.picks * 4, np.uint32).reshape(rows, config.picks)
+            assert np.array_equal(picks, experts)
+            counts = card.download(layer.layout.workspace, (len(held) + 1) * 4, np.uint32)
+            want = [int((experts == e).sum()) if e < config.experts else rows for e in held]
+            assert list(counts[:len(held)]) == want
+        finally:
+            card.close()
+    assert np.abs(total - expected).max() <= MAX_ABS and cosine(total, expected) >= COSINE
+
+
 def test_prefill_preparer_refusals(api):
     config = MoeConfig(hidden=256, inner=128, experts=4, shared=0, picks=2, row_capacity=16)
     widths = np.full(4, 3, dtype=np.uint32)
@@ -147,7 +177,7 @@ def test_prefill_preparer_refusals(api):
         import ctypes as C
         good = R.Exl3Prefill(layout.scores, layout.tokens, layout.expert_table, layout.widths, layout.picks,
                              layout.weights, layout.workspace, layout.pair_outputs, layout.row_output, layout.step,
-                             256, 128, 4, 0, 2, 16, 0, 1.0, 10.0, 0)
+                             256, 128, 0, 4, 0, 4, 0, 2, 16, 0, 1.0, 10.0)
         launches = (R.KernelLaunch * 7)()
         lib = api.library()
 
@@ -163,10 +193,12 @@ def test_prefill_preparer_refusals(api):
 
         assert status() == 0
         assert launches[4].grid[0] == 1 and launches[4].block[0] == 320 and launches[5].grid[0] == 2
+        assert status(local_first=2, local_count=2) == 0
         for changes in ({"input_size": 192}, {"inner_size": 64}, {"picks": 0}, {"picks": 5}, {"expert_count": 0},
-                        {"reserved_zero": 1}, {"workspace_offset": layout.workspace + 512},
+                        {"reserved_zero": (C.c_uint32 * 2)(0, 1)}, {"workspace_offset": layout.workspace + 512},
                         {"row_output_offset": layout.pair_outputs}, {"activation_limit": 0.0},
-                        {"row_capacity": 0}, {"scores_offset": card.arena_bytes}):
+                        {"row_capacity": 0}, {"scores_offset": card.arena_bytes}, {"local_first": 3},
+                        {"local_count": 0}, {"shared_inner_size": 128}, {"shared_count": 1}):
             assert status(**changes) == 1, changes  # STATUS_INVALID_ARGUMENT
     finally:
         card.close()
