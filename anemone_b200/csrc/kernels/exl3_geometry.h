@@ -47,7 +47,7 @@ AB_INLINE uint32_t exl3_moe_splits(uint32_t inputs)
 }
 
 /* ---- prefill (kernel_exl3_prefill) ---- */
-#define EXL3_PREFILL_GEMM_THREADS 320u /* a copy warp, an issuing warp, eight decode warps */
+#define EXL3_PREFILL_GEMM_THREADS 576u /* a copy warp, an issuing warp, sixteen decode warps */
 #define EXL3_PREFILL_GATE_UP_STAGES 3u
 #define EXL3_PREFILL_DOWN_STAGES 4u
 #define EXL3_PREFILL_TRELLIS_BYTES 4096u /* of one stage and matrix: four tile rows of eight K4 tiles */

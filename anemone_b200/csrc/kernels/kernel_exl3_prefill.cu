@@ -19,7 +19,8 @@
 #include "router_device.cuh"
 
 #define PREFILL_MOST_STAGES 4u
-#define PREFILL_DECODE_WARPS 8u
+#define PREFILL_DECODE_WARPS 16u
+#define PREFILL_WARP_TILES (EXL3_STAGE_STEPS * EXL3_GROUP_TILES / PREFILL_DECODE_WARPS) /* of a stage and matrix */
 #define PREFILL_DECODE_THREADS (PREFILL_DECODE_WARPS * EXL3_WARP)
 #define PREFILL_COLUMNS 128u /* tensor-memory columns of one accumulator tile */
 #define PREFILL_GROUP_THREADS 256u
@@ -377,10 +378,10 @@ __device__ __forceinline__ bool prefill_products(const unsigned char *const (&ma
 		return false;
 	}
 
-	/* decode: warp w takes K step w % 4 of the stage and the output tiles 4 (w / 4) .. + 3, of every matrix */
+	/* decode: warp w takes K step w % 4 of the stage and PREFILL_WARP_TILES adjacent output tiles, of every matrix */
 	{
 		const uint32_t decoder = warp - 2u, step = decoder % EXL3_STAGE_STEPS;
-		const uint32_t first_tile = decoder / EXL3_STAGE_STEPS * 4u;
+		const uint32_t first_tile = decoder / EXL3_STAGE_STEPS * PREFILL_WARP_TILES;
 		const uint32_t begin = ring::begin(lane);
 		const uint32_t word_index = begin / 32u, shift = begin % 32u, next_index = (word_index + 1u) % ring::words;
 		bool good = true;
@@ -398,7 +399,7 @@ __device__ __forceinline__ bool prefill_products(const unsigned char *const (&ma
 					at + m * EXL3_PREFILL_STAGE_BYTES + trellis_at + step * row_bytes);
 				unsigned char *const b_block = at + m * EXL3_PREFILL_STAGE_BYTES + EXL3_PREFILL_BLOCK_BYTES;
 #pragma unroll
-				for (uint32_t mine = 0; mine < 4; mine++) {
+				for (uint32_t mine = 0; mine < PREFILL_WARP_TILES; mine++) {
 					const uint32_t tile = first_tile + mine;
 					uint32_t fragment[4];
 					exl3_decode_fragment<BX2>(words[tile * ring::words + word_index],
@@ -429,17 +430,15 @@ __device__ __forceinline__ bool prefill_products(const unsigned char *const (&ma
 }
 
 /* The accumulator tile of matrix m into shared memory, FP32 [128 rows][EXL3_PREFILL_STAGING_ROW]. A warp reads the 32
- * tensor-memory lanes of its quarter (warp % 4) and one half of the columns. Decode warps only; ends with their
+ * tensor-memory lanes of its quarter (warp % 4) and one quarter of the columns. Decode warps only; ends with their
  * barrier. */
 __device__ __forceinline__ void prefill_stage_out(uint32_t accumulators, uint32_t matrices, float *staging)
 {
 	const uint32_t lane = threadIdx.x % EXL3_WARP, warp = threadIdx.x / EXL3_WARP;
-	const uint32_t quarter = warp % 4u, half = (warp - 2u) / 4u;
+	const uint32_t quarter = warp % 4u, column = (warp - 2u) / 4u * 32u;
 	__syncwarp();
-	for (uint32_t m = 0; m < matrices; m++)
-#pragma unroll
-		for (uint32_t piece = 0; piece < 2; piece++) {
-			const uint32_t column = half * 64u + piece * 32u;
+	for (uint32_t m = 0; m < matrices; m++) {
+		{
 			uint32_t r[32];
 			asm volatile(
 				"tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -460,6 +459,7 @@ __device__ __forceinline__ void prefill_stage_out(uint32_t accumulators, uint32_
 			for (uint32_t index = 0; index < 8; index++)
 				to[index] = make_uint4(r[4 * index], r[4 * index + 1], r[4 * index + 2], r[4 * index + 3]);
 		}
+	}
 	tensor_fence_before();
 	decode_sync();
 }
@@ -623,7 +623,7 @@ __device__ __forceinline__ void prefill_down(const struct exl3_prefill_record &r
 		break;                                                                     \
 	}
 
-/* grid (widest I / 128, tile capacity) x 320 */
+/* grid (widest I / 128, tile capacity) x 576 */
 extern "C" __global__ void __launch_bounds__(EXL3_PREFILL_GEMM_THREADS, 1)
 	exl3_prefill_gate_up(struct exl3_prefill_record record, unsigned char *arena)
 {
@@ -641,7 +641,7 @@ extern "C" __global__ void __launch_bounds__(EXL3_PREFILL_GEMM_THREADS, 1)
 	PREFILL_WIDTH_SWITCH(prefill_gate_up)
 }
 
-/* grid (H / 128, tile capacity) x 320 */
+/* grid (H / 128, tile capacity) x 576 */
 extern "C" __global__ void __launch_bounds__(EXL3_PREFILL_GEMM_THREADS, 1)
 	exl3_prefill_down(struct exl3_prefill_record record, unsigned char *arena)
 {
