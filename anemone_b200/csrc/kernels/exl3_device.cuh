@@ -23,7 +23,7 @@
 
 #include "exl3_geometry.h"
 
-#define EXL3_WAIT_POLLS (1u << 22) /* of ~100 ns each with the back-off below: well under a second */
+#define EXL3_WAIT_CYCLES 1500000000ll /* of the device clock: under a second */
 
 __device__ unsigned int exl3_wait_expired;
 
@@ -55,11 +55,14 @@ __device__ __forceinline__ void barrier_arrive(uint64_t *barrier)
 	asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_address(barrier)) : "memory");
 }
 
-/* true once the phase of the given parity has completed; false if the bounded wait ran out */
+/* true once the phase of the given parity has completed; false if the bounded wait ran out. The wait spins on
+ * try_wait (which itself suspends the thread for a short, hardware-chosen time) and never sleeps: a sleep's wake-up
+ * is far coarser than the hand-offs of a pipeline stage. The bound is a count of device clock cycles. */
 __device__ __forceinline__ bool barrier_wait(uint64_t *barrier, uint32_t parity)
 {
 	const uint32_t address = smem_address(barrier);
-	for (uint32_t poll = 0; poll < EXL3_WAIT_POLLS; poll++) {
+	long long begun = 0;
+	for (uint32_t poll = 1;; poll++) {
 		uint32_t complete;
 		asm volatile("{\n\t.reg .pred p;\n\t"
 			     "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
@@ -69,8 +72,13 @@ __device__ __forceinline__ bool barrier_wait(uint64_t *barrier, uint32_t parity)
 			     : "memory");
 		if (complete != 0)
 			return true;
-		if (poll > 64)
-			__nanosleep(64);
+		if ((poll & 255u) == 0u) {
+			const long long now = clock64();
+			if (begun == 0)
+				begun = now;
+			else if (now - begun > EXL3_WAIT_CYCLES)
+				break;
+		}
 	}
 	atomicExch(&exl3_wait_expired, 1u);
 	return false;

@@ -18,21 +18,24 @@
 #include "exl3_passes.cuh"
 #include "router_device.cuh"
 
-#define PREFILL_MOST_STAGES 4u
+#define PREFILL_FIRST_DECODE_WARP 3u /* behind the two copy warps and the issuing warp */
 #define PREFILL_DECODE_WARPS 16u
-#define PREFILL_WARP_TILES (EXL3_STAGE_STEPS * EXL3_GROUP_TILES / PREFILL_DECODE_WARPS) /* of a stage and matrix */
+#define PREFILL_GROUPS 2u /* groups of 128 outputs of one product CTA */
 #define PREFILL_DECODE_THREADS (PREFILL_DECODE_WARPS * EXL3_WARP)
 #define PREFILL_COLUMNS 128u /* tensor-memory columns of one accumulator tile */
 #define PREFILL_GROUP_THREADS 256u
 
 struct prefill_shared {
-	uint64_t full[PREFILL_MOST_STAGES]; /* the stage's copies have landed */
-	uint64_t decoded[PREFILL_MOST_STAGES]; /* the stage's B blocks are written */
-	uint64_t consumed[PREFILL_MOST_STAGES]; /* the stage's products are done */
+	uint64_t a_full[EXL3_PREFILL_A_STAGES]; /* the stage's operand blocks have landed */
+	uint64_t a_free[EXL3_PREFILL_A_STAGES]; /* the products that read them are done */
+	uint64_t b_full[EXL3_PREFILL_B_STAGES]; /* the stage's decoded weights are written */
+	uint64_t b_free[EXL3_PREFILL_B_STAGES]; /* the products that read them are done */
+	uint64_t t_full[EXL3_PREFILL_T_STAGES]; /* the stage's trellis rows have landed */
+	uint64_t t_free[EXL3_PREFILL_T_STAGES]; /* every decode warp has read them */
 	uint64_t done; /* every product of the CTA is done */
 	uint32_t tensor_memory;
 	volatile uint32_t failed;
-	uint32_t armed; /* K blocks whose copies were started */
+	uint32_t armed_a, armed_t; /* K blocks whose copies were started */
 	uint32_t issued; /* 1: products were issued and `done` will complete */
 };
 
@@ -232,16 +235,20 @@ extern "C" __global__ void __launch_bounds__(EXL3_TRANSFORM_THREADS)
 
 /* ------------------------------------------------------------------ tensor-core products */
 
-/* shared-memory matrix descriptor of an operand block at a 16-byte aligned address: no swizzle, K-major; 2048 bytes
- * between the two 16-byte K pieces of a K = 16 step, 128 bytes between groups of eight rows */
-__device__ __forceinline__ uint64_t prefill_descriptor(uint32_t shared_address)
+/* shared-memory matrix descriptor of an operand block at a 16-byte aligned address: no swizzle, K-major;
+ * piece_bytes between the two 16-byte K pieces of a K = 16 step (128 bytes a group of eight rows: 2048 for 128 rows,
+ * 4096 for 256), 128 bytes between groups of eight rows */
+__device__ __forceinline__ uint64_t prefill_descriptor(uint32_t shared_address, uint32_t piece_bytes)
 {
-	return (uint64_t)((shared_address >> 4) & 0x3FFFu) | (uint64_t)(2048u >> 4) << 16 | (uint64_t)(128u >> 4) << 32 |
-	       (uint64_t)1 << 46;
+	return (uint64_t)((shared_address >> 4) & 0x3FFFu) | (uint64_t)(piece_bytes >> 4) << 16 |
+	       (uint64_t)(128u >> 4) << 32 | (uint64_t)1 << 46;
 }
 
-/* FP16 A and B, both K-major, FP32 accumulators, M = 128, N = 128 */
-#define PREFILL_INSTRUCTION ((1u << 4) | ((128u >> 3) << 17) | ((128u >> 4) << 24))
+/* FP16 A and B, both K-major, FP32 accumulators, M = 128, N = 128 x groups */
+__device__ __forceinline__ uint32_t prefill_instruction(uint32_t groups)
+{
+	return (1u << 4) | ((groups * 128u >> 3) << 17) | ((128u >> 4) << 24);
+}
 
 __device__ __forceinline__ void tensor_fence_before()
 {
@@ -265,37 +272,71 @@ __device__ __forceinline__ void decode_sync()
 	asm volatile("bar.sync 1, %0;" ::"n"(PREFILL_DECODE_THREADS) : "memory");
 }
 
-/* The K loop of one CTA. matrices[m]: the codes of matrix m (`outputs` outputs), of which the CTA takes outputs
- * 128 group .. + 127; operand_blocks[m]: the row tile's first operand block for matrix m, `blocks` blocks of 64 inputs.
- * On return the decode warps (2 .. 9) know whether the accumulators (tensor-memory columns 128 m .. 128 m + 127 from
- * shared->tensor_memory) are complete; warps 0 and 1 return false. All threads call. */
-template <uint32_t BX2, uint32_t MATRICES, uint32_t STAGES>
+/* Dynamic shared memory of a product CTA, for MATRICES matrices, PREFILL_GROUPS groups of 128 outputs and stages of
+ * KSTEPS steps of 16 inputs. Three rings of different depth, because their contents wait for different things:
+ *   A ring        EXL3_PREFILL_A_STAGES x [matrix] operand blocks (128 rows x 16 KSTEPS FP16 in the tensor cores'
+ *                 layout, KSTEPS x 4096 bytes): bulk copies, mostly from L2
+ *   B ring        EXL3_PREFILL_B_STAGES x [matrix] blocks of decoded weights, 256 outputs x 16 KSTEPS FP16 in the same
+ *                 layout (so one instruction multiplies both groups and reads the operand rows once): written by the
+ *                 decode warps
+ *   trellis ring  EXL3_PREFILL_T_STAGES x [matrix][step][group][8 tiles] (2048 bytes a row): bulk copies from HBM, the
+ *                 longest latency, so the deepest ring */
+template <uint32_t MATRICES, uint32_t KSTEPS> struct prefill_rings {
+	static constexpr uint32_t block_bytes = KSTEPS * 4096u;
+	static constexpr uint32_t a_stage = MATRICES * block_bytes;
+	static constexpr uint32_t b_stage = MATRICES * PREFILL_GROUPS * block_bytes;
+	static constexpr uint32_t b_piece = PREFILL_GROUPS * 2048u; /* eight inputs of 256 outputs */
+	static constexpr uint32_t trellis_row = PREFILL_GROUPS * 1024u;
+	static constexpr uint32_t t_stage = MATRICES * KSTEPS * trellis_row;
+	static constexpr uint32_t b_at = EXL3_PREFILL_A_STAGES * a_stage;
+	static constexpr uint32_t t_at = b_at + EXL3_PREFILL_B_STAGES * b_stage;
+	static constexpr uint32_t bytes = t_at + EXL3_PREFILL_T_STAGES * t_stage;
+	static_assert(bytes == EXL3_PREFILL_DYNAMIC_BYTES, "the host sizes the rings");
+	static_assert(MATRICES * PREFILL_GROUPS * KSTEPS * 2u == PREFILL_DECODE_WARPS, "four tiles a decode warp");
+};
+
+/* The K loop of one CTA. matrices[m]: the codes of matrix m (`outputs` outputs), of which the CTA takes the `groups`
+ * (1 or 2) groups of 128 outputs from group `first_group`; operand_blocks[m]: the row tile's operand blocks for matrix
+ * m; `blocks` stages of 16 KSTEPS inputs. Warp 0 copies trellis rows, warp 1 operand blocks, one thread of warp 2
+ * issues the products, warps 3 .. decode. On return the decode warps know whether the accumulators (matrix m, group g:
+ * tensor-memory columns 128 (2 m + g) .. + 127 from shared->tensor_memory) are complete; the other warps return false.
+ * All threads call. */
+template <uint32_t BX2, uint32_t MATRICES, uint32_t KSTEPS>
 __device__ __forceinline__ bool prefill_products(const unsigned char *const (&matrices)[MATRICES], uint32_t outputs,
-						 uint32_t group, const unsigned char *const (&operand_blocks)[MATRICES],
-						 uint32_t blocks, unsigned char *dynamic_shared, prefill_shared *shared)
+						 uint32_t first_group, uint32_t groups,
+						 const unsigned char *const (&operand_blocks)[MATRICES], uint32_t blocks,
+						 unsigned char *dynamic_shared, prefill_shared *shared)
 {
 	typedef exl3_ring<BX2> ring;
-	constexpr uint32_t row_bytes = EXL3_GROUP_TILES * ring::tile_bytes;
-	constexpr uint32_t stage_bytes = MATRICES * EXL3_PREFILL_STAGE_BYTES;
-	constexpr uint32_t trellis_at = 2u * EXL3_PREFILL_BLOCK_BYTES;
+	typedef prefill_rings<MATRICES, KSTEPS> rings;
+	constexpr uint32_t AS = EXL3_PREFILL_A_STAGES, BS = EXL3_PREFILL_B_STAGES, TS = EXL3_PREFILL_T_STAGES;
+	constexpr uint32_t row_bytes = EXL3_GROUP_TILES * ring::tile_bytes; /* one group's part of a tile row */
 	const uint32_t lane = threadIdx.x % EXL3_WARP, warp = threadIdx.x / EXL3_WARP;
 
 	if (threadIdx.x == 0) {
-		for (uint32_t stage = 0; stage < STAGES; stage++) {
-			barrier_init(&shared->full[stage], 1);
-			barrier_init(&shared->decoded[stage], PREFILL_DECODE_WARPS);
-			barrier_init(&shared->consumed[stage], 1);
+		for (uint32_t stage = 0; stage < AS; stage++) {
+			barrier_init(&shared->a_full[stage], 1);
+			barrier_init(&shared->a_free[stage], 1);
+		}
+		for (uint32_t stage = 0; stage < BS; stage++) {
+			barrier_init(&shared->b_full[stage], PREFILL_DECODE_WARPS);
+			barrier_init(&shared->b_free[stage], 1);
+		}
+		for (uint32_t stage = 0; stage < TS; stage++) {
+			barrier_init(&shared->t_full[stage], 1);
+			barrier_init(&shared->t_free[stage], PREFILL_DECODE_WARPS);
 		}
 		barrier_init(&shared->done, 1);
 		shared->failed = 0;
-		shared->armed = 0;
+		shared->armed_a = 0;
+		shared->armed_t = 0;
 		shared->issued = 0;
 		asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 	}
 	if (warp == 1) {
 		asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
 				     smem_address(&shared->tensor_memory)),
-			     "r"(MATRICES * PREFILL_COLUMNS)
+			     "r"(MATRICES * PREFILL_GROUPS * PREFILL_COLUMNS)
 			     : "memory");
 		asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
 	}
@@ -305,67 +346,96 @@ __device__ __forceinline__ bool prefill_products(const unsigned char *const (&ma
 	const uint32_t accumulators = shared->tensor_memory;
 
 	if (warp == 0) {
-		/* copies: one thread */
-		if (lane == 0) {
-			const uint64_t matrix_row_bytes = (uint64_t)(outputs / EXL3_TILE) * ring::tile_bytes;
-			uint32_t block = 0;
-			for (; block < blocks; block++) {
-				const uint32_t stage = block % STAGES, use = block / STAGES;
-				if (use > 0 && !barrier_wait(&shared->consumed[stage], (use - 1u) & 1u)) {
-					shared->failed = 1;
-					break;
-				}
-				unsigned char *const at = dynamic_shared + stage * stage_bytes;
-				barrier_expect(&shared->full[stage],
-					       MATRICES * (EXL3_PREFILL_BLOCK_BYTES + EXL3_STAGE_STEPS * row_bytes));
-#pragma unroll
-				for (uint32_t m = 0; m < MATRICES; m++) {
-					bulk_load(at + m * EXL3_PREFILL_STAGE_BYTES,
-						  operand_blocks[m] + (uint64_t)block * EXL3_PREFILL_BLOCK_BYTES,
-						  EXL3_PREFILL_BLOCK_BYTES, &shared->full[stage]);
-#pragma unroll
-					for (uint32_t step = 0; step < EXL3_STAGE_STEPS; step++)
-						bulk_load(at + m * EXL3_PREFILL_STAGE_BYTES + trellis_at + step * row_bytes,
-							  matrices[m] +
-								  (uint64_t)(block * EXL3_STAGE_STEPS + step) * matrix_row_bytes +
-								  (uint64_t)group * row_bytes,
-							  row_bytes, &shared->full[stage]);
-				}
+		/* trellis copies: lane 0 waits for the stage and arms its barrier; lane (m, step) then copies the groups'
+		 * adjacent tiles of its tile row */
+		const uint64_t matrix_row_bytes = (uint64_t)(outputs / EXL3_TILE) * ring::tile_bytes;
+		const uint32_t m = lane / KSTEPS, step = lane % KSTEPS;
+		uint32_t block = 0;
+		for (; block < blocks; block++) {
+			const uint32_t stage = block % TS, use = block / TS;
+			uint32_t good = 1;
+			if (lane == 0) {
+				if (use > 0 && !barrier_wait(&shared->t_free[stage], (use - 1u) & 1u))
+					good = 0;
+				else
+					barrier_expect(&shared->t_full[stage], MATRICES * KSTEPS * groups * row_bytes);
 			}
-			shared->armed = block;
+			good = __shfl_sync(0xFFFFFFFFu, good, 0);
+			if (good == 0)
+				break;
+			if (lane < MATRICES * KSTEPS)
+				bulk_load(dynamic_shared + rings::t_at + stage * rings::t_stage + lane * rings::trellis_row,
+					  matrices[m] + (uint64_t)(block * KSTEPS + step) * matrix_row_bytes +
+						  (uint64_t)first_group * row_bytes,
+					  groups * row_bytes, &shared->t_full[stage]);
+		}
+		if (lane == 0) {
+			shared->armed_t = block;
+			if (block < blocks)
+				shared->failed = 1;
 		}
 		return false;
 	}
 	if (warp == 1) {
+		/* operand copies: lane m copies matrix m's block */
+		uint32_t block = 0;
+		for (; block < blocks; block++) {
+			const uint32_t stage = block % AS, use = block / AS;
+			uint32_t good = 1;
+			if (lane == 0) {
+				if (use > 0 && !barrier_wait(&shared->a_free[stage], (use - 1u) & 1u))
+					good = 0;
+				else
+					barrier_expect(&shared->a_full[stage], rings::a_stage);
+			}
+			good = __shfl_sync(0xFFFFFFFFu, good, 0);
+			if (good == 0)
+				break;
+			if (lane < MATRICES)
+				bulk_load(dynamic_shared + stage * rings::a_stage + lane * rings::block_bytes,
+					  operand_blocks[lane] + (uint64_t)block * rings::block_bytes, rings::block_bytes,
+					  &shared->a_full[stage]);
+		}
+		if (lane == 0) {
+			shared->armed_a = block;
+			if (block < blocks)
+				shared->failed = 1;
+		}
+		return false;
+	}
+	if (warp == 2) {
 		/* products: one thread */
 		if (lane == 0) {
 			bool good = true;
+			const uint32_t instruction = prefill_instruction(groups);
 			for (uint32_t block = 0; block < blocks && good; block++) {
-				const uint32_t stage = block % STAGES, use = block / STAGES;
-				good = barrier_wait(&shared->full[stage], use & 1u) &&
-				       barrier_wait(&shared->decoded[stage], use & 1u);
+				const uint32_t sa = block % AS, sb = block % BS;
+				good = barrier_wait(&shared->a_full[sa], (block / AS) & 1u) &&
+				       barrier_wait(&shared->b_full[sb], (block / BS) & 1u);
 				if (!good)
 					break;
 				tensor_fence_after();
-				const uint32_t at = smem_address(dynamic_shared + stage * stage_bytes);
+				const uint32_t a_at = smem_address(dynamic_shared + sa * rings::a_stage);
+				const uint32_t b_at = smem_address(dynamic_shared + rings::b_at + sb * rings::b_stage);
 #pragma unroll
 				for (uint32_t m = 0; m < MATRICES; m++)
 #pragma unroll
-					for (uint32_t step = 0; step < EXL3_STAGE_STEPS; step++) {
-						const uint64_t a = prefill_descriptor(at + m * EXL3_PREFILL_STAGE_BYTES +
-										      step * 2u * 2048u);
-						const uint64_t b =
-							prefill_descriptor(at + m * EXL3_PREFILL_STAGE_BYTES +
-									   EXL3_PREFILL_BLOCK_BYTES + step * 2u * 2048u);
+					for (uint32_t step = 0; step < KSTEPS; step++) {
+						const uint64_t a =
+							prefill_descriptor(a_at + m * rings::block_bytes + step * 2u * 2048u, 2048u);
+						const uint64_t b = prefill_descriptor(b_at + m * PREFILL_GROUPS * rings::block_bytes +
+										      step * 2u * rings::b_piece,
+										      rings::b_piece);
 						const uint32_t accumulate = block > 0 || step > 0 ? 1u : 0u;
 						asm volatile("{\n\t.reg .pred p;\n\t"
 							     "setp.ne.b32 p, %4, 0;\n\t"
 							     "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(
-								     accumulators + m * PREFILL_COLUMNS),
-							     "l"(a), "l"(b), "r"(PREFILL_INSTRUCTION), "r"(accumulate)
+								     accumulators + m * PREFILL_GROUPS * PREFILL_COLUMNS),
+							     "l"(a), "l"(b), "r"(instruction), "r"(accumulate)
 							     : "memory");
 					}
-				tensor_commit(&shared->consumed[stage]);
+				tensor_commit(&shared->a_free[sa]);
+				tensor_commit(&shared->b_free[sb]);
 				shared->issued = 1;
 			}
 			if (!good) {
@@ -378,46 +448,49 @@ __device__ __forceinline__ bool prefill_products(const unsigned char *const (&ma
 		return false;
 	}
 
-	/* decode: warp w takes K step w % 4 of the stage and PREFILL_WARP_TILES adjacent output tiles, of every matrix */
+	/* decode: warp d takes four adjacent output tiles of one (matrix, group, step) of the stage */
 	{
-		const uint32_t decoder = warp - 2u, step = decoder % EXL3_STAGE_STEPS;
-		const uint32_t first_tile = decoder / EXL3_STAGE_STEPS * PREFILL_WARP_TILES;
+		const uint32_t decoder = warp - PREFILL_FIRST_DECODE_WARP;
+		const uint32_t quad = decoder % 2u, step = decoder / 2u % KSTEPS, g = decoder / (2u * KSTEPS) % PREFILL_GROUPS;
+		const uint32_t m = decoder / (2u * KSTEPS * PREFILL_GROUPS);
 		const uint32_t begin = ring::begin(lane);
 		const uint32_t word_index = begin / 32u, shift = begin % 32u, next_index = (word_index + 1u) % ring::words;
+		const uint32_t words_at = rings::t_at + (m * KSTEPS + step) * rings::trellis_row +
+					  (g * EXL3_GROUP_TILES + quad * 4u) * ring::tile_bytes;
+		const uint32_t to_at = rings::b_at + m * PREFILL_GROUPS * rings::block_bytes + step * 2u * rings::b_piece +
+				       (g * EXL3_GROUP_TILES + quad * 4u) * 2u * 128u + lane * 4u;
 		bool good = true;
 		for (uint32_t block = 0; block < blocks && good; block++) {
-			const uint32_t stage = block % STAGES, use = block / STAGES;
-			if (use > 0)
-				good = barrier_wait(&shared->consumed[stage], (use - 1u) & 1u);
-			good = good && barrier_wait(&shared->full[stage], use & 1u);
+			const uint32_t st = block % TS, sb = block % BS;
+			if (block >= BS)
+				good = barrier_wait(&shared->b_free[sb], (block / BS - 1u) & 1u);
+			good = good && barrier_wait(&shared->t_full[st], (block / TS) & 1u);
 			if (!good)
 				break;
-			unsigned char *const at = dynamic_shared + stage * stage_bytes;
+			if (g < groups) {
+				const uint32_t *const words =
+					reinterpret_cast<const uint32_t *>(dynamic_shared + st * rings::t_stage + words_at);
+				unsigned char *const to_stage = dynamic_shared + sb * rings::b_stage + to_at;
 #pragma unroll
-			for (uint32_t m = 0; m < MATRICES; m++) {
-				const uint32_t *const words = reinterpret_cast<const uint32_t *>(
-					at + m * EXL3_PREFILL_STAGE_BYTES + trellis_at + step * row_bytes);
-				unsigned char *const b_block = at + m * EXL3_PREFILL_STAGE_BYTES + EXL3_PREFILL_BLOCK_BYTES;
-#pragma unroll
-				for (uint32_t mine = 0; mine < PREFILL_WARP_TILES; mine++) {
-					const uint32_t tile = first_tile + mine;
+				for (uint32_t mine = 0; mine < 4; mine++) {
 					uint32_t fragment[4];
-					exl3_decode_fragment<BX2>(words[tile * ring::words + word_index],
-								  words[tile * ring::words + next_index], shift, fragment);
+					exl3_decode_fragment<BX2>(words[mine * ring::words + word_index],
+								  words[mine * ring::words + next_index], shift, fragment);
 					/* fragment f: outputs 16 tile + g + 8 (f % 2), inputs 16 step + 2 t + 8 (f / 2), lane 4 g + t:
 					 * the warp's 32 words are the 128 bytes of one K piece of one group of eight outputs */
-					uint32_t *const to = reinterpret_cast<uint32_t *>(b_block + step * 2u * 2048u +
-											  tile * 2u * 128u + lane * 4u);
+					uint32_t *const to = reinterpret_cast<uint32_t *>(to_stage + mine * 2u * 128u);
 					to[0] = fragment[0];
 					to[128u / 4u] = fragment[1];
-					to[2048u / 4u] = fragment[2];
-					to[(2048u + 128u) / 4u] = fragment[3];
+					to[rings::b_piece / 4u] = fragment[2];
+					to[(rings::b_piece + 128u) / 4u] = fragment[3];
 				}
+				asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 			}
-			asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 			__syncwarp();
-			if (lane == 0)
-				barrier_arrive(&shared->decoded[stage]);
+			if (lane == 0) {
+				barrier_arrive(&shared->b_full[sb]);
+				barrier_arrive(&shared->t_free[st]);
+			}
 		}
 		if (good)
 			good = barrier_wait(&shared->done, 0u);
@@ -429,36 +502,34 @@ __device__ __forceinline__ bool prefill_products(const unsigned char *const (&ma
 	}
 }
 
-/* The accumulator tile of matrix m into shared memory, FP32 [128 rows][EXL3_PREFILL_STAGING_ROW]. A warp reads the 32
- * tensor-memory lanes of its quarter (warp % 4) and one quarter of the columns. Decode warps only; ends with their
- * barrier. */
-__device__ __forceinline__ void prefill_stage_out(uint32_t accumulators, uint32_t matrices, float *staging)
+/* The accumulator tiles (matrix m, group g) of every matrix into shared memory, FP32 [matrix][128 rows]
+ * [EXL3_PREFILL_STAGING_ROW]. A warp reads the 32 tensor-memory lanes of its quarter (warp % 4) and one quarter of the
+ * columns. Decode warps only; ends with their barrier. */
+__device__ __forceinline__ void prefill_stage_out(uint32_t accumulators, uint32_t matrices, uint32_t g, float *staging)
 {
 	const uint32_t lane = threadIdx.x % EXL3_WARP, warp = threadIdx.x / EXL3_WARP;
-	const uint32_t quarter = warp % 4u, column = (warp - 2u) / 4u * 32u;
+	const uint32_t quarter = warp % 4u, column = (warp - PREFILL_FIRST_DECODE_WARP) / 4u * 32u;
 	__syncwarp();
 	for (uint32_t m = 0; m < matrices; m++) {
-		{
-			uint32_t r[32];
-			asm volatile(
-				"tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-				"{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,"
-				"%26,%27,%28,%29,%30,%31}, [%32];"
-				: "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-				  "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
-				  "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
-				  "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
-				  "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-				: "r"(accumulators + ((quarter * 32u) << 16) + m * PREFILL_COLUMNS + column)
-				: "memory");
-			asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-			uint4 *const to = reinterpret_cast<uint4 *>(
-				staging + ((uint64_t)m * EXL3_PREFILL_TILE_ROWS + quarter * 32u + lane) * EXL3_PREFILL_STAGING_ROW +
-				column);
+		uint32_t r[32];
+		asm volatile(
+			"tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+			"{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,"
+			"%26,%27,%28,%29,%30,%31}, [%32];"
+			: "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+			  "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+			  "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]),
+			  "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]),
+			  "=r"(r[30]), "=r"(r[31])
+			: "r"(accumulators + ((quarter * 32u) << 16) + (m * PREFILL_GROUPS + g) * PREFILL_COLUMNS + column)
+			: "memory");
+		asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+		uint4 *const to = reinterpret_cast<uint4 *>(
+			staging + ((uint64_t)m * EXL3_PREFILL_TILE_ROWS + quarter * 32u + lane) * EXL3_PREFILL_STAGING_ROW +
+			column);
 #pragma unroll
-			for (uint32_t index = 0; index < 8; index++)
-				to[index] = make_uint4(r[4 * index], r[4 * index + 1], r[4 * index + 2], r[4 * index + 3]);
-		}
+		for (uint32_t index = 0; index < 8; index++)
+			to[index] = make_uint4(r[4 * index], r[4 * index + 1], r[4 * index + 2], r[4 * index + 3]);
 	}
 	tensor_fence_before();
 	decode_sync();
@@ -466,15 +537,18 @@ __device__ __forceinline__ void prefill_stage_out(uint32_t accumulators, uint32_
 
 /* All threads, at the end of a product CTA: wait (bounded) for what a failed CTA still has in flight, then free the
  * tensor memory. */
-template <uint32_t MATRICES, uint32_t STAGES> __device__ __forceinline__ void prefill_release(prefill_shared *shared)
+template <uint32_t MATRICES> __device__ __forceinline__ void prefill_release(prefill_shared *shared)
 {
 	tensor_fence_before();
 	__syncthreads();
 	if (shared->failed != 0 && threadIdx.x == 0) {
-		const uint32_t armed = shared->armed;
-		for (uint32_t back = 0; back < STAGES && back < armed; back++) {
-			const uint32_t block = armed - 1u - back;
-			(void)barrier_wait(&shared->full[block % STAGES], (block / STAGES) & 1u);
+		for (uint32_t back = 0; back < EXL3_PREFILL_A_STAGES && back < shared->armed_a; back++) {
+			const uint32_t block = shared->armed_a - 1u - back;
+			(void)barrier_wait(&shared->a_full[block % EXL3_PREFILL_A_STAGES], (block / EXL3_PREFILL_A_STAGES) & 1u);
+		}
+		for (uint32_t back = 0; back < EXL3_PREFILL_T_STAGES && back < shared->armed_t; back++) {
+			const uint32_t block = shared->armed_t - 1u - back;
+			(void)barrier_wait(&shared->t_full[block % EXL3_PREFILL_T_STAGES], (block / EXL3_PREFILL_T_STAGES) & 1u);
 		}
 		if (shared->issued != 0)
 			(void)barrier_wait(&shared->done, 0u);
@@ -484,7 +558,7 @@ template <uint32_t MATRICES, uint32_t STAGES> __device__ __forceinline__ void pr
 		tensor_fence_after();
 		__syncwarp();
 		asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(shared->tensor_memory),
-			     "r"(MATRICES * PREFILL_COLUMNS)
+			     "r"(MATRICES * PREFILL_GROUPS * PREFILL_COLUMNS)
 			     : "memory");
 	}
 }
@@ -516,7 +590,8 @@ __device__ __forceinline__ void prefill_gate_up(const struct exl3_prefill_record
 						unsigned char *dynamic_shared, prefill_shared *shared)
 {
 	const uint32_t H = record.input_size, I = prefill_inner_of(record, tile.tile.expert);
-	const uint32_t group = blockIdx.x, tile_index = blockIdx.y;
+	const uint32_t first_group = blockIdx.x * PREFILL_GROUPS, tile_index = blockIdx.y;
+	const uint32_t groups = min(PREFILL_GROUPS, I / EXL3_TRANSFORM - first_group);
 	const uint32_t lane = threadIdx.x % EXL3_WARP, warp = threadIdx.x / EXL3_WARP;
 	const unsigned char *const matrices[2] = { arena + tile.gate, arena + tile.up };
 	const uint64_t tile_bytes = (uint64_t)(H / EXL3_PREFILL_BLOCK_INPUTS) * EXL3_PREFILL_BLOCK_BYTES;
@@ -524,47 +599,50 @@ __device__ __forceinline__ void prefill_gate_up(const struct exl3_prefill_record
 		view.workspace + view.parts.gate_up_operands + tile_index * tile_bytes,
 		view.workspace + view.parts.gate_up_operands + ((uint64_t)view.parts.tile_capacity + tile_index) * tile_bytes
 	};
-	const bool complete = prefill_products<BX2, 2, EXL3_PREFILL_GATE_UP_STAGES>(
-		matrices, I, group, operands, H / EXL3_PREFILL_BLOCK_INPUTS, dynamic_shared, shared);
-	if (warp >= 2u && complete) {
+	const bool complete = prefill_products<BX2, 2, EXL3_PREFILL_GATE_UP_STEPS>(
+		matrices, I, first_group, groups, operands, H / (EXL3_PREFILL_GATE_UP_STEPS * EXL3_TILE), dynamic_shared,
+		shared);
+	if (warp >= PREFILL_FIRST_DECODE_WARP && complete) {
 		float *const staging = reinterpret_cast<float *>(dynamic_shared);
-		prefill_stage_out(shared->tensor_memory, 2, staging);
-		const uint32_t channel = group * EXL3_TRANSFORM + lane * 4u;
 		const uint64_t codes = exl3_code_bytes(H, I, BX2);
-		float gate_scale[4], up_scale[4], down_scale[4];
-		load_half4(reinterpret_cast<const __half *>(arena + tile.gate + codes) + H + channel, gate_scale);
-		load_half4(reinterpret_cast<const __half *>(arena + tile.up + codes) + H + channel, up_scale);
-		load_half4(reinterpret_cast<const __half *>(arena + tile.down + exl3_code_bytes(I, H, BX2)) + channel,
-			   down_scale);
-		unsigned char *const blocks =
-			view.workspace + view.parts.down_operands +
-			((uint64_t)tile_index * (view.widest / EXL3_PREFILL_BLOCK_INPUTS) +
-			 channel / EXL3_PREFILL_BLOCK_INPUTS) *
-				EXL3_PREFILL_BLOCK_BYTES;
-		for (uint32_t row = warp - 2u; row < tile.tile.row_count; row += PREFILL_DECODE_WARPS) {
-			const float4 gate_raw =
-				*reinterpret_cast<const float4 *>(staging + row * EXL3_PREFILL_STAGING_ROW + lane * 4u);
-			const float4 up_raw = *reinterpret_cast<const float4 *>(
-				staging + (EXL3_PREFILL_TILE_ROWS + row) * EXL3_PREFILL_STAGING_ROW + lane * 4u);
-			float gate[4] = { gate_raw.x, gate_raw.y, gate_raw.z, gate_raw.w };
-			float up[4] = { up_raw.x, up_raw.y, up_raw.z, up_raw.w };
-			hadamard128_warp(gate, lane);
-			hadamard128_warp(up, lane);
-			float hidden[4], fed[4];
-			exl3_swiglu4(gate, up, gate_scale, up_scale, record.activation_limit, hidden);
+		for (uint32_t g = 0; g < groups; g++) {
+			prefill_stage_out(shared->tensor_memory, 2, g, staging);
+			const uint32_t channel = (first_group + g) * EXL3_TRANSFORM + lane * 4u;
+			float gate_scale[4], up_scale[4], down_scale[4];
+			load_half4(reinterpret_cast<const __half *>(arena + tile.gate + codes) + H + channel, gate_scale);
+			load_half4(reinterpret_cast<const __half *>(arena + tile.up + codes) + H + channel, up_scale);
+			load_half4(reinterpret_cast<const __half *>(arena + tile.down + exl3_code_bytes(I, H, BX2)) + channel,
+				   down_scale);
+			unsigned char *const blocks = view.workspace + view.parts.down_operands +
+						      ((uint64_t)tile_index * (view.widest / EXL3_PREFILL_BLOCK_INPUTS) +
+						       channel / EXL3_PREFILL_BLOCK_INPUTS) *
+							      EXL3_PREFILL_BLOCK_BYTES;
+			for (uint32_t row = warp - PREFILL_FIRST_DECODE_WARP; row < tile.tile.row_count; row += PREFILL_DECODE_WARPS) {
+				const float4 gate_raw =
+					*reinterpret_cast<const float4 *>(staging + row * EXL3_PREFILL_STAGING_ROW + lane * 4u);
+				const float4 up_raw = *reinterpret_cast<const float4 *>(
+					staging + (EXL3_PREFILL_TILE_ROWS + row) * EXL3_PREFILL_STAGING_ROW + lane * 4u);
+				float gate[4] = { gate_raw.x, gate_raw.y, gate_raw.z, gate_raw.w };
+				float up[4] = { up_raw.x, up_raw.y, up_raw.z, up_raw.w };
+				hadamard128_warp(gate, lane);
+				hadamard128_warp(up, lane);
+				float hidden[4], fed[4];
+				exl3_swiglu4(gate, up, gate_scale, up_scale, record.activation_limit, hidden);
 #pragma unroll
-			for (uint32_t i = 0; i < 4; i++)
-				fed[i] = __fmul_rn(hidden[i], down_scale[i]);
-			hadamard128_warp(fed, lane);
+				for (uint32_t i = 0; i < 4; i++)
+					fed[i] = __fmul_rn(hidden[i], down_scale[i]);
+				hadamard128_warp(fed, lane);
 #pragma unroll
-			for (uint32_t i = 0; i < 4; i++)
-				fed[i] = __fmul_rn(fed[i], EXL3_NORMALIZATION);
-			store_half4(reinterpret_cast<__half *>(blocks +
-							       prefill_block_byte(row, channel % EXL3_PREFILL_BLOCK_INPUTS)),
-				    fed);
+				for (uint32_t i = 0; i < 4; i++)
+					fed[i] = __fmul_rn(fed[i], EXL3_NORMALIZATION);
+				store_half4(reinterpret_cast<__half *>(
+						    blocks + prefill_block_byte(row, channel % EXL3_PREFILL_BLOCK_INPUTS)),
+					    fed);
+			}
+			decode_sync(); /* the staging rows are read: the next group may overwrite them */
 		}
 	}
-	prefill_release<2, EXL3_PREFILL_GATE_UP_STAGES>(shared);
+	prefill_release<2>(shared);
 }
 
 template <uint32_t BX2>
@@ -573,36 +651,42 @@ __device__ __forceinline__ void prefill_down(const struct exl3_prefill_record &r
 					     unsigned char *dynamic_shared, prefill_shared *shared)
 {
 	const uint32_t H = record.input_size, I = prefill_inner_of(record, tile.tile.expert);
-	const uint32_t group = blockIdx.x, tile_index = blockIdx.y;
+	const uint32_t first_group = blockIdx.x * PREFILL_GROUPS, tile_index = blockIdx.y;
+	const uint32_t groups = min(PREFILL_GROUPS, H / EXL3_TRANSFORM - first_group);
 	const uint32_t lane = threadIdx.x % EXL3_WARP, warp = threadIdx.x / EXL3_WARP;
 	const unsigned char *const matrices[1] = { arena + tile.down };
 	const unsigned char *const operands[1] = { view.workspace + view.parts.down_operands +
 						   (uint64_t)tile_index * (view.widest / EXL3_PREFILL_BLOCK_INPUTS) *
 							   EXL3_PREFILL_BLOCK_BYTES };
-	const bool complete = prefill_products<BX2, 1, EXL3_PREFILL_DOWN_STAGES>(
-		matrices, H, group, operands, I / EXL3_PREFILL_BLOCK_INPUTS, dynamic_shared, shared);
-	if (warp >= 2u && complete) {
+	const bool complete = prefill_products<BX2, 1, EXL3_PREFILL_DOWN_STEPS>(
+		matrices, H, first_group, groups, operands, I / (EXL3_PREFILL_DOWN_STEPS * EXL3_TILE), dynamic_shared, shared);
+	if (warp >= PREFILL_FIRST_DECODE_WARP && complete) {
 		float *const staging = reinterpret_cast<float *>(dynamic_shared);
-		prefill_stage_out(shared->tensor_memory, 1, staging);
-		const uint32_t channel = group * EXL3_TRANSFORM + lane * 4u;
-		float scale[4];
-		load_half4(reinterpret_cast<const __half *>(arena + tile.down + exl3_code_bytes(I, H, BX2)) + I + channel,
-			   scale);
 		float *const outputs = reinterpret_cast<float *>(arena + record.pair_output_offset);
-		for (uint32_t row = warp - 2u; row < tile.tile.row_count; row += PREFILL_DECODE_WARPS) {
-			const struct exl3_prefill_entry entry = tile.entries[row];
-			const float4 raw =
-				*reinterpret_cast<const float4 *>(staging + row * EXL3_PREFILL_STAGING_ROW + lane * 4u);
-			float v[4] = { raw.x, raw.y, raw.z, raw.w };
-			hadamard128_warp(v, lane);
+		for (uint32_t g = 0; g < groups; g++) {
+			prefill_stage_out(shared->tensor_memory, 1, g, staging);
+			const uint32_t channel = (first_group + g) * EXL3_TRANSFORM + lane * 4u;
+			float scale[4];
+			load_half4(reinterpret_cast<const __half *>(arena + tile.down + exl3_code_bytes(I, H, BX2)) + I +
+					   channel,
+				   scale);
+			for (uint32_t row = warp - PREFILL_FIRST_DECODE_WARP; row < tile.tile.row_count; row += PREFILL_DECODE_WARPS) {
+				const struct exl3_prefill_entry entry = tile.entries[row];
+				const float4 raw =
+					*reinterpret_cast<const float4 *>(staging + row * EXL3_PREFILL_STAGING_ROW + lane * 4u);
+				float v[4] = { raw.x, raw.y, raw.z, raw.w };
+				hadamard128_warp(v, lane);
 #pragma unroll
-			for (uint32_t i = 0; i < 4; i++)
-				v[i] = __fmul_rn(__fmul_rn(__fmul_rn(v[i], EXL3_NORMALIZATION), scale[i]), entry.route_weight);
-			*reinterpret_cast<float4 *>(outputs + (uint64_t)entry.pair * H + channel) =
-				make_float4(v[0], v[1], v[2], v[3]);
+				for (uint32_t i = 0; i < 4; i++)
+					v[i] = __fmul_rn(__fmul_rn(__fmul_rn(v[i], EXL3_NORMALIZATION), scale[i]),
+							 entry.route_weight);
+				*reinterpret_cast<float4 *>(outputs + (uint64_t)entry.pair * H + channel) =
+					make_float4(v[0], v[1], v[2], v[3]);
+			}
+			decode_sync();
 		}
 	}
-	prefill_release<1, EXL3_PREFILL_DOWN_STAGES>(shared);
+	prefill_release<1>(shared);
 }
 
 #define PREFILL_WIDTH_SWITCH(function)                                                     \
@@ -623,7 +707,7 @@ __device__ __forceinline__ void prefill_down(const struct exl3_prefill_record &r
 		break;                                                                     \
 	}
 
-/* grid (widest I / 128, tile capacity) x 576 */
+/* grid (ceil(widest I / 256), tile capacity) x 608 */
 extern "C" __global__ void __launch_bounds__(EXL3_PREFILL_GEMM_THREADS, 1)
 	exl3_prefill_gate_up(struct exl3_prefill_record record, unsigned char *arena)
 {
@@ -636,20 +720,18 @@ extern "C" __global__ void __launch_bounds__(EXL3_PREFILL_GEMM_THREADS, 1)
 	    blockIdx.y >= reinterpret_cast<const uint32_t *>(view.workspace + view.parts.counts)[view.experts])
 		return;
 	const prefill_tile_view tile = prefill_tile_of(record, arena, view, blockIdx.y);
-	if (blockIdx.x >= prefill_inner_of(record, tile.tile.expert) / EXL3_TRANSFORM)
+	if (blockIdx.x * PREFILL_GROUPS >= prefill_inner_of(record, tile.tile.expert) / EXL3_TRANSFORM)
 		return; /* the grid is as wide as the widest expert */
 	PREFILL_WIDTH_SWITCH(prefill_gate_up)
 }
 
-/* grid (H / 128, tile capacity) x 576 */
+/* grid (ceil(H / 256), tile capacity) x 608 */
 extern "C" __global__ void __launch_bounds__(EXL3_PREFILL_GEMM_THREADS, 1)
 	exl3_prefill_down(struct exl3_prefill_record record, unsigned char *arena)
 {
 	extern __shared__ __align__(1024) unsigned char dynamic_shared[];
 	__shared__ prefill_shared shared;
 	const prefill_view view = prefill_view_of(record, arena);
-	/* once a wait has run out (the flag is never cleared while the kernel file stays loaded), later CTAs do not
-	 * queue up behind the same fault: the host reads the flag and rejects the result */
 	if (*reinterpret_cast<volatile unsigned int *>(&exl3_wait_expired) != 0u ||
 	    blockIdx.y >= reinterpret_cast<const uint32_t *>(view.workspace + view.parts.counts)[view.experts])
 		return;
