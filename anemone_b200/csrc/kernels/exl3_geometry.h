@@ -48,6 +48,7 @@ AB_INLINE uint32_t exl3_moe_splits(uint32_t inputs)
 
 /* ---- prefill (kernel_exl3_prefill) ---- */
 #define EXL3_PREFILL_GEMM_THREADS 608u /* two copy warps, an issuing warp, sixteen decode warps */
+#define EXL3_PREFILL_OPERAND_PARTS 4u /* an operand CTA takes a quarter of a tile's rows */
 #define EXL3_PREFILL_GATE_UP_STEPS 2u /* steps of 16 inputs of one stage: two matrices */
 #define EXL3_PREFILL_DOWN_STEPS 4u /* one matrix */
 /* ring depths: operand blocks (mostly from L2), decoded weights (made on the SM), trellis rows (from HBM) */

@@ -184,20 +184,28 @@ __device__ __forceinline__ uint32_t prefill_block_byte(uint32_t row, uint32_t in
 	return (input / 8u) * 2048u + (row / 8u) * 128u + (row % 8u) * 16u + (input % 8u) * 2u;
 }
 
-/* grid (tile capacity, ceil(H / 128 / 4), 2) x 128: x . suh, Hadamard, FP16 operands of gate (z = 0) and up (z = 1) */
+/* grid (tile capacity, ceil(H / 128 / 4) x EXL3_PREFILL_OPERAND_PARTS, 2) x 128: x . suh, Hadamard, FP16 operands of
+ * gate (z = 0) and up (z = 1). A warp takes one 128-channel block of a quarter of the tile's rows, eight rows at a time:
+ * the eight transforms are independent, and their FP16 rows go through shared memory so that every store to the
+ * operand blocks is a whole 128-byte piece (eight rows x eight inputs). Rows beyond the tile's count are written as
+ * zeros. */
+#define OPERAND_ROW_BYTES 272u /* 128 FP16 and a pad that spreads eight rows over the banks */
 extern "C" __global__ void __launch_bounds__(EXL3_TRANSFORM_THREADS)
 	exl3_prefill_operands(struct exl3_prefill_record record, unsigned char *arena)
 {
+	__shared__ __align__(16) unsigned char staged[EXL3_TRANSFORM_WARPS][8u * OPERAND_ROW_BYTES];
 	const prefill_view view = prefill_view_of(record, arena);
 	const uint32_t tile_index = blockIdx.x;
 	if (tile_index >= reinterpret_cast<const uint32_t *>(view.workspace + view.parts.counts)[view.experts])
 		return;
 	const struct exl3_prefill_tile tile =
 		reinterpret_cast<const struct exl3_prefill_tile *>(view.workspace + view.parts.tiles)[tile_index];
-	const uint32_t lane = threadIdx.x % EXL3_WARP;
-	const uint32_t block = blockIdx.y * EXL3_TRANSFORM_WARPS + threadIdx.x / EXL3_WARP;
+	const uint32_t lane = threadIdx.x % EXL3_WARP, warp = threadIdx.x / EXL3_WARP;
+	const uint32_t part = blockIdx.y % EXL3_PREFILL_OPERAND_PARTS;
+	const uint32_t block = blockIdx.y / EXL3_PREFILL_OPERAND_PARTS * EXL3_TRANSFORM_WARPS + warp;
 	const uint32_t H = record.input_size;
-	if (block >= H / EXL3_TRANSFORM)
+	constexpr uint32_t part_rows = EXL3_PREFILL_TILE_ROWS / EXL3_PREFILL_OPERAND_PARTS;
+	if (block >= H / EXL3_TRANSFORM || part * part_rows >= tile.row_count)
 		return;
 	const uint32_t channel = block * EXL3_TRANSFORM + lane * 4u;
 	const uint32_t bits_x2 = exl3_bits_x2(reinterpret_cast<const uint32_t *>(arena + record.widths_offset)[tile.expert]);
@@ -212,24 +220,46 @@ extern "C" __global__ void __launch_bounds__(EXL3_TRANSFORM_THREADS)
 		reinterpret_cast<const struct exl3_prefill_entry *>(view.workspace + view.parts.entries) +
 		(uint64_t)tile.expert * record.row_capacity + tile.first_entry;
 	const __nv_bfloat16 *const input = reinterpret_cast<const __nv_bfloat16 *>(arena + record.input_offset);
+	/* the two operand blocks (64 inputs each) this warp's 128 channels fall in */
 	unsigned char *const blocks = view.workspace + view.parts.gate_up_operands +
 				      (((uint64_t)blockIdx.z * view.parts.tile_capacity + tile_index) *
 					       (H / EXL3_PREFILL_BLOCK_INPUTS) +
-				       channel / EXL3_PREFILL_BLOCK_INPUTS) *
+				       2u * block) *
 					      EXL3_PREFILL_BLOCK_BYTES;
-	for (uint32_t row = 0; row < tile.row_count; row++) {
-		const uint32_t source_row = entries[row].pair / view.pairs_per_row;
-		const uint2 raw = *reinterpret_cast<const uint2 *>(input + (uint64_t)source_row * H + channel);
-		float v[4] = { __uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xFFFF0000u),
-			       __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xFFFF0000u) };
+	unsigned char *const mine = staged[warp];
+	for (uint32_t first = part * part_rows; first < (part + 1u) * part_rows && first < tile.row_count; first += 8u) {
+		uint2 raw[8];
 #pragma unroll
-		for (uint32_t i = 0; i < 4; i++)
-			v[i] = __fmul_rn(v[i], scale[i]);
-		hadamard128_warp(v, lane);
+		for (uint32_t r = 0; r < 8; r++) {
+			raw[r] = make_uint2(0u, 0u);
+			if (first + r < tile.row_count) {
+				const uint32_t source_row = entries[first + r].pair / view.pairs_per_row;
+				raw[r] = *reinterpret_cast<const uint2 *>(input + (uint64_t)source_row * H + channel);
+			}
+		}
 #pragma unroll
-		for (uint32_t i = 0; i < 4; i++)
-			v[i] = __fmul_rn(v[i], EXL3_NORMALIZATION);
-		store_half4(reinterpret_cast<__half *>(blocks + prefill_block_byte(row, channel % EXL3_PREFILL_BLOCK_INPUTS)), v);
+		for (uint32_t r = 0; r < 8; r++) {
+			float v[4] = { __uint_as_float(raw[r].x << 16), __uint_as_float(raw[r].x & 0xFFFF0000u),
+				       __uint_as_float(raw[r].y << 16), __uint_as_float(raw[r].y & 0xFFFF0000u) };
+#pragma unroll
+			for (uint32_t i = 0; i < 4; i++)
+				v[i] = __fmul_rn(v[i], scale[i]);
+			hadamard128_warp(v, lane);
+#pragma unroll
+			for (uint32_t i = 0; i < 4; i++)
+				v[i] = __fmul_rn(v[i], EXL3_NORMALIZATION);
+			store_half4(reinterpret_cast<__half *>(mine + r * OPERAND_ROW_BYTES + lane * 8u), v);
+		}
+		__syncwarp();
+		/* piece p (eight inputs) of the eight rows: 128 contiguous bytes of the block; lane = 8 (p % 4) + row */
+#pragma unroll
+		for (uint32_t turn = 0; turn < 4; turn++) {
+			const uint32_t piece = turn * 4u + lane / 8u, row = lane % 8u;
+			const uint4 value = *reinterpret_cast<const uint4 *>(mine + row * OPERAND_ROW_BYTES + piece * 16u);
+			*reinterpret_cast<uint4 *>(blocks + (piece / 8u) * EXL3_PREFILL_BLOCK_BYTES + (piece % 8u) * 2048u +
+						   (first / 8u) * 128u + row * 16u) = value;
+		}
+		__syncwarp();
 	}
 }
 
@@ -739,24 +769,29 @@ extern "C" __global__ void __launch_bounds__(EXL3_PREFILL_GEMM_THREADS, 1)
 	PREFILL_WIDTH_SWITCH(prefill_down)
 }
 
-/* grid (ceil(H / 128), row capacity) x 128: FP32 row sums over the row's local pairs from +0 in ascending slot order */
+/* grid (ceil(H / 512), row capacity) x 128: FP32 row sums over the row's local pairs from +0 in ascending slot order,
+ * four channels a thread */
 extern "C" __global__ void __launch_bounds__(EXL3_ROW_SUM_THREADS)
 	exl3_prefill_row_sum(struct exl3_prefill_record record, unsigned char *arena)
 {
 	const struct step_block step = *reinterpret_cast<const struct step_block *>(arena + record.step_offset);
-	const uint32_t channel = blockIdx.x * blockDim.x + threadIdx.x;
+	const uint32_t channel = (blockIdx.x * blockDim.x + threadIdx.x) * 4u;
 	const uint64_t row = blockIdx.y;
 	if (channel >= record.input_size || row >= min(step.row_count, record.row_capacity))
 		return;
 	const uint32_t width = record.input_size, slots = record.picks + record.shared_count;
 	const float *const pairs = reinterpret_cast<const float *>(arena + record.pair_output_offset);
 	const uint32_t *const picked = reinterpret_cast<const uint32_t *>(arena + record.picks_offset) + row * record.picks;
-	float sum = 0.0f;
+	float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 	for (uint32_t slot = 0; slot < slots; slot++) {
 		/* a routed pair counts where its expert is held; an always-on pair everywhere it exists */
 		if (slot < record.picks && picked[slot] - record.local_first >= record.local_count)
 			continue;
-		sum = __fadd_rn(sum, pairs[(row * slots + slot) * width + channel]);
+		const float4 value = *reinterpret_cast<const float4 *>(pairs + (row * slots + slot) * width + channel);
+		sum.x = __fadd_rn(sum.x, value.x);
+		sum.y = __fadd_rn(sum.y, value.y);
+		sum.z = __fadd_rn(sum.z, value.z);
+		sum.w = __fadd_rn(sum.w, value.w);
 	}
-	reinterpret_cast<float *>(arena + record.row_output_offset)[row * width + channel] = sum;
+	*reinterpret_cast<float4 *>(reinterpret_cast<float *>(arena + record.row_output_offset) + row * width + channel) = sum;
 }
