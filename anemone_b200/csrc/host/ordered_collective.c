@@ -108,10 +108,10 @@ result_status ordered_collective_host(const float *const *inputs, float *const *
 /* The checks the FP32 collectives and the bfloat16 reduction share: ranks, region and slots, peer table, step block.
  * arrays: the offsets inside a parity slot (each `bytes` long), pairwise disjoint, behind the signal lines. */
 static bool collective_is_valid(const struct ordered_collective_arguments *arguments, uint64_t capacity,
-				const uint64_t *arrays, uint32_t array_count, uint64_t bytes)
+				const uint64_t *arrays, uint32_t array_count, uint64_t bytes, uint32_t maximum_elements)
 {
 	const uint64_t table_bytes = (uint64_t)arguments->rank_count * sizeof(struct ordered_collective_peer);
-	if (arguments->element_count == 0 || arguments->element_count > ORDERED_COLLECTIVE_MAXIMUM_ELEMENTS ||
+	if (arguments->element_count == 0 || arguments->element_count > maximum_elements ||
 	    arguments->rank_count == 0 || arguments->rank_count > ORDERED_COLLECTIVE_MAXIMUM_RANKS ||
 	    arguments->rank >= arguments->rank_count || arguments->reserved_zero != 0 ||
 	    arguments->deadline_cycles == 0 || arguments->region_offset % ORDERED_COLLECTIVE_LINE_BYTES != 0 ||
@@ -146,7 +146,7 @@ result_status ordered_collective_prepare(const struct ordered_collective_descrip
 	const struct ordered_collective_arguments *const arguments = &description->arguments;
 	const uint64_t arrays[3] = { arguments->input_offset, arguments->output_offset, arguments->scratch_offset };
 	if (!collective_is_valid(arguments, description->arena_byte_count, arrays, 3,
-				 (uint64_t)arguments->element_count * VALUE_BYTES))
+				 (uint64_t)arguments->element_count * VALUE_BYTES, ORDERED_COLLECTIVE_MAXIMUM_ELEMENTS))
 		return STATUS_INVALID_ARGUMENT;
 	prepare_launch_fill(launch_out, kernels->handles[description->operation], 1, 1, 1, ORDERED_COLLECTIVE_THREADS, 0,
 			    arguments, sizeof(*arguments));
@@ -163,12 +163,13 @@ result_status ordered_reduce_bf16_prepare(const struct ordered_reduce_bf16_descr
 	const struct ordered_reduce_bf16_arguments *const reduce = &description->reduce;
 	const struct ordered_collective_arguments *const collective = &reduce->collective;
 	const uint64_t capacity = description->arena_byte_count;
-	if (reduce->reserved_zero != 0 || reduce->width == 0 || reduce->width % 4u != 0 ||
+	if (reduce->mode > ORDERED_REDUCE_OWNER_RUNS || reduce->width == 0 || reduce->width % 4u != 0 ||
 	    description->row_capacity == 0 || description->row_capacity > 65535u || description->pairs_per_row == 0 ||
 	    (uint64_t)description->row_capacity * reduce->width != collective->element_count)
 		return STATUS_INVALID_ARGUMENT;
 	const uint64_t input_bytes = (uint64_t)collective->element_count * VALUE_BYTES;
-	if (!collective_is_valid(collective, capacity, &collective->input_offset, 1, input_bytes))
+	if (!collective_is_valid(collective, capacity, &collective->input_offset, 1, input_bytes,
+				 ORDERED_B200_MAXIMUM_ELEMENTS))
 		return STATUS_INVALID_ARGUMENT;
 	const uint64_t region_bytes = collective->parity_stride * ORDERED_COLLECTIVE_SLOTS;
 	const struct checked_range ranges[5] = {
@@ -197,8 +198,12 @@ result_status ordered_reduce_bf16_prepare(const struct ordered_reduce_bf16_descr
 									      .pairs_per_row = description->pairs_per_row };
 	const uint32_t vectors = reduce->width / 4u;
 	uint32_t blocks = (collective->element_count / 4u + ORDERED_COLLECTIVE_THREADS - 1u) / ORDERED_COLLECTIVE_THREADS;
-	if (blocks > ORDERED_B200_MAXIMUM_BLOCKS)
-		blocks = ORDERED_B200_MAXIMUM_BLOCKS;
+	/* few rows: a small grid, whose last block is found quickly; many rows: enough blocks to fill the card */
+	const uint32_t most = collective->element_count > ORDERED_COLLECTIVE_MAXIMUM_ELEMENTS ?
+				      ORDERED_B200_MAXIMUM_BLOCKS_LARGE :
+				      ORDERED_B200_MAXIMUM_BLOCKS;
+	if (blocks > most)
+		blocks = most;
 	struct kernel_launch launches[ORDERED_REDUCE_BF16_LAUNCHES];
 	prepare_launch_fill(&launches[0], publish, (vectors + 127u) / 128u, description->row_capacity, 1, 128, 0,
 			    &publish_arguments, sizeof(publish_arguments));

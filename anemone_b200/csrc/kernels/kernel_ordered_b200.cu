@@ -6,9 +6,10 @@
  *   ordered_row_sum_publish  grid (ceil(width / 512), row capacity) x 128: waits until every rank has finished
  *       reading this slot's previous use (their DONE lines), writes this rank's FP32 row sums (slots added from +0 in
  *       ascending order) straight into its input array of the slot, and the last block to finish publishes READY.
- *   ordered_reduce_bf16      grid (up to 64 blocks) x 256: waits for every rank's READY, pulls every rank's rows by
- *       128-bit peer loads, adds them in rank order, rounds once, stores bfloat16 [rows][width] at the arena offset
- *       output_offset; the last block to finish publishes DONE.
+ *   ordered_reduce_bf16      grid (up to 64 blocks, or up to 592 for many rows) x 256: waits for every rank's READY,
+ *       pulls every rank's rows by 128-bit peer loads, adds them in rank order, rounds once, stores bfloat16
+ *       [rows][width] at the arena offset output_offset; the last block to finish publishes DONE. With owner runs
+ *       (mode 1) a rank adds only its run of the vectors and stores the result into every rank's memory.
  * Both read the live row count and the sequence from the step block. The read-complete barrier of the FP32
  * collectives is moved from the end of a step to the next refill of the same slot (two steps later), where it costs
  * nothing; the slot's input must therefore only ever be written by ordered_row_sum_publish.
@@ -89,18 +90,36 @@ extern "C" __global__ void __launch_bounds__(ORDERED_COLLECTIVE_THREADS)
 	unsigned char *const status = arena + arguments.status_offset;
 	unsigned char *const mine = ordered_slot(collective, arena, collective.rank, sequence);
 	const bool alive = ordered_wait_all(collective, arena, ORDERED_READY_PHASE, sequence, sequence, true, status, &verdict);
+	const bool owner_runs = arguments.mode == ORDERED_REDUCE_OWNER_RUNS;
 	if (alive) {
 		const uint32_t live = min(step.row_count * arguments.width, collective.element_count);
 		const uint32_t vectors = live / 4u;
 		const float *inputs[ORDERED_COLLECTIVE_MAXIMUM_RANKS];
+		uint2 *outputs[ORDERED_COLLECTIVE_MAXIMUM_RANKS];
 #pragma unroll
-		for (uint32_t rank = 0; rank < ORDERED_COLLECTIVE_MAXIMUM_RANKS; rank++)
+		for (uint32_t rank = 0; rank < ORDERED_COLLECTIVE_MAXIMUM_RANKS; rank++) {
 			inputs[rank] = rank < collective.rank_count ?
 					       reinterpret_cast<const float *>(ordered_slot(collective, arena, rank, sequence) +
 									       collective.input_offset) :
 					       nullptr;
-		uint2 *const output = reinterpret_cast<uint2 *>(arena + collective.output_offset);
-		for (uint32_t vector = blockIdx.x * blockDim.x + threadIdx.x; vector < vectors;
+			/* every rank keeps its result at the same arena offset */
+			outputs[rank] = rank == collective.rank ? reinterpret_cast<uint2 *>(arena + collective.output_offset) :
+					rank < collective.rank_count ?
+								  reinterpret_cast<uint2 *>(
+									  reinterpret_cast<unsigned char *>(
+										  ordered_peers(collective, arena)[rank].arena_address) +
+									  collective.output_offset) :
+								  nullptr;
+		}
+		uint2 *const own = reinterpret_cast<uint2 *>(arena + collective.output_offset);
+		/* this rank's run of vectors */
+		uint32_t first = 0, end = vectors;
+		if (owner_runs) {
+			const uint32_t share = vectors / collective.rank_count, longer = vectors % collective.rank_count;
+			first = collective.rank * share + min(collective.rank, longer);
+			end = first + share + (collective.rank < longer ? 1u : 0u);
+		}
+		for (uint32_t vector = first + blockIdx.x * blockDim.x + threadIdx.x; vector < end;
 		     vector += gridDim.x * blockDim.x) {
 			float4 values[ORDERED_COLLECTIVE_MAXIMUM_RANKS];
 #pragma unroll
@@ -116,12 +135,35 @@ extern "C" __global__ void __launch_bounds__(ORDERED_COLLECTIVE_THREADS)
 					sum.z = __fadd_rn(sum.z, values[rank].z);
 					sum.w = __fadd_rn(sum.w, values[rank].w);
 				}
-			output[vector] = make_uint2(bfloat16_bits(sum.x) | bfloat16_bits(sum.y) << 16,
-						    bfloat16_bits(sum.z) | bfloat16_bits(sum.w) << 16);
+			const uint2 rounded = make_uint2(bfloat16_bits(sum.x) | bfloat16_bits(sum.y) << 16,
+							 bfloat16_bits(sum.z) | bfloat16_bits(sum.w) << 16);
+			if (owner_runs) {
+#pragma unroll
+				for (uint32_t rank = 0; rank < ORDERED_COLLECTIVE_MAXIMUM_RANKS; rank++)
+					if (rank < collective.rank_count)
+						outputs[rank][vector] = rounded;
+			} else {
+				own[vector] = rounded;
+			}
 		}
 	}
-	/* this rank has read (or given up on) every peer's slot: say so, whatever happened */
+	if (owner_runs)
+		__threadfence_system(); /* this block's peer stores, before it counts itself */
+	/* this rank has read (or given up on) every peer's slot: say so, whatever happened. With owner runs the last
+	 * block first publishes that this rank's run of the result is in every rank's memory, and waits for every
+	 * rank's run to be in this rank's. */
 	unsigned char *const done_line = mine + ORDERED_DONE_PHASE * ORDERED_COLLECTIVE_LINE_BYTES;
-	if (last_block_of_grid(done_line, &last) && threadIdx.x == 0)
-		signal_store(done_line, sequence);
+	if (last_block_of_grid(done_line, &last)) {
+		if (owner_runs) {
+			if (alive && threadIdx.x == 0) { /* a rank that gave up leaves its peers to their own deadlines */
+				__threadfence_system();
+				signal_store(mine + ORDERED_REDUCED_PHASE * ORDERED_COLLECTIVE_LINE_BYTES, sequence);
+			}
+			if (alive)
+				(void)ordered_wait_all(collective, arena, ORDERED_REDUCED_PHASE, sequence, sequence, true, status,
+						       &verdict);
+		}
+		if (threadIdx.x == 0)
+			signal_store(done_line, sequence);
+	}
 }

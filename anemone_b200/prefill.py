@@ -3,11 +3,13 @@
 Launches of one call, all from libanemone_b200.so (kernel file kernel_exl3_prefill):
     exl3_prefill_picks -> exl3_prefill_group -> exl3_prefill_tiles -> exl3_prefill_operands
     -> exl3_prefill_gate_up -> exl3_prefill_down -> exl3_prefill_row_sum
+    -> ordered_row_sum_publish -> ordered_reduce_bf16 (owner runs)
 Rows are grouped per expert into tiles of 128; each (row tile, 128 outputs) is a tensor-core contraction with the
 expert's trellis tiles decoded on the way. The result is this rank's FP32 [rows][hidden] row sums over the pairs whose
 experts it holds. A rank holds a run of the routed experts with their full intermediate width (expert parallelism) or
 all of them with a slice of the intermediate columns (tensor parallelism), and a column slice of the always-on experts;
-the ranks' rows are then summed in rank order. Nothing here computes on the host.
+the ranks' rows are then summed in rank order by the ordered reduction (each rank adds its run of the result and stores
+it into every rank's memory) and rounded once to bfloat16. Nothing here computes on the host.
 """
 import ctypes as C
 from dataclasses import dataclass
@@ -17,7 +19,7 @@ import numpy as np
 from . import api
 from . import records as R
 from . import synthetic
-from .moe import rank_columns
+from .moe import LINE, SIGNAL_BYTES, rank_columns
 
 
 @dataclass
@@ -79,6 +81,8 @@ class PrefillLayout:
         self.pairs_per_row = c.picks + self.shared_count
         assert len(widths) == self.local_experts
         layout = api.Layout()
+        self.peer_table = layout.take(16 * 32)
+        self.status = layout.take(16)
         self.step = layout.take(256)
         self.tokens = layout.take(rows * H * 2)
         self.scores = layout.take(rows * c.experts * 4)
@@ -91,6 +95,11 @@ class PrefillLayout:
         self.workspace = layout.take(self.parts.total, 1024)
         self.pair_outputs = layout.take(rows * self.pairs_per_row * H * 4)
         self.row_output = layout.take(rows * H * 4)
+        # the reduction's region (two parity slots of signal lines and this rank's FP32 rows) and its result
+        self.slot_input = SIGNAL_BYTES
+        self.parity_stride = api.align(SIGNAL_BYTES + rows * H * 4, LINE)
+        self.region = layout.take(2 * self.parity_stride, LINE)
+        self.result = layout.take(rows * H * 2)
         self.matrices = []
         for local in range(self.local_experts):
             width = int(widths[local])
@@ -102,7 +111,8 @@ class PrefillLayout:
 
 
 class PrefillLayer:
-    def __init__(self, card, config, widths, matrices, share=None):
+    def __init__(self, card, config, widths, matrices, share=None, rank=0, rank_count=1,
+                 reduce_mode=R.ORDERED_REDUCE_OWNER_RUNS):
         """widths, matrices: by LOCAL expert (the rank's routed run, then its always-on experts): stored widths and
         this rank's (gate, up, down) stored bytes."""
         self.card, self.config = card, config
@@ -110,6 +120,7 @@ class PrefillLayer:
         self.layout = L = PrefillLayout(config, self.widths, share)
         share = L.share
         assert card.arena_bytes >= L.arena_bytes
+        self.rank, self.rank_count = rank, rank_count
         self.weight_bytes = 0
         table = np.zeros((L.local_experts, 3), dtype=np.uint64)
         for local, triple in enumerate(matrices):
@@ -121,6 +132,13 @@ class PrefillLayer:
         card.upload(L.expert_table, table)
         card.upload(L.widths, self.widths)
         card.fill(L.step, 0, 256)
+        card.fill(L.peer_table, 0, 16 * 32)
+        card.fill(L.status, 0, 16)
+        card.fill(L.region, 0, 2 * L.parity_stride)
+        peers = (R.OrderedPeer * rank_count)()
+        for peer in range(rank_count):
+            peers[peer].region_offset = L.region
+        card.upload(L.peer_table, np.frombuffer(bytes(peers), dtype=np.uint8))
         c = config
         self.record = R.Exl3Prefill(L.scores, L.tokens, L.expert_table, L.widths, L.picks, L.weights, L.workspace,
                                     L.pair_outputs, L.row_output, L.step, c.hidden, share.inner, share.shared_inner,
@@ -129,8 +147,36 @@ class PrefillLayer:
         self.launches = (R.KernelLaunch * 7)()
         api.check(api.library().exl3_prefill_prepare(C.byref(self.record), card.arena_bytes, card.ops_pointer,
                                                      card.handle, self.launches), "exl3_prefill_prepare")
-        self.graph = card.graph(self.launches)
+        lib = api.library()
+        reduce = R.OrderedReduceBf16Description()
+        reduce.reduce.collective = R.OrderedCollective(L.peer_table, L.region, L.slot_input, L.result, 0, L.step,
+                                                       L.parity_stride, c.deadline_cycles, c.row_capacity * c.hidden,
+                                                       rank_count, rank, 0)
+        reduce.reduce.status_offset, reduce.reduce.width, reduce.reduce.mode = L.status, c.hidden, reduce_mode
+        # the rows are already summed over the pairs: one "pair" a row
+        reduce.pair_output_offset, reduce.arena_byte_count = L.row_output, card.arena_bytes
+        reduce.pairs_per_row, reduce.row_capacity = 1, c.row_capacity
+        lib.ordered_reduce_bf16_prepare.argtypes = [C.POINTER(R.OrderedReduceBf16Description),
+                                                    C.POINTER(api.BackendOperations), C.c_void_p,
+                                                    C.POINTER(R.KernelLaunch)]
+        self.reduce_launches = (R.KernelLaunch * 2)()
+        api.check(lib.ordered_reduce_bf16_prepare(C.byref(reduce), card.ops_pointer, card.handle,
+                                                  self.reduce_launches), "ordered_reduce_bf16_prepare")
+        self.graph = card.graph(list(self.launches) + list(self.reduce_launches))
         self.sequence = 0
+
+    def connect_local(self, layers):
+        """All ranks in this process: peer_connect every card to every card."""
+        for peer, other in enumerate(layers):
+            self.card.peer_connect(other.card, 0, self.layout.peer_table + 32 * peer)
+
+    def connect_handles(self, handles):
+        """One process per GPU: handles[r] is rank r's exported arena handle (all-gathered by the caller)."""
+        for peer, handle in enumerate(handles):
+            if peer == self.rank:
+                self.card.peer_connect(self.card, 0, self.layout.peer_table + 32 * peer)
+            else:
+                self.card.ipc_connect(handle, 0, self.layout.peer_table + 32 * peer)
 
     def load(self, tokens, scores):
         """Place one call's inputs on the card: tokens bfloat16 bits [rows][hidden], scores FP32 [rows][experts]."""
@@ -150,6 +196,17 @@ class PrefillLayer:
             raise RuntimeError("a prefill CTA gave up a bounded wait: the result is incomplete")
         H = self.config.hidden
         return self.card.download(self.layout.row_output, count * H * 4, np.float32).reshape(count, H)
+
+    def result(self, count):
+        """bfloat16 bits [count][hidden]: the ranks' rows added in rank order, of the last run."""
+        if self.card.waits_expired():
+            raise RuntimeError("a prefill CTA gave up a bounded wait: the result is incomplete")
+        status = self.card.download(self.layout.status, 16, np.uint32)
+        if status[0] != 0:
+            raise RuntimeError("ordered reduction failed: code %d (1 timed out, 2 bad sequence), phase %d, rank %d"
+                               % (status[0], status[1], status[2]))
+        H = self.config.hidden
+        return self.card.download(self.layout.result, count * H * 2, np.uint16).reshape(count, H)
 
     def step(self, tokens, scores):
         self.load(tokens, scores)

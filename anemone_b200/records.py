@@ -96,9 +96,12 @@ class OrderedCollective(C.Structure):
                 ("rank_count", C.c_uint32), ("rank", C.c_uint32), ("reserved_zero", C.c_uint32)]
 
 
+ORDERED_REDUCE_EVERY_RANK, ORDERED_REDUCE_OWNER_RUNS = 0, 1
+
+
 class OrderedReduceBf16(C.Structure):
     _fields_ = [("collective", OrderedCollective), ("status_offset", C.c_uint64), ("width", C.c_uint32),
-                ("reserved_zero", C.c_uint32)]
+                ("mode", C.c_uint32)]
 
 
 class OrderedRowSumPublish(C.Structure):

@@ -289,11 +289,21 @@ struct ordered_collective_arguments {
 #define ORDERED_STATUS_OK 0u
 #define ORDERED_STATUS_TIMED_OUT 1u
 #define ORDERED_STATUS_BAD_SEQUENCE 2u
+#define ORDERED_B200_MAXIMUM_ELEMENTS (1u << 28) /* of this reduction; the FP32 collectives keep the reference's limit */
+#define ORDERED_B200_MAXIMUM_BLOCKS_LARGE 592u
+/* mode 0: every rank adds every element itself (no second hop: the lowest latency, the choice for decode steps).
+ * mode 1: rank r adds the r-th of rank_count equal runs of four-element vectors (the first vectors % rank_count runs
+ * one vector longer) and stores the bfloat16 values into EVERY rank's result by peer stores, publishes its REDUCED
+ * line and waits for every rank's: each rank then reads 1 / rank_count of what mode 0 reads over NVLink, which is what
+ * counts for many rows (prefill). Same arithmetic, same bits. In mode 1 the result of a step must be consumed in
+ * stream order before the rank's next publish, as the graph of a layer does. */
+#define ORDERED_REDUCE_EVERY_RANK 0u
+#define ORDERED_REDUCE_OWNER_RUNS 1u
 struct ordered_reduce_bf16_arguments {
 	struct ordered_collective_arguments collective;
 	uint64_t status_offset;
 	uint32_t width; /* elements of a row */
-	uint32_t reserved_zero;
+	uint32_t mode;
 };
 
 /* B200 extension: the row sum of a rank written straight into its collective input slot of this step's parity

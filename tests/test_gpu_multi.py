@@ -138,3 +138,56 @@ def test_fp32_all_reduce_across_cards(api, oracle):
         finally:
             for card in cards:
                 card.close()
+
+
+@pytest.mark.parametrize("mode", [0, 1])
+def test_prefill_expert_parallel(api, oracle, mode):
+    """Prefill over R cards, each holding a run of the routed experts and a column slice of the always-on one; the
+    ordered reduction adds the ranks' rows (mode 1: every rank its run of the result, stored into every rank)."""
+    from anemone_b200.prefill import PrefillLayer, PrefillLayout, Share
+    for ranks in world_sizes(api):
+        config = MoeConfig(hidden=512, inner=128 * ranks, experts=8 * ranks, shared=1, picks=4, row_capacity=333)
+        rng = np.random.default_rng(500 + ranks)
+        widths = np.concatenate([synthetic.expert_widths(rng, config.experts), [3]]).astype(np.uint32)
+        matrices = [(synthetic.exl3_matrix(rng, config.hidden, config.inner, int(w)),
+                     synthetic.exl3_matrix(rng, config.hidden, config.inner, int(w)),
+                     synthetic.exl3_matrix(rng, config.inner, config.hidden, int(w))) for w in widths]
+        cards, layers = [], []
+        try:
+            for rank in range(ranks):
+                share = Share.expert_parallel(config, ranks, rank)
+                held = share.experts(config)
+                card = api.Card(rank, PrefillLayout(config, widths[held], share).arena_bytes)
+                cards.append(card)
+                local = [share.matrices(config, e, int(widths[e]), *matrices[e]) for e in held]
+                layers.append(PrefillLayer(card, config, widths[held], local, share, rank=rank, rank_count=ranks,
+                                           reduce_mode=mode))
+            for layer in layers:
+                layer.connect_local(layers)
+            for card in cards:
+                card.wait()
+            for rows in (333, 40, 333):
+                tokens = synthetic.tokens(rng, rows, config.hidden)
+                scores = rng.normal(0, 1, size=(rows, config.experts)).astype(np.float32)
+                scores[:, :3] += 1.5  # the first rank gets more pairs than the others
+                experts, weights = moe_reference.route(oracle, config, scores)
+                expected = moe_reference.rank_partial(oracle, config, widths, matrices, tokens, experts, weights, 1, 0)[0]
+                for layer in layers:  # queue every rank before waiting for any
+                    layer.load(tokens, scores)
+                for layer in layers:
+                    layer.run()
+                outputs = [layer.result(rows).reshape(-1) for layer in layers]
+                for rank in range(1, ranks):  # every rank holds the same bits
+                    assert np.array_equal(outputs[rank], outputs[0])
+                a = synthetic.from_bfloat16(outputs[0]).reshape(rows, config.hidden)
+                assert np.abs(a - expected).max() <= 2e-2
+                assert float(a.astype(np.float64).reshape(-1) @ expected.astype(np.float64).reshape(-1)) / \
+                    (np.linalg.norm(a) * np.linalg.norm(expected)) >= 0.9999
+                # bit-exact ordered reduction of the FP32 rows the ranks computed
+                partials = [layer.rows(rows).reshape(-1).copy() for layer in layers]
+                want = np.zeros(rows * config.hidden, dtype=np.uint16)
+                oracle.orc_ordered_reduce_bf16(pointer_array(partials), ranks, want.size, ptr(want, u16p))
+                assert np.array_equal(outputs[0], want)
+        finally:
+            for card in cards:
+                card.close()

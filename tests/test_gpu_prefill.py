@@ -85,6 +85,8 @@ def test_prefill_rows_match_oracle(api, oracle, rows, capacity):
             assert np.array_equal(picks, experts)  # router indices: bit-exact
             assert np.isfinite(got).all()
             assert np.abs(got - expected).max() <= MAX_ABS and cosine(got, expected) >= COSINE
+        # one rank: the reduction's result is the rank's own rows added to +0 and rounded once
+        assert np.array_equal(layer.result(rows), synthetic.to_bfloat16(np.float32(0.0) + got))
         check_tables(card, layer, config, rows, experts)
         # fewer live rows than before: stale entries and tiles of the longer call must not be used
         fewer = max(1, rows // 3)
