@@ -205,8 +205,10 @@ result_status ordered_reduce_bf16_prepare(const struct ordered_reduce_bf16_descr
 	if (blocks > most)
 		blocks = most;
 	struct kernel_launch launches[ORDERED_REDUCE_BF16_LAUNCHES];
-	prepare_launch_fill(&launches[0], publish, (vectors + 127u) / 128u, description->row_capacity, 1, 128, 0,
-			    &publish_arguments, sizeof(publish_arguments));
+	prepare_launch_fill(&launches[0], publish, (vectors + 127u) / 128u,
+			    description->row_capacity < ORDERED_B200_PUBLISH_ROW_BLOCKS ? description->row_capacity :
+											  ORDERED_B200_PUBLISH_ROW_BLOCKS,
+			    1, 128, 0, &publish_arguments, sizeof(publish_arguments));
 	prepare_launch_fill(&launches[1], sum, blocks, 1, 1, ORDERED_COLLECTIVE_THREADS, 0, reduce, sizeof(*reduce));
 	memcpy(launches_out, launches, sizeof(launches));
 	return STATUS_OK;

@@ -3,7 +3,7 @@
  * reference; the arithmetic is its owner sums', source/kernel_tp_exchange.cu:190-247: FP32 adds in ascending rank
  * order from +0, ONE rounding to bfloat16).
  *
- *   ordered_row_sum_publish  grid (ceil(width / 512), row capacity) x 128: waits until every rank has finished
+ *   ordered_row_sum_publish  grid (ceil(width / 512), up to 128 row blocks) x 128: waits until every rank has finished
  *       reading this slot's previous use (their DONE lines), writes this rank's FP32 row sums (slots added from +0 in
  *       ascending order) straight into its input array of the slot, and the last block to finish publishes READY.
  *   ordered_reduce_bf16      grid (up to 64 blocks, or up to 592 for many rows) x 256: waits for every rank's READY,
@@ -53,13 +53,15 @@ extern "C" __global__ void __launch_bounds__(128)
 	bool alive = true;
 	if (previous != 0 && previous < sequence)
 		alive = ordered_wait_all(collective, arena, ORDERED_DONE_PHASE, sequence, previous, false, nullptr, &verdict);
-	const uint32_t row = blockIdx.y;
-	if (alive && row < step.row_count) {
+	/* a block takes rows blockIdx.y, blockIdx.y + gridDim.y, ...: the grid stays small for many rows, because every
+	 * block counts itself on one counter at the end */
+	const uint32_t live_rows = min(step.row_count, collective.element_count / arguments.width);
+	const uint32_t vectors = arguments.width / 4u;
+	const uint32_t vector = blockIdx.x * blockDim.x + threadIdx.x;
+	if (alive && vector < vectors) {
 		const float4 *const pairs = reinterpret_cast<const float4 *>(arena + arguments.pair_output_offset);
 		float4 *const out = reinterpret_cast<float4 *>(mine + collective.input_offset);
-		const uint32_t vectors = arguments.width / 4u;
-		const uint32_t vector = blockIdx.x * blockDim.x + threadIdx.x;
-		if (vector < vectors) {
+		for (uint32_t row = blockIdx.y; row < live_rows; row += gridDim.y) {
 			float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 			for (uint32_t slot = 0; slot < arguments.pairs_per_row; slot++) {
 				const float4 value = pairs[((uint64_t)row * arguments.pairs_per_row + slot) * vectors + vector];

@@ -51,6 +51,8 @@ def parse():
     parser.add_argument("--experts", type=int, default=256)
     parser.add_argument("--hidden", type=int, default=4096)
     parser.add_argument("--inner", type=int, default=2048)
+    parser.add_argument("--prefill-rows", type=int, default=4096, help="0 skips the prefill part")
+    parser.add_argument("--prefill-steps", type=int, default=5)
     return parser.parse_args()
 
 
@@ -124,6 +126,130 @@ def measured_peaks():
         with open(path) as handle:
             return float(json.load(handle)["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
     return 6650.0, "fallback (6.65 TB/s, an earlier measurement on this pool)"
+
+
+def measured_tensor_peak():
+    """Dense bf16 TFLOP/s of a kernel timed alone (the burst figure)."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as handle:
+            return float(json.load(handle)["bf16_tflops"]), "measured burst (MEASURED_PEAKS.json)"
+    return 1590.0, "fallback (1.59 PFLOP/s, an earlier measurement on this pool)"
+
+
+def prefill_inputs(config, rows, index):
+    """Tokens and router scores of one prefill call: expert popularity Zipf(1.1) over a seeded order of the experts."""
+    from anemone_b200 import synthetic
+    rng = np.random.default_rng([SEED, 11, index])
+    order = np.random.default_rng([SEED, 12]).permutation(config.experts)
+    popularity = 1.0 / np.arange(1, config.experts + 1, dtype=np.float64) ** 1.1
+    bias = np.log(popularity / popularity.mean())[order]
+    scores = (rng.normal(0.0, 1.0, size=(rows, config.experts)) + bias).astype(np.float32)
+    return synthetic.tokens(rng, rows, config.hidden), scores
+
+
+def run_prefill(args, api, base, widths, draw, rank, world, local_rank, dist, barrier, maximum):
+    """cfg4: the same layer for M = 4096 rows, experts sharded over the ranks (a run of routed experts each, the
+    always-on expert by columns), Zipf(1.1) routing, tensor-core products, ordered reduction to bfloat16."""
+    from anemone_b200 import records as R
+    from anemone_b200.moe import MoeConfig
+    from anemone_b200.prefill import PrefillLayer, PrefillLayout, Share
+    rows, steps, warmup = args.prefill_rows, args.prefill_steps, 3
+    config = MoeConfig(hidden=base.hidden, inner=base.inner, experts=base.experts, shared=base.shared,
+                       picks=base.picks, row_capacity=rows)
+    share = Share.expert_parallel(config, world, rank)
+    held = share.experts(config)
+    local_widths = widths[held]
+    layout = PrefillLayout(config, local_widths, share)
+    card = api.Card(local_rank, layout.arena_bytes, staging_bytes=128 << 20)
+    matrices = (share.matrices(config, e, int(widths[e]), *draw(e)) for e in held)
+    layer = PrefillLayer(card, config, local_widths, matrices, share, rank=rank, rank_count=world)
+    if dist is None:
+        layer.connect_local([layer])
+    else:
+        handles = [None] * world
+        dist.all_gather_object(handles, card.ipc_export())
+        layer.connect_handles(handles)
+    card.wait()
+    barrier()
+    inputs = [prefill_inputs(config, rows, index) for index in range(2)]
+
+    # ---- value: tokens and scores resident; only the 16-byte step block (the reduction's sequence) goes in ----
+    layer.load(*inputs[0])
+    first = layer.sequence
+    for index in range(warmup + steps):
+        block = R.StepBlock(first + 1 + index, rows, 0)
+        card.staging_view[64 * index:64 * index + 16] = np.frombuffer(bytes(block), dtype=np.uint8)
+
+    def resident(index):
+        card.upload_async(layout.step, 64 * index, 16)
+        layer.run()
+    for index in range(warmup):
+        resident(index)
+    card.wait()
+    barrier()
+    launches_before = card.launch_count()
+    card.measure_begin()
+    for index in range(warmup, warmup + steps):
+        resident(index)
+    card.measure_end()
+    device_ms = maximum(card.measure_elapsed_us() / 1000.0) / steps
+    card.wait()
+    launches = (card.launch_count() - launches_before) // steps
+    layer.sequence = first + warmup + steps
+    layer.result(1)  # raises if a wait expired or the reduction failed
+    barrier()
+
+    # ---- e2e: host arrays in, host array out, every call ----
+    for index in range(2):
+        layer.load(*inputs[index % 2])
+        layer.run()
+        layer.result(rows)
+    barrier()
+    wall_begin = time.perf_counter()
+    for index in range(steps):
+        layer.load(*inputs[index % 2])
+        layer.run()
+        layer.result(rows)
+    e2e_ms = maximum(1000.0 * (time.perf_counter() - wall_begin)) / steps
+    barrier()
+
+    # ---- roofline: the dominant kernel alone ----
+    roofline = None
+    counts = card.download(layout.workspace + layout.parts.counts, (len(held) + 1) * 4, np.uint32)
+    if rank == 0:
+        gate_up = (R.KernelLaunch * 1)(layer.launches[4])
+        card.run(gate_up)
+        card.wait()
+        card.measure_begin()
+        for _ in range(3):
+            card.run(gate_up)
+        card.measure_end()
+        us = card.measure_elapsed_us() / 3
+        flops = sum(int(counts[local]) * 2 * 2 * config.hidden *
+                    (share.inner if expert < config.experts else share.shared_inner)
+                    for local, expert in enumerate(held))
+        peak, source = measured_tensor_peak()
+        achieved = flops / us / 1e6  # TFLOP/s
+        roofline = {"kernel": "exl3_prefill_gate_up", "bound": "tensor", "achieved": achieved, "peak": peak,
+                    "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": source, "traffic": None,
+                    "algorithmic_flops_per_launch": flops, "us_per_launch": us,
+                    "row_tiles": int(counts[len(held)]), "pairs": int(counts[:len(held)].sum())}
+    card.wait()
+    barrier()
+    card.close()
+    return {"value": rows * 1000.0 / device_ms, "unit": "tok/s", "ms_per_step": device_ms, "rows": rows,
+            "steps": steps, "warmup": warmup, "gpu_launches_per_step": int(launches),
+            "e2e": {"value": rows * 1000.0 / e2e_ms, "unit": "tok/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": rows * config.hidden * 2 + rows * config.experts * 4 + 16,
+                    "d2h_bytes_per_step": rows * config.hidden * 2},
+            "roofline": roofline,
+            "config": {"workload": "cfg4 EXL3 MoE layer prefill: M=%d, Zipf(1.1) expert popularity, %d of %d routed "
+                                   "experts a GPU and 1/%d of the shared expert's columns" %
+                                   (rows, share.local_count, config.experts, world),
+                       "parallelism": "ep%d, ordered FP32->bf16 reduce (owner runs)" % world,
+                       "l2": "inputs larger than L2: a call streams its operand blocks (1 GB at N=1) and every "
+                             "local expert's matrices"}}
 
 
 def cpu_sample(config, widths, draw, tokens, scores, rank_count, job_limit):
@@ -341,10 +467,17 @@ def main():
                     "h2d_bytes_per_step": layout.step_input_bytes, "d2h_bytes_per_step": args.rows * config.hidden * 2},
             "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline,
         }
+        line = dict(line)
         if cpu is not None:
             line["cpu_baseline"] = cpu
-        print(json.dumps(line))
     card.close()
+    prefill = None
+    if args.prefill_rows > 0:
+        prefill = run_prefill(args, api, config, widths, draw, rank, world, local_rank, dist, barrier, maximum)
+    if rank == 0:
+        if prefill is not None:
+            line["prefill"] = prefill
+        print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()
 

@@ -291,6 +291,7 @@ struct ordered_collective_arguments {
 #define ORDERED_STATUS_BAD_SEQUENCE 2u
 #define ORDERED_B200_MAXIMUM_ELEMENTS (1u << 28) /* of this reduction; the FP32 collectives keep the reference's limit */
 #define ORDERED_B200_MAXIMUM_BLOCKS_LARGE 592u
+#define ORDERED_B200_PUBLISH_ROW_BLOCKS 128u /* grid rows of ordered_row_sum_publish at most; a block strides over rows */
 /* mode 0: every rank adds every element itself (no second hop: the lowest latency, the choice for decode steps).
  * mode 1: rank r adds the r-th of rank_count equal runs of four-element vectors (the first vectors % rank_count runs
  * one vector longer) and stores the bfloat16 values into EVERY rank's result by peer stores, publishes its REDUCED
@@ -308,7 +309,8 @@ struct ordered_reduce_bf16_arguments {
 
 /* B200 extension: the row sum of a rank written straight into its collective input slot of this step's parity
  * (FP32 [rows][width] at collective.input_offset of the slot), so that no copy stands between the experts and the
- * reduction. Rows at or beyond step.row_count are not written. grid (width / 128 rounded up, rows). */
+ * reduction. Rows at or beyond step.row_count are not written. grid (width / 512 rounded up, up to
+ * ORDERED_B200_PUBLISH_ROW_BLOCKS row blocks). */
 struct ordered_row_sum_publish_arguments {
 	struct ordered_collective_arguments collective;
 	uint64_t pair_output_offset; /* FP32 [rows * pairs_per_row][width] */
