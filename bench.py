@@ -37,8 +37,8 @@ sys.path.insert(0, ROOT)
 METRIC = "MoE expert-layer tok/s (decode M=8, prefill M=4096) at 1/2/4/8 B200"
 SEED = 20261125
 # dram bytes moved per algorithmic byte by exl3_moe_gate_up, from the ncu capture summarised in
-# profiles/exl3_moe_gate_up_k3_64experts_m8.md (dram__bytes_read.sum + dram__bytes_write.sum over the launch's bytes)
-GATE_UP_TRAFFIC_RATIO = 1.02
+# profiles/exl3_moe_gate_up_64experts_m8.md (dram__bytes_read.sum + dram__bytes_write.sum over the launch's bytes)
+GATE_UP_TRAFFIC_RATIO = 1.03
 
 
 def parse():
