@@ -290,7 +290,7 @@ result_status exl3_prefill_prepare(const struct exl3_prefill_record *record, uin
 	    experts == 0 || record->shared_count > ROUTER_B200_THREADS - ROUTER_B200_MAXIMUM_EXPERTS ||
 	    record->picks == 0 || record->picks > ROUTER_B200_MAXIMUM_PICKS || record->picks > record->expert_count ||
 	    record->row_capacity == 0 || record->row_capacity > EXL3_MAXIMUM_GRID_ROWS || H == 0 ||
-	    H % EXL3_TRANSFORM != 0 || I % EXL3_TRANSFORM != 0 || shared_I % EXL3_TRANSFORM != 0 || I > H || shared_I > H ||
+	    H % EXL3_TRANSFORM != 0 || I % EXL3_TRANSFORM != 0 || shared_I % EXL3_TRANSFORM != 0 ||
 	    (record->local_count != 0) != (I != 0) || (record->shared_count != 0) != (shared_I != 0) ||
 	    record->scoring > ROUTER_SCORING_SQRT_SOFTPLUS || !isfinite(record->route_scale) ||
 	    !isfinite(record->activation_limit) || record->activation_limit <= 0)
