@@ -52,8 +52,8 @@ def rank_partial(oracle, config, widths, matrices, tokens, experts, weights, ran
     record = R.Exl3Expert()
     record.jobs_offset = layout.take(job_capacity * 96)
     record.input_offset = layout.take(rows * H * 2)
-    record.operands_offset = layout.take(pairs * H * 4)
-    record.products_offset = record.output_offset = layout.take(pairs * H * 8)
+    record.operands_offset = layout.take(pairs * max(H, I) * 4)
+    record.products_offset = record.output_offset = layout.take(pairs * max(H, I) * 8)
     record.hidden_offset = layout.take(pairs * I * 2)
     row_output = layout.take(rows * H * 4)
     record.input_size, record.inner_size, record.pair_count, record.pairs_per_row = H, I, pairs, ppr

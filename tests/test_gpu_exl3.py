@@ -177,3 +177,97 @@ def test_single_expert_block_full_size(api, oracle):
         received = run_chain(api, case, moe=moe)
         worst, cos = check_chain(case, received, expected, moe=moe)
         assert worst < 1e-3  # far inside the tolerance: only the FP32 association of the products differs
+
+
+def test_shard_activation_equals_the_full_activation_on_its_columns(api, oracle):
+    """bb_exl3_activate_output_shard (prepared by bb_exl3_pass_prepare for rank 1 of a two-rank output-shard plan): on
+    the rank's 128 intermediate columns it must write the very bits the full activation writes for those columns
+    (a Hadamard block never straddles a shard)."""
+    from tests.test_host_preparers import PassDescription, ShardPlan
+    from anemone_b200.api import Layout
+    case = ChainCase(oracle, 91, hidden=512, inner=256, rows=5, picks=2, expert_count=4, widths=[3] * 4)
+    H, I, pairs, width = case.H, case.I, case.pairs, 3
+    lib = api.library()
+    card = api.Card(0, case.arena_bytes)
+    try:
+        card.upload(0, case.image)
+        launches = (R.KernelLaunch * 5)()
+        api.check(lib.exl3_experts_prepare(C.byref(case.record), case.arena_bytes, card.ops_pointer, card.handle, 100,
+                                           launches), "exl3_experts_prepare")
+        card.run(list(launches)[0:2])
+        card.wait()
+        products = card.download(case.record.products_offset, 2 * pairs * I * 4, np.float32).reshape(2, pairs, I).copy()
+        card.run(list(launches)[2:3])
+        card.wait()
+        hidden_full = card.download(case.record.hidden_offset, pairs * I * 2, np.uint16).reshape(pairs, I).copy()
+        operands_full = card.download(case.record.operands_offset, pairs * I * 2, np.uint16).reshape(pairs, I).copy()
+    finally:
+        card.close()
+    # rank 1 of 2: intermediate columns [128, 256); its down matrix holds the complete K and outputs [256, 512)
+    plan = ShardPlan()
+    lib.bb_exl3_output_shard_prepare.argtypes = [C.c_uint32] * 5 + [C.c_int, C.POINTER(ShardPlan)]
+    api.check(lib.bb_exl3_output_shard_prepare(H, I, width, 2, 1, 0, C.byref(plan)), "bb_exl3_output_shard_prepare")
+    begin, count = plan.gate_up.output_begin, plan.gate_up.output_count
+    assert (begin, count) == (128, 128) and (plan.down.output_begin, plan.down.output_count) == (256, 256)
+    layout = Layout()
+    placed, where = [], {}
+    full_bytes = (synthetic.matrix_bytes(H, I, width), synthetic.matrix_bytes(H, I, width),
+                  synthetic.matrix_bytes(I, H, width))
+    jobs = (R.ExpertJob * case.job_capacity).from_buffer_copy(bytes(case.jobs))
+    weights_begin = None
+    for job in jobs:
+        if job.row_count == 0:
+            continue
+        if job.expert not in where:
+            sources = [case.image[offset:offset + size] for offset, size in
+                       zip((job.gate_offset, job.up_offset, job.down_offset), full_bytes)]
+            local = (synthetic.slice_matrix(sources[0], H, I, width, 0, H, begin, count),
+                     synthetic.slice_matrix(sources[1], H, I, width, 0, H, begin, count),
+                     synthetic.slice_matrix(sources[2], I, H, width, 0, I, plan.down.output_begin,
+                                            plan.down.output_count))
+            offsets = []
+            for data in local:
+                offset = layout.take(data.size, 64)
+                weights_begin = offset if weights_begin is None else weights_begin
+                offsets.append(offset)
+                placed.append((offset, data))
+            where[job.expert] = offsets
+        job.gate_offset, job.up_offset, job.down_offset = where[job.expert]
+    weights_end = layout.cursor
+    record = R.Exl3Expert()
+    record.jobs_offset = layout.take(C.sizeof(jobs))
+    record.input_offset = layout.take(case.rows * H * 2)
+    record.operands_offset = layout.take(pairs * count * 2 + 64)
+    record.products_offset = record.output_offset = layout.take(2 * pairs * count * 4 + 64)
+    record.hidden_offset = layout.take(pairs * count * 2 + 64)
+    record.input_size, record.inner_size, record.pair_count, record.pairs_per_row = H, count, pairs, case.ppr
+    record.job_count, record.bits_per_weight, record.activation_limit = case.job_capacity, width, 10.0
+    arena_bytes = layout.take(0, 4096) + 4096
+    image = np.full(arena_bytes, 0xC3, dtype=np.uint8)
+    for offset, data in placed:
+        image[offset:offset + data.size] = data
+    image[record.jobs_offset:record.jobs_offset + C.sizeof(jobs)] = np.frombuffer(bytes(jobs), dtype=np.uint8)
+    local_products = np.ascontiguousarray(products[:, :, begin:begin + count])
+    image[record.products_offset:record.products_offset + local_products.nbytes] = local_products.view(np.uint8).reshape(-1)
+    description = PassDescription(C.pointer(plan), record, arena_bytes, weights_begin, weights_end - weights_begin, 2, 0)
+    lib.bb_exl3_pass_prepare.argtypes = [C.POINTER(PassDescription), C.POINTER(api.BackendOperations), C.c_void_p,
+                                         C.POINTER(R.KernelLaunch)]
+    card = api.Card(0, arena_bytes)
+    try:
+        card.upload(0, image)
+        launch = R.KernelLaunch()
+        api.check(lib.bb_exl3_pass_prepare(C.byref(description), card.ops_pointer, card.handle, C.byref(launch)),
+                  "bb_exl3_pass_prepare")
+        card.run([launch])
+        card.wait()
+        received = card.download(0, arena_bytes)
+    finally:
+        card.close()
+    hidden = received[record.hidden_offset:record.hidden_offset + pairs * count * 2].view(np.uint16).reshape(pairs, count)
+    operands = received[record.operands_offset:record.operands_offset + pairs * count * 2].view(np.uint16).reshape(pairs, count)
+    live = case.live_pairs()
+    assert np.array_equal(hidden[live], hidden_full[live][:, begin:begin + count])
+    assert np.array_equal(operands[live], operands_full[live][:, begin:begin + count])
+    for offset, size in ((record.hidden_offset, pairs * count * 2), (record.operands_offset, pairs * count * 2)):
+        assert (received[offset + size:offset + size + 64] == 0xC3).all()  # nothing written behind the ranges
+    assert np.array_equal(received[weights_begin:weights_end], image[weights_begin:weights_end])

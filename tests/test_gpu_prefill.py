@@ -205,3 +205,17 @@ def test_prefill_preparer_refusals(api):
             assert status(**changes) == 1, changes  # STATUS_INVALID_ARGUMENT
     finally:
         card.close()
+
+
+def test_prefill_intermediate_wider_than_hidden(api, oracle):
+    config = MoeConfig(hidden=256, inner=640, experts=6, shared=1, picks=2, row_capacity=200)
+    rows = 200
+    widths, matrices, tokens, scores = make_inputs(77, config, rows)
+    experts, weights = moe_reference.route(oracle, config, scores)
+    expected = moe_reference.rank_partial(oracle, config, widths, matrices, tokens, experts, weights, 1, 0)[0]
+    card = api.Card(0, PrefillLayout(config, widths).arena_bytes)
+    try:
+        got = PrefillLayer(card, config, widths, matrices).step(tokens, scores)
+        assert np.abs(got - expected).max() <= MAX_ABS and cosine(got, expected) >= COSINE
+    finally:
+        card.close()
