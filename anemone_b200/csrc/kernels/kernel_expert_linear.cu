@@ -8,7 +8,7 @@
  *   expert_down_<S>     grid (output_size / 16, jobs), block 32 S: bfloat16 [pair][output_size]
  *   expert_row_sum_entry  grid (ceil(width / block), rows): FP32 sums of bfloat16 pair outputs, ascending slots
  * A block owns one tile of 16 outputs of one job; the tile's words for all of K are contiguous in the stored format
- * (lane order), so a warp streams its slice with one 128-bit load a lane per 64 inputs, two loads ahead, and a code
+ * (lane order), so a warp streams its slice with one 128-bit load a lane per 64 inputs, four loads ahead, and a code
  * becomes an FP16 operand by bit placement alone: the E2M1 nibble placed is its value times 2^-14, the activation
  * operand (written by activation_quantize_entry) its E4M3 value times 2^-8. Per block of 32 inputs the tensor cores add
  * the 32 products from zero (two m16n8k16 instructions), and chain = fma(p, 2^e, chain) with 2^e the exact power of
@@ -20,6 +20,7 @@
 #include "anemone_b200_records.h"
 
 #define WARP 32u
+#define EXPERT_AHEAD 4u /* loads of a lane in flight */
 
 __device__ __forceinline__ uint32_t bfloat16_bits(float value)
 {
@@ -74,37 +75,52 @@ __device__ __forceinline__ void slice_chains(const unsigned char *matrix, uint32
 	chains[0] = chains[1] = chains[2] = chains[3] = 0.0f;
 	if (first_load >= last_load)
 		return;
-	uint4 next_words = __ldg(words + (uint64_t)first_load * WARP);
-	uint32_t next_scales = __ldg(scales + (uint64_t)first_load * 8u);
-	for (uint32_t load = first_load; load < last_load; load++) {
-		const uint4 current = next_words;
-		const uint32_t scale_word = next_scales;
-		if (load + 1u < last_load) {
-			next_words = __ldg(words + (uint64_t)(load + 1u) * WARP);
-			next_scales = __ldg(scales + (uint64_t)(load + 1u) * 8u);
+	/* EXPERT_AHEAD loads in flight a lane: a slice is short (a few KB a warp), so the depth of the prefetch, not the
+	 * occupancy, decides how much of the memory system a launch keeps busy */
+	uint4 ahead_words[EXPERT_AHEAD];
+	uint32_t ahead_scales[EXPERT_AHEAD];
+#pragma unroll
+	for (uint32_t slot = 0; slot < EXPERT_AHEAD; slot++)
+		if (first_load + slot < last_load) {
+			ahead_words[slot] = __ldcs(words + (uint64_t)(first_load + slot) * WARP);
+			ahead_scales[slot] = __ldcs(scales + (uint64_t)(first_load + slot) * 8u);
 		}
-		const uint4 fed_low = __ldg(fed + (uint64_t)load * 8u), fed_high = __ldg(fed + (uint64_t)load * 8u + 1u);
-		const uint32_t fed_registers[8] = { fed_low.x, fed_low.y, fed_low.z, fed_low.w,
-						    fed_high.x, fed_high.y, fed_high.z, fed_high.w };
-		const uint32_t step_words[4] = { current.x, current.y, current.z, current.w };
-		const uint32_t even = *reinterpret_cast<const uint16_t *>(exponents_even + 2u * load);
-		const uint32_t odd = *reinterpret_cast<const uint16_t *>(exponents_odd + 2u * load);
+	for (uint32_t base = first_load; base < last_load; base += EXPERT_AHEAD) {
 #pragma unroll
-		for (uint32_t q = 0; q < 2u; q++) {
-			float sum[4] = { 0.0f, 0.0f, 0.0f, 0.0f };
-#pragma unroll
-			for (uint32_t half = 0; half < 2u; half++) {
-				const uint32_t step = 2u * q + half, word = step_words[step];
-				const uint32_t a[4] = { place_e2m1<0>(word), place_e2m1<1>(word), place_e2m1<2>(word),
-							place_e2m1<3>(word) };
-				mma_f16(sum, a, fed_registers[2u * step], fed_registers[2u * step + 1u]);
+		for (uint32_t slot = 0; slot < EXPERT_AHEAD; slot++) {
+			const uint32_t load = base + slot;
+			if (load >= last_load)
+				break;
+			const uint4 current = ahead_words[slot];
+			const uint32_t scale_word = ahead_scales[slot];
+			if (load + EXPERT_AHEAD < last_load) {
+				ahead_words[slot] = __ldcs(words + (uint64_t)(load + EXPERT_AHEAD) * WARP);
+				ahead_scales[slot] = __ldcs(scales + (uint64_t)(load + EXPERT_AHEAD) * 8u);
 			}
-			const uint32_t low_row = (scale_word >> (16u * q)) & 0xFFu, high_row = (scale_word >> (16u * q + 8u)) & 0xFFu;
-			const uint32_t even_code = (even >> (8u * q)) & 0xFFu, odd_code = (odd >> (8u * q)) & 0xFFu;
-			chains[0] = __fmaf_rn(sum[0], block_scale(low_row, even_code), chains[0]);
-			chains[1] = __fmaf_rn(sum[1], block_scale(low_row, odd_code), chains[1]);
-			chains[2] = __fmaf_rn(sum[2], block_scale(high_row, even_code), chains[2]);
-			chains[3] = __fmaf_rn(sum[3], block_scale(high_row, odd_code), chains[3]);
+			const uint4 fed_low = __ldg(fed + (uint64_t)load * 8u), fed_high = __ldg(fed + (uint64_t)load * 8u + 1u);
+			const uint32_t fed_registers[8] = { fed_low.x, fed_low.y, fed_low.z, fed_low.w,
+							    fed_high.x, fed_high.y, fed_high.z, fed_high.w };
+			const uint32_t step_words[4] = { current.x, current.y, current.z, current.w };
+			const uint32_t even = *reinterpret_cast<const uint16_t *>(exponents_even + 2u * load);
+			const uint32_t odd = *reinterpret_cast<const uint16_t *>(exponents_odd + 2u * load);
+#pragma unroll
+			for (uint32_t q = 0; q < 2u; q++) {
+				float sum[4] = { 0.0f, 0.0f, 0.0f, 0.0f };
+#pragma unroll
+				for (uint32_t half = 0; half < 2u; half++) {
+					const uint32_t step = 2u * q + half, word = step_words[step];
+					const uint32_t a[4] = { place_e2m1<0>(word), place_e2m1<1>(word), place_e2m1<2>(word),
+								place_e2m1<3>(word) };
+					mma_f16(sum, a, fed_registers[2u * step], fed_registers[2u * step + 1u]);
+				}
+				const uint32_t low_row = (scale_word >> (16u * q)) & 0xFFu,
+					       high_row = (scale_word >> (16u * q + 8u)) & 0xFFu;
+				const uint32_t even_code = (even >> (8u * q)) & 0xFFu, odd_code = (odd >> (8u * q)) & 0xFFu;
+				chains[0] = __fmaf_rn(sum[0], block_scale(low_row, even_code), chains[0]);
+				chains[1] = __fmaf_rn(sum[1], block_scale(low_row, odd_code), chains[1]);
+				chains[2] = __fmaf_rn(sum[2], block_scale(high_row, even_code), chains[2]);
+				chains[3] = __fmaf_rn(sum[3], block_scale(high_row, odd_code), chains[3]);
+			}
 		}
 	}
 }

@@ -1,0 +1,178 @@
+"""One rank's original-weights routed-expert layer (MXFP4 weights by E4M3 block-quantized activations), prepared once
+and run per step through the C-ABI library. Launches of one step, all from libanemone_b200.so:
+    router_select_b200 -> activation_quantize_entry -> expert_gate_up_<S> -> activation_quantize_entry (hidden)
+    -> expert_down_<S> -> expert_row_sum_entry -> ordered_row_sum_publish -> ordered_reduce_bf16
+(the four middle ones are linear_routed_experts_prepare's). Tensor parallelism is by intermediate columns, as in the
+EXL3 decode layer; the ranks' FP32 rows are added in rank order and rounded once. Nothing here computes on the host.
+"""
+import ctypes as C
+
+import numpy as np
+
+from . import api
+from . import records as R
+from .moe import LINE, SIGNAL_BYTES, rank_columns
+
+WEIGHT_FORMAT_E2M1_SCALED = 3
+
+
+def matrix_bytes(outputs, inputs):
+    return outputs * inputs // 2 + outputs * inputs // 32
+
+
+class MxLayout:
+    def __init__(self, config, rank_count, rank):
+        assert config.shared == 0, "the always-on expert of this profile is FP8, which this library does not have"
+        self.config = c = config
+        self.inner_local = I = rank_columns(c.inner, rank_count, rank)[1]
+        H, rows = c.hidden, c.row_capacity
+        self.pairs = pairs = rows * c.picks
+        self.job_capacity = rows * c.picks
+        layout = api.Layout()
+        self.peer_table = layout.take(16 * 32)
+        self.status = layout.take(16)
+        self.step = layout.take(256)
+        self.tokens = layout.take(rows * H * 2)
+        self.scores = layout.take(rows * c.experts * 4)
+        self.step_input_bytes = layout.cursor - self.step
+        self.result = layout.take(rows * H * 2)
+        self.slot_input = SIGNAL_BYTES
+        self.parity_stride = api.align(SIGNAL_BYTES + rows * H * 4, LINE)
+        self.region = layout.take(2 * self.parity_stride, LINE)
+        self.picks = layout.take(rows * c.picks * 4)
+        self.weights = layout.take(rows * c.picks * 4)
+        self.jobs = layout.take(self.job_capacity * 96)
+        self.expert_table = layout.take(c.experts * 24)
+        self.sizes = {"codes": rows * H, "exponents": rows * H // 32, "operands": rows * H * 2,
+                      "hidden": pairs * I * 2, "hidden_codes": pairs * I, "hidden_exponents": pairs * I // 32,
+                      "hidden_operands": pairs * I * 2, "pair_output": pairs * H * 2, "row_output": rows * H * 4}
+        self.at = {name: layout.take(size) for name, size in self.sizes.items()}
+        self.weights_begin = api.align(layout.cursor, 64)
+        self.matrices = []
+        for _ in range(c.experts):
+            self.matrices.append((layout.take(matrix_bytes(I, H), 64), layout.take(matrix_bytes(I, H), 64),
+                                  layout.take(matrix_bytes(H, I), 64)))
+        self.weights_end = layout.cursor
+        self.arena_bytes = api.align(layout.cursor, 4096) + 4096
+
+
+class MxLayer:
+    def __init__(self, card, config, matrices, rank=0, rank_count=1, slices=(4, 4)):
+        """matrices: iterable over experts of this rank's (gate, up, down) stored bytes."""
+        self.card, self.config = card, config
+        self.layout = L = MxLayout(config, rank_count, rank)
+        assert card.arena_bytes >= L.arena_bytes
+        self.rank, self.rank_count = rank, rank_count
+        self.weight_bytes = 0
+        table = np.zeros((config.experts, 3), dtype=np.uint64)
+        for expert, triple in enumerate(matrices):
+            for which, data in enumerate(triple):
+                card.upload(L.matrices[expert][which], data)
+                table[expert, which] = L.matrices[expert][which]
+                self.weight_bytes += data.size
+        card.upload(L.expert_table, table)
+        for offset, size in ((L.peer_table, 16 * 32), (L.status, 16), (L.step, 256), (L.region, 2 * L.parity_stride)):
+            card.fill(offset, 0, size)
+        peers = (R.OrderedPeer * rank_count)()
+        for peer in range(rank_count):
+            peers[peer].region_offset = L.region
+        card.upload(L.peer_table, np.frombuffer(bytes(peers), dtype=np.uint8))
+        c, lib, H, I = config, api.library(), config.hidden, L.inner_local
+        router = R.RouterSelectB200(L.scores, L.expert_table, L.picks, L.weights, L.jobs, L.step, c.experts, 0,
+                                    c.picks, c.row_capacity, L.job_capacity, c.scoring, c.route_scale, 0)
+        lib.router_select_b200_prepare.argtypes = [C.POINTER(R.RouterSelectB200), C.c_uint64,
+                                                   C.POINTER(api.BackendOperations), C.c_void_p,
+                                                   C.POINTER(R.KernelLaunch)]
+        router_launch = R.KernelLaunch()
+        api.check(lib.router_select_b200_prepare(C.byref(router), card.arena_bytes, card.ops_pointer, card.handle,
+                                                 C.byref(router_launch)), "router_select_b200_prepare")
+        kernels = R.LinearKernels()
+        lib.linear_kernels_prepare.argtypes = [C.POINTER(api.BackendOperations), C.c_void_p, C.c_uint32,
+                                               C.POINTER(R.LinearKernels)]
+        api.check(lib.linear_kernels_prepare(card.ops_pointer, card.handle, 100, C.byref(kernels)),
+                  "linear_kernels_prepare")
+
+        def span(name):
+            return R.LinearRange(L.at[name], L.sizes[name])
+        quantize = R.LinearQuantizeDescription(R.LinearRange(L.tokens, c.row_capacity * H * 2), span("codes"),
+                                               span("exponents"), span("operands"), H, c.row_capacity)
+        lib.linear_quantize_prepare.argtypes = [C.POINTER(R.LinearQuantizeDescription), C.c_uint64,
+                                                C.POINTER(R.LinearKernels), C.POINTER(R.KernelLaunch)]
+        quantize_launch = R.KernelLaunch()
+        api.check(lib.linear_quantize_prepare(C.byref(quantize), card.arena_bytes, C.byref(kernels),
+                                              C.byref(quantize_launch)), "linear_quantize_prepare")
+        description = R.LinearRoutedExpertsDescription()
+        description.jobs = R.LinearRange(L.jobs, L.job_capacity * 96)
+        description.expert_weights = R.LinearRange(L.weights_begin, L.weights_end - L.weights_begin)
+        for name in L.sizes:
+            setattr(description, name, span(name))
+        description.gate_up_shape, description.down_shape = R.MatrixShape(I, H, 4, 0), R.MatrixShape(H, I, 4, 0)
+        description.weight_format, description.job_count = WEIGHT_FORMAT_E2M1_SCALED, L.job_capacity
+        description.row_count, description.pairs_per_row = c.row_capacity, c.picks
+        description.activation_limit = c.activation_limit
+        description.gate_up_slice_count, description.down_slice_count = slices
+        lib.linear_routed_experts_prepare.argtypes = [C.POINTER(R.LinearRoutedExpertsDescription), C.c_uint64,
+                                                      C.POINTER(R.LinearKernels), C.POINTER(R.KernelLaunch)]
+        self.expert_launches = (R.KernelLaunch * 4)()
+        api.check(lib.linear_routed_experts_prepare(C.byref(description), card.arena_bytes, C.byref(kernels),
+                                                    self.expert_launches), "linear_routed_experts_prepare")
+        reduce = R.OrderedReduceBf16Description()
+        reduce.reduce.collective = R.OrderedCollective(L.peer_table, L.region, L.slot_input, L.result, 0, L.step,
+                                                       L.parity_stride, c.deadline_cycles, c.row_capacity * H,
+                                                       rank_count, rank, 0)
+        reduce.reduce.status_offset, reduce.reduce.width = L.status, H
+        reduce.pair_output_offset, reduce.arena_byte_count = L.at["row_output"], card.arena_bytes
+        reduce.pairs_per_row, reduce.row_capacity = 1, c.row_capacity
+        lib.ordered_reduce_bf16_prepare.argtypes = [C.POINTER(R.OrderedReduceBf16Description),
+                                                    C.POINTER(api.BackendOperations), C.c_void_p,
+                                                    C.POINTER(R.KernelLaunch)]
+        reduce_launches = (R.KernelLaunch * 2)()
+        api.check(lib.ordered_reduce_bf16_prepare(C.byref(reduce), card.ops_pointer, card.handle, reduce_launches),
+                  "ordered_reduce_bf16_prepare")
+        self.launches = [router_launch, quantize_launch] + list(self.expert_launches) + list(reduce_launches)
+        self.graph = card.graph(self.launches)
+        self.sequence = 0
+
+    def connect_local(self, layers):
+        for peer, other in enumerate(layers):
+            self.card.peer_connect(other.card, 0, self.layout.peer_table + 32 * peer)
+
+    def connect_handles(self, handles):
+        for peer, handle in enumerate(handles):
+            if peer == self.rank:
+                self.card.peer_connect(self.card, 0, self.layout.peer_table + 32 * peer)
+            else:
+                self.card.ipc_connect(handle, 0, self.layout.peer_table + 32 * peer)
+
+    def stage_step(self, staging_offset, sequence, tokens, scores):
+        L, view = self.layout, self.card.staging_view
+        block = R.StepBlock(sequence, tokens.shape[0], 0)
+        view[staging_offset:staging_offset + 16] = np.frombuffer(bytes(block), dtype=np.uint8)
+        at = staging_offset + (L.tokens - L.step)
+        view[at:at + tokens.nbytes] = tokens.reshape(-1).view(np.uint8)
+        at = staging_offset + (L.scores - L.step)
+        view[at:at + scores.nbytes] = np.ascontiguousarray(scores, dtype=np.float32).reshape(-1).view(np.uint8)
+
+    def submit(self, staging_offset, result_staging_offset, rows):
+        L, card = self.layout, self.card
+        card.upload_async(L.step, staging_offset, L.step_input_bytes)
+        card.graph_run(self.graph)
+        return card.download_async(L.result, result_staging_offset, rows * self.config.hidden * 2)
+
+    def step(self, tokens, scores):
+        """One layer call on host arrays; returns bfloat16 bits [rows][hidden]."""
+        L, card = self.layout, self.card
+        rows = tokens.shape[0]
+        self.sequence += 1
+        result_at = api.align(L.step_input_bytes, 4096)
+        self.stage_step(0, self.sequence, tokens, scores)
+        card.transfer_wait(self.submit(0, result_at, rows))
+        self.check_status()
+        nbytes = rows * self.config.hidden * 2
+        return card.staging_view[result_at:result_at + nbytes].view(np.uint16).reshape(rows, self.config.hidden).copy()
+
+    def check_status(self):
+        status = self.card.download(self.layout.status, 16, np.uint32)
+        if status[0] != 0:
+            raise RuntimeError("ordered reduction failed: code %d (1 timed out, 2 bad sequence), phase %d, rank %d"
+                               % (status[0], status[1], status[2]))

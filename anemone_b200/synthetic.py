@@ -67,3 +67,12 @@ def zipf_scores(rng, rows, expert_count, exponent=1.1):
     popularity = -exponent * np.log(np.arange(1, expert_count + 1, dtype=np.float64))
     gumbel = rng.gumbel(size=(rows, expert_count))
     return (popularity[None, :] + gumbel).astype(np.float32)
+
+
+def mx_matrix(rng, outputs, inputs):
+    """Stored bytes of one WEIGHT_FORMAT_E2M1_SCALED matrix of the original-weights profile: uniform E2M1 nibbles
+    (every byte pattern is a valid pair of codes), then E8M0 scale codes 127 + e with e uniform in [-8, -4], one per
+    32 inputs. Independent draws, so the stored order of the format needs no permutation here."""
+    words = rng.integers(0, 256, size=outputs * inputs // 2, dtype=np.uint8)
+    scales = (127 + rng.integers(-8, -3, size=outputs * inputs // 32)).astype(np.uint8)
+    return np.concatenate([words, scales])

@@ -53,6 +53,7 @@ def parse():
     parser.add_argument("--inner", type=int, default=2048)
     parser.add_argument("--prefill-rows", type=int, default=4096, help="0 skips the prefill part")
     parser.add_argument("--prefill-steps", type=int, default=5)
+    parser.add_argument("--no-original-weights", action="store_true", help="skip the MXFP4 part")
     return parser.parse_args()
 
 
@@ -181,8 +182,12 @@ def run_prefill(args, api, base, widths, draw, rank, world, local_rank, dist, ba
         block = R.StepBlock(first + 1 + index, rows, 0)
         card.staging_view[64 * index:64 * index + 16] = np.frombuffer(bytes(block), dtype=np.uint8)
 
+    tickets = []
+
     def resident(index):
-        card.upload_async(layout.step, 64 * index, 16)
+        if len(tickets) >= 4:  # the card takes a bounded number of copies in flight
+            card.transfer_wait(tickets[-4])
+        tickets.append(card.upload_async(layout.step, 64 * index, 16))
         layer.run()
     for index in range(warmup):
         resident(index)
@@ -325,6 +330,107 @@ def workload_config(args, config, world):
                                                                                  config.inner, args.rows),
             "rows": args.rows, "parallelism": "tp%d by intermediate columns, ordered FP32->bf16 reduce" % world,
             "l2": "inputs larger than L2: every step routes to a different expert set (~58 experts of 257)"}
+
+
+def run_original_weights(args, api, base, rank, world, local_rank, dist, barrier, maximum):
+    """cfg5, routed experts only: MXFP4 weights (E8M0 scales 2^-8 .. 2^-4) by E4M3 block-quantized activations,
+    decode M = 8, tensor parallel by intermediate columns. The FP8 always-on expert of that configuration is not built."""
+    from anemone_b200 import records as R
+    from anemone_b200 import synthetic
+    from anemone_b200.moe import MoeConfig
+    from anemone_b200.mx import MxLayer, MxLayout, matrix_bytes
+    rows, steps, warmup = args.rows, args.steps, args.warmup
+    config = MoeConfig(hidden=base.hidden, inner=base.inner, experts=base.experts, shared=0, picks=base.picks,
+                       row_capacity=rows, activation_limit=7.0)
+    layout = MxLayout(config, world, rank)
+    H, I = config.hidden, layout.inner_local
+    card = api.Card(local_rank, layout.arena_bytes)
+
+    def draw(expert):
+        rng = np.random.default_rng([SEED, 2000 + expert, rank])
+        return (synthetic.mx_matrix(rng, I, H), synthetic.mx_matrix(rng, I, H), synthetic.mx_matrix(rng, H, I))
+    layer = MxLayer(card, config, (draw(expert) for expert in range(config.experts)), rank=rank, rank_count=world,
+                    slices=(2, 2))
+    if dist is None:
+        layer.connect_local([layer])
+    else:
+        handles = [None] * world
+        dist.all_gather_object(handles, card.ipc_export())
+        layer.connect_handles(handles)
+    card.wait()
+    barrier()
+    inputs = step_inputs(config, rows, warmup + steps)
+    stride = api.align(layout.step_input_bytes, 4096)
+    assert stride * (warmup + steps) + 2 * rows * H <= card.staging_bytes
+    # ---- value: every step's inputs wait in pinned memory; the copies in are inside the timed region all the same,
+    # because this part keeps no pool on the card (74 KB a step) ----
+    for index, (tokens, scores) in enumerate(inputs):
+        layer.stage_step(stride * index, index + 1, tokens, scores)
+
+    tickets = []
+
+    def queued(index):
+        if len(tickets) >= 4:  # the card takes a bounded number of copies in flight
+            card.transfer_wait(tickets[-4])
+        tickets.append(card.upload_async(layout.step, stride * index, layout.step_input_bytes))
+        card.graph_run(layer.graph)
+    for index in range(warmup):
+        queued(index)
+    card.wait()
+    barrier()
+    launches_before = card.launch_count()
+    card.measure_begin()
+    for index in range(warmup, warmup + steps):
+        queued(index)
+    card.measure_end()
+    device_ms = maximum(card.measure_elapsed_us() / 1000.0) / steps
+    card.wait()
+    launches = (card.launch_count() - launches_before) // steps
+    layer.sequence = warmup + steps
+    layer.check_status()
+    barrier()
+    # ---- e2e ----
+    for tokens, scores in inputs[:warmup]:
+        layer.step(tokens, scores)
+    barrier()
+    wall_begin = time.perf_counter()
+    for tokens, scores in inputs[warmup:]:
+        layer.step(tokens, scores)
+    e2e_ms = maximum(1000.0 * (time.perf_counter() - wall_begin)) / steps
+    barrier()
+    # ---- roofline: expert_gate_up alone ----
+    roofline = None
+    if rank == 0:
+        peak, source = measured_peaks()
+        gate_up = (R.KernelLaunch * 1)(layer.launches[2])
+        card.run(gate_up)
+        card.wait()
+        card.measure_begin()
+        for _ in range(5):
+            card.run(gate_up)
+        card.measure_end()
+        us = card.measure_elapsed_us() / 5
+        picks = card.download(layout.picks, rows * config.picks * 4, np.uint32)
+        active = len(set(picks.tolist()))
+        pairs = rows * config.picks
+        byte_total = active * 2 * matrix_bytes(I, H) + rows * H * 2 + rows * H // 32 + pairs * I * 2
+        achieved = byte_total / us / 1000.0
+        roofline = {"kernel": "expert_gate_up_2", "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                    "frac": achieved / peak, "peak_source": source, "traffic": None,
+                    "algorithmic_bytes_per_launch": byte_total, "us_per_launch": us, "active_experts": active}
+    card.wait()
+    barrier()
+    card.close()
+    return {"value": rows * 1000.0 / device_ms, "unit": "tok/s", "ms_per_step": device_ms, "rows": rows,
+            "steps": steps, "warmup": warmup, "gpu_launches_per_step": int(launches),
+            "e2e": {"value": rows * 1000.0 / e2e_ms, "unit": "tok/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": layout.step_input_bytes, "d2h_bytes_per_step": rows * H * 2},
+            "roofline": roofline, "dtype": "e2m1 x e4m3 -> f32",
+            "config": {"workload": "cfg5 routed experts only: MXFP4 (E2M1, one E8M0 scale per 32 inputs, exponents "
+                                   "-8..-4), %d experts, top-%d, hidden %d, intermediate %d, M=%d; the FP8 always-on "
+                                   "expert is not built" % (config.experts, config.picks, H, config.inner, rows),
+                       "parallelism": "tp%d by intermediate columns, ordered FP32->bf16 reduce" % world,
+                       "note": "value includes the 74 KB host->device copy of each step's inputs"}}
 
 
 def main():
@@ -474,9 +580,14 @@ def main():
     prefill = None
     if args.prefill_rows > 0:
         prefill = run_prefill(args, api, config, widths, draw, rank, world, local_rank, dist, barrier, maximum)
+    original = None
+    if not args.no_original_weights:
+        original = run_original_weights(args, api, config, rank, world, local_rank, dist, barrier, maximum)
     if rank == 0:
         if prefill is not None:
             line["prefill"] = prefill
+        if original is not None:
+            line["original_weights"] = original
         print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()

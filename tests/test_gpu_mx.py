@@ -182,3 +182,50 @@ def test_routed_experts_match_oracle(api, oracle, slices):
     assert np.array_equal(resummed.view(np.uint32), region(received, "row_output", np.uint32).reshape(rows, H))
     # weights and inputs untouched
     assert np.array_equal(received[:weights_end], image[:weights_end])
+
+
+def test_layer_matches_oracle(api, oracle):
+    """The whole original-weights layer (router -> quantize -> experts -> row sum -> ordered reduction) through
+    anemone_b200.mx.MxLayer: the card's own job table and quantized rows, then the oracle's experts on the same image."""
+    from anemone_b200.moe import MoeConfig
+    from anemone_b200.mx import MxLayer, MxLayout
+    from oracle import moe_reference
+    config = MoeConfig(hidden=512, inner=256, experts=12, shared=0, picks=3, row_capacity=8, activation_limit=7.0)
+    rng = np.random.default_rng(91)
+    H, I, rows = config.hidden, config.inner, 7
+    matrices = [(mx_matrix(oracle, rng, I, H), mx_matrix(oracle, rng, I, H), mx_matrix(oracle, rng, H, I))
+                for _ in range(config.experts)]
+    tokens = synthetic.tokens(rng, rows, H)
+    scores = rng.normal(0, 1, size=(rows, config.experts)).astype(np.float32)
+    L = MxLayout(config, 1, 0)
+    card = api.Card(0, L.arena_bytes)
+    try:
+        layer = MxLayer(card, config, matrices, slices=(2, 2))
+        layer.connect_local([layer])
+        result = layer.step(tokens, scores)
+        received = card.download(0, L.arena_bytes)
+    finally:
+        card.close()
+    experts, weights = moe_reference.route(oracle, config, scores)
+    picks = received[L.picks:L.picks + rows * config.picks * 4].view(np.uint32).reshape(rows, config.picks)
+    assert np.array_equal(picks, experts)
+    expected = received.copy()
+    at, pairs = L.at, L.pairs
+    gate_up = R.ExpertGateUp(L.jobs, at["codes"], at["exponents"], at["operands"], at["hidden"], I, H, pairs,
+                             config.picks, 7.0, 0)
+    down = R.ExpertDown(L.jobs, at["hidden_codes"], at["hidden_exponents"], at["hidden_operands"], at["pair_output"],
+                        H, I, pairs, 0)
+    oracle.orc_mx_experts(C.byref(gate_up), C.byref(down), L.job_capacity, 2, 2, at["hidden_codes"],
+                          at["hidden_exponents"], at["hidden_operands"], ptr(expected, u8p))
+    live = rows * config.picks
+    out_got = synthetic.from_bfloat16(received[at["pair_output"]:at["pair_output"] + live * H * 2].view(np.uint16))
+    out_want = synthetic.from_bfloat16(expected[at["pair_output"]:at["pair_output"] + live * H * 2].view(np.uint16))
+    assert np.isfinite(out_got).all() and np.abs(out_want).max() > 0
+    assert np.abs(out_got - out_want).max() <= max(2e-2, 2.0 ** -6 * np.abs(out_want).max())
+    # row sums and the reduction are bit-exact given the pair outputs the card wrote
+    resummed = np.zeros((rows, H), dtype=np.float32)
+    for slot in range(config.picks):
+        resummed = (resummed + out_got.reshape(rows, config.picks, H)[:, slot, :]).astype(np.float32)
+    row_output = received[at["row_output"]:at["row_output"] + rows * H * 4].view(np.float32).reshape(rows, H)
+    assert np.array_equal(resummed.view(np.uint32), row_output.view(np.uint32))
+    assert np.array_equal(result, synthetic.to_bfloat16(np.float32(0.0) + row_output))
