@@ -219,3 +219,51 @@ def test_prefill_intermediate_wider_than_hidden(api, oracle):
         assert np.abs(got - expected).max() <= MAX_ABS and cosine(got, expected) >= COSINE
     finally:
         card.close()
+
+
+def test_prefill_full_size_properties(api):
+    """The benchmark's shapes (256 + 1 experts, hidden 4096, intermediate 2048, top-8, 4096 rows), where the oracle is
+    too slow: size-independent properties instead. (1) A row's result does not depend on which other rows are in the
+    call or where it stands in its row tile: permuting the rows permutes the results bit for bit. (2) The first eight
+    rows through the decode launches agree with the same rows of the prefill call within the association of the FP32
+    products. (3) Every pair is grouped exactly once."""
+    config = MoeConfig(hidden=4096, inner=2048, experts=256, shared=1, picks=8, row_capacity=4096)
+    rows = 4096
+    rng = np.random.default_rng(2026)
+    widths = np.concatenate([synthetic.expert_widths(rng, config.experts), [3]]).astype(np.uint32)
+    matrices = [(synthetic.exl3_matrix(rng, config.hidden, config.inner, int(w)),
+                 synthetic.exl3_matrix(rng, config.hidden, config.inner, int(w)),
+                 synthetic.exl3_matrix(rng, config.inner, config.hidden, int(w))) for w in widths]
+    tokens = synthetic.tokens(rng, rows, config.hidden)
+    popularity = 1.0 / np.arange(1, config.experts + 1) ** 1.1
+    scores = (rng.normal(0, 1, size=(rows, config.experts)) +
+              np.log(popularity / popularity.mean())[rng.permutation(config.experts)]).astype(np.float32)
+    order = rng.permutation(rows)
+    card = api.Card(0, PrefillLayout(config, widths).arena_bytes)
+    try:
+        layer = PrefillLayer(card, config, widths, matrices)
+        first = layer.step(tokens, scores)
+        picks = card.download(layer.layout.picks, rows * config.picks * 4, np.uint32).reshape(rows, config.picks)
+        total = config.total_experts
+        counts = card.download(layer.layout.workspace, (total + 1) * 4, np.uint32)
+        want = np.bincount(picks.reshape(-1), minlength=total)
+        want[config.experts] = rows
+        assert np.array_equal(counts[:total], want) and counts[total] == ((want + 127) // 128).sum()
+        assert np.all(np.diff(picks.astype(np.int64), axis=1) > 0)  # slots in ascending expert order
+        second = layer.step(tokens[order], scores[order])
+        assert np.isfinite(first).all() and np.abs(first).max() > 0
+        assert np.array_equal(second.view(np.uint32), first[order].view(np.uint32))
+    finally:
+        card.close()
+    small = MoeConfig(hidden=4096, inner=2048, experts=256, shared=1, picks=8, row_capacity=8)
+    card = api.Card(0, MoeLayout(small, widths, 1, 0).arena_bytes)
+    try:
+        decode = MoeLayer(card, small, widths, matrices)
+        decode.connect_local([decode])
+        decode.step(tokens[:8], scores[:8])
+        slot = decode.layout.region + (decode.sequence & 1) * decode.layout.parity_stride + decode.layout.slot_input
+        decode_rows = card.download(slot, 8 * config.hidden * 4, np.float32).reshape(8, config.hidden)
+    finally:
+        card.close()
+    scale = max(float(np.abs(decode_rows).max()), 1.0)
+    assert np.abs(first[:8] - decode_rows).max() <= 2e-3 * scale and cosine(first[:8], decode_rows) >= 0.99999
