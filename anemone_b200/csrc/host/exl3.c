@@ -329,8 +329,7 @@ result_status exl3_prefill_prepare(const struct exl3_prefill_record *record, uin
 		{ 1, 1, 1, ROUTER_B200_THREADS, 0 },
 		{ parts.tile_capacity, transform_grid(H) * EXL3_PREFILL_OPERAND_PARTS, EXL3_PROJECTIONS,
 		  EXL3_TRANSFORM_THREADS, 0 },
-		{ (widest / EXL3_TRANSFORM + 1u) / 2u, parts.tile_capacity, 1, EXL3_PREFILL_GEMM_THREADS,
-		  EXL3_PREFILL_DYNAMIC_BYTES },
+		{ widest / EXL3_TRANSFORM, parts.tile_capacity, 1, EXL3_PREFILL_GEMM_THREADS, EXL3_PREFILL_DYNAMIC_BYTES },
 		{ (H / EXL3_TRANSFORM + 1u) / 2u, parts.tile_capacity, 1, EXL3_PREFILL_GEMM_THREADS,
 		  EXL3_PREFILL_DYNAMIC_BYTES },
 		{ (H / 4u + EXL3_ROW_SUM_THREADS - 1u) / EXL3_ROW_SUM_THREADS, record->row_capacity, 1, EXL3_ROW_SUM_THREADS,

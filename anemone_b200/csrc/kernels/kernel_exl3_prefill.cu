@@ -302,43 +302,53 @@ __device__ __forceinline__ void decode_sync()
 	asm volatile("bar.sync 1, %0;" ::"n"(PREFILL_DECODE_THREADS) : "memory");
 }
 
-/* Dynamic shared memory of a product CTA, for MATRICES matrices, PREFILL_GROUPS groups of 128 outputs and stages of
- * KSTEPS steps of 16 inputs. Three rings of different depth, because their contents wait for different things:
- *   A ring        EXL3_PREFILL_A_STAGES x [matrix] operand blocks (128 rows x 16 KSTEPS FP16 in the tensor cores'
+/* Dynamic shared memory of a product CTA, for TILES row tiles of one expert, MATRICES matrices, GROUPS groups of 128
+ * outputs and stages of KSTEPS steps of 16 inputs. Three rings of different depth, because their contents wait for
+ * different things:
+ *   A ring        EXL3_PREFILL_A_STAGES x [tile][matrix] operand blocks (128 rows x 16 KSTEPS FP16 in the tensor cores'
  *                 layout, KSTEPS x 4096 bytes): bulk copies, mostly from L2
- *   B ring        EXL3_PREFILL_B_STAGES x [matrix] blocks of decoded weights, 256 outputs x 16 KSTEPS FP16 in the same
- *                 layout (so one instruction multiplies both groups and reads the operand rows once): written by the
- *                 decode warps
- *   trellis ring  EXL3_PREFILL_T_STAGES x [matrix][step][group][8 tiles] (2048 bytes a row): bulk copies from HBM, the
- *                 longest latency, so the deepest ring */
-template <uint32_t MATRICES, uint32_t KSTEPS> struct prefill_rings {
+ *   B ring        EXL3_PREFILL_B_STAGES x [matrix] blocks of decoded weights, 128 GROUPS outputs x 16 KSTEPS FP16 in
+ *                 the same layout (one instruction multiplies all groups and reads the operand rows once): written by
+ *                 the decode warps, read by the products of EVERY row tile
+ *   trellis ring  EXL3_PREFILL_T_STAGES x [matrix][step][group][8 tiles] (1024 bytes a group): bulk copies from HBM */
+template <uint32_t MATRICES, uint32_t KSTEPS, uint32_t TILES, uint32_t GROUPS> struct prefill_rings {
 	static constexpr uint32_t block_bytes = KSTEPS * 4096u;
-	static constexpr uint32_t a_stage = MATRICES * block_bytes;
-	static constexpr uint32_t b_stage = MATRICES * PREFILL_GROUPS * block_bytes;
-	static constexpr uint32_t b_piece = PREFILL_GROUPS * 2048u; /* eight inputs of 256 outputs */
-	static constexpr uint32_t trellis_row = PREFILL_GROUPS * 1024u;
+	static constexpr uint32_t a_stage = TILES * MATRICES * block_bytes;
+	static constexpr uint32_t b_piece = GROUPS * 2048u; /* eight inputs of 128 GROUPS outputs */
+	static constexpr uint32_t b_block = GROUPS * block_bytes; /* of one matrix */
+	static constexpr uint32_t b_stage = MATRICES * b_block;
+	static constexpr uint32_t trellis_row = GROUPS * 1024u;
 	static constexpr uint32_t t_stage = MATRICES * KSTEPS * trellis_row;
 	static constexpr uint32_t b_at = EXL3_PREFILL_A_STAGES * a_stage;
 	static constexpr uint32_t t_at = b_at + EXL3_PREFILL_B_STAGES * b_stage;
 	static constexpr uint32_t bytes = t_at + EXL3_PREFILL_T_STAGES * t_stage;
-	static_assert(bytes == EXL3_PREFILL_DYNAMIC_BYTES, "the host sizes the rings");
-	static_assert(MATRICES * PREFILL_GROUPS * KSTEPS * 2u == PREFILL_DECODE_WARPS, "four tiles a decode warp");
+	static constexpr uint32_t columns = TILES * MATRICES * GROUPS * PREFILL_COLUMNS; /* of tensor memory */
+	static constexpr uint32_t stage_tiles = MATRICES * GROUPS * KSTEPS * EXL3_GROUP_TILES; /* decoded a stage */
+	static constexpr uint32_t warp_tiles = stage_tiles / PREFILL_DECODE_WARPS; /* adjacent tiles a decode warp */
+	static_assert(bytes <= EXL3_PREFILL_DYNAMIC_BYTES, "the host sizes the rings");
+	static_assert(columns <= 512u, "tensor memory has 512 columns");
+	static_assert(warp_tiles == 2u || warp_tiles == 4u, "a decode warp takes 2 or 4 adjacent tiles");
+	/* first column of the accumulator of (row tile, matrix, group) */
+	__device__ static constexpr uint32_t column(uint32_t tile, uint32_t m, uint32_t g)
+	{
+		return ((tile * MATRICES + m) * GROUPS + g) * PREFILL_COLUMNS;
+	}
 };
 
 /* The K loop of one CTA. matrices[m]: the codes of matrix m (`outputs` outputs), of which the CTA takes the `groups`
- * (1 or 2) groups of 128 outputs from group `first_group`; operand_blocks[m]: the row tile's operand blocks for matrix
- * m; `blocks` stages of 16 KSTEPS inputs. Warp 0 copies trellis rows, warp 1 operand blocks, one thread of warp 2
- * issues the products, warps 3 .. decode. On return the decode warps know whether the accumulators (matrix m, group g:
- * tensor-memory columns 128 (2 m + g) .. + 127 from shared->tensor_memory) are complete; the other warps return false.
+ * (1 .. GROUPS) groups of 128 outputs from group `first_group`; operand_blocks[tile * MATRICES + m]: row tile `tile`'s
+ * operand blocks for matrix m; `blocks` stages of 16 KSTEPS inputs. Warp 0 copies trellis rows, warp 1 operand blocks,
+ * one thread of warp 2 issues the products, warps 3 .. decode. On return the decode warps know whether the
+ * accumulators (prefill_rings::column from shared->tensor_memory) are complete; the other warps return false.
  * All threads call. */
-template <uint32_t BX2, uint32_t MATRICES, uint32_t KSTEPS>
+template <uint32_t BX2, uint32_t MATRICES, uint32_t KSTEPS, uint32_t TILES, uint32_t GROUPS>
 __device__ __forceinline__ bool prefill_products(const unsigned char *const (&matrices)[MATRICES], uint32_t outputs,
 						 uint32_t first_group, uint32_t groups,
-						 const unsigned char *const (&operand_blocks)[MATRICES], uint32_t blocks,
-						 unsigned char *dynamic_shared, prefill_shared *shared)
+						 const unsigned char *const (&operand_blocks)[TILES * MATRICES],
+						 uint32_t blocks, unsigned char *dynamic_shared, prefill_shared *shared)
 {
 	typedef exl3_ring<BX2> ring;
-	typedef prefill_rings<MATRICES, KSTEPS> rings;
+	typedef prefill_rings<MATRICES, KSTEPS, TILES, GROUPS> rings;
 	constexpr uint32_t AS = EXL3_PREFILL_A_STAGES, BS = EXL3_PREFILL_B_STAGES, TS = EXL3_PREFILL_T_STAGES;
 	constexpr uint32_t row_bytes = EXL3_GROUP_TILES * ring::tile_bytes; /* one group's part of a tile row */
 	const uint32_t lane = threadIdx.x % EXL3_WARP, warp = threadIdx.x / EXL3_WARP;
@@ -366,7 +376,7 @@ __device__ __forceinline__ bool prefill_products(const unsigned char *const (&ma
 	if (warp == 1) {
 		asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
 				     smem_address(&shared->tensor_memory)),
-			     "r"(MATRICES * PREFILL_GROUPS * PREFILL_COLUMNS)
+			     "r"(rings::columns)
 			     : "memory");
 		asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
 	}
@@ -407,7 +417,7 @@ __device__ __forceinline__ bool prefill_products(const unsigned char *const (&ma
 		return false;
 	}
 	if (warp == 1) {
-		/* operand copies: lane m copies matrix m's block */
+		/* operand copies: lane (tile, m) copies that block */
 		uint32_t block = 0;
 		for (; block < blocks; block++) {
 			const uint32_t stage = block % AS, use = block / AS;
@@ -421,7 +431,7 @@ __device__ __forceinline__ bool prefill_products(const unsigned char *const (&ma
 			good = __shfl_sync(0xFFFFFFFFu, good, 0);
 			if (good == 0)
 				break;
-			if (lane < MATRICES)
+			if (lane < TILES * MATRICES)
 				bulk_load(dynamic_shared + stage * rings::a_stage + lane * rings::block_bytes,
 					  operand_blocks[lane] + (uint64_t)block * rings::block_bytes, rings::block_bytes,
 					  &shared->a_full[stage]);
@@ -434,7 +444,7 @@ __device__ __forceinline__ bool prefill_products(const unsigned char *const (&ma
 		return false;
 	}
 	if (warp == 2) {
-		/* products: one thread */
+		/* products: one thread; every row tile's products read the same decoded weights */
 		if (lane == 0) {
 			bool good = true;
 			const uint32_t instruction = prefill_instruction(groups);
@@ -448,22 +458,23 @@ __device__ __forceinline__ bool prefill_products(const unsigned char *const (&ma
 				const uint32_t a_at = smem_address(dynamic_shared + sa * rings::a_stage);
 				const uint32_t b_at = smem_address(dynamic_shared + rings::b_at + sb * rings::b_stage);
 #pragma unroll
-				for (uint32_t m = 0; m < MATRICES; m++)
+				for (uint32_t tile = 0; tile < TILES; tile++)
 #pragma unroll
-					for (uint32_t step = 0; step < KSTEPS; step++) {
-						const uint64_t a =
-							prefill_descriptor(a_at + m * rings::block_bytes + step * 2u * 2048u, 2048u);
-						const uint64_t b = prefill_descriptor(b_at + m * PREFILL_GROUPS * rings::block_bytes +
-										      step * 2u * rings::b_piece,
-										      rings::b_piece);
-						const uint32_t accumulate = block > 0 || step > 0 ? 1u : 0u;
-						asm volatile("{\n\t.reg .pred p;\n\t"
-							     "setp.ne.b32 p, %4, 0;\n\t"
-							     "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(
-								     accumulators + m * PREFILL_GROUPS * PREFILL_COLUMNS),
-							     "l"(a), "l"(b), "r"(instruction), "r"(accumulate)
-							     : "memory");
-					}
+					for (uint32_t m = 0; m < MATRICES; m++)
+#pragma unroll
+						for (uint32_t step = 0; step < KSTEPS; step++) {
+							const uint64_t a = prefill_descriptor(
+								a_at + (tile * MATRICES + m) * rings::block_bytes + step * 2u * 2048u, 2048u);
+							const uint64_t b = prefill_descriptor(
+								b_at + m * rings::b_block + step * 2u * rings::b_piece, rings::b_piece);
+							const uint32_t accumulate = block > 0 || step > 0 ? 1u : 0u;
+							asm volatile("{\n\t.reg .pred p;\n\t"
+								     "setp.ne.b32 p, %4, 0;\n\t"
+								     "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(
+									     accumulators + rings::column(tile, m, 0)),
+								     "l"(a), "l"(b), "r"(instruction), "r"(accumulate)
+								     : "memory");
+						}
 				tensor_commit(&shared->a_free[sa]);
 				tensor_commit(&shared->b_free[sb]);
 				shared->issued = 1;
@@ -478,17 +489,18 @@ __device__ __forceinline__ bool prefill_products(const unsigned char *const (&ma
 		return false;
 	}
 
-	/* decode: warp d takes four adjacent output tiles of one (matrix, group, step) of the stage */
+	/* decode: warp d takes warp_tiles adjacent output tiles of one (matrix, group, step) of the stage */
 	{
+		constexpr uint32_t chunks = EXL3_GROUP_TILES / rings::warp_tiles;
 		const uint32_t decoder = warp - PREFILL_FIRST_DECODE_WARP;
-		const uint32_t quad = decoder % 2u, step = decoder / 2u % KSTEPS, g = decoder / (2u * KSTEPS) % PREFILL_GROUPS;
-		const uint32_t m = decoder / (2u * KSTEPS * PREFILL_GROUPS);
+		const uint32_t chunk = decoder % chunks, step = decoder / chunks % KSTEPS;
+		const uint32_t g = decoder / (chunks * KSTEPS) % GROUPS, m = decoder / (chunks * KSTEPS * GROUPS);
 		const uint32_t begin = ring::begin(lane);
 		const uint32_t word_index = begin / 32u, shift = begin % 32u, next_index = (word_index + 1u) % ring::words;
 		const uint32_t words_at = rings::t_at + (m * KSTEPS + step) * rings::trellis_row +
-					  (g * EXL3_GROUP_TILES + quad * 4u) * ring::tile_bytes;
-		const uint32_t to_at = rings::b_at + m * PREFILL_GROUPS * rings::block_bytes + step * 2u * rings::b_piece +
-				       (g * EXL3_GROUP_TILES + quad * 4u) * 2u * 128u + lane * 4u;
+					  (g * EXL3_GROUP_TILES + chunk * rings::warp_tiles) * ring::tile_bytes;
+		const uint32_t to_at = rings::b_at + m * rings::b_block + step * 2u * rings::b_piece +
+				       (g * EXL3_GROUP_TILES + chunk * rings::warp_tiles) * 2u * 128u + lane * 4u;
 		bool good = true;
 		for (uint32_t block = 0; block < blocks && good; block++) {
 			const uint32_t st = block % TS, sb = block % BS;
@@ -502,7 +514,7 @@ __device__ __forceinline__ bool prefill_products(const unsigned char *const (&ma
 					reinterpret_cast<const uint32_t *>(dynamic_shared + st * rings::t_stage + words_at);
 				unsigned char *const to_stage = dynamic_shared + sb * rings::b_stage + to_at;
 #pragma unroll
-				for (uint32_t mine = 0; mine < 4; mine++) {
+				for (uint32_t mine = 0; mine < rings::warp_tiles; mine++) {
 					uint32_t fragment[4];
 					exl3_decode_fragment<BX2>(words[mine * ring::words + word_index],
 								  words[mine * ring::words + next_index], shift, fragment);
@@ -532,10 +544,11 @@ __device__ __forceinline__ bool prefill_products(const unsigned char *const (&ma
 	}
 }
 
-/* The accumulator tiles (matrix m, group g) of every matrix into shared memory, FP32 [matrix][128 rows]
- * [EXL3_PREFILL_STAGING_ROW]. A warp reads the 32 tensor-memory lanes of its quarter (warp % 4) and one quarter of the
- * columns. Decode warps only; ends with their barrier. */
-__device__ __forceinline__ void prefill_stage_out(uint32_t accumulators, uint32_t matrices, uint32_t g, float *staging)
+/* `matrices` accumulator tiles (first columns first_column, first_column + column_stride, ...) into shared memory,
+ * FP32 [matrix][128 rows][EXL3_PREFILL_STAGING_ROW]. A warp reads the 32 tensor-memory lanes of its quarter (warp % 4)
+ * and one quarter of the columns. Decode warps only; ends with their barrier. */
+__device__ __forceinline__ void prefill_stage_out(uint32_t accumulators, uint32_t matrices, uint32_t first_column,
+						  uint32_t column_stride, float *staging)
 {
 	const uint32_t lane = threadIdx.x % EXL3_WARP, warp = threadIdx.x / EXL3_WARP;
 	const uint32_t quarter = warp % 4u, column = (warp - PREFILL_FIRST_DECODE_WARP) / 4u * 32u;
@@ -551,7 +564,7 @@ __device__ __forceinline__ void prefill_stage_out(uint32_t accumulators, uint32_
 			  "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]),
 			  "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]),
 			  "=r"(r[30]), "=r"(r[31])
-			: "r"(accumulators + ((quarter * 32u) << 16) + (m * PREFILL_GROUPS + g) * PREFILL_COLUMNS + column)
+			: "r"(accumulators + ((quarter * 32u) << 16) + first_column + m * column_stride + column)
 			: "memory");
 		asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 		uint4 *const to = reinterpret_cast<uint4 *>(
@@ -567,7 +580,7 @@ __device__ __forceinline__ void prefill_stage_out(uint32_t accumulators, uint32_
 
 /* All threads, at the end of a product CTA: wait (bounded) for what a failed CTA still has in flight, then free the
  * tensor memory. */
-template <uint32_t MATRICES> __device__ __forceinline__ void prefill_release(prefill_shared *shared)
+template <uint32_t COLUMNS> __device__ __forceinline__ void prefill_release(prefill_shared *shared)
 {
 	tensor_fence_before();
 	__syncthreads();
@@ -588,7 +601,7 @@ template <uint32_t MATRICES> __device__ __forceinline__ void prefill_release(pre
 		tensor_fence_after();
 		__syncwarp();
 		asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(shared->tensor_memory),
-			     "r"(MATRICES * PREFILL_GROUPS * PREFILL_COLUMNS)
+			     "r"(COLUMNS)
 			     : "memory");
 	}
 }
@@ -614,159 +627,229 @@ __device__ __forceinline__ prefill_tile_view prefill_tile_of(const struct exl3_p
 	return out;
 }
 
+/* An expert's row tiles are taken two at a time: the CTAs of an even-numbered tile that has a successor also take the
+ * successor's rows, so that every decoded weight is multiplied with 256 rows; the CTAs of an odd-numbered tile return. */
+#define PREFILL_SINGLE 0u
+#define PREFILL_FIRST_OF_TWO 1u
+#define PREFILL_SECOND_OF_TWO 2u
+__device__ __forceinline__ uint32_t prefill_pairing(const prefill_view &view, const struct exl3_prefill_tile &tile,
+						    uint32_t tile_index, uint32_t tile_count)
+{
+	if ((tile.first_entry / EXL3_PREFILL_TILE_ROWS) % 2u != 0u)
+		return PREFILL_SECOND_OF_TWO;
+	const struct exl3_prefill_tile *const tiles =
+		reinterpret_cast<const struct exl3_prefill_tile *>(view.workspace + view.parts.tiles);
+	return tile_index + 1u < tile_count && tiles[tile_index + 1u].expert == tile.expert ? PREFILL_FIRST_OF_TWO :
+											       PREFILL_SINGLE;
+}
+
+/* The gate/up epilogue of one row tile and one group of 128 outputs, from the staged accumulators (gate rows, then up
+ * rows): Hadamard, scales, SwiGLU, down-side transform, FP16 down operand blocks. Decode warps; a warp a row. */
 template <uint32_t BX2>
-__device__ __forceinline__ void prefill_gate_up(const struct exl3_prefill_record &record, unsigned char *arena,
-						const prefill_view &view, const prefill_tile_view &tile,
-						unsigned char *dynamic_shared, prefill_shared *shared)
+__device__ __forceinline__ void prefill_gate_up_rows(const struct exl3_prefill_record &record, unsigned char *arena,
+						     const prefill_view &view, const prefill_tile_view &tile,
+						     uint32_t tile_index, uint32_t group, const float *staging)
 {
 	const uint32_t H = record.input_size, I = prefill_inner_of(record, tile.tile.expert);
-	const uint32_t first_group = blockIdx.x * PREFILL_GROUPS, tile_index = blockIdx.y;
-	const uint32_t groups = min(PREFILL_GROUPS, I / EXL3_TRANSFORM - first_group);
 	const uint32_t lane = threadIdx.x % EXL3_WARP, warp = threadIdx.x / EXL3_WARP;
-	const unsigned char *const matrices[2] = { arena + tile.gate, arena + tile.up };
+	const uint32_t channel = group * EXL3_TRANSFORM + lane * 4u;
+	const uint64_t codes = exl3_code_bytes(H, I, BX2);
+	float gate_scale[4], up_scale[4], down_scale[4];
+	load_half4(reinterpret_cast<const __half *>(arena + tile.gate + codes) + H + channel, gate_scale);
+	load_half4(reinterpret_cast<const __half *>(arena + tile.up + codes) + H + channel, up_scale);
+	load_half4(reinterpret_cast<const __half *>(arena + tile.down + exl3_code_bytes(I, H, BX2)) + channel, down_scale);
+	unsigned char *const blocks = view.workspace + view.parts.down_operands +
+				      ((uint64_t)tile_index * (view.widest / EXL3_PREFILL_BLOCK_INPUTS) +
+				       channel / EXL3_PREFILL_BLOCK_INPUTS) *
+					      EXL3_PREFILL_BLOCK_BYTES;
+	for (uint32_t row = warp - PREFILL_FIRST_DECODE_WARP; row < tile.tile.row_count; row += PREFILL_DECODE_WARPS) {
+		const float4 gate_raw = *reinterpret_cast<const float4 *>(staging + row * EXL3_PREFILL_STAGING_ROW + lane * 4u);
+		const float4 up_raw = *reinterpret_cast<const float4 *>(
+			staging + (EXL3_PREFILL_TILE_ROWS + row) * EXL3_PREFILL_STAGING_ROW + lane * 4u);
+		float gate[4] = { gate_raw.x, gate_raw.y, gate_raw.z, gate_raw.w };
+		float up[4] = { up_raw.x, up_raw.y, up_raw.z, up_raw.w };
+		hadamard128_warp(gate, lane);
+		hadamard128_warp(up, lane);
+		float hidden[4], fed[4];
+		exl3_swiglu4(gate, up, gate_scale, up_scale, record.activation_limit, hidden);
+#pragma unroll
+		for (uint32_t i = 0; i < 4; i++)
+			fed[i] = __fmul_rn(hidden[i], down_scale[i]);
+		hadamard128_warp(fed, lane);
+#pragma unroll
+		for (uint32_t i = 0; i < 4; i++)
+			fed[i] = __fmul_rn(fed[i], EXL3_NORMALIZATION);
+		store_half4(reinterpret_cast<__half *>(blocks + prefill_block_byte(row, channel % EXL3_PREFILL_BLOCK_INPUTS)),
+			    fed);
+	}
+}
+
+/* TILES row tiles (tile_index, tile_index + 1) of one expert by GROUPS groups of 128 outputs from first_group */
+template <uint32_t BX2, uint32_t TILES, uint32_t GROUPS>
+__device__ __forceinline__ void prefill_gate_up(const struct exl3_prefill_record &record, unsigned char *arena,
+						const prefill_view &view, uint32_t tile_index, uint32_t first_group,
+						unsigned char *dynamic_shared, prefill_shared *shared)
+{
+	typedef prefill_rings<2, EXL3_PREFILL_GATE_UP_STEPS, TILES, GROUPS> rings;
+	prefill_tile_view tiles[TILES];
+#pragma unroll
+	for (uint32_t tile = 0; tile < TILES; tile++)
+		tiles[tile] = prefill_tile_of(record, arena, view, tile_index + tile);
+	const uint32_t H = record.input_size, I = prefill_inner_of(record, tiles[0].tile.expert);
+	const uint32_t groups = min(GROUPS, I / EXL3_TRANSFORM - first_group);
+	const uint32_t warp = threadIdx.x / EXL3_WARP;
+	const unsigned char *const matrices[2] = { arena + tiles[0].gate, arena + tiles[0].up };
 	const uint64_t tile_bytes = (uint64_t)(H / EXL3_PREFILL_BLOCK_INPUTS) * EXL3_PREFILL_BLOCK_BYTES;
-	const unsigned char *const operands[2] = {
-		view.workspace + view.parts.gate_up_operands + tile_index * tile_bytes,
-		view.workspace + view.parts.gate_up_operands + ((uint64_t)view.parts.tile_capacity + tile_index) * tile_bytes
-	};
-	const bool complete = prefill_products<BX2, 2, EXL3_PREFILL_GATE_UP_STEPS>(
+	const unsigned char *operands[TILES * 2];
+#pragma unroll
+	for (uint32_t tile = 0; tile < TILES; tile++) {
+		operands[tile * 2u] = view.workspace + view.parts.gate_up_operands + (tile_index + tile) * tile_bytes;
+		operands[tile * 2u + 1u] = view.workspace + view.parts.gate_up_operands +
+					   ((uint64_t)view.parts.tile_capacity + tile_index + tile) * tile_bytes;
+	}
+	const bool complete = prefill_products<BX2, 2, EXL3_PREFILL_GATE_UP_STEPS, TILES, GROUPS>(
 		matrices, I, first_group, groups, operands, H / (EXL3_PREFILL_GATE_UP_STEPS * EXL3_TILE), dynamic_shared,
 		shared);
 	if (warp >= PREFILL_FIRST_DECODE_WARP && complete) {
 		float *const staging = reinterpret_cast<float *>(dynamic_shared);
-		const uint64_t codes = exl3_code_bytes(H, I, BX2);
-		for (uint32_t g = 0; g < groups; g++) {
-			prefill_stage_out(shared->tensor_memory, 2, g, staging);
-			const uint32_t channel = (first_group + g) * EXL3_TRANSFORM + lane * 4u;
-			float gate_scale[4], up_scale[4], down_scale[4];
-			load_half4(reinterpret_cast<const __half *>(arena + tile.gate + codes) + H + channel, gate_scale);
-			load_half4(reinterpret_cast<const __half *>(arena + tile.up + codes) + H + channel, up_scale);
-			load_half4(reinterpret_cast<const __half *>(arena + tile.down + exl3_code_bytes(I, H, BX2)) + channel,
-				   down_scale);
-			unsigned char *const blocks = view.workspace + view.parts.down_operands +
-						      ((uint64_t)tile_index * (view.widest / EXL3_PREFILL_BLOCK_INPUTS) +
-						       channel / EXL3_PREFILL_BLOCK_INPUTS) *
-							      EXL3_PREFILL_BLOCK_BYTES;
-			for (uint32_t row = warp - PREFILL_FIRST_DECODE_WARP; row < tile.tile.row_count; row += PREFILL_DECODE_WARPS) {
-				const float4 gate_raw =
-					*reinterpret_cast<const float4 *>(staging + row * EXL3_PREFILL_STAGING_ROW + lane * 4u);
-				const float4 up_raw = *reinterpret_cast<const float4 *>(
-					staging + (EXL3_PREFILL_TILE_ROWS + row) * EXL3_PREFILL_STAGING_ROW + lane * 4u);
-				float gate[4] = { gate_raw.x, gate_raw.y, gate_raw.z, gate_raw.w };
-				float up[4] = { up_raw.x, up_raw.y, up_raw.z, up_raw.w };
-				hadamard128_warp(gate, lane);
-				hadamard128_warp(up, lane);
-				float hidden[4], fed[4];
-				exl3_swiglu4(gate, up, gate_scale, up_scale, record.activation_limit, hidden);
-#pragma unroll
-				for (uint32_t i = 0; i < 4; i++)
-					fed[i] = __fmul_rn(hidden[i], down_scale[i]);
-				hadamard128_warp(fed, lane);
-#pragma unroll
-				for (uint32_t i = 0; i < 4; i++)
-					fed[i] = __fmul_rn(fed[i], EXL3_NORMALIZATION);
-				store_half4(reinterpret_cast<__half *>(
-						    blocks + prefill_block_byte(row, channel % EXL3_PREFILL_BLOCK_INPUTS)),
-					    fed);
+		for (uint32_t tile = 0; tile < TILES; tile++)
+			for (uint32_t g = 0; g < groups; g++) {
+				prefill_stage_out(shared->tensor_memory, 2, rings::column(tile, 0, g), rings::column(0, 1, 0),
+						  staging);
+				prefill_gate_up_rows<BX2>(record, arena, view, tiles[tile], tile_index + tile, first_group + g,
+							  staging);
+				decode_sync(); /* the staging rows are read: the next tile may overwrite them */
 			}
-			decode_sync(); /* the staging rows are read: the next group may overwrite them */
-		}
 	}
-	prefill_release<2>(shared);
+	prefill_release<rings::columns>(shared);
 }
 
-template <uint32_t BX2>
+template <uint32_t BX2, uint32_t TILES, uint32_t KSTEPS>
 __device__ __forceinline__ void prefill_down(const struct exl3_prefill_record &record, unsigned char *arena,
-					     const prefill_view &view, const prefill_tile_view &tile,
+					     const prefill_view &view, uint32_t tile_index, uint32_t first_group,
 					     unsigned char *dynamic_shared, prefill_shared *shared)
 {
-	const uint32_t H = record.input_size, I = prefill_inner_of(record, tile.tile.expert);
-	const uint32_t first_group = blockIdx.x * PREFILL_GROUPS, tile_index = blockIdx.y;
+	typedef prefill_rings<1, KSTEPS, TILES, PREFILL_GROUPS> rings;
+	prefill_tile_view tiles[TILES];
+#pragma unroll
+	for (uint32_t tile = 0; tile < TILES; tile++)
+		tiles[tile] = prefill_tile_of(record, arena, view, tile_index + tile);
+	const uint32_t H = record.input_size, I = prefill_inner_of(record, tiles[0].tile.expert);
 	const uint32_t groups = min(PREFILL_GROUPS, H / EXL3_TRANSFORM - first_group);
 	const uint32_t lane = threadIdx.x % EXL3_WARP, warp = threadIdx.x / EXL3_WARP;
-	const unsigned char *const matrices[1] = { arena + tile.down };
-	const unsigned char *const operands[1] = { view.workspace + view.parts.down_operands +
-						   (uint64_t)tile_index * (view.widest / EXL3_PREFILL_BLOCK_INPUTS) *
-							   EXL3_PREFILL_BLOCK_BYTES };
-	const bool complete = prefill_products<BX2, 1, EXL3_PREFILL_DOWN_STEPS>(
-		matrices, H, first_group, groups, operands, I / (EXL3_PREFILL_DOWN_STEPS * EXL3_TILE), dynamic_shared, shared);
+	const unsigned char *const matrices[1] = { arena + tiles[0].down };
+	const unsigned char *operands[TILES];
+#pragma unroll
+	for (uint32_t tile = 0; tile < TILES; tile++)
+		operands[tile] = view.workspace + view.parts.down_operands +
+				 (uint64_t)(tile_index + tile) * (view.widest / EXL3_PREFILL_BLOCK_INPUTS) *
+					 EXL3_PREFILL_BLOCK_BYTES;
+	const bool complete = prefill_products<BX2, 1, KSTEPS, TILES, PREFILL_GROUPS>(
+		matrices, H, first_group, groups, operands, I / (KSTEPS * EXL3_TILE), dynamic_shared, shared);
 	if (warp >= PREFILL_FIRST_DECODE_WARP && complete) {
 		float *const staging = reinterpret_cast<float *>(dynamic_shared);
 		float *const outputs = reinterpret_cast<float *>(arena + record.pair_output_offset);
-		for (uint32_t g = 0; g < groups; g++) {
-			prefill_stage_out(shared->tensor_memory, 1, g, staging);
-			const uint32_t channel = (first_group + g) * EXL3_TRANSFORM + lane * 4u;
-			float scale[4];
-			load_half4(reinterpret_cast<const __half *>(arena + tile.down + exl3_code_bytes(I, H, BX2)) + I +
-					   channel,
-				   scale);
-			for (uint32_t row = warp - PREFILL_FIRST_DECODE_WARP; row < tile.tile.row_count; row += PREFILL_DECODE_WARPS) {
-				const struct exl3_prefill_entry entry = tile.entries[row];
-				const float4 raw =
-					*reinterpret_cast<const float4 *>(staging + row * EXL3_PREFILL_STAGING_ROW + lane * 4u);
-				float v[4] = { raw.x, raw.y, raw.z, raw.w };
-				hadamard128_warp(v, lane);
+		for (uint32_t tile = 0; tile < TILES; tile++)
+			for (uint32_t g = 0; g < groups; g++) {
+				prefill_stage_out(shared->tensor_memory, 1, rings::column(tile, 0, g), 0, staging);
+				const uint32_t channel = (first_group + g) * EXL3_TRANSFORM + lane * 4u;
+				float scale[4];
+				load_half4(reinterpret_cast<const __half *>(arena + tiles[tile].down + exl3_code_bytes(I, H, BX2)) +
+						   I + channel,
+					   scale);
+				for (uint32_t row = warp - PREFILL_FIRST_DECODE_WARP; row < tiles[tile].tile.row_count;
+				     row += PREFILL_DECODE_WARPS) {
+					const struct exl3_prefill_entry entry = tiles[tile].entries[row];
+					const float4 raw = *reinterpret_cast<const float4 *>(
+						staging + row * EXL3_PREFILL_STAGING_ROW + lane * 4u);
+					float v[4] = { raw.x, raw.y, raw.z, raw.w };
+					hadamard128_warp(v, lane);
 #pragma unroll
-				for (uint32_t i = 0; i < 4; i++)
-					v[i] = __fmul_rn(__fmul_rn(__fmul_rn(v[i], EXL3_NORMALIZATION), scale[i]),
-							 entry.route_weight);
-				*reinterpret_cast<float4 *>(outputs + (uint64_t)entry.pair * H + channel) =
-					make_float4(v[0], v[1], v[2], v[3]);
+					for (uint32_t i = 0; i < 4; i++)
+						v[i] = __fmul_rn(__fmul_rn(__fmul_rn(v[i], EXL3_NORMALIZATION), scale[i]),
+								 entry.route_weight);
+					*reinterpret_cast<float4 *>(outputs + (uint64_t)entry.pair * H + channel) =
+						make_float4(v[0], v[1], v[2], v[3]);
+				}
+				decode_sync();
 			}
-			decode_sync();
-		}
 	}
-	prefill_release<1>(shared);
+	prefill_release<rings::columns>(shared);
 }
 
-#define PREFILL_WIDTH_SWITCH(function)                                                     \
-	switch (exl3_bits_x2(reinterpret_cast<const uint32_t *>(arena + record.widths_offset)[tile.tile.expert])) { \
-	case EXL3_BITS_X2_K2:                                                              \
-		function<EXL3_BITS_X2_K2>(record, arena, view, tile, dynamic_shared, &shared);   \
-		break;                                                                     \
-	case EXL3_BITS_X2_K2_5:                                                            \
-		function<EXL3_BITS_X2_K2_5>(record, arena, view, tile, dynamic_shared, &shared); \
-		break;                                                                     \
-	case EXL3_BITS_X2_K3:                                                              \
-		function<EXL3_BITS_X2_K3>(record, arena, view, tile, dynamic_shared, &shared);   \
-		break;                                                                     \
-	case EXL3_BITS_X2_K4:                                                              \
-		function<EXL3_BITS_X2_K4>(record, arena, view, tile, dynamic_shared, &shared);   \
-		break;                                                                     \
-	default:                                                                           \
-		break;                                                                     \
+#define PREFILL_WIDTH_SWITCH(call)                                                                     \
+	switch (exl3_bits_x2(reinterpret_cast<const uint32_t *>(arena + record.widths_offset)[tile.expert])) { \
+	case EXL3_BITS_X2_K2: {                                                                        \
+		constexpr uint32_t BX2 = EXL3_BITS_X2_K2;                                              \
+		call;                                                                                  \
+	} break;                                                                                       \
+	case EXL3_BITS_X2_K2_5: {                                                                      \
+		constexpr uint32_t BX2 = EXL3_BITS_X2_K2_5;                                            \
+		call;                                                                                  \
+	} break;                                                                                       \
+	case EXL3_BITS_X2_K3: {                                                                        \
+		constexpr uint32_t BX2 = EXL3_BITS_X2_K3;                                              \
+		call;                                                                                  \
+	} break;                                                                                       \
+	case EXL3_BITS_X2_K4: {                                                                        \
+		constexpr uint32_t BX2 = EXL3_BITS_X2_K4;                                              \
+		call;                                                                                  \
+	} break;                                                                                       \
+	default:                                                                                       \
+		break;                                                                                 \
 	}
 
-/* grid (ceil(widest I / 256), tile capacity) x 608 */
+/* grid (widest I / 128, tile capacity) x 608: a single row tile is taken by the CTAs of even x with two groups of 128
+ * outputs each; two row tiles of one expert by every x with one group each (tensor memory holds 512 columns) */
 extern "C" __global__ void __launch_bounds__(EXL3_PREFILL_GEMM_THREADS, 1)
 	exl3_prefill_gate_up(struct exl3_prefill_record record, unsigned char *arena)
 {
 	extern __shared__ __align__(1024) unsigned char dynamic_shared[];
 	__shared__ prefill_shared shared;
 	const prefill_view view = prefill_view_of(record, arena);
+	const uint32_t tile_count = reinterpret_cast<const uint32_t *>(view.workspace + view.parts.counts)[view.experts];
 	/* once a wait has run out (the flag is never cleared while the kernel file stays loaded), later CTAs do not
 	 * queue up behind the same fault: the host reads the flag and rejects the result */
-	if (*reinterpret_cast<volatile unsigned int *>(&exl3_wait_expired) != 0u ||
-	    blockIdx.y >= reinterpret_cast<const uint32_t *>(view.workspace + view.parts.counts)[view.experts])
+	if (*reinterpret_cast<volatile unsigned int *>(&exl3_wait_expired) != 0u || blockIdx.y >= tile_count)
 		return;
-	const prefill_tile_view tile = prefill_tile_of(record, arena, view, blockIdx.y);
-	if (blockIdx.x * PREFILL_GROUPS >= prefill_inner_of(record, tile.tile.expert) / EXL3_TRANSFORM)
-		return; /* the grid is as wide as the widest expert */
-	PREFILL_WIDTH_SWITCH(prefill_gate_up)
+	const struct exl3_prefill_tile tile =
+		reinterpret_cast<const struct exl3_prefill_tile *>(view.workspace + view.parts.tiles)[blockIdx.y];
+	const uint32_t pairing = prefill_pairing(view, tile, blockIdx.y, tile_count);
+	const uint32_t group_count = prefill_inner_of(record, tile.expert) / EXL3_TRANSFORM;
+	if (pairing == PREFILL_SECOND_OF_TWO || blockIdx.x >= group_count ||
+	    (pairing == PREFILL_SINGLE && blockIdx.x % PREFILL_GROUPS != 0u))
+		return;
+	if (pairing == PREFILL_FIRST_OF_TWO) {
+		PREFILL_WIDTH_SWITCH((prefill_gate_up<BX2, 2, 1>(record, arena, view, blockIdx.y, blockIdx.x, dynamic_shared,
+								 &shared)))
+	} else {
+		PREFILL_WIDTH_SWITCH((prefill_gate_up<BX2, 1, PREFILL_GROUPS>(record, arena, view, blockIdx.y, blockIdx.x,
+									      dynamic_shared, &shared)))
+	}
 }
 
-/* grid (ceil(H / 256), tile capacity) x 608 */
+/* grid (ceil(H / 256), tile capacity) x 608: two groups of 128 outputs a CTA, for one row tile or for two of one expert */
 extern "C" __global__ void __launch_bounds__(EXL3_PREFILL_GEMM_THREADS, 1)
 	exl3_prefill_down(struct exl3_prefill_record record, unsigned char *arena)
 {
 	extern __shared__ __align__(1024) unsigned char dynamic_shared[];
 	__shared__ prefill_shared shared;
 	const prefill_view view = prefill_view_of(record, arena);
-	if (*reinterpret_cast<volatile unsigned int *>(&exl3_wait_expired) != 0u ||
-	    blockIdx.y >= reinterpret_cast<const uint32_t *>(view.workspace + view.parts.counts)[view.experts])
+	const uint32_t tile_count = reinterpret_cast<const uint32_t *>(view.workspace + view.parts.counts)[view.experts];
+	if (*reinterpret_cast<volatile unsigned int *>(&exl3_wait_expired) != 0u || blockIdx.y >= tile_count)
 		return;
-	const prefill_tile_view tile = prefill_tile_of(record, arena, view, blockIdx.y);
-	PREFILL_WIDTH_SWITCH(prefill_down)
+	const struct exl3_prefill_tile tile =
+		reinterpret_cast<const struct exl3_prefill_tile *>(view.workspace + view.parts.tiles)[blockIdx.y];
+	const uint32_t pairing = prefill_pairing(view, tile, blockIdx.y, tile_count);
+	if (pairing == PREFILL_SECOND_OF_TWO)
+		return;
+	if (pairing == PREFILL_FIRST_OF_TWO) {
+		PREFILL_WIDTH_SWITCH((prefill_down<BX2, 2, EXL3_PREFILL_GATE_UP_STEPS>(
+			record, arena, view, blockIdx.y, blockIdx.x * PREFILL_GROUPS, dynamic_shared, &shared)))
+	} else {
+		PREFILL_WIDTH_SWITCH((prefill_down<BX2, 1, EXL3_PREFILL_DOWN_STEPS>(
+			record, arena, view, blockIdx.y, blockIdx.x * PREFILL_GROUPS, dynamic_shared, &shared)))
+	}
 }
 
 /* grid (ceil(H / 512), row capacity) x 128: FP32 row sums over the row's local pairs from +0 in ascending slot order,
