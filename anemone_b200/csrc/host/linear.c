@@ -83,6 +83,16 @@ result_status linear_kernels_prepare(const struct backend_operations *backend, s
 	if (status == STATUS_OK)
 		status = backend->kernel_prepare(card, KERNEL_FILE_EXPERT_LINEAR, KERNEL_EXPERT_ROW_SUM,
 						 sizeof(struct expert_row_sum_arguments), &kernels.expert_row_sum);
+	for (uint32_t instance = 0; status == STATUS_OK && instance < LINEAR_SLICE_INSTANCES; instance++) {
+		char name[48];
+		(void)snprintf(name, sizeof(name), KERNEL_TRUNK_LINEAR_QUANTIZED_STEM "%u", slice_counts[instance]);
+		status = backend->kernel_prepare(card, KERNEL_FILE_TRUNK_LINEAR, name,
+						 sizeof(struct trunk_linear_quantized_arguments),
+						 &kernels.trunk_linear_quantized[instance]);
+	}
+	if (status == STATUS_OK)
+		status = backend->kernel_prepare(card, KERNEL_FILE_TRUNK_LINEAR, KERNEL_TRUNK_HIDDEN_VALUE,
+						 sizeof(struct trunk_hidden_arguments), &kernels.trunk_hidden);
 	if (status != STATUS_OK) {
 		(void)fprintf(stderr, "linear kernels: a kernel could not be prepared (%s)\n", status_text(status));
 		return status;
@@ -221,5 +231,147 @@ result_status linear_routed_experts_prepare(const struct linear_routed_experts_d
 			    (H + LINEAR_ELEMENT_THREADS - 1u) / LINEAR_ELEMENT_THREADS, description->row_count, 1,
 			    LINEAR_ELEMENT_THREADS, 0, &sum_arguments, sizeof(sum_arguments));
 	memcpy(launches_out, launches, sizeof(launches));
+	return STATUS_OK;
+}
+
+static result_status e4m3_stored_byte_count(const struct matrix_shape_record *shape, uint64_t *byte_count_out)
+{
+	if (shape == NULL || byte_count_out == NULL || shape->reserved_must_be_zero != 0 || shape->bits_per_weight != 8 ||
+	    shape->output_size == 0 || shape->input_size == 0 || shape->output_size % LINEAR_OUTPUTS_PER_TILE != 0 ||
+	    shape->input_size % LINEAR_VALUES_PER_BLOCK != 0)
+		return STATUS_INVALID_ARGUMENT;
+	*byte_count_out = e4m3_scaled_byte_count(shape->output_size, shape->input_size);
+	return STATUS_OK;
+}
+
+const struct weight_format_operations e4m3_scaled_weight_operations = { .name = "e4m3_scaled",
+									 .stored_byte_count = e4m3_stored_byte_count };
+
+/* a stored E4M3 matrix the trunk kernels can take: its exact bytes, whole loads of 64 inputs, a slice count on offer */
+static uint32_t trunk_matrix_instance(const struct linear_matrix *matrix, const struct linear_kernels_record *kernels)
+{
+	uint64_t bytes = 0;
+	if (matrix->weight_format != WEIGHT_FORMAT_E4M3_SCALED || matrix->reserved_zero != 0 || matrix->wide_form != 0 ||
+	    e4m3_stored_byte_count(&matrix->shape, &bytes) != STATUS_OK || matrix->stored.byte_count != bytes ||
+	    matrix->shape.input_size % LINEAR_VALUES_PER_LOAD != 0 ||
+	    matrix->stored.byte_offset % WEIGHT_FORMAT_MATRIX_ALIGNMENT_BYTES != 0)
+		return LINEAR_SLICE_INSTANCES;
+	const uint32_t instance = slice_instance(matrix->slice_count, matrix->shape.input_size);
+	return instance < LINEAR_SLICE_INSTANCES && kernels->trunk_linear_quantized[instance] != BACKEND_NO_KERNEL ?
+		       instance :
+		       LINEAR_SLICE_INSTANCES;
+}
+
+result_status linear_shared_expert_prepare(const struct linear_shared_expert_description *description,
+					   uint64_t arena_byte_count, const struct linear_kernels_record *kernels,
+					   struct kernel_launch *launches_out)
+{
+	if (description == NULL || kernels == NULL || launches_out == NULL || description->row_count == 0 ||
+	    description->row_count > LINEAR_MAXIMUM_ROWS || !isfinite(description->activation_limit) ||
+	    description->activation_limit <= 0 || kernels->trunk_hidden == BACKEND_NO_KERNEL ||
+	    kernels->activation_quantize == BACKEND_NO_KERNEL)
+		return STATUS_INVALID_ARGUMENT;
+	const struct linear_matrix *const gate = &description->gate, *const up = &description->up,
+				   *const down = &description->down;
+	const uint32_t gate_instance = trunk_matrix_instance(gate, kernels), up_instance = trunk_matrix_instance(up, kernels);
+	const uint32_t down_instance = trunk_matrix_instance(down, kernels);
+	if (gate_instance == LINEAR_SLICE_INSTANCES || up_instance != gate_instance ||
+	    down_instance == LINEAR_SLICE_INSTANCES || gate->shape.input_size != up->shape.input_size ||
+	    gate->shape.output_size != up->shape.output_size || down->shape.input_size != gate->shape.output_size)
+		return STATUS_INVALID_ARGUMENT;
+	const uint64_t rows = description->row_count;
+	const uint32_t H = gate->shape.input_size, I = gate->shape.output_size, O = down->shape.output_size;
+	if (!range_holds(&description->codes, linear_codes_byte_count(rows, H)) ||
+	    !range_holds(&description->exponents, linear_exponents_byte_count(rows, H)) ||
+	    !range_holds(&description->operands, linear_values_byte_count(rows, H)) ||
+	    !range_holds(&description->gate_output, linear_values_byte_count(rows, I)) ||
+	    !range_holds(&description->up_output, linear_values_byte_count(rows, I)) ||
+	    !range_holds(&description->hidden, linear_values_byte_count(rows, I)) ||
+	    !range_holds(&description->hidden_codes, linear_codes_byte_count(rows, I)) ||
+	    !range_holds(&description->hidden_exponents, linear_exponents_byte_count(rows, I)) ||
+	    !range_holds(&description->hidden_operands, linear_values_byte_count(rows, I)) ||
+	    !range_holds(&description->output, linear_values_byte_count(rows, O)))
+		return STATUS_INVALID_ARGUMENT;
+	const struct linear_range *const all[13] = { &gate->stored, &up->stored, &down->stored, &description->codes,
+						     &description->exponents, &description->operands,
+						     &description->gate_output, &description->up_output,
+						     &description->hidden, &description->hidden_codes,
+						     &description->hidden_exponents, &description->hidden_operands,
+						     &description->output };
+	static const char *const names[13] = { "gate", "up", "down", "codes", "exponents", "operands", "gate output",
+					       "up output", "hidden", "hidden codes", "hidden exponents",
+					       "hidden operands", "output" };
+	struct checked_range ranges[13];
+	for (uint32_t index = 0; index < 13; index++)
+		ranges[index] = (struct checked_range){ names[index], all[index]->byte_offset, all[index]->byte_count };
+	if (!prepare_ranges_are_valid("shared expert", ranges, 13, arena_byte_count))
+		return STATUS_INVALID_ARGUMENT;
+	const struct trunk_linear_quantized_arguments gate_up_arguments = {
+		{ gate->stored.byte_offset, up->stored.byte_offset },
+		{ description->gate_output.byte_offset, description->up_output.byte_offset },
+		description->codes.byte_offset,
+		description->exponents.byte_offset,
+		description->operands.byte_offset,
+		{ I, I },
+		H,
+		description->row_count
+	};
+	const struct trunk_hidden_arguments hidden_arguments = { description->gate_output.byte_offset,
+								 description->up_output.byte_offset,
+								 description->hidden.byte_offset, I,
+								 description->activation_limit };
+	const struct activation_quantize_arguments quantize_arguments = { description->hidden.byte_offset,
+									   description->hidden_codes.byte_offset,
+									   description->hidden_exponents.byte_offset,
+									   description->hidden_operands.byte_offset, I, 0 };
+	const struct trunk_linear_quantized_arguments down_arguments = { { down->stored.byte_offset, 0 },
+									 { description->output.byte_offset, 0 },
+									 description->hidden_codes.byte_offset,
+									 description->hidden_exponents.byte_offset,
+									 description->hidden_operands.byte_offset,
+									 { O, 0 },
+									 I,
+									 description->row_count };
+	struct kernel_launch launches[LINEAR_SHARED_EXPERT_LAUNCH_COUNT];
+	prepare_launch_fill(&launches[LINEAR_SHARED_EXPERT_GATE_UP], kernels->trunk_linear_quantized[gate_instance],
+			    2u * I / LINEAR_OUTPUTS_PER_TILE, 1, 1, 32u * gate->slice_count, 0, &gate_up_arguments,
+			    sizeof(gate_up_arguments));
+	prepare_launch_fill(&launches[LINEAR_SHARED_EXPERT_HIDDEN], kernels->trunk_hidden,
+			    (I + LINEAR_ELEMENT_THREADS - 1u) / LINEAR_ELEMENT_THREADS, description->row_count, 1,
+			    LINEAR_ELEMENT_THREADS, 0, &hidden_arguments, sizeof(hidden_arguments));
+	prepare_launch_fill(&launches[LINEAR_SHARED_EXPERT_QUANTIZE], kernels->activation_quantize,
+			    I / LINEAR_VALUES_PER_LOAD, description->row_count, 1, 32, 0, &quantize_arguments,
+			    sizeof(quantize_arguments));
+	prepare_launch_fill(&launches[LINEAR_SHARED_EXPERT_DOWN], kernels->trunk_linear_quantized[down_instance],
+			    O / LINEAR_OUTPUTS_PER_TILE, 1, 1, 32u * down->slice_count, 0, &down_arguments,
+			    sizeof(down_arguments));
+	memcpy(launches_out, launches, sizeof(launches));
+	return STATUS_OK;
+}
+
+result_status linear_rows_add_prepare(const struct linear_range *sums, const struct linear_range *values,
+				      uint32_t width, uint32_t row_count, uint64_t arena_byte_count,
+				      const struct backend_operations *backend, struct device_card *card,
+				      struct kernel_launch *launch_out)
+{
+	if (sums == NULL || values == NULL || backend == NULL || backend->kernel_prepare == NULL || card == NULL ||
+	    launch_out == NULL || width == 0 || row_count == 0 || row_count > 65535u ||
+	    !range_holds(sums, linear_sums_byte_count(row_count, width)) ||
+	    !range_holds(values, linear_values_byte_count(row_count, width)))
+		return STATUS_INVALID_ARGUMENT;
+	const struct checked_range ranges[2] = { { "sums", sums->byte_offset, sums->byte_count },
+						 { "values", values->byte_offset, values->byte_count } };
+	if (!prepare_ranges_are_valid("rows add", ranges, 2, arena_byte_count))
+		return STATUS_INVALID_ARGUMENT;
+	uint32_t kernel = BACKEND_NO_KERNEL;
+	const result_status status = backend->kernel_prepare(card, KERNEL_FILE_TRUNK_LINEAR, KERNEL_TRUNK_ROWS_ADD,
+							     sizeof(struct trunk_rows_add_arguments), &kernel);
+	if (status != STATUS_OK)
+		return status;
+	if (kernel == BACKEND_NO_KERNEL)
+		return STATUS_UNSUPPORTED;
+	const struct trunk_rows_add_arguments arguments = { sums->byte_offset, values->byte_offset, width, 0 };
+	prepare_launch_fill(launch_out, kernel, (width + LINEAR_ELEMENT_THREADS - 1u) / LINEAR_ELEMENT_THREADS, row_count,
+			    1, LINEAR_ELEMENT_THREADS, 0, &arguments, sizeof(arguments));
 	return STATUS_OK;
 }

@@ -172,6 +172,34 @@ class LinearRoutedExpertsDescription(C.Structure):
                 ("activation_limit", C.c_float), ("reserved_zero", C.c_uint32)]
 
 
+class TrunkLinearQuantized(C.Structure):
+    _fields_ = [("weights_offset", C.c_uint64 * 2), ("output_offset", C.c_uint64 * 2), ("codes_offset", C.c_uint64),
+                ("exponents_offset", C.c_uint64), ("operands_offset", C.c_uint64), ("output_size", C.c_uint32 * 2),
+                ("input_size", C.c_uint32), ("row_count", C.c_uint32)]
+
+
+class TrunkHidden(C.Structure):
+    _fields_ = [("gate_offset", C.c_uint64), ("up_offset", C.c_uint64), ("hidden_offset", C.c_uint64),
+                ("width", C.c_uint32), ("activation_limit", C.c_float)]
+
+
+class TrunkRowsAdd(C.Structure):
+    _fields_ = [("sums_offset", C.c_uint64), ("values_offset", C.c_uint64), ("width", C.c_uint32),
+                ("reserved_zero", C.c_uint32)]
+
+
+class LinearMatrix(C.Structure):
+    _fields_ = [("stored", LinearRange), ("shape", MatrixShape), ("weight_format", C.c_int),
+                ("slice_count", C.c_uint32), ("wide_form", C.c_uint32), ("reserved_zero", C.c_uint32)]
+
+
+class LinearSharedExpertDescription(C.Structure):
+    _fields_ = [("gate", LinearMatrix), ("up", LinearMatrix), ("down", LinearMatrix)] + \
+               [(name, LinearRange) for name in ("codes", "exponents", "operands", "gate_output", "up_output", "hidden",
+                                                 "hidden_codes", "hidden_exponents", "hidden_operands", "output")] + \
+               [("row_count", C.c_uint32), ("activation_limit", C.c_float)]
+
+
 class KernelLaunch(C.Structure):
     _fields_ = [("kernel", C.c_uint32), ("grid", C.c_uint32 * 3), ("block", C.c_uint32 * 3),
                 ("dynamic_shared_byte_count", C.c_uint32), ("argument_byte_count", C.c_uint32),
@@ -199,7 +227,7 @@ class OrderedCollectiveKernels(C.Structure):
 
 
 for _record, _bytes in ((Exl3Reconstruct, 32), (Exl3Expert, 80), (ExpertJob, 96), (ExpertRowSum, 24),
-                        (Exl3ShardActivation, 96), (Exl3Moe, 112), (Exl3Prefill, 136), (Exl3PrefillTile, 16), (Exl3PrefillEntry, 8), (Exl3PrefillParts, 56), (StepBlock, 16), (OrderedPeer, 32),
+                        (Exl3ShardActivation, 96), (Exl3Moe, 112), (TrunkLinearQuantized, 72), (TrunkHidden, 32), (TrunkRowsAdd, 24), (Exl3Prefill, 136), (Exl3PrefillTile, 16), (Exl3PrefillEntry, 8), (Exl3PrefillParts, 56), (StepBlock, 16), (OrderedPeer, 32),
                         (OrderedCollective, 80), (OrderedReduceBf16, 96), (OrderedRowSumPublish, 96),
                         (RouterSelectB200, 80), (StepInputSelect, 40), (ActivationQuantize, 40), (ExpertGateUp, 64), (ExpertDown, 56),
                         (KernelLaunch, 232), (CardDescription, 168)):

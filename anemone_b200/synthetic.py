@@ -76,3 +76,13 @@ def mx_matrix(rng, outputs, inputs):
     words = rng.integers(0, 256, size=outputs * inputs // 2, dtype=np.uint8)
     scales = (127 + rng.integers(-8, -3, size=outputs * inputs // 32)).astype(np.uint8)
     return np.concatenate([words, scales])
+
+
+def e4m3_matrix(rng, outputs, inputs):
+    """Stored bytes of one WEIGHT_FORMAT_E4M3_SCALED matrix: E4M3 bytes that are numbers (0x7F and 0xFF never occur),
+    then one E8M0 scale code per 32 outputs by 32 inputs, 127 + e with e uniform in [-9, -5] (weights of about the
+    size of the profile's routed experts'). Independent draws, so the format's stored order needs no permutation."""
+    codes = rng.integers(0, 127, size=outputs * inputs, dtype=np.uint8)
+    codes |= (rng.integers(0, 2, size=outputs * inputs, dtype=np.uint8) << 7)
+    scales = (127 + rng.integers(-9, -4, size=(outputs + 31) // 32 * (inputs // 32))).astype(np.uint8)
+    return np.concatenate([codes, scales])

@@ -496,6 +496,58 @@ AB_INLINE struct exl3_prefill_parts exl3_prefill_parts_of(uint32_t row_capacity,
 #define LINEAR_VALUES_PER_BLOCK 32u
 #define LINEAR_ELEMENT_THREADS 256u
 
+/* The always-on (shared) expert's matrices, WEIGHT_FORMAT_E4M3_SCALED (reference: include/anemone/
+ * weight_format_seam.h:36-42): bytes uint8 [tile = output / 16][group = input / 32][lane][16]: byte b of a lane is
+ * W[16 tile + g + 8 (b % 2)][32 group + 8 (b / 4) + 2 t + (b / 2) % 2], an E4M3 byte; then scales uint8
+ * [block = output / 32][group]: one E8M0 code per 32 outputs by 32 inputs (the last block may hold 16 outputs).
+ * output_size * input_size + ((output_size + 31) / 32) * (input_size / 32) bytes. Its products
+ * (trunk_linear_quantized_<S>, include/anemone/linear_records.h:308-330) are the routed experts' with a weight placed
+ * as FP16 by its seven low bits to bits 7..13 (its value times 2^-8): chain = fma(p, 2^(weight code + activation code -
+ * 111), chain) per block of 32 inputs, the same slices and roundings; rows 0 .. row_count - 1 (at most 8) stand in
+ * the columns. trunk_hidden_entry is the hidden step with a route weight of 1 on bfloat16 gate and up. */
+#define KERNEL_FILE_TRUNK_LINEAR "kernel_trunk_linear"
+#define KERNEL_TRUNK_LINEAR_QUANTIZED_STEM "trunk_linear_quantized_"
+#define KERNEL_TRUNK_HIDDEN_VALUE "trunk_hidden_entry"
+#define KERNEL_TRUNK_ROWS_ADD "trunk_rows_add_entry"
+#define LINEAR_MERGED_MATRICES 2u
+
+/* trunk_linear_quantized_<S>: grid ((output_size[0] + output_size[1]) / 16), block 32 S; matrix m takes the tiles from
+ * the first one's on (output_size[1] is 0 where there is one matrix); writes bfloat16 [row_count][output_size[m]] */
+struct trunk_linear_quantized_arguments {
+	uint64_t weights_offset[LINEAR_MERGED_MATRICES];
+	uint64_t output_offset[LINEAR_MERGED_MATRICES];
+	uint64_t codes_offset;
+	uint64_t exponents_offset;
+	uint64_t operands_offset;
+	uint32_t output_size[LINEAR_MERGED_MATRICES];
+	uint32_t input_size;
+	uint32_t row_count;
+};
+
+/* trunk_hidden_entry: grid (ceil(width / 256), vectors), block 256: bfloat16 gate and up [v][width] -> hidden */
+struct trunk_hidden_arguments {
+	uint64_t gate_offset;
+	uint64_t up_offset;
+	uint64_t hidden_offset;
+	uint32_t width;
+	float activation_limit;
+};
+
+/* B200 extension, trunk_rows_add_entry: grid (ceil(width / 256), rows), block 256: FP32 sums [rows][width] +=
+ * bfloat16 values [rows][width], one FP32 addition each: the always-on expert's rows joined to the routed experts'
+ * row sums before the ranks' reduction (the reference joins them in its FFN join, outside this path). */
+struct trunk_rows_add_arguments {
+	uint64_t sums_offset;
+	uint64_t values_offset;
+	uint32_t width;
+	uint32_t reserved_zero;
+};
+
+AB_INLINE uint64_t e4m3_scaled_byte_count(uint32_t output_size, uint32_t input_size)
+{
+	return (uint64_t)output_size * input_size + (uint64_t)((output_size + 31u) / 32u) * (input_size / 32u);
+}
+
 /* activation_quantize_entry: grid (width / 64, vectors), block 32 (a warp a load of 64 values) */
 struct activation_quantize_arguments {
 	uint64_t values_offset;
@@ -575,5 +627,8 @@ AB_RECORD_HAS(exl3_prefill_record, 136);
 AB_RECORD_HAS(activation_quantize_arguments, 40);
 AB_RECORD_HAS(expert_gate_up_arguments, 64);
 AB_RECORD_HAS(expert_down_arguments, 56);
+AB_RECORD_HAS(trunk_linear_quantized_arguments, 72);
+AB_RECORD_HAS(trunk_hidden_arguments, 32);
+AB_RECORD_HAS(trunk_rows_add_arguments, 24);
 
 #endif

@@ -98,5 +98,15 @@ void orc_mx_experts(const struct expert_gate_up_arguments *gate_up, const struct
 		    uint32_t job_count, uint32_t slices_gate_up, uint32_t slices_down, uint64_t hidden_codes_offset,
 		    uint64_t hidden_exponents_offset, uint64_t hidden_operands_offset, unsigned char *arena);
 void orc_mx_row_sum(const struct expert_row_sum_arguments *record, uint32_t rows, unsigned char *arena);
+/* the always-on expert: E4M3 weights, one E8M0 scale per 32 outputs by 32 inputs (tests/weight_format_reference.h:8-16,
+ * tests/linear_reference.h:30-37) */
+void orc_e4m3_weights_lay_out(const uint8_t *codes, const uint8_t *scales, uint32_t outputs, uint32_t inputs,
+			      uint8_t *stored_out);
+uint16_t orc_trunk_output(const uint8_t *stored, uint32_t outputs, uint32_t inputs, uint32_t output, const uint8_t *codes,
+			  const uint8_t *exponents, uint32_t slices);
+void orc_shared_expert(const struct trunk_linear_quantized_arguments *gate_up, const struct trunk_hidden_arguments *hidden,
+		       const struct activation_quantize_arguments *quantize,
+		       const struct trunk_linear_quantized_arguments *down, uint32_t slices_gate_up, uint32_t slices_down,
+		       unsigned char *arena);
 
 #endif

@@ -235,3 +235,95 @@ void orc_mx_row_sum(const struct expert_row_sum_arguments *record, uint32_t rows
 			sums[row * record->width + channel] = sum;
 		}
 }
+
+/* ---- the always-on expert: WEIGHT_FORMAT_E4M3_SCALED (include/anemone/weight_format_seam.h:36-42) ---- */
+
+/* the byte of a stored matrix that holds W[output][input], by the format's own sentence: byte b of lane 4 g + t of
+ * (tile, group) is W[16 tile + g + 8 (b % 2)][32 group + 8 (b / 4) + 2 t + (b / 2) % 2] */
+static size_t e4m3_place(uint32_t inputs, uint32_t output, uint32_t input)
+{
+	const uint32_t tile = output / 16u, g = output % 8u, upper = output % 16u / 8u;
+	const uint32_t group = input / 32u, within = input % 32u;
+	const uint32_t quarter = within / 8u, t = within % 8u / 2u, odd = within % 2u;
+	const uint32_t b = 4u * quarter + 2u * odd + upper;
+	return (((size_t)tile * (inputs / 32u) + group) * 32u + 4u * g + t) * 16u + b;
+}
+
+/* codes [output][input] E4M3 bytes and scales [(outputs + 31) / 32][inputs / 32] E8M0 codes -> the stored matrix */
+void orc_e4m3_weights_lay_out(const uint8_t *codes, const uint8_t *scales, uint32_t outputs, uint32_t inputs,
+			      uint8_t *stored_out)
+{
+	for (uint32_t output = 0; output < outputs; output++)
+		for (uint32_t input = 0; input < inputs; input++)
+			stored_out[e4m3_place(inputs, output, input)] = codes[(size_t)output * inputs + input];
+	memcpy(stored_out + (size_t)outputs * inputs, scales, (size_t)((outputs + 31u) / 32u) * (inputs / 32u));
+}
+
+/* One output of one row of trunk_linear_quantized_<S>: as orc_mx_output with E4M3 weights and one scale per 32 outputs
+ * by 32 inputs. codes/exponents: the row's NATURAL-order E4M3 codes and its block exponents. */
+uint16_t orc_trunk_output(const uint8_t *stored, uint32_t outputs, uint32_t inputs, uint32_t output, const uint8_t *codes,
+			  const uint8_t *exponents, uint32_t slices)
+{
+	const uint32_t loads = inputs / 64u;
+	const uint8_t *const scales = stored + (size_t)outputs * inputs + (size_t)(output / 32u) * (inputs / 32u);
+	float sum = 0.0f;
+	for (uint32_t slice = 0; slice < slices; slice++) {
+		float chain = 0.0f;
+		for (uint32_t load = loads * slice / slices; load < loads * (slice + 1u) / slices; load++)
+			for (uint32_t q = 0; q < 2u; q++) {
+				const uint32_t block = 2u * load + q;
+				double exact = 0.0;
+				for (uint32_t index = 0; index < 32u; index++)
+					exact += orc_e4m3_value(stored[e4m3_place(inputs, output, 32u * block + index)]) *
+						 orc_e4m3_value(codes[32u * block + index]);
+				const float p = (float)exact;
+				const float scale = (float)ldexp(1.0, (int)scales[block] - 127 + (int)exponents[block] - 127);
+				chain = fmaf(p, scale, chain);
+			}
+		sum = sum + chain;
+	}
+	return orc_bfloat16_bits(sum);
+}
+
+/* The always-on expert on an arena image, launch for launch (linear_shared_expert_prepare's four): gate and up,
+ * the hidden step with a route weight of 1, quantization of the hidden rows, down. */
+void orc_shared_expert(const struct trunk_linear_quantized_arguments *gate_up, const struct trunk_hidden_arguments *hidden,
+		       const struct activation_quantize_arguments *quantize,
+		       const struct trunk_linear_quantized_arguments *down, uint32_t slices_gate_up, uint32_t slices_down,
+		       unsigned char *arena)
+{
+	const uint32_t H = gate_up->input_size, I = gate_up->output_size[0], O = down->output_size[0];
+	const uint32_t rows = gate_up->row_count;
+	uint8_t *const natural = malloc(H > I ? H : I);
+	uint8_t *const scratch = malloc(I);
+	for (uint32_t row = 0; row < rows; row++) {
+		const uint8_t *const lane_codes = arena + gate_up->codes_offset + (size_t)row * H;
+		for (uint32_t byte = 0; byte < H; byte++) {
+			const uint32_t jj = byte % 4u, s = byte / 4u % 4u, t = byte / 16u % 4u, l = byte / 64u;
+			natural[64u * l + 16u * s + 2u * t + jj / 2u + 8u * (jj % 2u)] = lane_codes[byte];
+		}
+		const uint8_t *const exponents = arena + gate_up->exponents_offset + (size_t)row * (H / 32u);
+		uint16_t *const gate_out = (uint16_t *)(arena + gate_up->output_offset[0]) + (size_t)row * I;
+		uint16_t *const up_out = (uint16_t *)(arena + gate_up->output_offset[1]) + (size_t)row * I;
+		uint16_t *const hidden_out = (uint16_t *)(arena + hidden->hidden_offset) + (size_t)row * I;
+#pragma omp parallel for
+		for (uint32_t output = 0; output < I; output++) {
+			gate_out[output] = orc_trunk_output(arena + gate_up->weights_offset[0], I, H, output, natural, exponents,
+							    slices_gate_up);
+			up_out[output] = orc_trunk_output(arena + gate_up->weights_offset[1], I, H, output, natural, exponents,
+							  slices_gate_up);
+			hidden_out[output] = orc_mx_hidden(gate_out[output], up_out[output], hidden->activation_limit, 1.0f);
+		}
+		uint8_t *const hidden_exponents = arena + quantize->exponents_offset + (size_t)row * (I / 32u);
+		orc_mx_quantize(hidden_out, I, scratch, hidden_exponents);
+		orc_mx_codes_lay_out(scratch, I, arena + quantize->codes_offset + (size_t)row * I);
+		orc_mx_operands_lay_out(scratch, I, (uint16_t *)(arena + quantize->operands_offset) + (size_t)row * I);
+		uint16_t *const out = (uint16_t *)(arena + down->output_offset[0]) + (size_t)row * O;
+#pragma omp parallel for
+		for (uint32_t output = 0; output < O; output++)
+			out[output] = orc_trunk_output(arena + down->weights_offset[0], O, I, output, scratch, hidden_exponents,
+						       slices_down);
+	}
+	free(scratch);
+	free(natural);
+}

@@ -229,3 +229,105 @@ def test_layer_matches_oracle(api, oracle):
     row_output = received[at["row_output"]:at["row_output"] + rows * H * 4].view(np.float32).reshape(rows, H)
     assert np.array_equal(resummed.view(np.uint32), row_output.view(np.uint32))
     assert np.array_equal(result, synthetic.to_bfloat16(np.float32(0.0) + row_output))
+
+
+@pytest.mark.parametrize("rows,slices", [(1, (1, 1)), (5, (2, 4)), (8, (8, 2))])
+def test_shared_expert_matches_oracle(api, oracle, rows, slices):
+    """linear_shared_expert_prepare's four launches (E4M3 matrices, one scale per 32 by 32 weights) against the oracle
+    on the same image, from the card's own quantized rows: gate, up and down within the tolerance of a bfloat16
+    result, the hidden rows' quantization bit for bit given the hidden rows."""
+    rng = np.random.default_rng(60 + rows)
+    H, I = 512, 320  # a last scale block of 16 outputs in neither; 320 = 10 blocks of 32, 5 loads of 64
+    layout = api.Layout()
+    stored = {name: synthetic.e4m3_matrix(rng, o, i) for name, (o, i) in
+              (("gate", (I, H)), ("up", (I, H)), ("down", (H, I)))}
+    where = {name: layout.take(data.size, 64) for name, data in stored.items()}
+    sizes = {"values": rows * H * 2, "codes": rows * H, "exponents": rows * H // 32, "operands": rows * H * 2,
+             "gate_output": rows * I * 2, "up_output": rows * I * 2, "hidden": rows * I * 2, "hidden_codes": rows * I,
+             "hidden_exponents": rows * I // 32, "hidden_operands": rows * I * 2, "output": rows * H * 2}
+    at = {name: layout.take(size + 64) for name, size in sizes.items()}
+    arena_bytes = layout.take(4096, 4096)
+    image = np.full(arena_bytes, 0xC3, dtype=np.uint8)
+    for name, data in stored.items():
+        image[where[name]:where[name] + data.size] = data
+    tokens = synthetic.tokens(rng, rows, H)
+    image[at["values"]:at["values"] + sizes["values"]] = tokens.view(np.uint8).reshape(-1)
+    lib = api.library()
+    description = R.LinearSharedExpertDescription()
+    for name, (o, i), count in (("gate", (I, H), slices[0]), ("up", (I, H), slices[0]), ("down", (H, I), slices[1])):
+        setattr(description, name, R.LinearMatrix(R.LinearRange(where[name], stored[name].size), R.MatrixShape(o, i, 8, 0),
+                                                  5, count, 0, 0))
+    for name in ("codes", "exponents", "operands", "gate_output", "up_output", "hidden", "hidden_codes",
+                 "hidden_exponents", "hidden_operands", "output"):
+        setattr(description, name, R.LinearRange(at[name], sizes[name]))
+    description.row_count, description.activation_limit = rows, 7.0
+    lib.linear_quantize_prepare.argtypes = [C.POINTER(R.LinearQuantizeDescription), C.c_uint64,
+                                            C.POINTER(R.LinearKernels), C.POINTER(R.KernelLaunch)]
+    lib.linear_shared_expert_prepare.argtypes = [C.POINTER(R.LinearSharedExpertDescription), C.c_uint64,
+                                                 C.POINTER(R.LinearKernels), C.POINTER(R.KernelLaunch)]
+    card = api.Card(0, arena_bytes)
+    try:
+        kernels = prepare_kernels(api, card)
+        card.upload(0, image)
+        quantize = R.LinearQuantizeDescription(R.LinearRange(at["values"], sizes["values"]), description.codes,
+                                               description.exponents, description.operands, H, rows)
+        first = R.KernelLaunch()
+        api.check(lib.linear_quantize_prepare(C.byref(quantize), arena_bytes, C.byref(kernels), C.byref(first)), "quantize")
+        launches = (R.KernelLaunch * 4)()
+        api.check(lib.linear_shared_expert_prepare(C.byref(description), arena_bytes, C.byref(kernels), launches),
+                  "linear_shared_expert_prepare")
+        assert launches[0].grid[0] == 2 * I // 16 and launches[0].block[0] == 32 * slices[0]
+        assert launches[3].grid[0] == H // 16 and launches[3].block[0] == 32 * slices[1]
+        before = bytes(launches)
+        description.row_count = 9  # more rows than a thin launch takes
+        assert lib.linear_shared_expert_prepare(C.byref(description), arena_bytes, C.byref(kernels), launches) == 1
+        assert bytes(launches) == before
+        card.run([first] + list(launches))
+        card.wait()
+        received = card.download(0, arena_bytes)
+    finally:
+        card.close()
+    expected = image.copy()
+    for name in ("codes", "exponents", "operands"):
+        expected[at[name]:at[name] + sizes[name]] = received[at[name]:at[name] + sizes[name]]
+    gate_up = R.TrunkLinearQuantized((C.c_uint64 * 2)(where["gate"], where["up"]),
+                                     (C.c_uint64 * 2)(at["gate_output"], at["up_output"]), at["codes"],
+                                     at["exponents"], at["operands"], (C.c_uint32 * 2)(I, I), H, rows)
+    hidden = R.TrunkHidden(at["gate_output"], at["up_output"], at["hidden"], I, 7.0)
+    requantize = R.ActivationQuantize(at["hidden"], at["hidden_codes"], at["hidden_exponents"], at["hidden_operands"], I, 0)
+    down = R.TrunkLinearQuantized((C.c_uint64 * 2)(where["down"], 0), (C.c_uint64 * 2)(at["output"], 0),
+                                  at["hidden_codes"], at["hidden_exponents"], at["hidden_operands"],
+                                  (C.c_uint32 * 2)(H, 0), I, rows)
+    oracle.orc_shared_expert(C.byref(gate_up), C.byref(hidden), C.byref(requantize), C.byref(down), slices[0], slices[1],
+                             ptr(expected, u8p))
+
+    def ordinals(bits):
+        bits = bits.astype(np.int32)
+        return np.where(bits & 0x8000, -(bits & 0x7FFF), bits & 0x7FFF)
+
+    def region(data, name):
+        return data[at[name]:at[name] + sizes[name]].view(np.uint16)
+    for name in ("gate_output", "up_output"):
+        distance = np.abs(ordinals(region(received, name)) - ordinals(region(expected, name)))
+        assert distance.max() <= 2 and (distance == 0).mean() > 0.98, name
+    out_got = synthetic.from_bfloat16(region(received, "output"))
+    out_want = synthetic.from_bfloat16(region(expected, "output"))
+    assert np.isfinite(out_got).all() and np.abs(out_want).max() > 0
+    assert np.abs(out_got - out_want).max() <= max(2e-2, 2.0 ** -6 * np.abs(out_want).max())
+    cosine = float(out_got.astype(np.float64) @ out_want.astype(np.float64) /
+                   (np.linalg.norm(out_got) * np.linalg.norm(out_want)))
+    assert cosine >= 0.9999
+    # the hidden rows' quantization: the card's own kernel on the card's own hidden rows, against the oracle's quantizer
+    hidden_rows = region(received, "hidden").reshape(rows, I)
+    for row in range(rows):
+        natural, exponents = np.zeros(I, np.uint8), np.zeros(I // 32, np.uint8)
+        line = np.ascontiguousarray(hidden_rows[row])
+        oracle.orc_mx_quantize(ptr(line, u16p), I, ptr(natural, u8p), ptr(exponents, u8p))
+        lane_order = np.zeros(I, np.uint8)
+        oracle.orc_mx_codes_lay_out(ptr(natural, u8p), I, ptr(lane_order, u8p))
+        got = received[at["hidden_codes"] + row * I:at["hidden_codes"] + (row + 1) * I]
+        assert np.array_equal(got, lane_order), row
+    for name, size in sizes.items():  # nothing written behind a range, weights untouched
+        assert (received[at[name] + size:at[name] + size + 64] == 0xC3).all(), name
+    for name, data in stored.items():
+        assert np.array_equal(received[where[name]:where[name] + data.size], data)

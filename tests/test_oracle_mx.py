@@ -113,3 +113,51 @@ def test_hidden_equals_reference(oracle, reference):
                                                                                                float(np.float32(weight))))
             differing += abs(int(ours & 0x7FFF) - int(theirs & 0x7FFF)) > 1 or (ours ^ theirs) & 0x8000 and ours & 0x7FFF > 1
     assert differing == 0  # float32 steps against the double reference: never more than one last place apart
+
+
+def e4m3_codes(rng, count):
+    """E4M3 bytes that are numbers (no 0x7F, no 0xFF), both signs, subnormals included."""
+    codes = rng.integers(0, 127, size=count, dtype=np.uint8)
+    return (codes | (rng.integers(0, 2, size=count, dtype=np.uint8) << 7)).astype(np.uint8)
+
+
+def test_e4m3_weight_layout_equals_reference(oracle, reference):
+    rng = np.random.default_rng(25)
+    for outputs, inputs in ((48, 192), (64, 128)):  # the first: a last block of 16 outputs
+        codes = e4m3_codes(rng, outputs * inputs)
+        scales = rng.integers(110, 130, size=(outputs + 31) // 32 * (inputs // 32), dtype=np.uint8)
+        size = outputs * inputs + scales.size
+        ours, theirs = np.zeros(size, np.uint8), np.zeros(size, np.uint8)
+        oracle.orc_e4m3_weights_lay_out(ptr(codes, u8p), ptr(scales, u8p), outputs, inputs, ptr(ours, u8p))
+        shape = Shape(outputs, inputs, 8, 0)
+        assert reference.test_weight_format_lay_out(5, C.byref(shape), ptr(codes, u8p), codes.size, ptr(scales, u8p),
+                                                    scales.size, ptr(theirs, u8p), size) == 0
+        assert np.array_equal(ours, theirs)
+
+
+def test_trunk_outputs_within_reference_tolerance(oracle, reference):
+    rng = np.random.default_rng(26)
+    outputs, inputs = 48, 512
+    codes = e4m3_codes(rng, outputs * inputs)
+    scales = rng.integers(115, 125, size=(outputs + 31) // 32 * (inputs // 32), dtype=np.uint8)
+    stored = np.zeros(outputs * inputs + scales.size, np.uint8)
+    oracle.orc_e4m3_weights_lay_out(ptr(codes, u8p), ptr(scales, u8p), outputs, inputs, ptr(stored, u8p))
+    values = synthetic.to_bfloat16(rng.normal(0, 1, inputs).astype(np.float32))
+    fed_codes, fed_exp = np.zeros(inputs, np.uint8), np.zeros(inputs // 32, np.uint8)
+    oracle.orc_mx_quantize(ptr(values, u16p), inputs, ptr(fed_codes, u8p), ptr(fed_exp, u8p))
+    fed_values = np.zeros(inputs, np.float64)
+    assert reference.test_linear_fed_values_of_codes(ptr(fed_codes, u8p), inputs,
+                                                     fed_values.ctypes.data_as(C.POINTER(C.c_double))) == 0
+    products = (Product * outputs)()
+    shape = Shape(outputs, inputs, 8, 0)
+    reference.test_linear_products.argtypes = [C.c_int, C.c_void_p, u8p, C.c_uint64, C.c_uint32, C.c_uint32,
+                                               C.POINTER(C.c_double), u8p, C.c_uint32, C.c_uint32, C.c_void_p]
+    assert reference.test_linear_products(5, C.byref(shape), ptr(stored, u8p), stored.size, 0, outputs,
+                                          fed_values.ctypes.data_as(C.POINTER(C.c_double)), ptr(fed_exp, u8p), 1, 1,
+                                          C.byref(products)) == 0
+    reference.test_linear_output_is_within_tolerance.argtypes = [C.c_uint16, C.c_void_p, C.c_uint32, C.c_uint32]
+    for slices in (1, 2, 8):
+        for output in range(outputs):
+            bits = oracle.orc_trunk_output(ptr(stored, u8p), outputs, inputs, output, ptr(fed_codes, u8p),
+                                           ptr(fed_exp, u8p), slices)
+            assert reference.test_linear_output_is_within_tolerance(bits, C.byref(products[output]), inputs, slices)
