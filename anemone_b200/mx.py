@@ -1,8 +1,11 @@
 """One rank's original-weights routed-expert layer (MXFP4 weights by E4M3 block-quantized activations), prepared once
 and run per step through the C-ABI library. Launches of one step, all from libanemone_b200.so:
     router_select_b200 -> activation_quantize_entry -> expert_gate_up_<S> -> activation_quantize_entry (hidden)
-    -> expert_down_<S> -> expert_row_sum_entry -> ordered_row_sum_publish -> ordered_reduce_bf16
-(the four middle ones are linear_routed_experts_prepare's). Tensor parallelism is by intermediate columns, as in the
+    -> expert_down_<S> -> expert_row_sum_entry
+    [-> trunk_linear_quantized_<S> (gate, up) -> trunk_hidden_entry -> activation_quantize_entry
+     -> trunk_linear_quantized_<S> (down) -> trunk_rows_add_entry]          the always-on expert, E4M3 matrices
+    -> ordered_row_sum_publish -> ordered_reduce_bf16
+(linear_routed_experts_prepare's four, linear_shared_expert_prepare's four). Tensor parallelism is by intermediate columns, as in the
 EXL3 decode layer; the ranks' FP32 rows are added in rank order and rounded once. Nothing here computes on the host.
 """
 import ctypes as C
@@ -14,15 +17,20 @@ from . import records as R
 from .moe import LINE, SIGNAL_BYTES, rank_columns
 
 WEIGHT_FORMAT_E2M1_SCALED = 3
+WEIGHT_FORMAT_E4M3_SCALED = 5
 
 
 def matrix_bytes(outputs, inputs):
     return outputs * inputs // 2 + outputs * inputs // 32
 
 
+def shared_matrix_bytes(outputs, inputs):
+    return outputs * inputs + (outputs + 31) // 32 * (inputs // 32)
+
+
 class MxLayout:
     def __init__(self, config, rank_count, rank):
-        assert config.shared == 0, "the always-on expert of this profile is FP8, which this library does not have"
+        assert config.shared in (0, 1)
         self.config = c = config
         self.inner_local = I = rank_columns(c.inner, rank_count, rank)[1]
         H, rows = c.hidden, c.row_capacity
@@ -47,18 +55,26 @@ class MxLayout:
                       "hidden": pairs * I * 2, "hidden_codes": pairs * I, "hidden_exponents": pairs * I // 32,
                       "hidden_operands": pairs * I * 2, "pair_output": pairs * H * 2, "row_output": rows * H * 4}
         self.at = {name: layout.take(size) for name, size in self.sizes.items()}
+        self.shared_sizes = {"gate_output": rows * I * 2, "up_output": rows * I * 2, "hidden": rows * I * 2,
+                             "hidden_codes": rows * I, "hidden_exponents": rows * I // 32,
+                             "hidden_operands": rows * I * 2, "output": rows * H * 2} if c.shared else {}
+        self.shared_at = {name: layout.take(size) for name, size in self.shared_sizes.items()}
         self.weights_begin = api.align(layout.cursor, 64)
         self.matrices = []
         for _ in range(c.experts):
             self.matrices.append((layout.take(matrix_bytes(I, H), 64), layout.take(matrix_bytes(I, H), 64),
                                   layout.take(matrix_bytes(H, I), 64)))
         self.weights_end = layout.cursor
+        self.shared_matrices = (layout.take(shared_matrix_bytes(I, H), 64), layout.take(shared_matrix_bytes(I, H), 64),
+                                layout.take(shared_matrix_bytes(H, I), 64)) if c.shared else ()
         self.arena_bytes = api.align(layout.cursor, 4096) + 4096
 
 
 class MxLayer:
-    def __init__(self, card, config, matrices, rank=0, rank_count=1, slices=(4, 4)):
-        """matrices: iterable over experts of this rank's (gate, up, down) stored bytes."""
+    def __init__(self, card, config, matrices, rank=0, rank_count=1, slices=(4, 4), shared_matrices=None,
+                 shared_slices=(2, 2)):
+        """matrices: iterable over the routed experts of this rank's (gate, up, down) stored MXFP4 bytes;
+        shared_matrices: the always-on expert's (gate, up, down) stored E4M3 bytes, where the configuration has one."""
         self.card, self.config = card, config
         self.layout = L = MxLayout(config, rank_count, rank)
         assert card.arena_bytes >= L.arena_bytes
@@ -71,6 +87,12 @@ class MxLayer:
                 table[expert, which] = L.matrices[expert][which]
                 self.weight_bytes += data.size
         card.upload(L.expert_table, table)
+        if config.shared:
+            for which, data in enumerate(shared_matrices):
+                assert data.size == shared_matrix_bytes(*((L.inner_local, config.hidden) if which < 2 else
+                                                          (config.hidden, L.inner_local)))
+                card.upload(L.shared_matrices[which], data)
+                self.weight_bytes += data.size
         for offset, size in ((L.peer_table, 16 * 32), (L.status, 16), (L.step, 256), (L.region, 2 * L.parity_stride)):
             card.fill(offset, 0, size)
         peers = (R.OrderedPeer * rank_count)()
@@ -116,6 +138,30 @@ class MxLayer:
         self.expert_launches = (R.KernelLaunch * 4)()
         api.check(lib.linear_routed_experts_prepare(C.byref(description), card.arena_bytes, C.byref(kernels),
                                                     self.expert_launches), "linear_routed_experts_prepare")
+        shared_launches = []
+        if c.shared:
+            shared = R.LinearSharedExpertDescription()
+            for which, (name, (o, i)) in enumerate((("gate", (I, H)), ("up", (I, H)), ("down", (H, I)))):
+                setattr(shared, name, R.LinearMatrix(R.LinearRange(L.shared_matrices[which], shared_matrix_bytes(o, i)),
+                                                     R.MatrixShape(o, i, 8, 0), WEIGHT_FORMAT_E4M3_SCALED,
+                                                     shared_slices[0 if which < 2 else 1], 0, 0))
+            shared.codes, shared.exponents, shared.operands = span("codes"), span("exponents"), span("operands")
+            for name in L.shared_sizes:
+                setattr(shared, name, R.LinearRange(L.shared_at[name], L.shared_sizes[name]))
+            shared.row_count, shared.activation_limit = c.row_capacity, c.activation_limit
+            lib.linear_shared_expert_prepare.argtypes = [C.POINTER(R.LinearSharedExpertDescription), C.c_uint64,
+                                                         C.POINTER(R.LinearKernels), C.POINTER(R.KernelLaunch)]
+            four = (R.KernelLaunch * 4)()
+            api.check(lib.linear_shared_expert_prepare(C.byref(shared), card.arena_bytes, C.byref(kernels), four),
+                      "linear_shared_expert_prepare")
+            lib.linear_rows_add_prepare.argtypes = [C.POINTER(R.LinearRange), C.POINTER(R.LinearRange), C.c_uint32,
+                                                    C.c_uint32, C.c_uint64, C.POINTER(api.BackendOperations),
+                                                    C.c_void_p, C.POINTER(R.KernelLaunch)]
+            add = R.KernelLaunch()
+            sums, values = span("row_output"), R.LinearRange(L.shared_at["output"], L.shared_sizes["output"])
+            api.check(lib.linear_rows_add_prepare(C.byref(sums), C.byref(values), H, c.row_capacity, card.arena_bytes,
+                                                  card.ops_pointer, card.handle, C.byref(add)), "linear_rows_add_prepare")
+            shared_launches = list(four) + [add]
         reduce = R.OrderedReduceBf16Description()
         reduce.reduce.collective = R.OrderedCollective(L.peer_table, L.region, L.slot_input, L.result, 0, L.step,
                                                        L.parity_stride, c.deadline_cycles, c.row_capacity * H,
@@ -129,7 +175,8 @@ class MxLayer:
         reduce_launches = (R.KernelLaunch * 2)()
         api.check(lib.ordered_reduce_bf16_prepare(C.byref(reduce), card.ops_pointer, card.handle, reduce_launches),
                   "ordered_reduce_bf16_prepare")
-        self.launches = [router_launch, quantize_launch] + list(self.expert_launches) + list(reduce_launches)
+        self.launches = [router_launch, quantize_launch] + list(self.expert_launches) + shared_launches + \
+            list(reduce_launches)
         self.graph = card.graph(self.launches)
         self.sequence = 0
 

@@ -333,14 +333,15 @@ def workload_config(args, config, world):
 
 
 def run_original_weights(args, api, base, rank, world, local_rank, dist, barrier, maximum):
-    """cfg5, routed experts only: MXFP4 weights (E8M0 scales 2^-8 .. 2^-4) by E4M3 block-quantized activations,
-    decode M = 8, tensor parallel by intermediate columns. The FP8 always-on expert of that configuration is not built."""
+    """cfg5: routed experts MXFP4 (E8M0 scales 2^-8 .. 2^-4), the always-on expert E4M3 with one E8M0 scale per 32 by 32
+    weights (the reference's FP8 format; the configuration's 128 x 128 FP32-scaled variant is not in the reference and
+    not built), E4M3 block-quantized activations, decode M = 8, tensor parallel by intermediate columns."""
     from anemone_b200 import records as R
     from anemone_b200 import synthetic
     from anemone_b200.moe import MoeConfig
     from anemone_b200.mx import MxLayer, MxLayout, matrix_bytes
     rows, steps, warmup = args.rows, args.steps, args.warmup
-    config = MoeConfig(hidden=base.hidden, inner=base.inner, experts=base.experts, shared=0, picks=base.picks,
+    config = MoeConfig(hidden=base.hidden, inner=base.inner, experts=base.experts, shared=1, picks=base.picks,
                        row_capacity=rows, activation_limit=7.0)
     layout = MxLayout(config, world, rank)
     H, I = config.hidden, layout.inner_local
@@ -349,8 +350,11 @@ def run_original_weights(args, api, base, rank, world, local_rank, dist, barrier
     def draw(expert):
         rng = np.random.default_rng([SEED, 2000 + expert, rank])
         return (synthetic.mx_matrix(rng, I, H), synthetic.mx_matrix(rng, I, H), synthetic.mx_matrix(rng, H, I))
+    always_rng = np.random.default_rng([SEED, 2999, rank])
+    always = (synthetic.e4m3_matrix(always_rng, I, H), synthetic.e4m3_matrix(always_rng, I, H),
+              synthetic.e4m3_matrix(always_rng, H, I))
     layer = MxLayer(card, config, (draw(expert) for expert in range(config.experts)), rank=rank, rank_count=world,
-                    slices=(2, 2))
+                    slices=(2, 2), shared_matrices=always)
     if dist is None:
         layer.connect_local([layer])
     else:
@@ -426,9 +430,10 @@ def run_original_weights(args, api, base, rank, world, local_rank, dist, barrier
             "e2e": {"value": rows * 1000.0 / e2e_ms, "unit": "tok/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": layout.step_input_bytes, "d2h_bytes_per_step": rows * H * 2},
             "roofline": roofline, "dtype": "e2m1 x e4m3 -> f32",
-            "config": {"workload": "cfg5 routed experts only: MXFP4 (E2M1, one E8M0 scale per 32 inputs, exponents "
-                                   "-8..-4), %d experts, top-%d, hidden %d, intermediate %d, M=%d; the FP8 always-on "
-                                   "expert is not built" % (config.experts, config.picks, H, config.inner, rows),
+            "config": {"workload": "cfg5 original-weights MoE layer decode: %d routed MXFP4 experts (E2M1, one E8M0 "
+                                   "scale per 32 inputs, exponents -8..-4), top-%d, 1 always-on expert E4M3 with one "
+                                   "E8M0 scale per 32x32 weights, hidden %d, intermediate %d, M=%d" %
+                                   (config.experts, config.picks, H, config.inner, rows),
                        "parallelism": "tp%d by intermediate columns, ordered FP32->bf16 reduce" % world,
                        "note": "value includes the 74 KB host->device copy of each step's inputs"}}
 

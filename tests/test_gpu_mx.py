@@ -184,13 +184,14 @@ def test_routed_experts_match_oracle(api, oracle, slices):
     assert np.array_equal(received[:weights_end], image[:weights_end])
 
 
-def test_layer_matches_oracle(api, oracle):
+@pytest.mark.parametrize("shared", [0, 1])
+def test_layer_matches_oracle(api, oracle, shared):
     """The whole original-weights layer (router -> quantize -> experts -> row sum -> ordered reduction) through
     anemone_b200.mx.MxLayer: the card's own job table and quantized rows, then the oracle's experts on the same image."""
     from anemone_b200.moe import MoeConfig
     from anemone_b200.mx import MxLayer, MxLayout
     from oracle import moe_reference
-    config = MoeConfig(hidden=512, inner=256, experts=12, shared=0, picks=3, row_capacity=8, activation_limit=7.0)
+    config = MoeConfig(hidden=512, inner=256, experts=12, shared=shared, picks=3, row_capacity=8, activation_limit=7.0)
     rng = np.random.default_rng(91)
     H, I, rows = config.hidden, config.inner, 7
     matrices = [(mx_matrix(oracle, rng, I, H), mx_matrix(oracle, rng, I, H), mx_matrix(oracle, rng, H, I))
@@ -200,7 +201,9 @@ def test_layer_matches_oracle(api, oracle):
     L = MxLayout(config, 1, 0)
     card = api.Card(0, L.arena_bytes)
     try:
-        layer = MxLayer(card, config, matrices, slices=(2, 2))
+        always = (synthetic.e4m3_matrix(rng, I, H), synthetic.e4m3_matrix(rng, I, H),
+                  synthetic.e4m3_matrix(rng, H, I)) if shared else None
+        layer = MxLayer(card, config, matrices, slices=(2, 2), shared_matrices=always)
         layer.connect_local([layer])
         result = layer.step(tokens, scores)
         received = card.download(0, L.arena_bytes)
@@ -227,6 +230,13 @@ def test_layer_matches_oracle(api, oracle):
     for slot in range(config.picks):
         resummed = (resummed + out_got.reshape(rows, config.picks, H)[:, slot, :]).astype(np.float32)
     row_output = received[at["row_output"]:at["row_output"] + rows * H * 4].view(np.float32).reshape(rows, H)
+    if shared:
+        # the always-on expert's rows (checked against the oracle in test_shared_expert_matches_oracle) joined by one
+        # FP32 addition each
+        where = L.shared_at["output"]
+        joined = synthetic.from_bfloat16(received[where:where + rows * H * 2].view(np.uint16)).reshape(rows, H)
+        assert np.abs(joined).max() > 0
+        resummed = (resummed + joined).astype(np.float32)
     assert np.array_equal(resummed.view(np.uint32), row_output.view(np.uint32))
     assert np.array_equal(result, synthetic.to_bfloat16(np.float32(0.0) + row_output))
 
