@@ -85,6 +85,7 @@ def library():
         lib.backend_b200_launch_count.argtypes = [_card]
         lib.backend_b200_arena_address.restype = C.c_uint64
         lib.backend_b200_arena_address.argtypes = [_card]
+        lib.backend_b200_image_register.argtypes = [C.c_char_p, C.c_void_p, C.c_uint64]
         lib.backend_b200_waits_expired.argtypes = [_card, C.POINTER(C.c_uint32)]
         lib.backend_b200_fill.argtypes = [_card, C.c_uint64, C.c_ubyte, C.c_uint64]
         lib.backend_b200_ipc_export.argtypes = [_card, C.c_char_p]
@@ -110,6 +111,12 @@ def library():
 
 def operations():
     return library().backend_b200_operations()
+
+
+def image_register(file_name, image_bytes):
+    """One more kernel file for kernel_prepare: an sm_100a cubin the caller built (backend_b200_image_register)."""
+    data = bytes(image_bytes)
+    check(library().backend_b200_image_register(file_name.encode(), data, len(data)), "image_register")
 
 
 def card_count():

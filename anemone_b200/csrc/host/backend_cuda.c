@@ -524,6 +524,12 @@ static result_status cuda_upload_wait(struct device_card *card, uint64_t upload_
 
 /* ------------------------------------------------------------------ kernels */
 
+/* kernel images a caller registered at run time (backend_b200_image_register), behind the embedded ones */
+#define REGISTERED_IMAGES_MOST 4u
+static struct ab_kernel_image registered_images[REGISTERED_IMAGES_MOST];
+static char registered_names[REGISTERED_IMAGES_MOST][64];
+static uint32_t registered_image_count;
+
 static const struct ab_kernel_image *image_of(const char *kernel_file_name, uint32_t *index_out)
 {
 	for (uint32_t index = 0; index < ab_kernel_image_count; index++)
@@ -531,7 +537,47 @@ static const struct ab_kernel_image *image_of(const char *kernel_file_name, uint
 			*index_out = index;
 			return &ab_kernel_images[index];
 		}
-	return NULL;
+	const struct ab_kernel_image *found = NULL;
+	(void)pthread_mutex_lock(&global_mutex);
+	for (uint32_t index = 0; index < registered_image_count; index++)
+		if (strcmp(registered_images[index].file_name, kernel_file_name) == 0) {
+			*index_out = ab_kernel_image_count + index;
+			found = &registered_images[index];
+		}
+	(void)pthread_mutex_unlock(&global_mutex);
+	return found;
+}
+
+result_status backend_b200_image_register(const char *kernel_file_name, const void *image, uint64_t image_byte_count)
+{
+	if (kernel_file_name == NULL || image == NULL || image_byte_count == 0 || kernel_file_name[0] == 0 ||
+	    strlen(kernel_file_name) >= sizeof(registered_names[0]))
+		return STATUS_INVALID_ARGUMENT;
+	uint32_t taken = 0;
+	if (image_of(kernel_file_name, &taken) != NULL)
+		return STATUS_INVALID_ARGUMENT; /* a name is never given twice: no embedded file is shadowed */
+	unsigned char *const copy = malloc(image_byte_count + 1u);
+	if (copy == NULL)
+		return STATUS_OUT_OF_MEMORY;
+	memcpy(copy, image, image_byte_count);
+	copy[image_byte_count] = 0;
+	result_status status = STATUS_OK;
+	(void)pthread_mutex_lock(&global_mutex);
+	if (registered_image_count == REGISTERED_IMAGES_MOST ||
+	    ab_kernel_image_count + registered_image_count >= CARD_MODULES_MOST) {
+		status = STATUS_BUSY_VALUE;
+	} else {
+		const uint32_t slot = registered_image_count;
+		(void)snprintf(registered_names[slot], sizeof(registered_names[slot]), "%s", kernel_file_name);
+		registered_images[slot].file_name = registered_names[slot];
+		registered_images[slot].begin = copy;
+		registered_images[slot].end = copy + image_byte_count;
+		registered_image_count = slot + 1u;
+	}
+	(void)pthread_mutex_unlock(&global_mutex);
+	if (status != STATUS_OK)
+		free(copy);
+	return status;
 }
 
 static result_status cuda_kernel_prepare(struct device_card *card, const char *kernel_file_name,

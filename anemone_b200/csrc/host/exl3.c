@@ -204,8 +204,8 @@ void exl3_moe_sizes(uint32_t pair_count, uint32_t job_count, uint32_t input_size
 	if (sizes_out == NULL)
 		return;
 	if (input_size != 0 && inner_size != 0 && input_size % EXL3_TRANSFORM == 0 && inner_size % EXL3_TRANSFORM == 0) {
-		sizes.gate_up_splits = exl3_moe_splits(input_size);
-		sizes.down_splits = exl3_moe_splits(inner_size);
+		sizes.gate_up_splits = exl3_moe_splits(input_size, inner_size);
+		sizes.down_splits = exl3_moe_splits(inner_size, input_size);
 		const uint64_t gate_up = (uint64_t)EXL3_PROJECTIONS * sizes.gate_up_splits * pair_count * inner_size * 4u;
 		const uint64_t down = (uint64_t)sizes.down_splits * pair_count * input_size * 4u;
 		sizes.product_bytes = gate_up > down ? gate_up : down;

@@ -5,14 +5,12 @@
  *     mma.sync.m16n8k16 (the stream order of the format IS that fragment order);
  *   - the 128-point Hadamard butterfly on one warp, four values a lane, in the stage order of the reference's
  *     transform (source/kernel_exl3.cu:104-124), so the FP32 bits are the same;
- *   - a product core: one CTA computes 128 outputs of one job for up to eight rows. The CTA's trellis rows arrive
- *     through a ring of shared-memory stages filled by bulk asynchronous copies (cp.async.bulk, completion on an
- *     mbarrier); four warps take interleaved K steps, decode in registers and accumulate in FP32 on the tensor cores;
- *     the four partial sums are added in warp order from +0. A CTA may take a part of K only (split K): the caller then
- *     adds the parts in a fixed order.
- *
- * Every mbarrier wait is bounded: a wait that runs out raises exl3_wait_expired (a module global the host can read)
- * and the CTA leaves without touching its outputs; nothing traps.
+ *   - a product core: one CTA computes 128 outputs of one job for up to eight rows. Four warps take interleaved K
+ *     steps; a lane loads its ring words straight from global memory into registers one round ahead, decodes them in
+ *     registers and accumulates in FP32 on the tensor cores; the four partial sums are added in warp order from +0. A
+ *     CTA may take a part of K only (split K): the caller then adds the parts in a fixed order.
+ *   - mbarrier and bulk-copy helpers for the prefill kernels' rings. Every mbarrier wait is bounded: a wait that runs
+ *     out raises exl3_wait_expired (a module global the host can read); nothing traps.
  */
 #ifndef AB_EXL3_DEVICE_CUH
 #define AB_EXL3_DEVICE_CUH
@@ -188,13 +186,10 @@ __device__ __forceinline__ void hadamard128_warp(float v[4], uint32_t lane)
 /* ------------------------------------------------------------------ the product core */
 
 struct exl3_product_shared {
-	uint64_t full[EXL3_STAGES];
-	uint64_t empty[EXL3_STAGES];
-	uint32_t failed;
+	uint32_t failed; /* kept for the callers' sake: the core has no wait that could fail */
 };
 
-/* Dynamic shared memory of a product CTA (exl3_geometry.h): the stage ring, then (aliased onto it after the K loop)
- * the warps' partial sums; the barriers live in static shared memory. */
+/* Dynamic shared memory of a product CTA (exl3_geometry.h): the warps' partial sums after the K loop. */
 
 /* sums[tile][c]: this thread's share of the CTA's 128 outputs x 8 columns after the cross-warp reduction: thread
  * (warp w, lane (g, t)) returns, for tiles j = 2 w and 2 w + 1, the m16n8 accumulator layout
@@ -202,8 +197,12 @@ struct exl3_product_shared {
  * matrix: the codes of a matrix of `outputs` outputs; group: which 128 outputs; the K steps (tile rows)
  * [step_begin, step_begin + step_count), a multiple of EXL3_STAGE_STEPS; operand_row: FP16 [inputs] of the pair that
  * stands in this lane's column (lane / 4; columns beyond the job's rows repeat column 0 and are ignored by the caller).
- * Warp w takes step 4 r + w of round r; the next round's operands are fetched while this round decodes.
- * Returns false if a bounded wait expired (the caller then stores nothing). All 128 threads call it. */
+ * Warp w takes step 4 r + w of round r. A lane reads its two ring words of each of the eight tiles of a step straight
+ * from global memory into registers (the warp's 16 loads of a step cover 8 x 16 bits_x2 contiguous bytes), one round
+ * ahead of the round it decodes, together with that round's operands: no shared memory, no barrier and no producer
+ * stand between the memory system and the decode, whose instruction issue is what bounds the kernel.
+ * Returns true (the signature keeps a verdict for callers written for a core with bounded waits). All 128 threads
+ * call it. */
 template <uint32_t BX2>
 __device__ __forceinline__ bool exl3_product_core(const unsigned char *matrix, uint32_t outputs, uint32_t group,
 						  uint32_t step_begin, uint32_t step_count,
@@ -211,45 +210,20 @@ __device__ __forceinline__ bool exl3_product_core(const unsigned char *matrix, u
 						  exl3_product_shared *shared, float sums[2][4])
 {
 	typedef exl3_ring<BX2> ring;
-	constexpr uint32_t row_bytes = EXL3_GROUP_TILES * ring::tile_bytes; /* the CTA's part of one tile row */
-	constexpr uint32_t stage_bytes = EXL3_STAGE_STEPS * row_bytes;
+	(void)shared;
 	const uint32_t lane = threadIdx.x % EXL3_WARP, warp = threadIdx.x / EXL3_WARP;
 	const uint32_t rounds = step_count / EXL3_STAGE_STEPS;
-	const uint64_t matrix_row_bytes = (uint64_t)(outputs / EXL3_TILE) * ring::tile_bytes;
-	const unsigned char *const source = matrix + (uint64_t)step_begin * matrix_row_bytes + (uint64_t)group * row_bytes;
-
-	if (threadIdx.x == 0) {
-		for (uint32_t stage = 0; stage < EXL3_STAGES; stage++) {
-			barrier_init(&shared->full[stage], 1);
-			barrier_init(&shared->empty[stage], EXL3_PRODUCT_WARPS);
-		}
-		shared->failed = 0;
-		asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-	}
-	__syncthreads();
-
-	/* warp 0 fills: lane s < 4 copies tile row s of a stage */
-	auto fill = [&](uint32_t round) {
-		const uint32_t stage = round % EXL3_STAGES;
-		if (lane == 0)
-			barrier_expect(&shared->full[stage], stage_bytes);
-		__syncwarp();
-		if (lane < EXL3_STAGE_STEPS)
-			bulk_load(dynamic_shared + stage * stage_bytes + lane * row_bytes,
-				  source + (uint64_t)(round * EXL3_STAGE_STEPS + lane) * matrix_row_bytes, row_bytes,
-				  &shared->full[stage]);
-	};
-	if (warp == 0)
-		for (uint32_t round = 0; round < EXL3_STAGES && round < rounds; round++)
-			fill(round);
-
+	const uint64_t step_words = (uint64_t)(outputs / EXL3_TILE) * ring::words; /* of one tile row of the matrix */
 	const uint32_t begin = ring::begin(lane);
 	const uint32_t word_index = begin / 32u, shift = begin % 32u, next_index = (word_index + 1u) % ring::words;
+	/* this warp's first step, the CTA's first tile */
+	const uint32_t *const words = reinterpret_cast<const uint32_t *>(matrix) + (step_begin + warp) * step_words +
+				      (uint64_t)group * EXL3_GROUP_TILES * ring::words;
+	const uint64_t round_words = EXL3_STAGE_STEPS * step_words;
 	/* this lane's B operand of round r: inputs 2 t, 2 t + 1 and 2 t + 8, 2 t + 9 of step 4 r + warp */
 	const uint32_t *const fed = reinterpret_cast<const uint32_t *>(operand_row + (step_begin + warp) * EXL3_TILE +
 								      (lane % 4u) * 2u);
 	constexpr uint32_t fed_round_words = EXL3_STAGE_STEPS * EXL3_TILE / 2u;
-	uint32_t next0 = __ldg(fed), next1 = __ldg(fed + 4);
 	float accumulators[EXL3_GROUP_TILES][4];
 #pragma unroll
 	for (uint32_t tile = 0; tile < EXL3_GROUP_TILES; tile++)
@@ -257,40 +231,41 @@ __device__ __forceinline__ bool exl3_product_core(const unsigned char *matrix, u
 		for (uint32_t c = 0; c < 4; c++)
 			accumulators[tile][c] = 0.0f;
 
-	for (uint32_t round = 0; round < rounds; round++) {
-		const uint32_t stage = round % EXL3_STAGES, use = round / EXL3_STAGES;
-		if (warp == 0 && round >= 1 && round - 1u + EXL3_STAGES < rounds) {
-			/* the slot of the previous round is free once all four warps have read it */
-			if (barrier_wait(&shared->empty[(round - 1u) % EXL3_STAGES], ((round - 1u) / EXL3_STAGES) & 1u))
-				fill(round - 1u + EXL3_STAGES);
-			else
-				shared->failed = 1;
-		}
-		const uint32_t b0 = next0, b1 = next1;
-		if (round + 1u < rounds) {
-			next0 = __ldg(fed + (round + 1u) * fed_round_words);
-			next1 = __ldg(fed + (round + 1u) * fed_round_words + 4);
-		}
-		if (!barrier_wait(&shared->full[stage], use & 1u)) {
-			shared->failed = 1;
+	uint32_t first[EXL3_GROUP_TILES][2], second[EXL3_GROUP_TILES][2], first_fed[2], second_fed[2];
+#define EXL3_ROUND_LOAD(set, set_fed, round)                                                                  \
+	do {                                                                                                   \
+		const uint32_t *const from = words + (uint64_t)(round) * round_words;                          \
+		_Pragma("unroll") for (uint32_t tile = 0; tile < EXL3_GROUP_TILES; tile++)                     \
+		{                                                                                              \
+			set[tile][0] = __ldg(from + tile * ring::words + word_index);                          \
+			set[tile][1] = __ldg(from + tile * ring::words + next_index);                          \
+		}                                                                                              \
+		set_fed[0] = __ldg(fed + (uint64_t)(round) * fed_round_words);                                 \
+		set_fed[1] = __ldg(fed + (uint64_t)(round) * fed_round_words + 4);                             \
+	} while (0)
+#define EXL3_ROUND_MULTIPLY(set, set_fed)                                                                     \
+	do {                                                                                                   \
+		_Pragma("unroll") for (uint32_t tile = 0; tile < EXL3_GROUP_TILES; tile++)                     \
+		{                                                                                              \
+			uint32_t fragment[4];                                                                  \
+			exl3_decode_fragment<BX2>(set[tile][0], set[tile][1], shift, fragment);                \
+			mma_f16(accumulators[tile], fragment, set_fed[0], set_fed[1]);                         \
+		}                                                                                              \
+	} while (0)
+	EXL3_ROUND_LOAD(first, first_fed, 0u);
+	for (uint32_t round = 0; round < rounds; round += 2u) {
+		if (round + 1u < rounds)
+			EXL3_ROUND_LOAD(second, second_fed, round + 1u);
+		EXL3_ROUND_MULTIPLY(first, first_fed);
+		if (round + 1u >= rounds)
 			break;
-		}
-		const uint32_t *const words =
-			reinterpret_cast<const uint32_t *>(dynamic_shared + stage * stage_bytes + warp * row_bytes);
-#pragma unroll
-		for (uint32_t tile = 0; tile < EXL3_GROUP_TILES; tile++) {
-			uint32_t fragment[4];
-			exl3_decode_fragment<BX2>(words[tile * ring::words + word_index],
-						  words[tile * ring::words + next_index], shift, fragment);
-			mma_f16(accumulators[tile], fragment, b0, b1);
-		}
-		__syncwarp();
-		if (lane == 0)
-			barrier_arrive(&shared->empty[stage]);
+		if (round + 2u < rounds)
+			EXL3_ROUND_LOAD(first, first_fed, round + 2u);
+		EXL3_ROUND_MULTIPLY(second, second_fed);
 	}
-	__syncthreads(); /* every read of the ring is done: its memory now holds the partial sums */
-	if (shared->failed != 0)
-		return false;
+#undef EXL3_ROUND_LOAD
+#undef EXL3_ROUND_MULTIPLY
+
 	float4 *const partial = reinterpret_cast<float4 *>(dynamic_shared); /* [warp][tile][lane] */
 #pragma unroll
 	for (uint32_t tile = 0; tile < EXL3_GROUP_TILES; tile++)
@@ -314,11 +289,6 @@ __device__ __forceinline__ bool exl3_product_core(const unsigned char *matrix, u
 			sums[mine][c] = total[c];
 	}
 	__syncthreads(); /* the partial sums are consumed: the caller may reuse the dynamic shared memory */
-	if (threadIdx.x == 0) /* a CTA may run the core again: leave no live barrier behind */
-		for (uint32_t stage = 0; stage < EXL3_STAGES; stage++) {
-			barrier_invalidate(&shared->full[stage]);
-			barrier_invalidate(&shared->empty[stage]);
-		}
 	return true;
 }
 

@@ -10,38 +10,33 @@
 #define EXL3_PRODUCT_WARPS 4u
 #define EXL3_PRODUCT_THREADS (EXL3_PRODUCT_WARPS * EXL3_WARP)
 #define EXL3_GROUP_TILES 8u /* adjacent output tiles of a product CTA: 128 outputs, one Hadamard block */
-#define EXL3_STAGE_STEPS 4u /* K steps (tile rows) of one pipeline stage: one a warp */
-#define EXL3_STAGES 4u
+#define EXL3_STAGE_STEPS 4u /* K steps (tile rows) of one round of a product CTA: one a warp */
 #define EXL3_TRANSFORM_WARPS 4u /* a transform CTA: one warp per 128-channel block */
 #define EXL3_TRANSFORM_THREADS (EXL3_TRANSFORM_WARPS * EXL3_WARP)
 #define EXL3_RECONSTRUCT_THREADS 256u
 #define EXL3_ROW_SUM_THREADS 128u
 
-/* bytes of one pipeline stage: EXL3_STAGE_STEPS tile rows of EXL3_GROUP_TILES tiles of 16 bits_x2 bytes */
-AB_INLINE uint32_t exl3_product_stage_bytes(uint32_t bits_x2)
-{
-	return EXL3_STAGE_STEPS * EXL3_GROUP_TILES * 16u * bits_x2;
-}
-
-/* bytes of the cross-warp partial sums that reuse the ring after the K loop: [warp][tile][lane] float4 */
+/* bytes of the cross-warp partial sums of a product CTA: [warp][tile][lane] float4 */
 #define EXL3_PRODUCT_PARTIAL_BYTES (EXL3_PRODUCT_WARPS * EXL3_GROUP_TILES * EXL3_WARP * 16u)
 
-/* Dynamic shared memory of a product CTA for one width; a launch of mixed widths takes the widest (K4). */
+/* Dynamic shared memory of a product CTA: the partial sums (the same for every width). */
 AB_INLINE uint32_t exl3_product_dynamic_bytes(uint32_t bits_x2)
 {
-	const uint32_t ring = EXL3_STAGES * exl3_product_stage_bytes(bits_x2);
-	return ring > EXL3_PRODUCT_PARTIAL_BYTES ? ring : EXL3_PRODUCT_PARTIAL_BYTES;
+	(void)bits_x2;
+	return EXL3_PRODUCT_PARTIAL_BYTES;
 }
 
-/* Split K of the fused B200 launches: a product over `inputs` is cut in this many equal runs of whole 128-input
- * blocks, each its own CTA, so that a decode step has several waves of short work items instead of one wave of long
- * ones; the last CTA to finish a (job, 128 outputs) adds the runs in ascending order from +0. The largest power of two
- * up to 8 that divides inputs / 128 and leaves at least 8 blocks (64 K steps) a run. */
-AB_INLINE uint32_t exl3_moe_splits(uint32_t inputs)
+/* Split K of the fused B200 launches: a product of `outputs` outputs over `inputs` inputs is cut in this many equal
+ * runs of whole 128-input blocks, each its own CTA; the last CTA to finish a (job, 128 outputs) adds the runs in
+ * ascending order from +0. A CTA that streams all of K is the cheapest (no partial sums to store and add), but a rank
+ * with few outputs then starts too few CTAs to fill the card: the smallest power of two, at most 8, that gives a job
+ * at least 32 work items (groups of 128 outputs times runs), dividing inputs / 128 and leaving a run at least 4
+ * blocks (32 K steps). */
+AB_INLINE uint32_t exl3_moe_splits(uint32_t inputs, uint32_t outputs)
 {
-	const uint32_t blocks = inputs / EXL3_TRANSFORM;
+	const uint32_t blocks = inputs / EXL3_TRANSFORM, groups = outputs / EXL3_TRANSFORM;
 	uint32_t splits = 1u;
-	while (splits < 8u && blocks % (2u * splits) == 0u && blocks / (2u * splits) >= 8u)
+	while (splits < 8u && groups * splits < 32u && blocks % (2u * splits) == 0u && blocks / (2u * splits) >= 4u)
 		splits *= 2u;
 	return splits;
 }

@@ -1,7 +1,7 @@
 /*
  * kernel_exl3_b200.cu: the routed-expert layer of one rank in four launches (struct exl3_moe_record), with a stored
  * width per expert. No counterpart in the reference, whose chain is five launches of one width plus a row sum; the
- * arithmetic of every value is the same chain's (exl3_passes.cuh) except that a product is cut in exl3_moe_splits(K)
+ * arithmetic of every value is the same chain's (exl3_passes.cuh) except that a product is cut in exl3_moe_splits(K, outputs)
  * runs of K whose FP32 sums are added in ascending order from +0.
  *   exl3_moe_input    grid (ceil(H / 128 / 4), jobs, 2) x 128   x . suh, Hadamard, FP16 operands of gate and of up
  *   exl3_moe_gate_up  grid (I / 128 * S, jobs, 2) x 128        a CTA streams one run of K of 128 gate or up outputs of
@@ -88,7 +88,7 @@ __device__ __forceinline__ void moe_gate_up(const struct exl3_moe_record &moe, u
 	const struct exl3_expert_record &record = moe.base;
 	const uint32_t lane = threadIdx.x % EXL3_WARP, warp = threadIdx.x / EXL3_WARP;
 	const uint32_t H = record.input_size, I = record.inner_size, pairs = record.pair_count;
-	const uint32_t runs = exl3_moe_splits(H), groups = I / EXL3_TRANSFORM;
+	const uint32_t runs = exl3_moe_splits(H, I), groups = I / EXL3_TRANSFORM;
 	const uint32_t group = blockIdx.x / runs, run = blockIdx.x % runs, projection = blockIdx.z;
 	const uint32_t steps = H / EXL3_TILE / runs;
 	const uint32_t fed_column = lane / 4u < job->row_count ? lane / 4u : 0u;
@@ -156,7 +156,7 @@ __device__ __forceinline__ void moe_down(const struct exl3_moe_record &moe, unsi
 	const struct exl3_expert_record &record = moe.base;
 	const uint32_t lane = threadIdx.x % EXL3_WARP, warp = threadIdx.x / EXL3_WARP;
 	const uint32_t H = record.input_size, I = record.inner_size, pairs = record.pair_count;
-	const uint32_t runs = exl3_moe_splits(I), groups = H / EXL3_TRANSFORM;
+	const uint32_t runs = exl3_moe_splits(I, H), groups = H / EXL3_TRANSFORM;
 	const uint32_t group = blockIdx.x / runs, run = blockIdx.x % runs;
 	const uint32_t steps = I / EXL3_TILE / runs;
 	const uint32_t fed_column = lane / 4u < job->row_count ? lane / 4u : 0u;

@@ -54,6 +54,8 @@ def parse():
     parser.add_argument("--prefill-rows", type=int, default=4096, help="0 skips the prefill part")
     parser.add_argument("--prefill-steps", type=int, default=5)
     parser.add_argument("--no-original-weights", action="store_true", help="skip the MXFP4 part")
+    parser.add_argument("--no-reference-kernels", action="store_true",
+                        help="skip the reference's own kernels on this card (N = 1 only)")
     return parser.parse_args()
 
 
@@ -332,6 +334,72 @@ def workload_config(args, config, world):
             "l2": "inputs larger than L2: every step routes to a different expert set (~58 experts of 257)"}
 
 
+def run_reference_kernels(args, api, base, draw_k3, local_rank):
+    """The reference's own EXL3 kernels on this card, beside this library's, on the same inputs: its retained chain
+    and its fast form (source/kernel_exl3.cu, source/kernel_exl3_wide.cu), recompiled for sm_100a from its sources into
+    oracle/_ref and launched through its own preparer. Its chain takes ONE stored width a record, so every expert is
+    K3 here (3 bits a weight; the headline workload's mix averages 3.1). Expert launches only: the router (this
+    library's, which writes the job table both read) and the reduction are outside the timed region."""
+    from oracle import binding, reference_kernels
+    if not reference_kernels.available():
+        return {"unavailable": "oracle/_ref holds no reference kernel images (built where the reference tree is present)"}
+    import ctypes as C
+    from anemone_b200 import records as R
+    from anemone_b200.moe import MoeLayer, MoeLayout
+    reference = binding.load_reference()
+    widths = np.full(base.total_experts, 3, dtype=np.uint32)
+    layout = MoeLayout(base, widths, 1, 0)
+    card = api.Card(local_rank, layout.arena_bytes)
+    try:
+        layer = MoeLayer(card, base, widths, (draw_k3(expert) for expert in range(base.total_experts)))
+        layer.connect_local([layer])
+        record = R.Exl3Expert(layout.jobs, layout.tokens, layout.operands, layout.products, layout.hidden,
+                              layout.products, base.hidden, layout.inner_local, layout.pairs, base.pairs_per_row,
+                              layout.job_capacity, 3, base.activation_limit, 0)
+        backend = reference_kernels.RenamingBackend()
+        chains = {"retained": list(reference_kernels.chain_launches(reference, backend, card, record,
+                                                                    card.arena_bytes, False)),
+                  "fast": list(reference_kernels.chain_launches(reference, backend, card, record, card.arena_bytes,
+                                                                True)),
+                  "ours": list(layer.launches[1:4])}
+        row_sum = R.ExpertRowSum(layout.products, layout.row_output, base.hidden, base.pairs_per_row)
+        sum_launch = R.KernelLaunch()
+        api.check(api.library().bb_exl3_row_sum_prepare(C.byref(row_sum), base.row_capacity, card.arena_bytes,
+                                                        card.ops_pointer, card.handle, C.byref(sum_launch)),
+                  "bb_exl3_row_sum_prepare")
+        for name in chains:
+            chains[name].append(sum_launch)
+        steps = step_inputs(base, args.rows, 3 + args.steps)
+        elapsed = {name: 0.0 for name in chains}
+        rows_of = {}
+        for index, (tokens, scores) in enumerate(steps):
+            layer.sequence += 1
+            layer.stage_step(0, layer.sequence, tokens, scores)
+            card.transfer_wait(card.upload_async(layout.step, 0, layout.step_input_bytes))
+            card.run(layer.launches[0:1])  # the router: the job table every chain reads
+            card.wait()
+            for name, launches in chains.items():
+                card.measure_begin()
+                card.run(launches)
+                card.measure_end()
+                us = card.measure_elapsed_us()
+                if index >= 3:
+                    elapsed[name] += us
+                rows_of[name] = card.download(layout.row_output, args.rows * base.hidden * 4, np.float32)
+        worst = float(max(np.abs(rows_of["ours"] - rows_of[name]).max() for name in ("retained", "fast")))
+    finally:
+        card.close()
+    out = {name + "_us_per_step": elapsed[name] / args.steps for name in elapsed}
+    out.update({"unit": "us of the expert launches of one decode step (input transform, products, activation, "
+                        "output transform, row sum), CUDA events", "rows": args.rows, "stored_width": 3,
+                "speedup_over_fast": out["fast_us_per_step"] / out["ours_us_per_step"],
+                "speedup_over_retained": out["retained_us_per_step"] / out["ours_us_per_step"],
+                "max_abs_difference_of_row_sums": worst,
+                "kernels": "the reference's source/kernel_exl3.cu (retained) and source/kernel_exl3_wide.cu (fast), "
+                           "recompiled for sm_100a, through its own exl3_experts_prepare / exl3_experts_fast_prepare"})
+    return out
+
+
 def run_original_weights(args, api, base, rank, world, local_rank, dist, barrier, maximum):
     """cfg5: routed experts MXFP4 (E8M0 scales 2^-8 .. 2^-4), the always-on expert E4M3 with one E8M0 scale per 32 by 32
     weights (the reference's FP8 format; the configuration's 128 x 128 FP32-scaled variant is not in the reference and
@@ -585,6 +653,14 @@ def main():
     prefill = None
     if args.prefill_rows > 0:
         prefill = run_prefill(args, api, config, widths, draw, rank, world, local_rank, dist, barrier, maximum)
+    reference_kernels = None
+    if rank == 0 and world == 1 and not args.no_reference_kernels:
+        def draw_k3(expert):
+            rng = np.random.default_rng([SEED, 3000 + expert])
+            return (synthetic.exl3_matrix(rng, config.hidden, config.inner, 3),
+                    synthetic.exl3_matrix(rng, config.hidden, config.inner, 3),
+                    synthetic.exl3_matrix(rng, config.inner, config.hidden, 3))
+        reference_kernels = run_reference_kernels(args, api, config, draw_k3, local_rank)
     original = None
     if not args.no_original_weights:
         original = run_original_weights(args, api, config, rank, world, local_rank, dist, barrier, maximum)
@@ -593,6 +669,8 @@ def main():
             line["prefill"] = prefill
         if original is not None:
             line["original_weights"] = original
+        if reference_kernels is not None:
+            line["reference_kernels"] = reference_kernels
         print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()

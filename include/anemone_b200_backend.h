@@ -177,6 +177,11 @@ MUST_CHECK result_status backend_b200_ipc_connect(struct device_card *accessor,
 /* Queue a fill of arena bytes (zeroing signal lines and scratch at load), behind everything queued before. */
 MUST_CHECK result_status backend_b200_fill(struct device_card *card, uint64_t arena_byte_offset, unsigned char value,
 					   uint64_t byte_count);
+/* Registers one more kernel file for kernel_prepare: an sm_100a cubin image the caller built (the bytes are copied;
+ * at most four, never under the name of a file the library embeds or of one registered before). Kernels of such a file
+ * follow the same contract: extern "C" __global__ f(record, arena address). Cards opened before or after see it. */
+MUST_CHECK result_status backend_b200_image_register(const char *kernel_file_name, const void *image,
+						     uint64_t image_byte_count);
 /* Waits for the card's queue, then reports whether any kernel of the EXL3 kernel files gave up a bounded wait on a
  * shared-memory barrier since the files were loaded (such a CTA stores nothing and returns; nothing traps):
  * *expired_out is 0 or 1. */

@@ -187,7 +187,7 @@ struct bb_exl3_shard_activation_record {
  * base is read as the five-pass chain reads it, except:
  *   - base.bits_per_weight may be EXL3_WIDTH_PER_EXPERT: expert e's three matrices then have stored width widths[e]
  *     (uint32 [expert_count] at widths_offset);
- *   - a product over K inputs is cut in S = exl3_moe_splits(K) runs (exl3_geometry.h of the kernel sources; the host
+ *   - a product over K inputs is cut in S = exl3_moe_splits(K, outputs) runs (exl3_geometry.h of the kernel sources; the host
  *     preparer reports the sizes that follow through exl3_moe_sizes). products: FP32 partial sums
  *     [2][S(input_size)][pair_count][inner_size] for gate/up, then reused as [S(inner_size)][pair_count][input_size]
  *     for down; the pair outputs FP32 [pair_count][input_size] are run 0 of the latter (output_offset ==

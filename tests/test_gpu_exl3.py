@@ -271,3 +271,60 @@ def test_shard_activation_equals_the_full_activation_on_its_columns(api, oracle)
     for offset, size in ((record.hidden_offset, pairs * count * 2), (record.operands_offset, pairs * count * 2)):
         assert (received[offset + size:offset + size + 64] == 0xC3).all()  # nothing written behind the ranges
     assert np.array_equal(received[weights_begin:weights_end], image[weights_begin:weights_end])
+
+
+@pytest.mark.parametrize("fast", [False, True])
+@pytest.mark.parametrize("stored", [2, 3, 4])
+def test_against_the_reference_kernels_on_the_card(api, oracle, reference, stored, fast):
+    """The reference's own kernels (its retained chain and its fast form, recompiled for sm_100a from its sources) run
+    through its own preparer on the same image as this library's chain: the input pass and the activation are the
+    same FP32 operations in the same order, so operands agree bit for bit where their inputs do; products differ by
+    the association of their FP32 sums only."""
+    from oracle import reference_kernels
+    if not reference_kernels.available():
+        pytest.skip("oracle/_ref holds no reference kernel images (reference tree absent at build time)")
+    case = ChainCase(oracle, 300 + stored, hidden=512, inner=256, rows=7, picks=2, expert_count=5,
+                     widths=[stored] * 5)
+    mine = run_chain(api, case, moe=False)
+    backend = reference_kernels.RenamingBackend()
+    card = api.Card(0, case.arena_bytes)
+    try:
+        card.upload(0, case.image)
+        launches = reference_kernels.chain_launches(reference, backend, card, case.record, case.arena_bytes, fast)
+        card.run(list(launches)[0:1])
+        card.wait()
+        pairs, H, I = case.pairs, case.H, case.I
+        operands = card.download(case.record.operands_offset, 2 * pairs * H * 2, np.uint16).reshape(2, pairs, H).copy()
+        row_sum = R.ExpertRowSum(case.record.output_offset, case.row_output_offset, H, case.ppr)
+        sum_launch = R.KernelLaunch()
+        api.check(api.library().bb_exl3_row_sum_prepare(C.byref(row_sum), case.rows, case.arena_bytes, card.ops_pointer,
+                                                        card.handle, C.byref(sum_launch)), "bb_exl3_row_sum_prepare")
+        card.run(list(launches)[1:] + [sum_launch])
+        card.wait()
+        theirs = card.download(0, case.arena_bytes)
+    finally:
+        card.close()
+    assert case.guards_intact(theirs) is None
+    live = case.live_pairs()
+    # the input pass of this library, run alone, leaves the same bits
+    card = api.Card(0, case.arena_bytes)
+    try:
+        card.upload(0, case.image)
+        own = (R.KernelLaunch * 5)()
+        api.check(api.library().exl3_experts_prepare(C.byref(case.record), case.arena_bytes, card.ops_pointer,
+                                                     card.handle, 100, own), "exl3_experts_prepare")
+        card.run(list(own)[0:1])
+        card.wait()
+        own_operands = card.download(case.record.operands_offset, 2 * pairs * H * 2, np.uint16).reshape(2, pairs, H)
+    finally:
+        card.close()
+    assert np.array_equal(own_operands[:, live], operands[:, live])
+    for name, dtype, shape in (("hidden", np.uint16, (pairs, I)), ("row_output", np.float32, (case.rows, H))):
+        a, b = case.view(mine, name, dtype).reshape(shape), case.view(theirs, name, dtype).reshape(shape)
+        if dtype == np.uint16:
+            a, b = synthetic.from_bfloat16(a[live]), synthetic.from_bfloat16(b[live])
+        assert np.isfinite(b).all() and np.abs(b).max() > 0
+        assert np.abs(a - b).max() <= MAX_ABS and cosine(a, b) >= COSINE, name
+    out_mine = case.view(mine, "products", np.float32)[:pairs * H].reshape(pairs, H)[live]
+    out_theirs = case.view(theirs, "products", np.float32)[:pairs * H].reshape(pairs, H)[live]
+    assert np.abs(out_mine - out_theirs).max() <= 1e-3 * max(1.0, float(np.abs(out_theirs).max()))

@@ -112,7 +112,9 @@ def test_moe_prepare():
     sizes = api.moe_sizes(12, 7, 512, 256)
     assert (sizes.gate_up_splits, sizes.down_splits) == (1, 1) and sizes.counter_bytes == 7 * 6 * 4
     big = api.moe_sizes(72, 65, 4096, 2048)
-    assert (big.gate_up_splits, big.down_splits) == (4, 2) and big.product_bytes == 2 * 4 * 72 * 2048 * 4
+    assert (big.gate_up_splits, big.down_splits) == (2, 1) and big.product_bytes == 2 * 2 * 72 * 2048 * 4
+    eighth = api.moe_sizes(72, 65, 4096, 256)  # a rank of eight: few outputs, so more runs of K
+    assert (eighth.gate_up_splits, eighth.down_splits) == (8, 1)
     record.base.operands_offset = layout.take(sizes.operand_bytes)
     record.base.products_offset = record.base.output_offset = layout.take(max(sizes.product_bytes, 12 * 512 * 8))
     record.widths_offset, record.row_output_offset, record.expert_count = layout.take(64), layout.take(4 * 512 * 4), 9
