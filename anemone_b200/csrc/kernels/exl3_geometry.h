@@ -42,18 +42,15 @@ AB_INLINE uint32_t exl3_moe_splits(uint32_t inputs, uint32_t outputs)
 }
 
 /* ---- prefill (kernel_exl3_prefill) ---- */
-#define EXL3_PREFILL_GEMM_THREADS 608u /* two copy warps, an issuing warp, sixteen decode warps */
+#define EXL3_PREFILL_GEMM_THREADS 576u /* a copy warp, an issuing warp, sixteen decode warps */
 #define EXL3_PREFILL_OPERAND_PARTS 4u /* an operand CTA takes a quarter of a tile's rows */
 #define EXL3_PREFILL_GATE_UP_STEPS 2u /* steps of 16 inputs of one stage: two matrices */
 #define EXL3_PREFILL_DOWN_STEPS 4u /* one matrix */
-/* ring depths: operand blocks (mostly from L2), decoded weights (made on the SM), trellis rows (from HBM) */
+/* ring depths: operand blocks (bulk copies, mostly from L2), decoded weights (made on the SM) */
 #define EXL3_PREFILL_A_STAGES 4u
-#define EXL3_PREFILL_B_STAGES 3u
-#define EXL3_PREFILL_T_STAGES 8u
-/* matrices x steps is 4 in both launches: a stage is 4 x 4096 bytes of operands, 4 x 2 x 4096 of decoded weights (two
- * groups of 128 outputs), 4 x 2048 of trellis tiles */
-#define EXL3_PREFILL_DYNAMIC_BYTES \
-	(EXL3_PREFILL_A_STAGES * 16384u + EXL3_PREFILL_B_STAGES * 32768u + EXL3_PREFILL_T_STAGES * 8192u)
+#define EXL3_PREFILL_B_STAGES 4u
+/* the largest of the product CTAs' forms: a stage is 32 KB of one ring and 16 KB of the other */
+#define EXL3_PREFILL_DYNAMIC_BYTES (EXL3_PREFILL_A_STAGES * 32768u + EXL3_PREFILL_B_STAGES * 16384u)
 #define EXL3_PREFILL_STAGING_ROW 132u /* floats of a staged accumulator row */
 
 #endif

@@ -18,7 +18,7 @@
 #include "exl3_passes.cuh"
 #include "router_device.cuh"
 
-#define PREFILL_FIRST_DECODE_WARP 3u /* behind the two copy warps and the issuing warp */
+#define PREFILL_FIRST_DECODE_WARP 2u /* behind the copy warp and the issuing warp */
 #define PREFILL_DECODE_WARPS 16u
 #define PREFILL_GROUPS 2u /* groups of 128 outputs of one product CTA */
 #define PREFILL_DECODE_THREADS (PREFILL_DECODE_WARPS * EXL3_WARP)
@@ -30,12 +30,10 @@ struct prefill_shared {
 	uint64_t a_free[EXL3_PREFILL_A_STAGES]; /* the products that read them are done */
 	uint64_t b_full[EXL3_PREFILL_B_STAGES]; /* the stage's decoded weights are written */
 	uint64_t b_free[EXL3_PREFILL_B_STAGES]; /* the products that read them are done */
-	uint64_t t_full[EXL3_PREFILL_T_STAGES]; /* the stage's trellis rows have landed */
-	uint64_t t_free[EXL3_PREFILL_T_STAGES]; /* every decode warp has read them */
 	uint64_t done; /* every product of the CTA is done */
 	uint32_t tensor_memory;
 	volatile uint32_t failed;
-	uint32_t armed_a, armed_t; /* K blocks whose copies were started */
+	uint32_t armed_a; /* K blocks whose copies were started */
 	uint32_t issued; /* 1: products were issued and `done` will complete */
 };
 
@@ -303,25 +301,21 @@ __device__ __forceinline__ void decode_sync()
 }
 
 /* Dynamic shared memory of a product CTA, for TILES row tiles of one expert, MATRICES matrices, GROUPS groups of 128
- * outputs and stages of KSTEPS steps of 16 inputs. Three rings of different depth, because their contents wait for
- * different things:
+ * outputs and stages of KSTEPS steps of 16 inputs. Two rings:
  *   A ring        EXL3_PREFILL_A_STAGES x [tile][matrix] operand blocks (128 rows x 16 KSTEPS FP16 in the tensor cores'
  *                 layout, KSTEPS x 4096 bytes): bulk copies, mostly from L2
  *   B ring        EXL3_PREFILL_B_STAGES x [matrix] blocks of decoded weights, 128 GROUPS outputs x 16 KSTEPS FP16 in
  *                 the same layout (one instruction multiplies all groups and reads the operand rows once): written by
  *                 the decode warps, read by the products of EVERY row tile
- *   trellis ring  EXL3_PREFILL_T_STAGES x [matrix][step][group][8 tiles] (1024 bytes a group): bulk copies from HBM */
+ * The trellis words go straight from global memory into the decode warps' registers, one stage ahead. */
 template <uint32_t MATRICES, uint32_t KSTEPS, uint32_t TILES, uint32_t GROUPS> struct prefill_rings {
 	static constexpr uint32_t block_bytes = KSTEPS * 4096u;
 	static constexpr uint32_t a_stage = TILES * MATRICES * block_bytes;
 	static constexpr uint32_t b_piece = GROUPS * 2048u; /* eight inputs of 128 GROUPS outputs */
 	static constexpr uint32_t b_block = GROUPS * block_bytes; /* of one matrix */
 	static constexpr uint32_t b_stage = MATRICES * b_block;
-	static constexpr uint32_t trellis_row = GROUPS * 1024u;
-	static constexpr uint32_t t_stage = MATRICES * KSTEPS * trellis_row;
 	static constexpr uint32_t b_at = EXL3_PREFILL_A_STAGES * a_stage;
-	static constexpr uint32_t t_at = b_at + EXL3_PREFILL_B_STAGES * b_stage;
-	static constexpr uint32_t bytes = t_at + EXL3_PREFILL_T_STAGES * t_stage;
+	static constexpr uint32_t bytes = b_at + EXL3_PREFILL_B_STAGES * b_stage;
 	static constexpr uint32_t columns = TILES * MATRICES * GROUPS * PREFILL_COLUMNS; /* of tensor memory */
 	static constexpr uint32_t stage_tiles = MATRICES * GROUPS * KSTEPS * EXL3_GROUP_TILES; /* decoded a stage */
 	static constexpr uint32_t warp_tiles = stage_tiles / PREFILL_DECODE_WARPS; /* adjacent tiles a decode warp */
@@ -337,8 +331,8 @@ template <uint32_t MATRICES, uint32_t KSTEPS, uint32_t TILES, uint32_t GROUPS> s
 
 /* The K loop of one CTA. matrices[m]: the codes of matrix m (`outputs` outputs), of which the CTA takes the `groups`
  * (1 .. GROUPS) groups of 128 outputs from group `first_group`; operand_blocks[tile * MATRICES + m]: row tile `tile`'s
- * operand blocks for matrix m; `blocks` stages of 16 KSTEPS inputs. Warp 0 copies trellis rows, warp 1 operand blocks,
- * one thread of warp 2 issues the products, warps 3 .. decode. On return the decode warps know whether the
+ * operand blocks for matrix m; `blocks` stages of 16 KSTEPS inputs. Warp 0 copies operand blocks, one thread of warp 1
+ * issues the products, warps 2 .. decode. On return the decode warps know whether the
  * accumulators (prefill_rings::column from shared->tensor_memory) are complete; the other warps return false.
  * All threads call. */
 template <uint32_t BX2, uint32_t MATRICES, uint32_t KSTEPS, uint32_t TILES, uint32_t GROUPS>
@@ -349,8 +343,7 @@ __device__ __forceinline__ bool prefill_products(const unsigned char *const (&ma
 {
 	typedef exl3_ring<BX2> ring;
 	typedef prefill_rings<MATRICES, KSTEPS, TILES, GROUPS> rings;
-	constexpr uint32_t AS = EXL3_PREFILL_A_STAGES, BS = EXL3_PREFILL_B_STAGES, TS = EXL3_PREFILL_T_STAGES;
-	constexpr uint32_t row_bytes = EXL3_GROUP_TILES * ring::tile_bytes; /* one group's part of a tile row */
+	constexpr uint32_t AS = EXL3_PREFILL_A_STAGES, BS = EXL3_PREFILL_B_STAGES;
 	const uint32_t lane = threadIdx.x % EXL3_WARP, warp = threadIdx.x / EXL3_WARP;
 
 	if (threadIdx.x == 0) {
@@ -362,14 +355,9 @@ __device__ __forceinline__ bool prefill_products(const unsigned char *const (&ma
 			barrier_init(&shared->b_full[stage], PREFILL_DECODE_WARPS);
 			barrier_init(&shared->b_free[stage], 1);
 		}
-		for (uint32_t stage = 0; stage < TS; stage++) {
-			barrier_init(&shared->t_full[stage], 1);
-			barrier_init(&shared->t_free[stage], PREFILL_DECODE_WARPS);
-		}
 		barrier_init(&shared->done, 1);
 		shared->failed = 0;
 		shared->armed_a = 0;
-		shared->armed_t = 0;
 		shared->issued = 0;
 		asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 	}
@@ -386,37 +374,6 @@ __device__ __forceinline__ bool prefill_products(const unsigned char *const (&ma
 	const uint32_t accumulators = shared->tensor_memory;
 
 	if (warp == 0) {
-		/* trellis copies: lane 0 waits for the stage and arms its barrier; lane (m, step) then copies the groups'
-		 * adjacent tiles of its tile row */
-		const uint64_t matrix_row_bytes = (uint64_t)(outputs / EXL3_TILE) * ring::tile_bytes;
-		const uint32_t m = lane / KSTEPS, step = lane % KSTEPS;
-		uint32_t block = 0;
-		for (; block < blocks; block++) {
-			const uint32_t stage = block % TS, use = block / TS;
-			uint32_t good = 1;
-			if (lane == 0) {
-				if (use > 0 && !barrier_wait(&shared->t_free[stage], (use - 1u) & 1u))
-					good = 0;
-				else
-					barrier_expect(&shared->t_full[stage], MATRICES * KSTEPS * groups * row_bytes);
-			}
-			good = __shfl_sync(0xFFFFFFFFu, good, 0);
-			if (good == 0)
-				break;
-			if (lane < MATRICES * KSTEPS)
-				bulk_load(dynamic_shared + rings::t_at + stage * rings::t_stage + lane * rings::trellis_row,
-					  matrices[m] + (uint64_t)(block * KSTEPS + step) * matrix_row_bytes +
-						  (uint64_t)first_group * row_bytes,
-					  groups * row_bytes, &shared->t_full[stage]);
-		}
-		if (lane == 0) {
-			shared->armed_t = block;
-			if (block < blocks)
-				shared->failed = 1;
-		}
-		return false;
-	}
-	if (warp == 1) {
 		/* operand copies: lane (tile, m) copies that block */
 		uint32_t block = 0;
 		for (; block < blocks; block++) {
@@ -443,7 +400,7 @@ __device__ __forceinline__ bool prefill_products(const unsigned char *const (&ma
 		}
 		return false;
 	}
-	if (warp == 2) {
+	if (warp == 1) {
 		/* products: one thread; every row tile's products read the same decoded weights */
 		if (lane == 0) {
 			bool good = true;
@@ -497,27 +454,48 @@ __device__ __forceinline__ bool prefill_products(const unsigned char *const (&ma
 		const uint32_t g = decoder / (chunks * KSTEPS) % GROUPS, m = decoder / (chunks * KSTEPS * GROUPS);
 		const uint32_t begin = ring::begin(lane);
 		const uint32_t word_index = begin / 32u, shift = begin % 32u, next_index = (word_index + 1u) % ring::words;
-		const uint32_t words_at = rings::t_at + (m * KSTEPS + step) * rings::trellis_row +
-					  (g * EXL3_GROUP_TILES + chunk * rings::warp_tiles) * ring::tile_bytes;
 		const uint32_t to_at = rings::b_at + m * rings::b_block + step * 2u * rings::b_piece +
 				       (g * EXL3_GROUP_TILES + chunk * rings::warp_tiles) * 2u * 128u + lane * 4u;
+		/* this lane's ring words of the warp's tiles of block 0; a block further is KSTEPS tile rows further */
+		const uint64_t step_words = (uint64_t)(outputs / EXL3_TILE) * ring::words;
+		const uint32_t *const words = reinterpret_cast<const uint32_t *>(matrices[m]) + step * step_words +
+					      ((uint64_t)(first_group + g) * EXL3_GROUP_TILES + chunk * rings::warp_tiles) *
+						      ring::words;
+		const bool mine_exists = g < groups;
+		uint32_t ahead[rings::warp_tiles][2];
+		if (mine_exists)
+#pragma unroll
+			for (uint32_t mine = 0; mine < rings::warp_tiles; mine++) {
+				ahead[mine][0] = __ldg(words + mine * ring::words + word_index);
+				ahead[mine][1] = __ldg(words + mine * ring::words + next_index);
+			}
 		bool good = true;
 		for (uint32_t block = 0; block < blocks && good; block++) {
-			const uint32_t st = block % TS, sb = block % BS;
+			const uint32_t sb = block % BS;
+			uint32_t current[rings::warp_tiles][2];
+#pragma unroll
+			for (uint32_t mine = 0; mine < rings::warp_tiles; mine++) {
+				current[mine][0] = ahead[mine][0];
+				current[mine][1] = ahead[mine][1];
+			}
+			if (mine_exists && block + 1u < blocks) {
+				const uint32_t *const next = words + (uint64_t)(block + 1u) * KSTEPS * step_words;
+#pragma unroll
+				for (uint32_t mine = 0; mine < rings::warp_tiles; mine++) {
+					ahead[mine][0] = __ldg(next + mine * ring::words + word_index);
+					ahead[mine][1] = __ldg(next + mine * ring::words + next_index);
+				}
+			}
 			if (block >= BS)
 				good = barrier_wait(&shared->b_free[sb], (block / BS - 1u) & 1u);
-			good = good && barrier_wait(&shared->t_full[st], (block / TS) & 1u);
 			if (!good)
 				break;
-			if (g < groups) {
-				const uint32_t *const words =
-					reinterpret_cast<const uint32_t *>(dynamic_shared + st * rings::t_stage + words_at);
+			if (mine_exists) {
 				unsigned char *const to_stage = dynamic_shared + sb * rings::b_stage + to_at;
 #pragma unroll
 				for (uint32_t mine = 0; mine < rings::warp_tiles; mine++) {
 					uint32_t fragment[4];
-					exl3_decode_fragment<BX2>(words[mine * ring::words + word_index],
-								  words[mine * ring::words + next_index], shift, fragment);
+					exl3_decode_fragment<BX2>(current[mine][0], current[mine][1], shift, fragment);
 					/* fragment f: outputs 16 tile + g + 8 (f % 2), inputs 16 step + 2 t + 8 (f / 2), lane 4 g + t:
 					 * the warp's 32 words are the 128 bytes of one K piece of one group of eight outputs */
 					uint32_t *const to = reinterpret_cast<uint32_t *>(to_stage + mine * 2u * 128u);
@@ -529,10 +507,8 @@ __device__ __forceinline__ bool prefill_products(const unsigned char *const (&ma
 				asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 			}
 			__syncwarp();
-			if (lane == 0) {
+			if (lane == 0)
 				barrier_arrive(&shared->b_full[sb]);
-				barrier_arrive(&shared->t_free[st]);
-			}
 		}
 		if (good)
 			good = barrier_wait(&shared->done, 0u);
@@ -588,10 +564,6 @@ template <uint32_t COLUMNS> __device__ __forceinline__ void prefill_release(pref
 		for (uint32_t back = 0; back < EXL3_PREFILL_A_STAGES && back < shared->armed_a; back++) {
 			const uint32_t block = shared->armed_a - 1u - back;
 			(void)barrier_wait(&shared->a_full[block % EXL3_PREFILL_A_STAGES], (block / EXL3_PREFILL_A_STAGES) & 1u);
-		}
-		for (uint32_t back = 0; back < EXL3_PREFILL_T_STAGES && back < shared->armed_t; back++) {
-			const uint32_t block = shared->armed_t - 1u - back;
-			(void)barrier_wait(&shared->t_full[block % EXL3_PREFILL_T_STAGES], (block / EXL3_PREFILL_T_STAGES) & 1u);
 		}
 		if (shared->issued != 0)
 			(void)barrier_wait(&shared->done, 0u);
@@ -799,7 +771,7 @@ __device__ __forceinline__ void prefill_down(const struct exl3_prefill_record &r
 		break;                                                                                 \
 	}
 
-/* grid (widest I / 128, tile capacity) x 608: a single row tile is taken by the CTAs of even x with two groups of 128
+/* grid (widest I / 128, tile capacity) x 576: a single row tile is taken by the CTAs of even x with two groups of 128
  * outputs each; two row tiles of one expert by every x with one group each (tensor memory holds 512 columns) */
 extern "C" __global__ void __launch_bounds__(EXL3_PREFILL_GEMM_THREADS, 1)
 	exl3_prefill_gate_up(struct exl3_prefill_record record, unsigned char *arena)
@@ -828,7 +800,7 @@ extern "C" __global__ void __launch_bounds__(EXL3_PREFILL_GEMM_THREADS, 1)
 	}
 }
 
-/* grid (ceil(H / 256), tile capacity) x 608: two groups of 128 outputs a CTA, for one row tile or for two of one expert */
+/* grid (ceil(H / 256), tile capacity) x 576: two groups of 128 outputs a CTA, for one row tile or for two of one expert */
 extern "C" __global__ void __launch_bounds__(EXL3_PREFILL_GEMM_THREADS, 1)
 	exl3_prefill_down(struct exl3_prefill_record record, unsigned char *arena)
 {

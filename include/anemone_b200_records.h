@@ -369,8 +369,8 @@ struct router_select_b200_arguments {
  *                          ascending row order, and their count
  *   exl3_prefill_tiles     grid 1 x 1024: the tile table: (expert, first entry, rows) per 128-row tile, tile count
  *   exl3_prefill_operands  grid (tile capacity, 4 ceil(H / 512), 2) x 128: FP16 gate and up operands of every tile row
- *   exl3_prefill_gate_up   grid (max(I, shared I) / 128, tile capacity) x 608: both products, SwiGLU, FP16 down operands
- *   exl3_prefill_down      grid (ceil(H / 256), tile capacity) x 608: down product, output transform: FP32 pair outputs
+ *   exl3_prefill_gate_up   grid (max(I, shared I) / 128, tile capacity) x 576: both products, SwiGLU, FP16 down operands
+ *   exl3_prefill_down      grid (ceil(H / 256), tile capacity) x 576: down product, output transform: FP32 pair outputs
  *   exl3_prefill_row_sum   grid (ceil(H / 512), rows) x 128: FP32 row sums over the row's LOCAL pairs, ascending slots
  *                          from +0
  * Workspace at workspace_offset, parts in this order, each aligned to 1024 bytes (exl3_prefill_sizes gives them):

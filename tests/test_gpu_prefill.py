@@ -195,7 +195,7 @@ def test_prefill_preparer_refusals(api):
             return code
 
         assert status() == 0
-        assert launches[4].grid[0] == 1 and launches[4].block[0] == 608 and launches[5].grid[0] == 1
+        assert launches[4].grid[0] == 1 and launches[4].block[0] == 576 and launches[5].grid[0] == 1
         assert status(local_first=2, local_count=2) == 0
         for changes in ({"input_size": 192}, {"inner_size": 64}, {"picks": 0}, {"picks": 5}, {"expert_count": 0},
                         {"reserved_zero": (C.c_uint32 * 2)(0, 1)}, {"workspace_offset": layout.workspace + 512},
