@@ -18,8 +18,14 @@ One JSON line on rank 0:
   roofline  the dominant kernel (exl3_moe_gate_up) timed alone, launch by launch, with CUDA events, against the
             measured HBM copy bandwidth of MEASURED_PEAKS.json;
   cpu_baseline  the CPU oracle (OpenMP, all host cores) on a bounded sample of the same step, scaled to the step.
+Further objects of the same line, each with its own value, e2e and roofline where they apply:
+  prefill            cfg4: the same layer for M = 4096 rows, Zipf(1.1) routing, experts sharded over the ranks,
+                     tensor-core (tcgen05) grouped products, ordered reduction with owner runs;
+  original_weights   cfg5 decode: MXFP4 routed experts and the E4M3 always-on expert, E4M3 block-quantized activations;
+  reference_kernels  (N = 1) the reference's own EXL3 kernels, recompiled for sm_100a from its sources into oracle/_ref,
+                     timed on this card beside this library's expert launches on the same inputs (every expert K3).
 --impl reference times that CPU restatement of the reference's arithmetic alone (the reference has no engine CPU path
-for this layer and its GPU code has no sm_100 build), on the same metric and config.
+for this layer), on the same metric and config.
 """
 import argparse
 import json
