@@ -267,3 +267,33 @@ def test_prefill_full_size_properties(api):
         card.close()
     scale = max(float(np.abs(decode_rows).max()), 1.0)
     assert np.abs(first[:8] - decode_rows).max() <= 2e-3 * scale and cosine(first[:8], decode_rows) >= 0.99999
+
+
+def test_prefill_empty_and_full_calls(api, oracle):
+    """A call with no live row writes nothing and the next call is unaffected; a call at the row capacity, where one
+    expert takes every row (its tiles: one pair and none left over), matches the oracle."""
+    config = MoeConfig(hidden=256, inner=256, experts=4, shared=0, picks=1, row_capacity=256)
+    rows = 256
+    widths, matrices, tokens, scores = make_inputs(5, config, rows, 3)
+    scores[:, 2] += 100.0  # every row picks expert 2: 256 rows = exactly two full tiles, taken as one pair
+    experts, weights = moe_reference.route(oracle, config, scores)
+    assert (experts == 2).all()
+    expected = moe_reference.rank_partial(oracle, config, widths, matrices, tokens, experts, weights, 1, 0)[0]
+    card = api.Card(0, PrefillLayout(config, widths).arena_bytes)
+    try:
+        layer = PrefillLayer(card, config, widths, matrices)
+        first = layer.step(tokens, scores)
+        assert np.abs(first - expected).max() <= MAX_ABS and cosine(first, expected) >= COSINE
+        counts = card.download(layer.layout.workspace, 5 * 4, np.uint32)
+        assert list(counts) == [0, 0, 256, 0, 2]
+        before = card.download(layer.layout.row_output, rows * config.hidden * 4)
+        layer.load(tokens[:0], scores[:0])
+        layer.run()
+        assert layer.result(0).shape == (0, config.hidden)
+        counts = card.download(layer.layout.workspace, 5 * 4, np.uint32)
+        assert list(counts) == [0, 0, 0, 0, 0]
+        assert np.array_equal(card.download(layer.layout.row_output, rows * config.hidden * 4), before)
+        again = layer.step(tokens[:130], scores[:130])  # two tiles, the second with two rows
+        assert np.array_equal(again.view(np.uint32), first[:130].view(np.uint32))
+    finally:
+        card.close()
