@@ -318,11 +318,8 @@ template <uint32_t MATRICES, uint32_t KSTEPS, uint32_t TILES, uint32_t GROUPS> s
 	static constexpr uint32_t b_at = EXL3_PREFILL_A_STAGES * a_stage;
 	static constexpr uint32_t bytes = b_at + EXL3_PREFILL_B_STAGES * b_stage;
 	static constexpr uint32_t columns = TILES * MATRICES * GROUPS * PREFILL_COLUMNS; /* of tensor memory */
-	static constexpr uint32_t stage_tiles = MATRICES * GROUPS * KSTEPS * EXL3_GROUP_TILES; /* decoded a stage */
-	static constexpr uint32_t warp_tiles = stage_tiles / PREFILL_DECODE_WARPS; /* adjacent tiles a decode warp */
 	static_assert(bytes <= EXL3_PREFILL_DYNAMIC_BYTES, "the host sizes the rings");
 	static_assert(columns <= 512u, "tensor memory has 512 columns");
-	static_assert(warp_tiles == 2u || warp_tiles == 4u, "a decode warp takes 2 or 4 adjacent tiles");
 	/* first column of the accumulator of (row tile, matrix, group) */
 	__device__ static constexpr uint32_t column(uint32_t tile, uint32_t m, uint32_t g)
 	{
@@ -353,7 +350,7 @@ __device__ __forceinline__ bool prefill_products(const unsigned char *const (&ma
 			barrier_init(&shared->a_free[stage], 1);
 		}
 		for (uint32_t stage = 0; stage < BS; stage++) {
-			barrier_init(&shared->b_full[stage], PREFILL_DECODE_WARPS);
+			barrier_init(&shared->b_full[stage], 4u); /* the four warps of the team that decodes the stage */
 			barrier_init(&shared->b_free[stage], 1);
 		}
 		barrier_init(&shared->done, 1);
@@ -447,70 +444,89 @@ __device__ __forceinline__ bool prefill_products(const unsigned char *const (&ma
 		return false;
 	}
 
-	/* decode: warp d takes warp_tiles adjacent output tiles of one (matrix, group, step) of the stage */
+	/* decode: the sixteen warps are four teams of four; team q decodes the WHOLE stages q, q + 4, ... (with four
+	 * decoded-weights stages in the ring a team owns one of them), so that the teams work on four different stages
+	 * at once and a warp crosses a barrier and a proxy fence once per stage of 8 or 16 tiles, not once per 2 or 4.
+	 * Warp r of a team takes the stage's units r * units_a_warp .. : a unit is the eight adjacent tiles of one
+	 * (matrix, group, step), whose ring words the lane loads straight from global memory, one unit ahead. */
 	{
-		constexpr uint32_t chunks = EXL3_GROUP_TILES / rings::warp_tiles;
-		const uint32_t decoder = warp - PREFILL_FIRST_DECODE_WARP;
-		const uint32_t chunk = decoder % chunks, step = decoder / chunks % KSTEPS;
-		const uint32_t g = decoder / (chunks * KSTEPS) % GROUPS, m = decoder / (chunks * KSTEPS * GROUPS);
+		static_assert(EXL3_PREFILL_B_STAGES == 4u && PREFILL_DECODE_WARPS == 16u, "a team of four warps a stage");
+		constexpr uint32_t units = MATRICES * GROUPS * KSTEPS, units_a_warp = units / 4u;
+		static_assert(units % 4u == 0u, "whole units a warp");
+		const uint32_t decoder = warp - PREFILL_FIRST_DECODE_WARP, team = decoder / 4u, member = decoder % 4u;
 		const uint32_t begin = ring::begin(lane);
 		const uint32_t word_index = begin / 32u, shift = begin % 32u, next_index = (word_index + 1u) % ring::words;
-		const uint32_t to_at = rings::b_at + m * rings::b_block + step * 2u * rings::b_piece +
-				       (g * EXL3_GROUP_TILES + chunk * rings::warp_tiles) * 2u * 128u + lane * 4u;
-		/* this lane's ring words of the warp's tiles of block 0; a block further is KSTEPS tile rows further */
 		const uint64_t step_words = (uint64_t)(outputs / EXL3_TILE) * ring::words;
-		const uint32_t *const words = reinterpret_cast<const uint32_t *>(matrices[m]) + step * step_words +
-					      ((uint64_t)(first_group + g) * EXL3_GROUP_TILES + chunk * rings::warp_tiles) *
-						      ring::words;
-		const bool mine_exists = g < groups;
-		uint32_t ahead[rings::warp_tiles][2];
-		if (mine_exists)
-#pragma unroll
-			for (uint32_t mine = 0; mine < rings::warp_tiles; mine++) {
-				ahead[mine][0] = __ldg(words + mine * ring::words + word_index);
-				ahead[mine][1] = __ldg(words + mine * ring::words + next_index);
-			}
+		const uint32_t my_blocks = blocks > team ? (blocks - team + 3u) / 4u : 0u;
+		const uint32_t count = my_blocks * units_a_warp; /* units this warp decodes, in order */
+		/* unit i of this warp: block team + 4 (i / units_a_warp), unit member * units_a_warp + i % units_a_warp of
+		 * the stage = (matrix m, group g, step) in that order of significance */
+		uint32_t first[EXL3_GROUP_TILES][2], second[EXL3_GROUP_TILES][2];
+#define PREFILL_UNIT_PLACE(i, block, m, g, step)                                                             \
+	const uint32_t block = team + 4u * ((i) / units_a_warp);                                             \
+	const uint32_t unit_ = member * units_a_warp + (i) % units_a_warp;                                    \
+	const uint32_t step = unit_ % KSTEPS, g = unit_ / KSTEPS % GROUPS, m = unit_ / (KSTEPS * GROUPS)
+#define PREFILL_UNIT_LOAD(set, i)                                                                            \
+	do {                                                                                                  \
+		PREFILL_UNIT_PLACE(i, block_, m_, g_, step_);                                                 \
+		if (g_ < groups) {                                                                            \
+			const uint32_t *const from = reinterpret_cast<const uint32_t *>(matrices[m_]) +      \
+						     ((uint64_t)block_ * KSTEPS + step_) * step_words +        \
+						     (uint64_t)(first_group + g_) * EXL3_GROUP_TILES * ring::words; \
+			_Pragma("unroll") for (uint32_t tile = 0; tile < EXL3_GROUP_TILES; tile++)            \
+			{                                                                                     \
+				set[tile][0] = __ldg(from + tile * ring::words + word_index);                 \
+				set[tile][1] = __ldg(from + tile * ring::words + next_index);                 \
+			}                                                                                     \
+		}                                                                                             \
+	} while (0)
+#define PREFILL_UNIT_DECODE(set, i)                                                                          \
+	do {                                                                                                  \
+		PREFILL_UNIT_PLACE(i, block_, m_, g_, step_);                                                 \
+		if ((i) % units_a_warp == 0u && block_ >= BS)                                                 \
+			good = barrier_wait(&shared->b_free[team], (block_ / BS - 1u) & 1u);                  \
+		if (!good)                                                                                    \
+			break;                                                                                \
+		if (g_ < groups) {                                                                            \
+			unsigned char *const to_unit = dynamic_shared + rings::b_at + team * rings::b_stage + \
+						       m_ * rings::b_block + step_ * 2u * rings::b_piece +    \
+						       g_ * EXL3_GROUP_TILES * 2u * 128u + lane * 4u;           \
+			_Pragma("unroll") for (uint32_t tile = 0; tile < EXL3_GROUP_TILES; tile++)            \
+			{                                                                                     \
+				uint32_t fragment[4];                                                         \
+				exl3_decode_fragment<BX2>(set[tile][0], set[tile][1], shift, fragment);       \
+				/* fragment f: outputs 16 tile + g + 8 (f % 2), inputs 16 step + 2 t + 8 (f / 2): the warp's 32 \
+				 * words are the 128 bytes of one K piece of one group of eight outputs */   \
+				uint32_t *const to = reinterpret_cast<uint32_t *>(to_unit + tile * 2u * 128u); \
+				to[0] = fragment[0];                                                          \
+				to[128u / 4u] = fragment[1];                                                  \
+				to[rings::b_piece / 4u] = fragment[2];                                        \
+				to[(rings::b_piece + 128u) / 4u] = fragment[3];                               \
+			}                                                                                     \
+		}                                                                                             \
+		if ((i) % units_a_warp == units_a_warp - 1u) {                                                \
+			asm volatile("fence.proxy.async.shared::cta;" ::: "memory");                        \
+			__syncwarp();                                                                         \
+			if (lane == 0)                                                                        \
+				barrier_arrive(&shared->b_full[team]);                                        \
+		}                                                                                             \
+	} while (0)
 		bool good = true;
-		for (uint32_t block = 0; block < blocks && good; block++) {
-			const uint32_t sb = block % BS;
-			uint32_t current[rings::warp_tiles][2];
-#pragma unroll
-			for (uint32_t mine = 0; mine < rings::warp_tiles; mine++) {
-				current[mine][0] = ahead[mine][0];
-				current[mine][1] = ahead[mine][1];
-			}
-			if (mine_exists && block + 1u < blocks) {
-				const uint32_t *const next = words + (uint64_t)(block + 1u) * KSTEPS * step_words;
-#pragma unroll
-				for (uint32_t mine = 0; mine < rings::warp_tiles; mine++) {
-					ahead[mine][0] = __ldg(next + mine * ring::words + word_index);
-					ahead[mine][1] = __ldg(next + mine * ring::words + next_index);
-				}
-			}
-			if (block >= BS)
-				good = barrier_wait(&shared->b_free[sb], (block / BS - 1u) & 1u);
-			if (!good)
+		if (count > 0u)
+			PREFILL_UNIT_LOAD(first, 0u);
+		for (uint32_t i = 0; i < count && good; i += 2u) {
+			if (i + 1u < count)
+				PREFILL_UNIT_LOAD(second, i + 1u);
+			PREFILL_UNIT_DECODE(first, i);
+			if (i + 1u >= count || !good)
 				break;
-			if (mine_exists) {
-				unsigned char *const to_stage = dynamic_shared + sb * rings::b_stage + to_at;
-#pragma unroll
-				for (uint32_t mine = 0; mine < rings::warp_tiles; mine++) {
-					uint32_t fragment[4];
-					exl3_decode_fragment<BX2>(current[mine][0], current[mine][1], shift, fragment);
-					/* fragment f: outputs 16 tile + g + 8 (f % 2), inputs 16 step + 2 t + 8 (f / 2), lane 4 g + t:
-					 * the warp's 32 words are the 128 bytes of one K piece of one group of eight outputs */
-					uint32_t *const to = reinterpret_cast<uint32_t *>(to_stage + mine * 2u * 128u);
-					to[0] = fragment[0];
-					to[128u / 4u] = fragment[1];
-					to[rings::b_piece / 4u] = fragment[2];
-					to[(rings::b_piece + 128u) / 4u] = fragment[3];
-				}
-				asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-			}
-			__syncwarp();
-			if (lane == 0)
-				barrier_arrive(&shared->b_full[sb]);
+			if (i + 2u < count)
+				PREFILL_UNIT_LOAD(first, i + 2u);
+			PREFILL_UNIT_DECODE(second, i + 1u);
 		}
+#undef PREFILL_UNIT_PLACE
+#undef PREFILL_UNIT_LOAD
+#undef PREFILL_UNIT_DECODE
 		if (good)
 			good = barrier_wait(&shared->done, 0u);
 		if (!good)
