@@ -251,11 +251,16 @@ class Card:
         check(self.ops.measure_elapsed_us(self.handle, WAIT_NANOSECONDS, C.byref(value)), "measure_elapsed_us")
         return value.value
 
-    def waits_expired(self):
-        """Waits for the queue; True if a kernel gave up a bounded barrier wait (its CTA then stored nothing)."""
+    def expired_bits(self):
+        """Waits for the queue; the bits the card's kernels set when they gave up: 1 a bounded wait ran out, 2 a
+        sequence was replayed, 4 a step named more rows than were prepared (push and exchange kernels)."""
         expired = C.c_uint32()
         check(library().backend_b200_waits_expired(self.handle, C.byref(expired)), "waits_expired")
-        return expired.value != 0
+        return expired.value
+
+    def waits_expired(self):
+        """Waits for the queue; True if a kernel gave up a bounded wait (its CTA then stored nothing more)."""
+        return self.expired_bits() != 0
 
     def launch_count(self):
         return library().backend_b200_launch_count(self.handle)

@@ -18,7 +18,7 @@
 #include "driver_api.h"
 #include "kernel_images.h"
 
-#define CARD_MODULES_MOST 16u
+#define CARD_MODULES_MOST 24u
 #define NANOSECONDS_PER_SECOND 1000000000ull
 #define POLL_NANOSECONDS 20000l
 #define SMALL_WRITE_SLOTS 64u

@@ -109,6 +109,27 @@ class OrderedRowSumPublish(C.Structure):
                 ("pairs_per_row", C.c_uint32)]
 
 
+ORDERED_PUSH_FP32, ORDERED_PUSH_BF16 = 0, 1
+TP_EXCHANGE_FORM_PUSH, TP_EXCHANGE_FORM_OWNER_SUMS = 0, 1
+
+
+class OrderedPush(C.Structure):
+    _fields_ = [("peer_table_offset", C.c_uint64), ("region_offset", C.c_uint64), ("input_offset", C.c_uint64),
+                ("output_offset", C.c_uint64), ("inbox_offset", C.c_uint64), ("step_offset", C.c_uint64),
+                ("parity_stride", C.c_uint64), ("deadline_cycles", C.c_uint64), ("inbox_rank_stride", C.c_uint64),
+                ("element_count", C.c_uint32), ("rank_count", C.c_uint32), ("rank", C.c_uint32),
+                ("payload_format", C.c_uint32), ("incoming_host_mask", C.c_uint32), ("reserved_zero", C.c_uint32)]
+
+
+class TpExchange(C.Structure):
+    _fields_ = [("collective", OrderedPush), ("layer", C.c_uint32), ("layer_count", C.c_uint32),
+                ("row_width", C.c_uint32), ("reserved_zero", C.c_uint32)]
+
+
+class OrderedPushDescription(C.Structure):
+    _fields_ = [("arguments", OrderedPush), ("arena_byte_count", C.c_uint64)]
+
+
 class RouterSelectB200(C.Structure):
     _fields_ = [("scores_offset", C.c_uint64), ("expert_table_offset", C.c_uint64), ("picks_offset", C.c_uint64),
                 ("weights_offset", C.c_uint64), ("jobs_offset", C.c_uint64), ("step_offset", C.c_uint64),
@@ -228,7 +249,8 @@ class OrderedCollectiveKernels(C.Structure):
 
 for _record, _bytes in ((Exl3Reconstruct, 32), (Exl3Expert, 80), (ExpertJob, 96), (ExpertRowSum, 24),
                         (Exl3ShardActivation, 96), (Exl3Moe, 112), (TrunkLinearQuantized, 72), (TrunkHidden, 32), (TrunkRowsAdd, 24), (Exl3Prefill, 136), (Exl3PrefillTile, 16), (Exl3PrefillEntry, 8), (Exl3PrefillParts, 56), (StepBlock, 16), (OrderedPeer, 32),
-                        (OrderedCollective, 80), (OrderedReduceBf16, 96), (OrderedRowSumPublish, 96),
+                        (OrderedCollective, 80), (OrderedReduceBf16, 96), (OrderedRowSumPublish, 96), (OrderedPush, 96),
+                        (TpExchange, 112),
                         (RouterSelectB200, 80), (StepInputSelect, 40), (ActivationQuantize, 40), (ExpertGateUp, 64), (ExpertDown, 56),
                         (KernelLaunch, 232), (CardDescription, 168)):
     assert C.sizeof(_record) == _bytes, (_record.__name__, C.sizeof(_record), _bytes)

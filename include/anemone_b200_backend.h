@@ -182,9 +182,10 @@ MUST_CHECK result_status backend_b200_fill(struct device_card *card, uint64_t ar
  * follow the same contract: extern "C" __global__ f(record, arena address). Cards opened before or after see it. */
 MUST_CHECK result_status backend_b200_image_register(const char *kernel_file_name, const void *image,
 						     uint64_t image_byte_count);
-/* Waits for the card's queue, then reports whether any kernel of the EXL3 kernel files gave up a bounded wait on a
- * shared-memory barrier since the files were loaded (such a CTA stores nothing and returns; nothing traps):
- * *expired_out is 0 or 1. */
+/* Waits for the card's queue, then reports whether any kernel of the library's kernel files gave up a bounded wait
+ * since the files were loaded (a shared-memory barrier of the prefill products; a signal line of the push and the
+ * exchange, whose kernels also report a replayed sequence, 2, and a row count beyond the prepared rows, 4). Such a CTA
+ * stores nothing more and returns; nothing traps. *expired_out is 0, or the kernels' bits or-ed. */
 MUST_CHECK result_status backend_b200_waits_expired(struct device_card *card, uint32_t *expired_out);
 /* Kernel launches this card has queued since it was opened, graph launches counted by their kernel nodes. */
 uint64_t backend_b200_launch_count(const struct device_card *card);

@@ -85,6 +85,65 @@ MUST_CHECK result_status ordered_reduce_bf16_prepare(const struct ordered_reduce
 						     const struct backend_operations *backend,
 						     struct device_card *card, struct kernel_launch *launches_out);
 
+/* ---- one-shot push all-reduce (include/anemone/ordered_push.h:37-59) ---- */
+
+struct ordered_push_description {
+	struct ordered_push_arguments arguments;
+	uint64_t arena_byte_count;
+};
+
+/* include/anemone/ordered_push.h:42-44: the handle of ("kernel_ordered_push", "ordered_push"). */
+MUST_CHECK result_status ordered_push_kernel_prepare(const struct backend_operations *backend,
+						     struct device_card *card, uint32_t *kernel_out);
+
+/* include/anemone/ordered_push.h:45-47 (source/ordered_push.c:63-161): the reference's checks and refusals, its
+ * record copied unchanged into the launch. The launch is groups x blocks CTAs of 256 threads (the reference: one CTA).
+ * A record that is well formed but names a host mirror (incoming_host_mask != 0) is STATUS_UNSUPPORTED. The slot's
+ * signal lines, ORDERED_PUSH_PHASES * rank_count * 128 bytes, must be zero before the first launch. */
+MUST_CHECK result_status ordered_push_prepare(const struct ordered_push_description *description, uint32_t kernel,
+					      struct kernel_launch *launch_out);
+
+/* include/anemone/ordered_push.h:54-59: host_writer_masks_out[owner] = the sources that lack direct access to
+ * `owner` (direct_reader_masks[owner] then names the accessors qualified to WRITE the owner). All-reduce only. */
+MUST_CHECK result_status ordered_push_routes_prepare(const struct ordered_collective_route_description *description,
+						     uint32_t *host_writer_masks_out);
+
+/* ---- the exchange of a tensor-parallel layer site (include/anemone/tp_exchange.h:49-63) ---- */
+
+/* include/anemone/tp_exchange.h:49-51: the handle of ("kernel_tp_exchange", "tp_exchange"). */
+MUST_CHECK result_status tp_exchange_kernel_prepare(const struct backend_operations *backend,
+						    struct device_card *card, uint32_t *kernel_out);
+
+/* include/anemone/tp_exchange.h:52-55 (source/tp_exchange.c:26-48): the push of the step's live rows under the
+ * layer's own sequence, one launch. element_count is a whole number of rows; the reference's row is its model's 5120
+ * elements, and that is what this entry assumes; tp_exchange_rows_prepare takes the width. layer < layer_count <=
+ * TP_EXCHANGE_MAXIMUM_PHASES; element_count <= TP_EXCHANGE_MAXIMUM_ELEMENTS. */
+MUST_CHECK result_status tp_exchange_prepare(const struct ordered_push_description *description, uint32_t layer,
+					     uint32_t layer_count, uint32_t kernel, struct kernel_launch *launch_out);
+MUST_CHECK result_status tp_exchange_rows_prepare(const struct ordered_push_description *description,
+						  uint32_t row_width, uint32_t layer, uint32_t layer_count,
+						  uint32_t kernel, struct kernel_launch *launch_out);
+
+/* include/anemone/tp_exchange.h:56-58 (source/tp_exchange.c:50-88): the four handles of a form. Forms
+ * TP_EXCHANGE_FORM_PUSH and TP_EXCHANGE_FORM_OWNER_SUMS; the ring and copy-engine forms are STATUS_UNSUPPORTED. */
+MUST_CHECK result_status tp_exchange_wide_kernels_prepare(const struct backend_operations *backend,
+							  struct device_card *card, uint32_t form,
+							  uint32_t kernels_out[TP_EXCHANGE_WIDE_LAUNCHES]);
+
+/* include/anemone/tp_exchange.h:59-63 (source/tp_exchange.c:90-136): four launches a caller queues in order, as the
+ * reference's PUBLISH, READY, SUM, DONE are. Here the first launch is the whole exchange (values out, READY, the
+ * ordered sums, for the owner sums the one rounding to bfloat16 and the stores into every rank's output array, DONE)
+ * and the other three are empty kernels of one small CTA, kept so a caller's table keeps its four entries. The owner
+ * sums want every offset and stride a multiple of 16 bytes and no host route, as the reference does. */
+MUST_CHECK result_status tp_exchange_wide_prepare(const struct ordered_push_description *description, uint32_t layer,
+						  uint32_t layer_count,
+						  const uint32_t kernels[TP_EXCHANGE_WIDE_LAUNCHES], uint32_t form,
+						  struct kernel_launch launches_out[TP_EXCHANGE_WIDE_LAUNCHES]);
+MUST_CHECK result_status tp_exchange_wide_rows_prepare(const struct ordered_push_description *description,
+						       uint32_t row_width, uint32_t layer, uint32_t layer_count,
+						       const uint32_t kernels[TP_EXCHANGE_WIDE_LAUNCHES], uint32_t form,
+						       struct kernel_launch launches_out[TP_EXCHANGE_WIDE_LAUNCHES]);
+
 #ifdef __cplusplus
 }
 #endif

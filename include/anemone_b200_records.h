@@ -319,6 +319,82 @@ struct ordered_row_sum_publish_arguments {
 };
 
 /* ------------------------------------------------------------------------------------------------------------
+ * One-shot push all-reduce and the tensor-parallel exchange built on it (reference:
+ * include/anemone/ordered_push_records.h:8-33, include/anemone/tp_exchange_records.h:10-62).
+ *
+ * A slot begins with ORDERED_PUSH_PHASES * rank_count signal lines of 128 bytes: line (phase, source) of a rank's
+ * slot is written only by rank `source` (by a peer store), so every wait polls local memory. Behind the lines, at
+ * offsets relative to the slot: the FP32 input, the output, and rank_count inboxes inbox_rank_stride bytes apart.
+ * A source stores its input (FP32, or rounded to bfloat16: payload_format) into inbox [source] of every rank, then
+ * its READY line there; a rank adds its inboxes in ascending rank order from +0, one rounded FP32 add a rank; DONE
+ * lines are an all-rank barrier before return, so an inbox may be refilled as soon as the launch has returned.
+ * The launch runs groups x blocks CTAs (grid.x x grid.y, grid.x <= ORDERED_PUSH_GROUPS): group g moves and adds the
+ * g-th part of the payload and owns the g-th 8-byte word of every line, which holds the sequence itself; the second
+ * half of a rank's own READY and DONE lines holds the groups' arrival counters, touched by the rank's CTAs only.
+ * ---------------------------------------------------------------------------------------------------------- */
+#define KERNEL_FILE_ORDERED_PUSH "kernel_ordered_push"
+#define KERNEL_ORDERED_PUSH "ordered_push"
+#define ORDERED_PUSH_ARGUMENT_BYTES 96u
+#define ORDERED_PUSH_FP32 0u
+#define ORDERED_PUSH_BF16 1u
+#define ORDERED_PUSH_PHASES 2u
+#define ORDERED_PUSH_READY 0u
+#define ORDERED_PUSH_DONE 1u
+#define ORDERED_PUSH_GROUPS 8u /* grid.x at most: the flag words of a line */
+#define ORDERED_PUSH_GROUP_BLOCKS 16u /* grid.y at most */
+#define ORDERED_PUSH_BLOCK_VECTORS 1024u /* four-element vectors a CTA is given before another CTA is added */
+
+struct ordered_push_arguments {
+	uint64_t peer_table_offset; /* struct ordered_collective_peer [rank_count], indexed by destination */
+	uint64_t region_offset;
+	uint64_t input_offset; /* FP32 [element_count], inside a parity slot like the next two */
+	uint64_t output_offset; /* FP32 [element_count]; bfloat16 [element_count] for the owner sums */
+	uint64_t inbox_offset;
+	uint64_t step_offset;
+	uint64_t parity_stride;
+	uint64_t deadline_cycles;
+	uint64_t inbox_rank_stride;
+	uint32_t element_count;
+	uint32_t rank_count;
+	uint32_t rank;
+	uint32_t payload_format;
+	uint32_t incoming_host_mask; /* the reference's PCIe host mirrors: must be 0 here */
+	uint32_t reserved_zero;
+};
+
+/* The exchange of a tensor-parallel layer site: the push with the live rows of the step block and a sequence of its
+ * own for every layer, 2 * (step sequence * layer_count + layer) + (step sequence & 1), so that the layers of a step
+ * share one region and the step's parity still selects the slot. element_count is a whole number of rows of
+ * row_width elements (the reference fixes the width at compile time to its model's 5120 and keeps 8 reserved bytes
+ * where row_width is); step.row_count of them are exchanged.
+ * Forms: the push (every rank gets the FP32 sums), and the owner sums: rank d owns rows [R d / ranks, R (d + 1) / ranks)
+ * of the step's R, every rank stores only that shard into rank d's inbox, rank d adds it in rank order, rounds ONCE to
+ * bfloat16 (nearest even, a not-a-number to 0x7FC0) and stores the bfloat16 values into every rank's output array. */
+#define KERNEL_FILE_TP_EXCHANGE "kernel_tp_exchange"
+#define KERNEL_TP_EXCHANGE "tp_exchange"
+#define KERNEL_TP_EXCHANGE_OWNER "tp_exchange_owner"
+#define KERNEL_TP_EXCHANGE_SETTLED "tp_exchange_settled"
+#define TP_EXCHANGE_FORM_PUSH 0u
+#define TP_EXCHANGE_FORM_OWNER_SUMS 1u
+#define TP_EXCHANGE_FORM_OWNER_RING_SUMS 2u /* the reference's four-rank bfloat16 ring order: not offered */
+#define TP_EXCHANGE_FORM_CE_OWNER_SUMS 3u /* its copy-engine forms: not offered */
+#define TP_EXCHANGE_FORM_CE_OWNER_RING_SUMS 4u
+#define TP_EXCHANGE_OWNER_ALIGNMENT 16u
+#define TP_EXCHANGE_WIDE_LAUNCHES 4u
+#define TP_EXCHANGE_MAXIMUM_PHASES 1024u /* layer_count at most (the reference: 8 phases a layer, 40 layers) */
+#define TP_EXCHANGE_MAXIMUM_ELEMENTS (1u << 26) /* the reference: 5120 * 2 * 1024 */
+#define TP_EXCHANGE_REFERENCE_ROW_WIDTH 5120u
+#define TP_EXCHANGE_ARGUMENT_BYTES 112u
+
+struct tp_exchange_arguments {
+	struct ordered_push_arguments collective;
+	uint32_t layer;
+	uint32_t layer_count;
+	uint32_t row_width;
+	uint32_t reserved_zero;
+};
+
+/* ------------------------------------------------------------------------------------------------------------
  * Router (B200 extension of the reference's router_select_entry, include/anemone/router_records.h:7-52): scores
  * FP32 [rows][expert_count] -> for each live row the `picks` experts of largest score (a not-a-number above every
  * number, -0 below +0, the lower expert first among equals), slots in ascending expert order, affinity
@@ -619,6 +695,8 @@ AB_RECORD_HAS(ordered_collective_peer, 32);
 AB_RECORD_HAS(ordered_collective_arguments, 80);
 AB_RECORD_HAS(ordered_reduce_bf16_arguments, 96);
 AB_RECORD_HAS(ordered_row_sum_publish_arguments, 96);
+AB_RECORD_HAS(ordered_push_arguments, ORDERED_PUSH_ARGUMENT_BYTES);
+AB_RECORD_HAS(tp_exchange_arguments, TP_EXCHANGE_ARGUMENT_BYTES);
 AB_RECORD_HAS(router_select_b200_arguments, 80);
 AB_RECORD_HAS(step_input_select_arguments, 40);
 AB_RECORD_HAS(exl3_prefill_tile, 16);

@@ -67,6 +67,13 @@ void orc_ordered_sum(const float *const *inputs, uint32_t rank_count, uint32_t e
 /* The same sum rounded once to bfloat16. */
 void orc_ordered_reduce_bf16(const float *const *inputs, uint32_t rank_count, uint32_t element_count,
 			     uint16_t *output);
+/* The one-shot push (source/kernel_ordered_push.cuh:121-290): payload_format 0 = FP32 wire, the sum above; 1 = every
+ * rank's value (its own too) rounded to bfloat16 to nearest even (cvt.rn.bf16.f32) before the same adds. */
+void orc_ordered_push(const float *const *inputs, uint32_t rank_count, uint32_t element_count, uint32_t payload_format,
+		      float *output);
+/* The owner sums (source/kernel_tp_exchange.cu:190-247): the push's sum rounded once to bfloat16. */
+void orc_owner_sums(const float *const *inputs, uint32_t rank_count, uint32_t element_count, uint32_t payload_format,
+		    uint16_t *output);
 /* The four operations of the reference's host twin, same argument meaning as ordered_collective_host. */
 int orc_ordered_collective(const float *const *inputs, float *const *outputs, uint32_t rank_count,
 			   uint32_t element_count, int operation);

@@ -60,6 +60,10 @@ def load_oracle():
     lib.orc_ordered_sum.argtypes = [C.POINTER(f32p), C.c_uint32, C.c_uint32, f32p]
     lib.orc_ordered_reduce_bf16.restype = None
     lib.orc_ordered_reduce_bf16.argtypes = [C.POINTER(f32p), C.c_uint32, C.c_uint32, u16p]
+    lib.orc_ordered_push.restype = None
+    lib.orc_ordered_push.argtypes = [C.POINTER(f32p), C.c_uint32, C.c_uint32, C.c_uint32, f32p]
+    lib.orc_owner_sums.restype = None
+    lib.orc_owner_sums.argtypes = [C.POINTER(f32p), C.c_uint32, C.c_uint32, C.c_uint32, u16p]
     lib.orc_ordered_collective.restype = C.c_int
     lib.orc_ordered_collective.argtypes = [C.POINTER(f32p), C.POINTER(f32p), C.c_uint32, C.c_uint32, C.c_int]
     lib.orc_router_row.restype = None

@@ -32,6 +32,41 @@ void orc_ordered_reduce_bf16(const float *const *inputs, uint32_t rank_count, ui
 
 /* source/ordered_collective.c:144-206. Slices are ceil(n / ranks) elements; reduce-scatter writes only the owner's
  * output at full-array indices; gather copies slice owner's input. Returns 0, or 1 for arguments it refuses. */
+/* cvt.rn.bf16.f32 as the push's bfloat16 wire applies it to every rank's value (source/kernel_ordered_push.cuh:
+ * 143-158): to nearest even, a finite value beyond the format to infinity, a not-a-number to 0x7FFF. */
+static float push_wire_value(float value, uint32_t payload_format)
+{
+	if (payload_format == 0)
+		return value;
+	uint32_t bits;
+	memcpy(&bits, &value, sizeof(bits));
+	bits = (bits & 0x7FFFFFFFu) > 0x7F800000u ? 0x7FFF0000u : (bits + 0x7FFFu + ((bits >> 16) & 1u)) & 0xFFFF0000u;
+	memcpy(&value, &bits, sizeof(bits));
+	return value;
+}
+
+void orc_ordered_push(const float *const *inputs, uint32_t rank_count, uint32_t element_count, uint32_t payload_format,
+		      float *output)
+{
+	for (uint32_t element = 0; element < element_count; element++) {
+		volatile float sum = 0.0f;
+		for (uint32_t rank = 0; rank < rank_count; rank++)
+			sum = sum + push_wire_value(inputs[rank][element], payload_format);
+		output[element] = sum;
+	}
+}
+
+void orc_owner_sums(const float *const *inputs, uint32_t rank_count, uint32_t element_count, uint32_t payload_format,
+		    uint16_t *output)
+{
+	for (uint32_t element = 0; element < element_count; element++) {
+		volatile float sum = 0.0f;
+		for (uint32_t rank = 0; rank < rank_count; rank++)
+			sum = sum + push_wire_value(inputs[rank][element], payload_format);
+		output[element] = orc_bfloat16_bits(sum);
+	}
+}
+
 int orc_ordered_collective(const float *const *inputs, float *const *outputs, uint32_t rank_count,
 			   uint32_t element_count, int operation)
 {

@@ -191,3 +191,92 @@ def test_prefill_expert_parallel(api, oracle, mode):
         finally:
             for card in cards:
                 card.close()
+
+
+@pytest.mark.parametrize("payload", [0, 1])
+def test_push_and_owner_sums_across_cards(api, oracle, payload):
+    """The one-shot push and the exchange's owner sums between real cards: every rank stores into every rank's inbox
+    over NVLink, every wait polls local memory; FP32 sums and bfloat16 owner sums bit for bit on every rank."""
+    lib = api.library()
+    lib.ordered_push_kernel_prepare.argtypes = [C.POINTER(api.BackendOperations), C.c_void_p, C.POINTER(C.c_uint32)]
+    lib.ordered_push_prepare.argtypes = [C.POINTER(R.OrderedPushDescription), C.c_uint32, C.POINTER(R.KernelLaunch)]
+    lib.tp_exchange_wide_kernels_prepare.argtypes = [C.POINTER(api.BackendOperations), C.c_void_p, C.c_uint32,
+                                                     C.POINTER(C.c_uint32)]
+    lib.tp_exchange_wide_rows_prepare.argtypes = [C.POINTER(R.OrderedPushDescription), C.c_uint32, C.c_uint32,
+                                                  C.c_uint32, C.POINTER(C.c_uint32), C.c_uint32,
+                                                  C.POINTER(R.KernelLaunch)]
+    width, capacity, layers = 4096, 64, 2
+    elements = width * capacity
+    for ranks in world_sizes(api):
+        rng = np.random.default_rng(700 + ranks + payload)
+        layout = api.Layout()
+        peer_table, step = layout.take(16 * 32), layout.take(16)
+        signals = 2 * ranks * 128
+        input_at, output_at, inbox_at = signals, signals + 4 * elements, signals + 8 * elements
+        stride = api.align(inbox_at + ranks * 4 * elements, 128)
+        region = layout.take(2 * stride, 128)
+        arena_bytes = layout.take(4096, 4096)
+        cards = [api.Card(rank, arena_bytes) for rank in range(ranks)]
+        try:
+            push, owner = {}, {}
+            for rank, card in enumerate(cards):
+                card.fill(0, 0, arena_bytes)
+                peers = (R.OrderedPeer * ranks)()
+                for peer in range(ranks):
+                    peers[peer].region_offset = region
+                card.upload(peer_table, np.frombuffer(bytes(peers), dtype=np.uint8))
+                for peer, other in enumerate(cards):
+                    card.peer_connect(other, 0, peer_table + 32 * peer)
+                arguments = R.OrderedPush(peer_table, region, input_at, output_at, inbox_at, step, stride,
+                                          2_000_000_000, 4 * elements, elements, ranks, rank, payload, 0, 0)
+                description = R.OrderedPushDescription(arguments, arena_bytes)
+                kernel = C.c_uint32()
+                api.check(lib.ordered_push_kernel_prepare(card.ops_pointer, card.handle, C.byref(kernel)), "kernel")
+                push[rank] = R.KernelLaunch()
+                api.check(lib.ordered_push_prepare(C.byref(description), kernel.value, C.byref(push[rank])), "push")
+                kernels = (C.c_uint32 * 4)()
+                api.check(lib.tp_exchange_wide_kernels_prepare(card.ops_pointer, card.handle, 1, kernels), "kernels")
+                for layer in range(layers):
+                    owner[(rank, layer)] = (R.KernelLaunch * 4)()
+                    api.check(lib.tp_exchange_wide_rows_prepare(C.byref(description), width, layer, layers, kernels, 1,
+                                                                owner[(rank, layer)]), "owner")
+            for card in cards:
+                card.wait()
+            # the plain push: the step's sequence itself
+            for sequence in (1, 2, 3):
+                inputs = [rng.normal(0, 0.05, elements).astype(np.float32) for _ in range(ranks)]
+                inputs[0][0], inputs[1][0] = 16777216.0, 1.0
+                expected = np.zeros(elements, dtype=np.float32)
+                oracle.orc_ordered_push(pointer_array(inputs), ranks, elements, payload, ptr(expected, f32p))
+                for rank, card in enumerate(cards):
+                    card.upload(step, np.frombuffer(bytes(R.StepBlock(sequence, capacity, 0)), dtype=np.uint8))
+                    card.upload(region + (sequence & 1) * stride + input_at, inputs[rank])
+                for rank, card in enumerate(cards):  # queue every rank before waiting for any
+                    card.run([push[rank]])
+                for rank, card in enumerate(cards):
+                    card.wait()
+                    assert card.expired_bits() == 0
+                    got = card.download(region + (sequence & 1) * stride + output_at, 4 * elements, np.float32)
+                    assert np.array_equal(got.view(np.uint32), expected.view(np.uint32)), (ranks, sequence, rank)
+            # the owner sums, two layers a step sharing the region; the steps go on from the push's sequences
+            for model_step, rows in ((40, 64), (41, 37), (42, 1)):
+                for layer in range(layers):
+                    sequence = (model_step * layers + layer) * 2 + (model_step & 1)
+                    live = rows * width
+                    inputs = [rng.normal(0, 0.05, elements).astype(np.float32) for _ in range(ranks)]
+                    inputs[0][0], inputs[1][0] = 16777216.0, 1.0
+                    expected = np.zeros(live, dtype=np.uint16)
+                    oracle.orc_owner_sums(pointer_array(inputs), ranks, live, payload, ptr(expected, u16p))
+                    for rank, card in enumerate(cards):
+                        card.upload(step, np.frombuffer(bytes(R.StepBlock(model_step, rows, 0)), dtype=np.uint8))
+                        card.upload(region + (sequence & 1) * stride + input_at, inputs[rank])
+                    for rank, card in enumerate(cards):
+                        card.run(owner[(rank, layer)])
+                    for rank, card in enumerate(cards):
+                        card.wait()
+                        assert card.expired_bits() == 0
+                        got = card.download(region + (sequence & 1) * stride + output_at, 2 * live, np.uint16)
+                        assert np.array_equal(got, expected), (ranks, model_step, layer, rank)
+        finally:
+            for card in cards:
+                card.close()
