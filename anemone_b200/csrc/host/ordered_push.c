@@ -42,10 +42,11 @@ result_status ordered_push_kernel_prepare(const struct backend_operations *backe
 				       kernel_out);
 }
 
-/* what source/ordered_push.c:63-146 checks, in its order of concerns: scalars, region and tables, the three arrays
- * of a slot behind the signal lines and disjoint, region against table and step block */
+/* what source/ordered_push.c:63-146 checks, in its order of concerns: scalars, region and tables, the arrays of a
+ * slot behind the signal lines and disjoint (the inbox last; `slot_arrays` of input, output, inbox are in the slot),
+ * region against table and step block */
 static result_status push_is_valid(const struct ordered_push_description *description, uint32_t kernel,
-				   uint32_t maximum_elements)
+				   uint32_t maximum_elements, uint32_t slot_arrays)
 {
 	if (description == NULL || kernel == BACKEND_NO_KERNEL || maximum_elements == 0)
 		return STATUS_INVALID_ARGUMENT;
@@ -71,11 +72,11 @@ static result_status push_is_valid(const struct ordered_push_description *descri
 		return STATUS_INVALID_ARGUMENT;
 	const uint64_t offsets[3] = { a->input_offset, a->output_offset, a->inbox_offset };
 	const uint64_t sizes[3] = { value_bytes, value_bytes, a->inbox_rank_stride * a->rank_count };
-	for (uint32_t array = 0; array < 3; array++) {
+	for (uint32_t array = 3u - slot_arrays; array < 3; array++) {
 		if (offsets[array] < signal_bytes || offsets[array] % VALUE_BYTES != 0 ||
 		    !push_fits(offsets[array], sizes[array], a->parity_stride))
 			return STATUS_INVALID_ARGUMENT;
-		for (uint32_t earlier = 0; earlier < array; earlier++)
+		for (uint32_t earlier = 3u - slot_arrays; earlier < array; earlier++)
 			if (push_overlaps(offsets[array], sizes[array], offsets[earlier], sizes[earlier]))
 				return STATUS_INVALID_ARGUMENT;
 	}
@@ -107,7 +108,7 @@ result_status ordered_push_prepare(const struct ordered_push_description *descri
 {
 	if (launch_out == NULL)
 		return STATUS_INVALID_ARGUMENT;
-	const result_status status = push_is_valid(description, kernel, ORDERED_COLLECTIVE_MAXIMUM_ELEMENTS);
+	const result_status status = push_is_valid(description, kernel, ORDERED_COLLECTIVE_MAXIMUM_ELEMENTS, 3);
 	if (status != STATUS_OK)
 		return status;
 	uint32_t groups, blocks;
@@ -136,7 +137,7 @@ result_status tp_exchange_rows_prepare(const struct ordered_push_description *de
 	    layer >= layer_count || row_width == 0 || row_width % 4u != 0 ||
 	    description->arguments.element_count % row_width != 0)
 		return STATUS_INVALID_ARGUMENT;
-	const result_status status = push_is_valid(description, kernel, TP_EXCHANGE_MAXIMUM_ELEMENTS);
+	const result_status status = push_is_valid(description, kernel, TP_EXCHANGE_MAXIMUM_ELEMENTS, 3);
 	if (status != STATUS_OK)
 		return status;
 	const struct tp_exchange_arguments arguments = { description->arguments, layer, layer_count, row_width, 0 };
@@ -219,4 +220,44 @@ result_status tp_exchange_wide_prepare(const struct ordered_push_description *de
 {
 	return tp_exchange_wide_rows_prepare(description, TP_EXCHANGE_REFERENCE_ROW_WIDTH, layer, layer_count, kernels,
 					     form, launches_out);
+}
+
+/* ---- the expert layer's form: row sums pushed to every rank, added in rank order, one rounding to bfloat16 ---- */
+
+result_status ordered_rows_push_prepare(const struct ordered_rows_push_description *description,
+					const struct backend_operations *backend, struct device_card *card,
+					struct kernel_launch *launch_out)
+{
+	if (description == NULL || backend == NULL || backend->kernel_prepare == NULL || card == NULL || launch_out == NULL)
+		return STATUS_INVALID_ARGUMENT;
+	const struct ordered_rows_push_arguments *const rows = &description->arguments;
+	const struct ordered_push_arguments *const a = &rows->push;
+	if (rows->width == 0 || rows->width % 4u != 0 || rows->pairs_per_row == 0 || a->element_count % rows->width != 0 ||
+	    a->payload_format != ORDERED_PUSH_FP32 || a->input_offset != 0 ||
+	    (a->output_offset | a->inbox_offset | a->inbox_rank_stride | rows->pair_output_offset) % 16u != 0)
+		return STATUS_INVALID_ARGUMENT;
+	const struct ordered_push_description push = { *a, description->arena_byte_count };
+	result_status status = push_is_valid(&push, 0, ORDERED_B200_MAXIMUM_ELEMENTS, 1);
+	if (status != STATUS_OK)
+		return status;
+	const uint64_t value_bytes = (uint64_t)a->element_count * VALUE_BYTES;
+	if (value_bytes > UINT64_MAX / rows->pairs_per_row)
+		return STATUS_INVALID_ARGUMENT;
+	const struct checked_range ranges[4] = {
+		{ "result", a->output_offset, (uint64_t)a->element_count * 2u },
+		{ "pair outputs", rows->pair_output_offset, value_bytes * rows->pairs_per_row },
+		{ "region", a->region_offset, a->parity_stride * ORDERED_COLLECTIVE_SLOTS },
+		{ "peer table", a->peer_table_offset & ~(uint64_t)15u,
+		  (uint64_t)a->rank_count * sizeof(struct ordered_collective_peer) + 16u }
+	};
+	if (!prepare_ranges_are_valid("ordered rows push", ranges, 4, description->arena_byte_count))
+		return STATUS_INVALID_ARGUMENT;
+	uint32_t kernel = BACKEND_NO_KERNEL;
+	status = backend->kernel_prepare(card, KERNEL_FILE_ORDERED_B200, KERNEL_ORDERED_ROWS_PUSH, sizeof(*rows), &kernel);
+	if (status != STATUS_OK)
+		return status;
+	uint32_t groups, blocks;
+	push_grid(a->element_count, &groups, &blocks);
+	prepare_launch_fill(launch_out, kernel, groups, blocks, 1, ORDERED_COLLECTIVE_THREADS, 0, rows, sizeof(*rows));
+	return STATUS_OK;
 }

@@ -10,11 +10,13 @@
  *       pulls every rank's rows by 128-bit peer loads, adds them in rank order, rounds once, stores bfloat16
  *       [rows][width] at the arena offset output_offset; the last block to finish publishes DONE. With owner runs
  *       (mode 1) a rank adds only its run of the vectors and stores the result into every rank's memory.
- * Both read the live row count and the sequence from the step block. The read-complete barrier of the FP32
+ *   ordered_rows_push        the two above as ONE launch for decode steps, by stores instead of loads: row sums into
+ *       every rank's inbox, READY, the adds in rank order, one rounding, bfloat16 kept locally (ordered_push_device.cuh).
+ * All read the live row count and the sequence from the step block. The read-complete barrier of the FP32
  * collectives is moved from the end of a step to the next refill of the same slot (two steps later), where it costs
  * nothing; the slot's input must therefore only ever be written by ordered_row_sum_publish.
  */
-#include "ordered_device.cuh"
+#include "ordered_push_device.cuh"
 
 /* true for exactly one block: the last of the grid to arrive. The counter is the owner's own, at `line` + 64. Every
  * block orders its stores at device scope before it counts itself; the block that sees the count complete then
@@ -168,4 +170,27 @@ extern "C" __global__ void __launch_bounds__(ORDERED_COLLECTIVE_THREADS)
 		if (threadIdx.x == 0)
 			signal_store(done_line, sequence);
 	}
+}
+
+extern "C" __global__ void __launch_bounds__(ORDERED_COLLECTIVE_THREADS)
+	ordered_rows_push(struct ordered_rows_push_arguments arguments, unsigned char *arena)
+{
+	const struct step_block step = *reinterpret_cast<const struct step_block *>(arena + arguments.push.step_offset);
+	if (step.sequence == 0 || arguments.width == 0 || arguments.width % 4u != 0 || arguments.pairs_per_row == 0)
+		return;
+	if (step.row_count > arguments.push.element_count / arguments.width) {
+		if (threadIdx.x == 0)
+			atomicOr(&exl3_wait_expired, PUSH_EXPIRED_ROWS);
+		return;
+	}
+	struct push_call call;
+	call.a = arguments.push;
+	call.sequence = step.sequence;
+	call.live = step.row_count * arguments.width;
+	call.row_width = 0;
+	call.pairs = reinterpret_cast<const float4 *>(arena + arguments.pair_output_offset);
+	call.result = reinterpret_cast<uint2 *>(arena + arguments.push.output_offset);
+	call.pairs_per_row = arguments.pairs_per_row;
+	call.row_vectors = arguments.width / 4u;
+	push_run(call, arena);
 }

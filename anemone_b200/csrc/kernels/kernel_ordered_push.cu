@@ -14,5 +14,8 @@ extern "C" __global__ void __launch_bounds__(ORDERED_COLLECTIVE_THREADS)
 	call.sequence = reinterpret_cast<const struct step_block *>(arena + arguments.step_offset)->sequence;
 	call.live = arguments.element_count;
 	call.row_width = 0;
+	call.pairs = nullptr;
+	call.result = nullptr;
+	call.pairs_per_row = call.row_vectors = 0;
 	push_run(call, arena);
 }

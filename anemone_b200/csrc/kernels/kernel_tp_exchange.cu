@@ -29,6 +29,9 @@ __device__ __forceinline__ bool exchange_call(const struct tp_exchange_arguments
 	call->sequence = (step.sequence * arguments.layer_count + arguments.layer) * 2u + (step.sequence & 1u);
 	call->live = step.row_count * arguments.row_width;
 	call->row_width = owner ? arguments.row_width : 0u;
+	call->pairs = nullptr;
+	call->result = nullptr;
+	call->pairs_per_row = call->row_vectors = 0;
 	return true;
 }
 

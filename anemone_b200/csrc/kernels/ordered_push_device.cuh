@@ -34,6 +34,13 @@ struct push_call {
 	uint64_t sequence;
 	uint32_t live; /* elements exchanged by this launch */
 	uint32_t row_width; /* the owner sums: elements of a row; 0: the push */
+	/* the expert layer's form (push_rows): the values are row sums of pair outputs, added here from +0 in ascending
+	 * slot order; the sums over the ranks are rounded once to bfloat16 and kept by every rank at `result`; the DONE
+	 * barrier moves from the end of this use of the slot to the beginning of the next */
+	const float4 *pairs; /* FP32 [rows * pairs_per_row][row_vectors * 4], or NULL */
+	uint2 *result; /* bfloat16 [rows][row_vectors * 4] in this rank's memory, or NULL */
+	uint32_t pairs_per_row;
+	uint32_t row_vectors;
 };
 
 __device__ __forceinline__ unsigned char *push_slot(const struct ordered_push_arguments &a, unsigned char *arena,
@@ -126,10 +133,10 @@ __device__ __forceinline__ void push_signal_all(const struct push_call &call, un
 	}
 }
 
-/* every thread calls; true when word `group` of every source's line of `phase` in this rank's slot holds the
- * sequence */
+/* every thread calls; true when word `group` of every source's line of `phase` in this rank's slot holds `wanted`
+ * (exact: a phase of this use of the slot) or at least `wanted` (the DONE of the slot's previous use) */
 __device__ __forceinline__ bool push_wait_all(const struct push_call &call, unsigned char *arena, uint32_t phase,
-					      uint32_t *verdict)
+					      uint64_t wanted, bool exact, uint32_t *verdict)
 {
 	if (threadIdx.x == 0)
 		*verdict = 1;
@@ -141,9 +148,9 @@ __device__ __forceinline__ bool push_wait_all(const struct push_call &call, unsi
 		const long long begin = clock64();
 		for (;;) {
 			const uint64_t seen = signal_load(word);
-			if (seen == call.sequence)
+			if (exact ? seen == wanted : seen >= wanted)
 				break;
-			if (seen > call.sequence) {
+			if (seen > wanted) {
 				atomicOr(&exl3_wait_expired, PUSH_EXPIRED_SEQUENCE);
 				atomicExch(verdict, 0u);
 				break;
@@ -191,35 +198,70 @@ __device__ static void push_run(const struct push_call &call, unsigned char *are
 	if (!alive && threadIdx.x == 0)
 		atomicOr(&exl3_wait_expired, PUSH_EXPIRED_SEQUENCE);
 	const bool owner = call.row_width != 0;
+	const bool rows_form = call.pairs != nullptr;
 	const bool aligned = ((a.input_offset | a.output_offset | a.inbox_offset | a.inbox_rank_stride) % 16u) == 0;
 	const uint32_t vectors = aligned ? call.live / 4u : 0u;
 	const float *const input = reinterpret_cast<const float *>(mine + a.input_offset);
 	const uint32_t lane = blockIdx.y * blockDim.x + threadIdx.x, lanes = gridDim.y * blockDim.x;
+	if (rows_form && alive) {
+		/* the slot's previous use: every rank must have read its inboxes of it before they are written again */
+		const uint64_t previous = *reinterpret_cast<const volatile uint64_t *>(ready_line + PUSH_WORD_BYTES * blockIdx.x);
+		if (previous != 0)
+			alive = push_wait_all(call, arena, ORDERED_PUSH_DONE, previous, false, &verdict);
+	}
 
-	/* ---- this rank's values into the inboxes, a destination at a time from the next rank on ---- */
-	if (alive) {
+	/* ---- this rank's values into the inboxes, from the next rank on ---- */
+	if (alive && owner) {
 		for (uint32_t step = 1; step <= a.rank_count; step++) {
 			const uint32_t destination = (a.rank + step) % a.rank_count;
 			unsigned char *const inbox = push_slot(a, arena, destination, call.sequence) + a.inbox_offset +
 						     (uint64_t)a.rank * a.inbox_rank_stride;
 			uint32_t begin, end;
-			if (owner)
-				push_part(push_owner_first(call, destination), push_owner_first(call, destination + 1u), begin,
-					  end);
-			else
-				push_part(0, vectors, begin, end);
+			push_part(push_owner_first(call, destination), push_owner_first(call, destination + 1u), begin, end);
 			for (uint32_t vector = begin + lane; vector < end; vector += lanes)
 				push_store4(inbox, a.payload_format, vector,
 					    __ldg(reinterpret_cast<const float4 *>(input) + vector));
-			if (!owner && blockIdx.x == 0) /* what no vector covers: group 0's */
-				for (uint32_t element = vectors * 4u + lane; element < call.live; element += lanes)
-					push_store1(inbox, a.payload_format, element, input[element]);
 		}
+	} else if (alive) {
+		unsigned char *inboxes[ORDERED_COLLECTIVE_MAXIMUM_RANKS];
+#pragma unroll
+		for (uint32_t step = 0; step < ORDERED_COLLECTIVE_MAXIMUM_RANKS; step++)
+			inboxes[step] = step < a.rank_count ?
+						push_slot(a, arena, (a.rank + 1u + step) % a.rank_count, call.sequence) +
+							a.inbox_offset + (uint64_t)a.rank * a.inbox_rank_stride :
+						nullptr;
+		uint32_t begin, end;
+		push_part(0, vectors, begin, end);
+		for (uint32_t vector = begin + lane; vector < end; vector += lanes) {
+			float4 value;
+			if (rows_form) {
+				const uint32_t row = vector / call.row_vectors, column = vector % call.row_vectors;
+				value = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+				for (uint32_t slot = 0; slot < call.pairs_per_row; slot++) {
+					const float4 pair =
+						call.pairs[((uint64_t)row * call.pairs_per_row + slot) * call.row_vectors + column];
+					value.x = __fadd_rn(value.x, pair.x);
+					value.y = __fadd_rn(value.y, pair.y);
+					value.z = __fadd_rn(value.z, pair.z);
+					value.w = __fadd_rn(value.w, pair.w);
+				}
+			} else {
+				value = __ldg(reinterpret_cast<const float4 *>(input) + vector);
+			}
+#pragma unroll
+			for (uint32_t step = 0; step < ORDERED_COLLECTIVE_MAXIMUM_RANKS; step++)
+				if (step < a.rank_count)
+					push_store4(inboxes[step], a.payload_format, vector, value);
+		}
+		if (blockIdx.x == 0 && !rows_form) /* what no vector covers: group 0's */
+			for (uint32_t element = vectors * 4u + lane; element < call.live; element += lanes)
+				for (uint32_t step = 0; step < a.rank_count; step++)
+					push_store1(inboxes[step], a.payload_format, element, input[element]);
 	}
 	/* a group that moved nothing publishes nothing: its peers' waits run out and report, rather than add stale bytes */
 	if (push_group_last(ready_line, &last) && alive)
 		push_signal_all(call, arena, ORDERED_PUSH_READY);
-	alive = alive && push_wait_all(call, arena, ORDERED_PUSH_READY, &verdict);
+	alive = alive && push_wait_all(call, arena, ORDERED_PUSH_READY, call.sequence, true, &verdict);
 
 	/* ---- the adds, ascending ranks from +0 ---- */
 	if (alive) {
@@ -245,18 +287,20 @@ __device__ static void push_run(const struct push_call &call, unsigned char *are
 					sum.z = __fadd_rn(sum.z, values[source].z);
 					sum.w = __fadd_rn(sum.w, values[source].w);
 				}
-			if (!owner) {
+			if (!owner && !rows_form) {
 				reinterpret_cast<float4 *>(mine + a.output_offset)[vector] = sum;
-			} else {
-				const uint2 rounded = make_uint2(bfloat16_bits(sum.x) | bfloat16_bits(sum.y) << 16,
-								 bfloat16_bits(sum.z) | bfloat16_bits(sum.w) << 16);
-				for (uint32_t step = 1; step <= a.rank_count; step++)
-					reinterpret_cast<uint2 *>(push_slot(a, arena, (a.rank + step) % a.rank_count,
-									    call.sequence) +
-								  a.output_offset)[vector] = rounded;
+				continue;
 			}
+			const uint2 rounded = make_uint2(bfloat16_bits(sum.x) | bfloat16_bits(sum.y) << 16,
+							 bfloat16_bits(sum.z) | bfloat16_bits(sum.w) << 16);
+			if (rows_form)
+				call.result[vector] = rounded;
+			else
+				for (uint32_t step = 1; step <= a.rank_count; step++)
+					reinterpret_cast<uint2 *>(push_slot(a, arena, (a.rank + step) % a.rank_count, call.sequence) +
+								  a.output_offset)[vector] = rounded;
 		}
-		if (!owner && blockIdx.x == 0)
+		if (!owner && !rows_form && blockIdx.x == 0)
 			for (uint32_t element = vectors * 4u + lane; element < call.live; element += lanes) {
 				float sum = 0.0f;
 				for (uint32_t source = 0; source < a.rank_count; source++)
@@ -265,11 +309,12 @@ __device__ static void push_run(const struct push_call &call, unsigned char *are
 				reinterpret_cast<float *>(mine + a.output_offset)[element] = sum;
 			}
 	}
-	/* ---- every rank has read its inboxes (and stored its sums) before any returns ---- */
+	/* ---- every rank has read its inboxes (and stored its sums) before any returns; the expert layer's form only
+	 * says so, and looks at the others' word before the slot's next use ---- */
 	if (push_group_last(done_line, &last)) {
 		push_signal_all(call, arena, ORDERED_PUSH_DONE);
-		if (alive)
-			(void)push_wait_all(call, arena, ORDERED_PUSH_DONE, &verdict);
+		if (alive && !rows_form)
+			(void)push_wait_all(call, arena, ORDERED_PUSH_DONE, call.sequence, true, &verdict);
 	}
 }
 

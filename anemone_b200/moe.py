@@ -66,9 +66,10 @@ def local_matrices(gate, up, down, config, width, rank_count, rank):
 class MoeLayout:
     """Byte offsets of everything one rank keeps in its arena. Identical on every rank of a group."""
 
-    def __init__(self, config, widths, rank_count, rank, pool_entries=0):
+    def __init__(self, config, widths, rank_count, rank, pool_entries=0, reduce_form="pull"):
         self.config, self.rank_count, self.rank = config, rank_count, rank
         self.pool_entries = pool_entries
+        self.reduce_form = reduce_form
         self.inner_local = rank_columns(config.inner, rank_count, rank)[1]
         c, H, I = config, config.hidden, self.inner_local
         rows, pairs = c.row_capacity, c.row_capacity * c.pairs_per_row
@@ -88,8 +89,15 @@ class MoeLayout:
         self.cursor = layout.take(16)
         self.pool = layout.take(self.pool_stride * pool_entries) if pool_entries else 0
         # the reduction's region: two parity slots of signal lines and this rank's FP32 partial rows
-        self.slot_input = SIGNAL_BYTES
-        self.parity_stride = api.align(SIGNAL_BYTES + rows * H * 4, LINE)
+        if reduce_form == "pull":  # ordered_row_sum_publish + ordered_reduce_bf16: peers read this rank's rows
+            self.slot_input = SIGNAL_BYTES
+            self.parity_stride = api.align(SIGNAL_BYTES + rows * H * 4, LINE)
+        else:  # ordered_rows_push: one launch; every rank stores its rows into an inbox of every rank's slot
+            assert reduce_form == "push"
+            self.inbox = 2 * rank_count * LINE
+            self.inbox_stride = rows * H * 4
+            self.slot_input = self.inbox + rank * self.inbox_stride  # where this rank's own rows end up
+            self.parity_stride = api.align(self.inbox + rank_count * self.inbox_stride, LINE)
         self.region = layout.take(2 * self.parity_stride, LINE)
         self.picks = layout.take(rows * c.picks * 4)
         self.weights = layout.take(rows * c.picks * 4)
@@ -113,11 +121,14 @@ class MoeLayout:
 
 
 class MoeLayer:
-    def __init__(self, card, config, widths, matrices, rank=0, rank_count=1, pool_entries=0):
-        """matrices: iterable over experts (routed, then shared) of this rank's (gate, up, down) stored bytes."""
+    def __init__(self, card, config, widths, matrices, rank=0, rank_count=1, pool_entries=0, reduce_form="pull"):
+        """matrices: iterable over experts (routed, then shared) of this rank's (gate, up, down) stored bytes.
+        reduce_form: "pull" (two launches, the ranks read each other's rows: the faster of the two over NVLink, where a
+        system-scope fence behind remote stores costs more than a second launch) or "push" (one launch, the ranks
+        store their rows into each other's inboxes); the same sums and bits."""
         self.card, self.config = card, config
         self.widths = np.asarray(widths, dtype=np.uint32)
-        self.layout = L = MoeLayout(config, self.widths, rank_count, rank, pool_entries)
+        self.layout = L = MoeLayout(config, self.widths, rank_count, rank, pool_entries, reduce_form)
         assert card.arena_bytes >= L.arena_bytes
         self.rank, self.rank_count = rank, rank_count
         self.weight_bytes = 0
@@ -175,22 +186,35 @@ class MoeLayer:
         moe_launches = (R.KernelLaunch * 4)()
         api.check(lib.exl3_moe_prepare(C.byref(moe), card.arena_bytes, card.ops_pointer, card.handle, moe_launches),
                   "exl3_moe_prepare")
-        reduce = R.OrderedReduceBf16Description()
-        reduce.reduce.collective = R.OrderedCollective(L.peer_table, L.region, L.slot_input, L.result, 0, L.step,
-                                                       L.parity_stride, c.deadline_cycles,
-                                                       c.row_capacity * c.hidden, self.rank_count, self.rank, 0)
-        reduce.reduce.status_offset, reduce.reduce.width = L.status, c.hidden
-        reduce.pair_output_offset, reduce.arena_byte_count = L.products, card.arena_bytes
-        reduce.pairs_per_row, reduce.row_capacity = c.pairs_per_row, c.row_capacity
-        lib.ordered_reduce_bf16_prepare.argtypes = [C.POINTER(R.OrderedReduceBf16Description),
-                                                    C.POINTER(api.BackendOperations), C.c_void_p,
-                                                    C.POINTER(R.KernelLaunch)]
-        reduce_launches = (R.KernelLaunch * 2)()
-        api.check(lib.ordered_reduce_bf16_prepare(C.byref(reduce), card.ops_pointer, card.handle, reduce_launches),
-                  "ordered_reduce_bf16_prepare")
+        if L.reduce_form == "pull":
+            reduce = R.OrderedReduceBf16Description()
+            reduce.reduce.collective = R.OrderedCollective(L.peer_table, L.region, L.slot_input, L.result, 0, L.step,
+                                                           L.parity_stride, c.deadline_cycles,
+                                                           c.row_capacity * c.hidden, self.rank_count, self.rank, 0)
+            reduce.reduce.status_offset, reduce.reduce.width = L.status, c.hidden
+            reduce.pair_output_offset, reduce.arena_byte_count = L.products, card.arena_bytes
+            reduce.pairs_per_row, reduce.row_capacity = c.pairs_per_row, c.row_capacity
+            lib.ordered_reduce_bf16_prepare.argtypes = [C.POINTER(R.OrderedReduceBf16Description),
+                                                        C.POINTER(api.BackendOperations), C.c_void_p,
+                                                        C.POINTER(R.KernelLaunch)]
+            reduce_launches = (R.KernelLaunch * 2)()
+            api.check(lib.ordered_reduce_bf16_prepare(C.byref(reduce), card.ops_pointer, card.handle, reduce_launches),
+                      "ordered_reduce_bf16_prepare")
+        else:
+            push = R.OrderedRowsPushDescription()
+            push.arguments.push = R.OrderedPush(L.peer_table, L.region, 0, L.result, L.inbox, L.step, L.parity_stride,
+                                                c.deadline_cycles, L.inbox_stride, c.row_capacity * c.hidden,
+                                                self.rank_count, self.rank, R.ORDERED_PUSH_FP32, 0, 0)
+            push.arguments.pair_output_offset, push.arguments.width = L.products, c.hidden
+            push.arguments.pairs_per_row, push.arena_byte_count = c.pairs_per_row, card.arena_bytes
+            lib.ordered_rows_push_prepare.argtypes = [C.POINTER(R.OrderedRowsPushDescription),
+                                                      C.POINTER(api.BackendOperations), C.c_void_p,
+                                                      C.POINTER(R.KernelLaunch)]
+            reduce_launches = (R.KernelLaunch * 1)()
+            api.check(lib.ordered_rows_push_prepare(C.byref(push), card.ops_pointer, card.handle, reduce_launches),
+                      "ordered_rows_push_prepare")
         # the fused chain's own row sum is replaced by the reduction's, which sums straight into the exchange slot
-        self.launches = [router_launch, moe_launches[0], moe_launches[1], moe_launches[2], reduce_launches[0],
-                         reduce_launches[1]]
+        self.launches = [router_launch, moe_launches[0], moe_launches[1], moe_launches[2]] + list(reduce_launches)
         self.graph = card.graph(self.launches)
         self.resident_graph = None
         if L.pool_entries:
@@ -253,6 +277,12 @@ class MoeLayer:
         return card.staging_view[result_at:result_at + nbytes].view(np.uint16).reshape(rows, self.config.hidden).copy()
 
     def check_status(self):
+        if self.layout.reduce_form == "push":
+            bits = self.card.expired_bits()
+            if bits != 0:
+                raise RuntimeError("ordered reduction failed: bits %d (1 a wait ran out, 2 bad sequence, 4 too many "
+                                   "rows)" % bits)
+            return
         status = self.card.download(self.layout.status, 16, np.uint32)
         if status[0] != 0:
             raise RuntimeError("ordered reduction failed: code %d (1 timed out, 2 bad sequence), phase %d, rank %d"

@@ -126,6 +126,15 @@ class TpExchange(C.Structure):
                 ("row_width", C.c_uint32), ("reserved_zero", C.c_uint32)]
 
 
+class OrderedRowsPush(C.Structure):
+    _fields_ = [("push", OrderedPush), ("pair_output_offset", C.c_uint64), ("width", C.c_uint32),
+                ("pairs_per_row", C.c_uint32)]
+
+
+class OrderedRowsPushDescription(C.Structure):
+    _fields_ = [("arguments", OrderedRowsPush), ("arena_byte_count", C.c_uint64)]
+
+
 class OrderedPushDescription(C.Structure):
     _fields_ = [("arguments", OrderedPush), ("arena_byte_count", C.c_uint64)]
 
@@ -250,7 +259,7 @@ class OrderedCollectiveKernels(C.Structure):
 for _record, _bytes in ((Exl3Reconstruct, 32), (Exl3Expert, 80), (ExpertJob, 96), (ExpertRowSum, 24),
                         (Exl3ShardActivation, 96), (Exl3Moe, 112), (TrunkLinearQuantized, 72), (TrunkHidden, 32), (TrunkRowsAdd, 24), (Exl3Prefill, 136), (Exl3PrefillTile, 16), (Exl3PrefillEntry, 8), (Exl3PrefillParts, 56), (StepBlock, 16), (OrderedPeer, 32),
                         (OrderedCollective, 80), (OrderedReduceBf16, 96), (OrderedRowSumPublish, 96), (OrderedPush, 96),
-                        (TpExchange, 112),
+                        (TpExchange, 112), (OrderedRowsPush, 112),
                         (RouterSelectB200, 80), (StepInputSelect, 40), (ActivationQuantize, 40), (ExpertGateUp, 64), (ExpertDown, 56),
                         (KernelLaunch, 232), (CardDescription, 168)):
     assert C.sizeof(_record) == _bytes, (_record.__name__, C.sizeof(_record), _bytes)

@@ -60,6 +60,8 @@ def parse():
     parser.add_argument("--prefill-rows", type=int, default=4096, help="0 skips the prefill part")
     parser.add_argument("--prefill-steps", type=int, default=5)
     parser.add_argument("--no-original-weights", action="store_true", help="skip the MXFP4 part")
+    parser.add_argument("--no-reduction", action="store_true",
+                        help="skip the reduction-alone measurement of runs on two or more GPUs")
     parser.add_argument("--no-reference-kernels", action="store_true",
                         help="skip the reference's own kernels on this card (N = 1 only)")
     return parser.parse_args()
@@ -512,6 +514,169 @@ def run_original_weights(args, api, base, rank, world, local_rank, dist, barrier
                        "note": "value includes the 74 KB host->device copy of each step's inputs"}}
 
 
+def run_reduction(args, api, hidden, rank, world, local_rank, dist, barrier, maximum):
+    """cfg2: the fixed-order reduction ALONE between the ranks: FP32 [M][hidden] a rank, added in rank order, rounded
+    once to bfloat16, M in {1, 8, 64}. Four forms of this library: every rank stores its rows into every rank's inbox and adds
+    its inboxes (one launch: what a decode step uses), every rank pulls every rank's rows, owner runs (every rank adds its run and stores it into every rank), and the exchange's owner sums
+    (every rank stores each owner's rows into the owner's inbox: the reference's tp_exchange entry points). Times are
+    device times of a captured graph a call, the 16-byte step block copied in before each, max over ranks."""
+    import ctypes as C
+    from anemone_b200 import records as R
+    lib = api.library()
+    most = 64
+    elements = most * hidden
+    layout = api.Layout()
+    peer_table, step, status = layout.take(16 * 32), layout.take(16), layout.take(16)
+    pull_stride = api.align(384 + 4 * elements, 128)
+    pull_region = layout.take(2 * pull_stride, 128)
+    result, rows_at = layout.take(2 * elements), layout.take(4 * elements)
+    signals = 2 * world * 128
+    push_input, push_output, push_inbox = signals, signals + 4 * elements, signals + 8 * elements
+    push_stride = api.align(push_inbox + world * 4 * elements, 128)
+    push_region = layout.take(2 * push_stride, 128)
+    # every call's step block waits in a pool on the card; a select launch in front of each call takes the next
+    # the order the timings run in; the exchange last: its sequences (twice a step's and more) leave no room above
+    forms = ("pull_every_rank", "pull_owner_runs", "push_every_rank", "exchange_owner_sums")
+    row_counts, repeats, warm_graphs, timed_graphs = (1, 8, 64), 10, 1, 4
+    pool_entries = len(forms) * len(row_counts) * repeats * (warm_graphs + timed_graphs)
+    pool, cursor = layout.take(64 * pool_entries, 64), layout.take(16)
+    arena_bytes = layout.take(4096, 4096)
+    card = api.Card(local_rank, arena_bytes)
+    card.fill(0, 0, arena_bytes)
+    blocks = np.zeros(64 * pool_entries, dtype=np.uint8)
+    entry = 0
+    for form in forms:  # the order the timings below run in; sequences strictly increasing
+        for rows in row_counts:
+            for _ in range(repeats * (warm_graphs + timed_graphs)):
+                blocks[64 * entry:64 * entry + 16] = np.frombuffer(bytes(R.StepBlock(entry + 1, rows, 0)), dtype=np.uint8)
+                entry += 1
+    card.upload(pool, blocks)
+    select = R.StepInputSelect(pool, 64, step, cursor, pool_entries, 16)
+    lib.step_input_select_prepare.argtypes = [C.POINTER(R.StepInputSelect), C.c_uint64,
+                                              C.POINTER(api.BackendOperations), C.c_void_p, C.POINTER(R.KernelLaunch)]
+    select_launch = R.KernelLaunch()
+    api.check(lib.step_input_select_prepare(C.byref(select), arena_bytes, card.ops_pointer, card.handle,
+                                            C.byref(select_launch)), "step_input_select_prepare")
+    rng = np.random.default_rng([SEED, 4000, rank])
+    values = rng.normal(0, 0.05, elements).astype(np.float32)
+    card.upload(rows_at, values)
+    for parity in range(2):
+        card.upload(push_region + parity * push_stride + push_input, values)
+    lib.ordered_reduce_bf16_prepare.argtypes = [C.POINTER(R.OrderedReduceBf16Description),
+                                                C.POINTER(api.BackendOperations), C.c_void_p,
+                                                C.POINTER(R.KernelLaunch)]
+    lib.tp_exchange_wide_kernels_prepare.argtypes = [C.POINTER(api.BackendOperations), C.c_void_p, C.c_uint32,
+                                                     C.POINTER(C.c_uint32)]
+    lib.tp_exchange_wide_rows_prepare.argtypes = [C.POINTER(R.OrderedPushDescription), C.c_uint32, C.c_uint32,
+                                                  C.c_uint32, C.POINTER(C.c_uint32), C.c_uint32,
+                                                  C.POINTER(R.KernelLaunch)]
+    graphs = {}
+
+    def connect(region_of):
+        peers = (R.OrderedPeer * world)()
+        for peer in range(world):
+            peers[peer].region_offset = region_of
+        card.upload(peer_table, np.frombuffer(bytes(peers), dtype=np.uint8))
+        if dist is None:
+            card.peer_connect(card, 0, peer_table)
+        else:
+            handles = [None] * world
+            dist.all_gather_object(handles, card.ipc_export())
+            for peer, handle in enumerate(handles):
+                if peer == rank:
+                    card.peer_connect(card, 0, peer_table + 32 * peer)
+                else:
+                    card.ipc_connect(handle, 0, peer_table + 32 * peer)
+    # the peer table names a rank's region: written for the pull forms first, rewritten for the exchange below
+    connect(pull_region)
+    for mode, name in ((R.ORDERED_REDUCE_EVERY_RANK, "pull_every_rank"), (R.ORDERED_REDUCE_OWNER_RUNS, "pull_owner_runs")):
+        for rows in (1, 8, 64):
+            reduce = R.OrderedReduceBf16Description()
+            reduce.reduce.collective = R.OrderedCollective(peer_table, pull_region, 384, result, 0, step, pull_stride,
+                                                           2_000_000_000, rows * hidden, world, rank, 0)
+            reduce.reduce.status_offset, reduce.reduce.width, reduce.reduce.mode = status, hidden, mode
+            reduce.pair_output_offset, reduce.arena_byte_count = rows_at, arena_bytes
+            reduce.pairs_per_row, reduce.row_capacity = 1, rows
+            launches = (R.KernelLaunch * 2)()
+            api.check(lib.ordered_reduce_bf16_prepare(C.byref(reduce), card.ops_pointer, card.handle, launches),
+                      "ordered_reduce_bf16_prepare")
+            graphs[(name, rows)] = (card.graph(([select_launch] + list(launches)) * repeats), 2)
+    results = {}
+
+    def timed(name, rows):
+        graph, launches = graphs[(name, rows)]
+        barrier()
+        for _ in range(warm_graphs):
+            card.graph_run(graph)
+        card.wait()
+        barrier()
+        card.measure_begin()
+        for _ in range(timed_graphs):
+            card.graph_run(graph)
+        card.measure_end()
+        card.wait()
+        return maximum(card.measure_elapsed_us() / (timed_graphs * repeats)), launches
+    for name in ("pull_every_rank", "pull_owner_runs"):
+        for rows in (1, 8, 64):
+            results[(name, rows)] = timed(name, rows)
+    if card.download(status, 16, np.uint32)[0] != 0:
+        raise RuntimeError("ordered reduction failed in the reduction bench")
+    barrier()
+    connect(push_region)
+    lib.ordered_rows_push_prepare.argtypes = [C.POINTER(R.OrderedRowsPushDescription), C.POINTER(api.BackendOperations),
+                                              C.c_void_p, C.POINTER(R.KernelLaunch)]
+    for rows in (1, 8, 64):
+        push = R.OrderedRowsPushDescription()
+        push.arguments.push = R.OrderedPush(peer_table, push_region, 0, result, push_inbox, step, push_stride,
+                                            2_000_000_000, 4 * elements, rows * hidden, world, rank,
+                                            R.ORDERED_PUSH_FP32, 0, 0)
+        push.arguments.pair_output_offset, push.arguments.width, push.arguments.pairs_per_row = rows_at, hidden, 1
+        push.arena_byte_count = arena_bytes
+        one = (R.KernelLaunch * 1)()
+        api.check(lib.ordered_rows_push_prepare(C.byref(push), card.ops_pointer, card.handle, one),
+                  "ordered_rows_push_prepare")
+        graphs[("push_every_rank", rows)] = (card.graph(([select_launch] + list(one)) * repeats), 1)
+    for rows in (1, 8, 64):
+        results[("push_every_rank", rows)] = timed("push_every_rank", rows)
+    kernels = (C.c_uint32 * 4)()
+    api.check(lib.tp_exchange_wide_kernels_prepare(card.ops_pointer, card.handle, R.TP_EXCHANGE_FORM_OWNER_SUMS, kernels),
+              "tp_exchange_wide_kernels_prepare")
+    for rows in (1, 8, 64):
+        arguments = R.OrderedPush(peer_table, push_region, push_input, push_output, push_inbox, step, push_stride,
+                                  2_000_000_000, 4 * elements, rows * hidden, world, rank, R.ORDERED_PUSH_FP32, 0, 0)
+        description = R.OrderedPushDescription(arguments, arena_bytes)
+        launches = (R.KernelLaunch * 4)()
+        api.check(lib.tp_exchange_wide_rows_prepare(C.byref(description), hidden, 0, 1, kernels,
+                                                    R.TP_EXCHANGE_FORM_OWNER_SUMS, launches),
+                  "tp_exchange_wide_rows_prepare")
+        graphs[("exchange_owner_sums", rows)] = (card.graph(([select_launch] + list(launches)) * repeats), 4)
+    for rows in (1, 8, 64):
+        results[("exchange_owner_sums", rows)] = timed("exchange_owner_sums", rows)
+    expired = card.expired_bits()
+    barrier()
+    card.close()
+    if expired:
+        raise RuntimeError("an exchange kernel gave up (bits %d) in the reduction bench" % expired)
+    share = (world - 1) / world
+    remote = {"pull_every_rank": lambda rows: (world - 1) * rows * hidden * 4,
+              "pull_owner_runs": lambda rows: share * rows * hidden * (4 + 2),
+              "exchange_owner_sums": lambda rows: share * rows * hidden * (4 + 2),
+              "push_every_rank": lambda rows: (world - 1) * rows * hidden * 4}
+    out = []
+    for (name, rows), (us, launches) in sorted(results.items()):
+        moved = remote[name](rows)
+        out.append({"form": name, "rows": rows, "us_per_call": us, "launches_per_call": launches,
+                    "remote_bytes_per_rank": int(moved), "nvlink_gbs": moved / us / 1000.0,
+                    "frac_of_770_measured": moved / us / 1000.0 / 770.0,
+                    "frac_of_900_nominal": moved / us / 1000.0 / 900.0})
+    return {"config": {"workload": "cfg2 ordered reduction alone: FP32 [M][%d] a rank, N(0, 0.05^2), rank order, one "
+                                   "rounding to bfloat16, M in {1, 8, 64}, %d ranks" % (hidden, world)},
+            "note": "a call is a select launch (the next step block from a pool on the card) and the form's "
+                    "launches; ten calls a captured graph, four graphs timed back to back; the exchange's rows "
+                    "wait in its slot, the pull forms first add one 'pair' a row into theirs (their publish launch)",
+            "calls": out}
+
+
 def main():
     args = parse()
     from anemone_b200.moe import MoeConfig
@@ -670,7 +835,12 @@ def main():
     original = None
     if not args.no_original_weights:
         original = run_original_weights(args, api, config, rank, world, local_rank, dist, barrier, maximum)
+    reduction = None
+    if world > 1 and not args.no_reduction:
+        reduction = run_reduction(args, api, config.hidden, rank, world, local_rank, dist, barrier, maximum)
     if rank == 0:
+        if reduction is not None:
+            line["reduction"] = reduction
         if prefill is not None:
             line["prefill"] = prefill
         if original is not None:

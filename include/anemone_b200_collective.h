@@ -144,6 +144,22 @@ MUST_CHECK result_status tp_exchange_wide_rows_prepare(const struct ordered_push
 						       const uint32_t kernels[TP_EXCHANGE_WIDE_LAUNCHES], uint32_t form,
 						       struct kernel_launch launches_out[TP_EXCHANGE_WIDE_LAUNCHES]);
 
+/* ---- B200 extension: the expert layer's reduction of a decode step as one launch ---- */
+
+struct ordered_rows_push_description {
+	struct ordered_rows_push_arguments arguments;
+	uint64_t arena_byte_count;
+};
+
+/* No reference counterpart as one call: the push's stores and waits (source/kernel_ordered_push.cuh) around the owner
+ * sums' arithmetic (source/kernel_tp_exchange.cu:190-247). One launch of ("kernel_ordered_b200", "ordered_rows_push").
+ * Validates the push record (its inbox the only array inside the slot), width a multiple of 4, element_count a whole
+ * number of rows, the FP32 wire, 16-byte offsets, the result and pair output ranges. Fewer bytes cross NVLink with
+ * ordered_reduce_bf16's owner runs once a step has many rows; this form is the one for decode steps. */
+MUST_CHECK result_status ordered_rows_push_prepare(const struct ordered_rows_push_description *description,
+						   const struct backend_operations *backend, struct device_card *card,
+						   struct kernel_launch *launch_out);
+
 #ifdef __cplusplus
 }
 #endif

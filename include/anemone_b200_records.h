@@ -362,6 +362,20 @@ struct ordered_push_arguments {
 	uint32_t reserved_zero;
 };
 
+/* B200 extension, kernel file "kernel_ordered_b200", entry "ordered_rows_push": the expert layer's reduction for a
+ * decode step as ONE launch. Every rank adds its pair outputs to row sums (from +0, ascending slot), stores the FP32
+ * rows of the step (step.row_count of them) into its inbox in every rank's slot, then adds its inboxes in rank order
+ * from +0, rounds ONCE to bfloat16 (nearest even, a not-a-number to 0x7FC0) and keeps bfloat16 [rows][width] at the
+ * ARENA offset push.output_offset. push.input_offset is unused (0); the wire is FP32. The DONE lines are published at
+ * the end and looked at before the slot's next use, so no rank waits for another after its own adds. */
+#define KERNEL_ORDERED_ROWS_PUSH "ordered_rows_push"
+struct ordered_rows_push_arguments {
+	struct ordered_push_arguments push;
+	uint64_t pair_output_offset; /* FP32 [rows * pairs_per_row][width] */
+	uint32_t width;
+	uint32_t pairs_per_row;
+};
+
 /* The exchange of a tensor-parallel layer site: the push with the live rows of the step block and a sequence of its
  * own for every layer, 2 * (step sequence * layer_count + layer) + (step sequence & 1), so that the layers of a step
  * share one region and the step's parity still selects the slot. element_count is a whole number of rows of
@@ -695,8 +709,9 @@ AB_RECORD_HAS(ordered_collective_peer, 32);
 AB_RECORD_HAS(ordered_collective_arguments, 80);
 AB_RECORD_HAS(ordered_reduce_bf16_arguments, 96);
 AB_RECORD_HAS(ordered_row_sum_publish_arguments, 96);
-AB_RECORD_HAS(ordered_push_arguments, ORDERED_PUSH_ARGUMENT_BYTES);
-AB_RECORD_HAS(tp_exchange_arguments, TP_EXCHANGE_ARGUMENT_BYTES);
+AB_RECORD_HAS(ordered_push_arguments, 96);
+AB_RECORD_HAS(tp_exchange_arguments, 112);
+AB_RECORD_HAS(ordered_rows_push_arguments, 112);
 AB_RECORD_HAS(router_select_b200_arguments, 80);
 AB_RECORD_HAS(step_input_select_arguments, 40);
 AB_RECORD_HAS(exl3_prefill_tile, 16);

@@ -38,15 +38,16 @@ def cosine(a, b):
     return float(a @ b / (np.linalg.norm(a) * np.linalg.norm(b) + 1e-300))
 
 
+@pytest.mark.parametrize("form", ["push", "pull"])
 @pytest.mark.parametrize("rows", [1, 4, 8, 32])
-def test_layer_single_rank(api, oracle, rows):
+def test_layer_single_rank(api, oracle, rows, form):
     config = MoeConfig(hidden=512, inner=256, experts=32, shared=1, picks=4, row_capacity=rows)
     widths, matrices, tokens, scores = make_layer_inputs(10 + rows, config, rows)
     expected, _, experts, weights = moe_reference.layer(oracle, config, widths, matrices, tokens, scores, 1)
-    layout = MoeLayout(config, widths, 1, 0)
+    layout = MoeLayout(config, widths, 1, 0, reduce_form=form)
     card = api.Card(0, layout.arena_bytes)
     try:
-        layer = MoeLayer(card, config, widths, matrices)
+        layer = MoeLayer(card, config, widths, matrices, reduce_form=form)
         layer.connect_local([layer])
         for repeat in range(3):  # both parity slots and a reuse
             got = layer.step(tokens, scores)

@@ -27,7 +27,8 @@ def world_sizes(api):
     return [size for size in (2, 4, 8) if size <= api.card_count()]
 
 
-def test_layer_tensor_parallel(api, oracle):
+@pytest.mark.parametrize("form", ["push", "pull"])
+def test_layer_tensor_parallel(api, oracle, form):
     for ranks in world_sizes(api):
         config = MoeConfig(hidden=512, inner=128 * ranks * 2, experts=24, shared=1, picks=4, row_capacity=8)
         rng = np.random.default_rng(300 + ranks)
@@ -38,11 +39,11 @@ def test_layer_tensor_parallel(api, oracle):
         cards, layers = [], []
         try:
             for rank in range(ranks):
-                card = api.Card(rank, MoeLayout(config, widths, ranks, rank).arena_bytes)
+                card = api.Card(rank, MoeLayout(config, widths, ranks, rank, reduce_form=form).arena_bytes)
                 cards.append(card)
                 local = [local_matrices(*matrices[e], config, int(widths[e]), ranks, rank)
                          for e in range(config.total_experts)]
-                layers.append(MoeLayer(card, config, widths, local, rank=rank, rank_count=ranks))
+                layers.append(MoeLayer(card, config, widths, local, rank=rank, rank_count=ranks, reduce_form=form))
             for layer in layers:
                 layer.connect_local(layers)
             for card in cards:

@@ -178,7 +178,7 @@ def test_router_and_reduce_prepare():
     lib, fake = api.library(), FakeBackend()
     from anemone_b200.moe import MoeConfig, MoeLayout
     config = MoeConfig(hidden=512, inner=256, experts=32, shared=1, picks=4, row_capacity=8)
-    L = MoeLayout(config, np.full(33, 3, dtype=np.uint32), 2, 1)
+    L = MoeLayout(config, np.full(33, 3, dtype=np.uint32), 2, 1, reduce_form="pull")
     lib.router_select_b200_prepare.argtypes = [C.POINTER(R.RouterSelectB200), C.c_uint64,
                                                C.POINTER(api.BackendOperations), C.c_void_p, C.POINTER(R.KernelLaunch)]
     lib.router_b200_job_capacity.restype = C.c_uint32
@@ -217,6 +217,31 @@ def test_router_and_reduce_prepare():
     description.reduce.width = 510
     assert lib.ordered_reduce_bf16_prepare(C.byref(description), C.byref(fake.table), fake.card, launches) == 1
     assert bytes(launches) == untouched
+    # the same reduction as one launch, by stores
+    L = MoeLayout(config, np.full(33, 3, dtype=np.uint32), 2, 1, reduce_form="push")
+    lib.ordered_rows_push_prepare.argtypes = [C.POINTER(R.OrderedRowsPushDescription), C.POINTER(api.BackendOperations),
+                                              C.c_void_p, C.POINTER(R.KernelLaunch)]
+    push = R.OrderedRowsPushDescription()
+    push.arguments.push = R.OrderedPush(L.peer_table, L.region, 0, L.result, L.inbox, L.step, L.parity_stride, 1000,
+                                        L.inbox_stride, 8 * 512, 2, 1, 0, 0, 0)
+    push.arguments.pair_output_offset, push.arguments.width, push.arguments.pairs_per_row = L.products, 512, 5
+    push.arena_byte_count = L.arena_bytes
+    one = (R.KernelLaunch * 1)()
+    assert lib.ordered_rows_push_prepare(C.byref(push), C.byref(fake.table), fake.card, one) == 0
+    assert tuple(one[0].grid) == (2, 1, 1) and one[0].block[0] == 256 and one[0].argument_byte_count == 112
+    assert fake.asked[-1] == ("kernel_ordered_b200", "ordered_rows_push", 112)
+    untouched = bytes(one)
+    for path, value in (("rank", 2), ("payload_format", 1), ("input_offset", 16), ("inbox_offset", 256),
+                        ("inbox_rank_stride", 8 * 512 * 4 - 16), ("output_offset", L.region),
+                        ("incoming_host_mask", 1), ("deadline_cycles", 0)):
+        broken = R.OrderedRowsPushDescription.from_buffer_copy(bytes(push))
+        setattr(broken.arguments.push, path, value)
+        assert lib.ordered_rows_push_prepare(C.byref(broken), C.byref(fake.table), fake.card, one) != 0, path
+    for path, value in (("width", 510), ("pairs_per_row", 0), ("pair_output_offset", L.result)):
+        broken = R.OrderedRowsPushDescription.from_buffer_copy(bytes(push))
+        setattr(broken.arguments, path, value)
+        assert lib.ordered_rows_push_prepare(C.byref(broken), C.byref(fake.table), fake.card, one) == 1, path
+    assert bytes(one) == untouched
 
 
 # ---- byte for byte against the reference's own preparers (oracle/_ref) ----
