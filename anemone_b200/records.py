@@ -126,6 +126,26 @@ class TpExchange(C.Structure):
                 ("row_width", C.c_uint32), ("reserved_zero", C.c_uint32)]
 
 
+class Tp2Join(C.Structure):
+    _fields_ = [("source_offset", C.c_uint64), ("routed_sums_offset", C.c_uint64), ("output_offset", C.c_uint64),
+                ("step_offset", C.c_uint64), ("source_slot_stride", C.c_uint64), ("output_slot_stride", C.c_uint64),
+                ("width", C.c_uint32), ("row_count", C.c_uint32), ("source_row_stride", C.c_uint32),
+                ("routed_row_stride", C.c_uint32), ("output_row_stride", C.c_uint32), ("operation", C.c_uint32),
+                ("has_routed_sums", C.c_uint32), ("reserved_zero", C.c_uint32)]
+
+
+class Tp2JoinRange(C.Structure):
+    _fields_ = [("byte_offset", C.c_uint64), ("byte_count", C.c_uint64)]
+
+
+class Tp2JoinDescription(C.Structure):
+    _fields_ = [("source", Tp2JoinRange), ("routed_sums", Tp2JoinRange), ("output", Tp2JoinRange),
+                ("step", Tp2JoinRange), ("source_slot_stride", C.c_uint64), ("output_slot_stride", C.c_uint64),
+                ("width", C.c_uint32), ("row_count", C.c_uint32), ("source_row_stride", C.c_uint32),
+                ("routed_row_stride", C.c_uint32), ("output_row_stride", C.c_uint32), ("operation", C.c_uint32),
+                ("reserved_zero", C.c_uint32)]
+
+
 class OrderedRowsPush(C.Structure):
     _fields_ = [("push", OrderedPush), ("pair_output_offset", C.c_uint64), ("width", C.c_uint32),
                 ("pairs_per_row", C.c_uint32)]
@@ -259,7 +279,7 @@ class OrderedCollectiveKernels(C.Structure):
 for _record, _bytes in ((Exl3Reconstruct, 32), (Exl3Expert, 80), (ExpertJob, 96), (ExpertRowSum, 24),
                         (Exl3ShardActivation, 96), (Exl3Moe, 112), (TrunkLinearQuantized, 72), (TrunkHidden, 32), (TrunkRowsAdd, 24), (Exl3Prefill, 136), (Exl3PrefillTile, 16), (Exl3PrefillEntry, 8), (Exl3PrefillParts, 56), (StepBlock, 16), (OrderedPeer, 32),
                         (OrderedCollective, 80), (OrderedReduceBf16, 96), (OrderedRowSumPublish, 96), (OrderedPush, 96),
-                        (TpExchange, 112), (OrderedRowsPush, 112),
+                        (TpExchange, 112), (OrderedRowsPush, 112), (Tp2Join, 80),
                         (RouterSelectB200, 80), (StepInputSelect, 40), (ActivationQuantize, 40), (ExpertGateUp, 64), (ExpertDown, 56),
                         (KernelLaunch, 232), (CardDescription, 168)):
     assert C.sizeof(_record) == _bytes, (_record.__name__, C.sizeof(_record), _bytes)

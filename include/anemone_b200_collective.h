@@ -144,6 +144,41 @@ MUST_CHECK result_status tp_exchange_wide_rows_prepare(const struct ordered_push
 						       const uint32_t kernels[TP_EXCHANGE_WIDE_LAUNCHES], uint32_t form,
 						       struct kernel_launch launches_out[TP_EXCHANGE_WIDE_LAUNCHES]);
 
+/* ---- local completion around the exchange (include/anemone/tp2_join.h:36-59) ---- */
+
+struct tp2_join_range { /* the reference's struct linear_range */
+	uint64_t byte_offset;
+	uint64_t byte_count;
+};
+
+struct tp2_join_description {
+	struct tp2_join_range source;
+	struct tp2_join_range routed_sums; /* {0, 0}: none; else FP32 rows added first (operations 0, 4, 5 only) */
+	struct tp2_join_range output;
+	struct tp2_join_range step; /* {0, 0} unless a slot stride is given */
+	uint64_t source_slot_stride;
+	uint64_t output_slot_stride;
+	uint32_t width;
+	uint32_t row_count;
+	uint32_t source_row_stride;
+	uint32_t routed_row_stride;
+	uint32_t output_row_stride;
+	uint32_t operation;
+	uint32_t reserved_zero;
+};
+
+/* include/anemone/tp2_join.h:52-54: the handle of ("kernel_tp2_join", "tp2_join"). *kernel_out only on STATUS_OK. */
+MUST_CHECK result_status tp2_join_kernel_prepare(const struct backend_operations *backend, struct device_card *card,
+						 uint32_t *kernel_out);
+
+/* include/anemone/tp2_join.h:55-58 (source/tp2_join.c:47-205): 1 to 1024 rows of 1 to 32768 elements, every row
+ * stride at least the width; ranges on 16-byte multiples, inside the arena, large enough for the last strided row in
+ * both parity slots; used spans, both parities and the step block disjoint (so no conversion in place); a routed array
+ * only where the operation adds one; a static operation with step exactly {0, 0}; the ring orders with a width that
+ * is a multiple of 4 and dense ring rows. A refusal leaves the launch untouched. */
+MUST_CHECK result_status tp2_join_prepare(const struct tp2_join_description *description, uint64_t arena_byte_count,
+					  uint32_t kernel, struct kernel_launch *launch_out);
+
 /* ---- B200 extension: the expert layer's reduction of a decode step as one launch ---- */
 
 struct ordered_rows_push_description {

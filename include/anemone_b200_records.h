@@ -409,6 +409,51 @@ struct tp_exchange_arguments {
 };
 
 /* ------------------------------------------------------------------------------------------------------------
+ * Local completion around the exchange (reference: include/anemone/tp2_join_records.h:11-48): element-wise conversions,
+ * the join of the always-on expert's bfloat16 rows with the routed FP32 sums, strided copies. Row strides count
+ * elements, slot strides bytes; with a slot stride, source or output advance by (step.sequence & 1) strides.
+ *   0 BFLOAT16_TO_FLOAT32        out f32 = [routed f32 +] value(bf16)          (one rounded FP32 add, routed first)
+ *   1 FLOAT32_TO_BFLOAT16        out bf16 = round(f32): nearest even, a not-a-number to 0x7FC0
+ *   2 BFLOAT16_COPY, 3 FLOAT32_COPY   raw words (negative zeros and not-a-number payloads kept)
+ *   4 BFLOAT16_SUM_TO_BFLOAT16   out bf16 = round([routed f32 +] value(bf16)): 0 then 1 without the FP32 store
+ *   5 RING_PACK, 6 RING_UNPACK   4 into, and bfloat16 rows back out of, the owner-major order of the reference's
+ *                                four-rank ring: owner o holds quarter o of every slab of 8 rows, slab after slab
+ * ---------------------------------------------------------------------------------------------------------- */
+#define KERNEL_FILE_TP2_JOIN "kernel_tp2_join"
+#define KERNEL_TP2_JOIN "tp2_join"
+#define TP2_JOIN_ARGUMENT_BYTES 80u
+#define TP2_JOIN_THREADS 256u
+#define TP2_JOIN_BFLOAT16_TO_FLOAT32 0u
+#define TP2_JOIN_FLOAT32_TO_BFLOAT16 1u
+#define TP2_JOIN_BFLOAT16_COPY 2u
+#define TP2_JOIN_FLOAT32_COPY 3u
+#define TP2_JOIN_BFLOAT16_SUM_TO_BFLOAT16 4u
+#define TP2_JOIN_RING_PACK 5u
+#define TP2_JOIN_RING_UNPACK 6u
+#define TP2_JOIN_RING_OWNERS 4u
+#define TP2_JOIN_RING_SLAB_ROWS 8u
+#define TP2_JOIN_OPERATION_COUNT 7u
+#define TP2_JOIN_MAXIMUM_WIDTH 32768u /* the reference: its model's heads x head dimensions, the same number */
+#define TP2_JOIN_MAXIMUM_ROWS 1024u
+
+struct tp2_join_arguments {
+	uint64_t source_offset;
+	uint64_t routed_sums_offset;
+	uint64_t output_offset;
+	uint64_t step_offset;
+	uint64_t source_slot_stride;
+	uint64_t output_slot_stride;
+	uint32_t width;
+	uint32_t row_count;
+	uint32_t source_row_stride;
+	uint32_t routed_row_stride;
+	uint32_t output_row_stride;
+	uint32_t operation;
+	uint32_t has_routed_sums;
+	uint32_t reserved_zero;
+};
+
+/* ------------------------------------------------------------------------------------------------------------
  * Router (B200 extension of the reference's router_select_entry, include/anemone/router_records.h:7-52): scores
  * FP32 [rows][expert_count] -> for each live row the `picks` experts of largest score (a not-a-number above every
  * number, -0 below +0, the lower expert first among equals), slots in ascending expert order, affinity
@@ -712,6 +757,7 @@ AB_RECORD_HAS(ordered_row_sum_publish_arguments, 96);
 AB_RECORD_HAS(ordered_push_arguments, 96);
 AB_RECORD_HAS(tp_exchange_arguments, 112);
 AB_RECORD_HAS(ordered_rows_push_arguments, 112);
+AB_RECORD_HAS(tp2_join_arguments, 80);
 AB_RECORD_HAS(router_select_b200_arguments, 80);
 AB_RECORD_HAS(step_input_select_arguments, 40);
 AB_RECORD_HAS(exl3_prefill_tile, 16);

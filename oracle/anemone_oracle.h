@@ -74,6 +74,8 @@ void orc_ordered_push(const float *const *inputs, uint32_t rank_count, uint32_t 
 /* The owner sums (source/kernel_tp_exchange.cu:190-247): the push's sum rounded once to bfloat16. */
 void orc_owner_sums(const float *const *inputs, uint32_t rank_count, uint32_t element_count, uint32_t payload_format,
 		    uint16_t *output);
+/* The local completion around the exchange (source/kernel_tp2_join.cu:43-108) on a host copy of the arena. */
+void orc_tp2_join(const struct tp2_join_arguments *record, unsigned char *arena);
 /* The four operations of the reference's host twin, same argument meaning as ordered_collective_host. */
 int orc_ordered_collective(const float *const *inputs, float *const *outputs, uint32_t rank_count,
 			   uint32_t element_count, int operation);

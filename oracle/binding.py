@@ -64,6 +64,8 @@ def load_oracle():
     lib.orc_ordered_push.argtypes = [C.POINTER(f32p), C.c_uint32, C.c_uint32, C.c_uint32, f32p]
     lib.orc_owner_sums.restype = None
     lib.orc_owner_sums.argtypes = [C.POINTER(f32p), C.c_uint32, C.c_uint32, C.c_uint32, u16p]
+    lib.orc_tp2_join.restype = None
+    lib.orc_tp2_join.argtypes = [C.c_void_p, C.c_void_p]
     lib.orc_ordered_collective.restype = C.c_int
     lib.orc_ordered_collective.argtypes = [C.POINTER(f32p), C.POINTER(f32p), C.c_uint32, C.c_uint32, C.c_int]
     lib.orc_router_row.restype = None

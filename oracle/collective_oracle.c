@@ -5,6 +5,7 @@
 #include "anemone_oracle.h"
 
 #include <math.h>
+#include <stdlib.h>
 #include <string.h>
 
 /* source/ordered_collective.c:187-196: sum = +0; for each rank ascending: sum = sum + input[rank][element] */
@@ -65,6 +66,59 @@ void orc_owner_sums(const float *const *inputs, uint32_t rank_count, uint32_t el
 			sum = sum + push_wire_value(inputs[rank][element], payload_format);
 		output[element] = orc_bfloat16_bits(sum);
 	}
+}
+
+/* The local completion, element by element as source/kernel_tp2_join.cu:43-108 states it. The ring orders are built
+ * from their definition (owner o holds quarter o of every slab of 8 rows, counted row by row; slab after slab, owner
+ * after owner), not from the kernel's closed form. */
+void orc_tp2_join(const struct tp2_join_arguments *record, unsigned char *arena)
+{
+	const uint32_t rows = record->row_count, width = record->width, operation = record->operation;
+	const uint64_t parity = record->source_slot_stride != 0 || record->output_slot_stride != 0 ?
+					((const struct step_block *)(arena + record->step_offset))->sequence & 1u :
+					0u;
+	const unsigned char *const source = arena + record->source_offset + parity * record->source_slot_stride;
+	unsigned char *const output = arena + record->output_offset + parity * record->output_slot_stride;
+	uint64_t *place = NULL;
+	if (operation == TP2_JOIN_RING_PACK || operation == TP2_JOIN_RING_UNPACK) {
+		place = malloc((size_t)rows * width * sizeof(*place));
+		uint64_t next = 0;
+		for (uint32_t owner = 0; owner < TP2_JOIN_RING_OWNERS; owner++)
+			for (uint32_t first = 0; first < rows; first += TP2_JOIN_RING_SLAB_ROWS) {
+				const uint32_t slab_rows = rows - first < TP2_JOIN_RING_SLAB_ROWS ? rows - first :
+												    TP2_JOIN_RING_SLAB_ROWS;
+				const uint32_t quarter = slab_rows * width / TP2_JOIN_RING_OWNERS;
+				for (uint32_t index = owner * quarter; index < (owner + 1u) * quarter; index++)
+					place[(uint64_t)(first + index / width) * width + index % width] = next++;
+			}
+	}
+	for (uint32_t row = 0; row < rows; row++)
+		for (uint32_t column = 0; column < width; column++) {
+			const uint64_t from = (uint64_t)row * record->source_row_stride + column;
+			const uint64_t to = (uint64_t)row * record->output_row_stride + column;
+			if (operation == TP2_JOIN_BFLOAT16_COPY) {
+				((uint16_t *)output)[to] = ((const uint16_t *)source)[from];
+			} else if (operation == TP2_JOIN_FLOAT32_COPY) {
+				((uint32_t *)output)[to] = ((const uint32_t *)source)[from];
+			} else if (operation == TP2_JOIN_RING_UNPACK) {
+				((uint16_t *)output)[to] = ((const uint16_t *)source)[place[(uint64_t)row * width + column]];
+			} else if (operation == TP2_JOIN_FLOAT32_TO_BFLOAT16) {
+				((uint16_t *)output)[to] = orc_bfloat16_bits(((const float *)source)[from]);
+			} else {
+				volatile float value = orc_bfloat16_value(((const uint16_t *)source)[from]);
+				if (record->has_routed_sums != 0)
+					value = ((const float *)(arena + record->routed_sums_offset))
+							[(uint64_t)row * record->routed_row_stride + column] +
+						value;
+				if (operation == TP2_JOIN_BFLOAT16_TO_FLOAT32)
+					((float *)output)[to] = value;
+				else if (operation == TP2_JOIN_BFLOAT16_SUM_TO_BFLOAT16)
+					((uint16_t *)output)[to] = orc_bfloat16_bits(value);
+				else
+					((uint16_t *)output)[place[(uint64_t)row * width + column]] = orc_bfloat16_bits(value);
+			}
+		}
+	free(place);
 }
 
 int orc_ordered_collective(const float *const *inputs, float *const *outputs, uint32_t rank_count,

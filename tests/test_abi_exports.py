@@ -53,7 +53,7 @@ def test_record_sizes_match_the_headers():
               "ordered_collective_arguments": R.OrderedCollective, "ordered_reduce_bf16_arguments": R.OrderedReduceBf16,
               "ordered_row_sum_publish_arguments": R.OrderedRowSumPublish,
               "ordered_push_arguments": R.OrderedPush, "tp_exchange_arguments": R.TpExchange,
-              "ordered_rows_push_arguments": R.OrderedRowsPush,
+              "ordered_rows_push_arguments": R.OrderedRowsPush, "tp2_join_arguments": R.Tp2Join,
               "router_select_b200_arguments": R.RouterSelectB200, "step_input_select_arguments": R.StepInputSelect,
               "activation_quantize_arguments": R.ActivationQuantize, "expert_gate_up_arguments": R.ExpertGateUp,
               "expert_down_arguments": R.ExpertDown, "trunk_linear_quantized_arguments": R.TrunkLinearQuantized,
