@@ -50,7 +50,9 @@ AB_INLINE uint32_t exl3_moe_splits(uint32_t inputs, uint32_t outputs)
 #define EXL3_PREFILL_A_STAGES 4u
 #define EXL3_PREFILL_B_STAGES 4u
 /* the largest of the product CTAs' forms: a stage is 32 KB of one ring and 16 KB of the other */
-#define EXL3_PREFILL_DYNAMIC_BYTES (EXL3_PREFILL_A_STAGES * 32768u + EXL3_PREFILL_B_STAGES * 16384u)
+#define EXL3_PREFILL_W_STAGE 8192u /* trellis words of one stage at most: 16 x 16 x 64 weights x 4 bits */
+#define EXL3_PREFILL_DYNAMIC_BYTES \
+	(EXL3_PREFILL_A_STAGES * 32768u + EXL3_PREFILL_B_STAGES * (16384u + EXL3_PREFILL_W_STAGE))
 #define EXL3_PREFILL_STAGING_ROW 132u /* floats of a staged accumulator row */
 
 #endif

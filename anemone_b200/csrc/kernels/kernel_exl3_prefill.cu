@@ -31,10 +31,12 @@ struct prefill_shared {
 	uint64_t a_free[EXL3_PREFILL_A_STAGES]; /* the products that read them are done */
 	uint64_t b_full[EXL3_PREFILL_B_STAGES]; /* the stage's decoded weights are written */
 	uint64_t b_free[EXL3_PREFILL_B_STAGES]; /* the products that read them are done */
+	uint64_t w_full[EXL3_PREFILL_B_STAGES]; /* the stage's trellis words have landed */
 	uint64_t done; /* every product of the CTA is done */
 	uint32_t tensor_memory;
 	volatile uint32_t failed;
-	uint32_t armed_a; /* K blocks whose copies were started */
+	uint32_t armed_a; /* K blocks whose operand copies were started */
+	uint32_t armed_w[EXL3_PREFILL_B_STAGES]; /* a team's stages whose trellis copies were started */
 	uint32_t issued; /* 1: products were issued and `done` will complete */
 };
 
@@ -302,13 +304,16 @@ __device__ __forceinline__ void decode_sync()
 }
 
 /* Dynamic shared memory of a product CTA, for TILES row tiles of one expert, MATRICES matrices, GROUPS groups of 128
- * outputs and stages of KSTEPS steps of 16 inputs. Two rings:
+ * outputs and stages of KSTEPS steps of 16 inputs. Three rings:
  *   A ring        EXL3_PREFILL_A_STAGES x [tile][matrix] operand blocks (128 rows x 16 KSTEPS FP16 in the tensor cores'
  *                 layout, KSTEPS x 4096 bytes): bulk copies, mostly from L2
  *   B ring        EXL3_PREFILL_B_STAGES x [matrix] blocks of decoded weights, 128 GROUPS outputs x 16 KSTEPS FP16 in
  *                 the same layout (one instruction multiplies all groups and reads the operand rows once): written by
  *                 the decode warps, read by the products of EVERY row tile
- * The trellis words go straight from global memory into the decode warps' registers, one stage ahead. */
+ *   W ring        EXL3_PREFILL_B_STAGES x EXL3_PREFILL_W_STAGE bytes: the stage's trellis words as they lie in the
+ *                 matrix, one run of GROUPS x 8 tiles for every (matrix, step): bulk copies by the copy warp, read by the
+ *                 decode warps with shared-memory loads. The team that owns a stage starts the copies of its next use
+ *                 as soon as its four warps have read this one, a whole turn of the ring before it needs them. */
 template <uint32_t MATRICES, uint32_t KSTEPS, uint32_t TILES, uint32_t GROUPS> struct prefill_rings {
 	static constexpr uint32_t block_bytes = KSTEPS * 4096u;
 	static constexpr uint32_t a_stage = TILES * MATRICES * block_bytes;
@@ -316,7 +321,8 @@ template <uint32_t MATRICES, uint32_t KSTEPS, uint32_t TILES, uint32_t GROUPS> s
 	static constexpr uint32_t b_block = GROUPS * block_bytes; /* of one matrix */
 	static constexpr uint32_t b_stage = MATRICES * b_block;
 	static constexpr uint32_t b_at = EXL3_PREFILL_A_STAGES * a_stage;
-	static constexpr uint32_t bytes = b_at + EXL3_PREFILL_B_STAGES * b_stage;
+	static constexpr uint32_t w_at = b_at + EXL3_PREFILL_B_STAGES * b_stage;
+	static constexpr uint32_t bytes = w_at + EXL3_PREFILL_B_STAGES * EXL3_PREFILL_W_STAGE;
 	static constexpr uint32_t columns = TILES * MATRICES * GROUPS * PREFILL_COLUMNS; /* of tensor memory */
 	static_assert(bytes <= EXL3_PREFILL_DYNAMIC_BYTES, "the host sizes the rings");
 	static_assert(columns <= 512u, "tensor memory has 512 columns");
@@ -330,7 +336,7 @@ template <uint32_t MATRICES, uint32_t KSTEPS, uint32_t TILES, uint32_t GROUPS> s
 /* The K loop of one CTA. matrices[m]: the codes of matrix m (`outputs` outputs), of which the CTA takes the `groups`
  * (1 .. GROUPS) groups of 128 outputs from group `first_group`; operand_blocks[tile * MATRICES + m]: row tile `tile`'s
  * operand blocks for matrix m; `blocks` stages of 16 KSTEPS inputs. Warp 0 copies operand blocks, one thread of warp 1
- * issues the products, warps 2 .. decode. On return the decode warps know whether the
+ * issues the products, warps 2 .. copy trellis words and decode. On return the decode warps know whether the
  * accumulators (prefill_rings::column from shared->tensor_memory) are complete; the other warps return false.
  * All threads call. */
 template <uint32_t BX2, uint32_t MATRICES, uint32_t KSTEPS, uint32_t TILES, uint32_t GROUPS>
@@ -342,7 +348,12 @@ __device__ __forceinline__ bool prefill_products(const unsigned char *const (&ma
 	typedef exl3_ring<BX2> ring;
 	typedef prefill_rings<MATRICES, KSTEPS, TILES, GROUPS> rings;
 	constexpr uint32_t AS = EXL3_PREFILL_A_STAGES, BS = EXL3_PREFILL_B_STAGES;
+	/* the trellis words of one (matrix, step) of a stage: GROUPS groups of eight tiles, adjacent in the matrix */
+	constexpr uint32_t w_chunk = GROUPS * EXL3_GROUP_TILES * ring::words * 4u;
+	static_assert(MATRICES * KSTEPS * w_chunk <= EXL3_PREFILL_W_STAGE, "the W ring holds a stage");
+	static_assert(MATRICES <= 2u && MATRICES * KSTEPS <= EXL3_WARP && w_chunk % 16u == 0u, "a lane a copy, whole 16 bytes");
 	const uint32_t lane = threadIdx.x % EXL3_WARP, warp = threadIdx.x / EXL3_WARP;
+	const uint64_t step_words = (uint64_t)(outputs / EXL3_TILE) * ring::words; /* of one step of 16 inputs */
 
 	if (threadIdx.x == 0) {
 		for (uint32_t stage = 0; stage < AS; stage++) {
@@ -352,10 +363,13 @@ __device__ __forceinline__ bool prefill_products(const unsigned char *const (&ma
 		for (uint32_t stage = 0; stage < BS; stage++) {
 			barrier_init(&shared->b_full[stage], 4u); /* the four warps of the team that decodes the stage */
 			barrier_init(&shared->b_free[stage], 1);
+			barrier_init(&shared->w_full[stage], 1);
 		}
 		barrier_init(&shared->done, 1);
 		shared->failed = 0;
 		shared->armed_a = 0;
+		for (uint32_t stage = 0; stage < BS; stage++)
+			shared->armed_w[stage] = 0;
 		shared->issued = 0;
 		asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 	}
@@ -410,18 +424,20 @@ __device__ __forceinline__ bool prefill_products(const unsigned char *const (&ma
 				if (!good)
 					break;
 				tensor_fence_after();
-				const uint32_t a_at = smem_address(dynamic_shared + sa * rings::a_stage);
-				const uint32_t b_at = smem_address(dynamic_shared + rings::b_at + sb * rings::b_stage);
+				/* the stage's first descriptors; every other one lies a constant number of 16-byte units behind */
+				const uint64_t a_first =
+					prefill_descriptor(smem_address(dynamic_shared + sa * rings::a_stage), 2048u);
+				const uint64_t b_first = prefill_descriptor(
+					smem_address(dynamic_shared + rings::b_at + sb * rings::b_stage), rings::b_piece);
 #pragma unroll
 				for (uint32_t tile = 0; tile < TILES; tile++)
 #pragma unroll
 					for (uint32_t m = 0; m < MATRICES; m++)
 #pragma unroll
 						for (uint32_t step = 0; step < KSTEPS; step++) {
-							const uint64_t a = prefill_descriptor(
-								a_at + (tile * MATRICES + m) * rings::block_bytes + step * 2u * 2048u, 2048u);
-							const uint64_t b = prefill_descriptor(
-								b_at + m * rings::b_block + step * 2u * rings::b_piece, rings::b_piece);
+							const uint64_t a =
+								a_first + (((tile * MATRICES + m) * rings::block_bytes + step * 2u * 2048u) >> 4);
+							const uint64_t b = b_first + ((m * rings::b_block + step * 2u * rings::b_piece) >> 4);
 							const uint32_t accumulate = block > 0 || step > 0 ? 1u : 0u;
 							asm volatile("{\n\t.reg .pred p;\n\t"
 								     "setp.ne.b32 p, %4, 0;\n\t"
@@ -445,10 +461,10 @@ __device__ __forceinline__ bool prefill_products(const unsigned char *const (&ma
 	}
 
 	/* decode: the sixteen warps are four teams of four; team q decodes the WHOLE stages q, q + 4, ... (with four
-	 * decoded-weights stages in the ring a team owns one of them), so that the teams work on four different stages
-	 * at once and a warp crosses a barrier and a proxy fence once per stage of 8 or 16 tiles, not once per 2 or 4.
-	 * Warp r of a team takes the stage's units r * units_a_warp .. : a unit is the eight adjacent tiles of one
-	 * (matrix, group, step), whose ring words the lane loads straight from global memory, one unit ahead. */
+	 * decoded-weights stages in the ring a team owns one of them, and the W stage of the same number), so that the
+	 * teams work on four different stages at once and a warp crosses a barrier and a proxy fence once per stage of 8
+	 * or 16 tiles, not once per 2 or 4. Warp r of a team takes the stage's units r * units_a_warp .. : a unit is the
+	 * eight adjacent tiles of one (matrix, group, step), whose ring words the lane reads from the W ring. */
 	{
 		static_assert(EXL3_PREFILL_B_STAGES == 4u && PREFILL_DECODE_WARPS == 16u, "a team of four warps a stage");
 		constexpr uint32_t units = MATRICES * GROUPS * KSTEPS, units_a_warp = units / 4u;
@@ -456,77 +472,75 @@ __device__ __forceinline__ bool prefill_products(const unsigned char *const (&ma
 		const uint32_t decoder = warp - PREFILL_FIRST_DECODE_WARP, team = decoder / 4u, member = decoder % 4u;
 		const uint32_t begin = ring::begin(lane);
 		const uint32_t word_index = begin / 32u, shift = begin % 32u, next_index = (word_index + 1u) % ring::words;
-		const uint64_t step_words = (uint64_t)(outputs / EXL3_TILE) * ring::words;
-		const uint32_t my_blocks = blocks > team ? (blocks - team + 3u) / 4u : 0u;
-		const uint32_t count = my_blocks * units_a_warp; /* units this warp decodes, in order */
-		/* unit i of this warp: block team + 4 (i / units_a_warp), unit member * units_a_warp + i % units_a_warp of
-		 * the stage = (matrix m, group g, step) in that order of significance */
-		uint32_t first[EXL3_GROUP_TILES][2], second[EXL3_GROUP_TILES][2];
-#define PREFILL_UNIT_PLACE(i, block, m, g, step)                                                             \
-	const uint32_t block = team + 4u * ((i) / units_a_warp);                                             \
-	const uint32_t unit_ = member * units_a_warp + (i) % units_a_warp;                                    \
-	const uint32_t step = unit_ % KSTEPS, g = unit_ / KSTEPS % GROUPS, m = unit_ / (KSTEPS * GROUPS)
-#define PREFILL_UNIT_LOAD(set, i)                                                                            \
+		const uint32_t *const words_at =
+			reinterpret_cast<const uint32_t *>(dynamic_shared + rings::w_at + team * EXL3_PREFILL_W_STAGE);
+		unsigned char *const b_at = dynamic_shared + rings::b_at + team * rings::b_stage + lane * 4u;
+		/* the team's first warp copies the stage's trellis words: lane (m, step) the run of that matrix and step */
+		const uint32_t w_bytes = groups * EXL3_GROUP_TILES * ring::words * 4u;
+		const unsigned char *const w_from =
+			(MATRICES > 1u && lane >= KSTEPS ? matrices[MATRICES - 1u] : matrices[0]) +
+			((uint64_t)(lane % KSTEPS) * step_words + (uint64_t)first_group * EXL3_GROUP_TILES * ring::words) * 4u;
+		unsigned char *const w_to = dynamic_shared + rings::w_at + team * EXL3_PREFILL_W_STAGE + lane * w_chunk;
+#define PREFILL_WORDS_COPY(block)                                                                             \
 	do {                                                                                                  \
-		PREFILL_UNIT_PLACE(i, block_, m_, g_, step_);                                                 \
-		if (g_ < groups) {                                                                            \
-			const uint32_t *const from = reinterpret_cast<const uint32_t *>(matrices[m_]) +      \
-						     ((uint64_t)block_ * KSTEPS + step_) * step_words +        \
-						     (uint64_t)(first_group + g_) * EXL3_GROUP_TILES * ring::words; \
-			_Pragma("unroll") for (uint32_t tile = 0; tile < EXL3_GROUP_TILES; tile++)            \
-			{                                                                                     \
-				set[tile][0] = __ldg(from + tile * ring::words + word_index);                 \
-				set[tile][1] = __ldg(from + tile * ring::words + next_index);                 \
-			}                                                                                     \
+		if (lane == 0) {                                                                              \
+			barrier_expect(&shared->w_full[team], MATRICES * KSTEPS * w_bytes);                   \
+			shared->armed_w[team] = (block) / BS + 1u;                                            \
 		}                                                                                             \
-	} while (0)
-#define PREFILL_UNIT_DECODE(set, i)                                                                          \
-	do {                                                                                                  \
-		PREFILL_UNIT_PLACE(i, block_, m_, g_, step_);                                                 \
-		if ((i) % units_a_warp == 0u && block_ >= BS)                                                 \
-			good = barrier_wait(&shared->b_free[team], (block_ / BS - 1u) & 1u);                  \
-		if (!good)                                                                                    \
-			break;                                                                                \
-		if (g_ < groups) {                                                                            \
-			unsigned char *const to_unit = dynamic_shared + rings::b_at + team * rings::b_stage + \
-						       m_ * rings::b_block + step_ * 2u * rings::b_piece +    \
-						       g_ * EXL3_GROUP_TILES * 2u * 128u + lane * 4u;           \
-			_Pragma("unroll") for (uint32_t tile = 0; tile < EXL3_GROUP_TILES; tile++)            \
-			{                                                                                     \
-				uint32_t fragment[4];                                                         \
-				exl3_decode_fragment<BX2>(set[tile][0], set[tile][1], shift, fragment);       \
-				/* fragment f: outputs 16 tile + g + 8 (f % 2), inputs 16 step + 2 t + 8 (f / 2): the warp's 32 \
-				 * words are the 128 bytes of one K piece of one group of eight outputs */   \
-				uint32_t *const to = reinterpret_cast<uint32_t *>(to_unit + tile * 2u * 128u); \
-				to[0] = fragment[0];                                                          \
-				to[128u / 4u] = fragment[1];                                                  \
-				to[rings::b_piece / 4u] = fragment[2];                                        \
-				to[(rings::b_piece + 128u) / 4u] = fragment[3];                               \
-			}                                                                                     \
-		}                                                                                             \
-		if ((i) % units_a_warp == units_a_warp - 1u) {                                                \
-			asm volatile("fence.proxy.async.shared::cta;" ::: "memory");                        \
-			__syncwarp();                                                                         \
-			if (lane == 0)                                                                        \
-				barrier_arrive(&shared->b_full[team]);                                        \
-		}                                                                                             \
+		__syncwarp();                                                                                 \
+		if (lane < MATRICES * KSTEPS)                                                                 \
+			bulk_load(w_to, w_from + (uint64_t)(block) * KSTEPS * step_words * 4u, w_bytes,      \
+				  &shared->w_full[team]);                                                     \
 	} while (0)
 		bool good = true;
-		if (count > 0u)
-			PREFILL_UNIT_LOAD(first, 0u);
-		for (uint32_t i = 0; i < count && good; i += 2u) {
-			if (i + 1u < count)
-				PREFILL_UNIT_LOAD(second, i + 1u);
-			PREFILL_UNIT_DECODE(first, i);
-			if (i + 1u >= count || !good)
+		if (member == 0u && team < blocks)
+			PREFILL_WORDS_COPY(team);
+		for (uint32_t block = team; block < blocks; block += 4u) {
+			const uint32_t use = block / BS;
+			if (use > 0u)
+				good = barrier_wait(&shared->b_free[team], (use - 1u) & 1u);
+			if (good)
+				good = barrier_wait(&shared->w_full[team], use & 1u);
+			if (!good)
 				break;
-			if (i + 2u < count)
-				PREFILL_UNIT_LOAD(first, i + 2u);
-			PREFILL_UNIT_DECODE(second, i + 1u);
+#pragma unroll
+			for (uint32_t turn = 0; turn < units_a_warp; turn++) {
+				/* unit = (matrix m, group g, step) in that order of significance */
+				const uint32_t unit = member * units_a_warp + turn;
+				const uint32_t step = unit % KSTEPS, g = unit / KSTEPS % GROUPS, m = unit / (KSTEPS * GROUPS);
+				if (g >= groups)
+					continue;
+				const uint32_t *const from =
+					words_at + (m * KSTEPS + step) * (w_chunk / 4u) + g * EXL3_GROUP_TILES * ring::words;
+				unsigned char *const to_unit = b_at + m * rings::b_block + step * 2u * rings::b_piece +
+							       g * EXL3_GROUP_TILES * 2u * 128u;
+#pragma unroll
+				for (uint32_t tile = 0; tile < EXL3_GROUP_TILES; tile++) {
+					uint32_t fragment[4];
+					exl3_decode_fragment<BX2>(from[tile * ring::words + word_index],
+								  from[tile * ring::words + next_index], shift, fragment);
+					/* fragment f: outputs 16 tile + g + 8 (f % 2), inputs 16 step + 2 t + 8 (f / 2): the warp's 32
+					 * words are the 128 bytes of one K piece of one group of eight outputs */
+					uint32_t *const to = reinterpret_cast<uint32_t *>(to_unit + tile * 2u * 128u);
+					to[0] = fragment[0];
+					to[128u / 4u] = fragment[1];
+					to[rings::b_piece / 4u] = fragment[2];
+					to[(rings::b_piece + 128u) / 4u] = fragment[3];
+				}
+			}
+			asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+			__syncwarp();
+			if (lane == 0)
+				barrier_arrive(&shared->b_full[team]);
+			/* the stage's next use: its words may be overwritten once all four warps have read these */
+			if (member == 0u && block + 4u < blocks) {
+				good = barrier_wait(&shared->b_full[team], use & 1u);
+				if (!good)
+					break;
+				PREFILL_WORDS_COPY(block + 4u);
+			}
 		}
-#undef PREFILL_UNIT_PLACE
-#undef PREFILL_UNIT_LOAD
-#undef PREFILL_UNIT_DECODE
+#undef PREFILL_WORDS_COPY
 		if (good)
 			good = barrier_wait(&shared->done, 0u);
 		if (!good)
@@ -582,6 +596,9 @@ template <uint32_t COLUMNS> __device__ __forceinline__ void prefill_release(pref
 			const uint32_t block = shared->armed_a - 1u - back;
 			(void)barrier_wait(&shared->a_full[block % EXL3_PREFILL_A_STAGES], (block / EXL3_PREFILL_A_STAGES) & 1u);
 		}
+		for (uint32_t team = 0; team < EXL3_PREFILL_B_STAGES; team++)
+			if (shared->armed_w[team] != 0)
+				(void)barrier_wait(&shared->w_full[team], (shared->armed_w[team] - 1u) & 1u);
 		if (shared->issued != 0)
 			(void)barrier_wait(&shared->done, 0u);
 	}
