@@ -188,7 +188,7 @@ def run_prefill(args, api, base, widths, draw, rank, world, local_rank, dist, ba
     # ---- value: tokens and scores resident; only the 16-byte step block (the reduction's sequence) goes in ----
     layer.load(*inputs[0])
     first = layer.sequence
-    for index in range(warmup + steps):
+    for index in range(warmup + steps + 1):  # one more: the untimed call behind the barrier that aligns the ranks
         block = R.StepBlock(first + 1 + index, rows, 0)
         card.staging_view[64 * index:64 * index + 16] = np.frombuffer(bytes(block), dtype=np.uint8)
 
@@ -203,15 +203,16 @@ def run_prefill(args, api, base, widths, draw, rank, world, local_rank, dist, ba
         resident(index)
     card.wait()
     barrier()
+    resident(warmup)  # untimed: the ranks meet in its reduction, so the timed region begins together on every card
     launches_before = card.launch_count()
     card.measure_begin()
-    for index in range(warmup, warmup + steps):
+    for index in range(warmup + 1, warmup + 1 + steps):
         resident(index)
     card.measure_end()
     device_ms = maximum(card.measure_elapsed_us() / 1000.0) / steps
     card.wait()
     launches = (card.launch_count() - launches_before) // steps
-    layer.sequence = first + warmup + steps
+    layer.sequence = first + warmup + steps + 1
     layer.result(1)  # raises if a wait expired or the reduction failed
     barrier()
 
@@ -339,7 +340,9 @@ def workload_config(args, config, world):
                                                                                  config.picks, config.hidden,
                                                                                  config.inner, args.rows),
             "rows": args.rows, "parallelism": "tp%d by intermediate columns, ordered FP32->bf16 reduce" % world,
-            "l2": "inputs larger than L2: every step routes to a different expert set (~58 experts of 257)"}
+            "l2": "inputs larger than L2: every step routes to a different expert set (~58 experts of 257)",
+            "timing": "W warm-up steps, barrier and synchronize, one more untimed step in which the ranks meet on the "
+                      "device, then K steps between two CUDA events on the launching stream, max over ranks"}
 
 
 def run_reference_kernels(args, api, base, draw_k3, local_rank):
@@ -439,9 +442,9 @@ def run_original_weights(args, api, base, rank, world, local_rank, dist, barrier
         layer.connect_handles(handles)
     card.wait()
     barrier()
-    inputs = step_inputs(config, rows, warmup + steps)
+    inputs = step_inputs(config, rows, warmup + steps + 1)  # the last: the untimed step behind the barrier
     stride = api.align(layout.step_input_bytes, 4096)
-    assert stride * (warmup + steps) + 2 * rows * H <= card.staging_bytes
+    assert stride * (warmup + steps + 1) + 2 * rows * H <= card.staging_bytes
     # ---- value: every step's inputs wait in pinned memory; the copies in are inside the timed region all the same,
     # because this part keeps no pool on the card (74 KB a step) ----
     for index, (tokens, scores) in enumerate(inputs):
@@ -458,15 +461,16 @@ def run_original_weights(args, api, base, rank, world, local_rank, dist, barrier
         queued(index)
     card.wait()
     barrier()
+    queued(warmup)  # untimed: the ranks meet in its reduction, so the timed region begins together on every card
     launches_before = card.launch_count()
     card.measure_begin()
-    for index in range(warmup, warmup + steps):
+    for index in range(warmup + 1, warmup + 1 + steps):
         queued(index)
     card.measure_end()
     device_ms = maximum(card.measure_elapsed_us() / 1000.0) / steps
     card.wait()
     launches = (card.launch_count() - launches_before) // steps
-    layer.sequence = warmup + steps
+    layer.sequence = warmup + steps + 1
     layer.check_status()
     barrier()
     # ---- e2e ----
@@ -474,7 +478,7 @@ def run_original_weights(args, api, base, rank, world, local_rank, dist, barrier
         layer.step(tokens, scores)
     barrier()
     wall_begin = time.perf_counter()
-    for tokens, scores in inputs[warmup:]:
+    for tokens, scores in inputs[warmup:warmup + steps]:
         layer.step(tokens, scores)
     e2e_ms = maximum(1000.0 * (time.perf_counter() - wall_begin)) / steps
     barrier()
@@ -538,7 +542,7 @@ def run_reduction(args, api, hidden, rank, world, local_rank, dist, barrier, max
     # the order the timings run in; the exchange last: its sequences (twice a step's and more) leave no room above
     forms = ("pull_every_rank", "pull_owner_runs", "push_every_rank", "exchange_owner_sums")
     row_counts, repeats, warm_graphs, timed_graphs = (1, 8, 64), 10, 1, 4
-    pool_entries = len(forms) * len(row_counts) * repeats * (warm_graphs + timed_graphs)
+    pool_entries = len(forms) * len(row_counts) * repeats * (warm_graphs + 1 + timed_graphs)
     pool, cursor = layout.take(64 * pool_entries, 64), layout.take(16)
     arena_bytes = layout.take(4096, 4096)
     card = api.Card(local_rank, arena_bytes)
@@ -547,7 +551,7 @@ def run_reduction(args, api, hidden, rank, world, local_rank, dist, barrier, max
     entry = 0
     for form in forms:  # the order the timings below run in; sequences strictly increasing
         for rows in row_counts:
-            for _ in range(repeats * (warm_graphs + timed_graphs)):
+            for _ in range(repeats * (warm_graphs + 1 + timed_graphs)):
                 blocks[64 * entry:64 * entry + 16] = np.frombuffer(bytes(R.StepBlock(entry + 1, rows, 0)), dtype=np.uint8)
                 entry += 1
     card.upload(pool, blocks)
@@ -610,6 +614,7 @@ def run_reduction(args, api, hidden, rank, world, local_rank, dist, barrier, max
             card.graph_run(graph)
         card.wait()
         barrier()
+        card.graph_run(graph)  # untimed: the ranks meet on the device before the timed graphs begin
         card.measure_begin()
         for _ in range(timed_graphs):
             card.graph_run(graph)
@@ -715,7 +720,8 @@ def main():
 
     if api.card_count() <= local_rank:
         raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
-    total_steps = args.warmup + args.steps
+    # one step more than the warm-up and the timed ones: it runs untimed behind the barrier (see below)
+    total_steps = args.warmup + args.steps + 1
     layout = MoeLayout(config, widths, world, rank, pool_entries=total_steps)
     card = api.Card(local_rank, layout.arena_bytes)
     matrices = (local_matrices(*draw(expert), config, int(widths[expert]), world, rank)
@@ -730,15 +736,21 @@ def main():
     card.wait()
     barrier()
     steps = step_inputs(config, args.rows, total_steps)
+    aligning, steps = steps[-1], steps[:-1]
 
     # ---- value: inputs resident on the card ----
-    layer.load_pool([(index + 1, tokens, scores) for index, (tokens, scores) in enumerate(steps)])
+    order = steps[:args.warmup] + [aligning] + steps[args.warmup:]
+    layer.load_pool([(index + 1, tokens, scores) for index, (tokens, scores) in enumerate(order)])
     barrier()
     for _ in range(args.warmup):
         layer.run_resident()
     card.wait()
     barrier()
     sampler = ClockSampler(local_rank) if rank == 0 else None
+    # The ranks leave the barrier microseconds to milliseconds apart on the host. One untimed step queued first makes
+    # them meet on the device (its reduction waits for every rank), so the timed region begins at the same moment on
+    # every card and holds exactly the timed steps, not a rank's wait for a late one.
+    layer.run_resident()
     launches_before = card.launch_count()
     card.measure_begin()
     for _ in range(args.steps):
