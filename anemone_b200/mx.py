@@ -29,8 +29,9 @@ def shared_matrix_bytes(outputs, inputs):
 
 
 class MxLayout:
-    def __init__(self, config, rank_count, rank):
+    def __init__(self, config, rank_count, rank, pool_entries=0):
         assert config.shared in (0, 1)
+        self.pool_entries = pool_entries
         self.config = c = config
         self.inner_local = I = rank_columns(c.inner, rank_count, rank)[1]
         H, rows = c.hidden, c.row_capacity
@@ -44,6 +45,10 @@ class MxLayout:
         self.scores = layout.take(rows * c.experts * 4)
         self.step_input_bytes = layout.cursor - self.step
         self.result = layout.take(rows * H * 2)
+        # optional: a pool of prepared step inputs resident on the card (step_input_select walks it)
+        self.pool_stride = api.align(self.step_input_bytes, 256)
+        self.cursor = layout.take(16)
+        self.pool = layout.take(self.pool_stride * pool_entries) if pool_entries else 0
         self.slot_input = SIGNAL_BYTES
         self.parity_stride = api.align(SIGNAL_BYTES + rows * H * 4, LINE)
         self.region = layout.take(2 * self.parity_stride, LINE)
@@ -72,11 +77,11 @@ class MxLayout:
 
 class MxLayer:
     def __init__(self, card, config, matrices, rank=0, rank_count=1, slices=(4, 4), shared_matrices=None,
-                 shared_slices=(2, 2)):
+                 shared_slices=(2, 2), pool_entries=0):
         """matrices: iterable over the routed experts of this rank's (gate, up, down) stored MXFP4 bytes;
         shared_matrices: the always-on expert's (gate, up, down) stored E4M3 bytes, where the configuration has one."""
         self.card, self.config = card, config
-        self.layout = L = MxLayout(config, rank_count, rank)
+        self.layout = L = MxLayout(config, rank_count, rank, pool_entries)
         assert card.arena_bytes >= L.arena_bytes
         self.rank, self.rank_count = rank, rank_count
         self.weight_bytes = 0
@@ -178,7 +183,31 @@ class MxLayer:
         self.launches = [router_launch, quantize_launch] + list(self.expert_launches) + shared_launches + \
             list(reduce_launches)
         self.graph = card.graph(self.launches)
+        self.resident_graph = None
+        if L.pool_entries:
+            select = R.StepInputSelect(L.pool, L.pool_stride, L.step, L.cursor, L.pool_entries, L.step_input_bytes)
+            lib.step_input_select_prepare.argtypes = [C.POINTER(R.StepInputSelect), C.c_uint64,
+                                                      C.POINTER(api.BackendOperations), C.c_void_p,
+                                                      C.POINTER(R.KernelLaunch)]
+            select_launch = R.KernelLaunch()
+            api.check(lib.step_input_select_prepare(C.byref(select), card.arena_bytes, card.ops_pointer, card.handle,
+                                                    C.byref(select_launch)), "step_input_select_prepare")
+            self.resident_graph = card.graph([select_launch] + self.launches)
         self.sequence = 0
+
+    def load_pool(self, steps):
+        """steps: pool_entries tuples (sequence, tokens, scores), sequences strictly increasing. Their input areas go
+        to the card's pool; run_resident() then takes them one after the other without touching the host."""
+        L, card = self.layout, self.card
+        assert len(steps) == L.pool_entries
+        for index, (sequence, tokens, scores) in enumerate(steps):
+            self.stage_step(0, sequence, tokens, scores)
+            card.transfer_wait(card.upload_async(L.pool + index * L.pool_stride, 0, L.step_input_bytes))
+        card.fill(L.cursor, 0, 16)
+        card.wait()
+
+    def run_resident(self):
+        self.card.graph_run(self.resident_graph)
 
     def connect_local(self, layers):
         for peer, other in enumerate(layers):

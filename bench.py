@@ -422,7 +422,8 @@ def run_original_weights(args, api, base, rank, world, local_rank, dist, barrier
     rows, steps, warmup = args.rows, args.steps, args.warmup
     config = MoeConfig(hidden=base.hidden, inner=base.inner, experts=base.experts, shared=1, picks=base.picks,
                        row_capacity=rows, activation_limit=7.0)
-    layout = MxLayout(config, world, rank)
+    pool_entries = warmup + steps + 1  # the last: the untimed step behind the barrier
+    layout = MxLayout(config, world, rank, pool_entries)
     H, I = config.hidden, layout.inner_local
     card = api.Card(local_rank, layout.arena_bytes)
 
@@ -433,7 +434,7 @@ def run_original_weights(args, api, base, rank, world, local_rank, dist, barrier
     always = (synthetic.e4m3_matrix(always_rng, I, H), synthetic.e4m3_matrix(always_rng, I, H),
               synthetic.e4m3_matrix(always_rng, H, I))
     layer = MxLayer(card, config, (draw(expert) for expert in range(config.experts)), rank=rank, rank_count=world,
-                    slices=(2, 2), shared_matrices=always)
+                    slices=(2, 2), shared_matrices=always, pool_entries=pool_entries)
     if dist is None:
         layer.connect_local([layer])
     else:
@@ -442,30 +443,19 @@ def run_original_weights(args, api, base, rank, world, local_rank, dist, barrier
         layer.connect_handles(handles)
     card.wait()
     barrier()
-    inputs = step_inputs(config, rows, warmup + steps + 1)  # the last: the untimed step behind the barrier
-    stride = api.align(layout.step_input_bytes, 4096)
-    assert stride * (warmup + steps + 1) + 2 * rows * H <= card.staging_bytes
-    # ---- value: every step's inputs wait in pinned memory; the copies in are inside the timed region all the same,
-    # because this part keeps no pool on the card (74 KB a step) ----
-    for index, (tokens, scores) in enumerate(inputs):
-        layer.stage_step(stride * index, index + 1, tokens, scores)
-
-    tickets = []
-
-    def queued(index):
-        if len(tickets) >= 4:  # the card takes a bounded number of copies in flight
-            card.transfer_wait(tickets[-4])
-        tickets.append(card.upload_async(layout.step, stride * index, layout.step_input_bytes))
-        card.graph_run(layer.graph)
-    for index in range(warmup):
-        queued(index)
+    inputs = step_inputs(config, rows, pool_entries)
+    # ---- value: every step's inputs wait in a pool on the card; a select launch in front of each step takes the next
+    layer.load_pool([(index + 1, tokens, scores) for index, (tokens, scores) in enumerate(inputs)])
+    barrier()
+    for _ in range(warmup):
+        layer.run_resident()
     card.wait()
     barrier()
-    queued(warmup)  # untimed: the ranks meet in its reduction, so the timed region begins together on every card
+    layer.run_resident()  # untimed: the ranks meet in its reduction, so the timed region begins together on every card
     launches_before = card.launch_count()
     card.measure_begin()
-    for index in range(warmup + 1, warmup + 1 + steps):
-        queued(index)
+    for _ in range(steps):
+        layer.run_resident()
     card.measure_end()
     device_ms = maximum(card.measure_elapsed_us() / 1000.0) / steps
     card.wait()
@@ -515,7 +505,8 @@ def run_original_weights(args, api, base, rank, world, local_rank, dist, barrier
                                    "E8M0 scale per 32x32 weights, hidden %d, intermediate %d, M=%d" %
                                    (config.experts, config.picks, H, config.inner, rows),
                        "parallelism": "tp%d by intermediate columns, ordered FP32->bf16 reduce" % world,
-                       "note": "value includes the 74 KB host->device copy of each step's inputs"}}
+                       "l2": "inputs larger than L2: every step routes to a different expert set; a step's inputs are taken "
+                             "from a pool on the card by a select launch"}}
 
 
 def run_reduction(args, api, hidden, rank, world, local_rank, dist, barrier, maximum):
