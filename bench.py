@@ -12,7 +12,8 @@ step streams a different set of about 58 experts (about 0.55 GB at N = 1, more t
 
 One JSON line on rank 0:
   value     tokens/s with every step's inputs already resident in HBM (a device-side step_input_select hands them over),
-            timed with CUDA events on the card's stream, max over ranks;
+            timed with CUDA events on the card's stream, max over ranks; behind the barrier one untimed step lets
+            the ranks meet on the device, so that the events hold the K steps and no rank's wait for a late one;
   e2e       the same through the public call with host buffers: per step the host -> device copy of the step's inputs
             from pinned memory, the layer's graph, the device -> host copy of the bfloat16 result, and the wait for it;
   roofline  the dominant kernel (exl3_moe_gate_up) timed alone, launch by launch, with CUDA events, against the
@@ -22,6 +23,8 @@ Further objects of the same line, each with its own value, e2e and roofline wher
   prefill            cfg4: the same layer for M = 4096 rows, Zipf(1.1) routing, experts sharded over the ranks,
                      tensor-core (tcgen05) grouped products, ordered reduction with owner runs;
   original_weights   cfg5 decode: MXFP4 routed experts and the E4M3 always-on expert, E4M3 block-quantized activations;
+  reduction          (N > 1) cfg2: the fixed-order reduction alone, FP32 [M][4096] a rank, M in {1, 8, 64}, in this
+                     library's four forms, microseconds a call and NVLink bytes a second;
   reference_kernels  (N = 1) the reference's own EXL3 kernels, recompiled for sm_100a from its sources into oracle/_ref,
                      timed on this card beside this library's expert launches on the same inputs (every expert K3).
 --impl reference times that CPU restatement of the reference's arithmetic alone (the reference has no engine CPU path
