@@ -6,16 +6,23 @@
  */
 #include "ordered_push_device.cuh"
 
+/* the plain push: no live-row count, no owner shards, no row sums, FP32 sums kept in the slot */
+__device__ __forceinline__ void plain_push_describe(const struct ordered_push_arguments &record,
+						    const unsigned char *arena, struct push_call *call)
+{
+	const struct step_block *const step = reinterpret_cast<const struct step_block *>(arena + record.step_offset);
+	call->a = record;
+	call->live = record.element_count;
+	call->sequence = step->sequence;
+	call->row_width = call->pairs_per_row = call->row_vectors = 0;
+	call->pairs = nullptr;
+	call->result = nullptr;
+}
+
 extern "C" __global__ void __launch_bounds__(ORDERED_COLLECTIVE_THREADS)
 	ordered_push(struct ordered_push_arguments arguments, unsigned char *arena)
 {
 	struct push_call call;
-	call.a = arguments;
-	call.sequence = reinterpret_cast<const struct step_block *>(arena + arguments.step_offset)->sequence;
-	call.live = arguments.element_count;
-	call.row_width = 0;
-	call.pairs = nullptr;
-	call.result = nullptr;
-	call.pairs_per_row = call.row_vectors = 0;
+	plain_push_describe(arguments, arena, &call);
 	push_run(call, arena);
 }
