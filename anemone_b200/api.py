@@ -103,6 +103,10 @@ def library():
         lib.exl3_prefill_sizes.argtypes = [C.c_uint32] * 6 + [C.POINTER(R.Exl3PrefillParts)]
         lib.exl3_moe_sizes.restype = None
         lib.exl3_moe_sizes.argtypes = [C.c_uint32] * 4 + [C.POINTER(R.Exl3MoeSizes)]
+        lib.exl3_layer_sizes.restype = None
+        lib.exl3_layer_sizes.argtypes = [C.c_uint32] * 4 + [C.POINTER(R.Exl3MoeSizes)]
+        lib.exl3_layer_prepare.argtypes = [C.POINTER(R.Exl3LayerDescription), C.POINTER(BackendOperations), _card,
+                                           C.POINTER(R.KernelLaunch)]
         lib.bb_exl3_row_sum_prepare.argtypes = [C.POINTER(R.ExpertRowSum), C.c_uint32, C.c_uint64,
                                                 C.POINTER(BackendOperations), _card, C.POINTER(R.KernelLaunch)]
         _library = lib
@@ -129,6 +133,13 @@ def moe_sizes(pair_count, job_count, input_size, inner_size):
     """Scratch sizes of the fused launches for these shapes (exl3_moe_sizes)."""
     sizes = R.Exl3MoeSizes()
     library().exl3_moe_sizes(pair_count, job_count, input_size, inner_size, C.byref(sizes))
+    return sizes
+
+
+def layer_sizes(pair_count, job_count, input_size, inner_size):
+    """Scratch sizes of the decode step's four launches for these shapes (exl3_layer_sizes)."""
+    sizes = R.Exl3MoeSizes()
+    library().exl3_layer_sizes(pair_count, job_count, input_size, inner_size, C.byref(sizes))
     return sizes
 
 

@@ -276,12 +276,152 @@ result_status exl3_moe_prepare(const struct exl3_moe_record *record, uint64_t ar
 	return STATUS_OK;
 }
 
+void exl3_layer_sizes(uint32_t pair_count, uint32_t job_count, uint32_t input_size, uint32_t inner_size,
+		      struct exl3_moe_sizes *sizes_out)
+{
+	struct exl3_moe_sizes sizes = { 0, 0, 0, 0, 0 };
+	if (sizes_out == NULL)
+		return;
+	if (input_size != 0 && inner_size != 0 && input_size % EXL3_TRANSFORM == 0 && inner_size % EXL3_TRANSFORM == 0) {
+		const uint64_t gate_up = (uint64_t)EXL3_PROJECTIONS * EXL3_LAYER_MAXIMUM_RUNS * pair_count * inner_size * 4u;
+		const uint64_t down = (uint64_t)EXL3_LAYER_MAXIMUM_RUNS * pair_count * input_size * 4u;
+		sizes.product_bytes = gate_up > down ? gate_up : down;
+		sizes.operand_bytes = (uint64_t)pair_count * input_size * EXL3_OPERAND_BYTES_PER_INPUT +
+				      (uint64_t)pair_count * inner_size * EXL3_HALF_BYTES;
+		sizes.counter_bytes = exl3_layer_counter_bytes(job_count, input_size, inner_size);
+	}
+	*sizes_out = sizes;
+}
+
+result_status exl3_layer_prepare(const struct exl3_layer_description *description,
+				 const struct backend_operations *backend, struct device_card *card,
+				 struct kernel_launch *launches_out)
+{
+	if (description == NULL || backend == NULL || card == NULL || launches_out == NULL ||
+	    backend->kernel_prepare == NULL || description->reserved_zero != 0)
+		return STATUS_INVALID_ARGUMENT;
+	const struct exl3_layer_route_record *const route = &description->route;
+	const struct exl3_layer_publish_arguments *const publish = &description->publish;
+	const struct exl3_moe_record *const moe = &route->moe;
+	const struct exl3_expert_record *const base = &moe->base;
+	const bool per_expert = base->bits_per_weight == EXL3_WIDTH_PER_EXPERT;
+	const uint64_t capacity = description->arena_byte_count;
+	const uint32_t H = base->input_size, I = base->inner_size, rows = route->row_capacity;
+	const uint32_t slots = route->picks + route->shared_count;
+	if (moe->reserved_zero != 0 || publish->reserved_zero != 0 || route->routed_count == 0 ||
+	    route->routed_count + route->shared_count > ROUTER_B200_MAXIMUM_EXPERTS ||
+	    route->routed_count + route->shared_count < route->routed_count || route->picks == 0 ||
+	    route->picks > ROUTER_B200_MAXIMUM_PICKS || route->picks > route->routed_count || rows == 0 ||
+	    rows > ROUTER_B200_MAXIMUM_ROWS || route->scoring > ROUTER_SCORING_SQRT_SOFTPLUS ||
+	    !isfinite(route->route_scale) || route->route_scale <= 0 || base->pairs_per_row != slots ||
+	    base->pair_count != rows * slots || moe->expert_count != route->routed_count + route->shared_count ||
+	    base->job_count < rows * route->picks + route->shared_count * ((rows + LINEAR_MAXIMUM_ROWS - 1u) / LINEAR_MAXIMUM_ROWS) ||
+	    publish->rank_count == 0 || publish->rank_count > ORDERED_COLLECTIVE_MAXIMUM_RANKS ||
+	    publish->rank >= publish->rank_count || publish->row_capacity != rows || publish->deadline_cycles == 0 ||
+	    publish->step_offset != route->step_offset || publish->input_offset < EXL3_LAYER_SIGNAL_BYTES ||
+	    publish->input_offset % 16u != 0 || publish->parity_stride % ORDERED_COLLECTIVE_LINE_BYTES != 0 ||
+	    publish->region_offset % ORDERED_COLLECTIVE_LINE_BYTES != 0 || H == 0 ||
+	    publish->parity_stride < publish->input_offset + (uint64_t)rows * H * 4u ||
+	    description->product_ctas > 65535u)
+		return STATUS_INVALID_ARGUMENT;
+	struct exl3_moe_sizes sizes;
+	exl3_layer_sizes(base->pair_count, base->job_count, H, I, &sizes);
+	if (sizes.operand_bytes == 0)
+		return STATUS_INVALID_ARGUMENT;
+	const uint64_t chain_operands = (uint64_t)base->pair_count * H * EXL3_OPERAND_BYTES_PER_INPUT;
+	const uint64_t chain_products = (uint64_t)base->pair_count * H * EXL3_PRODUCT_BYTES_PER_INPUT;
+	if (base->operands_offset > UINT64_MAX - chain_operands || base->products_offset > UINT64_MAX - chain_products)
+		return STATUS_INVALID_ARGUMENT;
+	const struct checked_range extra[11] = {
+		{ "width table", moe->widths_offset, per_expert ? (uint64_t)moe->expert_count * 4u : 0u },
+		{ "down operands", base->operands_offset + chain_operands, sizes.operand_bytes - chain_operands },
+		{ "run products", base->products_offset + chain_products,
+		  sizes.product_bytes > chain_products ? sizes.product_bytes - chain_products : 0u },
+		{ "counters", moe->counters_offset, sizes.counter_bytes },
+		{ "scores", route->scores_offset, (uint64_t)rows * route->routed_count * 4u },
+		{ "expert table", route->expert_table_offset, (uint64_t)moe->expert_count * 24u },
+		{ "picks", route->picks_offset, (uint64_t)rows * route->picks * 4u },
+		{ "weights", route->weights_offset, (uint64_t)rows * route->picks * 4u },
+		{ "bias", route->bias_offset, route->bias_offset != 0 ? (uint64_t)route->routed_count * 4u : 0u },
+		{ "step block", route->step_offset, sizeof(struct step_block) },
+		{ "result", description->result_offset, (uint64_t)rows * H * 2u }
+	};
+	const result_status valid = chain_validate("EXL3 layer", base, capacity, !per_expert, extra, 11);
+	if (valid != STATUS_OK)
+		return valid;
+	const struct checked_range reduction[3] = {
+		{ "region", publish->region_offset, publish->parity_stride * ORDERED_COLLECTIVE_SLOTS },
+		{ "status", publish->status_offset, ORDERED_B200_STATUS_BYTES },
+		{ "peer table", publish->peer_table_offset,
+		  (uint64_t)publish->rank_count * sizeof(struct ordered_collective_peer) }
+	};
+	if (!prepare_ranges_are_valid("EXL3 layer", reduction, 3, capacity))
+		return STATUS_INVALID_ARGUMENT;
+	const struct exl3_layer_down_record down = { .moe = *moe, .publish = *publish };
+	const struct ordered_reduce_bf16_arguments reduce = {
+		.collective = { .peer_table_offset = publish->peer_table_offset,
+				.region_offset = publish->region_offset,
+				.input_offset = publish->input_offset,
+				.output_offset = description->result_offset,
+				.scratch_offset = 0,
+				.step_offset = publish->step_offset,
+				.parity_stride = publish->parity_stride,
+				.deadline_cycles = publish->deadline_cycles,
+				.element_count = rows * H,
+				.rank_count = publish->rank_count,
+				.rank = publish->rank,
+				.reserved_zero = 0 },
+		.status_offset = publish->status_offset,
+		.width = H,
+		.mode = ORDERED_REDUCE_EVERY_RANK
+	};
+	const uint32_t product_ctas = description->product_ctas != 0 ?
+					      description->product_ctas :
+					      EXL3_LAYER_DEFAULT_SMS * EXL3_LAYER_PRODUCT_CTAS_PER_SM;
+	/* the transform's warp tasks: (pair, gate or up, 128 inputs); eight warps a CTA, a few tasks a warp */
+	const uint64_t tasks = (uint64_t)rows * slots * EXL3_PROJECTIONS * (H / EXL3_TRANSFORM);
+	uint64_t transform_ctas = (tasks + 15u) / 16u;
+	if (transform_ctas > 2u * EXL3_LAYER_DEFAULT_SMS - 1u)
+		transform_ctas = 2u * EXL3_LAYER_DEFAULT_SMS - 1u;
+	uint32_t reduce_blocks = (rows * H / 4u + ORDERED_COLLECTIVE_THREADS - 1u) / ORDERED_COLLECTIVE_THREADS;
+	if (reduce_blocks > ORDERED_B200_MAXIMUM_BLOCKS)
+		reduce_blocks = ORDERED_B200_MAXIMUM_BLOCKS;
+	const uint32_t shared = exl3_product_dynamic_bytes(EXL3_BITS_X2_K4);
+	const struct {
+		const char *file, *name;
+		const void *record;
+		uint32_t record_bytes, grid, threads, shared;
+	} shapes[EXL3_LAYER_LAUNCHES] = {
+		{ EXL3_LAYER_KERNEL_FILE, "exl3_layer_route_input", route, sizeof(*route), 1u + (uint32_t)transform_ctas,
+		  EXL3_LAYER_ROUTE_THREADS, 0 },
+		{ EXL3_LAYER_KERNEL_FILE, "exl3_layer_gate_up", moe, sizeof(*moe), product_ctas, EXL3_PRODUCT_THREADS, shared },
+		{ EXL3_LAYER_KERNEL_FILE, "exl3_layer_down_publish", &down, sizeof(down), product_ctas, EXL3_PRODUCT_THREADS,
+		  shared },
+		{ KERNEL_FILE_ORDERED_B200, "ordered_reduce_flags", &reduce, sizeof(reduce), reduce_blocks,
+		  ORDERED_COLLECTIVE_THREADS, 0 }
+	};
+	struct kernel_launch launches[EXL3_LAYER_LAUNCHES];
+	for (uint32_t index = 0; index < EXL3_LAYER_LAUNCHES; index++) {
+		uint32_t kernel = BACKEND_NO_KERNEL;
+		const result_status status = backend->kernel_prepare(card, shapes[index].file, shapes[index].name,
+								     shapes[index].record_bytes, &kernel);
+		if (status != STATUS_OK)
+			return status;
+		if (kernel == BACKEND_NO_KERNEL)
+			return STATUS_UNSUPPORTED;
+		prepare_launch_fill(&launches[index], kernel, shapes[index].grid, 1, 1, shapes[index].threads,
+				    shapes[index].shared, shapes[index].record, shapes[index].record_bytes);
+	}
+	memcpy(launches_out, launches, sizeof(launches));
+	return STATUS_OK;
+}
+
 result_status exl3_prefill_prepare(const struct exl3_prefill_record *record, uint64_t arena_byte_count,
 				   const struct backend_operations *backend, struct device_card *card,
 				   struct kernel_launch *launches_out)
 {
 	if (record == NULL || backend == NULL || card == NULL || launches_out == NULL ||
-	    backend->kernel_prepare == NULL || record->reserved_zero[0] != 0 || record->reserved_zero[1] != 0)
+	    backend->kernel_prepare == NULL)
 		return STATUS_INVALID_ARGUMENT;
 	const uint32_t H = record->input_size, I = record->inner_size, shared_I = record->shared_inner_size;
 	const uint32_t experts = record->local_count + record->shared_count;
@@ -301,7 +441,8 @@ result_status exl3_prefill_prepare(const struct exl3_prefill_record *record, uin
 	if (parts.tile_capacity > EXL3_MAXIMUM_GRID_ROWS)
 		return STATUS_INVALID_ARGUMENT;
 	const uint64_t rows = record->row_capacity, slots = record->picks + record->shared_count;
-	const struct checked_range ranges[10] = {
+	const struct checked_range ranges[11] = {
+		{ "bias", record->bias_offset, record->bias_offset != 0 ? (uint64_t)record->expert_count * 4u : 0u },
 		{ "scores", record->scores_offset, rows * record->expert_count * 4u },
 		{ "input", record->input_offset, rows * H * EXL3_HALF_BYTES },
 		{ "expert table", record->expert_table_offset, (uint64_t)experts * 24u },
@@ -314,7 +455,7 @@ result_status exl3_prefill_prepare(const struct exl3_prefill_record *record, uin
 		{ "step", record->step_offset, sizeof(struct step_block) }
 	};
 	if (record->workspace_offset % 1024u != 0 ||
-	    !prepare_ranges_are_valid("EXL3 prefill", ranges, 10, arena_byte_count))
+	    !prepare_ranges_are_valid("EXL3 prefill", ranges, 11, arena_byte_count))
 		return STATUS_INVALID_ARGUMENT;
 	static const char *const names[EXL3_PREFILL_LAUNCHES] = { "exl3_prefill_picks",	   "exl3_prefill_group",
 								  "exl3_prefill_tiles",	   "exl3_prefill_operands",

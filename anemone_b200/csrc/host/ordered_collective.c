@@ -195,7 +195,8 @@ result_status ordered_reduce_bf16_prepare(const struct ordered_reduce_bf16_descr
 									      .pair_output_offset =
 										      description->pair_output_offset,
 									      .width = reduce->width,
-									      .pairs_per_row = description->pairs_per_row };
+									      .pairs_per_row = description->pairs_per_row,
+									      .status_offset = reduce->status_offset };
 	const uint32_t vectors = reduce->width / 4u;
 	uint32_t blocks = (collective->element_count / 4u + ORDERED_COLLECTIVE_THREADS - 1u) / ORDERED_COLLECTIVE_THREADS;
 	/* few rows: a small grid, whose last block is found quickly; many rows: enough blocks to fill the card */

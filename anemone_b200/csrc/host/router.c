@@ -27,7 +27,8 @@ result_status router_select_b200_prepare(const struct router_select_b200_argumen
 		    router_b200_job_capacity(arguments->row_capacity, arguments->picks, arguments->shared_count))
 		return STATUS_INVALID_ARGUMENT;
 	const uint64_t rows = arguments->row_capacity;
-	const struct checked_range ranges[6] = {
+	const struct checked_range ranges[7] = {
+		{ "bias", arguments->bias_offset, arguments->bias_offset != 0 ? (uint64_t)arguments->expert_count * 4u : 0u },
 		{ "scores", arguments->scores_offset, rows * arguments->expert_count * 4u },
 		{ "expert table", arguments->expert_table_offset,
 		  (uint64_t)(arguments->expert_count + arguments->shared_count) * 24u },
@@ -36,7 +37,7 @@ result_status router_select_b200_prepare(const struct router_select_b200_argumen
 		{ "jobs", arguments->jobs_offset, (uint64_t)arguments->job_capacity * sizeof(struct expert_job_record) },
 		{ "step block", arguments->step_offset, sizeof(struct step_block) }
 	};
-	if (!prepare_ranges_are_valid("router select", ranges, 6, arena_byte_count))
+	if (!prepare_ranges_are_valid("router select", ranges, 7, arena_byte_count))
 		return STATUS_INVALID_ARGUMENT;
 	uint32_t kernel = BACKEND_NO_KERNEL;
 	const result_status status = backend->kernel_prepare(card, KERNEL_FILE_ROUTER_B200, KERNEL_ROUTER_SELECT_B200,

@@ -1,0 +1,145 @@
+/*
+ * exl3_fused.cuh: what the fused expert launches share (kernel_exl3_b200.cu: a fixed cut of K per CTA;
+ * kernel_exl3_layer.cu: one sequence of K rounds cut evenly over the grid): partial sums of a run of K in the arena,
+ * the counter that finds the CTA completing a (job, 128 outputs), the sum of the runs in ascending order from +0, and
+ * the two epilogues (activation with the down-side transform; output transform, scale and route weight). The
+ * arithmetic of every value is the retained chain's (exl3_passes.cuh).
+ */
+#ifndef AB_EXL3_FUSED_CUH
+#define AB_EXL3_FUSED_CUH
+
+#include "exl3_passes.cuh"
+
+__device__ __forceinline__ const uint32_t *moe_widths(const struct exl3_moe_record &record, const unsigned char *arena)
+{
+	return record.base.bits_per_weight == EXL3_WIDTH_PER_EXPERT ?
+		       reinterpret_cast<const uint32_t *>(arena + record.widths_offset) :
+		       nullptr;
+}
+
+/* this thread's sums (exl3_product_core's layout) to partial rows: row(column) + 128 group + output */
+__device__ __forceinline__ void store_partial(const float sums[2][4], float *const rows[LINEAR_MAXIMUM_ROWS],
+					      uint32_t row_count)
+{
+	const uint32_t lane = threadIdx.x % EXL3_WARP, warp = threadIdx.x / EXL3_WARP;
+	const uint32_t group_lane = lane / 4u, place = lane % 4u;
+#pragma unroll
+	for (uint32_t mine = 0; mine < 2; mine++)
+#pragma unroll
+		for (uint32_t c = 0; c < 4; c++) {
+			const uint32_t column = place * 2u + (c & 1u);
+			if (column < row_count)
+				rows[column][(warp * 2u + mine) * EXL3_TILE + group_lane + (c >> 1) * 8u] = sums[mine][c];
+		}
+}
+
+/* true in exactly one CTA of the `expected` that work on this counter: the last to arrive. Every CTA's partial sums are
+ * visible to it. The counter is left at zero for the next launch. */
+__device__ __forceinline__ bool last_of(uint32_t *counter, uint32_t expected, uint32_t *flag)
+{
+	__threadfence();
+	__syncthreads();
+	if (threadIdx.x == 0) {
+		const uint32_t arrived = atomicAdd(counter, 1u) + 1u;
+		*flag = arrived == expected ? 1u : 0u;
+		if (arrived == expected)
+			*counter = 0u;
+		__threadfence();
+	}
+	__syncthreads();
+	return *flag != 0u;
+}
+
+/* FP32 sum over the runs, in ascending order from +0, of this lane's four channels of one partial row */
+__device__ __forceinline__ void sum_runs(const float *first_run, uint64_t run_stride, uint32_t runs, float out[4])
+{
+	float4 total = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+	for (uint32_t run = 0; run < runs; run++) {
+		const float4 part = __ldcg(reinterpret_cast<const float4 *>(first_run + run * run_stride));
+		total.x = __fadd_rn(total.x, part.x);
+		total.y = __fadd_rn(total.y, part.y);
+		total.z = __fadd_rn(total.z, part.z);
+		total.w = __fadd_rn(total.w, part.w);
+	}
+	out[0] = total.x, out[1] = total.y, out[2] = total.z, out[3] = total.w;
+}
+
+/* The activation of a job's rows for one group of 128 inner channels, a warp a row, by the CTA that completed the
+ * group's gate and up products: gate_first / up_first: run 0 of the FP32 partial rows [pair][inner] of each, the
+ * further runs run_stride floats apart. Writes the bfloat16 hidden values and the FP16 down operands (behind the
+ * gate/up operands, which other CTAs of the launch still read). All 128 threads call. */
+template <uint32_t BX2>
+__device__ __forceinline__ void exl3_gate_up_epilogue(const struct exl3_moe_record &moe, unsigned char *arena,
+						      const struct expert_job_record *job, uint32_t group,
+						      const float *gate_first, const float *up_first, uint64_t run_stride,
+						      uint32_t gate_runs, uint32_t up_runs)
+{
+	const struct exl3_expert_record &record = moe.base;
+	const uint32_t lane = threadIdx.x % EXL3_WARP, warp = threadIdx.x / EXL3_WARP;
+	const uint32_t H = record.input_size, I = record.inner_size, pairs = record.pair_count;
+	const uint32_t channel = group * EXL3_TRANSFORM + lane * 4u;
+	const uint64_t codes = exl3_code_bytes(H, I, BX2);
+	float gate_scale[4], up_scale[4], down_scale[4];
+	load_half4(reinterpret_cast<const __half *>(arena + job->gate_offset + codes) + H + channel, gate_scale);
+	load_half4(reinterpret_cast<const __half *>(arena + job->up_offset + codes) + H + channel, up_scale);
+	load_half4(reinterpret_cast<const __half *>(arena + job->down_offset + exl3_code_bytes(I, H, BX2)) + channel,
+		   down_scale);
+	for (uint32_t column = warp; column < job->row_count; column += EXL3_PRODUCT_WARPS) {
+		const uint64_t at = (uint64_t)job->pair_index[column] * I + channel;
+		float gate[4], up[4];
+		sum_runs(gate_first + at, run_stride, gate_runs, gate);
+		sum_runs(up_first + at, run_stride, up_runs, up);
+		hadamard128_warp(gate, lane);
+		hadamard128_warp(up, lane);
+		float hidden[4];
+		exl3_swiglu4(gate, up, gate_scale, up_scale, record.activation_limit, hidden);
+		const __nv_bfloat162 low = __halves2bfloat162(__float2bfloat16_rn(hidden[0]), __float2bfloat16_rn(hidden[1]));
+		const __nv_bfloat162 high = __halves2bfloat162(__float2bfloat16_rn(hidden[2]), __float2bfloat16_rn(hidden[3]));
+		uint2 stored;
+		stored.x = *reinterpret_cast<const uint32_t *>(&low);
+		stored.y = *reinterpret_cast<const uint32_t *>(&high);
+		*reinterpret_cast<uint2 *>(reinterpret_cast<__nv_bfloat16 *>(arena + record.hidden_offset) + at) = stored;
+		float fed[4];
+#pragma unroll
+		for (uint32_t i = 0; i < 4; i++)
+			fed[i] = __fmul_rn(hidden[i], down_scale[i]);
+		hadamard128_warp(fed, lane);
+#pragma unroll
+		for (uint32_t i = 0; i < 4; i++)
+			fed[i] = __fmul_rn(fed[i], EXL3_NORMALIZATION);
+		store_half4(reinterpret_cast<__half *>(arena + record.operands_offset) + (uint64_t)EXL3_PROJECTIONS * pairs * H +
+				    at,
+			    fed);
+	}
+}
+
+/* The finish of a job's rows for one group of 128 outputs by the CTA that completed the group's down products:
+ * first: run 0 of the FP32 partial rows [pair][input_size]; writes the pair outputs (transform, scale, route
+ * weight) at output_offset. All 128 threads call. */
+template <uint32_t BX2>
+__device__ __forceinline__ void exl3_down_epilogue(const struct exl3_moe_record &moe, unsigned char *arena,
+						   const struct expert_job_record *job, uint32_t group, const float *first,
+						   uint64_t run_stride, uint32_t runs)
+{
+	const struct exl3_expert_record &record = moe.base;
+	const uint32_t lane = threadIdx.x % EXL3_WARP, warp = threadIdx.x / EXL3_WARP;
+	const uint32_t H = record.input_size, I = record.inner_size;
+	const uint32_t channel = group * EXL3_TRANSFORM + lane * 4u;
+	float scale[4];
+	load_half4(reinterpret_cast<const __half *>(arena + job->down_offset + exl3_code_bytes(I, H, BX2)) + I + channel,
+		   scale);
+	for (uint32_t column = warp; column < job->row_count; column += EXL3_PRODUCT_WARPS) {
+		const uint64_t at = (uint64_t)job->pair_index[column] * H + channel;
+		float v[4];
+		sum_runs(first + at, run_stride, runs, v);
+		hadamard128_warp(v, lane);
+		const float weight = job->route_weight[column];
+#pragma unroll
+		for (uint32_t i = 0; i < 4; i++)
+			v[i] = __fmul_rn(__fmul_rn(__fmul_rn(v[i], EXL3_NORMALIZATION), scale[i]), weight);
+		*reinterpret_cast<float4 *>(reinterpret_cast<float *>(arena + record.output_offset) + at) =
+			make_float4(v[0], v[1], v[2], v[3]);
+	}
+}
+
+#endif

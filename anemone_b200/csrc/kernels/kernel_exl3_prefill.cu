@@ -74,6 +74,7 @@ extern "C" __global__ void __launch_bounds__(ROUTER_B200_THREADS)
 	if (row >= live)
 		return;
 	router_row(reinterpret_cast<const float *>(arena + record.scores_offset) + (uint64_t)row * record.expert_count,
+		   record.bias_offset != 0 ? reinterpret_cast<const float *>(arena + record.bias_offset) : nullptr,
 		   record.expert_count, record.picks, record.scoring, record.route_scale, lane, chosen[warp], weight[warp],
 		   reinterpret_cast<uint32_t *>(arena + record.picks_offset) + (uint64_t)row * record.picks,
 		   reinterpret_cast<float *>(arena + record.weights_offset) + (uint64_t)row * record.picks);

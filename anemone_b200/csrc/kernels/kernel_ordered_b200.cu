@@ -54,7 +54,12 @@ extern "C" __global__ void __launch_bounds__(128)
 	const uint64_t previous = *reinterpret_cast<const uint64_t *>(ready_line + ORDERED_LOCAL_PREVIOUS_OFFSET);
 	bool alive = true;
 	if (previous != 0 && previous < sequence)
-		alive = ordered_wait_all(collective, arena, ORDERED_DONE_PHASE, sequence, previous, false, nullptr, &verdict);
+		alive = ordered_wait_all(collective, arena, ORDERED_DONE_PHASE, sequence, previous, false,
+					 arena + arguments.status_offset, &verdict);
+	/* a block whose wait ran out writes no rows: the grid must then not publish them */
+	unsigned int *const gave_up = reinterpret_cast<unsigned int *>(ready_line + ORDERED_LOCAL_GAVE_UP_OFFSET);
+	if (!alive && threadIdx.x == 0)
+		atomicExch(gave_up, 1u);
 	/* a block takes rows blockIdx.y, blockIdx.y + gridDim.y, ...: the grid stays small for many rows, because every
 	 * block counts itself on one counter at the end */
 	const uint32_t live_rows = min(step.row_count, collective.element_count / arguments.width);
@@ -76,6 +81,9 @@ extern "C" __global__ void __launch_bounds__(128)
 		}
 	}
 	if (last_block_of_grid(ready_line, &last) && threadIdx.x == 0) {
+		/* some block gave up: READY stays unpublished, the peers' own READY waits run out and say so */
+		if (atomicExch(gave_up, 0u) != 0u)
+			return;
 		*reinterpret_cast<uint64_t *>(ready_line + ORDERED_LOCAL_PREVIOUS_OFFSET) = sequence;
 		__threadfence_system();
 		signal_store(ready_line, sequence);
@@ -157,19 +165,108 @@ extern "C" __global__ void __launch_bounds__(ORDERED_COLLECTIVE_THREADS)
 	 * block first publishes that this rank's run of the result is in every rank's memory, and waits for every
 	 * rank's run to be in this rank's. */
 	unsigned char *const done_line = mine + ORDERED_DONE_PHASE * ORDERED_COLLECTIVE_LINE_BYTES;
+	unsigned int *const gave_up = reinterpret_cast<unsigned int *>(done_line + ORDERED_LOCAL_GAVE_UP_OFFSET);
+	if (owner_runs && !alive && threadIdx.x == 0)
+		atomicExch(gave_up, 1u); /* this block stored nothing of the rank's run */
 	if (last_block_of_grid(done_line, &last)) {
 		if (owner_runs) {
-			if (alive && threadIdx.x == 0) { /* a rank that gave up leaves its peers to their own deadlines */
+			/* REDUCED says the rank's WHOLE run is in every rank's result: only if every block of the grid was
+			 * alive */
+			if (threadIdx.x == 0)
+				verdict = atomicExch(gave_up, 0u) == 0u ? 1u : 0u;
+			__syncthreads();
+			const bool whole = verdict != 0u;
+			__syncthreads();
+			if (whole && threadIdx.x == 0) { /* a rank that gave up leaves its peers to their own deadlines */
 				__threadfence_system();
 				signal_store(mine + ORDERED_REDUCED_PHASE * ORDERED_COLLECTIVE_LINE_BYTES, sequence);
 			}
-			if (alive)
+			if (whole)
 				(void)ordered_wait_all(collective, arena, ORDERED_REDUCED_PHASE, sequence, sequence, true, status,
 						       &verdict);
 		}
 		if (threadIdx.x == 0)
 			signal_store(done_line, sequence);
 	}
+}
+
+/* The reduction of the decode step's four launches (struct exl3_layer_route_record explains the slot): the ranks'
+ * READY words arrive in this rank's OWN memory (each rank stores its word into every rank's slot), so the wait polls
+ * locally and one trip over NVLink remains: the peer loads of the rows. Then the adds in rank order from +0, one
+ * rounding to bfloat16, and this rank's DONE word into every rank's slot, whatever happened, so that no peer is held
+ * at its next refill of the slot. grid (up to ORDERED_B200_MAXIMUM_BLOCKS) x 256. */
+extern "C" __global__ void __launch_bounds__(ORDERED_COLLECTIVE_THREADS)
+	ordered_reduce_flags(struct ordered_reduce_bf16_arguments arguments, unsigned char *arena)
+{
+	__shared__ uint32_t verdict, last;
+	const struct ordered_collective_arguments &collective = arguments.collective;
+	const struct step_block step = *reinterpret_cast<const struct step_block *>(arena + collective.step_offset);
+	const uint64_t sequence = step.sequence;
+	if (sequence == 0 || collective.rank_count == 0 || collective.rank_count > ORDERED_COLLECTIVE_MAXIMUM_RANKS)
+		return;
+	unsigned char *const status = arena + arguments.status_offset;
+	unsigned char *const mine = ordered_slot(collective, arena, collective.rank, sequence);
+	if (threadIdx.x == 0)
+		verdict = 1u;
+	__syncthreads();
+	if (threadIdx.x < collective.rank_count) {
+		const unsigned char *const line = mine + (EXL3_LAYER_READY_LINE + threadIdx.x) * ORDERED_COLLECTIVE_LINE_BYTES;
+		const long long begin = clock64();
+		for (;;) {
+			const uint64_t seen = signal_load(line);
+			if (seen == sequence)
+				break;
+			if (seen > sequence) {
+				ordered_status_set(status, ORDERED_STATUS_BAD_SEQUENCE, ORDERED_READY_PHASE, threadIdx.x);
+				atomicExch(&verdict, 0u);
+				break;
+			}
+			if ((uint64_t)(clock64() - begin) > collective.deadline_cycles) {
+				ordered_status_set(status, ORDERED_STATUS_TIMED_OUT, ORDERED_READY_PHASE, threadIdx.x);
+				atomicExch(&verdict, 0u);
+				break;
+			}
+			__nanosleep(40);
+		}
+	}
+	__syncthreads();
+	if (verdict != 0u) {
+		const uint32_t live = min(step.row_count * arguments.width, collective.element_count);
+		const uint32_t vectors = live / 4u;
+		const float *inputs[ORDERED_COLLECTIVE_MAXIMUM_RANKS];
+#pragma unroll
+		for (uint32_t rank = 0; rank < ORDERED_COLLECTIVE_MAXIMUM_RANKS; rank++)
+			inputs[rank] = rank < collective.rank_count ?
+					       reinterpret_cast<const float *>(ordered_slot(collective, arena, rank, sequence) +
+									       collective.input_offset) :
+					       nullptr;
+		uint2 *const own = reinterpret_cast<uint2 *>(arena + collective.output_offset);
+		for (uint32_t vector = blockIdx.x * blockDim.x + threadIdx.x; vector < vectors;
+		     vector += gridDim.x * blockDim.x) {
+			float4 values[ORDERED_COLLECTIVE_MAXIMUM_RANKS];
+#pragma unroll
+			for (uint32_t rank = 0; rank < ORDERED_COLLECTIVE_MAXIMUM_RANKS; rank++)
+				if (rank < collective.rank_count)
+					values[rank] = ordered_load4(inputs[rank] + 4u * (uint64_t)vector);
+			float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+			for (uint32_t rank = 0; rank < ORDERED_COLLECTIVE_MAXIMUM_RANKS; rank++)
+				if (rank < collective.rank_count) {
+					sum.x = __fadd_rn(sum.x, values[rank].x);
+					sum.y = __fadd_rn(sum.y, values[rank].y);
+					sum.z = __fadd_rn(sum.z, values[rank].z);
+					sum.w = __fadd_rn(sum.w, values[rank].w);
+				}
+			own[vector] = make_uint2(bfloat16_bits(sum.x) | bfloat16_bits(sum.y) << 16,
+						 bfloat16_bits(sum.z) | bfloat16_bits(sum.w) << 16);
+		}
+	}
+	/* this rank has read (or given up on) every rank's rows of this step */
+	if (last_block_of_grid(mine + EXL3_LAYER_LOCAL_LINE * ORDERED_COLLECTIVE_LINE_BYTES, &last) &&
+	    threadIdx.x < collective.rank_count)
+		signal_store(ordered_slot(collective, arena, threadIdx.x, sequence) +
+				     (EXL3_LAYER_DONE_LINE + collective.rank) * ORDERED_COLLECTIVE_LINE_BYTES,
+			     sequence);
 }
 
 extern "C" __global__ void __launch_bounds__(ORDERED_COLLECTIVE_THREADS)

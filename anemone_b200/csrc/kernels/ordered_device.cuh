@@ -21,6 +21,7 @@
 #define ORDERED_DONE_PHASE 2u
 #define ORDERED_LOCAL_COUNTER_OFFSET 64u /* inside a line: a counter only the owner's own CTAs touch */
 #define ORDERED_LOCAL_PREVIOUS_OFFSET 72u /* inside the READY line: the sequence of the slot's previous use */
+#define ORDERED_LOCAL_GAVE_UP_OFFSET 80u /* inside a line: set by a block of the owner's grid whose wait ran out */
 
 __device__ __forceinline__ void signal_store(unsigned char *line, uint64_t sequence)
 {

@@ -3,7 +3,9 @@
 Host-side mirror of how the reference's model program uses the path (source/model_v41_program.c:4227-4531, 2618-2770):
 at load, matrices are placed in the arena, every launch is prepared by the library's preparers and captured into one
 graph; per step the caller writes the step block, the tokens and the router scores, runs the graph and reads the
-bfloat16 result. Launches of one step, all from libanemone_b200.so:
+bfloat16 result. Launches of one step, all from libanemone_b200.so, in the default form ("fused", exl3_layer_prepare):
+    exl3_layer_route_input -> exl3_layer_gate_up -> exl3_layer_down_publish -> ordered_reduce_flags
+and in the forms kept for callers of the separate preparers ("pull": six launches, "push": five):
     router_select_b200 -> exl3_moe_input -> exl3_moe_gate_up -> exl3_moe_down -> ordered_row_sum_publish
     -> ordered_reduce_bf16
 Tensor parallelism is by intermediate columns: this rank holds columns [begin, begin + inner_local) of every expert's
@@ -35,6 +37,7 @@ class MoeConfig:
     scoring: int = 0  # ROUTER_SCORING_SIGMOID
     route_scale: float = 1.0
     deadline_cycles: int = 2_000_000_000  # about a second of device clock
+    bias: bool = False  # a per-expert selection bias (FP32 [experts]) is added to the affinities for the choice
 
     @property
     def pairs_per_row(self):
@@ -66,7 +69,7 @@ def local_matrices(gate, up, down, config, width, rank_count, rank):
 class MoeLayout:
     """Byte offsets of everything one rank keeps in its arena. Identical on every rank of a group."""
 
-    def __init__(self, config, widths, rank_count, rank, pool_entries=0, reduce_form="pull"):
+    def __init__(self, config, widths, rank_count, rank, pool_entries=0, reduce_form="fused"):
         self.config, self.rank_count, self.rank = config, rank_count, rank
         self.pool_entries = pool_entries
         self.reduce_form = reduce_form
@@ -89,7 +92,10 @@ class MoeLayout:
         self.cursor = layout.take(16)
         self.pool = layout.take(self.pool_stride * pool_entries) if pool_entries else 0
         # the reduction's region: two parity slots of signal lines and this rank's FP32 partial rows
-        if reduce_form == "pull":  # ordered_row_sum_publish + ordered_reduce_bf16: peers read this rank's rows
+        if reduce_form == "fused":  # exl3_layer_prepare: READY and DONE words arrive in the reader's own memory
+            self.slot_input = R.EXL3_LAYER_SIGNAL_BYTES
+            self.parity_stride = api.align(self.slot_input + rows * H * 4, LINE)
+        elif reduce_form == "pull":  # ordered_row_sum_publish + ordered_reduce_bf16: peers read this rank's rows
             self.slot_input = SIGNAL_BYTES
             self.parity_stride = api.align(SIGNAL_BYTES + rows * H * 4, LINE)
         else:  # ordered_rows_push: one launch; every rank stores its rows into an inbox of every rank's slot
@@ -104,7 +110,8 @@ class MoeLayout:
         self.jobs = layout.take(self.job_capacity * 96)
         self.expert_table = layout.take(c.total_experts * 24)
         self.widths = layout.take(c.total_experts * 4)
-        sizes = api.moe_sizes(pairs, self.job_capacity, H, I)
+        self.bias = layout.take(c.experts * 4) if c.bias else 0
+        sizes = (api.layer_sizes if reduce_form == "fused" else api.moe_sizes)(pairs, self.job_capacity, H, I)
         self.operands = layout.take(sizes.operand_bytes)
         self.products = layout.take(max(sizes.product_bytes, pairs * H * 8))
         self.counters = layout.take(sizes.counter_bytes)
@@ -121,11 +128,14 @@ class MoeLayout:
 
 
 class MoeLayer:
-    def __init__(self, card, config, widths, matrices, rank=0, rank_count=1, pool_entries=0, reduce_form="pull"):
+    def __init__(self, card, config, widths, matrices, rank=0, rank_count=1, pool_entries=0, reduce_form="fused",
+                 bias=None, product_ctas=0):
         """matrices: iterable over experts (routed, then shared) of this rank's (gate, up, down) stored bytes.
-        reduce_form: "pull" (two launches, the ranks read each other's rows: the faster of the two over NVLink, where a
-        system-scope fence behind remote stores costs more than a second launch) or "push" (one launch, the ranks
-        store their rows into each other's inboxes); the same sums and bits."""
+        reduce_form: "fused" (the step in four launches: the router with the input transform, products cut evenly
+        over the card, row sums and READY behind the down products, flags that arrive in the reader's memory),
+        "pull" (router, four expert launches, two reduction launches: the ranks read each other's rows) or "push"
+        (one reduction launch: the ranks store their rows into each other's inboxes); the same sums of the ranks'
+        rows and the same bits given those rows. bias: FP32 [experts] for a config with bias=True."""
         self.card, self.config = card, config
         self.widths = np.asarray(widths, dtype=np.uint32)
         self.layout = L = MoeLayout(config, self.widths, rank_count, rank, pool_entries, reduce_form)
@@ -146,6 +156,9 @@ class MoeLayer:
         card.fill(L.step, 0, 256)
         card.fill(L.region, 0, 2 * L.parity_stride)
         card.fill(L.counters, 0, L.counter_bytes)
+        if config.bias:
+            card.upload(L.bias, np.ascontiguousarray(bias, dtype=np.float32))
+        self.product_ctas = product_ctas
         peers = (R.OrderedPeer * rank_count)()
         for peer in range(rank_count):
             peers[peer].region_offset = L.region
@@ -167,10 +180,41 @@ class MoeLayer:
             else:
                 self.card.ipc_connect(handle, 0, self.layout.peer_table + 32 * peer)
 
+    def _prepare_fused(self):
+        c, L, card, lib = self.config, self.layout, self.card, api.library()
+        description = R.Exl3LayerDescription()
+        route = description.route
+        route.moe.base = R.Exl3Expert(L.jobs, L.tokens, L.operands, L.products, L.hidden, L.products, c.hidden,
+                                      L.inner_local, L.pairs, c.pairs_per_row, L.job_capacity,
+                                      R.EXL3_WIDTH_PER_EXPERT, c.activation_limit, 0)
+        route.moe.widths_offset, route.moe.row_output_offset = L.widths, L.row_output
+        route.moe.counters_offset, route.moe.expert_count = L.counters, c.total_experts
+        route.scores_offset, route.expert_table_offset, route.picks_offset = L.scores, L.expert_table, L.picks
+        route.weights_offset, route.bias_offset, route.step_offset = L.weights, L.bias, L.step
+        route.routed_count, route.shared_count, route.picks, route.row_capacity = (c.experts, c.shared, c.picks,
+                                                                                     c.row_capacity)
+        route.scoring, route.route_scale = c.scoring, c.route_scale
+        description.publish = R.Exl3LayerPublish(L.peer_table, L.region, L.slot_input, L.status, L.step,
+                                                 L.parity_stride, c.deadline_cycles, self.rank_count, self.rank,
+                                                 c.row_capacity, 0)
+        description.result_offset, description.arena_byte_count = L.result, card.arena_bytes
+        description.product_ctas = self.product_ctas
+        launches = (R.KernelLaunch * 4)()
+        api.check(lib.exl3_layer_prepare(C.byref(description), card.ops_pointer, card.handle, launches),
+                  "exl3_layer_prepare")
+        return list(launches)
+
     def _prepare(self):
         c, L, card, lib = self.config, self.layout, self.card, api.library()
+        # which launches stand before the gate/up products, and which launch they are (for callers that time them)
+        self.gate_up_index = 1 if L.reduce_form == "fused" else 2
+        self.gate_up_kernel = "exl3_layer_gate_up" if L.reduce_form == "fused" else "exl3_moe_gate_up"
+        if L.reduce_form == "fused":
+            self.launches = self._prepare_fused()
+            self._capture()
+            return
         router = R.RouterSelectB200(L.scores, L.expert_table, L.picks, L.weights, L.jobs, L.step, c.experts, c.shared,
-                                    c.picks, c.row_capacity, L.job_capacity, c.scoring, c.route_scale, 0)
+                                    c.picks, c.row_capacity, L.job_capacity, c.scoring, c.route_scale, 0, L.bias)
         lib.router_select_b200_prepare.argtypes = [C.POINTER(R.RouterSelectB200), C.c_uint64,
                                                    C.POINTER(api.BackendOperations), C.c_void_p,
                                                    C.POINTER(R.KernelLaunch)]
@@ -215,6 +259,10 @@ class MoeLayer:
                       "ordered_rows_push_prepare")
         # the fused chain's own row sum is replaced by the reduction's, which sums straight into the exchange slot
         self.launches = [router_launch, moe_launches[0], moe_launches[1], moe_launches[2]] + list(reduce_launches)
+        self._capture()
+
+    def _capture(self):
+        c, L, card, lib = self.config, self.layout, self.card, api.library()
         self.graph = card.graph(self.launches)
         self.resident_graph = None
         if L.pool_entries:

@@ -49,6 +49,34 @@ class Exl3Moe(C.Structure):
                 ("counters_offset", C.c_uint64), ("expert_count", C.c_uint32), ("reserved_zero", C.c_uint32)]
 
 
+class Exl3LayerRoute(C.Structure):
+    _fields_ = [("moe", Exl3Moe), ("scores_offset", C.c_uint64), ("expert_table_offset", C.c_uint64),
+                ("picks_offset", C.c_uint64), ("weights_offset", C.c_uint64), ("bias_offset", C.c_uint64),
+                ("step_offset", C.c_uint64), ("routed_count", C.c_uint32), ("shared_count", C.c_uint32),
+                ("picks", C.c_uint32), ("row_capacity", C.c_uint32), ("scoring", C.c_uint32),
+                ("route_scale", C.c_float)]
+
+
+class Exl3LayerPublish(C.Structure):
+    _fields_ = [("peer_table_offset", C.c_uint64), ("region_offset", C.c_uint64), ("input_offset", C.c_uint64),
+                ("status_offset", C.c_uint64), ("step_offset", C.c_uint64), ("parity_stride", C.c_uint64),
+                ("deadline_cycles", C.c_uint64), ("rank_count", C.c_uint32), ("rank", C.c_uint32),
+                ("row_capacity", C.c_uint32), ("reserved_zero", C.c_uint32)]
+
+
+class Exl3LayerDown(C.Structure):
+    _fields_ = [("moe", Exl3Moe), ("publish", Exl3LayerPublish)]
+
+
+class Exl3LayerDescription(C.Structure):
+    _fields_ = [("route", Exl3LayerRoute), ("publish", Exl3LayerPublish), ("result_offset", C.c_uint64),
+                ("arena_byte_count", C.c_uint64), ("product_ctas", C.c_uint32), ("reserved_zero", C.c_uint32)]
+
+
+EXL3_LAYER_SIGNAL_BYTES = 33 * 128
+EXL3_LAYER_READY_LINE, EXL3_LAYER_DONE_LINE, EXL3_LAYER_LOCAL_LINE = 0, 16, 32
+
+
 class Exl3MoeSizes(C.Structure):
     _fields_ = [("operand_bytes", C.c_uint64), ("product_bytes", C.c_uint64), ("counter_bytes", C.c_uint64),
                 ("gate_up_splits", C.c_uint32), ("down_splits", C.c_uint32)]
@@ -62,7 +90,7 @@ class Exl3Prefill(C.Structure):
                 ("inner_size", C.c_uint32), ("shared_inner_size", C.c_uint32), ("expert_count", C.c_uint32),
                 ("local_first", C.c_uint32), ("local_count", C.c_uint32), ("shared_count", C.c_uint32),
                 ("picks", C.c_uint32), ("row_capacity", C.c_uint32), ("scoring", C.c_uint32),
-                ("route_scale", C.c_float), ("activation_limit", C.c_float), ("reserved_zero", C.c_uint32 * 2)]
+                ("route_scale", C.c_float), ("activation_limit", C.c_float), ("bias_offset", C.c_uint64)]
 
 
 class Exl3PrefillTile(C.Structure):
@@ -106,7 +134,7 @@ class OrderedReduceBf16(C.Structure):
 
 class OrderedRowSumPublish(C.Structure):
     _fields_ = [("collective", OrderedCollective), ("pair_output_offset", C.c_uint64), ("width", C.c_uint32),
-                ("pairs_per_row", C.c_uint32)]
+                ("pairs_per_row", C.c_uint32), ("status_offset", C.c_uint64)]
 
 
 ORDERED_PUSH_FP32, ORDERED_PUSH_BF16 = 0, 1
@@ -164,7 +192,7 @@ class RouterSelectB200(C.Structure):
                 ("weights_offset", C.c_uint64), ("jobs_offset", C.c_uint64), ("step_offset", C.c_uint64),
                 ("expert_count", C.c_uint32), ("shared_count", C.c_uint32), ("picks", C.c_uint32),
                 ("row_capacity", C.c_uint32), ("job_capacity", C.c_uint32), ("scoring", C.c_uint32),
-                ("route_scale", C.c_float), ("reserved_zero", C.c_uint32)]
+                ("route_scale", C.c_float), ("reserved_zero", C.c_uint32), ("bias_offset", C.c_uint64)]
 
 
 class StepInputSelect(C.Structure):
@@ -277,9 +305,9 @@ class OrderedCollectiveKernels(C.Structure):
 
 
 for _record, _bytes in ((Exl3Reconstruct, 32), (Exl3Expert, 80), (ExpertJob, 96), (ExpertRowSum, 24),
-                        (Exl3ShardActivation, 96), (Exl3Moe, 112), (TrunkLinearQuantized, 72), (TrunkHidden, 32), (TrunkRowsAdd, 24), (Exl3Prefill, 136), (Exl3PrefillTile, 16), (Exl3PrefillEntry, 8), (Exl3PrefillParts, 56), (StepBlock, 16), (OrderedPeer, 32),
-                        (OrderedCollective, 80), (OrderedReduceBf16, 96), (OrderedRowSumPublish, 96), (OrderedPush, 96),
+                        (Exl3ShardActivation, 96), (Exl3Moe, 112), (Exl3LayerRoute, 184), (Exl3LayerPublish, 72), (Exl3LayerDown, 184), (TrunkLinearQuantized, 72), (TrunkHidden, 32), (TrunkRowsAdd, 24), (Exl3Prefill, 136), (Exl3PrefillTile, 16), (Exl3PrefillEntry, 8), (Exl3PrefillParts, 56), (StepBlock, 16), (OrderedPeer, 32),
+                        (OrderedCollective, 80), (OrderedReduceBf16, 96), (OrderedRowSumPublish, 104), (OrderedPush, 96),
                         (TpExchange, 112), (OrderedRowsPush, 112), (Tp2Join, 80),
-                        (RouterSelectB200, 80), (StepInputSelect, 40), (ActivationQuantize, 40), (ExpertGateUp, 64), (ExpertDown, 56),
+                        (RouterSelectB200, 88), (StepInputSelect, 40), (ActivationQuantize, 40), (ExpertGateUp, 64), (ExpertDown, 56),
                         (KernelLaunch, 232), (CardDescription, 168)):
     assert C.sizeof(_record) == _bytes, (_record.__name__, C.sizeof(_record), _bytes)

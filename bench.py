@@ -16,7 +16,7 @@ One JSON line on rank 0:
             the ranks meet on the device, so that the events hold the K steps and no rank's wait for a late one;
   e2e       the same through the public call with host buffers: per step the host -> device copy of the step's inputs
             from pinned memory, the layer's graph, the device -> host copy of the bfloat16 result, and the wait for it;
-  roofline  the dominant kernel (exl3_moe_gate_up) timed alone, launch by launch, with CUDA events, against the
+  roofline  the dominant kernel (exl3_layer_gate_up) timed alone, launch by launch, with CUDA events, against the
             measured HBM copy bandwidth of MEASURED_PEAKS.json;
   cpu_baseline  the CPU oracle (OpenMP, all host cores) on a bounded sample of the same step, scaled to the step.
 Further objects of the same line, each with its own value, e2e and roofline where they apply:
@@ -45,8 +45,9 @@ sys.path.insert(0, ROOT)
 
 METRIC = "MoE expert-layer tok/s (decode M=8, prefill M=4096) at 1/2/4/8 B200"
 SEED = 20261125
-# dram bytes moved per algorithmic byte by exl3_moe_gate_up, from the ncu capture summarised in
-# profiles/exl3_moe_gate_up_64experts_m8.md (dram__bytes_read.sum + dram__bytes_write.sum over the launch's bytes)
+# dram bytes moved per algorithmic byte by the gate/up product kernel: dram__bytes_read.sum + dram__bytes_write.sum of
+# one ncu capture of a 64-expert, 8-row launch over that launch's algorithmic bytes (the capture is too large for the
+# full workload; traffic grows in proportion to the experts streamed)
 GATE_UP_TRAFFIC_RATIO = 1.03
 
 
@@ -271,62 +272,74 @@ def run_prefill(args, api, base, widths, draw, rank, world, local_rank, dist, ba
                              "local expert's matrices"}}
 
 
-def cpu_sample(config, widths, draw, tokens, scores, rank_count, job_limit):
-    """The CPU oracle on the first job_limit jobs of a step, scaled by weight bytes to the whole step."""
+def host_threads():
+    """The threads the CPU legs use: every core this process may run on (a launcher's OMP_NUM_THREADS is not obeyed:
+    the thread count is handed to the oracle explicitly)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def cpu_step(config, widths, cached, tokens, scores, threads):
+    """Seconds of ONE whole layer call on the CPU oracle (every expert job of the step, all columns: the CPU has no
+    ranks), matrices drawn before the clock starts."""
     from oracle import binding, moe_reference
-    from anemone_b200 import synthetic
-    from anemone_b200.moe import rank_columns
     oracle = binding.load_oracle()
     experts, weights = moe_reference.route(oracle, config, scores)
-    cores = os.cpu_count() or 1
-    inner_local = rank_columns(config.inner, rank_count, 0)[1]
+    for expert in sorted(set(experts.reshape(-1).tolist())) + list(range(config.experts, config.total_experts)):
+        cached(expert)
+    begin = time.perf_counter()
+    experts, weights = moe_reference.route(oracle, config, scores)
+    _, _, kept = moe_reference.rank_partial(oracle, config, widths, cached, tokens, experts, weights, 1, 0, threads)
+    return time.perf_counter() - begin, kept
 
-    def job_bytes(jobs, count):
-        return sum(3 * config.hidden * inner_local // 16 * synthetic.bits_x2(int(widths[jobs[i].expert]))
-                   for i in range(count))
-    # the timed call: matrices are drawn before the clock starts
+
+def matrix_cache(draw):
     cache = {}
 
     def cached(expert):
         if expert not in cache:
             cache[expert] = draw(expert)
         return cache[expert]
-    _, jobs, kept = moe_reference.rank_partial(oracle, config, widths, cached, tokens, experts, weights, rank_count, 0,
-                                               0, job_limit)  # also the warm-up
-    begin = time.perf_counter()
-    _, jobs, kept = moe_reference.rank_partial(oracle, config, widths, cached, tokens, experts, weights, rank_count, 0,
-                                               0, job_limit)
-    seconds = time.perf_counter() - begin
-    import ctypes as C
-    from anemone_b200 import records as R
-    from oracle.binding import f32p, ptr, u32p, u64p
-    capacity = tokens.shape[0] * config.picks + config.shared * ((tokens.shape[0] + 7) // 8)
-    every = (R.ExpertJob * capacity)()
-    table = np.zeros((config.total_experts, 3), dtype=np.uint64)
-    total = oracle.orc_router_jobs(ptr(np.ascontiguousarray(experts), u32p), ptr(np.ascontiguousarray(weights), f32p),
-                                   tokens.shape[0], config.picks, config.experts, config.shared, ptr(table, u64p),
-                                   capacity, C.byref(every))
-    scale = job_bytes(every, total) / max(1, job_bytes(jobs, kept))
-    step_seconds = seconds * scale
-    return {"value": tokens.shape[0] / step_seconds, "unit": "tok/s", "cores": cores, "kind": "port",
-            "sample": "%d of the step's %d expert jobs (rank 0 of %d) on the OpenMP CPU oracle, %.2f s, scaled by "
-                      "weight bytes x%.2f" % (kept, total, rank_count, seconds, scale)}, step_seconds
+    return cached
+
+
+def cpu_baseline(config, widths, draw, steps, rows):
+    """The CPU oracle beside the GPU number: whole steps of the same workload on every host thread."""
+    threads = host_threads()
+    cached = matrix_cache(draw)
+    seconds, jobs = [], 0
+    for index, (tokens, scores) in enumerate(steps):
+        elapsed, jobs = cpu_step(config, widths, cached, tokens, scores, threads)
+        if index > 0 or len(steps) == 1:
+            seconds.append(elapsed)
+    mean = float(np.mean(seconds))
+    return {"value": rows / mean, "unit": "tok/s", "cores": threads, "kind": "port", "extrapolated": False,
+            "sample": "%d whole steps (the last of %d expert jobs) of the same workload on the OpenMP CPU oracle, "
+                      "%d threads, %.2f s a step; one more step first as warm-up" % (len(seconds), jobs, threads, mean)}
 
 
 def run_reference(args, config, widths, draw, rank, world):
-    """--impl reference: the CPU restatement of the reference's arithmetic, all host threads, bounded samples."""
+    """--impl reference: the CPU restatement of the reference's arithmetic, every host thread, WHOLE steps of the
+    whole layer (a CPU has no ranks: the value does not depend on the GPU count the arm is launched for)."""
     if rank != 0:
         return
+    threads = host_threads()
     steps = step_inputs(config, args.rows, args.warmup + args.steps)
-    times = []
-    info = None
+    cached = matrix_cache(draw)
+    times, jobs = [], 0
+    wall_begin = time.perf_counter()
     for index, (tokens, scores) in enumerate(steps):
-        info, seconds = cpu_sample(config, widths, draw, tokens, scores, world, job_limit=6)
+        seconds, jobs = cpu_step(config, widths, cached, tokens, scores, threads)
         if index >= args.warmup:
             times.append(seconds)
     ms = 1000.0 * float(np.mean(times))
     value = args.rows * 1000.0 / ms
-    info["value"] = value
+    info = {"value": value, "unit": "tok/s", "cores": threads, "kind": "port", "extrapolated": False,
+            "sample": "%d whole steps of the whole layer (about %d expert jobs a step), %d threads; drawing a step's "
+                      "matrices is outside its timed region (%.0f s of wall clock in all)" %
+                      (len(times), jobs, threads, time.perf_counter() - wall_begin)}
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
@@ -334,7 +347,48 @@ def run_reference(args, config, widths, draw, rank, world):
         "config": workload_config(args, config, world), "cpu_baseline": info,
         "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "the reference has no engine CPU path for this layer and no sm_100 kernel build; this arm times the "
-                "CPU restatement of its arithmetic (oracle/, pinned to its known-answer vectors) on the host cores"}))
+                "CPU restatement of its arithmetic (oracle/, pinned to its known-answer vectors and to its own host "
+                "code compiled from its sources) on the host cores"}))
+
+
+def checked_step(config, widths, draw, layer, step, rank, world, dist):
+    """One more step whose result is CHECKED: every rank's bfloat16 result against the rank-ordered FP32 sum of the rows
+    the ranks really published, rounded once, bit for bit (the CPU oracle's ordered reduction), and against the CPU
+    oracle's whole layer within the path's tolerance (max-abs 2e-2, cosine 0.9999). Rank 0 gathers and checks."""
+    from anemone_b200 import synthetic
+    tokens, scores = step
+    rows = tokens.shape[0]
+    got = layer.step(tokens, scores).reshape(-1)
+    L = layer.layout
+    slot = L.region + (layer.sequence & 1) * L.parity_stride + L.slot_input
+    published = layer.card.download(slot, rows * config.hidden * 4, np.float32)
+    picks = layer.card.download(L.picks, rows * config.picks * 4, np.uint32).reshape(rows, config.picks)
+    if dist is None:
+        everyone = [(published, got, picks)]
+    else:
+        everyone = [None] * world if rank == 0 else None
+        dist.gather_object((published, got, picks), everyone, dst=0)
+    if rank != 0:
+        return None
+    from oracle import binding, moe_reference
+    from oracle.binding import pointer_array, ptr, u16p
+    oracle = binding.load_oracle()
+    want = np.zeros(rows * config.hidden, dtype=np.uint16)
+    inputs = [np.ascontiguousarray(entry[0]) for entry in everyone]
+    oracle.orc_ordered_reduce_bf16(pointer_array(inputs), world, want.size, ptr(want, u16p))
+    bit_exact = all(np.array_equal(entry[1], want) for entry in everyone)
+    expected, _, experts, _ = moe_reference.layer(oracle, config, widths, matrix_cache(draw), tokens, scores, world,
+                                                  host_threads())
+    a = synthetic.from_bfloat16(got).astype(np.float64)
+    b = synthetic.from_bfloat16(expected.reshape(-1)).astype(np.float64)
+    worst = float(np.abs(a - b).max())
+    cosine = float(a @ b / (np.linalg.norm(a) * np.linalg.norm(b) + 1e-300))
+    picks_exact = all(np.array_equal(entry[2], experts) for entry in everyone)
+    return {"ok": bool(bit_exact and picks_exact and worst <= 2e-2 and cosine >= 0.9999),
+            "ordered_reduction_bit_exact_on_every_rank": bool(bit_exact), "router_picks_bit_exact": bool(picks_exact),
+            "layer_max_abs_vs_cpu_oracle": worst, "layer_cosine_vs_cpu_oracle": cosine, "ranks": world,
+            "what": "one more step after the timed regions: every rank's result against the oracle's rank-ordered "
+                    "sum of the FP32 rows the ranks published over NVLink, and against the oracle's whole layer"}
 
 
 def workload_config(args, config, world):
@@ -352,8 +406,13 @@ def run_reference_kernels(args, api, base, draw_k3, local_rank):
     """The reference's own EXL3 kernels on this card, beside this library's, on the same inputs: its retained chain
     and its fast form (source/kernel_exl3.cu, source/kernel_exl3_wide.cu), recompiled for sm_100a from its sources into
     oracle/_ref and launched through its own preparer. Its chain takes ONE stored width a record, so every expert is
-    K3 here (3 bits a weight; the headline workload's mix averages 3.1). Expert launches only: the router (this
-    library's, which writes the job table both read) and the reduction are outside the timed region."""
+    K3 here (3 bits a weight; the headline workload's mix averages 3.1). Two comparisons, each the mean of three
+    passes over the steps with the spread between the passes:
+      expert launches alone (input transform, products, activation, output transform, row sum; the job table written
+      before the clock starts): the reference's two chains and this library's launches of the separate preparers;
+      the step WITH its router: the reference's fast chain behind a router launch (up to its FP32 row sums), against
+      this library's four launches of the whole decode step (router and input transform; gate/up; down, row sums,
+      READY; the one-rank reduction to bfloat16, which the reference's side of this comparison does not have)."""
     from oracle import binding, reference_kernels
     if not reference_kernels.available():
         return {"unavailable": "oracle/_ref holds no reference kernel images (built where the reference tree is present)"}
@@ -362,11 +421,18 @@ def run_reference_kernels(args, api, base, draw_k3, local_rank):
     from anemone_b200.moe import MoeLayer, MoeLayout
     reference = binding.load_reference()
     widths = np.full(base.total_experts, 3, dtype=np.uint32)
-    layout = MoeLayout(base, widths, 1, 0)
+    layout = MoeLayout(base, widths, 1, 0, reduce_form="pull")
     card = api.Card(local_rank, layout.arena_bytes)
+    fused_layout = MoeLayout(base, widths, 1, 0, reduce_form="fused")
+    fused_card = api.Card(local_rank, fused_layout.arena_bytes)
+    passes = 3
     try:
-        layer = MoeLayer(card, base, widths, (draw_k3(expert) for expert in range(base.total_experts)))
+        layer = MoeLayer(card, base, widths, (draw_k3(expert) for expert in range(base.total_experts)),
+                         reduce_form="pull")
         layer.connect_local([layer])
+        fused = MoeLayer(fused_card, base, widths, (draw_k3(expert) for expert in range(base.total_experts)),
+                         reduce_form="fused")
+        fused.connect_local([fused])
         record = R.Exl3Expert(layout.jobs, layout.tokens, layout.operands, layout.products, layout.hidden,
                               layout.products, base.hidden, layout.inner_local, layout.pairs, base.pairs_per_row,
                               layout.job_capacity, 3, base.activation_limit, 0)
@@ -383,32 +449,57 @@ def run_reference_kernels(args, api, base, draw_k3, local_rank):
                   "bb_exl3_row_sum_prepare")
         for name in chains:
             chains[name].append(sum_launch)
+        routed = {"fast_with_router": (card, list(layer.launches[0:1]) + chains["fast"]),
+                  "ours_step_with_router": (fused_card, list(fused.launches))}
         steps = step_inputs(base, args.rows, 3 + args.steps)
-        elapsed = {name: 0.0 for name in chains}
+        elapsed = {name: [0.0] * passes for name in list(chains) + list(routed)}
         rows_of = {}
-        for index, (tokens, scores) in enumerate(steps):
-            layer.sequence += 1
-            layer.stage_step(0, layer.sequence, tokens, scores)
-            card.transfer_wait(card.upload_async(layout.step, 0, layout.step_input_bytes))
-            card.run(layer.launches[0:1])  # the router: the job table every chain reads
-            card.wait()
-            for name, launches in chains.items():
-                card.measure_begin()
-                card.run(launches)
-                card.measure_end()
-                us = card.measure_elapsed_us()
-                if index >= 3:
-                    elapsed[name] += us
-                rows_of[name] = card.download(layout.row_output, args.rows * base.hidden * 4, np.float32)
+        for repeat in range(passes):
+            for index, (tokens, scores) in enumerate(steps):
+                for each in (layer, fused):
+                    each.sequence += 1
+                    each.stage_step(0, each.sequence, tokens, scores)
+                    each.card.transfer_wait(each.card.upload_async(each.layout.step, 0, each.layout.step_input_bytes))
+                card.run(layer.launches[0:1])  # the router: the job table every chain reads
+                card.wait()
+                for name, launches in chains.items():
+                    card.measure_begin()
+                    card.run(launches)
+                    card.measure_end()
+                    us = card.measure_elapsed_us()
+                    if index >= 3:
+                        elapsed[name][repeat] += us
+                    if repeat == 0:
+                        rows_of[name] = card.download(layout.row_output, args.rows * base.hidden * 4, np.float32)
+                for name, (where, launches) in routed.items():
+                    where.measure_begin()
+                    where.run(launches)
+                    where.measure_end()
+                    us = where.measure_elapsed_us()
+                    if index >= 3:
+                        elapsed[name][repeat] += us
+                if repeat == 0:
+                    slot = (fused_layout.region + (fused.sequence & 1) * fused_layout.parity_stride +
+                            fused_layout.slot_input)
+                    rows_of["ours_step_with_router"] = fused_card.download(slot, args.rows * base.hidden * 4, np.float32)
         worst = float(max(np.abs(rows_of["ours"] - rows_of[name]).max() for name in ("retained", "fast")))
+        worst_fused = float(np.abs(rows_of["ours_step_with_router"] - rows_of["fast"]).max())
     finally:
         card.close()
-    out = {name + "_us_per_step": elapsed[name] / args.steps for name in elapsed}
-    out.update({"unit": "us of the expert launches of one decode step (input transform, products, activation, "
-                        "output transform, row sum), CUDA events", "rows": args.rows, "stored_width": 3,
+        fused_card.close()
+    out = {}
+    for name, totals in elapsed.items():
+        per_step = [total / args.steps for total in totals]
+        out[name + "_us_per_step"] = float(np.mean(per_step))
+        out[name + "_spread"] = float((max(per_step) - min(per_step)) / np.mean(per_step))
+    out.update({"unit": "us of one decode step's launches, CUDA events; mean of %d passes over %d steps, spread = "
+                        "(max - min) / mean of the passes" % (passes, args.steps), "rows": args.rows, "stored_width": 3,
                 "speedup_over_fast": out["fast_us_per_step"] / out["ours_us_per_step"],
                 "speedup_over_retained": out["retained_us_per_step"] / out["ours_us_per_step"],
+                "step_speedup_over_fast_with_router": out["fast_with_router_us_per_step"] /
+                                                      out["ours_step_with_router_us_per_step"],
                 "max_abs_difference_of_row_sums": worst,
+                "max_abs_difference_of_row_sums_step": worst_fused,
                 "kernels": "the reference's source/kernel_exl3.cu (retained) and source/kernel_exl3_wide.cu (fast), "
                            "recompiled for sm_100a, through its own exl3_experts_prepare / exl3_experts_fast_prepare"})
     return out
@@ -776,12 +867,16 @@ def main():
     layer.check_status()
     barrier()
 
+    # ---- parity of this very build on these very cards: one checked step at every N ----
+    parity = checked_step(config, widths, draw, layer, steps[args.warmup], rank, world, dist)
+    barrier()
+
     # ---- roofline: the dominant kernel alone, launch by launch ----
     roofline = None
     if rank == 0:
         peak, peak_source = measured_peaks()
-        gate_up = layer.launches[2:3]
-        prologue = layer.launches[0:2]
+        gate_up = layer.launches[layer.gate_up_index:layer.gate_up_index + 1]
+        prologue = layer.launches[0:layer.gate_up_index]
         elapsed_us, byte_total = 0.0, 0
         inner_local = layout.inner_local
         for index, (tokens, scores) in enumerate(steps[args.warmup:]):
@@ -800,7 +895,7 @@ def main():
             byte_total += sum(2 * synthetic.matrix_bytes(config.hidden, inner_local, int(widths[e])) for e in active)
             byte_total += 2 * pairs * config.hidden * 2 + pairs * inner_local * 4  # operands in, hidden + operands out
         achieved = byte_total / elapsed_us / 1000.0  # GB/s
-        roofline = {"kernel": "exl3_moe_gate_up", "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+        roofline = {"kernel": layer.gate_up_kernel, "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                     "frac": achieved / peak, "peak_source": peak_source,
                     "traffic": GATE_UP_TRAFFIC_RATIO * byte_total / args.steps,
                     "algorithmic_bytes_per_launch": byte_total / args.steps,
@@ -811,8 +906,7 @@ def main():
     # ---- the CPU oracle beside it (rank 0 at N = 1 only) ----
     cpu = None
     if rank == 0 and world == 1:
-        tokens, scores = steps[args.warmup]
-        cpu, _ = cpu_sample(config, widths, draw, tokens, scores, 1, job_limit=12)
+        cpu = cpu_baseline(config, widths, draw, steps[args.warmup:args.warmup + 4], args.rows)
     if rank == 0:
         line = {
             "metric": METRIC, "value": args.rows * 1000.0 / ms_per_step, "unit": "tok/s", "n_gpus": world,
@@ -822,6 +916,7 @@ def main():
             "e2e": {"value": args.rows * 1000.0 / e2e_ms, "unit": "tok/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": layout.step_input_bytes, "d2h_bytes_per_step": args.rows * config.hidden * 2},
             "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline,
+            "parity_checked": parity["ok"], "parity": parity,
         }
         line = dict(line)
         if cpu is not None:
@@ -856,6 +951,8 @@ def main():
         print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()
+    if rank == 0 and not line["parity_checked"]:
+        raise SystemExit("bench.py: the checked step differs from the CPU oracle: " + json.dumps(line["parity"]))
 
 
 if __name__ == "__main__":

@@ -217,6 +217,80 @@ struct step_block {
 };
 
 /* ------------------------------------------------------------------------------------------------------------
+ * B200 extension, kernel file "kernel_exl3_layer": one decode step (up to ROUTER_B200_MAXIMUM_ROWS rows) of a rank's
+ * whole expert layer in FOUR launches, made for the step's latency on one to eight ranks:
+ *   exl3_layer_route_input   grid (1 + T) x 256: every CTA chooses the live rows' experts itself (a warp a row, the
+ *                            router's arithmetic, so all agree); CTA 0 writes picks, weights and the job table
+ *                            (router_select_b200's bytes) and the live job count; the others transform the rows into
+ *                            the FP16 operands of every (pair, gate or up): no launch and no trip through memory
+ *                            stands between the router and the transform.
+ *   exl3_layer_gate_up       grid C x 128: the products of all live (job, gate or up, 128 outputs) items, as ONE
+ *                            sequence of K rounds cut in C equal runs (a CTA streams its run, which may cover the end
+ *                            of one item and the start of the next), so that every SM is busy to the end whatever
+ *                            the number of live experts and the rank's share of the columns; the CTA that completes
+ *                            a (job, 128 outputs) adds the runs' FP32 partial sums in ascending K order from +0 and
+ *                            applies the transform, SwiGLU and the down-side transform (exl3_moe_gate_up's epilogue).
+ *   exl3_layer_down_publish  the same for down; the CTA that completes a (job, 128 outputs) writes the pair outputs;
+ *                            the CTA that completes a 128-column group over ALL live jobs adds the rows' pairs in
+ *                            ascending slot order from +0 straight into this rank's rows of the reduction slot, and
+ *                            the CTA that completes the last group stores this rank's READY word into EVERY rank's
+ *                            slot (plain peer stores), so that nobody polls across NVLink.
+ *   ordered_reduce_flags     (kernel file "kernel_ordered_b200") waits for the READY words in its OWN memory, pulls
+ *                            the ranks' rows by peer loads, adds them in rank order from +0, rounds once to bfloat16,
+ *                            and stores its DONE word into every rank's slot.
+ * A slot of the reduction region in this form (two parity slots, parity_stride apart): 16 READY lines of 128 bytes
+ * (line s: a 64-bit sequence written only by rank s), 16 DONE lines likewise, one local line (a block counter at
+ * byte 64, the sequence of the slot's previous use at byte 72), then the FP32 rows at input_offset.
+ * The cut of a product depends on the live job count and the grid, not on the data: the same inputs give the same
+ * bits on every run. partial sums: FP32 [2][EXL3_LAYER_MAXIMUM_RUNS][pair_count][inner_size] for gate/up, reused as
+ * [EXL3_LAYER_MAXIMUM_RUNS][pair_count][input_size] for down (run 0 is also where the pair outputs go); counters:
+ * what struct exl3_moe_record asks for, then EXL3_LAYER_COUNTER_WORDS + input_size / 128 more uint32, zero at load.
+ * ---------------------------------------------------------------------------------------------------------- */
+#define EXL3_LAYER_KERNEL_FILE "kernel_exl3_layer"
+#define EXL3_LAYER_LAUNCHES 4u
+#define EXL3_LAYER_MAXIMUM_RUNS 8u /* runs of one item at most: a run is at least a seventh of an item's rounds */
+#define EXL3_LAYER_ROUTE_THREADS 256u
+#define EXL3_LAYER_COUNTER_WORDS 4u /* live job count, group counter of the publish, failed flag, reserved */
+#define EXL3_LAYER_READY_LINE 0u
+#define EXL3_LAYER_DONE_LINE 16u
+#define EXL3_LAYER_LOCAL_LINE 32u
+#define EXL3_LAYER_SIGNAL_BYTES (33u * 128u)
+struct exl3_layer_route_record {
+	struct exl3_moe_record moe;
+	uint64_t scores_offset; /* FP32 [row_capacity][routed_count] */
+	uint64_t expert_table_offset; /* uint64 [routed_count + shared_count][3] */
+	uint64_t picks_offset; /* written: uint32 [row_capacity][picks] */
+	uint64_t weights_offset; /* written: FP32 [row_capacity][picks] */
+	uint64_t bias_offset; /* FP32 [routed_count], 0: none */
+	uint64_t step_offset;
+	uint32_t routed_count;
+	uint32_t shared_count;
+	uint32_t picks;
+	uint32_t row_capacity;
+	uint32_t scoring;
+	float route_scale;
+};
+
+struct exl3_layer_publish_arguments {
+	uint64_t peer_table_offset; /* struct ordered_collective_peer [rank_count] */
+	uint64_t region_offset;
+	uint64_t input_offset; /* of the FP32 rows inside a slot, at least EXL3_LAYER_SIGNAL_BYTES */
+	uint64_t status_offset; /* the 16-byte status block of the reduction (arena offset) */
+	uint64_t step_offset;
+	uint64_t parity_stride;
+	uint64_t deadline_cycles;
+	uint32_t rank_count;
+	uint32_t rank;
+	uint32_t row_capacity;
+	uint32_t reserved_zero;
+};
+
+struct exl3_layer_down_record {
+	struct exl3_moe_record moe;
+	struct exl3_layer_publish_arguments publish;
+};
+
+/* ------------------------------------------------------------------------------------------------------------
  * Fixed-order reduction over ranks (reference: include/anemone/ordered_collective_records.h:45-98).
  *
  * Each rank owns a region of two parity slots (slot = sequence & 1) of parity_stride bytes. A slot begins with three
@@ -316,6 +390,7 @@ struct ordered_row_sum_publish_arguments {
 	uint64_t pair_output_offset; /* FP32 [rows * pairs_per_row][width] */
 	uint32_t width;
 	uint32_t pairs_per_row;
+	uint64_t status_offset; /* the reduction's 16-byte status block: a wait for the slot that runs out is reported */
 };
 
 /* ------------------------------------------------------------------------------------------------------------
@@ -485,6 +560,7 @@ struct router_select_b200_arguments {
 	uint32_t scoring;
 	float route_scale;
 	uint32_t reserved_zero;
+	uint64_t bias_offset; /* FP32 [expert_count] added to the affinities for the choice alone; 0: none */
 };
 
 /* ------------------------------------------------------------------------------------------------------------
@@ -557,7 +633,7 @@ struct exl3_prefill_record {
 	uint32_t scoring;
 	float route_scale;
 	float activation_limit;
-	uint32_t reserved_zero[2];
+	uint64_t bias_offset; /* FP32 [expert_count] added to the affinities for the choice alone; 0: none */
 };
 
 /* Offsets of the workspace parts from workspace_offset, the workspace's bytes and the tile capacity. */
@@ -753,13 +829,16 @@ AB_RECORD_HAS(step_block, 16);
 AB_RECORD_HAS(ordered_collective_peer, 32);
 AB_RECORD_HAS(ordered_collective_arguments, 80);
 AB_RECORD_HAS(ordered_reduce_bf16_arguments, 96);
-AB_RECORD_HAS(ordered_row_sum_publish_arguments, 96);
+AB_RECORD_HAS(ordered_row_sum_publish_arguments, 104);
 AB_RECORD_HAS(ordered_push_arguments, 96);
 AB_RECORD_HAS(tp_exchange_arguments, 112);
 AB_RECORD_HAS(ordered_rows_push_arguments, 112);
 AB_RECORD_HAS(tp2_join_arguments, 80);
-AB_RECORD_HAS(router_select_b200_arguments, 80);
+AB_RECORD_HAS(router_select_b200_arguments, 88);
 AB_RECORD_HAS(step_input_select_arguments, 40);
+AB_RECORD_HAS(exl3_layer_route_record, 184);
+AB_RECORD_HAS(exl3_layer_publish_arguments, 72);
+AB_RECORD_HAS(exl3_layer_down_record, 184);
 AB_RECORD_HAS(exl3_prefill_tile, 16);
 AB_RECORD_HAS(exl3_prefill_entry, 8);
 AB_RECORD_HAS(exl3_prefill_record, 136);

@@ -84,6 +84,12 @@ int orc_ordered_collective(const float *const *inputs, float *const *outputs, ui
 /* One row: `picks` experts by slot (ascending expert) and their weights. scoring: ROUTER_SCORING_*. */
 void orc_router_row(const float *scores, uint32_t expert_count, uint32_t picks, uint32_t scoring, float route_scale,
 		    uint32_t *experts_out, float *weights_out);
+/* The same with a per-expert selection bias (NULL: none): picks by affinity + bias, weights from the affinity alone. */
+void orc_router_row_biased(const float *scores, const float *bias, uint32_t expert_count, uint32_t picks,
+			   uint32_t scoring, float route_scale, uint32_t *experts_out, float *weights_out);
+/* The affinity of one score: a fixed sequence of FP32 roundings with no library function, so the card's bits equal
+ * the host's. */
+float orc_router_affinity(float score, uint32_t scoring);
 /* The job table of the live rows (same bytes as router_select_b200 writes). Returns the number of non-empty jobs. */
 uint32_t orc_router_jobs(const uint32_t *experts, const float *weights, uint32_t live_rows, uint32_t picks,
 			 uint32_t expert_count, uint32_t shared_count, const uint64_t *expert_table,

@@ -70,6 +70,10 @@ def load_oracle():
     lib.orc_ordered_collective.argtypes = [C.POINTER(f32p), C.POINTER(f32p), C.c_uint32, C.c_uint32, C.c_int]
     lib.orc_router_row.restype = None
     lib.orc_router_row.argtypes = [f32p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_float, u32p, f32p]
+    lib.orc_router_row_biased.restype = None
+    lib.orc_router_row_biased.argtypes = [f32p, f32p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_float, u32p, f32p]
+    lib.orc_router_affinity.restype = C.c_float
+    lib.orc_router_affinity.argtypes = [C.c_float, C.c_uint32]
     lib.orc_router_jobs.restype = C.c_uint32
     lib.orc_router_jobs.argtypes = [u32p, f32p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, u64p, C.c_uint32,
                                     C.c_void_p]

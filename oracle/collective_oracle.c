@@ -159,20 +159,84 @@ static uint64_t router_key(float score, uint32_t expert)
 	return (uint64_t)ordered << 32 | (uint32_t)~expert;
 }
 
-static float router_affinity(float score, uint32_t scoring)
+/* e^a in FP32 by a fixed sequence of single roundings (the router's own definition, the same on the card): nothing
+ * of the mathematics library, so the host and the card give the same bits. a is a number; below -104 the result is
+ * +0, above 88.75 +infinity. n = rint(a log2 e); r = a - n ln 2 in two exact-product steps; a degree-7 polynomial;
+ * the scale 2^n as two powers of two, so that only the last product can round (a subnormal result). */
+static float router_power_of_two(int32_t exponent)
 {
-	if (scoring == ROUTER_SCORING_SQRT_SOFTPLUS) /* include/anemone/router_records.h:10-12 */
-		return sqrtf(score > 20.0f ? score : log1pf(expf(score)));
-	return 1.0f / (1.0f + expf(-score));
+	const uint32_t bits = (uint32_t)(exponent + 127) << 23;
+	float value;
+	memcpy(&value, &bits, sizeof(value));
+	return value;
 }
 
-void orc_router_row(const float *scores, uint32_t expert_count, uint32_t picks, uint32_t scoring, float route_scale,
-		    uint32_t *experts_out, float *weights_out)
+static float router_exponential(float a)
+{
+	if (a < -104.0f)
+		return 0.0f;
+	if (a > 88.75f)
+		return INFINITY;
+	const float n = rintf(a * 1.44269504f);
+	float r = a - n * 0.693359375f;
+	r = r - n * -2.12194440e-4f;
+	float p = 1.9875691500e-4f;
+	p = p * r + 1.3981999507e-3f;
+	p = p * r + 8.3334519073e-3f;
+	p = p * r + 4.1665795894e-2f;
+	p = p * r + 1.6666665459e-1f;
+	p = p * r + 5.0000001201e-1f;
+	p = p * (r * r) + r;
+	p = p + 1.0f;
+	const int32_t whole = (int32_t)n, first = whole >> 1;
+	return p * router_power_of_two(first) * router_power_of_two(whole - first);
+}
+
+/* log(1 + t) for 0 <= t <= 1 as 2 atanh(z), z = t / (2 + t) <= 1/3, by nine terms of its series in z^2 */
+static float router_log_one_plus(float t)
+{
+	const float z = t / (2.0f + t), w = z * z;
+	float p = 1.0f / 17.0f;
+	p = p * w + 1.0f / 15.0f;
+	p = p * w + 1.0f / 13.0f;
+	p = p * w + 1.0f / 11.0f;
+	p = p * w + 1.0f / 9.0f;
+	p = p * w + 1.0f / 7.0f;
+	p = p * w + 1.0f / 5.0f;
+	p = p * w + 1.0f / 3.0f;
+	p = p * w + 1.0f;
+	return 2.0f * z * p;
+}
+
+/* The affinity of a router score. SQRT_SOFTPLUS (include/anemone/router_records.h:10-12): sqrt(softplus(s)),
+ * softplus(s) = s above 20, else max(s, 0) + log(1 + e^-|s|); SIGMOID: 1 / (1 + e^-s). A not-a-number stays one. */
+float orc_router_affinity(float score, uint32_t scoring)
+{
+	if (score != score)
+		return score;
+	if (scoring == ROUTER_SCORING_SQRT_SOFTPLUS) {
+		if (score > 20.0f)
+			return sqrtf(score);
+		const float magnitude = score < 0.0f ? -score : score;
+		const float tail = router_log_one_plus(router_exponential(-magnitude));
+		return sqrtf((score > 0.0f ? score : 0.0f) + tail);
+	}
+	return 1.0f / (1.0f + router_exponential(-score));
+}
+
+/* source/kernel_router.cuh:47-119 and tests/router_reference.c:150-190: the `picks` experts of the largest
+ * affinity + bias (bias may be NULL: none), one at a time, the lower expert first among equals; slots in ascending
+ * expert order; weights from the unbiased affinities, their sum from +0 in ascending expert order. */
+void orc_router_row_biased(const float *scores, const float *bias, uint32_t expert_count, uint32_t picks,
+			   uint32_t scoring, float route_scale, uint32_t *experts_out, float *weights_out)
 {
 	uint64_t keys[ROUTER_B200_MAXIMUM_EXPERTS];
+	float affinities[ROUTER_B200_MAXIMUM_EXPERTS];
 	uint32_t chosen[ROUTER_B200_MAXIMUM_PICKS];
-	for (uint32_t expert = 0; expert < expert_count; expert++)
-		keys[expert] = router_key(scores[expert], expert);
+	for (uint32_t expert = 0; expert < expert_count; expert++) {
+		affinities[expert] = orc_router_affinity(scores[expert], scoring);
+		keys[expert] = router_key(bias != NULL ? affinities[expert] + bias[expert] : affinities[expert], expert);
+	}
 	for (uint32_t pick = 0; pick < picks; pick++) {
 		uint32_t best = 0;
 		for (uint32_t expert = 1; expert < expert_count; expert++)
@@ -190,11 +254,17 @@ void orc_router_row(const float *scores, uint32_t expert_count, uint32_t picks, 
 	}
 	float sum = 0.0f;
 	for (uint32_t slot = 0; slot < picks; slot++) {
-		weights_out[slot] = router_affinity(scores[experts_out[slot]], scoring);
+		weights_out[slot] = affinities[experts_out[slot]];
 		sum += weights_out[slot];
 	}
 	for (uint32_t slot = 0; slot < picks; slot++)
 		weights_out[slot] = weights_out[slot] / (sum + 1e-20f) * route_scale;
+}
+
+void orc_router_row(const float *scores, uint32_t expert_count, uint32_t picks, uint32_t scoring, float route_scale,
+		    uint32_t *experts_out, float *weights_out)
+{
+	orc_router_row_biased(scores, NULL, expert_count, picks, scoring, route_scale, experts_out, weights_out);
 }
 
 uint32_t orc_router_jobs(const uint32_t *experts, const float *weights, uint32_t live_rows, uint32_t picks,

@@ -14,7 +14,8 @@ import numpy as np
 
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 sys.path.insert(0, ROOT)
-from oracle.binding import load_reference, pointer_array, ptr, u8p  # noqa: E402
+from oracle.binding import f32p, load_oracle, load_reference, pointer_array, ptr, u32p, u64p, u8p  # noqa: E402
+from tests.golden_util import router_case_inputs  # noqa: E402
 
 
 def fnv64(values):
@@ -59,6 +60,36 @@ def main():
                            "sum_fnv64": hex(fnv64(outputs[0])),
                            "first": [hex(v) for v in outputs[0][:8].view(np.uint32).tolist()]})
     out["ordered_all_reduce"] = reduce
+    # the router at the reference's geometry (384 experts, 6 picks, scale 1.5, sqrt(softplus) affinities): its own
+    # test_router_select / test_router_jobs on the affinities of seeded scores. The affinities are this library's
+    # fixed FP32 sequence (the reference takes a card's affinities as given and bounds them by
+    # test_router_affinity_holds, which make_golden asserts for every one of them).
+    import ctypes as C
+    oracle = load_oracle()
+    reference.test_router_affinity_holds.restype = C.c_bool
+    reference.test_router_affinity_holds.argtypes = [C.c_float, C.c_float]
+    reference.test_router_select.argtypes = [f32p, f32p, C.c_bool, u32p, f32p]
+    router = []
+    for seed in (0x707E0, 0x707E1, 0x707E2, 0x707E7):
+        scores, bias, table = router_case_inputs(seed)
+        rows = scores.shape[0]
+        affinities = np.array([[oracle.orc_router_affinity(float(s), 1) for s in row] for row in scores],
+                              dtype=np.float32)
+        for row in range(rows):
+            for expert in range(384):
+                assert reference.test_router_affinity_holds(float(scores[row, expert]), float(affinities[row, expert]))
+        experts = np.zeros((rows, 6), dtype=np.uint32)
+        weights = np.zeros((rows, 6), dtype=np.float32)
+        for row in range(rows):
+            reference.test_router_select(ptr(affinities[row], f32p), ptr(bias, f32p), False, ptr(experts[row], u32p),
+                                         ptr(weights[row], f32p))
+        jobs = np.zeros(rows * 6 * 96, dtype=np.uint8)
+        reference.test_router_jobs(ptr(experts, u32p), ptr(weights, f32p), rows, rows, ptr(table, u64p),
+                                   jobs.ctypes.data_as(C.c_void_p))
+        router.append({"seed": seed, "rows": rows, "experts": experts.tolist(),
+                       "weights": [[hex(v) for v in row] for row in weights.view(np.uint32).tolist()],
+                       "jobs_fnv64": hex(fnv64(jobs))})
+    out["router_select"] = router
     with open(os.path.join(ROOT, "tests", "golden", "reference_vectors.json"), "w") as handle:
         json.dump(out, handle, indent=1)
     print("wrote tests/golden/reference_vectors.json")

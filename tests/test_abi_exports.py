@@ -57,7 +57,9 @@ def test_record_sizes_match_the_headers():
               "router_select_b200_arguments": R.RouterSelectB200, "step_input_select_arguments": R.StepInputSelect,
               "activation_quantize_arguments": R.ActivationQuantize, "expert_gate_up_arguments": R.ExpertGateUp,
               "expert_down_arguments": R.ExpertDown, "trunk_linear_quantized_arguments": R.TrunkLinearQuantized,
-              "trunk_hidden_arguments": R.TrunkHidden, "trunk_rows_add_arguments": R.TrunkRowsAdd}
+              "trunk_hidden_arguments": R.TrunkHidden, "trunk_rows_add_arguments": R.TrunkRowsAdd,
+              "exl3_layer_route_record": R.Exl3LayerRoute, "exl3_layer_publish_arguments": R.Exl3LayerPublish,
+              "exl3_layer_down_record": R.Exl3LayerDown}
     assert set(declared) == set(mirror)
     for name, record in mirror.items():
         assert C.sizeof(record) == int(declared[name]), name

@@ -27,7 +27,7 @@ def world_sizes(api):
     return [size for size in (2, 4, 8) if size <= api.card_count()]
 
 
-@pytest.mark.parametrize("form", ["push", "pull"])
+@pytest.mark.parametrize("form", ["fused", "push", "pull"])
 def test_layer_tensor_parallel(api, oracle, form):
     for ranks in world_sizes(api):
         config = MoeConfig(hidden=512, inner=128 * ranks * 2, experts=24, shared=1, picks=4, row_capacity=8)
