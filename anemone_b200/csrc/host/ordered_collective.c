@@ -46,6 +46,86 @@ result_status ordered_collective_routes_prepare(const struct ordered_collective_
 	return STATUS_OK;
 }
 
+static bool policy_row_is_well_formed(const struct ordered_collective_route_policy *row)
+{
+	if (row->rank_count == 0 || row->rank_count > ORDERED_COLLECTIVE_MAXIMUM_RANKS || row->element_count == 0 ||
+	    row->element_count > ORDERED_COLLECTIVE_MAXIMUM_ELEMENTS ||
+	    (uint32_t)row->operation >= ORDERED_COLLECTIVE_OPERATIONS ||
+	    (row->paired_scatter_gather && row->operation != ORDERED_REDUCE_SCATTER && row->operation != ORDERED_GATHER))
+		return false;
+	const uint32_t group = (1u << row->rank_count) - 1u;
+	for (uint32_t source = 0; source < row->rank_count; source++) {
+		const uint32_t direct = row->expected_direct_reader_masks[source], host = row->host_reader_masks[source];
+		const uint32_t self = 1u << source;
+		/* inside the group; a source reads itself directly and never through a mirror; whoever is denied direct
+		 * access has a mirror */
+		if (((direct | host) & ~group) != 0 || (direct & self) == 0 || (host & self) != 0 ||
+		    (group & ~direct & ~host) != 0)
+			return false;
+	}
+	return true;
+}
+
+static bool policy_rows_bind_alike(const struct ordered_collective_route_policy *first,
+				   const struct ordered_collective_route_policy *second)
+{
+	for (uint32_t source = 0; source < first->rank_count; source++)
+		if (first->host_reader_masks[source] != second->host_reader_masks[source] ||
+		    first->expected_direct_reader_masks[source] != second->expected_direct_reader_masks[source] ||
+		    first->arithmetic_classes[source] != second->arithmetic_classes[source] ||
+		    first->link_generations[source] != second->link_generations[source] ||
+		    first->link_lane_counts[source] != second->link_lane_counts[source])
+			return false;
+	return true;
+}
+
+result_status ordered_collective_routes_prepare_measured(const struct ordered_collective_route_description *description,
+							 const struct ordered_collective_route_policy *rows,
+							 uint32_t row_count, uint32_t *host_reader_masks_out)
+{
+	if (description == NULL || host_reader_masks_out == NULL || row_count > ORDERED_ROUTE_POLICY_MAXIMUM_ROWS ||
+	    (row_count != 0 && rows == NULL))
+		return STATUS_INVALID_ARGUMENT;
+	/* what holds without a table: direct where qualified, a host mirror where denied */
+	uint32_t masks[ORDERED_COLLECTIVE_MAXIMUM_RANKS];
+	struct ordered_collective_route_description plain = *description;
+	plain.common_numa_root = false;
+	const result_status status = ordered_collective_routes_prepare(&plain, masks);
+	if (status != STATUS_OK)
+		return status;
+	const struct ordered_collective_route_policy *match = NULL;
+	for (uint32_t index = 0; index < row_count; index++) {
+		const struct ordered_collective_route_policy *const row = &rows[index];
+		if (!policy_row_is_well_formed(row))
+			return STATUS_INVALID_ARGUMENT;
+		for (uint32_t earlier = 0; earlier < index; earlier++) {
+			const struct ordered_collective_route_policy *const other = &rows[earlier];
+			if (other->rank_count != row->rank_count || other->element_count != row->element_count)
+				continue;
+			if (other->operation == row->operation && other->paired_scatter_gather == row->paired_scatter_gather)
+				return STATUS_INVALID_ARGUMENT; /* one key twice */
+			if (other->paired_scatter_gather && row->paired_scatter_gather && !policy_rows_bind_alike(other, row))
+				return STATUS_INVALID_ARGUMENT; /* the two rows of a pair must be one plan */
+		}
+		if (row->rank_count == description->rank_count && row->element_count == description->element_count &&
+		    row->operation == description->operation &&
+		    row->paired_scatter_gather == description->paired_scatter_gather)
+			match = row;
+	}
+	if (match != NULL)
+		for (uint32_t source = 0; source < description->rank_count; source++) {
+			const struct card_description_record *const card = &description->cards[source];
+			if (match->expected_direct_reader_masks[source] != description->direct_reader_masks[source] ||
+			    match->arithmetic_classes[source] != (uint32_t)card->arithmetic_class ||
+			    match->link_generations[source] != card->link_generation ||
+			    match->link_lane_counts[source] != card->link_lane_count)
+				return STATUS_UNSUPPORTED; /* measured under another access pattern or on other cards */
+			masks[source] = match->host_reader_masks[source];
+		}
+	memcpy(host_reader_masks_out, masks, description->rank_count * sizeof(masks[0]));
+	return STATUS_OK;
+}
+
 result_status ordered_collective_kernels_prepare(const struct backend_operations *backend, struct device_card *card,
 						 struct ordered_collective_kernels *kernels_out)
 {

@@ -24,102 +24,14 @@ extern "C" __global__ void __launch_bounds__(EXL3_TRANSFORM_THREADS)
 	exl3_input_pass(record.base, arena, moe_widths(record, arena));
 }
 
-template <uint32_t BX2>
-__device__ __forceinline__ void moe_gate_up(const struct exl3_moe_record &moe, unsigned char *arena,
-					    const struct expert_job_record *job, unsigned char *dynamic_shared,
-					    exl3_product_shared *shared, uint32_t *flag)
-{
-	const struct exl3_expert_record &record = moe.base;
-	const uint32_t lane = threadIdx.x % EXL3_WARP, warp = threadIdx.x / EXL3_WARP;
-	const uint32_t H = record.input_size, I = record.inner_size, pairs = record.pair_count;
-	const uint32_t runs = exl3_moe_splits(H, I), groups = I / EXL3_TRANSFORM;
-	const uint32_t group = blockIdx.x / runs, run = blockIdx.x % runs, projection = blockIdx.z;
-	const uint32_t steps = H / EXL3_TILE / runs;
-	const uint32_t fed_column = lane / 4u < job->row_count ? lane / 4u : 0u;
-	const __half *const operands = reinterpret_cast<const __half *>(arena + record.operands_offset);
-	float sums[2][4];
-	if (!exl3_product_core<BX2>(arena + (projection == 0 ? job->gate_offset : job->up_offset), I, group, run * steps,
-				    steps, operands + ((uint64_t)projection * pairs + job->pair_index[fed_column]) * H,
-				    dynamic_shared, shared, sums))
-		return;
-	/* partial sums: FP32 [projection][run][pair][I] */
-	float *const partials = reinterpret_cast<float *>(arena + record.products_offset);
-	const uint64_t run_stride = (uint64_t)pairs * I;
-	float *rows[LINEAR_MAXIMUM_ROWS];
-#pragma unroll
-	for (uint32_t column = 0; column < LINEAR_MAXIMUM_ROWS; column++)
-		rows[column] = partials + ((uint64_t)projection * runs + run) * run_stride +
-			       (uint64_t)job->pair_index[column < job->row_count ? column : 0u] * I + group * EXL3_TRANSFORM;
-	store_partial(sums, rows, job->row_count);
-	uint32_t *const counter = reinterpret_cast<uint32_t *>(arena + moe.counters_offset) + blockIdx.y * groups + group;
-	if (!last_of(counter, EXL3_PROJECTIONS * runs, flag))
-		return;
-	exl3_gate_up_epilogue<BX2>(moe, arena, job, group, partials, partials + (uint64_t)runs * run_stride, run_stride, runs,
-				   runs);
-}
-
-template <uint32_t BX2>
-__device__ __forceinline__ void moe_down(const struct exl3_moe_record &moe, unsigned char *arena,
-					 const struct expert_job_record *job, unsigned char *dynamic_shared,
-					 exl3_product_shared *shared, uint32_t *flag)
-{
-	const struct exl3_expert_record &record = moe.base;
-	const uint32_t lane = threadIdx.x % EXL3_WARP, warp = threadIdx.x / EXL3_WARP;
-	const uint32_t H = record.input_size, I = record.inner_size, pairs = record.pair_count;
-	const uint32_t runs = exl3_moe_splits(I, H), groups = H / EXL3_TRANSFORM;
-	const uint32_t group = blockIdx.x / runs, run = blockIdx.x % runs;
-	const uint32_t steps = I / EXL3_TILE / runs;
-	const uint32_t fed_column = lane / 4u < job->row_count ? lane / 4u : 0u;
-	const __half *const operands =
-		reinterpret_cast<const __half *>(arena + record.operands_offset) + (uint64_t)EXL3_PROJECTIONS * pairs * H;
-	float sums[2][4];
-	if (!exl3_product_core<BX2>(arena + job->down_offset, H, group, run * steps, steps,
-				    operands + (uint64_t)job->pair_index[fed_column] * I, dynamic_shared, shared, sums))
-		return;
-	/* partial sums: FP32 [run][pair][H]; run 0's rows are also where the pair outputs go */
-	float *const partials = reinterpret_cast<float *>(arena + record.products_offset);
-	const uint64_t run_stride = (uint64_t)pairs * H;
-	float *rows[LINEAR_MAXIMUM_ROWS];
-#pragma unroll
-	for (uint32_t column = 0; column < LINEAR_MAXIMUM_ROWS; column++)
-		rows[column] = partials + run * run_stride +
-			       (uint64_t)job->pair_index[column < job->row_count ? column : 0u] * H + group * EXL3_TRANSFORM;
-	store_partial(sums, rows, job->row_count);
-	uint32_t *const counter = reinterpret_cast<uint32_t *>(arena + moe.counters_offset) +
-				  (uint64_t)record.job_count * (I / EXL3_TRANSFORM) + blockIdx.y * groups + group;
-	if (!last_of(counter, runs, flag))
-		return;
-	exl3_down_epilogue<BX2>(moe, arena, job, group, partials, run_stride, runs);
-}
-
-#define MOE_WIDTH_SWITCH(function)                                                         \
-	switch (exl3_job_bits_x2(record.base, job, moe_widths(record, arena))) {           \
-	case EXL3_BITS_X2_K2:                                                              \
-		function<EXL3_BITS_X2_K2>(record, arena, job, dynamic_shared, &shared, &flag);   \
-		break;                                                                     \
-	case EXL3_BITS_X2_K2_5:                                                            \
-		function<EXL3_BITS_X2_K2_5>(record, arena, job, dynamic_shared, &shared, &flag); \
-		break;                                                                     \
-	case EXL3_BITS_X2_K3:                                                              \
-		function<EXL3_BITS_X2_K3>(record, arena, job, dynamic_shared, &shared, &flag);   \
-		break;                                                                     \
-	case EXL3_BITS_X2_K4:                                                              \
-		function<EXL3_BITS_X2_K4>(record, arena, job, dynamic_shared, &shared, &flag);   \
-		break;                                                                     \
-	default:                                                                           \
-		break;                                                                     \
-	}
-
 extern "C" __global__ void __launch_bounds__(EXL3_PRODUCT_THREADS)
 	exl3_moe_gate_up(struct exl3_moe_record record, unsigned char *arena)
 {
 	extern __shared__ __align__(128) unsigned char dynamic_shared[];
 	__shared__ exl3_product_shared shared;
 	__shared__ uint32_t flag;
-	const struct expert_job_record *const job = exl3_job(record.base, arena, blockIdx.y);
-	if (job->row_count == 0)
-		return;
-	MOE_WIDTH_SWITCH(moe_gate_up)
+	exl3_moe_gate_up_block(record, arena, exl3_moe_splits(record.base.input_size, record.base.inner_size),
+			       dynamic_shared, &shared, &flag);
 }
 
 extern "C" __global__ void __launch_bounds__(EXL3_PRODUCT_THREADS)
@@ -128,10 +40,8 @@ extern "C" __global__ void __launch_bounds__(EXL3_PRODUCT_THREADS)
 	extern __shared__ __align__(128) unsigned char dynamic_shared[];
 	__shared__ exl3_product_shared shared;
 	__shared__ uint32_t flag;
-	const struct expert_job_record *const job = exl3_job(record.base, arena, blockIdx.y);
-	if (job->row_count == 0)
-		return;
-	MOE_WIDTH_SWITCH(moe_down)
+	exl3_moe_down_block(record, arena, exl3_moe_splits(record.base.inner_size, record.base.input_size),
+			    dynamic_shared, &shared, &flag);
 }
 
 extern "C" __global__ void exl3_moe_row_sum(struct exl3_moe_record record, unsigned char *arena)

@@ -17,8 +17,12 @@
  *   - every call on a device shares the one array and finds the previous call's contents in it. Each call rewrites
  *     everything it later reads, and nothing in it needs to start at zero, but two calls that overlap on the same GPU
  *     (different streams, different threads) race on it: serialise them;
- *   - the first call on each device looks up the array's device address (cudaGetSymbolAddress with that device current)
- *     and raises the kernels' shared-memory limit; that first call should come before any stream capture begins.
+ *   - every call looks up the array's device address for the device that is current (cudaGetSymbolAddress, which
+ *     allocates nothing and keeps no state here: nothing goes stale when a context is reset, and two host threads
+ *     share no variable of this file). The first call on a device makes the CUDA runtime load this library's device
+ *     code there; that first call should come before any stream capture begins. The address is that of the context
+ *     the CUDA runtime uses for the calling thread (the device's primary context unless the caller made another one
+ *     current); asking on every call is what keeps it right.
  * It calls no cudaMalloc, cudaFree or any allocating routine. The arithmetic is the five-pass chain's
  * (exl3_passes.cuh), so its results equal exl3_experts_prepare's launches on the same inputs.
  */
@@ -41,11 +45,10 @@ static_assert(NOALLOC_JOB_BYTES + NOALLOC_OPERAND_BYTES + NOALLOC_PRODUCT_BYTES 
 	      "the stated scratch size is the sum of its parts");
 
 /* In host code this name is only a stand-in for the symbol: it is not a device address. Host code gets the address
- * from cudaGetSymbolAddress, once per device, and hands it to the kernels as their arena. */
+ * from cudaGetSymbolAddress, with the device current, and hands it to the kernels as their arena. */
 static __device__ __align__(256) unsigned char noalloc_scratch[EXL3_NOALLOC_SCRATCH_BYTES];
-
-#define NOALLOC_MOST_DEVICES 64
-static unsigned char *scratch_address[NOALLOC_MOST_DEVICES];
+static_assert(EXL3_PRODUCT_PARTIAL_BYTES <= 48u * 1024u,
+	      "the product kernels' dynamic shared memory needs no opt-in attribute (no per-device set-up to keep)");
 
 /* The chain's records name memory by offset from an arena. Here the arena is the scratch array and a caller's pointer
  * becomes the (wrapping) 64-bit distance from it, so the shared device functions run unchanged. */
@@ -110,27 +113,11 @@ extern "C" result_status exl3_expert_block_noalloc(const void *gate, const void 
 			      rows, hidden, inner, EXL3_NOALLOC_MOST_ROWS, EXL3_NOALLOC_MOST_HIDDEN, EXL3_NOALLOC_MOST_INNER);
 		return STATUS_INVALID_ARGUMENT;
 	}
-	int device = -1;
-	cudaError_t error = cudaGetDevice(&device);
-	if (error != cudaSuccess)
-		return runtime_failure("cudaGetDevice", error);
-	if (device < 0 || device >= NOALLOC_MOST_DEVICES)
-		return STATUS_UNSUPPORTED;
-	if (scratch_address[device] == NULL) {
-		/* set-up, once per device, with that device current */
-		unsigned char *address = NULL;
-		error = cudaGetSymbolAddress((void **)&address, noalloc_scratch);
-		if (error != cudaSuccess)
-			return runtime_failure("cudaGetSymbolAddress", error);
-		const int most = (int)exl3_product_dynamic_bytes(EXL3_BITS_X2_K4);
-		error = cudaFuncSetAttribute(noalloc_product<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
-		if (error == cudaSuccess)
-			error = cudaFuncSetAttribute(noalloc_product<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
-		if (error != cudaSuccess)
-			return runtime_failure("cudaFuncSetAttribute", error);
-		scratch_address[device] = address;
-	}
-	unsigned char *const arena = scratch_address[device];
+	/* the scratch's address on the device that is current: asked for on every call (it allocates nothing) */
+	unsigned char *arena = NULL;
+	cudaError_t error = cudaGetSymbolAddress((void **)&arena, noalloc_scratch);
+	if (error != cudaSuccess || arena == NULL)
+		return runtime_failure("cudaGetSymbolAddress", error);
 	struct expert_job_record job;
 	memset(&job, 0, sizeof(job));
 	job.gate_offset = distance_from(arena, gate);

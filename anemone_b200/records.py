@@ -77,6 +77,27 @@ EXL3_LAYER_SIGNAL_BYTES = 33 * 128
 EXL3_LAYER_READY_LINE, EXL3_LAYER_DONE_LINE, EXL3_LAYER_LOCAL_LINE = 0, 16, 32
 
 
+class Exl3Tc(C.Structure):
+    _fields_ = [("jobs_offset", C.c_uint64), ("hidden_offset", C.c_uint64), ("workspace_offset", C.c_uint64),
+                ("output_offset", C.c_uint64), ("row_count", C.c_uint32), ("job_capacity", C.c_uint32),
+                ("intermediate", C.c_uint32), ("bits_x2", C.c_uint32), ("activation_limit", C.c_float),
+                ("pass_", C.c_uint32), ("rotation", C.c_uint32), ("shared_sum", C.c_uint32),
+                ("shared_offset", C.c_uint64)]
+
+
+class RouterPick(C.Structure):
+    _fields_ = [("expert", C.c_uint32), ("route_weight", C.c_float)]
+
+
+class Exl3Tcp(C.Structure):
+    _fields_ = [("picks_offset", C.c_uint64), ("expert_offsets_offset", C.c_uint64), ("hidden_offset", C.c_uint64),
+                ("workspace_offset", C.c_uint64), ("output_offset", C.c_uint64), ("row_count", C.c_uint32),
+                ("intermediate", C.c_uint32), ("bits_x2", C.c_uint32), ("pass_", C.c_uint32),
+                ("activation_limit", C.c_float), ("rotation", C.c_uint32), ("half_rows", C.c_uint32),
+                ("part", C.c_uint32), ("step_offset", C.c_uint64), ("cone_layer", C.c_uint32),
+                ("two_blocks", C.c_uint32)]
+
+
 class Exl3MoeSizes(C.Structure):
     _fields_ = [("operand_bytes", C.c_uint64), ("product_bytes", C.c_uint64), ("counter_bytes", C.c_uint64),
                 ("gate_up_splits", C.c_uint32), ("down_splits", C.c_uint32)]
@@ -305,7 +326,7 @@ class OrderedCollectiveKernels(C.Structure):
 
 
 for _record, _bytes in ((Exl3Reconstruct, 32), (Exl3Expert, 80), (ExpertJob, 96), (ExpertRowSum, 24),
-                        (Exl3ShardActivation, 96), (Exl3Moe, 112), (Exl3LayerRoute, 184), (Exl3LayerPublish, 72), (Exl3LayerDown, 184), (TrunkLinearQuantized, 72), (TrunkHidden, 32), (TrunkRowsAdd, 24), (Exl3Prefill, 136), (Exl3PrefillTile, 16), (Exl3PrefillEntry, 8), (Exl3PrefillParts, 56), (StepBlock, 16), (OrderedPeer, 32),
+                        (Exl3ShardActivation, 96), (Exl3Moe, 112), (Exl3Tc, 72), (Exl3Tcp, 88), (RouterPick, 8), (Exl3LayerRoute, 184), (Exl3LayerPublish, 72), (Exl3LayerDown, 184), (TrunkLinearQuantized, 72), (TrunkHidden, 32), (TrunkRowsAdd, 24), (Exl3Prefill, 136), (Exl3PrefillTile, 16), (Exl3PrefillEntry, 8), (Exl3PrefillParts, 56), (StepBlock, 16), (OrderedPeer, 32),
                         (OrderedCollective, 80), (OrderedReduceBf16, 96), (OrderedRowSumPublish, 104), (OrderedPush, 96),
                         (TpExchange, 112), (OrderedRowsPush, 112), (Tp2Join, 80),
                         (RouterSelectB200, 88), (StepInputSelect, 40), (ActivationQuantize, 40), (ExpertGateUp, 64), (ExpertDown, 56),

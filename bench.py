@@ -422,17 +422,37 @@ def run_reference_kernels(args, api, base, draw_k3, local_rank):
     reference = binding.load_reference()
     widths = np.full(base.total_experts, 3, dtype=np.uint32)
     layout = MoeLayout(base, widths, 1, 0, reduce_form="pull")
-    card = api.Card(local_rank, layout.arena_bytes)
     fused_layout = MoeLayout(base, widths, 1, 0, reduce_form="fused")
-    fused_card = api.Card(local_rank, fused_layout.arena_bytes)
     passes = 3
+    steps = step_inputs(base, args.rows, 3 + args.steps)
+    names = ("retained", "fast", "ours", "fast_with_router", "ours_step_with_router")
+    elapsed = {name: [0.0] * passes for name in names}
+    rows_of = {}
+
+    def timed(where, chains, before, each, rows_at):
+        """Every chain on every step, `passes` times over; before(): what runs untimed in front of a step's chains."""
+        for repeat in range(passes):
+            for index, (tokens, scores) in enumerate(steps):
+                each.sequence += 1
+                each.stage_step(0, each.sequence, tokens, scores)
+                where.transfer_wait(where.upload_async(each.layout.step, 0, each.layout.step_input_bytes))
+                before()
+                for name, launches in chains.items():
+                    where.measure_begin()
+                    where.run(launches)
+                    where.measure_end()
+                    us = where.measure_elapsed_us()
+                    if index >= 3:
+                        elapsed[name][repeat] += us
+                    if repeat == 0:
+                        rows_of[name] = where.download(rows_at(), args.rows * base.hidden * 4, np.float32)
+
+    # one card of a device at a time: the reference's chains and this library's separate launches first
+    card = api.Card(local_rank, layout.arena_bytes)
     try:
         layer = MoeLayer(card, base, widths, (draw_k3(expert) for expert in range(base.total_experts)),
                          reduce_form="pull")
         layer.connect_local([layer])
-        fused = MoeLayer(fused_card, base, widths, (draw_k3(expert) for expert in range(base.total_experts)),
-                         reduce_form="fused")
-        fused.connect_local([fused])
         record = R.Exl3Expert(layout.jobs, layout.tokens, layout.operands, layout.products, layout.hidden,
                               layout.products, base.hidden, layout.inner_local, layout.pairs, base.pairs_per_row,
                               layout.job_capacity, 3, base.activation_limit, 0)
@@ -449,44 +469,27 @@ def run_reference_kernels(args, api, base, draw_k3, local_rank):
                   "bb_exl3_row_sum_prepare")
         for name in chains:
             chains[name].append(sum_launch)
-        routed = {"fast_with_router": (card, list(layer.launches[0:1]) + chains["fast"]),
-                  "ours_step_with_router": (fused_card, list(fused.launches))}
-        steps = step_inputs(base, args.rows, 3 + args.steps)
-        elapsed = {name: [0.0] * passes for name in list(chains) + list(routed)}
-        rows_of = {}
-        for repeat in range(passes):
-            for index, (tokens, scores) in enumerate(steps):
-                for each in (layer, fused):
-                    each.sequence += 1
-                    each.stage_step(0, each.sequence, tokens, scores)
-                    each.card.transfer_wait(each.card.upload_async(each.layout.step, 0, each.layout.step_input_bytes))
-                card.run(layer.launches[0:1])  # the router: the job table every chain reads
-                card.wait()
-                for name, launches in chains.items():
-                    card.measure_begin()
-                    card.run(launches)
-                    card.measure_end()
-                    us = card.measure_elapsed_us()
-                    if index >= 3:
-                        elapsed[name][repeat] += us
-                    if repeat == 0:
-                        rows_of[name] = card.download(layout.row_output, args.rows * base.hidden * 4, np.float32)
-                for name, (where, launches) in routed.items():
-                    where.measure_begin()
-                    where.run(launches)
-                    where.measure_end()
-                    us = where.measure_elapsed_us()
-                    if index >= 3:
-                        elapsed[name][repeat] += us
-                if repeat == 0:
-                    slot = (fused_layout.region + (fused.sequence & 1) * fused_layout.parity_stride +
-                            fused_layout.slot_input)
-                    rows_of["ours_step_with_router"] = fused_card.download(slot, args.rows * base.hidden * 4, np.float32)
-        worst = float(max(np.abs(rows_of["ours"] - rows_of[name]).max() for name in ("retained", "fast")))
-        worst_fused = float(np.abs(rows_of["ours_step_with_router"] - rows_of["fast"]).max())
+        chains["fast_with_router"] = list(layer.launches[0:1]) + chains["fast"]
+
+        def route():  # the router: the job table every chain reads
+            card.run(layer.launches[0:1])
+            card.wait()
+        timed(card, chains, route, layer, lambda: layout.row_output)
     finally:
         card.close()
-        fused_card.close()
+    # then the decode step's four launches on a card of their own
+    card = api.Card(local_rank, fused_layout.arena_bytes)
+    try:
+        fused = MoeLayer(card, base, widths, (draw_k3(expert) for expert in range(base.total_experts)),
+                         reduce_form="fused")
+        fused.connect_local([fused])
+        timed(card, {"ours_step_with_router": list(fused.launches)}, lambda: None, fused,
+              lambda: fused_layout.region + (fused.sequence & 1) * fused_layout.parity_stride + fused_layout.slot_input)
+        fused.check_status()
+    finally:
+        card.close()
+    worst = float(max(np.abs(rows_of["ours"] - rows_of[name]).max() for name in ("retained", "fast")))
+    worst_fused = float(np.abs(rows_of["ours_step_with_router"] - rows_of["fast"]).max())
     out = {}
     for name, totals in elapsed.items():
         per_step = [total / args.steps for total in totals]
@@ -932,7 +935,10 @@ def main():
             return (synthetic.exl3_matrix(rng, config.hidden, config.inner, 3),
                     synthetic.exl3_matrix(rng, config.hidden, config.inner, 3),
                     synthetic.exl3_matrix(rng, config.inner, config.hidden, 3))
-        reference_kernels = run_reference_kernels(args, api, config, draw_k3, local_rank)
+        try:
+            reference_kernels = run_reference_kernels(args, api, config, draw_k3, local_rank)
+        except Exception as error:  # this leg is a comparison beside the numbers: it must not take the line with it
+            reference_kernels = {"error": "%s: %s" % (type(error).__name__, error)}
     original = None
     if not args.no_original_weights:
         original = run_original_weights(args, api, config, rank, world, local_rank, dist, barrier, maximum)

@@ -49,6 +49,29 @@ struct ordered_collective_route_description {
 MUST_CHECK result_status ordered_collective_routes_prepare(
 	const struct ordered_collective_route_description *description, uint32_t *host_reader_masks_out);
 
+/* include/anemone/ordered_collective.h:70-100 (source/ordered_routes_measured.c): routes with a caller-qualified table
+ * of measured overrides. A row names one operation at one exact size in caller rank order: the direct reader masks
+ * it was measured under, the cards' arithmetic class and link fields, and the host reader masks to use. Malformed
+ * rows (counts, operation, a mask outside the group, a source that does not read itself or mirrors itself, a denied
+ * reader without a mirror), duplicate keys and unequal rows of one scatter/gather pair: STATUS_INVALID_ARGUMENT;
+ * a row whose key matches the description but whose masks, class or link fields do not: STATUS_UNSUPPORTED; no
+ * matching row: the qualified-direct / denied-host masks of ordered_collective_routes_prepare. Errors leave the
+ * output untouched. Pure preparation: no allocation, no backend call. */
+#define ORDERED_ROUTE_POLICY_MAXIMUM_ROWS 256u
+struct ordered_collective_route_policy {
+	uint32_t rank_count, element_count;
+	enum ordered_collective_operation operation;
+	bool paired_scatter_gather;
+	uint32_t arithmetic_classes[ORDERED_COLLECTIVE_MAXIMUM_RANKS];
+	uint32_t link_generations[ORDERED_COLLECTIVE_MAXIMUM_RANKS];
+	uint32_t link_lane_counts[ORDERED_COLLECTIVE_MAXIMUM_RANKS];
+	uint32_t expected_direct_reader_masks[ORDERED_COLLECTIVE_MAXIMUM_RANKS];
+	uint32_t host_reader_masks[ORDERED_COLLECTIVE_MAXIMUM_RANKS];
+};
+MUST_CHECK result_status ordered_collective_routes_prepare_measured(
+	const struct ordered_collective_route_description *description,
+	const struct ordered_collective_route_policy *rows, uint32_t row_count, uint32_t *host_reader_masks_out);
+
 /* include/anemone/ordered_collective.h:101-103 (source/ordered_collective.c:117-142): the four FP32 kernels. */
 MUST_CHECK result_status ordered_collective_kernels_prepare(const struct backend_operations *backend,
 							    struct device_card *card,

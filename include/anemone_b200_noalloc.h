@@ -35,8 +35,11 @@ extern "C" {
  * inner <= hidden, both multiples of 128, a stored width of 2, 40 (2.5 bits), 3 or 4; anything else is
  * STATUS_INVALID_ARGUMENT (sizes beyond the limits also print one line on stderr). It allocates nothing.
  * All calls on one GPU share the fixed scratch: calls that overlap in time on the same GPU race and must be serialised
- * by the caller. The first call on a device performs a one-time set-up (it looks up the scratch's device address with
- * that device current) and should come before any stream capture is begun. */
+ * by the caller. Every call looks up the scratch's device address for the current device (no allocation, no state
+ * kept between calls); the first call on a device makes the CUDA runtime load the library's device code there and
+ * should come before any stream capture is begun. The scratch lives in the context the CUDA runtime uses for the
+ * calling thread (the device's primary context unless the caller made another current) and does not outlive a
+ * cudaDeviceReset (the next call finds the new one). */
 MUST_CHECK result_status exl3_expert_block_noalloc(const void *gate, const void *up, const void *down,
 						   const void *tokens, const float *route_weights, void *output,
 						   uint32_t rows, uint32_t hidden, uint32_t inner, uint32_t stored_width,

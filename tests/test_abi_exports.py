@@ -63,3 +63,56 @@ def test_record_sizes_match_the_headers():
     assert set(declared) == set(mirror)
     for name, record in mirror.items():
         assert C.sizeof(record) == int(declared[name]), name
+
+
+REFERENCE = os.environ.get("ANEMONE_REFERENCE", "/root/reference")
+
+# every function the reference's boundary for this path names (its own headers declare them), and its card table
+BOUNDARY = {
+    "anemone/exl3.h": ["exl3_width_name", "exl3_reconstruct_prepare", "exl3_scratch_byte_count", "exl3_experts_prepare",
+                       "exl3_experts_fast_prepare", "exl3_experts_relaxed_prepare"],
+    "anemone/exl3_layout.h": ["bb_exl3_matrix_slice_prepare", "bb_exl3_matrix_slice_copy",
+                              "bb_exl3_output_shard_prepare"],
+    "anemone/exl3_tp.h": ["bb_exl3_pass_prepare", "bb_exl3_row_sum_prepare"],
+    "anemone/exl3_tc.h": ["exl3_tc_prepare", "exl3_tc_prepare_short", "exl3_tc_prepare_paired", "exl3_tcp_prepare",
+                          "exl3_tcp_prepare_base", "exl3_tcp_prepare_hybrid"],
+    "anemone/ordered_collective.h": ["ordered_collective_routes_prepare", "ordered_collective_routes_prepare_measured",
+                                     "ordered_collective_kernels_prepare", "ordered_collective_prepare",
+                                     "ordered_collective_host"],
+    "anemone/ordered_push.h": ["ordered_push_kernel_prepare", "ordered_push_prepare", "ordered_push_routes_prepare"],
+    "anemone/tp_exchange.h": ["tp_exchange_kernel_prepare", "tp_exchange_prepare", "tp_exchange_wide_kernels_prepare",
+                              "tp_exchange_wide_prepare"],
+}
+
+
+def test_a_caller_built_on_the_reference_headers_links_against_the_library(tmp_path):
+    """A C file that includes the REFERENCE's own headers and takes the address of every function of its boundary for
+    this path (and of its card table) compiles against those headers and links against libanemone_b200.so alone: the
+    reference's callers find every symbol they bind. Runs where the reference tree is present."""
+    import shutil
+    import subprocess
+    import pytest
+    if not os.path.isdir(os.path.join(REFERENCE, "include", "anemone")):
+        pytest.skip("the reference tree is not on this machine")
+    from anemone_b200 import api
+    api.library()
+    lines = ['#include "%s"' % header for header in BOUNDARY] + ['#include "anemone/backend_seam.h"', "#include <stdio.h>",
+                                                                  "int main(void)", "{",
+                                                                  "\tconst void *const bound[] = {"]
+    lines += ["\t\t(const void *)%s," % name for names in BOUNDARY.values() for name in names]
+    lines += ["\t\t(const void *)&backend_cuda_value, (const void *)&exl3_weight_operations,", "\t};",
+              "\tunsigned found = 0;", "\tfor (unsigned i = 0; i < sizeof(bound) / sizeof(bound[0]); i++)",
+              "\t\tfound += bound[i] != NULL;", '\tprintf("%u\\n", found);',
+              "\treturn backend_cuda_value.card_count == NULL;", "}"]
+    source = tmp_path / "caller.c"
+    source.write_text("\n".join(lines) + "\n")
+    binary = tmp_path / "caller"
+    library_dir = os.path.dirname(api.LIBRARY)
+    compiler = "/usr/bin/gcc" if os.path.exists("/usr/bin/gcc") else shutil.which("gcc")
+    build = subprocess.run([compiler, "-std=c11", "-D_GNU_SOURCE", "-DCHECKING_HOOKS_ENABLED=0",
+                            "-DTIMING_HOOKS_ENABLED=0", "-I" + os.path.join(REFERENCE, "include"), "-o", str(binary),
+                            str(source), "-L" + library_dir, "-lanemone_b200", "-Wl,-rpath," + library_dir],
+                           capture_output=True, text=True)
+    assert build.returncode == 0, build.stderr
+    ran = subprocess.run([str(binary)], capture_output=True, text=True)
+    assert ran.returncode == 0 and int(ran.stdout) == sum(len(names) for names in BOUNDARY.values()) + 2

@@ -198,7 +198,7 @@ def test_prefill_preparer_refusals(api):
         assert launches[4].grid[0] == 1 and launches[4].block[0] == 576 and launches[5].grid[0] == 1
         assert status(local_first=2, local_count=2) == 0
         for changes in ({"input_size": 192}, {"inner_size": 64}, {"picks": 0}, {"picks": 5}, {"expert_count": 0},
-                        {"reserved_zero": (C.c_uint32 * 2)(0, 1)}, {"workspace_offset": layout.workspace + 512},
+                        {"bias_offset": 8}, {"bias_offset": card.arena_bytes}, {"workspace_offset": layout.workspace + 512},
                         {"row_output_offset": layout.pair_outputs}, {"activation_limit": 0.0},
                         {"row_capacity": 0}, {"scores_offset": card.arena_bytes}, {"local_first": 3},
                         {"local_count": 0}, {"shared_inner_size": 128}, {"shared_count": 1}):

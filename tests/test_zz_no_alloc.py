@@ -22,7 +22,9 @@ def test_no_alloc_entry_matches_the_chain_twice(oracle):
     lib = api.library()
     lib.exl3_expert_block_noalloc.argtypes = [C.c_void_p] * 4 + [C.POINTER(C.c_float), C.c_void_p] + \
         [C.c_uint32] * 4 + [C.c_float, C.c_void_p, C.c_uint32]
-    for seed, (hidden, inner, rows, stored) in enumerate([(512, 256, 3, 3), (1024, 512, 8, 4), (512, 384, 1, 40)]):
+    # the last two cases fill parts of the fixed scratch exactly: hidden at its limit, and inner == hidden at 8 rows
+    for seed, (hidden, inner, rows, stored) in enumerate([(512, 256, 3, 3), (1024, 512, 8, 4), (512, 384, 1, 40),
+                                                          (8192, 256, 8, 2), (2048, 2048, 8, 3)]):
         case = ChainCase(oracle, 600 + seed, hidden=hidden, inner=inner, rows=rows, picks=1, expert_count=1,
                          widths=[stored])
         # one job holding every row, with distinct route weights
@@ -45,6 +47,12 @@ def test_no_alloc_entry_matches_the_chain_twice(oracle):
             card.wait()
             expected = card.download(case.record.output_offset, rows * hidden * 4, np.float32)
             assert np.isfinite(expected).all() and np.abs(expected).max() > 0
+            # the chain itself against the CPU oracle, within the path's tolerance
+            oracle_rows = case.run_oracle(False)[case.record.output_offset:
+                                                 case.record.output_offset + rows * hidden * 4].view(np.float32)
+            assert np.abs(expected - oracle_rows).max() <= 2e-2
+            assert float(expected.astype(np.float64) @ oracle_rows.astype(np.float64) /
+                         (np.linalg.norm(expected) * np.linalg.norm(oracle_rows))) >= 0.9999
             base = api.library().backend_b200_arena_address(card.handle)
             gate, up, down = (base + case.ranges["matrix_0_%d" % which][0] for which in range(3))
             tokens = base + case.record.input_offset
@@ -57,14 +65,16 @@ def test_no_alloc_entry_matches_the_chain_twice(oracle):
                                                        base + output_offset, rows, hidden, inner, stored, 10.0, None, 1)
                 assert status == 0, status
                 got = card.download(output_offset, rows * hidden * 4, np.float32)
-                assert np.abs(got - expected).max() <= 2e-2
-                cosine = float(got.astype(np.float64) @ expected.astype(np.float64) /
-                               (np.linalg.norm(got) * np.linalg.norm(expected)))
-                assert cosine >= 0.9999
+                # the same device code, the same build flags, the same order of operations: the same bits
+                assert np.array_equal(got.view(np.uint32), expected.view(np.uint32))
+                assert np.abs(got - oracle_rows).max() <= 2e-2  # and the CPU oracle within the path's tolerance
             # sizes beyond the fixed scratch are refused, and nothing is written
+            card.fill(output_offset, 0xC3, rows * hidden * 4)
+            card.wait()
             assert lib.exl3_expert_block_noalloc(gate, up, down, tokens, None, base + output_offset, 9, hidden, inner,
                                                  stored, 10.0, None, 1) == R.STATUS_INVALID_ARGUMENT
             assert lib.exl3_expert_block_noalloc(gate, up, down, tokens, None, base + output_offset, rows, 16384,
                                                  inner, stored, 10.0, None, 1) == R.STATUS_INVALID_ARGUMENT
+            assert (card.download(output_offset, rows * hidden * 4) == 0xC3).all()
         finally:
             card.close()
