@@ -88,6 +88,8 @@ def library():
         lib.backend_b200_image_register.argtypes = [C.c_char_p, C.c_void_p, C.c_uint64]
         lib.backend_b200_waits_expired.argtypes = [_card, C.POINTER(C.c_uint32)]
         lib.backend_b200_fill.argtypes = [_card, C.c_uint64, C.c_ubyte, C.c_uint64]
+        lib.backend_b200_step_run.argtypes = [_card, C.c_uint32, C.c_uint64, C.c_void_p, C.c_uint64, C.c_uint64,
+                                              C.c_void_p, C.c_uint64]
         lib.backend_b200_ipc_export.argtypes = [_card, C.c_char_p]
         lib.backend_b200_ipc_connect.argtypes = [_card, C.c_char_p, C.c_uint64, C.c_uint64]
         lib.exl3_reconstruct_prepare.argtypes = [C.POINTER(R.Exl3Reconstruct), C.c_uint64, C.c_uint32,
@@ -250,6 +252,15 @@ class Card:
 
     def graph_run(self, graph):
         check(self.ops.graph_run(self.handle, graph), "graph_run")
+
+    def step_run(self, graph, input_offset, input_staging_offset, input_bytes, output_offset, output_staging_offset,
+                 output_bytes):
+        """Copy in, run the graph, copy out and wait, in one call of the library (backend_b200_step_run)."""
+        check(library().backend_b200_step_run(self.handle, graph, input_offset,
+                                              C.c_void_p(self.staging.value + input_staging_offset), input_bytes,
+                                              output_offset,
+                                              C.c_void_p(self.staging.value + output_staging_offset), output_bytes),
+              "step_run")
 
     def measure_begin(self):
         check(self.ops.measure_begin(self.handle), "measure_begin")

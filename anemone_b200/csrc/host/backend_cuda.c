@@ -1060,6 +1060,40 @@ done:
 	CARD_LEAVE(card);
 }
 
+result_status backend_b200_step_run(struct device_card *card, uint32_t graph, uint64_t input_arena_offset,
+				    const void *page_locked_input, uint64_t input_byte_count,
+				    uint64_t output_arena_offset, void *page_locked_output, uint64_t output_byte_count)
+{
+	if (card == NULL ||
+	    (input_byte_count != 0 &&
+	     (page_locked_input == NULL || !range_inside(input_arena_offset, input_byte_count, card->arena_byte_count) ||
+	      !inside_one_staging_block(page_locked_input, input_byte_count))) ||
+	    (output_byte_count != 0 &&
+	     (page_locked_output == NULL || !range_inside(output_arena_offset, output_byte_count, card->arena_byte_count) ||
+	      !inside_one_staging_block(page_locked_output, output_byte_count))))
+		return STATUS_INVALID_ARGUMENT;
+	CARD_ENTER(card);
+	if (card->failed) {
+		status = STATUS_DEVICE_ERROR;
+		goto done;
+	}
+	if (graph >= card->graph_count) {
+		status = STATUS_INVALID_ARGUMENT;
+		goto done;
+	}
+	if (input_byte_count != 0)
+		DRIVER(card, cuMemcpyHtoDAsync(card->arena + input_arena_offset, page_locked_input, input_byte_count,
+					       card->stream));
+	DRIVER(card, cuGraphLaunch(card->graphs[graph], card->stream));
+	card->launches_queued += card->graph_kernel_nodes[graph];
+	if (output_byte_count != 0)
+		DRIVER(card, cuMemcpyDtoHAsync(page_locked_output, card->arena + output_arena_offset, output_byte_count,
+					       card->stream));
+	DRIVER(card, cuStreamSynchronize(card->stream));
+done:
+	CARD_LEAVE(card);
+}
+
 uint64_t backend_b200_launch_count(const struct device_card *card)
 {
 	return card != NULL ? card->launches_queued : 0;

@@ -80,13 +80,14 @@ class MoeLayout:
         self.job_capacity = rows * c.picks + c.shared * ((rows + 7) // 8)
         layout = api.Layout()
         self.peer_table = layout.take(16 * 32)
-        self.status = layout.take(16)
         # per-step inputs, contiguous so that one copy brings a whole step: step block, tokens, scores
         self.step = layout.take(256)
         self.tokens = layout.take(rows * H * 2)
         self.scores = layout.take(rows * c.experts * 4)
         self.step_input_bytes = layout.cursor - self.step
-        self.result = layout.take(rows * H * 2)
+        # the status block stands directly in front of the result: one copy brings both back
+        self.status = layout.take(16 + rows * H * 2)
+        self.result = self.status + 16
         # optional: a pool of prepared step inputs resident on the card (step_input_select walks it)
         self.pool_stride = api.align(self.step_input_bytes, 256)
         self.cursor = layout.take(16)
@@ -317,12 +318,16 @@ class MoeLayer:
         rows = tokens.shape[0]
         self.sequence += 1
         result_at = api.align(L.step_input_bytes, 4096)
-        self.stage_step(0, self.sequence, tokens, scores)
-        ticket = self.submit(0, result_at, rows)
-        card.transfer_wait(ticket)
-        self.check_status()
         nbytes = rows * self.config.hidden * 2
-        return card.staging_view[result_at:result_at + nbytes].view(np.uint16).reshape(rows, self.config.hidden).copy()
+        self.stage_step(0, self.sequence, tokens, scores)
+        # one library call: inputs in, the graph, status block and result out, wait
+        card.step_run(self.graph, L.step, 0, L.step_input_bytes, L.status, result_at, 16 + nbytes)
+        if L.reduce_form == "push":
+            self.check_status()
+        else:
+            self._raise_on(card.staging_view[result_at:result_at + 16].view(np.uint32))
+        return card.staging_view[result_at + 16:result_at + 16 + nbytes].view(np.uint16).reshape(
+            rows, self.config.hidden).copy()
 
     def check_status(self):
         if self.layout.reduce_form == "push":
@@ -331,7 +336,10 @@ class MoeLayer:
                 raise RuntimeError("ordered reduction failed: bits %d (1 a wait ran out, 2 bad sequence, 4 too many "
                                    "rows)" % bits)
             return
-        status = self.card.download(self.layout.status, 16, np.uint32)
+        self._raise_on(self.card.download(self.layout.status, 16, np.uint32))
+
+    @staticmethod
+    def _raise_on(status):
         if status[0] != 0:
             raise RuntimeError("ordered reduction failed: code %d (1 timed out, 2 bad sequence), phase %d, rank %d"
                                % (status[0], status[1], status[2]))

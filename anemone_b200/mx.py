@@ -39,12 +39,13 @@ class MxLayout:
         self.job_capacity = rows * c.picks
         layout = api.Layout()
         self.peer_table = layout.take(16 * 32)
-        self.status = layout.take(16)
         self.step = layout.take(256)
         self.tokens = layout.take(rows * H * 2)
         self.scores = layout.take(rows * c.experts * 4)
         self.step_input_bytes = layout.cursor - self.step
-        self.result = layout.take(rows * H * 2)
+        # the status block stands directly in front of the result: one copy brings both back
+        self.status = layout.take(16 + rows * H * 2)
+        self.result = self.status + 16
         # optional: a pool of prepared step inputs resident on the card (step_input_select walks it)
         self.pool_stride = api.align(self.step_input_bytes, 256)
         self.cursor = layout.take(16)
@@ -242,10 +243,15 @@ class MxLayer:
         self.sequence += 1
         result_at = api.align(L.step_input_bytes, 4096)
         self.stage_step(0, self.sequence, tokens, scores)
-        card.transfer_wait(self.submit(0, result_at, rows))
-        self.check_status()
         nbytes = rows * self.config.hidden * 2
-        return card.staging_view[result_at:result_at + nbytes].view(np.uint16).reshape(rows, self.config.hidden).copy()
+        # one library call: inputs in, the graph, status block and result out, wait
+        card.step_run(self.graph, L.step, 0, L.step_input_bytes, L.status, result_at, 16 + nbytes)
+        status = card.staging_view[result_at:result_at + 16].view(np.uint32)
+        if status[0] != 0:
+            raise RuntimeError("ordered reduction failed: code %d (1 timed out, 2 bad sequence), phase %d, rank %d"
+                               % (status[0], status[1], status[2]))
+        return card.staging_view[result_at + 16:result_at + 16 + nbytes].view(np.uint16).reshape(
+            rows, self.config.hidden).copy()
 
     def check_status(self):
         status = self.card.download(self.layout.status, 16, np.uint32)

@@ -82,10 +82,12 @@ class PrefillLayout:
         assert len(widths) == self.local_experts
         layout = api.Layout()
         self.peer_table = layout.take(16 * 32)
-        self.status = layout.take(16)
+        # one call's inputs, contiguous so that one copy brings them: step block, tokens, scores
         self.step = layout.take(256)
         self.tokens = layout.take(rows * H * 2)
         self.scores = layout.take(rows * c.experts * 4)
+        self.input_bytes = layout.cursor - self.step
+        assert self.tokens == self.step + 256 and self.scores == self.tokens + rows * H * 2
         self.picks = layout.take(rows * c.picks * 4)
         self.weights = layout.take(rows * c.picks * 4)
         self.expert_table = layout.take(self.local_experts * 24)
@@ -99,7 +101,9 @@ class PrefillLayout:
         self.slot_input = SIGNAL_BYTES
         self.parity_stride = api.align(SIGNAL_BYTES + rows * H * 4, LINE)
         self.region = layout.take(2 * self.parity_stride, LINE)
-        self.result = layout.take(rows * H * 2)
+        # the status block stands directly in front of the result: one copy brings both back
+        self.status = layout.take(16 + rows * H * 2)
+        self.result = self.status + 16
         self.matrices = []
         for local in range(self.local_experts):
             width = int(widths[local])
@@ -189,6 +193,34 @@ class PrefillLayer:
 
     def run(self):
         self.card.graph_run(self.graph)
+
+    def stage(self, staging_offset, tokens, scores):
+        """Write one call's inputs into the card's page-locked staging block, in the layout of the input area (a caller
+        that produces its tokens and scores in page-locked memory does this once, in place). The rows must fill the
+        capacity, so that tokens and scores are one contiguous range."""
+        L, view = self.layout, self.card.staging_view
+        assert tokens.shape[0] == self.config.row_capacity
+        at = staging_offset + 256
+        view[at:at + tokens.nbytes] = tokens.reshape(-1).view(np.uint8)
+        at += tokens.nbytes
+        scores = np.ascontiguousarray(scores, dtype=np.float32)
+        view[at:at + scores.nbytes] = scores.reshape(-1).view(np.uint8)
+
+    def call(self, staging_offset, result_staging_offset):
+        """One whole call on staged inputs in ONE library call: inputs in, the graph, status block and bfloat16 result
+        out, wait. Returns the result as a view of the staging block (bfloat16 bits [rows][hidden])."""
+        L, card, rows = self.layout, self.card, self.config.row_capacity
+        self.sequence += 1
+        block = R.StepBlock(self.sequence, rows, 0)
+        card.staging_view[staging_offset:staging_offset + 16] = np.frombuffer(bytes(block), dtype=np.uint8)
+        nbytes = rows * self.config.hidden * 2
+        card.step_run(self.graph, L.step, staging_offset, L.input_bytes, L.status, result_staging_offset, 16 + nbytes)
+        status = card.staging_view[result_staging_offset:result_staging_offset + 16].view(np.uint32)
+        if status[0] != 0:
+            raise RuntimeError("ordered reduction failed: code %d (1 timed out, 2 bad sequence), phase %d, rank %d"
+                               % (status[0], status[1], status[2]))
+        return card.staging_view[result_staging_offset + 16:result_staging_offset + 16 + nbytes].view(
+            np.uint16).reshape(rows, self.config.hidden)
 
     def rows(self, count):
         """FP32 [count][hidden] row sums of the last run. Raises if a CTA gave up a bounded wait."""

@@ -187,6 +187,16 @@ MUST_CHECK result_status backend_b200_image_register(const char *kernel_file_nam
  * exchange, whose kernels also report a replayed sequence, 2, and a row count beyond the prepared rows, 4). Such a CTA
  * stores nothing more and returns; nothing traps. *expired_out is 0, or the kernels' bits or-ed. */
 MUST_CHECK result_status backend_b200_waits_expired(struct device_card *card, uint32_t *expired_out);
+/* One step in ONE call, for a serving loop that must not pay a foreign-function call, a ticket and a polled wait per
+ * transfer: queue the copy of input_byte_count bytes from page-locked memory to the arena, the captured graph, the
+ * copy of output_byte_count arena bytes back to page-locked memory, then block (the driver's stream wait, which
+ * returns as the last copy completes) until all of it is done. Both host ranges lie in staging blocks of
+ * staging_allocate; either byte count may be 0 (no such copy). Equivalent to upload_begin + graph_run +
+ * download_begin + upload_wait of the table. */
+MUST_CHECK result_status backend_b200_step_run(struct device_card *card, uint32_t graph,
+					       uint64_t input_arena_offset, const void *page_locked_input,
+					       uint64_t input_byte_count, uint64_t output_arena_offset,
+					       void *page_locked_output, uint64_t output_byte_count);
 /* Kernel launches this card has queued since it was opened, graph launches counted by their kernel nodes. */
 uint64_t backend_b200_launch_count(const struct device_card *card);
 /* The device address of the arena (diagnostics and interoperation with other libraries of the same process). */
