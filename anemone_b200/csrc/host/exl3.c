@@ -293,12 +293,17 @@ void exl3_layer_sizes(uint32_t pair_count, uint32_t job_count, uint32_t input_si
 	*sizes_out = sizes;
 }
 
+static bool layer_runs_are_valid(uint32_t runs, uint32_t blocks)
+{
+	return runs != 0 && runs <= EXL3_LAYER_MAXIMUM_RUNS && (runs & (runs - 1u)) == 0 && blocks % runs == 0;
+}
+
 result_status exl3_layer_prepare(const struct exl3_layer_description *description,
 				 const struct backend_operations *backend, struct device_card *card,
 				 struct kernel_launch *launches_out)
 {
 	if (description == NULL || backend == NULL || card == NULL || launches_out == NULL ||
-	    backend->kernel_prepare == NULL || description->reserved_zero != 0)
+	    backend->kernel_prepare == NULL)
 		return STATUS_INVALID_ARGUMENT;
 	const struct exl3_layer_route_record *const route = &description->route;
 	const struct exl3_layer_publish_arguments *const publish = &description->publish;
@@ -321,8 +326,14 @@ result_status exl3_layer_prepare(const struct exl3_layer_description *descriptio
 	    publish->step_offset != route->step_offset || publish->input_offset < EXL3_LAYER_SIGNAL_BYTES ||
 	    publish->input_offset % 16u != 0 || publish->parity_stride % ORDERED_COLLECTIVE_LINE_BYTES != 0 ||
 	    publish->region_offset % ORDERED_COLLECTIVE_LINE_BYTES != 0 || H == 0 ||
-	    publish->parity_stride < publish->input_offset + (uint64_t)rows * H * 4u ||
-	    description->product_ctas > 65535u)
+	    publish->parity_stride < publish->input_offset + (uint64_t)rows * H * 4u || H % EXL3_TRANSFORM != 0 ||
+	    I == 0 || I % EXL3_TRANSFORM != 0)
+		return STATUS_INVALID_ARGUMENT;
+	/* the cut of the two product launches: the caller's, or the fixed cut's (measured on one to eight ranks' shapes:
+	 * between 2 and 8 runs of gate/up differ by a few percent, fewer lose) */
+	const uint32_t gate_up_runs = description->gate_up_runs != 0 ? description->gate_up_runs : exl3_moe_splits(H, I);
+	const uint32_t down_runs = description->down_runs != 0 ? description->down_runs : exl3_moe_splits(I, H);
+	if (!layer_runs_are_valid(gate_up_runs, H / EXL3_TRANSFORM) || !layer_runs_are_valid(down_runs, I / EXL3_TRANSFORM))
 		return STATUS_INVALID_ARGUMENT;
 	struct exl3_moe_sizes sizes;
 	exl3_layer_sizes(base->pair_count, base->job_count, H, I, &sizes);
@@ -357,8 +368,7 @@ result_status exl3_layer_prepare(const struct exl3_layer_description *descriptio
 	};
 	if (!prepare_ranges_are_valid("EXL3 layer", reduction, 3, capacity))
 		return STATUS_INVALID_ARGUMENT;
-	const struct exl3_layer_down_record down = { .moe = *moe, .publish = *publish };
-	const struct ordered_reduce_bf16_arguments reduce = {
+	const struct ordered_publish_reduce_arguments reduce = {
 		.collective = { .peer_table_offset = publish->peer_table_offset,
 				.region_offset = publish->region_offset,
 				.input_offset = publish->input_offset,
@@ -372,15 +382,15 @@ result_status exl3_layer_prepare(const struct exl3_layer_description *descriptio
 				.rank = publish->rank,
 				.reserved_zero = 0 },
 		.status_offset = publish->status_offset,
+		.pair_output_offset = base->output_offset,
 		.width = H,
-		.mode = ORDERED_REDUCE_EVERY_RANK
+		.pairs_per_row = slots
 	};
-	const uint32_t product_ctas = description->product_ctas != 0 ?
-					      description->product_ctas :
-					      EXL3_LAYER_DEFAULT_SMS * EXL3_LAYER_PRODUCT_CTAS_PER_SM;
 	/* the transform's warp tasks: (pair, gate or up, 128 inputs); eight warps a CTA, a few tasks a warp */
 	const uint64_t tasks = (uint64_t)rows * slots * EXL3_PROJECTIONS * (H / EXL3_TRANSFORM);
-	uint64_t transform_ctas = (tasks + 15u) / 16u;
+	/* a task is a chain of dependent loads (pick, table, scale, row): one a warp where the card holds that many
+	 * CTAs, so that the launch lasts one such chain and not several */
+	uint64_t transform_ctas = (tasks + EXL3_LAYER_ROUTE_THREADS / EXL3_WARP - 1u) / (EXL3_LAYER_ROUTE_THREADS / EXL3_WARP);
 	if (transform_ctas > 2u * EXL3_LAYER_DEFAULT_SMS - 1u)
 		transform_ctas = 2u * EXL3_LAYER_DEFAULT_SMS - 1u;
 	uint32_t reduce_blocks = (rows * H / 4u + ORDERED_COLLECTIVE_THREADS - 1u) / ORDERED_COLLECTIVE_THREADS;
@@ -390,14 +400,15 @@ result_status exl3_layer_prepare(const struct exl3_layer_description *descriptio
 	const struct {
 		const char *file, *name;
 		const void *record;
-		uint32_t record_bytes, grid, threads, shared;
+		uint32_t record_bytes, x, y, z, threads, shared;
 	} shapes[EXL3_LAYER_LAUNCHES] = {
-		{ EXL3_LAYER_KERNEL_FILE, "exl3_layer_route_input", route, sizeof(*route), 1u + (uint32_t)transform_ctas,
+		{ EXL3_LAYER_KERNEL_FILE, "exl3_layer_route_input", route, sizeof(*route), 1u + (uint32_t)transform_ctas, 1, 1,
 		  EXL3_LAYER_ROUTE_THREADS, 0 },
-		{ EXL3_LAYER_KERNEL_FILE, "exl3_layer_gate_up", moe, sizeof(*moe), product_ctas, EXL3_PRODUCT_THREADS, shared },
-		{ EXL3_LAYER_KERNEL_FILE, "exl3_layer_down_publish", &down, sizeof(down), product_ctas, EXL3_PRODUCT_THREADS,
-		  shared },
-		{ KERNEL_FILE_ORDERED_B200, "ordered_reduce_flags", &reduce, sizeof(reduce), reduce_blocks,
+		{ EXL3_LAYER_KERNEL_FILE, "exl3_layer_gate_up", moe, sizeof(*moe), I / EXL3_TRANSFORM * gate_up_runs,
+		  base->job_count, EXL3_PROJECTIONS, EXL3_PRODUCT_THREADS, shared },
+		{ EXL3_LAYER_KERNEL_FILE, "exl3_layer_down", moe, sizeof(*moe), H / EXL3_TRANSFORM * down_runs, base->job_count,
+		  1, EXL3_PRODUCT_THREADS, shared },
+		{ KERNEL_FILE_ORDERED_B200, KERNEL_ORDERED_PUBLISH_REDUCE_FLAGS, &reduce, sizeof(reduce), reduce_blocks, 1, 1,
 		  ORDERED_COLLECTIVE_THREADS, 0 }
 	};
 	struct kernel_launch launches[EXL3_LAYER_LAUNCHES];
@@ -409,8 +420,9 @@ result_status exl3_layer_prepare(const struct exl3_layer_description *descriptio
 			return status;
 		if (kernel == BACKEND_NO_KERNEL)
 			return STATUS_UNSUPPORTED;
-		prepare_launch_fill(&launches[index], kernel, shapes[index].grid, 1, 1, shapes[index].threads,
-				    shapes[index].shared, shapes[index].record, shapes[index].record_bytes);
+		prepare_launch_fill(&launches[index], kernel, shapes[index].x, shapes[index].y, shapes[index].z,
+				    shapes[index].threads, shapes[index].shared, shapes[index].record,
+				    shapes[index].record_bytes);
 	}
 	memcpy(launches_out, launches, sizeof(launches));
 	return STATUS_OK;

@@ -45,8 +45,6 @@ AB_INLINE uint32_t exl3_moe_splits(uint32_t inputs, uint32_t outputs)
 #define EXL3_LAYER_PRODUCT_CTAS_PER_SM 5u /* resident product CTAs of 128 threads at their register count */
 #define EXL3_LAYER_DEFAULT_SMS 148u
 #define EXL3_LAYER_WORD_LIVE_JOBS 0u
-#define EXL3_LAYER_WORD_GROUPS_DONE 1u
-#define EXL3_LAYER_WORD_FAILED 2u
 
 /* uint32 words of the moe record's counters that lie before the layer's own words */
 AB_INLINE uint64_t exl3_layer_counter_begin(uint32_t job_count, uint32_t input_size, uint32_t inner_size)
@@ -54,27 +52,10 @@ AB_INLINE uint64_t exl3_layer_counter_begin(uint32_t job_count, uint32_t input_s
 	return (uint64_t)job_count * (inner_size / EXL3_TRANSFORM + input_size / EXL3_TRANSFORM);
 }
 
-/* bytes at counters_offset in the layer form: the per-(job, group) counters, the layer's words, a counter per group of
- * 128 output columns */
+/* bytes at counters_offset in the layer form: the per-(job, group) counters, then the layer's words */
 AB_INLINE uint64_t exl3_layer_counter_bytes(uint32_t job_count, uint32_t input_size, uint32_t inner_size)
 {
-	return (exl3_layer_counter_begin(job_count, input_size, inner_size) + EXL3_LAYER_COUNTER_WORDS +
-		input_size / EXL3_TRANSFORM) * 4u;
-}
-
-/* rounds (four K steps of 16 inputs) of one item: 128 outputs over all of `inputs` */
-AB_INLINE uint32_t exl3_layer_item_rounds(uint32_t inputs)
-{
-	return inputs / EXL3_TILE / EXL3_STAGE_STEPS;
-}
-
-/* rounds a CTA of a grid of `ctas` takes of a sequence of total_rounds: an even share, but never so short that an
- * item would be cut in more than EXL3_LAYER_MAXIMUM_RUNS runs */
-AB_INLINE uint32_t exl3_layer_quantum(uint32_t total_rounds, uint32_t item_rounds, uint32_t ctas)
-{
-	const uint32_t even = (total_rounds + ctas - 1u) / ctas;
-	const uint32_t least = (item_rounds + EXL3_LAYER_MAXIMUM_RUNS - 2u) / (EXL3_LAYER_MAXIMUM_RUNS - 1u);
-	return even > least ? even : least;
+	return (exl3_layer_counter_begin(job_count, input_size, inner_size) + EXL3_LAYER_COUNTER_WORDS) * 4u;
 }
 
 /* ---- prefill (kernel_exl3_prefill) ---- */

@@ -190,13 +190,19 @@ extern "C" __global__ void __launch_bounds__(ORDERED_COLLECTIVE_THREADS)
 	}
 }
 
-/* The reduction of the decode step's four launches (struct exl3_layer_route_record explains the slot): the ranks'
- * READY words arrive in this rank's OWN memory (each rank stores its word into every rank's slot), so the wait polls
- * locally and one trip over NVLink remains: the peer loads of the rows. Then the adds in rank order from +0, one
- * rounding to bfloat16, and this rank's DONE word into every rank's slot, whatever happened, so that no peer is held
- * at its next refill of the slot. grid (up to ORDERED_B200_MAXIMUM_BLOCKS) x 256. */
+/* The reduction of the decode step's four launches as ONE launch (struct exl3_layer_route_record explains the slot):
+ *   - wait until every rank has said it is done with the slot's previous use (their DONE words arrive in this rank's
+ *     own memory, so the wait is local and normally over at once);
+ *   - this rank's FP32 row sums (a row's pairs added from +0 in ascending slot order) straight into its rows of the
+ *     slot; the last block to finish stores this rank's READY word into EVERY rank's slot (plain peer stores);
+ *   - wait for all ranks' READY words, again in this rank's own memory: one trip over NVLink remains, the peer loads
+ *     of the rows; the adds in rank order from +0, one rounding to bfloat16;
+ *   - the last block stores this rank's DONE word into every rank's slot, whatever happened, so that no peer is held.
+ * The blocks wait for a word their own grid's last block stores: the grid is at most ORDERED_B200_MAXIMUM_BLOCKS blocks
+ * of 256 threads, which a card always holds at once. Every wait is bounded; one that runs out sets the status block
+ * and, before READY, leaves READY unpublished (the peers' own waits then say so). */
 extern "C" __global__ void __launch_bounds__(ORDERED_COLLECTIVE_THREADS)
-	ordered_reduce_flags(struct ordered_reduce_bf16_arguments arguments, unsigned char *arena)
+	ordered_publish_reduce_flags(struct ordered_publish_reduce_arguments arguments, unsigned char *arena)
 {
 	__shared__ uint32_t verdict, last;
 	const struct ordered_collective_arguments &collective = arguments.collective;
@@ -206,6 +212,68 @@ extern "C" __global__ void __launch_bounds__(ORDERED_COLLECTIVE_THREADS)
 		return;
 	unsigned char *const status = arena + arguments.status_offset;
 	unsigned char *const mine = ordered_slot(collective, arena, collective.rank, sequence);
+	unsigned char *const local = mine + EXL3_LAYER_LOCAL_LINE * ORDERED_COLLECTIVE_LINE_BYTES;
+	unsigned int *const gave_up = reinterpret_cast<unsigned int *>(local + ORDERED_FLAGS_GAVE_UP_OFFSET);
+	const uint32_t live_rows = min(step.row_count, collective.element_count / arguments.width);
+	const uint32_t row_vectors = arguments.width / 4u, vectors = live_rows * row_vectors;
+	/* the slot's previous use */
+	const uint64_t previous = *reinterpret_cast<const volatile uint64_t *>(local + ORDERED_LOCAL_PREVIOUS_OFFSET);
+	if (threadIdx.x == 0)
+		verdict = 1u;
+	__syncthreads();
+	if (previous >= sequence) {
+		if (threadIdx.x == 0) {
+			ordered_status_set(status, ORDERED_STATUS_BAD_SEQUENCE, ORDERED_READY_PHASE, collective.rank);
+			verdict = 0u;
+		}
+	} else if (previous != 0 && threadIdx.x < collective.rank_count) {
+		const unsigned char *const line = mine + (EXL3_LAYER_DONE_LINE + threadIdx.x) * ORDERED_COLLECTIVE_LINE_BYTES;
+		const long long begin = clock64();
+		while (signal_load(line) < previous) {
+			if ((uint64_t)(clock64() - begin) > collective.deadline_cycles) {
+				ordered_status_set(status, ORDERED_STATUS_TIMED_OUT, ORDERED_DONE_PHASE, threadIdx.x);
+				atomicExch(&verdict, 0u);
+				break;
+			}
+			__nanosleep(40);
+		}
+	}
+	__syncthreads();
+	if (verdict != 0u) {
+		const float4 *const pairs = reinterpret_cast<const float4 *>(arena + arguments.pair_output_offset);
+		float4 *const rows = reinterpret_cast<float4 *>(mine + collective.input_offset);
+		for (uint32_t vector = blockIdx.x * blockDim.x + threadIdx.x; vector < vectors; vector += gridDim.x * blockDim.x) {
+			const uint32_t row = vector / row_vectors, column = vector % row_vectors;
+			float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+			for (uint32_t slot = 0; slot < arguments.pairs_per_row; slot++) {
+				const float4 value = __ldcg(pairs + ((uint64_t)row * arguments.pairs_per_row + slot) * row_vectors + column);
+				sum.x = __fadd_rn(sum.x, value.x);
+				sum.y = __fadd_rn(sum.y, value.y);
+				sum.z = __fadd_rn(sum.z, value.z);
+				sum.w = __fadd_rn(sum.w, value.w);
+			}
+			rows[vector] = sum;
+		}
+	} else if (threadIdx.x == 0) {
+		atomicExch(gave_up, 1u);
+	}
+	if (last_block_of_grid(local, &last)) {
+		if (threadIdx.x == 0)
+			verdict = atomicExch(gave_up, 0u) == 0u ? 1u : 0u;
+		__syncthreads();
+		if (verdict != 0u) {
+			if (threadIdx.x == 0)
+				*reinterpret_cast<volatile uint64_t *>(local + ORDERED_LOCAL_PREVIOUS_OFFSET) = sequence;
+			if (threadIdx.x < collective.rank_count) {
+				__threadfence_system();
+				signal_store(ordered_slot(collective, arena, threadIdx.x, sequence) +
+						     (EXL3_LAYER_READY_LINE + collective.rank) * ORDERED_COLLECTIVE_LINE_BYTES,
+					     sequence);
+			}
+		}
+	}
+	/* every rank's READY word, in this rank's own memory */
+	__syncthreads();
 	if (threadIdx.x == 0)
 		verdict = 1u;
 	__syncthreads();
@@ -231,8 +299,6 @@ extern "C" __global__ void __launch_bounds__(ORDERED_COLLECTIVE_THREADS)
 	}
 	__syncthreads();
 	if (verdict != 0u) {
-		const uint32_t live = min(step.row_count * arguments.width, collective.element_count);
-		const uint32_t vectors = live / 4u;
 		const float *inputs[ORDERED_COLLECTIVE_MAXIMUM_RANKS];
 #pragma unroll
 		for (uint32_t rank = 0; rank < ORDERED_COLLECTIVE_MAXIMUM_RANKS; rank++)
@@ -261,9 +327,8 @@ extern "C" __global__ void __launch_bounds__(ORDERED_COLLECTIVE_THREADS)
 						 bfloat16_bits(sum.z) | bfloat16_bits(sum.w) << 16);
 		}
 	}
-	/* this rank has read (or given up on) every rank's rows of this step */
-	if (last_block_of_grid(mine + EXL3_LAYER_LOCAL_LINE * ORDERED_COLLECTIVE_LINE_BYTES, &last) &&
-	    threadIdx.x < collective.rank_count)
+	/* this rank has read (or given up on) every rank's rows of this step: a second counter of the local line */
+	if (last_block_of_grid(local + ORDERED_FLAGS_SECOND_COUNTER_SHIFT, &last) && threadIdx.x < collective.rank_count)
 		signal_store(ordered_slot(collective, arena, threadIdx.x, sequence) +
 				     (EXL3_LAYER_DONE_LINE + collective.rank) * ORDERED_COLLECTIVE_LINE_BYTES,
 			     sequence);

@@ -22,6 +22,10 @@
 #define ORDERED_LOCAL_COUNTER_OFFSET 64u /* inside a line: a counter only the owner's own CTAs touch */
 #define ORDERED_LOCAL_PREVIOUS_OFFSET 72u /* inside the READY line: the sequence of the slot's previous use */
 #define ORDERED_LOCAL_GAVE_UP_OFFSET 80u /* inside a line: set by a block of the owner's grid whose wait ran out */
+/* the local line of the flags form (ordered_publish_reduce_flags): a counter at 64, the previous sequence at 72, a
+ * second counter at 64 + 16, the gave-up word at 88 */
+#define ORDERED_FLAGS_SECOND_COUNTER_SHIFT 16u
+#define ORDERED_FLAGS_GAVE_UP_OFFSET 88u
 
 __device__ __forceinline__ void signal_store(unsigned char *line, uint64_t sequence)
 {

@@ -130,13 +130,14 @@ class MoeLayout:
 
 class MoeLayer:
     def __init__(self, card, config, widths, matrices, rank=0, rank_count=1, pool_entries=0, reduce_form="fused",
-                 bias=None, product_ctas=0):
+                 bias=None, cut=(0, 0)):
         """matrices: iterable over experts (routed, then shared) of this rank's (gate, up, down) stored bytes.
         reduce_form: "fused" (the step in four launches: the router with the input transform, products cut evenly
         over the card, row sums and READY behind the down products, flags that arrive in the reader's memory),
         "pull" (router, four expert launches, two reduction launches: the ranks read each other's rows) or "push"
         (one reduction launch: the ranks store their rows into each other's inboxes); the same sums of the ranks'
-        rows and the same bits given those rows. bias: FP32 [experts] for a config with bias=True."""
+        rows and the same bits given those rows. bias: FP32 [experts] for a config with bias=True. cut: (gate/up
+        runs of K, down runs of K) of the fused form, 0 for the library's choice."""
         self.card, self.config = card, config
         self.widths = np.asarray(widths, dtype=np.uint32)
         self.layout = L = MoeLayout(config, self.widths, rank_count, rank, pool_entries, reduce_form)
@@ -159,7 +160,7 @@ class MoeLayer:
         card.fill(L.counters, 0, L.counter_bytes)
         if config.bias:
             card.upload(L.bias, np.ascontiguousarray(bias, dtype=np.float32))
-        self.product_ctas = product_ctas
+        self.cut = cut
         peers = (R.OrderedPeer * rank_count)()
         for peer in range(rank_count):
             peers[peer].region_offset = L.region
@@ -199,7 +200,7 @@ class MoeLayer:
                                                  L.parity_stride, c.deadline_cycles, self.rank_count, self.rank,
                                                  c.row_capacity, 0)
         description.result_offset, description.arena_byte_count = L.result, card.arena_bytes
-        description.product_ctas = self.product_ctas
+        description.gate_up_runs, description.down_runs = self.cut
         launches = (R.KernelLaunch * 4)()
         api.check(lib.exl3_layer_prepare(C.byref(description), card.ops_pointer, card.handle, launches),
                   "exl3_layer_prepare")

@@ -64,13 +64,9 @@ class Exl3LayerPublish(C.Structure):
                 ("row_capacity", C.c_uint32), ("reserved_zero", C.c_uint32)]
 
 
-class Exl3LayerDown(C.Structure):
-    _fields_ = [("moe", Exl3Moe), ("publish", Exl3LayerPublish)]
-
-
 class Exl3LayerDescription(C.Structure):
     _fields_ = [("route", Exl3LayerRoute), ("publish", Exl3LayerPublish), ("result_offset", C.c_uint64),
-                ("arena_byte_count", C.c_uint64), ("product_ctas", C.c_uint32), ("reserved_zero", C.c_uint32)]
+                ("arena_byte_count", C.c_uint64), ("gate_up_runs", C.c_uint32), ("down_runs", C.c_uint32)]
 
 
 EXL3_LAYER_SIGNAL_BYTES = 33 * 128
@@ -151,6 +147,11 @@ ORDERED_REDUCE_EVERY_RANK, ORDERED_REDUCE_OWNER_RUNS = 0, 1
 class OrderedReduceBf16(C.Structure):
     _fields_ = [("collective", OrderedCollective), ("status_offset", C.c_uint64), ("width", C.c_uint32),
                 ("mode", C.c_uint32)]
+
+
+class OrderedPublishReduce(C.Structure):
+    _fields_ = [("collective", OrderedCollective), ("status_offset", C.c_uint64), ("pair_output_offset", C.c_uint64),
+                ("width", C.c_uint32), ("pairs_per_row", C.c_uint32)]
 
 
 class OrderedRowSumPublish(C.Structure):
@@ -326,8 +327,8 @@ class OrderedCollectiveKernels(C.Structure):
 
 
 for _record, _bytes in ((Exl3Reconstruct, 32), (Exl3Expert, 80), (ExpertJob, 96), (ExpertRowSum, 24),
-                        (Exl3ShardActivation, 96), (Exl3Moe, 112), (Exl3Tc, 72), (Exl3Tcp, 88), (RouterPick, 8), (Exl3LayerRoute, 184), (Exl3LayerPublish, 72), (Exl3LayerDown, 184), (TrunkLinearQuantized, 72), (TrunkHidden, 32), (TrunkRowsAdd, 24), (Exl3Prefill, 136), (Exl3PrefillTile, 16), (Exl3PrefillEntry, 8), (Exl3PrefillParts, 56), (StepBlock, 16), (OrderedPeer, 32),
-                        (OrderedCollective, 80), (OrderedReduceBf16, 96), (OrderedRowSumPublish, 104), (OrderedPush, 96),
+                        (Exl3ShardActivation, 96), (Exl3Moe, 112), (Exl3Tc, 72), (Exl3Tcp, 88), (RouterPick, 8), (Exl3LayerRoute, 184), (Exl3LayerPublish, 72), (TrunkLinearQuantized, 72), (TrunkHidden, 32), (TrunkRowsAdd, 24), (Exl3Prefill, 136), (Exl3PrefillTile, 16), (Exl3PrefillEntry, 8), (Exl3PrefillParts, 56), (StepBlock, 16), (OrderedPeer, 32),
+                        (OrderedCollective, 80), (OrderedReduceBf16, 96), (OrderedRowSumPublish, 104), (OrderedPublishReduce, 104), (OrderedPush, 96),
                         (TpExchange, 112), (OrderedRowsPush, 112), (Tp2Join, 80),
                         (RouterSelectB200, 88), (StepInputSelect, 40), (ActivationQuantize, 40), (ExpertGateUp, 64), (ExpertDown, 56),
                         (KernelLaunch, 232), (CardDescription, 168)):

@@ -383,18 +383,31 @@ def checked_step(config, widths, draw, layer, step, rank, world, dist):
     inputs = [np.ascontiguousarray(entry[0]) for entry in everyone]
     oracle.orc_ordered_reduce_bf16(pointer_array(inputs), world, want.size, ptr(want, u16p))
     bit_exact = all(np.array_equal(entry[1], want) for entry in everyone)
-    expected, _, experts, _ = moe_reference.layer(oracle, config, widths, matrix_cache(draw), tokens, scores, world,
-                                                  host_threads())
+    expected, partials, experts, _ = moe_reference.layer(oracle, config, widths, matrix_cache(draw), tokens, scores,
+                                                         world, host_threads())
     a = synthetic.from_bfloat16(got).astype(np.float64)
     b = synthetic.from_bfloat16(expected.reshape(-1)).astype(np.float64)
     worst = float(np.abs(a - b).max())
     cosine = float(a @ b / (np.linalg.norm(a) * np.linalg.norm(b) + 1e-300))
+    # before the one rounding: the rank-ordered FP32 sums of the published rows against the oracle's
+    total, wanted = np.zeros(rows * config.hidden, dtype=np.float32), np.zeros(rows * config.hidden, dtype=np.float32)
+    for entry, partial in zip(everyone, partials):
+        total = total + entry[0]
+        wanted = wanted + partial.reshape(-1)
+    worst_fp32 = float(np.abs(total.astype(np.float64) - wanted.astype(np.float64)).max())
+    # a bfloat16 value of magnitude 4 or more has steps of 2^-5 and more: where the FP32 sums straddle a rounding
+    # boundary the results differ by one such step, which the 2e-2 bound on the sums does not forbid
+    step = float(2.0 ** (np.floor(np.log2(max(np.abs(b).max(), 1e-30))) - 7))
     picks_exact = all(np.array_equal(entry[2], experts) for entry in everyone)
-    return {"ok": bool(bit_exact and picks_exact and worst <= 2e-2 and cosine >= 0.9999),
-            "ordered_reduction_bit_exact_on_every_rank": bool(bit_exact), "router_picks_bit_exact": bool(picks_exact),
-            "layer_max_abs_vs_cpu_oracle": worst, "layer_cosine_vs_cpu_oracle": cosine, "ranks": world,
+    ok = bit_exact and picks_exact and cosine >= 0.9999 and worst_fp32 <= 2e-2 and worst <= max(2e-2, step)
+    return {"ok": bool(ok), "ordered_reduction_bit_exact_on_every_rank": bool(bit_exact),
+            "router_picks_bit_exact": bool(picks_exact), "layer_max_abs_vs_cpu_oracle": worst,
+            "layer_cosine_vs_cpu_oracle": cosine, "fp32_sums_max_abs_vs_cpu_oracle": worst_fp32,
+            "bfloat16_step_at_largest_output": step, "ranks": world,
             "what": "one more step after the timed regions: every rank's result against the oracle's rank-ordered "
-                    "sum of the FP32 rows the ranks published over NVLink, and against the oracle's whole layer"}
+                    "sum of the FP32 rows the ranks published over NVLink (bit for bit), the ranks' FP32 sums before "
+                    "the one rounding and the bfloat16 layer output against the oracle's whole layer (max-abs 2e-2, "
+                    "or one bfloat16 step where outputs reach magnitude 4; cosine 0.9999)"}
 
 
 def workload_config(args, config, world):

@@ -85,19 +85,20 @@ MUST_CHECK result_status exl3_prefill_prepare(const struct exl3_prefill_record *
 
 /* B200 extension (no reference counterpart: its step is a router launch, five expert launches, a row sum and a
  * one-CTA exchange): ONE decode step of a rank's whole expert layer in the four launches of struct
- * exl3_layer_route_record (router with input transform; gate/up; down with row sums and READY; the reduction).
+ * exl3_layer_route_record (router with input transform; gate/up; down; row sums, READY and the reduction).
  * route.moe is read as exl3_moe_prepare reads it, with the scratch sizes of exl3_layer_sizes; publish names the
  * reduction's region (two parity slots of parity_stride bytes, the FP32 rows at input_offset inside a slot, behind
  * EXL3_LAYER_SIGNAL_BYTES of signal lines), the peer table (struct ordered_collective_peer [rank_count]), the status
- * block and the step block; result_offset: bfloat16 [row_capacity][input_size]. product_ctas: the grid of the two
- * product launches (0: five CTAs on each of 148 SMs). The region must be zero at load. */
+ * block and the step block; result_offset: bfloat16 [row_capacity][input_size]. gate_up_runs, down_runs (powers of two
+ * up to EXL3_LAYER_MAXIMUM_RUNS that divide the products' 128-input blocks): the cut of K of the two product
+ * launches, 0 for this library's choice from the shapes. The region must be zero at load. */
 struct exl3_layer_description {
 	struct exl3_layer_route_record route;
 	struct exl3_layer_publish_arguments publish;
 	uint64_t result_offset;
 	uint64_t arena_byte_count;
-	uint32_t product_ctas;
-	uint32_t reserved_zero;
+	uint32_t gate_up_runs;
+	uint32_t down_runs;
 };
 /* Scratch bytes of the layer form (see struct exl3_layer_route_record): operands as exl3_moe_sizes gives them;
  * products for EXL3_LAYER_MAXIMUM_RUNS runs; counters with the layer's own words. The two split counts are zero. */

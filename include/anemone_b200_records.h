@@ -224,33 +224,31 @@ struct step_block {
  *                            (router_select_b200's bytes) and the live job count; the others transform the rows into
  *                            the FP16 operands of every (pair, gate or up): no launch and no trip through memory
  *                            stands between the router and the transform.
- *   exl3_layer_gate_up       grid C x 128: the products of all live (job, gate or up, 128 outputs) items, as ONE
- *                            sequence of K rounds cut in C equal runs (a CTA streams its run, which may cover the end
- *                            of one item and the start of the next), so that every SM is busy to the end whatever
- *                            the number of live experts and the rank's share of the columns; the CTA that completes
- *                            a (job, 128 outputs) adds the runs' FP32 partial sums in ascending K order from +0 and
- *                            applies the transform, SwiGLU and the down-side transform (exl3_moe_gate_up's epilogue).
- *   exl3_layer_down_publish  the same for down; the CTA that completes a (job, 128 outputs) writes the pair outputs;
- *                            the CTA that completes a 128-column group over ALL live jobs adds the rows' pairs in
- *                            ascending slot order from +0 straight into this rank's rows of the reduction slot, and
- *                            the CTA that completes the last group stores this rank's READY word into EVERY rank's
- *                            slot (plain peer stores), so that nobody polls across NVLink.
- *   ordered_reduce_flags     (kernel file "kernel_ordered_b200") waits for the READY words in its OWN memory, pulls
- *                            the ranks' rows by peer loads, adds them in rank order from +0, rounds once to bfloat16,
- *                            and stores its DONE word into every rank's slot.
+ *   exl3_layer_gate_up       grid (inner_size / 128 * runs, jobs, 2) x 128: exl3_moe_gate_up's CTAs with the cut of K
+ *                            the preparer was given or chose (the grid tells it); the CTA that completes a (job, 128
+ *                            outputs) adds the runs' FP32 partial sums in ascending K order from +0 and applies the
+ *                            transform, SwiGLU and the down-side transform.
+ *   exl3_layer_down          grid (input_size / 128 * runs, jobs) x 128: the same for down; the CTA that completes a
+ *                            (job, 128 outputs) writes the pair outputs (transform, scale, route weight).
+ *   ordered_publish_reduce_flags  (kernel file "kernel_ordered_b200") adds each row's pairs in ascending slot order
+ *                            from +0 straight into this rank's rows of the reduction slot, stores this rank's READY
+ *                            word into EVERY rank's slot (plain peer stores), waits for the ranks' READY words in
+ *                            its OWN memory (nobody polls across NVLink), pulls the ranks' rows by peer loads, adds
+ *                            them in rank order from +0, rounds once to bfloat16, and stores its DONE word into
+ *                            every rank's slot.
  * A slot of the reduction region in this form (two parity slots, parity_stride apart): 16 READY lines of 128 bytes
  * (line s: a 64-bit sequence written only by rank s), 16 DONE lines likewise, one local line (a block counter at
  * byte 64, the sequence of the slot's previous use at byte 72), then the FP32 rows at input_offset.
- * The cut of a product depends on the live job count and the grid, not on the data: the same inputs give the same
- * bits on every run. partial sums: FP32 [2][EXL3_LAYER_MAXIMUM_RUNS][pair_count][inner_size] for gate/up, reused as
- * [EXL3_LAYER_MAXIMUM_RUNS][pair_count][input_size] for down (run 0 is also where the pair outputs go); counters:
- * what struct exl3_moe_record asks for, then EXL3_LAYER_COUNTER_WORDS + input_size / 128 more uint32, zero at load.
+ * The cut of a product depends on the prepared shapes alone: the same inputs give the same bits on every run.
+ * partial sums: FP32 [2][runs][pair_count][inner_size] for gate/up, reused as [runs][pair_count][input_size] for down
+ * (run 0 is also where the pair outputs go), sized for EXL3_LAYER_MAXIMUM_RUNS runs; counters:
+ * what struct exl3_moe_record asks for, then EXL3_LAYER_COUNTER_WORDS more uint32, zero at load.
  * ---------------------------------------------------------------------------------------------------------- */
 #define EXL3_LAYER_KERNEL_FILE "kernel_exl3_layer"
 #define EXL3_LAYER_LAUNCHES 4u
-#define EXL3_LAYER_MAXIMUM_RUNS 8u /* runs of one item at most: a run is at least a seventh of an item's rounds */
-#define EXL3_LAYER_ROUTE_THREADS 256u
-#define EXL3_LAYER_COUNTER_WORDS 4u /* live job count, group counter of the publish, failed flag, reserved */
+#define EXL3_LAYER_MAXIMUM_RUNS 8u /* runs of K of one product at most */
+#define EXL3_LAYER_ROUTE_THREADS 1024u
+#define EXL3_LAYER_COUNTER_WORDS 4u /* the live job count and three reserved words */
 #define EXL3_LAYER_READY_LINE 0u
 #define EXL3_LAYER_DONE_LINE 16u
 #define EXL3_LAYER_LOCAL_LINE 32u
@@ -271,6 +269,7 @@ struct exl3_layer_route_record {
 	float route_scale;
 };
 
+/* what exl3_layer_prepare is told about the reduction */
 struct exl3_layer_publish_arguments {
 	uint64_t peer_table_offset; /* struct ordered_collective_peer [rank_count] */
 	uint64_t region_offset;
@@ -283,11 +282,6 @@ struct exl3_layer_publish_arguments {
 	uint32_t rank;
 	uint32_t row_capacity;
 	uint32_t reserved_zero;
-};
-
-struct exl3_layer_down_record {
-	struct exl3_moe_record moe;
-	struct exl3_layer_publish_arguments publish;
 };
 
 /* ------------------------------------------------------------------------------------------------------------
@@ -379,6 +373,18 @@ struct ordered_reduce_bf16_arguments {
 	uint64_t status_offset;
 	uint32_t width; /* elements of a row */
 	uint32_t mode;
+};
+
+/* B200 extension: row sums, READY, the rank-ordered sum, one rounding and DONE of a decode step in one launch
+ * (ordered_publish_reduce_flags; the slot layout is the flags form's, see struct exl3_layer_route_record).
+ * collective is read as struct ordered_reduce_bf16_arguments reads it. */
+#define KERNEL_ORDERED_PUBLISH_REDUCE_FLAGS "ordered_publish_reduce_flags"
+struct ordered_publish_reduce_arguments {
+	struct ordered_collective_arguments collective;
+	uint64_t status_offset;
+	uint64_t pair_output_offset; /* FP32 [rows * pairs_per_row][width] */
+	uint32_t width;
+	uint32_t pairs_per_row;
 };
 
 /* B200 extension: the row sum of a rank written straight into its collective input slot of this step's parity
@@ -830,6 +836,7 @@ AB_RECORD_HAS(ordered_collective_peer, 32);
 AB_RECORD_HAS(ordered_collective_arguments, 80);
 AB_RECORD_HAS(ordered_reduce_bf16_arguments, 96);
 AB_RECORD_HAS(ordered_row_sum_publish_arguments, 104);
+AB_RECORD_HAS(ordered_publish_reduce_arguments, 104);
 AB_RECORD_HAS(ordered_push_arguments, 96);
 AB_RECORD_HAS(tp_exchange_arguments, 112);
 AB_RECORD_HAS(ordered_rows_push_arguments, 112);
@@ -838,7 +845,6 @@ AB_RECORD_HAS(router_select_b200_arguments, 88);
 AB_RECORD_HAS(step_input_select_arguments, 40);
 AB_RECORD_HAS(exl3_layer_route_record, 184);
 AB_RECORD_HAS(exl3_layer_publish_arguments, 72);
-AB_RECORD_HAS(exl3_layer_down_record, 184);
 AB_RECORD_HAS(exl3_prefill_tile, 16);
 AB_RECORD_HAS(exl3_prefill_entry, 8);
 AB_RECORD_HAS(exl3_prefill_record, 136);

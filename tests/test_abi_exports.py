@@ -59,7 +59,7 @@ def test_record_sizes_match_the_headers():
               "expert_down_arguments": R.ExpertDown, "trunk_linear_quantized_arguments": R.TrunkLinearQuantized,
               "trunk_hidden_arguments": R.TrunkHidden, "trunk_rows_add_arguments": R.TrunkRowsAdd,
               "exl3_layer_route_record": R.Exl3LayerRoute, "exl3_layer_publish_arguments": R.Exl3LayerPublish,
-              "exl3_layer_down_record": R.Exl3LayerDown}
+              "ordered_publish_reduce_arguments": R.OrderedPublishReduce}
     assert set(declared) == set(mirror)
     for name, record in mirror.items():
         assert C.sizeof(record) == int(declared[name]), name
