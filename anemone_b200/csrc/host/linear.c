@@ -247,23 +247,82 @@ static result_status e4m3_stored_byte_count(const struct matrix_shape_record *sh
 const struct weight_format_operations e4m3_scaled_weight_operations = { .name = "e4m3_scaled",
 									 .stored_byte_count = e4m3_stored_byte_count };
 
-/* a stored E4M3 matrix the trunk kernels can take: its exact bytes, whole loads of 64 inputs, a slice count on offer */
-static uint32_t trunk_matrix_instance(const struct linear_matrix *matrix, const struct linear_kernels_record *kernels)
+#define E4M3_BLOCK128 128u
+static result_status e4m3_block128_stored_byte_count(const struct matrix_shape_record *shape, uint64_t *byte_count_out)
+{
+	if (shape == NULL || byte_count_out == NULL || shape->reserved_must_be_zero != 0 || shape->bits_per_weight != 8 ||
+	    shape->output_size == 0 || shape->input_size == 0 || shape->output_size % LINEAR_OUTPUTS_PER_TILE != 0 ||
+	    shape->input_size % E4M3_BLOCK128 != 0)
+		return STATUS_INVALID_ARGUMENT;
+	*byte_count_out = (uint64_t)shape->output_size * shape->input_size +
+			  (uint64_t)((shape->output_size + E4M3_BLOCK128 - 1u) / E4M3_BLOCK128) *
+				  (shape->input_size / E4M3_BLOCK128) * 4u;
+	return STATUS_OK;
+}
+
+const struct weight_format_operations e4m3_block128_weight_operations = {
+	.name = "e4m3_block128", .stored_byte_count = e4m3_block128_stored_byte_count
+};
+
+/* a stored E4M3 matrix the trunk kernels can take: its exact bytes, whole loads of 64 inputs, a slice count on offer.
+ * handles: the kernels of the matrix's format, by slice instance. */
+static uint32_t trunk_matrix_instance(const struct linear_matrix *matrix, enum weight_format_code format,
+				      const uint32_t *handles)
 {
 	uint64_t bytes = 0;
-	if (matrix->weight_format != WEIGHT_FORMAT_E4M3_SCALED || matrix->reserved_zero != 0 || matrix->wide_form != 0 ||
-	    e4m3_stored_byte_count(&matrix->shape, &bytes) != STATUS_OK || matrix->stored.byte_count != bytes ||
-	    matrix->shape.input_size % LINEAR_VALUES_PER_LOAD != 0 ||
+	const result_status sized = format == WEIGHT_FORMAT_E4M3_BLOCK128 ?
+					    e4m3_block128_stored_byte_count(&matrix->shape, &bytes) :
+					    e4m3_stored_byte_count(&matrix->shape, &bytes);
+	if (matrix->weight_format != format || matrix->reserved_zero != 0 || matrix->wide_form != 0 || sized != STATUS_OK ||
+	    matrix->stored.byte_count != bytes || matrix->shape.input_size % LINEAR_VALUES_PER_LOAD != 0 ||
 	    matrix->stored.byte_offset % WEIGHT_FORMAT_MATRIX_ALIGNMENT_BYTES != 0)
 		return LINEAR_SLICE_INSTANCES;
 	const uint32_t instance = slice_instance(matrix->slice_count, matrix->shape.input_size);
-	return instance < LINEAR_SLICE_INSTANCES && kernels->trunk_linear_quantized[instance] != BACKEND_NO_KERNEL ?
-		       instance :
-		       LINEAR_SLICE_INSTANCES;
+	return instance < LINEAR_SLICE_INSTANCES && handles[instance] != BACKEND_NO_KERNEL ? instance :
+											       LINEAR_SLICE_INSTANCES;
 }
+
+static result_status shared_expert_prepare(const struct linear_shared_expert_description *description,
+					   uint64_t arena_byte_count, const struct linear_kernels_record *kernels,
+					   enum weight_format_code format, const uint32_t *handles,
+					   struct kernel_launch *launches_out);
 
 result_status linear_shared_expert_prepare(const struct linear_shared_expert_description *description,
 					   uint64_t arena_byte_count, const struct linear_kernels_record *kernels,
+					   struct kernel_launch *launches_out)
+{
+	if (kernels == NULL)
+		return STATUS_INVALID_ARGUMENT;
+	return shared_expert_prepare(description, arena_byte_count, kernels, WEIGHT_FORMAT_E4M3_SCALED,
+				     kernels->trunk_linear_quantized, launches_out);
+}
+
+result_status linear_shared_expert_block128_prepare(const struct linear_shared_expert_description *description,
+						    uint64_t arena_byte_count,
+						    const struct linear_kernels_record *kernels,
+						    const struct backend_operations *backend, struct device_card *card,
+						    struct kernel_launch *launches_out)
+{
+	if (kernels == NULL || backend == NULL || backend->kernel_prepare == NULL || card == NULL)
+		return STATUS_INVALID_ARGUMENT;
+	uint32_t handles[LINEAR_SLICE_INSTANCES];
+	for (uint32_t instance = 0; instance < LINEAR_SLICE_INSTANCES; instance++) {
+		char name[48];
+		(void)snprintf(name, sizeof(name), "trunk_linear_block128_%u", slice_counts[instance]);
+		handles[instance] = BACKEND_NO_KERNEL;
+		const result_status status = backend->kernel_prepare(card, KERNEL_FILE_TRUNK_LINEAR, name,
+								     sizeof(struct trunk_linear_quantized_arguments),
+								     &handles[instance]);
+		if (status != STATUS_OK)
+			return status;
+	}
+	return shared_expert_prepare(description, arena_byte_count, kernels, WEIGHT_FORMAT_E4M3_BLOCK128, handles,
+				     launches_out);
+}
+
+static result_status shared_expert_prepare(const struct linear_shared_expert_description *description,
+					   uint64_t arena_byte_count, const struct linear_kernels_record *kernels,
+					   enum weight_format_code format, const uint32_t *handles,
 					   struct kernel_launch *launches_out)
 {
 	if (description == NULL || kernels == NULL || launches_out == NULL || description->row_count == 0 ||
@@ -273,8 +332,9 @@ result_status linear_shared_expert_prepare(const struct linear_shared_expert_des
 		return STATUS_INVALID_ARGUMENT;
 	const struct linear_matrix *const gate = &description->gate, *const up = &description->up,
 				   *const down = &description->down;
-	const uint32_t gate_instance = trunk_matrix_instance(gate, kernels), up_instance = trunk_matrix_instance(up, kernels);
-	const uint32_t down_instance = trunk_matrix_instance(down, kernels);
+	const uint32_t gate_instance = trunk_matrix_instance(gate, format, handles);
+	const uint32_t up_instance = trunk_matrix_instance(up, format, handles);
+	const uint32_t down_instance = trunk_matrix_instance(down, format, handles);
 	if (gate_instance == LINEAR_SLICE_INSTANCES || up_instance != gate_instance ||
 	    down_instance == LINEAR_SLICE_INSTANCES || gate->shape.input_size != up->shape.input_size ||
 	    gate->shape.output_size != up->shape.output_size || down->shape.input_size != gate->shape.output_size)
@@ -333,7 +393,7 @@ result_status linear_shared_expert_prepare(const struct linear_shared_expert_des
 									 I,
 									 description->row_count };
 	struct kernel_launch launches[LINEAR_SHARED_EXPERT_LAUNCH_COUNT];
-	prepare_launch_fill(&launches[LINEAR_SHARED_EXPERT_GATE_UP], kernels->trunk_linear_quantized[gate_instance],
+	prepare_launch_fill(&launches[LINEAR_SHARED_EXPERT_GATE_UP], handles[gate_instance],
 			    2u * I / LINEAR_OUTPUTS_PER_TILE, 1, 1, 32u * gate->slice_count, 0, &gate_up_arguments,
 			    sizeof(gate_up_arguments));
 	prepare_launch_fill(&launches[LINEAR_SHARED_EXPERT_HIDDEN], kernels->trunk_hidden,
@@ -342,7 +402,7 @@ result_status linear_shared_expert_prepare(const struct linear_shared_expert_des
 	prepare_launch_fill(&launches[LINEAR_SHARED_EXPERT_QUANTIZE], kernels->activation_quantize,
 			    I / LINEAR_VALUES_PER_LOAD, description->row_count, 1, 32, 0, &quantize_arguments,
 			    sizeof(quantize_arguments));
-	prepare_launch_fill(&launches[LINEAR_SHARED_EXPERT_DOWN], kernels->trunk_linear_quantized[down_instance],
+	prepare_launch_fill(&launches[LINEAR_SHARED_EXPERT_DOWN], handles[down_instance],
 			    O / LINEAR_OUTPUTS_PER_TILE, 1, 1, 32u * down->slice_count, 0, &down_arguments,
 			    sizeof(down_arguments));
 	memcpy(launches_out, launches, sizeof(launches));

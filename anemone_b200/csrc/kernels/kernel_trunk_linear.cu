@@ -5,6 +5,9 @@
  * 467-539; contract include/anemone/linear_records.h:100-118, 308-330, 352-362), new for sm_100a.
  *
  *   trunk_linear_quantized_<S>  grid ((output_size[0] + output_size[1]) / 16), block 32 S: bfloat16 [row][output]
+ *   trunk_linear_block128_<S>   the same for WEIGHT_FORMAT_E4M3_BLOCK128 (no counterpart in the reference): the same
+ *                               bytes, one FP32 scale per 128 outputs by 128 inputs instead of the E8M0 codes; chain =
+ *                               fma(p, scale * 2^(activation code - 127 + 16), chain)
  *   trunk_hidden_entry          grid (ceil(width / 256), vectors), block 256: the hidden step, route weight 1
  *   trunk_rows_add_entry        grid (ceil(width / 256), rows), block 256: FP32 row sums += bfloat16 rows
  * A block owns one tile of 16 outputs of one of the matrices; the tile's bytes for all of K are contiguous in the
@@ -60,7 +63,17 @@ __device__ __forceinline__ float block_scale(uint32_t weight_code, uint32_t acti
 	return field < 1 ? 0.0f : __uint_as_float((uint32_t)(field > 254 ? 254 : field) << 23);
 }
 
-template <uint32_t S>
+/* the same factor for a weight scale that is an FP32 number (one per 128 by 128 weights): scale * 2^(activation code
+ * - 127 + 16); the product of a number and a power of two is exact unless it leaves the normal range */
+__device__ __forceinline__ float block128_scale(float weight_scale, uint32_t activation_code)
+{
+	const uint32_t field = activation_code + 16u;
+	return __fmul_rn(weight_scale, __uint_as_float((field > 254u ? 254u : field) << 23));
+}
+
+/* BLOCK128 false: WEIGHT_FORMAT_E4M3_SCALED (the reference's: one E8M0 code per 32 by 32 weights behind the bytes);
+ * true: WEIGHT_FORMAT_E4M3_BLOCK128 (one FP32 scale per 128 outputs by 128 inputs behind the same bytes). */
+template <uint32_t S, bool BLOCK128>
 __device__ __forceinline__ void trunk_linear_quantized(const struct trunk_linear_quantized_arguments &arguments,
 						       unsigned char *arena)
 {
@@ -77,6 +90,8 @@ __device__ __forceinline__ void trunk_linear_quantized(const struct trunk_linear
 	const uint32_t even_row = 2u * place < rows ? 2u * place : 0u, odd_row = 2u * place + 1u < rows ? 2u * place + 1u : 0u;
 	const uint4 *const bytes = reinterpret_cast<const uint4 *>(matrix) + ((uint64_t)tile * groups) * WARP + lane;
 	const unsigned char *const scales = matrix + (uint64_t)outputs * inputs + (uint64_t)(tile / 2u) * groups;
+	const float *const scales128 =
+		reinterpret_cast<const float *>(matrix + (uint64_t)outputs * inputs) + (uint64_t)(tile / 8u) * (groups / 4u);
 	/* operand order of a vector: per load of 64 values, lane place t holds eight 32-bit registers (two 128-bit loads) */
 	const uint4 *const fed =
 		reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(arena + arguments.operands_offset) +
@@ -114,9 +129,16 @@ __device__ __forceinline__ void trunk_linear_quantized(const struct trunk_linear
 							place_odd_bytes(words[2u * step + 1u]) };
 				mma_f16(sum, a, fed_words[2u * step], fed_words[2u * step + 1u]);
 			}
-			const uint32_t weight_code = scales[group];
-			const float even = block_scale(weight_code, exponents_even[group]);
-			const float odd = block_scale(weight_code, exponents_odd[group]);
+			float even, odd;
+			if (BLOCK128) {
+				const float weight_scale = __ldg(scales128 + group / 4u);
+				even = block128_scale(weight_scale, exponents_even[group]);
+				odd = block128_scale(weight_scale, exponents_odd[group]);
+			} else {
+				const uint32_t weight_code = scales[group];
+				even = block_scale(weight_code, exponents_even[group]);
+				odd = block_scale(weight_code, exponents_odd[group]);
+			}
 			chains[0] = __fmaf_rn(sum[0], even, chains[0]);
 			chains[1] = __fmaf_rn(sum[1], odd, chains[1]);
 			chains[2] = __fmaf_rn(sum[2], even, chains[2]);
@@ -148,7 +170,12 @@ __device__ __forceinline__ void trunk_linear_quantized(const struct trunk_linear
 	extern "C" __global__ void __launch_bounds__(32 * S)                                                   \
 		trunk_linear_quantized_##S(struct trunk_linear_quantized_arguments arguments, unsigned char *arena) \
 	{                                                                                                      \
-		trunk_linear_quantized<S>(arguments, arena);                                                   \
+		trunk_linear_quantized<S, false>(arguments, arena);                                            \
+	}                                                                                                      \
+	extern "C" __global__ void __launch_bounds__(32 * S)                                                   \
+		trunk_linear_block128_##S(struct trunk_linear_quantized_arguments arguments, unsigned char *arena) \
+	{                                                                                                      \
+		trunk_linear_quantized<S, true>(arguments, arena);                                             \
 	}
 TRUNK_ENTRIES(1)
 TRUNK_ENTRIES(2)

@@ -18,19 +18,25 @@ from .moe import LINE, SIGNAL_BYTES, rank_columns
 
 WEIGHT_FORMAT_E2M1_SCALED = 3
 WEIGHT_FORMAT_E4M3_SCALED = 5
+WEIGHT_FORMAT_E4M3_BLOCK128 = 6
 
 
 def matrix_bytes(outputs, inputs):
     return outputs * inputs // 2 + outputs * inputs // 32
 
 
-def shared_matrix_bytes(outputs, inputs):
+def shared_matrix_bytes(outputs, inputs, block128=False):
+    """Stored bytes of an E4M3 matrix: one E8M0 code per 32 by 32 weights (the reference's format), or one FP32 scale
+    per 128 by 128 (the original-weights checkpoints' block-scaled FP8)."""
+    if block128:
+        return outputs * inputs + (outputs + 127) // 128 * (inputs // 128) * 4
     return outputs * inputs + (outputs + 31) // 32 * (inputs // 32)
 
 
 class MxLayout:
-    def __init__(self, config, rank_count, rank, pool_entries=0):
+    def __init__(self, config, rank_count, rank, pool_entries=0, block128=False):
         assert config.shared in (0, 1)
+        self.block128 = block128
         self.pool_entries = pool_entries
         self.config = c = config
         self.inner_local = I = rank_columns(c.inner, rank_count, rank)[1]
@@ -71,18 +77,20 @@ class MxLayout:
             self.matrices.append((layout.take(matrix_bytes(I, H), 64), layout.take(matrix_bytes(I, H), 64),
                                   layout.take(matrix_bytes(H, I), 64)))
         self.weights_end = layout.cursor
-        self.shared_matrices = (layout.take(shared_matrix_bytes(I, H), 64), layout.take(shared_matrix_bytes(I, H), 64),
-                                layout.take(shared_matrix_bytes(H, I), 64)) if c.shared else ()
+        self.shared_matrices = (layout.take(shared_matrix_bytes(I, H, block128), 64),
+                                layout.take(shared_matrix_bytes(I, H, block128), 64),
+                                layout.take(shared_matrix_bytes(H, I, block128), 64)) if c.shared else ()
         self.arena_bytes = api.align(layout.cursor, 4096) + 4096
 
 
 class MxLayer:
     def __init__(self, card, config, matrices, rank=0, rank_count=1, slices=(4, 4), shared_matrices=None,
-                 shared_slices=(2, 2), pool_entries=0):
+                 shared_slices=(2, 2), pool_entries=0, block128=False):
         """matrices: iterable over the routed experts of this rank's (gate, up, down) stored MXFP4 bytes;
-        shared_matrices: the always-on expert's (gate, up, down) stored E4M3 bytes, where the configuration has one."""
+        shared_matrices: the always-on expert's (gate, up, down) stored E4M3 bytes, where the configuration has one:
+        WEIGHT_FORMAT_E4M3_SCALED, or with block128 WEIGHT_FORMAT_E4M3_BLOCK128 (one FP32 scale per 128 by 128)."""
         self.card, self.config = card, config
-        self.layout = L = MxLayout(config, rank_count, rank, pool_entries)
+        self.layout = L = MxLayout(config, rank_count, rank, pool_entries, block128)
         assert card.arena_bytes >= L.arena_bytes
         self.rank, self.rank_count = rank, rank_count
         self.weight_bytes = 0
@@ -96,7 +104,7 @@ class MxLayer:
         if config.shared:
             for which, data in enumerate(shared_matrices):
                 assert data.size == shared_matrix_bytes(*((L.inner_local, config.hidden) if which < 2 else
-                                                          (config.hidden, L.inner_local)))
+                                                          (config.hidden, L.inner_local)), block128)
                 card.upload(L.shared_matrices[which], data)
                 self.weight_bytes += data.size
         for offset, size in ((L.peer_table, 16 * 32), (L.status, 16), (L.step, 256), (L.region, 2 * L.parity_stride)):
@@ -148,8 +156,11 @@ class MxLayer:
         if c.shared:
             shared = R.LinearSharedExpertDescription()
             for which, (name, (o, i)) in enumerate((("gate", (I, H)), ("up", (I, H)), ("down", (H, I)))):
-                setattr(shared, name, R.LinearMatrix(R.LinearRange(L.shared_matrices[which], shared_matrix_bytes(o, i)),
-                                                     R.MatrixShape(o, i, 8, 0), WEIGHT_FORMAT_E4M3_SCALED,
+                setattr(shared, name, R.LinearMatrix(R.LinearRange(L.shared_matrices[which],
+                                                                   shared_matrix_bytes(o, i, L.block128)),
+                                                     R.MatrixShape(o, i, 8, 0),
+                                                     WEIGHT_FORMAT_E4M3_BLOCK128 if L.block128 else
+                                                     WEIGHT_FORMAT_E4M3_SCALED,
                                                      shared_slices[0 if which < 2 else 1], 0, 0))
             shared.codes, shared.exponents, shared.operands = span("codes"), span("exponents"), span("operands")
             for name in L.shared_sizes:
@@ -157,9 +168,18 @@ class MxLayer:
             shared.row_count, shared.activation_limit = c.row_capacity, c.activation_limit
             lib.linear_shared_expert_prepare.argtypes = [C.POINTER(R.LinearSharedExpertDescription), C.c_uint64,
                                                          C.POINTER(R.LinearKernels), C.POINTER(R.KernelLaunch)]
+            lib.linear_shared_expert_block128_prepare.argtypes = [C.POINTER(R.LinearSharedExpertDescription), C.c_uint64,
+                                                                  C.POINTER(R.LinearKernels),
+                                                                  C.POINTER(api.BackendOperations), C.c_void_p,
+                                                                  C.POINTER(R.KernelLaunch)]
             four = (R.KernelLaunch * 4)()
-            api.check(lib.linear_shared_expert_prepare(C.byref(shared), card.arena_bytes, C.byref(kernels), four),
-                      "linear_shared_expert_prepare")
+            if L.block128:
+                api.check(lib.linear_shared_expert_block128_prepare(C.byref(shared), card.arena_bytes, C.byref(kernels),
+                                                                    card.ops_pointer, card.handle, four),
+                          "linear_shared_expert_block128_prepare")
+            else:
+                api.check(lib.linear_shared_expert_prepare(C.byref(shared), card.arena_bytes, C.byref(kernels), four),
+                          "linear_shared_expert_prepare")
             lib.linear_rows_add_prepare.argtypes = [C.POINTER(R.LinearRange), C.POINTER(R.LinearRange), C.c_uint32,
                                                     C.c_uint32, C.c_uint64, C.POINTER(api.BackendOperations),
                                                     C.c_void_p, C.POINTER(R.KernelLaunch)]

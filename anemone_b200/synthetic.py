@@ -86,3 +86,12 @@ def e4m3_matrix(rng, outputs, inputs):
     codes |= (rng.integers(0, 2, size=outputs * inputs, dtype=np.uint8) << 7)
     scales = (127 + rng.integers(-9, -4, size=(outputs + 31) // 32 * (inputs // 32))).astype(np.uint8)
     return np.concatenate([codes, scales])
+
+
+def e4m3_block128_matrix(rng, outputs, inputs):
+    """Stored bytes of one WEIGHT_FORMAT_E4M3_BLOCK128 matrix (the block-scaled FP8 of the original-weights profile):
+    E4M3 bytes that are numbers, then one FP32 scale per 128 outputs by 128 inputs drawn U(0.5, 2) / 448."""
+    codes = rng.integers(0, 127, size=outputs * inputs, dtype=np.uint8)
+    codes |= (rng.integers(0, 2, size=outputs * inputs, dtype=np.uint8) << 7)
+    scales = (rng.uniform(0.5, 2.0, size=(outputs + 127) // 128 * (inputs // 128)) / 448.0).astype(np.float32)
+    return np.concatenate([codes, scales.view(np.uint8)])

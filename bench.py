@@ -528,9 +528,10 @@ def run_reference_kernels(args, api, base, draw_k3, local_rank):
 
 
 def run_original_weights(args, api, base, rank, world, local_rank, dist, barrier, maximum):
-    """cfg5: routed experts MXFP4 (E8M0 scales 2^-8 .. 2^-4), the always-on expert E4M3 with one E8M0 scale per 32 by 32
-    weights (the reference's FP8 format; the configuration's 128 x 128 FP32-scaled variant is not in the reference and
-    not built), E4M3 block-quantized activations, decode M = 8, tensor parallel by intermediate columns."""
+    """cfg5: routed experts MXFP4 (E8M0 scales 2^-8 .. 2^-4), the always-on expert E4M3 with one FP32 scale per 128 by 128
+    weights drawn U(0.5, 2) / 448 (the configuration's block-scaled FP8; the reference's own E4M3 format, one E8M0 code
+    per 32 by 32 weights, is the library's other option), E4M3 block-quantized activations, decode M = 8, tensor
+    parallel by intermediate columns."""
     from anemone_b200 import records as R
     from anemone_b200 import synthetic
     from anemone_b200.moe import MoeConfig
@@ -539,7 +540,7 @@ def run_original_weights(args, api, base, rank, world, local_rank, dist, barrier
     config = MoeConfig(hidden=base.hidden, inner=base.inner, experts=base.experts, shared=1, picks=base.picks,
                        row_capacity=rows, activation_limit=7.0)
     pool_entries = warmup + steps + 1  # the last: the untimed step behind the barrier
-    layout = MxLayout(config, world, rank, pool_entries)
+    layout = MxLayout(config, world, rank, pool_entries, block128=True)
     H, I = config.hidden, layout.inner_local
     card = api.Card(local_rank, layout.arena_bytes)
 
@@ -547,10 +548,10 @@ def run_original_weights(args, api, base, rank, world, local_rank, dist, barrier
         rng = np.random.default_rng([SEED, 2000 + expert, rank])
         return (synthetic.mx_matrix(rng, I, H), synthetic.mx_matrix(rng, I, H), synthetic.mx_matrix(rng, H, I))
     always_rng = np.random.default_rng([SEED, 2999, rank])
-    always = (synthetic.e4m3_matrix(always_rng, I, H), synthetic.e4m3_matrix(always_rng, I, H),
-              synthetic.e4m3_matrix(always_rng, H, I))
+    always = (synthetic.e4m3_block128_matrix(always_rng, I, H), synthetic.e4m3_block128_matrix(always_rng, I, H),
+              synthetic.e4m3_block128_matrix(always_rng, H, I))
     layer = MxLayer(card, config, (draw(expert) for expert in range(config.experts)), rank=rank, rank_count=world,
-                    slices=(2, 2), shared_matrices=always, pool_entries=pool_entries)
+                    slices=(2, 2), shared_matrices=always, pool_entries=pool_entries, block128=True)
     if dist is None:
         layer.connect_local([layer])
     else:
@@ -618,7 +619,7 @@ def run_original_weights(args, api, base, rank, world, local_rank, dist, barrier
             "roofline": roofline, "dtype": "e2m1 x e4m3 -> f32",
             "config": {"workload": "cfg5 original-weights MoE layer decode: %d routed MXFP4 experts (E2M1, one E8M0 "
                                    "scale per 32 inputs, exponents -8..-4), top-%d, 1 always-on expert E4M3 with one "
-                                   "E8M0 scale per 32x32 weights, hidden %d, intermediate %d, M=%d" %
+                                   "FP32 scale per 128x128 weights U(0.5,2)/448, hidden %d, intermediate %d, M=%d" %
                                    (config.experts, config.picks, H, config.inner, rows),
                        "parallelism": "tp%d by intermediate columns, ordered FP32->bf16 reduce" % world,
                        "l2": "inputs larger than L2: every step routes to a different expert set; a step's inputs are taken "

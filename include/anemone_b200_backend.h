@@ -60,7 +60,10 @@ enum weight_format_code {
 	WEIGHT_FORMAT_E2M1_SCALED = 3,
 	WEIGHT_FORMAT_INT4_SCALED = 4,
 	WEIGHT_FORMAT_E4M3_SCALED = 5,
-	WEIGHT_FORMAT_COUNT = 6
+	WEIGHT_FORMAT_COUNT = 6,
+	/* B200 extension, behind the reference's codes: E4M3 bytes in WEIGHT_FORMAT_E4M3_SCALED's order with one FP32 scale
+	 * per 128 outputs by 128 inputs (the block-scaled FP8 of the original-weights checkpoints) */
+	WEIGHT_FORMAT_E4M3_BLOCK128 = 6
 };
 
 struct matrix_shape_record {

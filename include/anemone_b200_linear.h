@@ -138,6 +138,18 @@ MUST_CHECK result_status linear_shared_expert_prepare(const struct linear_shared
 						      const struct linear_kernels_record *kernels,
 						      struct kernel_launch *launches_out);
 
+/* B200 extension (no counterpart in the reference, whose E4M3 format is one E8M0 code per 32 by 32 weights): the
+ * always-on expert with WEIGHT_FORMAT_E4M3_BLOCK128 matrices: stored bytes = the E4M3 bytes in
+ * WEIGHT_FORMAT_E4M3_SCALED's lane order, then FP32 scales [ceil(output_size / 128)][input_size / 128]; input sizes
+ * multiples of 128. Everything else as linear_shared_expert_prepare (same description, same four launches, the hidden
+ * step and the quantization shared); the kernels are "trunk_linear_block128_<S>", prepared here. */
+MUST_CHECK result_status linear_shared_expert_block128_prepare(const struct linear_shared_expert_description *description,
+							       uint64_t arena_byte_count,
+							       const struct linear_kernels_record *kernels,
+							       const struct backend_operations *backend,
+							       struct device_card *card, struct kernel_launch *launches_out);
+extern const struct weight_format_operations e4m3_block128_weight_operations;
+
 /* B200 extension (the reference joins the two in its FFN join, outside this path): one launch of
  * trunk_rows_add_entry: FP32 sums [row_count][width] += bfloat16 values [row_count][width]. */
 MUST_CHECK result_status linear_rows_add_prepare(const struct linear_range *sums, const struct linear_range *values,

@@ -123,5 +123,16 @@ void orc_shared_expert(const struct trunk_linear_quantized_arguments *gate_up, c
 		       const struct activation_quantize_arguments *quantize,
 		       const struct trunk_linear_quantized_arguments *down, uint32_t slices_gate_up, uint32_t slices_down,
 		       unsigned char *arena);
+/* the same three for WEIGHT_FORMAT_E4M3_BLOCK128 (one FP32 scale per 128 outputs by 128 inputs; not a format of the
+ * reference: the chain rule is its own with that scale in the place of 2^(weight code - 127)) */
+void orc_e4m3_block128_lay_out(const uint8_t *codes, const float *scales, uint32_t outputs, uint32_t inputs,
+			       uint8_t *stored_out);
+uint16_t orc_trunk_output_block128(const uint8_t *stored, uint32_t outputs, uint32_t inputs, uint32_t output,
+				   const uint8_t *codes, const uint8_t *exponents, uint32_t slices);
+void orc_shared_expert_block128(const struct trunk_linear_quantized_arguments *gate_up,
+				const struct trunk_hidden_arguments *hidden,
+				const struct activation_quantize_arguments *quantize,
+				const struct trunk_linear_quantized_arguments *down, uint32_t slices_gate_up,
+				uint32_t slices_down, unsigned char *arena);
 
 #endif

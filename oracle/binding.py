@@ -98,6 +98,12 @@ def load_oracle():
     lib.orc_trunk_output.argtypes = [u8, C.c_uint32, C.c_uint32, C.c_uint32, u8, u8, C.c_uint32]
     lib.orc_shared_expert.restype = None
     lib.orc_shared_expert.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, u8]
+    lib.orc_shared_expert_block128.restype = None
+    lib.orc_shared_expert_block128.argtypes = lib.orc_shared_expert.argtypes
+    lib.orc_trunk_output_block128.restype = C.c_uint16
+    lib.orc_trunk_output_block128.argtypes = lib.orc_trunk_output.argtypes
+    lib.orc_e4m3_block128_lay_out.restype = None
+    lib.orc_e4m3_block128_lay_out.argtypes = [u8, f32p, C.c_uint32, C.c_uint32, u8]
     lib.orc_mx_experts.restype = None
     lib.orc_mx_experts.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint64,
                                    C.c_uint64, C.c_uint64, u8]

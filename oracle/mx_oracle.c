@@ -260,12 +260,17 @@ void orc_e4m3_weights_lay_out(const uint8_t *codes, const uint8_t *scales, uint3
 }
 
 /* One output of one row of trunk_linear_quantized_<S>: as orc_mx_output with E4M3 weights and one scale per 32 outputs
- * by 32 inputs. codes/exponents: the row's NATURAL-order E4M3 codes and its block exponents. */
-uint16_t orc_trunk_output(const uint8_t *stored, uint32_t outputs, uint32_t inputs, uint32_t output, const uint8_t *codes,
-			  const uint8_t *exponents, uint32_t slices)
+ * by 32 inputs (block128 0), or one FP32 scale per 128 outputs by 128 inputs behind the same bytes (block128 1: the
+ * original-weights checkpoints' block-scaled FP8, which the reference does not have; the chain rule is the
+ * reference's, include/anemone/linear_records.h:45-99, with that scale in the place of 2^(weight code - 127)).
+ * codes/exponents: the row's NATURAL-order E4M3 codes and its block exponents. */
+static uint16_t trunk_output(const uint8_t *stored, uint32_t outputs, uint32_t inputs, uint32_t output,
+			     const uint8_t *codes, const uint8_t *exponents, uint32_t slices, int block128)
 {
 	const uint32_t loads = inputs / 64u;
 	const uint8_t *const scales = stored + (size_t)outputs * inputs + (size_t)(output / 32u) * (inputs / 32u);
+	const float *const scales128 =
+		(const float *)(const void *)(stored + (size_t)outputs * inputs) + (size_t)(output / 128u) * (inputs / 128u);
 	float sum = 0.0f;
 	for (uint32_t slice = 0; slice < slices; slice++) {
 		float chain = 0.0f;
@@ -277,7 +282,8 @@ uint16_t orc_trunk_output(const uint8_t *stored, uint32_t outputs, uint32_t inpu
 					exact += orc_e4m3_value(stored[e4m3_place(inputs, output, 32u * block + index)]) *
 						 orc_e4m3_value(codes[32u * block + index]);
 				const float p = (float)exact;
-				const float scale = (float)ldexp(1.0, (int)scales[block] - 127 + (int)exponents[block] - 127);
+				const float scale = block128 ? scales128[block / 4u] * (float)ldexp(1.0, (int)exponents[block] - 127) :
+							       (float)ldexp(1.0, (int)scales[block] - 127 + (int)exponents[block] - 127);
 				chain = fmaf(p, scale, chain);
 			}
 		sum = sum + chain;
@@ -285,12 +291,35 @@ uint16_t orc_trunk_output(const uint8_t *stored, uint32_t outputs, uint32_t inpu
 	return orc_bfloat16_bits(sum);
 }
 
+uint16_t orc_trunk_output(const uint8_t *stored, uint32_t outputs, uint32_t inputs, uint32_t output, const uint8_t *codes,
+			  const uint8_t *exponents, uint32_t slices)
+{
+	return trunk_output(stored, outputs, inputs, output, codes, exponents, slices, 0);
+}
+
+uint16_t orc_trunk_output_block128(const uint8_t *stored, uint32_t outputs, uint32_t inputs, uint32_t output,
+				   const uint8_t *codes, const uint8_t *exponents, uint32_t slices)
+{
+	return trunk_output(stored, outputs, inputs, output, codes, exponents, slices, 1);
+}
+
+/* E4M3 codes [output][input] in natural order and FP32 scales [ceil(outputs / 128)][inputs / 128] -> the stored matrix
+ * of WEIGHT_FORMAT_E4M3_BLOCK128 */
+void orc_e4m3_block128_lay_out(const uint8_t *codes, const float *scales, uint32_t outputs, uint32_t inputs,
+			       uint8_t *stored_out)
+{
+	for (uint32_t output = 0; output < outputs; output++)
+		for (uint32_t input = 0; input < inputs; input++)
+			stored_out[e4m3_place(inputs, output, input)] = codes[(size_t)output * inputs + input];
+	memcpy(stored_out + (size_t)outputs * inputs, scales, (size_t)((outputs + 127u) / 128u) * (inputs / 128u) * 4u);
+}
+
 /* The always-on expert on an arena image, launch for launch (linear_shared_expert_prepare's four): gate and up,
  * the hidden step with a route weight of 1, quantization of the hidden rows, down. */
-void orc_shared_expert(const struct trunk_linear_quantized_arguments *gate_up, const struct trunk_hidden_arguments *hidden,
-		       const struct activation_quantize_arguments *quantize,
-		       const struct trunk_linear_quantized_arguments *down, uint32_t slices_gate_up, uint32_t slices_down,
-		       unsigned char *arena)
+static void shared_expert(const struct trunk_linear_quantized_arguments *gate_up, const struct trunk_hidden_arguments *hidden,
+			  const struct activation_quantize_arguments *quantize,
+			  const struct trunk_linear_quantized_arguments *down, uint32_t slices_gate_up, uint32_t slices_down,
+			  unsigned char *arena, int block128)
 {
 	const uint32_t H = gate_up->input_size, I = gate_up->output_size[0], O = down->output_size[0];
 	const uint32_t rows = gate_up->row_count;
@@ -308,10 +337,10 @@ void orc_shared_expert(const struct trunk_linear_quantized_arguments *gate_up, c
 		uint16_t *const hidden_out = (uint16_t *)(arena + hidden->hidden_offset) + (size_t)row * I;
 #pragma omp parallel for
 		for (uint32_t output = 0; output < I; output++) {
-			gate_out[output] = orc_trunk_output(arena + gate_up->weights_offset[0], I, H, output, natural, exponents,
-							    slices_gate_up);
-			up_out[output] = orc_trunk_output(arena + gate_up->weights_offset[1], I, H, output, natural, exponents,
-							  slices_gate_up);
+			gate_out[output] = trunk_output(arena + gate_up->weights_offset[0], I, H, output, natural, exponents,
+							slices_gate_up, block128);
+			up_out[output] = trunk_output(arena + gate_up->weights_offset[1], I, H, output, natural, exponents,
+						      slices_gate_up, block128);
 			hidden_out[output] = orc_mx_hidden(gate_out[output], up_out[output], hidden->activation_limit, 1.0f);
 		}
 		uint8_t *const hidden_exponents = arena + quantize->exponents_offset + (size_t)row * (I / 32u);
@@ -321,9 +350,26 @@ void orc_shared_expert(const struct trunk_linear_quantized_arguments *gate_up, c
 		uint16_t *const out = (uint16_t *)(arena + down->output_offset[0]) + (size_t)row * O;
 #pragma omp parallel for
 		for (uint32_t output = 0; output < O; output++)
-			out[output] = orc_trunk_output(arena + down->weights_offset[0], O, I, output, scratch, hidden_exponents,
-						       slices_down);
+			out[output] = trunk_output(arena + down->weights_offset[0], O, I, output, scratch, hidden_exponents,
+						   slices_down, block128);
 	}
 	free(scratch);
 	free(natural);
+}
+
+void orc_shared_expert(const struct trunk_linear_quantized_arguments *gate_up, const struct trunk_hidden_arguments *hidden,
+		       const struct activation_quantize_arguments *quantize,
+		       const struct trunk_linear_quantized_arguments *down, uint32_t slices_gate_up, uint32_t slices_down,
+		       unsigned char *arena)
+{
+	shared_expert(gate_up, hidden, quantize, down, slices_gate_up, slices_down, arena, 0);
+}
+
+void orc_shared_expert_block128(const struct trunk_linear_quantized_arguments *gate_up,
+				const struct trunk_hidden_arguments *hidden,
+				const struct activation_quantize_arguments *quantize,
+				const struct trunk_linear_quantized_arguments *down, uint32_t slices_gate_up,
+				uint32_t slices_down, unsigned char *arena)
+{
+	shared_expert(gate_up, hidden, quantize, down, slices_gate_up, slices_down, arena, 1);
 }

@@ -241,16 +241,20 @@ def test_layer_matches_oracle(api, oracle, shared):
     assert np.array_equal(result, synthetic.to_bfloat16(np.float32(0.0) + row_output))
 
 
+@pytest.mark.parametrize("block128", [False, True])
 @pytest.mark.parametrize("rows,slices", [(1, (1, 1)), (5, (2, 4)), (8, (8, 2))])
-def test_shared_expert_matches_oracle(api, oracle, rows, slices):
-    """linear_shared_expert_prepare's four launches (E4M3 matrices, one scale per 32 by 32 weights) against the oracle
-    on the same image, from the card's own quantized rows: gate, up and down within the tolerance of a bfloat16
-    result, the hidden rows' quantization bit for bit given the hidden rows."""
+def test_shared_expert_matches_oracle(api, oracle, rows, slices, block128):
+    """linear_shared_expert_prepare's four launches (E4M3 matrices, one scale per 32 by 32 weights) and
+    linear_shared_expert_block128_prepare's (one FP32 scale per 128 by 128 weights) against the oracle on the same
+    image, from the card's own quantized rows: gate, up and down within the tolerance of a bfloat16 result, the
+    hidden rows' quantization bit for bit given the hidden rows."""
     rng = np.random.default_rng(60 + rows)
-    H, I = 512, 320  # a last scale block of 16 outputs in neither; 320 = 10 blocks of 32, 5 loads of 64
+    # 320 = 10 blocks of 32, 5 loads of 64, a last scale block of 16 outputs; the FP32-scaled format wants whole
+    # blocks of 128 inputs: 384 outputs = three blocks, 512 = four
+    H, I = (512, 384) if block128 else (512, 320)
     layout = api.Layout()
-    stored = {name: synthetic.e4m3_matrix(rng, o, i) for name, (o, i) in
-              (("gate", (I, H)), ("up", (I, H)), ("down", (H, I)))}
+    draw = synthetic.e4m3_block128_matrix if block128 else synthetic.e4m3_matrix
+    stored = {name: draw(rng, o, i) for name, (o, i) in (("gate", (I, H)), ("up", (I, H)), ("down", (H, I)))}
     where = {name: layout.take(data.size, 64) for name, data in stored.items()}
     sizes = {"values": rows * H * 2, "codes": rows * H, "exponents": rows * H // 32, "operands": rows * H * 2,
              "gate_output": rows * I * 2, "up_output": rows * I * 2, "hidden": rows * I * 2, "hidden_codes": rows * I,
@@ -266,7 +270,7 @@ def test_shared_expert_matches_oracle(api, oracle, rows, slices):
     description = R.LinearSharedExpertDescription()
     for name, (o, i), count in (("gate", (I, H), slices[0]), ("up", (I, H), slices[0]), ("down", (H, I), slices[1])):
         setattr(description, name, R.LinearMatrix(R.LinearRange(where[name], stored[name].size), R.MatrixShape(o, i, 8, 0),
-                                                  5, count, 0, 0))
+                                                  6 if block128 else 5, count, 0, 0))
     for name in ("codes", "exponents", "operands", "gate_output", "up_output", "hidden", "hidden_codes",
                  "hidden_exponents", "hidden_operands", "output"):
         setattr(description, name, R.LinearRange(at[name], sizes[name]))
@@ -275,7 +279,17 @@ def test_shared_expert_matches_oracle(api, oracle, rows, slices):
                                             C.POINTER(R.LinearKernels), C.POINTER(R.KernelLaunch)]
     lib.linear_shared_expert_prepare.argtypes = [C.POINTER(R.LinearSharedExpertDescription), C.c_uint64,
                                                  C.POINTER(R.LinearKernels), C.POINTER(R.KernelLaunch)]
+    lib.linear_shared_expert_block128_prepare.argtypes = [C.POINTER(R.LinearSharedExpertDescription), C.c_uint64,
+                                                          C.POINTER(R.LinearKernels),
+                                                          C.POINTER(api.BackendOperations), C.c_void_p,
+                                                          C.POINTER(R.KernelLaunch)]
     card = api.Card(0, arena_bytes)
+
+    def prepare(description, launches):
+        if block128:
+            return lib.linear_shared_expert_block128_prepare(C.byref(description), arena_bytes, C.byref(kernels),
+                                                             card.ops_pointer, card.handle, launches)
+        return lib.linear_shared_expert_prepare(C.byref(description), arena_bytes, C.byref(kernels), launches)
     try:
         kernels = prepare_kernels(api, card)
         card.upload(0, image)
@@ -284,13 +298,15 @@ def test_shared_expert_matches_oracle(api, oracle, rows, slices):
         first = R.KernelLaunch()
         api.check(lib.linear_quantize_prepare(C.byref(quantize), arena_bytes, C.byref(kernels), C.byref(first)), "quantize")
         launches = (R.KernelLaunch * 4)()
-        api.check(lib.linear_shared_expert_prepare(C.byref(description), arena_bytes, C.byref(kernels), launches),
-                  "linear_shared_expert_prepare")
+        api.check(prepare(description, launches), "linear_shared_expert_prepare")
+        if block128:  # a matrix of the other format is refused by either preparer
+            assert lib.linear_shared_expert_prepare(C.byref(description), arena_bytes, C.byref(kernels),
+                                                    (R.KernelLaunch * 4)()) == 1
         assert launches[0].grid[0] == 2 * I // 16 and launches[0].block[0] == 32 * slices[0]
         assert launches[3].grid[0] == H // 16 and launches[3].block[0] == 32 * slices[1]
         before = bytes(launches)
         description.row_count = 9  # more rows than a thin launch takes
-        assert lib.linear_shared_expert_prepare(C.byref(description), arena_bytes, C.byref(kernels), launches) == 1
+        assert prepare(description, launches) == 1
         assert bytes(launches) == before
         card.run([first] + list(launches))
         card.wait()
@@ -308,8 +324,8 @@ def test_shared_expert_matches_oracle(api, oracle, rows, slices):
     down = R.TrunkLinearQuantized((C.c_uint64 * 2)(where["down"], 0), (C.c_uint64 * 2)(at["output"], 0),
                                   at["hidden_codes"], at["hidden_exponents"], at["hidden_operands"],
                                   (C.c_uint32 * 2)(H, 0), I, rows)
-    oracle.orc_shared_expert(C.byref(gate_up), C.byref(hidden), C.byref(requantize), C.byref(down), slices[0], slices[1],
-                             ptr(expected, u8p))
+    (oracle.orc_shared_expert_block128 if block128 else oracle.orc_shared_expert)(
+        C.byref(gate_up), C.byref(hidden), C.byref(requantize), C.byref(down), slices[0], slices[1], ptr(expected, u8p))
 
     def ordinals(bits):
         bits = bits.astype(np.int32)

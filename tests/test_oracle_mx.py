@@ -161,3 +161,31 @@ def test_trunk_outputs_within_reference_tolerance(oracle, reference):
             bits = oracle.orc_trunk_output(ptr(stored, u8p), outputs, inputs, output, ptr(fed_codes, u8p),
                                            ptr(fed_exp, u8p), slices)
             assert reference.test_linear_output_is_within_tolerance(bits, C.byref(products[output]), inputs, slices)
+
+
+def test_block128_outputs_follow_the_same_chain(oracle):
+    """WEIGHT_FORMAT_E4M3_BLOCK128 is not a format of the reference (parity unpinned for it): its oracle is the pinned
+    chain with the FP32 scale of the 128 by 128 block in the place of 2^(weight code - 127). Where every FP32 scale IS
+    such a power of two, the outputs equal the pinned format's bit for bit."""
+    rng = np.random.default_rng(27)
+    outputs, inputs = 256, 512
+    codes = e4m3_codes(rng, outputs * inputs)
+    exponent_codes = rng.integers(115, 125, size=(outputs // 128, inputs // 128), dtype=np.uint8)
+    scales32 = np.ldexp(np.float32(1.0), exponent_codes.astype(np.int32) - 127).astype(np.float32)
+    scales8 = np.repeat(np.repeat(exponent_codes, 4, axis=0), 4, axis=1)  # one code per 32 by 32
+    block128 = np.zeros(outputs * inputs + scales32.size * 4, np.uint8)
+    scaled = np.zeros(outputs * inputs + scales8.size, np.uint8)
+    oracle.orc_e4m3_block128_lay_out(ptr(codes, u8p), scales32.ctypes.data_as(C.POINTER(C.c_float)), outputs, inputs,
+                                     ptr(block128, u8p))
+    oracle.orc_e4m3_weights_lay_out(ptr(codes, u8p), ptr(np.ascontiguousarray(scales8).reshape(-1), u8p), outputs,
+                                    inputs, ptr(scaled, u8p))
+    assert np.array_equal(block128[:outputs * inputs], scaled[:outputs * inputs])
+    values = synthetic.to_bfloat16(rng.normal(0, 1, inputs).astype(np.float32))
+    fed_codes, fed_exp = np.zeros(inputs, np.uint8), np.zeros(inputs // 32, np.uint8)
+    oracle.orc_mx_quantize(ptr(values, u16p), inputs, ptr(fed_codes, u8p), ptr(fed_exp, u8p))
+    for slices in (1, 4):
+        for output in range(0, outputs, 7):
+            assert oracle.orc_trunk_output_block128(ptr(block128, u8p), outputs, inputs, output, ptr(fed_codes, u8p),
+                                                    ptr(fed_exp, u8p), slices) == \
+                oracle.orc_trunk_output(ptr(scaled, u8p), outputs, inputs, output, ptr(fed_codes, u8p),
+                                        ptr(fed_exp, u8p), slices)
