@@ -159,6 +159,24 @@ class OrderedRowSumPublish(C.Structure):
                 ("pairs_per_row", C.c_uint32), ("status_offset", C.c_uint64)]
 
 
+class ExactRing(C.Structure):
+    _fields_ = [("input_offset", C.c_uint64), ("output_offset", C.c_uint64), ("bank_offset", C.c_uint64),
+                ("peer_table_offset", C.c_uint64), ("peer_bank_delta", C.c_uint64), ("deadline_cycles", C.c_uint64),
+                ("packs_per_owner", C.c_uint32), ("vectors", C.c_uint32), ("rank", C.c_uint32), ("mode", C.c_uint32),
+                ("reserved_words", C.c_uint64 * 2)]
+
+
+class RingExchangeDescription(C.Structure):
+    _fields_ = [("arguments", ExactRing), ("arena_byte_count", C.c_uint64), ("kind", C.c_uint32),
+                ("blocks", C.c_uint32)]
+
+
+RING_EXCHANGE_EXACT, RING_EXCHANGE_COMPRESSED, RING_EXCHANGE_ROUND_ONCE = 0, 1, 2
+EXACT_RING_GATHER, EXACT_RING_BF16_SUM, EXACT_RING_BF16_SUM_COLUMNS = 0, 1, 2
+EXACT_RING_PACK_BYTES, EXACT_RING_BLOCKS, EXACT_RING_METADATA_BYTES, EXACT_RING_STATUS_OFFSET = 16, 16, 128, 64
+COMPRESSED_RING_PACKS, COMPRESSED_RING_PACKET_WORDS = 32, 136
+COMPRESSED_RING_READY_WORD, COMPRESSED_RING_ACK_WORD = 132, 133
+
 ORDERED_PUSH_FP32, ORDERED_PUSH_BF16 = 0, 1
 TP_EXCHANGE_FORM_PUSH, TP_EXCHANGE_FORM_OWNER_SUMS = 0, 1
 
@@ -328,7 +346,7 @@ class OrderedCollectiveKernels(C.Structure):
 
 for _record, _bytes in ((Exl3Reconstruct, 32), (Exl3Expert, 80), (ExpertJob, 96), (ExpertRowSum, 24),
                         (Exl3ShardActivation, 96), (Exl3Moe, 112), (Exl3Tc, 72), (Exl3Tcp, 88), (RouterPick, 8), (Exl3LayerRoute, 184), (Exl3LayerPublish, 72), (TrunkLinearQuantized, 72), (TrunkHidden, 32), (TrunkRowsAdd, 24), (Exl3Prefill, 136), (Exl3PrefillTile, 16), (Exl3PrefillEntry, 8), (Exl3PrefillParts, 56), (StepBlock, 16), (OrderedPeer, 32),
-                        (OrderedCollective, 80), (OrderedReduceBf16, 96), (OrderedRowSumPublish, 104), (OrderedPublishReduce, 104), (OrderedPush, 96),
+                        (OrderedCollective, 80), (OrderedReduceBf16, 96), (OrderedRowSumPublish, 104), (OrderedPublishReduce, 104), (OrderedPush, 96), (ExactRing, 80),
                         (TpExchange, 112), (OrderedRowsPush, 112), (Tp2Join, 80),
                         (RouterSelectB200, 88), (StepInputSelect, 40), (ActivationQuantize, 40), (ExpertGateUp, 64), (ExpertDown, 56),
                         (KernelLaunch, 232), (CardDescription, 168)):

@@ -218,6 +218,28 @@ MUST_CHECK result_status ordered_rows_push_prepare(const struct ordered_rows_pus
 						   const struct backend_operations *backend, struct device_card *card,
 						   struct kernel_launch *launch_out);
 
+/* ---- the output-axis exchanges (struct exact_ring_arguments of the records header) ----
+ * The reference's model program fills these launches itself (source/model_v41_program.c:8445); this library offers a
+ * preparer with the usual checks. kind: which of the three entries. blocks: the grid, 1 to EXACT_RING_BLOCKS (0: 16).
+ * Checks: 2, 4 or 8 ranks, the rank, a mode the entry has, packs_per_owner a positive multiple of 32, vectors as the
+ * mode needs them, a positive deadline; input and output of rank_count * packs_per_owner packs each, 16-byte aligned,
+ * inside the arena, disjoint (the sums may also work in place: input_offset == output_offset); the bank of
+ * ring_exchange_bank_bytes bytes, disjoint from both; the peer table. The bank's bytes for four ranks never exceed
+ * what the reference's formulas reserve (round once: 128 + 128 packs + 512; exact sum: 128 + 192 packs; gather: 128
+ * + 120 packs; compressed: 128 + 6 (packs / 32) 544). */
+enum ring_exchange_kind { RING_EXCHANGE_EXACT = 0, RING_EXCHANGE_COMPRESSED = 1, RING_EXCHANGE_ROUND_ONCE = 2 };
+uint64_t ring_exchange_bank_bytes(enum ring_exchange_kind kind, uint32_t mode, uint32_t rank_count,
+				  uint32_t packs_per_owner);
+struct ring_exchange_description {
+	struct exact_ring_arguments arguments;
+	uint64_t arena_byte_count;
+	enum ring_exchange_kind kind;
+	uint32_t blocks;
+};
+MUST_CHECK result_status ring_exchange_prepare(const struct ring_exchange_description *description,
+					       const struct backend_operations *backend, struct device_card *card,
+					       struct kernel_launch *launch_out);
+
 #ifdef __cplusplus
 }
 #endif

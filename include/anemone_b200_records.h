@@ -400,6 +400,69 @@ struct ordered_row_sum_publish_arguments {
 };
 
 /* ------------------------------------------------------------------------------------------------------------
+ * The output-axis exchanges of a tensor-parallel group (reference: include/anemone/exact_ring_records.h:43-56,
+ * round_once_ring_records.h, compressed_ring_records.h): one record, three entries, packs of 16 bytes (eight
+ * bfloat16 values, or any 16 bytes for the gather).
+ *   ("kernel_exact_ring", "exact_ring")                      mode 0: a lossless gather of every owner's
+ *       packs_per_owner packs (input owner-major, this rank's part read; output owner-major or, with vectors,
+ *       [vector][all owners' channels]); modes 1, 2: the BF16 sum whose additions round to bfloat16 one after the
+ *       other in the order the reference's ring visits the ranks: for owner o from rank o + 1 round to o; a +0 half
+ *       that travels arrives as -0 (the reference's transport), so the owner keeps its sum and every other rank holds
+ *       it without +0 halves;
+ *   ("kernel_bf16_compressed_ring", "bf16_compressed_ring")  modes 1, 2: the same sum, every pack on the wire in the
+ *       lossless exponent-delta code (anemone_b200_wire_codec.h): three words a lane where a warp's exponents allow;
+ *   ("kernel_bf16_round_once_ring", "bf16_round_once_ring")  modes 1, 2 (the layout alone): FP32 sums of the ranks'
+ *       bfloat16 values in rank order from +0, ONE rounding to bfloat16, the same bits on every rank.
+ * Mode 1: owner o's part is the o-th run of packs_per_owner packs; mode 2 (column owners): input and output are
+ * [vectors][row], owner o the o-th run of every row's packs. grid (at most EXACT_RING_BLOCKS) x EXACT_RING_THREADS;
+ * packs_per_owner a positive multiple of 32; every rank the same counts and grid on one ordered stream. The bank:
+ * EXACT_RING_METADATA_BYTES (a generation counter a block, a status word at EXACT_RING_STATUS_OFFSET), then the
+ * exchange's own space (ring_exchange_bank_bytes of the host header); zero before the first call. Peers: the ordered
+ * collective's table; a peer's bank lies at its region offset + peer_bank_delta. B200: 2, 4 or 8 ranks in
+ * reserved_words[0] (0: the reference's 4); a deadline, an exhausted generation counter or a malformed record sets
+ * the status word (1, 2, 3) and the kernel returns: nothing traps, and a bank with a status is not used again.
+ * ---------------------------------------------------------------------------------------------------------- */
+#define KERNEL_FILE_EXACT_RING "kernel_exact_ring"
+#define KERNEL_EXACT_RING "exact_ring"
+#define KERNEL_FILE_COMPRESSED_RING "kernel_bf16_compressed_ring"
+#define KERNEL_COMPRESSED_RING "bf16_compressed_ring"
+#define KERNEL_FILE_ROUND_ONCE_RING "kernel_bf16_round_once_ring"
+#define KERNEL_ROUND_ONCE_RING "bf16_round_once_ring"
+#define EXACT_RING_PACK_BYTES 16u
+#define EXACT_RING_BLOCKS 16u
+#define EXACT_RING_THREADS 256u
+#define EXACT_RING_RANKS 4u
+#define EXACT_RING_METADATA_BYTES 128u
+#define EXACT_RING_STATUS_OFFSET 64u
+#define EXACT_RING_STATUS_DEADLINE 1u
+#define EXACT_RING_STATUS_GENERATION 2u
+#define EXACT_RING_STATUS_ARGUMENTS 3u
+#define EXACT_RING_GATHER 0u
+#define EXACT_RING_BF16_SUM 1u
+#define EXACT_RING_BF16_SUM_COLUMNS 2u
+#define COMPRESSED_RING_PACKS 32u
+#define COMPRESSED_RING_PACKET_WORDS 136u
+#define COMPRESSED_RING_PACKET_BYTES 544u
+#define COMPRESSED_RING_PAYLOAD_WORD 4u
+#define COMPRESSED_RING_RAW_MASK_WORD 1u
+#define COMPRESSED_RING_READY_WORD 132u
+#define COMPRESSED_RING_ACK_WORD 133u
+#define COMPRESSED_RING_COMPRESSED_WORDS 3u
+struct exact_ring_arguments {
+	uint64_t input_offset;
+	uint64_t output_offset;
+	uint64_t bank_offset;
+	uint64_t peer_table_offset;
+	uint64_t peer_bank_delta;
+	uint64_t deadline_cycles;
+	uint32_t packs_per_owner;
+	uint32_t vectors;
+	uint32_t rank;
+	uint32_t mode;
+	uint64_t reserved_words[2]; /* [0]: the rank count (0: four); [1]: zero */
+};
+
+/* ------------------------------------------------------------------------------------------------------------
  * One-shot push all-reduce and the tensor-parallel exchange built on it (reference:
  * include/anemone/ordered_push_records.h:8-33, include/anemone/tp_exchange_records.h:10-62).
  *
@@ -843,6 +906,7 @@ AB_RECORD_HAS(ordered_rows_push_arguments, 112);
 AB_RECORD_HAS(tp2_join_arguments, 80);
 AB_RECORD_HAS(router_select_b200_arguments, 88);
 AB_RECORD_HAS(step_input_select_arguments, 40);
+AB_RECORD_HAS(exact_ring_arguments, 80);
 AB_RECORD_HAS(exl3_layer_route_record, 184);
 AB_RECORD_HAS(exl3_layer_publish_arguments, 72);
 AB_RECORD_HAS(exl3_prefill_tile, 16);

@@ -135,4 +135,16 @@ void orc_shared_expert_block128(const struct trunk_linear_quantized_arguments *g
 				const struct trunk_linear_quantized_arguments *down, uint32_t slices_gate_up,
 				uint32_t slices_down, unsigned char *arena);
 
+/* ---- the output-axis exchanges (ring_oracle.c) ----
+ * inputs[rank]: that rank's bfloat16 values, rank_count * packs_per_owner packs of eight. vectors: 0 for owner-major
+ * parts, else the rows of [row][owner][the row's packs]. */
+uint16_t orc_ring_bf16_add(uint16_t left, uint16_t right);
+void orc_ring_bf16_sum(const uint16_t *const *inputs, uint32_t rank_count, uint32_t packs_per_owner, uint32_t vectors,
+		       uint16_t *const *outputs);
+void orc_ring_round_once(const uint16_t *const *inputs, uint32_t rank_count, uint64_t value_count, uint16_t *output);
+void orc_ring_gather(const uint16_t *const *inputs, uint32_t rank_count, uint32_t packs_per_owner, uint32_t vectors,
+		     uint16_t *output);
+void orc_ring_packet_encode(const uint16_t *values, uint32_t *packet);
+void orc_ring_packet_decode(const uint32_t *packet, uint16_t *values);
+
 #endif

@@ -109,6 +109,18 @@ def load_oracle():
                                    C.c_uint64, C.c_uint64, u8]
     lib.orc_mx_row_sum.restype = None
     lib.orc_mx_row_sum.argtypes = [C.c_void_p, C.c_uint32, u8]
+    lib.orc_ring_bf16_add.restype = C.c_uint16
+    lib.orc_ring_bf16_add.argtypes = [C.c_uint16, C.c_uint16]
+    lib.orc_ring_bf16_sum.restype = None
+    lib.orc_ring_bf16_sum.argtypes = [C.POINTER(u16p), C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(u16p)]
+    lib.orc_ring_round_once.restype = None
+    lib.orc_ring_round_once.argtypes = [C.POINTER(u16p), C.c_uint32, C.c_uint64, u16p]
+    lib.orc_ring_gather.restype = None
+    lib.orc_ring_gather.argtypes = [C.POINTER(u16p), C.c_uint32, C.c_uint32, C.c_uint32, u16p]
+    lib.orc_ring_packet_encode.restype = None
+    lib.orc_ring_packet_encode.argtypes = [u16p, u32p]
+    lib.orc_ring_packet_decode.restype = None
+    lib.orc_ring_packet_decode.argtypes = [u32p, u16p]
     return lib
 
 
@@ -138,6 +150,12 @@ def load_reference():
     lib.test_linear_output_is_within_tolerance.restype = C.c_bool
     lib.ordered_collective_host.restype = C.c_int
     lib.ordered_collective_host.argtypes = [C.POINTER(f32p), C.POINTER(f32p), C.c_uint32, C.c_uint32, C.c_int]
+    if hasattr(lib, "ref_bf16_wire_pair_pack"):
+        lib.ref_bf16_wire_pair_pack.restype = lib.ref_bf16_wire_pair_unpack.restype = C.c_uint32
+        lib.ref_bf16_wire_pair_pack.argtypes = [C.c_uint32, C.c_uint32]
+        lib.ref_bf16_wire_pair_unpack.argtypes = [C.c_uint32, C.c_uint32, C.c_uint32]
+        lib.ref_bf16_wire_digest.restype = C.c_uint64
+        lib.ref_bf16_wire_digest.argtypes = []
     return lib
 
 

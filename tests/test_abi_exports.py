@@ -17,7 +17,9 @@ def declared_symbols():
             names.add(match.group(1))
         for match in re.finditer(r"extern const struct [a-z_]+ ([a-z_0-9]+);", text):
             names.add(match.group(1))
-    inline = {"exl3_bits_x2", "exl3_window_end", "exl3_code_bytes", "exl3_matrix_bytes", "exl3_tile_position"}
+    inline = {"exl3_bits_x2", "exl3_window_end", "exl3_code_bytes", "exl3_matrix_bytes", "exl3_tile_position",
+              "bf16_wire_byte", "bf16_wire_half", "bf16_wire_high_exponent", "bf16_wire_low_exponent",
+              "bf16_wire_pair_pack", "bf16_wire_pair_unpack"}
     return sorted(names - inline)
 
 
@@ -59,7 +61,8 @@ def test_record_sizes_match_the_headers():
               "expert_down_arguments": R.ExpertDown, "trunk_linear_quantized_arguments": R.TrunkLinearQuantized,
               "trunk_hidden_arguments": R.TrunkHidden, "trunk_rows_add_arguments": R.TrunkRowsAdd,
               "exl3_layer_route_record": R.Exl3LayerRoute, "exl3_layer_publish_arguments": R.Exl3LayerPublish,
-              "ordered_publish_reduce_arguments": R.OrderedPublishReduce}
+              "ordered_publish_reduce_arguments": R.OrderedPublishReduce,
+              "exact_ring_arguments": R.ExactRing}
     assert set(declared) == set(mirror)
     for name, record in mirror.items():
         assert C.sizeof(record) == int(declared[name]), name

@@ -281,3 +281,39 @@ def test_push_and_owner_sums_across_cards(api, oracle, payload):
         finally:
             for card in cards:
                 card.close()
+
+
+@pytest.mark.parametrize("kind,mode", [("exact", 0), ("exact", 1), ("exact", 2), ("compressed", 1), ("compressed", 2),
+                                       ("round_once", 1)])
+def test_output_axis_exchanges_across_cards(api, oracle, kind, mode):
+    """The gather, the BF16 sum in the ring's order (plain and on the coded wire) and the round-once sum between real
+    cards: every rank stores into every rank's bank over NVLink and waits on its own; bit for bit against the oracle
+    on every rank, three calls in a row on the same banks."""
+    from anemone_b200.ring import RingExchange
+    from tests.test_gpu_ring import expected_for, values_for
+    for ranks in world_sizes(api):
+        packs, vectors = 32 * 24, (4 if mode != 1 else 0)
+        rng = np.random.default_rng(900 + ranks + mode)
+        cards, exchanges = [], []
+        try:
+            for rank in range(ranks):
+                cards.append(api.Card(rank, 64 << 20))
+                exchanges.append(RingExchange(cards[-1], kind, mode, rank, ranks, packs, vectors))
+            for exchange in exchanges:
+                exchange.connect_local(exchanges)
+            for card in cards:
+                card.wait()
+            for call in range(3):
+                inputs = values_for(rng, ranks, packs, "wide" if call == 1 else "near")
+                expected = expected_for(oracle, kind, mode, inputs, ranks, packs, vectors)
+                for exchange, values in zip(exchanges, inputs):
+                    exchange.load(values)
+                for exchange in exchanges:  # queue every rank before waiting for any
+                    exchange.run()
+                for card in cards:
+                    card.wait()
+                for rank, exchange in enumerate(exchanges):
+                    assert np.array_equal(exchange.result(), expected[rank]), (ranks, call, rank)
+        finally:
+            for card in cards:
+                card.close()
