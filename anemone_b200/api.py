@@ -111,6 +111,7 @@ def library():
                                            C.POINTER(R.KernelLaunch)]
         lib.bb_exl3_row_sum_prepare.argtypes = [C.POINTER(R.ExpertRowSum), C.c_uint32, C.c_uint64,
                                                 C.POINTER(BackendOperations), _card, C.POINTER(R.KernelLaunch)]
+        lib.backend_b200_launch_order.argtypes = [C.POINTER(R.KernelLaunch), C.c_uint32, C.POINTER(R.LaunchOrder)]
         lib.ring_exchange_bank_bytes.restype = C.c_uint64
         lib.ring_exchange_bank_bytes.argtypes = [C.c_uint32] * 4
         lib.ring_exchange_prepare.argtypes = [C.POINTER(R.RingExchangeDescription), C.POINTER(BackendOperations),

@@ -35,6 +35,14 @@ struct transfer_ticket {
 	uint64_t ticket; /* 0: slot free */
 };
 
+/* An address word of the arena as the host remembers it: copy launches name memory by such words. */
+#define PEER_WORDS_MOST 256u
+struct peer_word {
+	uint64_t word_offset;
+	CUdeviceptr address;
+	uint64_t byte_count; /* from the address to the end of the owner's arena */
+};
+
 struct ipc_mapping {
 	unsigned char handle[BACKEND_B200_IPC_HANDLE_BYTES];
 	CUdeviceptr base;
@@ -65,6 +73,8 @@ struct device_card {
 	int measure_state; /* 0 idle, 1 begun, 2 ended */
 	struct ipc_mapping mappings[BACKEND_MAXIMUM_CARDS];
 	uint32_t mapping_count;
+	struct peer_word peer_words[PEER_WORDS_MOST]; /* what peer_connect wrote where: a copy launch's places */
+	uint32_t peer_word_count;
 	uint64_t *small_words; /* page-locked: address words written at load */
 	uint32_t small_word_next;
 	uint64_t launches_queued;
@@ -651,8 +661,61 @@ done:
 	CARD_LEAVE(card);
 }
 
+/* A copy's place: the card's own arena, or the memory behind an address word a connect call wrote. */
+static bool copy_place_resolve(const struct device_card *card, struct exchange_place place, uint64_t byte_count,
+			       CUdeviceptr *address_out)
+{
+	CUdeviceptr base = card->arena;
+	uint64_t limit = card->arena_byte_count;
+	if (place.address_word_offset != EXCHANGE_OWN_ARENA) {
+		const struct peer_word *found = NULL;
+		for (uint32_t entry = 0; entry < card->peer_word_count; entry++)
+			if (card->peer_words[entry].word_offset == place.address_word_offset)
+				found = &card->peer_words[entry];
+		if (found == NULL)
+			return false;
+		base = found->address;
+		limit = found->byte_count;
+	}
+	if (!range_inside(place.offset, byte_count, limit))
+		return false;
+	*address_out = base + place.offset;
+	return true;
+}
+
+static bool copy_is_valid(const struct device_card *card, const struct kernel_launch *launch, CUdeviceptr *source_out,
+			  CUdeviceptr *destination_out)
+{
+	struct exchange_copy_arguments copy;
+	if (launch->argument_byte_count != sizeof(copy) || launch->dynamic_shared_byte_count != 0 ||
+	    launch->branch > LAUNCH_SIDE_MORE)
+		return false;
+	for (uint32_t byte = sizeof(copy); byte < LAUNCH_ARGUMENT_BYTES; byte++)
+		if (launch->argument[byte] != 0)
+			return false;
+	memcpy(&copy, launch->argument, sizeof(copy));
+	return copy.byte_count != 0 && copy_place_resolve(card, copy.source, copy.byte_count, source_out) &&
+	       copy_place_resolve(card, copy.destination, copy.byte_count, destination_out);
+}
+
+static void peer_word_remember(struct device_card *card, uint64_t word_offset, CUdeviceptr address, uint64_t byte_count)
+{
+	uint32_t entry = 0;
+	while (entry < card->peer_word_count && card->peer_words[entry].word_offset != word_offset)
+		entry++;
+	if (entry == PEER_WORDS_MOST)
+		return; /* the word is written all the same: kernels read it; only copy launches cannot name it */
+	card->peer_words[entry] = (struct peer_word){ word_offset, address, byte_count };
+	if (entry == card->peer_word_count)
+		card->peer_word_count++;
+}
+
 static bool launch_is_valid(const struct device_card *card, const struct kernel_launch *launch)
 {
+	if (launch->kernel == BACKEND_COPY) {
+		CUdeviceptr source, destination;
+		return copy_is_valid(card, launch, &source, &destination);
+	}
 	if (launch->kernel >= card->kernel_count ||
 	    launch->argument_byte_count != card->kernels[launch->kernel].argument_byte_count ||
 	    launch->dynamic_shared_byte_count > (uint32_t)card->shared_memory_most ||
@@ -679,6 +742,15 @@ static result_status launches_queue(const struct ab_driver *cu, struct device_ca
 	result_status status = STATUS_OK;
 	for (uint32_t index = 0; index < launch_count; index++) {
 		const struct kernel_launch *const launch = &launches[index];
+		if (launch->kernel == BACKEND_COPY) {
+			CUdeviceptr source = 0, destination = 0;
+			struct exchange_copy_arguments copy;
+			memcpy(&copy, launch->argument, sizeof(copy));
+			if (!copy_is_valid(card, launch, &source, &destination))
+				return STATUS_INVALID_ARGUMENT;
+			DRIVER(card, cuMemcpyDtoDAsync(destination, source, copy.byte_count, card->stream));
+			continue;
+		}
 		unsigned char record[LAUNCH_ARGUMENT_BYTES];
 		memcpy(record, launch->argument, launch->argument_byte_count);
 		CUdeviceptr arena = card->arena;
@@ -692,19 +764,145 @@ done:
 }
 
 static result_status table_check(const struct device_card *card, const struct kernel_launch *launches,
-				 uint32_t launch_count, bool chain_only)
+				 uint32_t launch_count)
 {
 	if (card == NULL || launches == NULL || launch_count == 0)
 		return STATUS_INVALID_ARGUMENT;
-	for (uint32_t index = 0; index < launch_count; index++) {
-		if (launches[index].kernel == BACKEND_COPY)
-			return STATUS_UNSUPPORTED; /* copy-engine nodes: not offered */
+	for (uint32_t index = 0; index < launch_count; index++)
 		if (!launch_is_valid(card, &launches[index]))
 			return STATUS_INVALID_ARGUMENT;
-		if (chain_only && launches[index].branch != LAUNCH_CHAIN)
-			return STATUS_UNSUPPORTED;
+	return STATUS_OK;
+}
+
+static uint32_t kernel_launches_of(const struct kernel_launch *launches, uint32_t launch_count)
+{
+	uint32_t kernels = 0;
+	for (uint32_t index = 0; index < launch_count; index++)
+		kernels += launches[index].kernel != BACKEND_COPY;
+	return kernels;
+}
+
+result_status backend_b200_launch_order(const struct kernel_launch *launches, uint32_t launch_count,
+					struct launch_order *order_out)
+{
+	if (launches == NULL || order_out == NULL || launch_count == 0)
+		return STATUS_INVALID_ARGUMENT;
+	/* two passes: the grammar first, so that a refusal leaves order_out as it was */
+	for (uint32_t pass = 0; pass < 2; pass++) {
+		const uint32_t none = UINT32_MAX;
+		uint32_t fork = none, run_last[LAUNCH_MOST_SIDE_RUNS], runs = 0;
+		for (uint32_t index = 0; index < launch_count; index++) {
+			const uint32_t branch = launches[index].branch, previous = index == 0 ? none : index - 1u;
+			const uint32_t before = index == 0 ? LAUNCH_CHAIN : launches[index - 1u].branch;
+			const bool in_side = before == LAUNCH_SIDE || before == LAUNCH_SIDE_MORE;
+			uint32_t wanted[1u + LAUNCH_MOST_SIDE_RUNS], wanted_count = 0;
+			switch (branch) {
+			case LAUNCH_CHAIN:
+				wanted[wanted_count++] = previous;
+				break;
+			case LAUNCH_SIDE:
+				if (before == LAUNCH_SIDE_MORE)
+					return STATUS_INVALID_ARGUMENT;
+				if (before == LAUNCH_SIDE) { /* the run goes on */
+					wanted[wanted_count++] = previous;
+					run_last[runs - 1u] = index;
+				} else { /* a fork: the launch before the run */
+					fork = previous;
+					wanted[wanted_count++] = fork;
+					runs = 1;
+					run_last[0] = index;
+				}
+				break;
+			case LAUNCH_SIDE_MORE:
+				if (!in_side || runs == LAUNCH_MOST_SIDE_RUNS)
+					return STATUS_INVALID_ARGUMENT;
+				wanted[wanted_count++] = fork;
+				run_last[runs++] = index;
+				break;
+			case LAUNCH_RESUME:
+				if (!in_side)
+					return STATUS_INVALID_ARGUMENT;
+				wanted[wanted_count++] = fork;
+				break;
+			case LAUNCH_JOIN:
+				if (runs == 0)
+					return STATUS_INVALID_ARGUMENT;
+				for (uint32_t run = 0; run < runs; run++)
+					if (run_last[run] != previous)
+						wanted[wanted_count++] = run_last[run];
+				wanted[wanted_count++] = previous; /* the largest index: the list stays ascending */
+				runs = 0;
+				break;
+			default:
+				return STATUS_INVALID_ARGUMENT;
+			}
+			if (pass == 0)
+				continue;
+			struct launch_order *const order = &order_out[index];
+			memset(order, 0, sizeof(*order));
+			for (uint32_t entry = 0; entry < wanted_count; entry++)
+				if (wanted[entry] != none)
+					order->behind[order->behind_count++] = wanted[entry];
+		}
 	}
 	return STATUS_OK;
+}
+
+static bool table_is_a_plain_chain(const struct kernel_launch *launches, uint32_t launch_count)
+{
+	for (uint32_t index = 0; index < launch_count; index++)
+		if (launches[index].kernel == BACKEND_COPY || launches[index].branch != LAUNCH_CHAIN)
+			return false;
+	return true;
+}
+
+/* The table as a graph built node by node, every node behind the nodes its launch's order names. Context current,
+ * mutex held; the table has passed table_check and backend_b200_launch_order. */
+static result_status graph_build(const struct ab_driver *cu, struct device_card *card,
+				 const struct kernel_launch *launches, const struct launch_order *order,
+				 uint32_t launch_count, CUgraphNode *nodes, CUgraph graph)
+{
+	result_status status = STATUS_OK;
+	for (uint32_t index = 0; index < launch_count; index++) {
+		const struct kernel_launch *const launch = &launches[index];
+		CUgraphNode behind[1u + LAUNCH_MOST_SIDE_RUNS];
+		for (uint32_t entry = 0; entry < order[index].behind_count; entry++)
+			behind[entry] = nodes[order[index].behind[entry]];
+		const CUgraphNode *const depends = order[index].behind_count == 0 ? NULL : behind;
+		if (launch->kernel == BACKEND_COPY) {
+			CUdeviceptr source = 0, destination = 0;
+			struct exchange_copy_arguments copy;
+			memcpy(&copy, launch->argument, sizeof(copy));
+			if (!copy_is_valid(card, launch, &source, &destination))
+				return STATUS_INVALID_ARGUMENT;
+			CUDA_MEMCPY3D parameters;
+			memset(&parameters, 0, sizeof(parameters));
+			parameters.srcMemoryType = parameters.dstMemoryType = CU_MEMORYTYPE_DEVICE;
+			parameters.srcDevice = source;
+			parameters.dstDevice = destination;
+			parameters.srcPitch = parameters.dstPitch = parameters.WidthInBytes = copy.byte_count;
+			parameters.Height = parameters.Depth = 1;
+			DRIVER(card, cuGraphAddMemcpyNode(&nodes[index], graph, depends, order[index].behind_count,
+							  &parameters, card->context));
+			continue;
+		}
+		unsigned char record[LAUNCH_ARGUMENT_BYTES];
+		memcpy(record, launch->argument, launch->argument_byte_count);
+		CUdeviceptr arena = card->arena;
+		void *kernel_parameters[] = { record, &arena };
+		CUDA_KERNEL_NODE_PARAMS parameters;
+		memset(&parameters, 0, sizeof(parameters));
+		parameters.func = card->kernels[launch->kernel].handle;
+		parameters.gridDimX = launch->grid[0], parameters.gridDimY = launch->grid[1];
+		parameters.gridDimZ = launch->grid[2];
+		parameters.blockDimX = launch->block[0], parameters.blockDimY = launch->block[1];
+		parameters.blockDimZ = launch->block[2];
+		parameters.sharedMemBytes = launch->dynamic_shared_byte_count;
+		parameters.kernelParams = kernel_parameters; /* copied into the node by the call */
+		DRIVER(card, cuGraphAddKernelNode(&nodes[index], graph, depends, order[index].behind_count, &parameters));
+	}
+done:
+	return status;
 }
 
 static result_status cuda_launch_run(struct device_card *card, const struct kernel_launch *launches,
@@ -713,12 +911,12 @@ static result_status cuda_launch_run(struct device_card *card, const struct kern
 	if (card == NULL)
 		return STATUS_INVALID_ARGUMENT;
 	CARD_ENTER(card);
-	status = card->failed ? STATUS_DEVICE_ERROR : table_check(card, launches, launch_count, false);
+	status = card->failed ? STATUS_DEVICE_ERROR : table_check(card, launches, launch_count);
 	if (status == STATUS_OK) {
 		/* the eager form runs the table in its serial order, whatever its branches */
 		status = launches_queue(cu, card, launches, launch_count);
 		if (status == STATUS_OK)
-			card->launches_queued += launch_count;
+			card->launches_queued += kernel_launches_of(launches, launch_count);
 	}
 	CARD_LEAVE(card);
 }
@@ -770,28 +968,44 @@ static result_status cuda_graph_capture(struct device_card *card, const struct k
 		return STATUS_INVALID_ARGUMENT;
 	CARD_ENTER(card);
 	CUgraph graph = NULL;
-	status = card->failed ? STATUS_DEVICE_ERROR : table_check(card, launches, launch_count, true);
+	struct launch_order *order = NULL;
+	CUgraphNode *nodes = NULL;
+	status = card->failed ? STATUS_DEVICE_ERROR : table_check(card, launches, launch_count);
+	if (status != STATUS_OK)
+		goto done;
+	order = calloc(launch_count, sizeof(*order));
+	nodes = calloc(launch_count, sizeof(*nodes));
+	if (order == NULL || nodes == NULL) {
+		status = STATUS_OUT_OF_MEMORY;
+		goto done;
+	}
+	status = backend_b200_launch_order(launches, launch_count, order);
 	if (status != STATUS_OK)
 		goto done;
 	if (card->graph_count == BACKEND_MAXIMUM_GRAPHS) {
 		status = STATUS_BUSY_VALUE;
 		goto done;
 	}
-	DRIVER(card, cuStreamBeginCapture(card->stream, CU_STREAM_CAPTURE_MODE_THREAD_LOCAL));
-	status = launches_queue(cu, card, launches, launch_count);
-	{
+	if (table_is_a_plain_chain(launches, launch_count)) {
+		DRIVER(card, cuStreamBeginCapture(card->stream, CU_STREAM_CAPTURE_MODE_THREAD_LOCAL));
+		status = launches_queue(cu, card, launches, launch_count);
 		const CUresult ended = cu->cuStreamEndCapture(card->stream, &graph);
 		if (status == STATUS_OK && ended != CUDA_SUCCESS)
 			status = driver_failure(card, "ending the capture", ended);
+	} else {
+		DRIVER(card, cuGraphCreate(&graph, 0));
+		status = graph_build(cu, card, launches, order, launch_count, nodes, graph);
 	}
 	if (status != STATUS_OK)
 		goto done;
 	DRIVER(card, cuGraphInstantiateWithFlags(&card->graphs[card->graph_count], graph, 0));
-	card->graph_kernel_nodes[card->graph_count] = launch_count;
+	card->graph_kernel_nodes[card->graph_count] = kernel_launches_of(launches, launch_count);
 	*graph_out = card->graph_count++;
 done:
 	if (graph != NULL)
 		(void)cu->cuGraphDestroy(graph);
+	free(order);
+	free(nodes);
 	CARD_LEAVE(card);
 }
 
@@ -886,6 +1100,9 @@ static result_status cuda_peer_connect(struct device_card *accessor, struct devi
 		}
 	}
 	status = address_word_write(cu, accessor, (uint64_t)owner->arena + owner_offset, address_word_offset);
+	if (status == STATUS_OK)
+		peer_word_remember(accessor, address_word_offset, owner->arena + owner_offset,
+				   owner->arena_byte_count - owner_offset);
 done:
 	CARD_LEAVE(accessor);
 }
@@ -1015,6 +1232,15 @@ result_status backend_b200_ipc_connect(struct device_card *accessor,
 		accessor->mappings[accessor->mapping_count++].base = base;
 	}
 	status = address_word_write(cu, accessor, (uint64_t)base + owner_offset, address_word_offset);
+	if (status == STATUS_OK) {
+		/* how much of the owner's allocation lies behind the word: what a copy launch may name through it */
+		CUdeviceptr range_base = 0;
+		size_t range_bytes = 0;
+		if (cu->cuMemGetAddressRange(&range_base, &range_bytes, base) == CUDA_SUCCESS &&
+		    owner_offset < range_bytes - (size_t)(base - range_base))
+			peer_word_remember(accessor, address_word_offset, base + owner_offset,
+					   range_bytes - (size_t)(base - range_base) - owner_offset);
+	}
 done:
 	CARD_LEAVE(accessor);
 }

@@ -57,6 +57,11 @@
 	X(cuGraphDestroy)         \
 	X(cuGraphExecDestroy)     \
 	X(cuGraphGetNodes)        \
+	X(cuGraphCreate)          \
+	X(cuGraphAddKernelNode)   \
+	X(cuGraphAddMemcpyNode)   \
+	X(cuMemcpyDtoDAsync)      \
+	X(cuMemGetAddressRange)   \
 	X(cuDeviceCanAccessPeer)  \
 	X(cuCtxEnablePeerAccess)  \
 	X(cuIpcGetMemHandle)      \

@@ -324,6 +324,33 @@ class KernelLaunch(C.Structure):
                 ("branch", C.c_uint32), ("argument", C.c_ubyte * LAUNCH_ARGUMENT_BYTES)]
 
 
+LAUNCH_CHAIN, LAUNCH_SIDE, LAUNCH_RESUME, LAUNCH_JOIN, LAUNCH_SIDE_MORE = range(5)
+BACKEND_COPY, EXCHANGE_OWN_ARENA = 0xFFFFFFFE, 0xFFFFFFFFFFFFFFFF
+
+
+class ExchangePlace(C.Structure):
+    _fields_ = [("address_word_offset", C.c_uint64), ("offset", C.c_uint64)]
+
+
+class ExchangeCopy(C.Structure):
+    _fields_ = [("source", ExchangePlace), ("destination", ExchangePlace), ("byte_count", C.c_uint64)]
+
+
+class LaunchOrder(C.Structure):
+    _fields_ = [("behind_count", C.c_uint32), ("behind", C.c_uint32 * 5)]
+
+
+def copy_launch(source_offset, destination_offset, byte_count, branch=LAUNCH_CHAIN, source_word=EXCHANGE_OWN_ARENA,
+                destination_word=EXCHANGE_OWN_ARENA):
+    """A launch of BACKEND_COPY: byte_count bytes between two places (own arena, or behind an address word)."""
+    launch = KernelLaunch()
+    launch.kernel, launch.branch, launch.argument_byte_count = BACKEND_COPY, branch, C.sizeof(ExchangeCopy)
+    record = ExchangeCopy(ExchangePlace(source_word, source_offset), ExchangePlace(destination_word, destination_offset),
+                          byte_count)
+    C.memmove(launch.argument, C.byref(record), C.sizeof(record))
+    return launch
+
+
 class CardDescription(C.Structure):
     _fields_ = [("name", C.c_char * 96), ("bus_address", C.c_char * 32), ("arithmetic_class", C.c_uint32),
                 ("link_generation", C.c_uint32), ("link_lane_count", C.c_uint32), ("reserved_zero", C.c_uint32),

@@ -16,9 +16,12 @@
  *     source/backend_cuda_launch.c:170, does not exist in CUDA 12.9);
  *   - the card uses the device's primary context, so that runtime-API code of the same process shares its memory;
  *   - peer_connect needs no gate record: on NVLink/NVSwitch every ordered pair is direct;
- *   - exchange memory, peer_attach (the gated form), digest, staging_retire and BACKEND_COPY launches are not offered
- *     (NULL members / STATUS_UNSUPPORTED), as the table's contract allows for an entry a backend does not have;
- *   - graph_capture takes LAUNCH_CHAIN tables only (fork/join branches: STATUS_UNSUPPORTED).
+ *   - exchange memory, peer_attach (the gated form), digest and staging_retire are not offered (NULL members /
+ *     STATUS_UNSUPPORTED), as the table's contract allows for an entry a backend does not have;
+ *   - a table whose branches do not follow the grammar of LAUNCH_* is refused with STATUS_INVALID_ARGUMENT before the
+ *     driver is asked for anything (the reference finds out while it builds the graph: STATUS_DEVICE_ERROR);
+ *   - a table of LAUNCH_CHAIN kernel launches alone becomes a graph by stream capture; any other table (side runs,
+ *     BACKEND_COPY launches) is built node by node with the dependencies backend_b200_launch_order states.
  */
 #ifndef ANEMONE_B200_BACKEND_H
 #define ANEMONE_B200_BACKEND_H
@@ -100,6 +103,7 @@ struct device_card; /* opaque to every caller */
 #define LAUNCH_RESUME 2u
 #define LAUNCH_JOIN 3u
 #define LAUNCH_SIDE_MORE 4u
+#define LAUNCH_MOST_SIDE_RUNS 4u
 struct kernel_launch {
 	uint32_t kernel;
 	uint32_t grid[LAUNCH_DIMENSIONS];
@@ -108,6 +112,35 @@ struct kernel_launch {
 	uint32_t argument_byte_count;
 	uint32_t branch;
 	unsigned char argument[LAUNCH_ARGUMENT_BYTES];
+};
+
+/* A launch whose kernel is BACKEND_COPY is a copy between device memories, run by a copy engine (a memcpy node of a
+ * graph, an asynchronous copy of launch_run); its record (include/anemone/exchange_records.h:81-84, 128-133): */
+#define EXCHANGE_OWN_ARENA UINT64_MAX /* in place of an address word: the card's own arena */
+#define EXCHANGE_COPY_ARGUMENT_BYTES 40u
+struct exchange_place {
+	uint64_t address_word_offset; /* of a word peer_connect wrote into the card's arena, or EXCHANGE_OWN_ARENA */
+	uint64_t offset;	      /* from the address the word holds */
+};
+struct exchange_copy_arguments {
+	struct exchange_place source;
+	struct exchange_place destination;
+	uint64_t byte_count; /* 1 or more */
+};
+#ifdef __cplusplus
+static_assert(sizeof(struct exchange_copy_arguments) == EXCHANGE_COPY_ARGUMENT_BYTES, "a copy launch's record");
+#else
+_Static_assert(sizeof(struct exchange_copy_arguments) == EXCHANGE_COPY_ARGUMENT_BYTES, "a copy launch's record");
+#endif
+
+/* The launches a launch of a table waits for in a graph: CHAIN behind the launch before it; a run of SIDE launches
+ * behind the launch before the run (the fork), each behind the one before it; SIDE_MORE behind the fork alone (another
+ * side run of one launch, at most LAUNCH_MOST_SIDE_RUNS runs a fork); RESUME behind the fork, not the side runs; JOIN
+ * behind the launch before it and every side run's last. A side run at the head of the table forks at the graph's
+ * root (behind nothing, as RESUME then is). */
+struct launch_order {
+	uint32_t behind_count;
+	uint32_t behind[1u + LAUNCH_MOST_SIDE_RUNS]; /* indices into the table, ascending, none twice */
 };
 
 /* include/anemone/backend_seam.h:206-308, member for member. */
@@ -201,6 +234,13 @@ MUST_CHECK result_status backend_b200_step_run(struct device_card *card, uint32_
 					       uint64_t input_byte_count, uint64_t output_arena_offset,
 					       void *page_locked_output, uint64_t output_byte_count);
 /* Kernel launches this card has queued since it was opened, graph launches counted by their kernel nodes. */
+/* The dependencies graph_capture gives every launch of a table (order_out[launch_count]), from the branches alone: no
+ * card is needed. STATUS_INVALID_ARGUMENT for a NULL, an empty table, a branch that is none of LAUNCH_* or a table
+ * outside the grammar (SIDE right behind SIDE_MORE; SIDE_MORE or RESUME not behind a side run; a fifth side run; JOIN
+ * without a side run); order_out is then untouched. */
+MUST_CHECK result_status backend_b200_launch_order(const struct kernel_launch *launches, uint32_t launch_count,
+						   struct launch_order *order_out);
+
 uint64_t backend_b200_launch_count(const struct device_card *card);
 /* The device address of the arena (diagnostics and interoperation with other libraries of the same process). */
 uint64_t backend_b200_arena_address(const struct device_card *card);

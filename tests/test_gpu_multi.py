@@ -317,3 +317,34 @@ def test_output_axis_exchanges_across_cards(api, oracle, kind, mode):
         finally:
             for card in cards:
                 card.close()
+
+
+def test_copy_launches_to_peers_at_once(api):
+    """One graph on card 0: a copy into every other card's arena, each on a side run of its own (the reference's use of
+    LAUNCH_SIDE_MORE, include/anemone/backend_seam.h:183-195), and a copy behind the join."""
+    for ranks in world_sizes(api):
+        ranks = min(ranks, 5)  # a fork has at most four side runs
+        bytes_each, arena_bytes = 1 << 20, 8 << 20
+        cards = [api.Card(rank, arena_bytes) for rank in range(ranks)]
+        try:
+            rng = np.random.default_rng(ranks)
+            payload = rng.integers(0, 256, bytes_each).astype(np.uint8)
+            for card in cards:
+                card.fill(0, 0, arena_bytes)
+            cards[0].upload(1 << 20, payload)
+            table = [R.copy_launch(1 << 20, 2 << 20, bytes_each)]
+            for peer in range(1, ranks):
+                cards[0].peer_connect(cards[peer], 4 << 20, 8 * peer)
+                table.append(R.copy_launch(2 << 20, 0, bytes_each, R.LAUNCH_SIDE if peer == 1 else R.LAUNCH_SIDE_MORE,
+                                           destination_word=8 * peer))
+            table.append(R.copy_launch(2 << 20, 3 << 20, bytes_each, R.LAUNCH_JOIN))
+            graph = cards[0].graph(table)
+            cards[0].graph_run(graph)
+            cards[0].wait()
+            assert np.array_equal(cards[0].download(3 << 20, bytes_each), payload)
+            for peer in range(1, ranks):
+                cards[peer].wait()
+                assert np.array_equal(cards[peer].download(4 << 20, bytes_each), payload)
+        finally:
+            for card in cards:
+                card.close()

@@ -29,7 +29,7 @@ def values_for(rng, ranks, packs, kind):
              (120 - rng.integers(0, spread, count)) << 7).astype(np.uint16)
         x[::17], x[1::17], x[5::131] = 0, 0x8000, 0x0003
         inputs.append(x)
-    inputs[0][2::257] = 0x7F80
+    inputs[0][2::4099] = 0x7F80
     return inputs
 
 
