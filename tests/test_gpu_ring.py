@@ -194,7 +194,7 @@ def test_compressed_exchange(api, oracle, mode, rank, ranks, packs, vectors, kin
                         used = 4 + 96 + bin(int(want[1])).count("1")
                         assert np.array_equal(packet[:used], want[:used])  # the same words on the wire
                         coded += 32 - bin(int(want[1])).count("1")
-            assert coded > 0
+            assert coded > 0 or kind == "wide"  # near exponents: most lanes travel as three words
             for slot in range(2 * (ranks - 1)):  # and it told every sender that its packet was taken
                 sender = (rank + 1 + slot % (ranks - 1)) % ranks
                 for group in range(packs // 32):
