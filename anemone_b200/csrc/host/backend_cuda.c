@@ -719,7 +719,7 @@ static bool launch_is_valid(const struct device_card *card, const struct kernel_
 	if (launch->kernel >= card->kernel_count ||
 	    launch->argument_byte_count != card->kernels[launch->kernel].argument_byte_count ||
 	    launch->dynamic_shared_byte_count > (uint32_t)card->shared_memory_most ||
-	    launch->branch > LAUNCH_SIDE_MORE)
+	    (launch->branch > LAUNCH_SIDE_MORE && launch->branch != (LAUNCH_CHAIN | LAUNCH_OVERLAPS_PREVIOUS)))
 		return false;
 	uint64_t threads = 1;
 	for (uint32_t axis = 0; axis < LAUNCH_DIMENSIONS; axis++) {
@@ -755,6 +755,24 @@ static result_status launches_queue(const struct ab_driver *cu, struct device_ca
 		memcpy(record, launch->argument, launch->argument_byte_count);
 		CUdeviceptr arena = card->arena;
 		void *parameters[] = { record, &arena };
+		if ((launch->branch & LAUNCH_OVERLAPS_PREVIOUS) != 0 && index != 0) {
+			/* behind the launch before it by a programmatic edge: it may start once that launch lets it */
+			CUlaunchAttribute attribute;
+			memset(&attribute, 0, sizeof(attribute));
+			attribute.id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
+			attribute.value.programmaticStreamSerializationAllowed = 1;
+			CUlaunchConfig config;
+			memset(&config, 0, sizeof(config));
+			config.gridDimX = launch->grid[0], config.gridDimY = launch->grid[1], config.gridDimZ = launch->grid[2];
+			config.blockDimX = launch->block[0], config.blockDimY = launch->block[1];
+			config.blockDimZ = launch->block[2];
+			config.sharedMemBytes = launch->dynamic_shared_byte_count;
+			config.hStream = card->stream;
+			config.attrs = &attribute;
+			config.numAttrs = 1;
+			DRIVER(card, cuLaunchKernelEx(&config, card->kernels[launch->kernel].handle, parameters, NULL));
+			continue;
+		}
 		DRIVER(card, cuLaunchKernel(card->kernels[launch->kernel].handle, launch->grid[0], launch->grid[1],
 					    launch->grid[2], launch->block[0], launch->block[1], launch->block[2],
 					    launch->dynamic_shared_byte_count, card->stream, parameters, NULL));
@@ -792,8 +810,11 @@ result_status backend_b200_launch_order(const struct kernel_launch *launches, ui
 		const uint32_t none = UINT32_MAX;
 		uint32_t fork = none, run_last[LAUNCH_MOST_SIDE_RUNS], runs = 0;
 		for (uint32_t index = 0; index < launch_count; index++) {
-			const uint32_t branch = launches[index].branch, previous = index == 0 ? none : index - 1u;
-			const uint32_t before = index == 0 ? LAUNCH_CHAIN : launches[index - 1u].branch;
+			const uint32_t overlap = (uint32_t)LAUNCH_OVERLAPS_PREVIOUS;
+			const uint32_t branch = launches[index].branch == (LAUNCH_CHAIN | overlap) ? LAUNCH_CHAIN :
+												  launches[index].branch;
+			const uint32_t previous = index == 0 ? none : index - 1u;
+			const uint32_t before = index == 0 ? LAUNCH_CHAIN : launches[index - 1u].branch & ~overlap;
 			const bool in_side = before == LAUNCH_SIDE || before == LAUNCH_SIDE_MORE;
 			uint32_t wanted[1u + LAUNCH_MOST_SIDE_RUNS], wanted_count = 0;
 			switch (branch) {
@@ -851,7 +872,8 @@ result_status backend_b200_launch_order(const struct kernel_launch *launches, ui
 static bool table_is_a_plain_chain(const struct kernel_launch *launches, uint32_t launch_count)
 {
 	for (uint32_t index = 0; index < launch_count; index++)
-		if (launches[index].kernel == BACKEND_COPY || launches[index].branch != LAUNCH_CHAIN)
+		if (launches[index].kernel == BACKEND_COPY ||
+		    (launches[index].branch & ~(uint32_t)LAUNCH_OVERLAPS_PREVIOUS) != LAUNCH_CHAIN)
 			return false;
 	return true;
 }

@@ -50,6 +50,7 @@
 	X(cuFuncGetAttribute)     \
 	X(cuFuncSetAttribute)     \
 	X(cuLaunchKernel)         \
+	X(cuLaunchKernelEx)       \
 	X(cuStreamBeginCapture)   \
 	X(cuStreamEndCapture)     \
 	X(cuGraphInstantiateWithFlags) \

@@ -283,9 +283,10 @@ void exl3_layer_sizes(uint32_t pair_count, uint32_t job_count, uint32_t input_si
 	if (sizes_out == NULL)
 		return;
 	if (input_size != 0 && inner_size != 0 && input_size % EXL3_TRANSFORM == 0 && inner_size % EXL3_TRANSFORM == 0) {
-		const uint64_t gate_up = (uint64_t)EXL3_PROJECTIONS * EXL3_LAYER_MAXIMUM_RUNS * pair_count * inner_size * 4u;
+		/* down's partial sums in a range of their own: the down launch may write while gate/up's are still read */
+		const uint64_t gate_up = exl3_layer_gate_up_product_bytes(pair_count, inner_size);
 		const uint64_t down = (uint64_t)EXL3_LAYER_MAXIMUM_RUNS * pair_count * input_size * 4u;
-		sizes.product_bytes = gate_up > down ? gate_up : down;
+		sizes.product_bytes = gate_up + down;
 		sizes.operand_bytes = (uint64_t)pair_count * input_size * EXL3_OPERAND_BYTES_PER_INPUT +
 				      (uint64_t)pair_count * inner_size * EXL3_HALF_BYTES;
 		sizes.counter_bytes = exl3_layer_counter_bytes(job_count, input_size, inner_size);
@@ -382,10 +383,14 @@ result_status exl3_layer_prepare(const struct exl3_layer_description *descriptio
 				.rank = publish->rank,
 				.reserved_zero = 0 },
 		.status_offset = publish->status_offset,
-		.pair_output_offset = base->output_offset,
+		.pair_output_offset = base->output_offset + exl3_layer_gate_up_product_bytes(base->pair_count, I),
 		.width = H,
 		.pairs_per_row = slots
 	};
+	/* the down launch's record: its partial sums and the pair outputs (run 0 of them) behind gate/up's */
+	struct exl3_moe_record down_record = *moe;
+	down_record.base.products_offset += exl3_layer_gate_up_product_bytes(base->pair_count, I);
+	down_record.base.output_offset = down_record.base.products_offset;
 	/* the transform's warp tasks: (pair, gate or up, 128 inputs); eight warps a CTA, a few tasks a warp */
 	const uint64_t tasks = (uint64_t)rows * slots * EXL3_PROJECTIONS * (H / EXL3_TRANSFORM);
 	/* a task is a chain of dependent loads (pick, table, scale, row): one a warp where the card holds that many
@@ -406,8 +411,8 @@ result_status exl3_layer_prepare(const struct exl3_layer_description *descriptio
 		  EXL3_LAYER_ROUTE_THREADS, 0 },
 		{ EXL3_LAYER_KERNEL_FILE, "exl3_layer_gate_up", moe, sizeof(*moe), I / EXL3_TRANSFORM * gate_up_runs,
 		  base->job_count, EXL3_PROJECTIONS, EXL3_PRODUCT_THREADS, shared },
-		{ EXL3_LAYER_KERNEL_FILE, "exl3_layer_down", moe, sizeof(*moe), H / EXL3_TRANSFORM * down_runs, base->job_count,
-		  1, EXL3_PRODUCT_THREADS, shared },
+		{ EXL3_LAYER_KERNEL_FILE, "exl3_layer_down", &down_record, sizeof(down_record), H / EXL3_TRANSFORM * down_runs,
+		  base->job_count, 1, EXL3_PRODUCT_THREADS, shared },
 		{ KERNEL_FILE_ORDERED_B200, KERNEL_ORDERED_PUBLISH_REDUCE_FLAGS, &reduce, sizeof(reduce), reduce_blocks, 1, 1,
 		  ORDERED_COLLECTIVE_THREADS, 0 }
 	};
@@ -424,6 +429,11 @@ result_status exl3_layer_prepare(const struct exl3_layer_description *descriptio
 				    shapes[index].threads, shapes[index].shared, shapes[index].record,
 				    shapes[index].record_bytes);
 	}
+	/* Each launch may be given its place on the card while the one before it still runs: the gate/up products and the
+	 * reduction wait for the whole launch before them as their first act, the down products' CTAs for their job's
+	 * operands (so that they fill the room the last gate/up CTAs leave). */
+	for (uint32_t index = 1; index < EXL3_LAYER_LAUNCHES; index++)
+		launches[index].branch = LAUNCH_CHAIN | LAUNCH_OVERLAPS_PREVIOUS;
 	memcpy(launches_out, launches, sizeof(launches));
 	return STATUS_OK;
 }

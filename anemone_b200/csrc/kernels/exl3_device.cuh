@@ -200,7 +200,8 @@ struct exl3_product_shared {
  * Warp w takes step 4 r + w of round r. A lane reads its two ring words of each of the eight tiles of a step straight
  * from global memory into registers (the warp's 16 loads of a step cover 8 x 16 bits_x2 contiguous bytes), one round
  * ahead of the round it decodes, together with that round's operands: no shared memory, no barrier and no producer
- * stand between the memory system and the decode, whose instruction issue is what bounds the kernel.
+ * stand between the memory system and the decode, whose instruction issue is what bounds the kernel. The operands are
+ * read past the L1 (they may have been written by a launch that still runs beside this one); the weights through it.
  * Returns true (the signature keeps a verdict for callers written for a core with bounded waits). All 128 threads
  * call it. */
 template <uint32_t BX2>
@@ -240,8 +241,8 @@ __device__ __forceinline__ bool exl3_product_core(const unsigned char *matrix, u
 			set[tile][0] = __ldg(from + tile * ring::words + word_index);                          \
 			set[tile][1] = __ldg(from + tile * ring::words + next_index);                          \
 		}                                                                                              \
-		set_fed[0] = __ldg(fed + (uint64_t)(round) * fed_round_words);                                 \
-		set_fed[1] = __ldg(fed + (uint64_t)(round) * fed_round_words + 4);                             \
+		set_fed[0] = __ldcg(fed + (uint64_t)(round) * fed_round_words);                                \
+		set_fed[1] = __ldcg(fed + (uint64_t)(round) * fed_round_words + 4);                            \
 	} while (0)
 #define EXL3_ROUND_MULTIPLY(set, set_fed)                                                                     \
 	do {                                                                                                   \

@@ -147,7 +147,8 @@ __device__ __forceinline__ void exl3_down_epilogue(const struct exl3_moe_record 
 template <uint32_t BX2>
 __device__ __forceinline__ void moe_gate_up(const struct exl3_moe_record &moe, unsigned char *arena,
 					    const struct expert_job_record *job, uint32_t runs,
-					    unsigned char *dynamic_shared, exl3_product_shared *shared, uint32_t *flag)
+					    unsigned char *dynamic_shared, exl3_product_shared *shared, uint32_t *flag,
+					    uint32_t *ready)
 {
 	const struct exl3_expert_record &record = moe.base;
 	const uint32_t lane = threadIdx.x % EXL3_WARP;
@@ -176,13 +177,20 @@ __device__ __forceinline__ void moe_gate_up(const struct exl3_moe_record &moe, u
 		return;
 	exl3_gate_up_epilogue<BX2>(moe, arena, job, group, partials, partials + (uint64_t)runs * run_stride, run_stride, runs,
 				   runs);
+	if (ready != nullptr) { /* one more group of the job's down operands is in place, for a launch that runs beside */
+		__threadfence();
+		__syncthreads();
+		if (threadIdx.x == 0)
+			atomicAdd(ready + blockIdx.y, 1u);
+	}
 }
 
 /* The same for down: grid (input_size / 128 * runs, jobs). */
 template <uint32_t BX2>
 __device__ __forceinline__ void moe_down(const struct exl3_moe_record &moe, unsigned char *arena,
 					 const struct expert_job_record *job, uint32_t runs,
-					 unsigned char *dynamic_shared, exl3_product_shared *shared, uint32_t *flag)
+					 unsigned char *dynamic_shared, exl3_product_shared *shared, uint32_t *flag,
+					 uint32_t *)
 {
 	const struct exl3_expert_record &record = moe.base;
 	const uint32_t lane = threadIdx.x % EXL3_WARP;
@@ -216,16 +224,16 @@ __device__ __forceinline__ void moe_down(const struct exl3_moe_record &moe, unsi
 #define EXL3_FUSED_WIDTH_SWITCH(function)                                                      \
 	switch (exl3_job_bits_x2(record.base, job, moe_widths(record, arena))) {               \
 	case EXL3_BITS_X2_K2:                                                                  \
-		function<EXL3_BITS_X2_K2>(record, arena, job, runs, dynamic_shared, shared, flag);   \
+		function<EXL3_BITS_X2_K2>(record, arena, job, runs, dynamic_shared, shared, flag, ready);   \
 		break;                                                                         \
 	case EXL3_BITS_X2_K2_5:                                                                \
-		function<EXL3_BITS_X2_K2_5>(record, arena, job, runs, dynamic_shared, shared, flag); \
+		function<EXL3_BITS_X2_K2_5>(record, arena, job, runs, dynamic_shared, shared, flag, ready); \
 		break;                                                                         \
 	case EXL3_BITS_X2_K3:                                                                  \
-		function<EXL3_BITS_X2_K3>(record, arena, job, runs, dynamic_shared, shared, flag);   \
+		function<EXL3_BITS_X2_K3>(record, arena, job, runs, dynamic_shared, shared, flag, ready);   \
 		break;                                                                         \
 	case EXL3_BITS_X2_K4:                                                                  \
-		function<EXL3_BITS_X2_K4>(record, arena, job, runs, dynamic_shared, shared, flag);   \
+		function<EXL3_BITS_X2_K4>(record, arena, job, runs, dynamic_shared, shared, flag, ready);   \
 		break;                                                                         \
 	default:                                                                               \
 		break;                                                                         \
@@ -234,7 +242,8 @@ __device__ __forceinline__ void moe_down(const struct exl3_moe_record &moe, unsi
 /* the bodies of the two product kernels of the fixed cut, for any entry that holds a struct exl3_moe_record */
 __device__ __forceinline__ void exl3_moe_gate_up_block(const struct exl3_moe_record &record, unsigned char *arena,
 						       uint32_t runs, unsigned char *dynamic_shared,
-						       exl3_product_shared *shared, uint32_t *flag)
+						       exl3_product_shared *shared, uint32_t *flag,
+						       uint32_t *ready = nullptr)
 {
 	const struct expert_job_record *const job = exl3_job(record.base, arena, blockIdx.y);
 	if (job->row_count == 0)
@@ -246,6 +255,7 @@ __device__ __forceinline__ void exl3_moe_down_block(const struct exl3_moe_record
 						    uint32_t runs, unsigned char *dynamic_shared,
 						    exl3_product_shared *shared, uint32_t *flag)
 {
+	uint32_t *const ready = nullptr;
 	const struct expert_job_record *const job = exl3_job(record.base, arena, blockIdx.y);
 	if (job->row_count == 0)
 		return;

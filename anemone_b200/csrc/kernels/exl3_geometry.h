@@ -52,10 +52,19 @@ AB_INLINE uint64_t exl3_layer_counter_begin(uint32_t job_count, uint32_t input_s
 	return (uint64_t)job_count * (inner_size / EXL3_TRANSFORM + input_size / EXL3_TRANSFORM);
 }
 
-/* bytes at counters_offset in the layer form: the per-(job, group) counters, then the layer's words */
+/* bytes at counters_offset in the layer form: the per-(job, group) counters, then the layer's words, then a word a
+ * job: how many groups of 128 inner channels of the job have their down operands in place (the router's launch
+ * zeroes them, the gate/up launch counts, the down launch, which may begin before the gate/up launch ends, reads) */
 AB_INLINE uint64_t exl3_layer_counter_bytes(uint32_t job_count, uint32_t input_size, uint32_t inner_size)
 {
-	return (exl3_layer_counter_begin(job_count, input_size, inner_size) + EXL3_LAYER_COUNTER_WORDS) * 4u;
+	return (exl3_layer_counter_begin(job_count, input_size, inner_size) + EXL3_LAYER_COUNTER_WORDS + job_count) * 4u;
+}
+
+/* the FP32 partial sums of the layer form: gate/up's [2][runs][pairs][inner], then, in a range of their own (the down
+ * launch may write while the gate/up launch still reads), down's [runs][pairs][input] */
+AB_INLINE uint64_t exl3_layer_gate_up_product_bytes(uint32_t pair_count, uint32_t inner_size)
+{
+	return (uint64_t)EXL3_PROJECTIONS * EXL3_LAYER_MAXIMUM_RUNS * pair_count * inner_size * 4u;
 }
 
 /* ---- prefill (kernel_exl3_prefill) ---- */

@@ -12,6 +12,8 @@
 #include "exl3_fused.cuh"
 #include "router_device.cuh"
 
+#define EXL3_LAYER_READY_POLLS 2048u /* of about 200 ns each, before a down CTA waits for the whole launch before it */
+
 __device__ __forceinline__ uint32_t *layer_words(const struct exl3_moe_record &moe, unsigned char *arena)
 {
 	return reinterpret_cast<uint32_t *>(arena + moe.counters_offset) +
@@ -28,6 +30,8 @@ extern "C" __global__ void __launch_bounds__(EXL3_LAYER_ROUTE_THREADS)
 	__shared__ unsigned long long row_mask[ROUTER_B200_MAXIMUM_EXPERTS];
 	__shared__ uint32_t first_job[ROUTER_B200_MAXIMUM_EXPERTS];
 	const struct exl3_expert_record &base = record.moe.base;
+	/* the gate/up launch may take its place on the card now: it waits for the whole of this launch before it reads */
+	asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 	const struct step_block step = *reinterpret_cast<const struct step_block *>(arena + record.step_offset);
 	const uint32_t live = min(step.row_count, record.row_capacity);
 	const uint32_t routed = record.routed_count, picks = record.picks, shared = record.shared_count;
@@ -46,6 +50,8 @@ extern "C" __global__ void __launch_bounds__(EXL3_LAYER_ROUTE_THREADS)
 	const uint64_t *const table = reinterpret_cast<const uint64_t *>(arena + record.expert_table_offset);
 	if (writer) {
 		uint32_t *const words = layer_words(record.moe, arena);
+		for (uint32_t job = threadIdx.x; job < base.job_count; job += blockDim.x)
+			words[EXL3_LAYER_COUNTER_WORDS + job] = 0u; /* no job's down operands are in place yet */
 		router_job_table(live, routed, picks, shared, base.job_count, chosen, weight, row_mask, first_job,
 				 reinterpret_cast<struct expert_job_record *>(arena + base.jobs_offset), table,
 				 &words[EXL3_LAYER_WORD_LIVE_JOBS]);
@@ -92,8 +98,14 @@ extern "C" __global__ void __launch_bounds__(EXL3_PRODUCT_THREADS)
 	extern __shared__ __align__(128) unsigned char dynamic_shared[];
 	__shared__ exl3_product_shared shared;
 	__shared__ uint32_t flag;
+	/* This launch may have begun while the router's still runs: everything it reads is that launch's, so it waits for
+	 * the whole of it. Only then may the down launch be given the card's free room (once every CTA of this grid has
+	 * said so or ended, which is when the last of them has begun): its CTAs read the job table, which must be this
+	 * step's, and wait for their job's operands themselves. */
+	asm volatile("griddepcontrol.wait;" ::: "memory");
+	asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 	exl3_moe_gate_up_block(record, arena, gridDim.x / (record.base.inner_size / EXL3_TRANSFORM), dynamic_shared, &shared,
-			       &flag);
+			       &flag, layer_words(record, arena) + EXL3_LAYER_COUNTER_WORDS);
 }
 
 /* ------------------------------------------------------------------ down products */
@@ -105,6 +117,27 @@ extern "C" __global__ void __launch_bounds__(EXL3_PRODUCT_THREADS)
 	extern __shared__ __align__(128) unsigned char dynamic_shared[];
 	__shared__ exl3_product_shared shared;
 	__shared__ uint32_t flag;
+	/* This launch may have begun while the gate/up launch still runs. The job table is older than both; the job's
+	 * down operands are in place once every group of its inner channels has been counted. A CTA looks for that a
+	 * bounded number of times, then waits for the whole gate/up launch (which is all a launch that began behind it
+	 * does anyway): it cannot wait in vain. */
+	asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); /* the reduction's launch waits for all of this one */
+	if (exl3_job(record.base, arena, blockIdx.y)->row_count == 0)
+		return;
+	if (threadIdx.x == 0) {
+		const uint32_t *const ready = layer_words(record, arena) + EXL3_LAYER_COUNTER_WORDS + blockIdx.y;
+		const uint32_t wanted = record.base.inner_size / EXL3_TRANSFORM;
+		uint32_t seen = 0;
+		for (uint32_t poll = 0; poll < EXL3_LAYER_READY_POLLS; poll++) {
+			asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(ready) : "memory");
+			if (seen == wanted)
+				break;
+			__nanosleep(200);
+		}
+		if (seen != wanted)
+			asm volatile("griddepcontrol.wait;" ::: "memory");
+	}
+	__syncthreads();
 	exl3_moe_down_block(record, arena, gridDim.x / (record.base.input_size / EXL3_TRANSFORM), dynamic_shared, &shared,
 			    &flag);
 }

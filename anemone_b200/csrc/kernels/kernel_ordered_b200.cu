@@ -206,6 +206,8 @@ extern "C" __global__ void __launch_bounds__(ORDERED_COLLECTIVE_THREADS)
 {
 	__shared__ uint32_t verdict, last;
 	const struct ordered_collective_arguments &collective = arguments.collective;
+	/* the launch may have been given its place on the card while the down products still run: all of them first */
+	asm volatile("griddepcontrol.wait;" ::: "memory");
 	const struct step_block step = *reinterpret_cast<const struct step_block *>(arena + collective.step_offset);
 	const uint64_t sequence = step.sequence;
 	if (sequence == 0 || collective.rank_count == 0 || collective.rank_count > ORDERED_COLLECTIVE_MAXIMUM_RANKS)

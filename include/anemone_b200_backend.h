@@ -104,6 +104,12 @@ struct device_card; /* opaque to every caller */
 #define LAUNCH_JOIN 3u
 #define LAUNCH_SIDE_MORE 4u
 #define LAUNCH_MOST_SIDE_RUNS 4u
+/* New with this library, OR-ed into a LAUNCH_CHAIN branch: the launch may begin while the launch before it still runs
+ * (programmatic dependent launch). Only for a kernel that orders itself behind what it reads of that launch (with
+ * griddepcontrol.wait, or flags that launch sets); launch_run and a captured chain honour it, a graph built node by
+ * node runs the launch behind the whole of the launch before it. The bit is set only in launches this library's own layer preparers write; the
+ * reference's backend would refuse it as a branch it does not know. */
+#define LAUNCH_OVERLAPS_PREVIOUS 0x100u
 struct kernel_launch {
 	uint32_t kernel;
 	uint32_t grid[LAUNCH_DIMENSIONS];
