@@ -330,10 +330,10 @@ result_status exl3_layer_prepare(const struct exl3_layer_description *descriptio
 	    publish->parity_stride < publish->input_offset + (uint64_t)rows * H * 4u || H % EXL3_TRANSFORM != 0 ||
 	    I == 0 || I % EXL3_TRANSFORM != 0)
 		return STATUS_INVALID_ARGUMENT;
-	/* the cut of the two product launches: the caller's, or the fixed cut's (measured on one to eight ranks' shapes:
-	 * between 2 and 8 runs of gate/up differ by a few percent, fewer lose) */
-	const uint32_t gate_up_runs = description->gate_up_runs != 0 ? description->gate_up_runs : exl3_moe_splits(H, I);
-	const uint32_t down_runs = description->down_runs != 0 ? description->down_runs : exl3_moe_splits(I, H);
+	/* the cut of the products: the caller's, or the measured default of exl3_geometry.h */
+	const uint32_t gate_up_runs =
+		description->gate_up_runs != 0 ? description->gate_up_runs : exl3_layer_gate_up_runs(H, I);
+	const uint32_t down_runs = description->down_runs != 0 ? description->down_runs : 1u;
 	if (!layer_runs_are_valid(gate_up_runs, H / EXL3_TRANSFORM) || !layer_runs_are_valid(down_runs, I / EXL3_TRANSFORM))
 		return STATUS_INVALID_ARGUMENT;
 	struct exl3_moe_sizes sizes;
@@ -387,10 +387,13 @@ result_status exl3_layer_prepare(const struct exl3_layer_description *descriptio
 		.width = H,
 		.pairs_per_row = slots
 	};
-	/* the down launch's record: its partial sums and the pair outputs (run 0 of them) behind gate/up's */
-	struct exl3_moe_record down_record = *moe;
-	down_record.base.products_offset += exl3_layer_gate_up_product_bytes(base->pair_count, I);
-	down_record.base.output_offset = down_record.base.products_offset;
+	/* the products' record: down's partial sums and the pair outputs (run 0 of them) behind gate/up's */
+	const struct exl3_layer_products_record products = {
+		.moe = *moe,
+		.down_products_offset = base->products_offset + exl3_layer_gate_up_product_bytes(base->pair_count, I),
+		.gate_up_runs = gate_up_runs,
+		.down_runs = down_runs
+	};
 	/* the transform's warp tasks: (pair, gate or up, 128 inputs); eight warps a CTA, a few tasks a warp */
 	const uint64_t tasks = (uint64_t)rows * slots * EXL3_PROJECTIONS * (H / EXL3_TRANSFORM);
 	/* a task is a chain of dependent loads (pick, table, scale, row): one a warp where the card holds that many
@@ -409,10 +412,9 @@ result_status exl3_layer_prepare(const struct exl3_layer_description *descriptio
 	} shapes[EXL3_LAYER_LAUNCHES] = {
 		{ EXL3_LAYER_KERNEL_FILE, "exl3_layer_route_input", route, sizeof(*route), 1u + (uint32_t)transform_ctas, 1, 1,
 		  EXL3_LAYER_ROUTE_THREADS, 0 },
-		{ EXL3_LAYER_KERNEL_FILE, "exl3_layer_gate_up", moe, sizeof(*moe), I / EXL3_TRANSFORM * gate_up_runs,
-		  base->job_count, EXL3_PROJECTIONS, EXL3_PRODUCT_THREADS, shared },
-		{ EXL3_LAYER_KERNEL_FILE, "exl3_layer_down", &down_record, sizeof(down_record), H / EXL3_TRANSFORM * down_runs,
-		  base->job_count, 1, EXL3_PRODUCT_THREADS, shared },
+		{ EXL3_LAYER_KERNEL_FILE, "exl3_layer_products", &products, sizeof(products),
+		  base->job_count * (EXL3_PROJECTIONS * (I / EXL3_TRANSFORM) * gate_up_runs + H / EXL3_TRANSFORM * down_runs), 1,
+		  1, EXL3_PRODUCT_THREADS, shared },
 		{ KERNEL_FILE_ORDERED_B200, KERNEL_ORDERED_PUBLISH_REDUCE_FLAGS, &reduce, sizeof(reduce), reduce_blocks, 1, 1,
 		  ORDERED_COLLECTIVE_THREADS, 0 }
 	};
@@ -429,9 +431,8 @@ result_status exl3_layer_prepare(const struct exl3_layer_description *descriptio
 				    shapes[index].threads, shapes[index].shared, shapes[index].record,
 				    shapes[index].record_bytes);
 	}
-	/* Each launch may be given its place on the card while the one before it still runs: the gate/up products and the
-	 * reduction wait for the whole launch before them as their first act, the down products' CTAs for their job's
-	 * operands (so that they fill the room the last gate/up CTAs leave). */
+	/* Each launch may be given its place on the card while the one before it still runs: the products and the
+	 * reduction wait for the whole launch before them as their first act. */
 	for (uint32_t index = 1; index < EXL3_LAYER_LAUNCHES; index++)
 		launches[index].branch = LAUNCH_CHAIN | LAUNCH_OVERLAPS_PREVIOUS;
 	memcpy(launches_out, launches, sizeof(launches));

@@ -119,7 +119,7 @@ __device__ __forceinline__ void exl3_gate_up_epilogue(const struct exl3_moe_reco
 template <uint32_t BX2>
 __device__ __forceinline__ void exl3_down_epilogue(const struct exl3_moe_record &moe, unsigned char *arena,
 						   const struct expert_job_record *job, uint32_t group, const float *first,
-						   uint64_t run_stride, uint32_t runs)
+						   uint64_t run_stride, uint32_t runs, uint64_t output_offset)
 {
 	const struct exl3_expert_record &record = moe.base;
 	const uint32_t lane = threadIdx.x % EXL3_WARP, warp = threadIdx.x / EXL3_WARP;
@@ -137,24 +137,30 @@ __device__ __forceinline__ void exl3_down_epilogue(const struct exl3_moe_record 
 #pragma unroll
 		for (uint32_t i = 0; i < 4; i++)
 			v[i] = __fmul_rn(__fmul_rn(__fmul_rn(v[i], EXL3_NORMALIZATION), scale[i]), weight);
-		*reinterpret_cast<float4 *>(reinterpret_cast<float *>(arena + record.output_offset) + at) =
+		*reinterpret_cast<float4 *>(reinterpret_cast<float *>(arena + output_offset) + at) =
 			make_float4(v[0], v[1], v[2], v[3]);
 	}
 }
 
-/* One CTA of the fixed cut: grid (outputs / 128 * runs, jobs, gate and up): run `blockIdx.x % runs` of K of 128 gate or
- * up outputs of job blockIdx.y; the CTA that completes the (job, 128 outputs) applies the activation. */
+/* what one pass of a product CTA works on: run `run` of the cut of K, of 128 outputs (`group`) of one matrix
+ * (`projection`: gate or up; 0 for down) of job `job` */
+struct moe_item {
+	uint32_t job, group, run, projection;
+};
+
+/* One item of gate or up: run item.run of K of 128 outputs of the job; the CTA that completes the (job, 128 outputs)
+ * applies the activation. ready (may be null): a word a job that counts the groups whose down operands are in place. */
 template <uint32_t BX2>
 __device__ __forceinline__ void moe_gate_up(const struct exl3_moe_record &moe, unsigned char *arena,
 					    const struct expert_job_record *job, uint32_t runs,
 					    unsigned char *dynamic_shared, exl3_product_shared *shared, uint32_t *flag,
-					    uint32_t *ready)
+					    uint32_t *ready, const struct moe_item &item, uint64_t)
 {
 	const struct exl3_expert_record &record = moe.base;
 	const uint32_t lane = threadIdx.x % EXL3_WARP;
 	const uint32_t H = record.input_size, I = record.inner_size, pairs = record.pair_count;
 	const uint32_t groups = I / EXL3_TRANSFORM;
-	const uint32_t group = blockIdx.x / runs, run = blockIdx.x % runs, projection = blockIdx.z;
+	const uint32_t group = item.group, run = item.run, projection = item.projection;
 	const uint32_t steps = H / EXL3_TILE / runs;
 	const uint32_t fed_column = lane / 4u < job->row_count ? lane / 4u : 0u;
 	const __half *const operands = reinterpret_cast<const __half *>(arena + record.operands_offset);
@@ -172,7 +178,7 @@ __device__ __forceinline__ void moe_gate_up(const struct exl3_moe_record &moe, u
 		rows[column] = partials + ((uint64_t)projection * runs + run) * run_stride +
 			       (uint64_t)job->pair_index[column < job->row_count ? column : 0u] * I + group * EXL3_TRANSFORM;
 	store_partial(sums, rows, job->row_count);
-	uint32_t *const counter = reinterpret_cast<uint32_t *>(arena + moe.counters_offset) + blockIdx.y * groups + group;
+	uint32_t *const counter = reinterpret_cast<uint32_t *>(arena + moe.counters_offset) + item.job * groups + group;
 	if (!last_of(counter, EXL3_PROJECTIONS * runs, flag))
 		return;
 	exl3_gate_up_epilogue<BX2>(moe, arena, job, group, partials, partials + (uint64_t)runs * run_stride, run_stride, runs,
@@ -181,7 +187,7 @@ __device__ __forceinline__ void moe_gate_up(const struct exl3_moe_record &moe, u
 		__threadfence();
 		__syncthreads();
 		if (threadIdx.x == 0)
-			atomicAdd(ready + blockIdx.y, 1u);
+			atomicAdd(ready + item.job, 1u);
 	}
 }
 
@@ -190,13 +196,13 @@ template <uint32_t BX2>
 __device__ __forceinline__ void moe_down(const struct exl3_moe_record &moe, unsigned char *arena,
 					 const struct expert_job_record *job, uint32_t runs,
 					 unsigned char *dynamic_shared, exl3_product_shared *shared, uint32_t *flag,
-					 uint32_t *)
+					 uint32_t *, const struct moe_item &item, uint64_t products_offset)
 {
 	const struct exl3_expert_record &record = moe.base;
 	const uint32_t lane = threadIdx.x % EXL3_WARP;
 	const uint32_t H = record.input_size, I = record.inner_size, pairs = record.pair_count;
 	const uint32_t groups = H / EXL3_TRANSFORM;
-	const uint32_t group = blockIdx.x / runs, run = blockIdx.x % runs;
+	const uint32_t group = item.group, run = item.run;
 	const uint32_t steps = I / EXL3_TILE / runs;
 	const uint32_t fed_column = lane / 4u < job->row_count ? lane / 4u : 0u;
 	const __half *const operands =
@@ -205,8 +211,8 @@ __device__ __forceinline__ void moe_down(const struct exl3_moe_record &moe, unsi
 	if (!exl3_product_core<BX2>(arena + job->down_offset, H, group, run * steps, steps,
 				    operands + (uint64_t)job->pair_index[fed_column] * I, dynamic_shared, shared, sums))
 		return;
-	/* partial sums: FP32 [run][pair][H]; run 0's rows are also where the pair outputs go */
-	float *const partials = reinterpret_cast<float *>(arena + record.products_offset);
+	/* partial sums: FP32 [run][pair][H] at products_offset; run 0's rows are also where the pair outputs go */
+	float *const partials = reinterpret_cast<float *>(arena + products_offset);
 	const uint64_t run_stride = (uint64_t)pairs * H;
 	float *rows[LINEAR_MAXIMUM_ROWS];
 #pragma unroll
@@ -215,29 +221,50 @@ __device__ __forceinline__ void moe_down(const struct exl3_moe_record &moe, unsi
 			       (uint64_t)job->pair_index[column < job->row_count ? column : 0u] * H + group * EXL3_TRANSFORM;
 	store_partial(sums, rows, job->row_count);
 	uint32_t *const counter = reinterpret_cast<uint32_t *>(arena + moe.counters_offset) +
-				  (uint64_t)record.job_count * (I / EXL3_TRANSFORM) + blockIdx.y * groups + group;
+				  (uint64_t)record.job_count * (I / EXL3_TRANSFORM) + item.job * groups + group;
 	if (!last_of(counter, runs, flag))
 		return;
-	exl3_down_epilogue<BX2>(moe, arena, job, group, partials, run_stride, runs);
+	exl3_down_epilogue<BX2>(moe, arena, job, group, partials, run_stride, runs, products_offset);
 }
 
 #define EXL3_FUSED_WIDTH_SWITCH(function)                                                      \
 	switch (exl3_job_bits_x2(record.base, job, moe_widths(record, arena))) {               \
 	case EXL3_BITS_X2_K2:                                                                  \
-		function<EXL3_BITS_X2_K2>(record, arena, job, runs, dynamic_shared, shared, flag, ready);   \
+		function<EXL3_BITS_X2_K2>(record, arena, job, runs, dynamic_shared, shared, flag, ready, item, products_offset);   \
 		break;                                                                         \
 	case EXL3_BITS_X2_K2_5:                                                                \
-		function<EXL3_BITS_X2_K2_5>(record, arena, job, runs, dynamic_shared, shared, flag, ready); \
+		function<EXL3_BITS_X2_K2_5>(record, arena, job, runs, dynamic_shared, shared, flag, ready, item, products_offset); \
 		break;                                                                         \
 	case EXL3_BITS_X2_K3:                                                                  \
-		function<EXL3_BITS_X2_K3>(record, arena, job, runs, dynamic_shared, shared, flag, ready);   \
+		function<EXL3_BITS_X2_K3>(record, arena, job, runs, dynamic_shared, shared, flag, ready, item, products_offset);   \
 		break;                                                                         \
 	case EXL3_BITS_X2_K4:                                                                  \
-		function<EXL3_BITS_X2_K4>(record, arena, job, runs, dynamic_shared, shared, flag, ready);   \
+		function<EXL3_BITS_X2_K4>(record, arena, job, runs, dynamic_shared, shared, flag, ready, item, products_offset);   \
 		break;                                                                         \
 	default:                                                                               \
 		break;                                                                         \
 	}
+
+/* one item of either kind, for an entry that walks a list of items (job: the item's) */
+__device__ __forceinline__ void exl3_moe_gate_up_item(const struct exl3_moe_record &record, unsigned char *arena,
+						      const struct moe_item &item, uint32_t runs,
+						      unsigned char *dynamic_shared, exl3_product_shared *shared,
+						      uint32_t *flag, uint32_t *ready)
+{
+	const uint64_t products_offset = 0;
+	const struct expert_job_record *const job = exl3_job(record.base, arena, item.job);
+	EXL3_FUSED_WIDTH_SWITCH(moe_gate_up)
+}
+
+__device__ __forceinline__ void exl3_moe_down_item(const struct exl3_moe_record &record, unsigned char *arena,
+						   const struct moe_item &item, uint32_t runs,
+						   unsigned char *dynamic_shared, exl3_product_shared *shared, uint32_t *flag,
+						   uint64_t products_offset)
+{
+	uint32_t *const ready = nullptr;
+	const struct expert_job_record *const job = exl3_job(record.base, arena, item.job);
+	EXL3_FUSED_WIDTH_SWITCH(moe_down)
+}
 
 /* the bodies of the two product kernels of the fixed cut, for any entry that holds a struct exl3_moe_record */
 __device__ __forceinline__ void exl3_moe_gate_up_block(const struct exl3_moe_record &record, unsigned char *arena,
@@ -245,6 +272,8 @@ __device__ __forceinline__ void exl3_moe_gate_up_block(const struct exl3_moe_rec
 						       exl3_product_shared *shared, uint32_t *flag,
 						       uint32_t *ready = nullptr)
 {
+	const uint64_t products_offset = 0;
+	const struct moe_item item = { blockIdx.y, blockIdx.x / runs, blockIdx.x % runs, blockIdx.z };
 	const struct expert_job_record *const job = exl3_job(record.base, arena, blockIdx.y);
 	if (job->row_count == 0)
 		return;
@@ -256,6 +285,8 @@ __device__ __forceinline__ void exl3_moe_down_block(const struct exl3_moe_record
 						    exl3_product_shared *shared, uint32_t *flag)
 {
 	uint32_t *const ready = nullptr;
+	const uint64_t products_offset = record.base.products_offset;
+	const struct moe_item item = { blockIdx.y, blockIdx.x / runs, blockIdx.x % runs, 0u };
 	const struct expert_job_record *const job = exl3_job(record.base, arena, blockIdx.y);
 	if (job->row_count == 0)
 		return;

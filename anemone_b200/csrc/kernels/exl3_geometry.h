@@ -45,6 +45,19 @@ AB_INLINE uint32_t exl3_moe_splits(uint32_t inputs, uint32_t outputs)
 #define EXL3_LAYER_PRODUCT_CTAS_PER_SM 5u /* resident product CTAs of 128 threads at their register count */
 #define EXL3_LAYER_DEFAULT_SMS 148u
 #define EXL3_LAYER_WORD_LIVE_JOBS 0u
+#define EXL3_LAYER_WORD_TICKET 1u /* the next item of the products' list; zero between steps */
+/* The default cut of the layer's products, measured on one to eight ranks' shapes of a hidden width of 4096 and an
+ * intermediate width of 2048 (a CTA an item; an item's fixed cost, the chain of dependent loads from its ticket to its
+ * first weights, is about 2.5 us of its place on the card): gate and up in 4 runs of K where the rank holds at least
+ * 1024 inner channels, in 8 below (more items of the fewer outputs); down in one run. Halved while it does not divide
+ * the K blocks of 128. */
+AB_INLINE uint32_t exl3_layer_gate_up_runs(uint32_t input_size, uint32_t inner_size)
+{
+	uint32_t runs = inner_size >= 1024u ? 4u : 8u;
+	while (runs > 1u && (input_size / EXL3_TRANSFORM) % runs != 0)
+		runs /= 2u;
+	return runs;
+}
 
 /* uint32 words of the moe record's counters that lie before the layer's own words */
 AB_INLINE uint64_t exl3_layer_counter_begin(uint32_t job_count, uint32_t input_size, uint32_t inner_size)

@@ -1,18 +1,19 @@
 /*
- * kernel_exl3_layer.cu: one decode step of a rank's expert layer in four launches (struct exl3_layer_route_record,
- * struct exl3_moe_record; the fourth launch is ordered_publish_reduce_flags of kernel_ordered_b200.cu). No counterpart file in the reference, whose step is a router launch, five expert launches,
- * a row sum and an exchange of one CTA; the arithmetic of every value is its retained chain's (exl3_passes.cuh), the
- * router's conventions its router_select_entry's (router_device.cuh), the reduction's order its owner sums'.
+ * kernel_exl3_layer.cu: one decode step of a rank's expert layer in three launches (struct exl3_layer_route_record,
+ * struct exl3_layer_products_record; the third launch is ordered_publish_reduce_flags of kernel_ordered_b200.cu). No
+ * counterpart file in the reference, whose step is a router launch, five expert launches, a row sum and an exchange of
+ * one CTA; the arithmetic of every value is its retained chain's (exl3_passes.cuh), the router's conventions its
+ * router_select_entry's (router_device.cuh), the reduction's order its owner sums'.
  *
- * The two product launches are the fused products of the fixed cut (exl3_fused.cuh) with a cut the preparer chooses
- * for the step's size and the rank's share of the columns (the grid tells it): a CTA streams one run of K of 128
- * outputs of one job; the runs leave FP32 partial sums in the arena and the CTA that completes a (job, 128 outputs),
- * found with a counter, adds them in ascending K order from +0. The cut depends on the prepared shapes alone.
+ * The products are one launch. The step's work is a list of items of the fused products of the fixed cut
+ * (exl3_fused.cuh): one run of K of 128 outputs of one matrix of one job; the runs leave FP32 partial sums in the
+ * arena and the CTA that completes a (job, 128 outputs), found with a counter, adds them in ascending K order from +0.
+ * Gate and up items come first, in job order, then the down items, which wait for their job's activation; a CTA takes
+ * the next item of the list when it begins. The cut depends on the prepared shapes alone, and so does every sum: which
+ * CTA computes an item, and when, does not matter to its bits.
  */
 #include "exl3_fused.cuh"
 #include "router_device.cuh"
-
-#define EXL3_LAYER_READY_POLLS 2048u /* of about 200 ns each, before a down CTA waits for the whole launch before it */
 
 __device__ __forceinline__ uint32_t *layer_words(const struct exl3_moe_record &moe, unsigned char *arena)
 {
@@ -88,56 +89,78 @@ extern "C" __global__ void __launch_bounds__(EXL3_LAYER_ROUTE_THREADS)
 	}
 }
 
-/* ------------------------------------------------------------------ gate/up products */
+/* ------------------------------------------------------------------ the products */
 
-/* grid (inner_size / 128 * runs, jobs, 2) x 128: exl3_moe_gate_up's CTAs with the cut of K the preparer chose
- * (gridDim.x tells it) */
-extern "C" __global__ void __launch_bounds__(EXL3_PRODUCT_THREADS)
-	exl3_layer_gate_up(struct exl3_moe_record record, unsigned char *arena)
+/* one thread: true once *word == wanted, false after EXL3_WAIT_CYCLES (the expiry is recorded) */
+__device__ __forceinline__ bool layer_word_wait(const uint32_t *word, uint32_t wanted)
 {
-	extern __shared__ __align__(128) unsigned char dynamic_shared[];
-	__shared__ exl3_product_shared shared;
-	__shared__ uint32_t flag;
-	/* This launch may have begun while the router's still runs: everything it reads is that launch's, so it waits for
-	 * the whole of it. Only then may the down launch be given the card's free room (once every CTA of this grid has
-	 * said so or ended, which is when the last of them has begun): its CTAs read the job table, which must be this
-	 * step's, and wait for their job's operands themselves. */
-	asm volatile("griddepcontrol.wait;" ::: "memory");
-	asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-	exl3_moe_gate_up_block(record, arena, gridDim.x / (record.base.inner_size / EXL3_TRANSFORM), dynamic_shared, &shared,
-			       &flag, layer_words(record, arena) + EXL3_LAYER_COUNTER_WORDS);
+	long long begun = 0;
+	for (uint32_t poll = 1;; poll++) {
+		uint32_t seen;
+		asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(word) : "memory");
+		if (seen == wanted)
+			return true;
+		if ((poll & 63u) == 0u) {
+			const long long now = clock64();
+			if (begun == 0)
+				begun = now;
+			else if (now - begun > EXL3_WAIT_CYCLES)
+				break;
+		}
+		__nanosleep(100);
+	}
+	atomicExch(&exl3_wait_expired, 1u);
+	return false;
 }
 
-/* ------------------------------------------------------------------ down products */
-
-/* grid (input_size / 128 * runs, jobs) x 128: exl3_moe_down's CTAs with the cut the preparer chose */
+/* grid (job_count * items a job) x 128: a CTA an item. A CTA takes a ticket as its first act and works on the item of
+ * that number: the gate and up items of every live job in job order, then the down items (tickets beyond the step's
+ * items end at once). Tickets are handed out in the order the CTAs begin, so every gate/up item has begun before any
+ * down item begins; a down item's CTA waits for its job's word to reach the number of groups of inner channels, which
+ * the gate/up items count up without waiting for anything, so the wait ends. It is bounded all the same: an item whose
+ * wait ran out is skipped and the host finds exl3_wait_expired set. The card hands a freed place to the next CTA, so
+ * its room is filled to the last item whatever the step's size. (A grid that walks the items in a loop keeps the
+ * loop's words alive through the products and spills: a CTA an item does not.) */
 extern "C" __global__ void __launch_bounds__(EXL3_PRODUCT_THREADS)
-	exl3_layer_down(struct exl3_moe_record record, unsigned char *arena)
+	exl3_layer_products(struct exl3_layer_products_record record, unsigned char *arena)
 {
 	extern __shared__ __align__(128) unsigned char dynamic_shared[];
 	__shared__ exl3_product_shared shared;
-	__shared__ uint32_t flag;
-	/* This launch may have begun while the gate/up launch still runs. The job table is older than both; the job's
-	 * down operands are in place once every group of its inner channels has been counted. A CTA looks for that a
-	 * bounded number of times, then waits for the whole gate/up launch (which is all a launch that began behind it
-	 * does anyway): it cannot wait in vain. */
-	asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); /* the reduction's launch waits for all of this one */
-	if (exl3_job(record.base, arena, blockIdx.y)->row_count == 0)
-		return;
+	__shared__ uint32_t flag, ticket, ready_seen;
+	/* This launch may have been given its place while the router's still runs: everything it reads is that launch's,
+	 * so it waits for the whole of it; the reduction's launch may then take its place behind this one. */
+	asm volatile("griddepcontrol.wait;" ::: "memory");
+	asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+	const struct exl3_moe_record &moe = record.moe;
+	uint32_t *const words = layer_words(moe, arena);
+	uint32_t *const ready = words + EXL3_LAYER_COUNTER_WORDS;
 	if (threadIdx.x == 0) {
-		const uint32_t *const ready = layer_words(record, arena) + EXL3_LAYER_COUNTER_WORDS + blockIdx.y;
-		const uint32_t wanted = record.base.inner_size / EXL3_TRANSFORM;
-		uint32_t seen = 0;
-		for (uint32_t poll = 0; poll < EXL3_LAYER_READY_POLLS; poll++) {
-			asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(ready) : "memory");
-			if (seen == wanted)
-				break;
-			__nanosleep(200);
-		}
-		if (seen != wanted)
-			asm volatile("griddepcontrol.wait;" ::: "memory");
+		ticket = atomicAdd(&words[EXL3_LAYER_WORD_TICKET], 1u);
+		if (ticket == gridDim.x - 1u)
+			words[EXL3_LAYER_WORD_TICKET] = 0u; /* the last one: the word is zero again for the next step */
 	}
 	__syncthreads();
-	exl3_moe_down_block(record, arena, gridDim.x / (record.base.input_size / EXL3_TRANSFORM), dynamic_shared, &shared,
-			    &flag);
+	const uint32_t index = ticket;
+	const uint32_t jobs = min(words[EXL3_LAYER_WORD_LIVE_JOBS], moe.base.job_count);
+	const uint32_t inner_groups = moe.base.inner_size / EXL3_TRANSFORM, outer_groups = moe.base.input_size / EXL3_TRANSFORM;
+	const uint32_t gate_up_a_matrix = inner_groups * record.gate_up_runs;
+	const uint32_t gate_up_a_job = EXL3_PROJECTIONS * gate_up_a_matrix, down_a_job = outer_groups * record.down_runs;
+	const uint32_t gate_up_items = jobs * gate_up_a_job, items = gate_up_items + jobs * down_a_job;
+	if (index >= items)
+		return;
+	if (index < gate_up_items) {
+		const uint32_t within = index % gate_up_a_job, of_matrix = within % gate_up_a_matrix;
+		const struct moe_item item = { index / gate_up_a_job, of_matrix / record.gate_up_runs,
+					       of_matrix % record.gate_up_runs, within / gate_up_a_matrix };
+		exl3_moe_gate_up_item(moe, arena, item, record.gate_up_runs, dynamic_shared, &shared, &flag, ready);
+		return;
+	}
+	const uint32_t behind = index - gate_up_items, within = behind % down_a_job;
+	const struct moe_item item = { behind / down_a_job, within / record.down_runs, within % record.down_runs, 0u };
+	if (threadIdx.x == 0)
+		ready_seen = layer_word_wait(ready + item.job, inner_groups) ? 1u : 0u;
+	__syncthreads();
+	if (ready_seen != 0u)
+		exl3_moe_down_item(moe, arena, item, record.down_runs, dynamic_shared, &shared, &flag,
+				   record.down_products_offset);
 }

@@ -132,8 +132,9 @@ class MoeLayer:
     def __init__(self, card, config, widths, matrices, rank=0, rank_count=1, pool_entries=0, reduce_form="fused",
                  bias=None, cut=(0, 0)):
         """matrices: iterable over experts (routed, then shared) of this rank's (gate, up, down) stored bytes.
-        reduce_form: "fused" (the step in four launches: the router with the input transform, products cut evenly
-        over the card, row sums and READY behind the down products, flags that arrive in the reader's memory),
+        reduce_form: "fused" (the step in three launches: the router with the input transform; the products as one
+        resident grid that walks the step's items; row sums, READY and the reduction, with flags that arrive in the
+        reader's memory),
         "pull" (router, four expert launches, two reduction launches: the ranks read each other's rows) or "push"
         (one reduction launch: the ranks store their rows into each other's inboxes); the same sums of the ranks'
         rows and the same bits given those rows. bias: FP32 [experts] for a config with bias=True. cut: (gate/up
@@ -201,7 +202,7 @@ class MoeLayer:
                                                  c.row_capacity, 0)
         description.result_offset, description.arena_byte_count = L.result, card.arena_bytes
         description.gate_up_runs, description.down_runs = self.cut
-        launches = (R.KernelLaunch * 4)()
+        launches = (R.KernelLaunch * R.EXL3_LAYER_LAUNCHES)()
         api.check(lib.exl3_layer_prepare(C.byref(description), card.ops_pointer, card.handle, launches),
                   "exl3_layer_prepare")
         return list(launches)
@@ -210,7 +211,9 @@ class MoeLayer:
         c, L, card, lib = self.config, self.layout, self.card, api.library()
         # which launches stand before the gate/up products, and which launch they are (for callers that time them)
         self.gate_up_index = 1 if L.reduce_form == "fused" else 2
-        self.gate_up_kernel = "exl3_layer_gate_up" if L.reduce_form == "fused" else "exl3_moe_gate_up"
+        self.gate_up_kernel = "exl3_layer_products" if L.reduce_form == "fused" else "exl3_moe_gate_up"
+        # the launch at gate_up_index holds the down products too (callers that count a launch's bytes ask)
+        self.products_in_one_launch = L.reduce_form == "fused"
         if L.reduce_form == "fused":
             self.launches = self._prepare_fused()
             self._capture()

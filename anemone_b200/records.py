@@ -70,6 +70,7 @@ class Exl3LayerDescription(C.Structure):
 
 
 EXL3_LAYER_SIGNAL_BYTES = 33 * 128
+EXL3_LAYER_LAUNCHES = 3
 EXL3_LAYER_READY_LINE, EXL3_LAYER_DONE_LINE, EXL3_LAYER_LOCAL_LINE = 0, 16, 32
 
 
@@ -157,6 +158,11 @@ class OrderedPublishReduce(C.Structure):
 class OrderedRowSumPublish(C.Structure):
     _fields_ = [("collective", OrderedCollective), ("pair_output_offset", C.c_uint64), ("width", C.c_uint32),
                 ("pairs_per_row", C.c_uint32), ("status_offset", C.c_uint64)]
+
+
+class Exl3LayerProducts(C.Structure):
+    _fields_ = [("moe", Exl3Moe), ("down_products_offset", C.c_uint64), ("gate_up_runs", C.c_uint32),
+                ("down_runs", C.c_uint32)]
 
 
 class ExactRing(C.Structure):

@@ -16,7 +16,8 @@ One JSON line on rank 0:
             the ranks meet on the device, so that the events hold the K steps and no rank's wait for a late one;
   e2e       the same through the public call with host buffers: per step the host -> device copy of the step's inputs
             from pinned memory, the layer's graph, the device -> host copy of the bfloat16 result, and the wait for it;
-  roofline  the dominant kernel (exl3_layer_gate_up) timed alone, launch by launch, with CUDA events, against the
+  roofline  the dominant kernel (exl3_layer_products: every product of the step) timed alone, launch by launch, with
+            CUDA events, against the
             measured HBM copy bandwidth of MEASURED_PEAKS.json;
   cpu_baseline  the CPU oracle (OpenMP, all host cores) on a bounded sample of the same step, scaled to the step.
 Further objects of the same line, each with its own value, e2e and roofline where they apply:
@@ -913,8 +914,12 @@ def main():
             picks = card.download(layout.picks, args.rows * config.picks * 4, np.uint32)
             active = sorted(set(picks.tolist())) + list(range(config.experts, config.total_experts))
             pairs = args.rows * config.pairs_per_row
-            byte_total += sum(2 * synthetic.matrix_bytes(config.hidden, inner_local, int(widths[e])) for e in active)
+            matrices = 3 if getattr(layer, "products_in_one_launch", False) else 2  # gate, up (and down) in the launch
+            byte_total += sum(matrices * synthetic.matrix_bytes(config.hidden, inner_local, int(widths[e]))
+                              for e in active)
             byte_total += 2 * pairs * config.hidden * 2 + pairs * inner_local * 4  # operands in, hidden + operands out
+            if matrices == 3:
+                byte_total += pairs * inner_local * 2 + pairs * config.hidden * 4  # down operands in, pair outputs out
         achieved = byte_total / elapsed_us / 1000.0  # GB/s
         roofline = {"kernel": layer.gate_up_kernel, "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                     "frac": achieved / peak, "peak_source": peak_source,

@@ -84,14 +84,17 @@ MUST_CHECK result_status exl3_prefill_prepare(const struct exl3_prefill_record *
 					      struct kernel_launch *launches_out);
 
 /* B200 extension (no reference counterpart: its step is a router launch, five expert launches, a row sum and a
- * one-CTA exchange): ONE decode step of a rank's whole expert layer in the four launches of struct
- * exl3_layer_route_record (router with input transform; gate/up; down; row sums, READY and the reduction).
+ * one-CTA exchange): ONE decode step of a rank's whole expert layer in the EXL3_LAYER_LAUNCHES launches of struct
+ * exl3_layer_route_record (router with input transform; the products, one resident grid that walks the step's
+ * items; row sums, READY and the reduction). Each launch is given its place on the card while the one before it still
+ * runs (LAUNCH_OVERLAPS_PREVIOUS) and waits for that launch itself.
  * route.moe is read as exl3_moe_prepare reads it, with the scratch sizes of exl3_layer_sizes; publish names the
  * reduction's region (two parity slots of parity_stride bytes, the FP32 rows at input_offset inside a slot, behind
  * EXL3_LAYER_SIGNAL_BYTES of signal lines), the peer table (struct ordered_collective_peer [rank_count]), the status
  * block and the step block; result_offset: bfloat16 [row_capacity][input_size]. gate_up_runs, down_runs (powers of two
- * up to EXL3_LAYER_MAXIMUM_RUNS that divide the products' 128-input blocks): the cut of K of the two product
- * launches, 0 for this library's choice from the shapes. The region must be zero at load. */
+ * up to EXL3_LAYER_MAXIMUM_RUNS that divide the products' 128-input blocks): the cut of K of gate and up and of
+ * down, 0 for this library's choice from the shapes. The region and the counters must be zero at load; after a
+ * bounded wait has run out (backend_b200_waits_expired) the counters must be zeroed again before the next step. */
 struct exl3_layer_description {
 	struct exl3_layer_route_record route;
 	struct exl3_layer_publish_arguments publish;

@@ -224,12 +224,15 @@ struct step_block {
  *                            (router_select_b200's bytes) and the live job count; the others transform the rows into
  *                            the FP16 operands of every (pair, gate or up): no launch and no trip through memory
  *                            stands between the router and the transform.
- *   exl3_layer_gate_up       grid (inner_size / 128 * runs, jobs, 2) x 128: exl3_moe_gate_up's CTAs with the cut of K
- *                            the preparer was given or chose (the grid tells it); the CTA that completes a (job, 128
- *                            outputs) adds the runs' FP32 partial sums in ascending K order from +0 and applies the
- *                            transform, SwiGLU and the down-side transform.
- *   exl3_layer_down          grid (input_size / 128 * runs, jobs) x 128: the same for down; the CTA that completes a
- *                            (job, 128 outputs) writes the pair outputs (transform, scale, route weight).
+ *   exl3_layer_products      grid (job_count * items a job) x 128, a CTA an item of the step's list: first every
+ *                            (job, gate or up, 128 outputs, run of the cut of K) in job order, then every (job, 128
+ *                            outputs of down, run); a CTA takes the next item as it begins (a ticket), so the card
+ *                            hands every freed place to the next item and its room is filled to the last one. The
+ *                            CTA that completes a (job, 128 outputs) adds the runs' FP32 partial sums in ascending K
+ *                            order from +0 and applies the epilogue (transform, SwiGLU and the down-side transform;
+ *                            transform, scale and route weight). A down item waits (bounded) until the job's down
+ *                            operands are all in place: a word a job counts the groups of inner channels done.
+ *                            Every gate/up item has begun before any down item begins, so no wait is in vain.
  *   ordered_publish_reduce_flags  (kernel file "kernel_ordered_b200") adds each row's pairs in ascending slot order
  *                            from +0 straight into this rank's rows of the reduction slot, stores this rank's READY
  *                            word into EVERY rank's slot (plain peer stores), waits for the ranks' READY words in
@@ -240,15 +243,16 @@ struct step_block {
  * (line s: a 64-bit sequence written only by rank s), 16 DONE lines likewise, one local line (a block counter at
  * byte 64, the sequence of the slot's previous use at byte 72), then the FP32 rows at input_offset.
  * The cut of a product depends on the prepared shapes alone: the same inputs give the same bits on every run.
- * partial sums: FP32 [2][runs][pair_count][inner_size] for gate/up, reused as [runs][pair_count][input_size] for down
- * (run 0 is also where the pair outputs go), sized for EXL3_LAYER_MAXIMUM_RUNS runs; counters:
- * what struct exl3_moe_record asks for, then EXL3_LAYER_COUNTER_WORDS more uint32, zero at load.
+ * partial sums: FP32 [2][runs][pair_count][inner_size] for gate/up, then, in a range of their own, [runs][pair_count]
+ * [input_size] for down (run 0 is also where the pair outputs go), both sized for EXL3_LAYER_MAXIMUM_RUNS runs; counters:
+ * what struct exl3_moe_record asks for, then EXL3_LAYER_COUNTER_WORDS more uint32 (the live job count first), then a
+ * word a job; zero at load.
  * ---------------------------------------------------------------------------------------------------------- */
 #define EXL3_LAYER_KERNEL_FILE "kernel_exl3_layer"
-#define EXL3_LAYER_LAUNCHES 4u
-#define EXL3_LAYER_MAXIMUM_RUNS 8u /* runs of K of one product at most */
+#define EXL3_LAYER_LAUNCHES 3u
+#define EXL3_LAYER_MAXIMUM_RUNS 16u /* runs of K of one product at most */
 #define EXL3_LAYER_ROUTE_THREADS 1024u
-#define EXL3_LAYER_COUNTER_WORDS 4u /* the live job count and three reserved words */
+#define EXL3_LAYER_COUNTER_WORDS 4u /* the live job count, the products' ticket and two reserved words */
 #define EXL3_LAYER_READY_LINE 0u
 #define EXL3_LAYER_DONE_LINE 16u
 #define EXL3_LAYER_LOCAL_LINE 32u
@@ -267,6 +271,14 @@ struct exl3_layer_route_record {
 	uint32_t row_capacity;
 	uint32_t scoring;
 	float route_scale;
+};
+
+/* the record of exl3_layer_products */
+struct exl3_layer_products_record {
+	struct exl3_moe_record moe;
+	uint64_t down_products_offset; /* down's partial sums; run 0 of them the pair outputs */
+	uint32_t gate_up_runs; /* the cut of K = input_size of gate and up */
+	uint32_t down_runs; /* the cut of K = inner_size of down */
 };
 
 /* what exl3_layer_prepare is told about the reduction */
@@ -908,6 +920,7 @@ AB_RECORD_HAS(router_select_b200_arguments, 88);
 AB_RECORD_HAS(step_input_select_arguments, 40);
 AB_RECORD_HAS(exact_ring_arguments, 80);
 AB_RECORD_HAS(exl3_layer_route_record, 184);
+AB_RECORD_HAS(exl3_layer_products_record, 128);
 AB_RECORD_HAS(exl3_layer_publish_arguments, 72);
 AB_RECORD_HAS(exl3_prefill_tile, 16);
 AB_RECORD_HAS(exl3_prefill_entry, 8);
