@@ -126,41 +126,59 @@ extern "C" __global__ void __launch_bounds__(EXL3_PRODUCT_THREADS)
 {
 	extern __shared__ __align__(128) unsigned char dynamic_shared[];
 	__shared__ exl3_product_shared shared;
-	__shared__ uint32_t flag, ticket, ready_seen;
+	__shared__ uint32_t flag;
+	__shared__ struct moe_item taken; /* the CTA's item; job UINT32_MAX: none */
+	__shared__ uint32_t kind; /* 0: gate or up, 1: down, 2: a down item whose wait ran out */
 	/* This launch may have been given its place while the router's still runs: everything it reads is that launch's,
 	 * so it waits for the whole of it; the reduction's launch may then take its place behind this one. */
 	asm volatile("griddepcontrol.wait;" ::: "memory");
 	asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 	const struct exl3_moe_record &moe = record.moe;
-	uint32_t *const words = layer_words(moe, arena);
-	uint32_t *const ready = words + EXL3_LAYER_COUNTER_WORDS;
 	if (threadIdx.x == 0) {
-		ticket = atomicAdd(&words[EXL3_LAYER_WORD_TICKET], 1u);
-		if (ticket == gridDim.x - 1u)
+		/* one thread takes the ticket and finds its item (the divisions are its alone), and waits where the item must */
+		uint32_t *const words = layer_words(moe, arena);
+		const uint32_t index = atomicAdd(&words[EXL3_LAYER_WORD_TICKET], 1u);
+		if (index == gridDim.x - 1u)
 			words[EXL3_LAYER_WORD_TICKET] = 0u; /* the last one: the word is zero again for the next step */
+		const uint32_t jobs = min(words[EXL3_LAYER_WORD_LIVE_JOBS], moe.base.job_count);
+		const uint32_t inner_groups = moe.base.inner_size / EXL3_TRANSFORM;
+		const uint32_t gate_up_a_matrix = inner_groups * record.gate_up_runs;
+		const uint32_t gate_up_a_job = EXL3_PROJECTIONS * gate_up_a_matrix;
+		const uint32_t down_a_job = moe.base.input_size / EXL3_TRANSFORM * record.down_runs;
+		const uint32_t gate_up_items = jobs * gate_up_a_job, items = gate_up_items + jobs * down_a_job;
+		struct moe_item item = { UINT32_MAX, 0u, 0u, 0u };
+		uint32_t what = 0;
+		if (index < gate_up_items) {
+			const uint32_t within = index % gate_up_a_job, of_matrix = within % gate_up_a_matrix;
+			item.job = index / gate_up_a_job;
+			item.group = of_matrix / record.gate_up_runs;
+			item.run = of_matrix % record.gate_up_runs;
+			item.projection = within / gate_up_a_matrix;
+		} else if (index < items) {
+			const uint32_t behind = index - gate_up_items, within = behind % down_a_job;
+			item.job = behind / down_a_job;
+			item.group = within / record.down_runs;
+			item.run = within % record.down_runs;
+			what = layer_word_wait(words + EXL3_LAYER_COUNTER_WORDS + item.job, inner_groups) ? 1u : 2u;
+		}
+		taken = item;
+		kind = what;
 	}
 	__syncthreads();
-	const uint32_t index = ticket;
-	const uint32_t jobs = min(words[EXL3_LAYER_WORD_LIVE_JOBS], moe.base.job_count);
-	const uint32_t inner_groups = moe.base.inner_size / EXL3_TRANSFORM, outer_groups = moe.base.input_size / EXL3_TRANSFORM;
-	const uint32_t gate_up_a_matrix = inner_groups * record.gate_up_runs;
-	const uint32_t gate_up_a_job = EXL3_PROJECTIONS * gate_up_a_matrix, down_a_job = outer_groups * record.down_runs;
-	const uint32_t gate_up_items = jobs * gate_up_a_job, items = gate_up_items + jobs * down_a_job;
-	if (index >= items)
+	/* through a lane's register, so that the compiler knows every lane of a warp holds the same item (what depends on
+	 * it then lives in the warp's uniform registers, not in every lane's) */
+	const struct moe_item item = { (uint32_t)__shfl_sync(0xFFFFFFFFu, taken.job, 0),
+				       (uint32_t)__shfl_sync(0xFFFFFFFFu, taken.group, 0),
+				       (uint32_t)__shfl_sync(0xFFFFFFFFu, taken.run, 0),
+				       (uint32_t)__shfl_sync(0xFFFFFFFFu, taken.projection, 0) };
+	const uint32_t what = (uint32_t)__shfl_sync(0xFFFFFFFFu, kind, 0);
+	if (item.job == UINT32_MAX || what == 2u)
 		return;
-	if (index < gate_up_items) {
-		const uint32_t within = index % gate_up_a_job, of_matrix = within % gate_up_a_matrix;
-		const struct moe_item item = { index / gate_up_a_job, of_matrix / record.gate_up_runs,
-					       of_matrix % record.gate_up_runs, within / gate_up_a_matrix };
-		exl3_moe_gate_up_item(moe, arena, item, record.gate_up_runs, dynamic_shared, &shared, &flag, ready);
+	if (what == 0u) {
+		exl3_moe_gate_up_item(moe, arena, item, record.gate_up_runs, dynamic_shared, &shared, &flag,
+				      layer_words(moe, arena) + EXL3_LAYER_COUNTER_WORDS);
 		return;
 	}
-	const uint32_t behind = index - gate_up_items, within = behind % down_a_job;
-	const struct moe_item item = { behind / down_a_job, within / record.down_runs, within % record.down_runs, 0u };
-	if (threadIdx.x == 0)
-		ready_seen = layer_word_wait(ready + item.job, inner_groups) ? 1u : 0u;
-	__syncthreads();
-	if (ready_seen != 0u)
-		exl3_moe_down_item(moe, arena, item, record.down_runs, dynamic_shared, &shared, &flag,
+	exl3_moe_down_item(moe, arena, item, record.down_runs, dynamic_shared, &shared, &flag,
 				   record.down_products_offset);
 }

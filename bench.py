@@ -64,6 +64,8 @@ def parse():
     parser.add_argument("--inner", type=int, default=2048)
     parser.add_argument("--prefill-rows", type=int, default=4096, help="0 skips the prefill part")
     parser.add_argument("--prefill-steps", type=int, default=5)
+    parser.add_argument("--cut", default="0,0",
+                        help="runs of K of the decode products (gate/up,down); 0: the library's measured default")
     parser.add_argument("--no-original-weights", action="store_true", help="skip the MXFP4 part")
     parser.add_argument("--no-reduction", action="store_true",
                         help="skip the reduction-alone measurement of runs on two or more GPUs")
@@ -835,7 +837,8 @@ def main():
     card = api.Card(local_rank, layout.arena_bytes)
     matrices = (local_matrices(*draw(expert), config, int(widths[expert]), world, rank)
                 for expert in range(config.total_experts))
-    layer = MoeLayer(card, config, widths, matrices, rank=rank, rank_count=world, pool_entries=total_steps)
+    layer = MoeLayer(card, config, widths, matrices, rank=rank, rank_count=world, pool_entries=total_steps,
+                     cut=tuple(int(part) for part in args.cut.split(",")))
     if dist is None:
         layer.connect_local([layer])
     else:
