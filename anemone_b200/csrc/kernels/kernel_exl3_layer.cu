@@ -30,6 +30,8 @@ extern "C" __global__ void __launch_bounds__(EXL3_LAYER_ROUTE_THREADS)
 	__shared__ float weight[ROUTER_B200_MAXIMUM_ROWS][ROUTER_B200_MAXIMUM_PICKS];
 	__shared__ unsigned long long row_mask[ROUTER_B200_MAXIMUM_EXPERTS];
 	__shared__ uint32_t first_job[ROUTER_B200_MAXIMUM_EXPERTS];
+	__shared__ uint64_t candidates[EXL3_LAYER_ROUTE_THREADS / WARP / ROUTER_TEAM_WARPS]
+				      [ROUTER_TEAM_WARPS * ROUTER_B200_MAXIMUM_PICKS];
 	const struct exl3_expert_record &base = record.moe.base;
 	/* the gate/up launch may take its place on the card now: it waits for the whole of this launch before it reads */
 	asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -41,12 +43,19 @@ extern "C" __global__ void __launch_bounds__(EXL3_LAYER_ROUTE_THREADS)
 	const float *const scores = reinterpret_cast<const float *>(arena + record.scores_offset);
 	const float *const bias =
 		record.bias_offset != 0 ? reinterpret_cast<const float *>(arena + record.bias_offset) : nullptr;
-	/* every CTA chooses every live row's experts itself: the same arithmetic, the same picks */
-	for (uint32_t row = warp; row < live; row += warps)
-		router_row(scores + (uint64_t)row * routed, bias, routed, picks, record.scoring, record.route_scale, lane,
-			   chosen[row], weight[row],
-			   writer ? reinterpret_cast<uint32_t *>(arena + record.picks_offset) + (uint64_t)row * picks : nullptr,
-			   writer ? reinterpret_cast<float *>(arena + record.weights_offset) + (uint64_t)row * picks : nullptr);
+	/* every CTA chooses every live row's experts itself (the same arithmetic, the same picks), a team of four warps
+	 * a row: the launch lasts as long as one row's chain of dependent instructions */
+	const uint32_t team = warp / ROUTER_TEAM_WARPS, teams = warps / ROUTER_TEAM_WARPS;
+	for (uint32_t first = 0; first < live; first += teams) { /* a whole team leaves the loop together */
+		const uint32_t row = first + team;
+		if (row < live)
+			router_row_team(scores + (uint64_t)row * routed, bias, routed, picks, record.scoring, record.route_scale,
+					lane, warp % ROUTER_TEAM_WARPS, 1u + team, candidates[team], chosen[row], weight[row],
+					writer ? reinterpret_cast<uint32_t *>(arena + record.picks_offset) + (uint64_t)row * picks :
+						 nullptr,
+					writer ? reinterpret_cast<float *>(arena + record.weights_offset) + (uint64_t)row * picks :
+						 nullptr);
+	}
 	__syncthreads();
 	const uint64_t *const table = reinterpret_cast<const uint64_t *>(arena + record.expert_table_offset);
 	if (writer) {

@@ -148,6 +148,94 @@ __device__ __forceinline__ void router_row(const float *scores, const float *bia
 	__syncwarp();
 }
 
+/* the largest of the warp's keys (0: none), by two 32-bit reductions: the ordered score, then the expert among those
+ * that hold it */
+__device__ __forceinline__ uint64_t router_warp_largest(uint64_t key)
+{
+	const uint32_t high = __reduce_max_sync(0xFFFFFFFFu, (uint32_t)(key >> 32));
+	const uint32_t low = __reduce_max_sync(0xFFFFFFFFu, (uint32_t)(key >> 32) == high ? (uint32_t)key : 0u);
+	return (uint64_t)high << 32 | low;
+}
+
+/* One row by a TEAM of ROUTER_TEAM_WARPS warps (member: 0 ..), for a launch whose time is this chain of dependent
+ * instructions: every member takes a quarter of the experts (interleaved by runs of 32), finds its `picks` largest
+ * keys and leaves them in `candidates` (shared memory, ROUTER_TEAM_WARPS x ROUTER_B200_MAXIMUM_PICKS keys of this row's
+ * team); behind the team's barrier (a named barrier `barrier` of the team's threads alone) member 0 picks the
+ * largest `picks` of the candidates. The picks are router_row's: the largest keys are the largest keys however they
+ * are found; slots, weights and their sum are formed as there. All lanes of all members call. */
+#define ROUTER_TEAM_WARPS 4u
+#define ROUTER_TEAM_SLOTS (ROUTER_B200_MAXIMUM_EXPERTS / (ROUTER_TEAM_WARPS * WARP))
+__device__ __forceinline__ void router_row_team(const float *scores, const float *bias, uint32_t experts, uint32_t picks,
+						uint32_t scoring, float route_scale, uint32_t lane, uint32_t member,
+						uint32_t barrier, uint64_t *candidates, uint32_t *chosen, float *weight,
+						uint32_t *picks_out, float *weights_out)
+{
+	uint64_t keys[ROUTER_TEAM_SLOTS];
+#pragma unroll
+	for (uint32_t place = 0; place < ROUTER_TEAM_SLOTS; place++) {
+		const uint32_t expert = (place * ROUTER_TEAM_WARPS + member) * WARP + lane;
+		if (expert < experts) {
+			const float affinity = router_affinity(scores[expert], scoring);
+			keys[place] = router_key(bias != nullptr ? __fadd_rn(affinity, bias[expert]) : affinity, expert);
+		} else {
+			keys[place] = 0ull;
+		}
+	}
+	for (uint32_t pick = 0; pick < picks; pick++) {
+		uint64_t best = 0;
+#pragma unroll
+		for (uint32_t place = 0; place < ROUTER_TEAM_SLOTS; place++)
+			best = keys[place] > best ? keys[place] : best;
+		best = router_warp_largest(best);
+#pragma unroll
+		for (uint32_t place = 0; place < ROUTER_TEAM_SLOTS; place++)
+			keys[place] = keys[place] == best ? 0ull : keys[place];
+		if (lane == pick)
+			candidates[member * ROUTER_B200_MAXIMUM_PICKS + pick] = best;
+	}
+	asm volatile("bar.sync %0, %1;" ::"r"(barrier), "n"(ROUTER_TEAM_WARPS * WARP) : "memory");
+	if (member != 0)
+		return;
+	/* the team's candidates: two a lane */
+	uint64_t held[2];
+#pragma unroll
+	for (uint32_t place = 0; place < 2; place++) {
+		const uint32_t index = place * WARP + lane;
+		held[place] = index % ROUTER_B200_MAXIMUM_PICKS < picks ? candidates[index] : 0ull;
+	}
+	uint32_t mine = 0; /* lane p keeps pick p */
+	for (uint32_t pick = 0; pick < picks; pick++) {
+		const uint64_t best = router_warp_largest(held[0] > held[1] ? held[0] : held[1]);
+		held[0] = held[0] == best ? 0ull : held[0];
+		held[1] = held[1] == best ? 0ull : held[1];
+		if (lane == pick)
+			mine = ~(uint32_t)best;
+	}
+	uint32_t slot = 0; /* the number of picked experts below mine */
+	for (uint32_t pick = 0; pick < picks; pick++) {
+		const uint32_t other = __shfl_sync(0xFFFFFFFFu, mine, pick);
+		slot += lane < picks && other < mine ? 1u : 0u;
+	}
+	if (lane < picks) {
+		chosen[slot] = mine;
+		weight[slot] = router_affinity(scores[mine], scoring);
+	}
+	__syncwarp();
+	float sum = 0.0f;
+	for (uint32_t place = 0; place < picks; place++)
+		sum = __fadd_rn(sum, weight[place]);
+	__syncwarp();
+	if (lane < picks) {
+		const float value = __fmul_rn(__fdiv_rn(weight[lane], __fadd_rn(sum, 1e-20f)), route_scale);
+		weight[lane] = value;
+		if (picks_out != nullptr) {
+			picks_out[lane] = chosen[lane];
+			weights_out[lane] = value;
+		}
+	}
+	__syncwarp();
+}
+
 /* The job table of `live` rows' choices, by one block of any whole number of warps (every thread calls; the block's
  * barriers are passed by all). chosen and weight: [row][ROUTER_B200_MAXIMUM_PICKS] by slot; row_mask and first_job:
  * ROUTER_B200_MAXIMUM_EXPERTS entries of shared memory each. Jobs in ascending expert order, an expert's rows
