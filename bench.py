@@ -50,6 +50,11 @@ SEED = 20261125
 # one ncu capture of a 64-expert, 8-row launch over that launch's algorithmic bytes (the capture is too large for the
 # full workload; traffic grows in proportion to the experts streamed)
 GATE_UP_TRAFFIC_RATIO = 1.03
+# the same for the prefill's gate/up products (one capture at 32 experts and 1024 rows: 401.3 MB read and 45.0 MB
+# written against 444 MB of codes, scales, operand blocks read and down operand blocks written) and for the
+# original-weights gate/up products (one capture at 64 experts: 360.1 MB against 356.8 MB)
+PREFILL_TRAFFIC_RATIO = 1.00
+MX_GATE_UP_TRAFFIC_RATIO = 1.01
 
 
 def parse():
@@ -170,6 +175,7 @@ def run_prefill(args, api, base, widths, draw, rank, world, local_rank, dist, ba
     """cfg4: the same layer for M = 4096 rows, experts sharded over the ranks (a run of routed experts each, the
     always-on expert by columns), Zipf(1.1) routing, tensor-core products, ordered reduction to bfloat16."""
     from anemone_b200 import records as R
+    from anemone_b200 import synthetic
     from anemone_b200.moe import MoeConfig
     from anemone_b200.prefill import PrefillLayer, PrefillLayout, Share
     rows, steps, warmup = args.prefill_rows, args.prefill_steps, 3
@@ -260,8 +266,17 @@ def run_prefill(args, api, base, widths, draw, rank, world, local_rank, dist, ba
                     for local, expert in enumerate(held))
         peak, source = measured_tensor_peak()
         achieved = flops / us / 1e6  # TFLOP/s
+        # bytes of the launch: gate and up of every expert that has a row; a row tile's operand blocks of both in, its
+        # down operand blocks out (whole tiles of 128 rows move, filled or not)
+        tiles_of = [(int(counts[local]) + 127) // 128 for local in range(len(held))]
+        byte_total = sum((2 * synthetic.matrix_bytes(config.hidden, share.inner if expert < config.experts else
+                                                     share.shared_inner, int(widths[expert])) if tiles else 0) +
+                         tiles * 128 * (2 * config.hidden * 2 +
+                                        (share.inner if expert < config.experts else share.shared_inner) * 2)
+                         for (local, expert), tiles in zip(enumerate(held), tiles_of))
         roofline = {"kernel": "exl3_prefill_gate_up", "bound": "tensor", "achieved": achieved, "peak": peak,
-                    "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": source, "traffic": None,
+                    "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": source,
+                    "traffic": PREFILL_TRAFFIC_RATIO * byte_total, "algorithmic_bytes_per_launch": byte_total,
                     "algorithmic_flops_per_launch": flops, "us_per_launch": us,
                     "row_tiles": int(counts[len(held)]), "pairs": int(counts[:len(held)].sum())}
     card.wait()
@@ -610,7 +625,7 @@ def run_original_weights(args, api, base, rank, world, local_rank, dist, barrier
         byte_total = active * 2 * matrix_bytes(I, H) + rows * H * 2 + rows * H // 32 + pairs * I * 2
         achieved = byte_total / us / 1000.0
         roofline = {"kernel": "expert_gate_up_2", "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                    "frac": achieved / peak, "peak_source": source, "traffic": None,
+                    "frac": achieved / peak, "peak_source": source, "traffic": MX_GATE_UP_TRAFFIC_RATIO * byte_total,
                     "algorithmic_bytes_per_launch": byte_total, "us_per_launch": us, "active_experts": active}
     card.wait()
     barrier()
