@@ -670,9 +670,12 @@ def run_reduction(args, api, hidden, rank, world, local_rank, dist, barrier, max
     row_counts, repeats, warm_graphs, timed_graphs = (1, 8, 64), 10, 1, 4
     pool_entries = len(forms) * len(row_counts) * repeats * (warm_graphs + 1 + timed_graphs)
     pool, cursor = layout.take(64 * pool_entries, 64), layout.take(16)
+    copy_bytes = 64 << 20  # a peer copy's rate, measured here: what the calls' NVLink bytes a second are set against
+    copy_from, copy_to = layout.take(copy_bytes, 4096), layout.take(copy_bytes, 4096)
     arena_bytes = layout.take(4096, 4096)
     card = api.Card(local_rank, arena_bytes)
     card.fill(0, 0, arena_bytes)
+    card.fill(copy_from, rank + 1, copy_bytes)
     blocks = np.zeros(64 * pool_entries, dtype=np.uint8)
     entry = 0
     for form in forms:  # the order the timings below run in; sequences strictly increasing
@@ -719,6 +722,21 @@ def run_reduction(args, api, hidden, rank, world, local_rank, dist, barrier, max
                     card.ipc_connect(handle, 0, peer_table + 32 * peer)
     # the peer table names a rank's region: written for the pull forms first, rewritten for the exchange below
     connect(pull_region)
+    # every rank copies 64 MB into its right neighbour's arena at once (a copy launch: the card's copy engine), eight
+    # times between two events; the rate is the slowest rank's
+    neighbour = (rank + 1) % world
+    copies = [R.copy_launch(copy_from, copy_to, copy_bytes, destination_word=peer_table + 32 * neighbour)] * 8
+    card.run(copies[:1])
+    card.wait()
+    barrier()
+    card.measure_begin()
+    card.run(copies)
+    card.measure_end()
+    peer_copy_gbs = len(copies) * copy_bytes / maximum(card.measure_elapsed_us()) / 1000.0
+    received = card.download(copy_to, 64, np.uint8)  # the left neighbour's bytes have arrived (its rank in every byte)
+    barrier()
+    if not (received == (rank - 1) % world + 1).all():
+        raise RuntimeError("the peer copy did not arrive")
     for mode, name in ((R.ORDERED_REDUCE_EVERY_RANK, "pull_every_rank"), (R.ORDERED_REDUCE_OWNER_RUNS, "pull_owner_runs")):
         for rows in (1, 8, 64):
             reduce = R.OrderedReduceBf16Description()
@@ -798,13 +816,16 @@ def run_reduction(args, api, hidden, rank, world, local_rank, dist, barrier, max
         moved = remote[name](rows)
         out.append({"form": name, "rows": rows, "us_per_call": us, "launches_per_call": launches,
                     "remote_bytes_per_rank": int(moved), "nvlink_gbs": moved / us / 1000.0,
-                    "frac_of_770_measured": moved / us / 1000.0 / 770.0,
+                    "frac_of_peer_copy_measured": moved / us / 1000.0 / peer_copy_gbs,
                     "frac_of_900_nominal": moved / us / 1000.0 / 900.0})
     return {"config": {"workload": "cfg2 ordered reduction alone: FP32 [M][%d] a rank, N(0, 0.05^2), rank order, one "
                                    "rounding to bfloat16, M in {1, 8, 64}, %d ranks" % (hidden, world)},
             "note": "a call is a select launch (the next step block from a pool on the card) and the form's "
                     "launches; ten calls a captured graph, four graphs timed back to back; the exchange's rows "
                     "wait in its slot, the pull forms first add one 'pair' a row into theirs (their publish launch)",
+            "peer_copy_gbs": peer_copy_gbs,
+            "peer_copy": "every rank copies 64 MB into its right neighbour's arena at once, eight copies between two "
+                         "CUDA events, the slowest rank's rate: GB/s a direction a GPU, measured in this run",
             "calls": out}
 
 
