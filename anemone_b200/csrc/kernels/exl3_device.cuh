@@ -127,13 +127,23 @@ __device__ __forceinline__ uint32_t exl3_pair(uint32_t low_state, uint32_t high_
 	return *reinterpret_cast<const uint32_t *>(&value);
 }
 
-/* state of the lane's symbol e from its two ring words, already shifted so that its first window starts at the top */
+/* state of the lane's symbol e from its two ring words, already shifted so that its first window starts at the top.
+ * Widths whose windows start on a few distinct bit positions modulo 8 (K2: four, K4: two) take a state as two bytes of
+ * the word shifted by that position (one shift serves every state that shares it, one byte permute a state: the
+ * compiler keeps the shifted word); the other widths shift and mask. */
 template <uint32_t BX2>
 __device__ __forceinline__ uint32_t exl3_state_of(uint32_t high, uint32_t low, uint32_t e)
 {
 	const uint32_t offset = exl3_ring<BX2>::offset(e);
 	if (offset == 0u)
 		return high >> 16;
+	if (BX2 == 4u || BX2 == 8u) {
+		/* the 32 bits the state lies in: the first word, or the window that begins 16 bits into it */
+		const uint32_t word = offset <= 16u ? high : __funnelshift_r(low, high, 16);
+		const uint32_t distance = (offset <= 16u ? 16u : 32u) - offset; /* of the state's last bit from the word's */
+		const uint32_t byte = distance / 8u; /* 0, 1 or 2: the state is bytes byte, byte + 1 of the shifted word */
+		return __byte_perm(word >> (distance % 8u), 0u, byte == 0u ? 0x4410u : byte == 1u ? 0x4421u : 0x4432u);
+	}
 	if (offset <= 16u)
 		return (high >> (16u - offset)) & 0xFFFFu;
 	return __funnelshift_r(low, high, 48u - offset) & 0xFFFFu;
