@@ -144,14 +144,9 @@ __device__ __forceinline__ uint32_t exl3_state_of(uint32_t high, uint32_t low, u
 		const uint32_t byte = distance / 8u; /* 0, 1 or 2: the state is bytes byte, byte + 1 of the shifted word */
 		return __byte_perm(word >> (distance % 8u), 0u, byte == 0u ? 0x4410u : byte == 1u ? 0x4421u : 0x4432u);
 	}
-	/* the other widths: one bit-field extract a state (a slower instruction than a shift or a mask, but one issue slot
-	 * instead of two where issue slots are what the kernel lacks) */
-	uint32_t state;
 	if (offset <= 16u)
-		asm("bfe.u32 %0, %1, %2, 16;" : "=r"(state) : "r"(high), "r"(16u - offset));
-	else
-		asm("bfe.u32 %0, %1, %2, 16;" : "=r"(state) : "r"(__funnelshift_r(low, high, 16)), "r"(32u - offset));
-	return state;
+		return (high >> (16u - offset)) & 0xFFFFu;
+	return __funnelshift_r(low, high, 48u - offset) & 0xFFFFu;
 }
 
 /* The four A registers of m16n8k16 for one tile: symbols {0,1}, {4,5}, {2,3}, {6,7} of the lane. */
