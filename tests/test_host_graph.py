@@ -47,6 +47,13 @@ def test_tables_outside_the_grammar(branches):
     assert order_of(branches) == R.STATUS_INVALID_ARGUMENT
 
 
+def test_a_launch_that_may_overlap_the_one_before_it_is_a_chain_launch():
+    overlap = 0x100  # LAUNCH_OVERLAPS_PREVIOUS
+    assert order_of([CHAIN, CHAIN | overlap, CHAIN | overlap]) == [[], [0], [1]]
+    assert order_of([CHAIN, SIDE, RESUME | overlap]) == R.STATUS_INVALID_ARGUMENT  # the bit goes with CHAIN alone
+    assert order_of([CHAIN | overlap, SIDE, RESUME, JOIN]) == [[], [0], [0], [1, 2]]
+
+
 def test_null_and_empty():
     lib = api.library()
     table, order = (R.KernelLaunch * 1)(), (R.LaunchOrder * 1)()

@@ -321,3 +321,71 @@ def test_collective_host_equals_reference(reference):
         for a, b in zip(ours, theirs):
             assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
     assert lib.ordered_collective_host(pointer_array(inputs), pointer_array(inputs), 5, 999, 0) == 1  # overlap
+
+
+def layer_description(rows=8, hidden=4096, inner=2048, experts=256, picks=8, ranks=1):
+    """A decode step's description laid out in an arena, for exl3_layer_prepare (fake card: nothing is read)."""
+    slots, jobs = picks + 1, rows * picks + 1
+    pairs = rows * slots
+    sizes = api.layer_sizes(pairs, jobs, hidden, inner)
+    layout = api.Layout(256)
+    description = R.Exl3LayerDescription()
+    route = description.route
+    peer_table, status, step = layout.take(16 * 32), layout.take(16), layout.take(16)
+    stride = api.align(R.EXL3_LAYER_SIGNAL_BYTES + rows * hidden * 4, 128)
+    region = layout.take(2 * stride, 128)
+    products = layout.take(max(sizes.product_bytes, pairs * hidden * 8))
+    route.moe.base = R.Exl3Expert(layout.take(jobs * 96), layout.take(rows * hidden * 2), layout.take(sizes.operand_bytes),
+                                  products, layout.take(pairs * inner * 2), products, hidden, inner, pairs, slots, jobs,
+                                  R.EXL3_WIDTH_PER_EXPERT, 10.0, 0)
+    route.moe.widths_offset, route.moe.row_output_offset = layout.take((experts + 1) * 4), layout.take(rows * hidden * 4)
+    route.moe.counters_offset, route.moe.expert_count = layout.take(sizes.counter_bytes), experts + 1
+    route.scores_offset, route.expert_table_offset = layout.take(rows * experts * 4), layout.take((experts + 1) * 24)
+    route.picks_offset, route.weights_offset = layout.take(rows * picks * 4), layout.take(rows * picks * 4)
+    route.step_offset, route.routed_count, route.shared_count, route.picks, route.row_capacity = step, experts, 1, picks, rows
+    route.scoring, route.route_scale = 0, 1.0
+    description.publish = R.Exl3LayerPublish(peer_table, region, R.EXL3_LAYER_SIGNAL_BYTES, status, step, stride,
+                                             1_000_000, ranks, 0, rows, 0)
+    description.result_offset = layout.take(rows * hidden * 2)
+    description.arena_byte_count = layout.take(0, 4096) + 4096
+    return description, sizes
+
+
+def test_layer_prepare_three_launches():
+    lib, fake = api.library(), FakeBackend()
+    for inner, runs in ((2048, 4), (1024, 4), (512, 8), (256, 8)):  # one, two, four and eight ranks' shares
+        description, sizes = layer_description(inner=inner)
+        assert sizes.product_bytes == (2 * 16 * 72 * inner + 16 * 72 * 4096) * 4  # gate/up's, then down's own
+        assert sizes.counter_bytes == (65 * (inner // 128 + 32) + 4 + 65) * 4
+        launches = (R.KernelLaunch * R.EXL3_LAYER_LAUNCHES)()
+        assert lib.exl3_layer_prepare(C.byref(description), C.byref(fake.table), fake.card, launches) == 0
+        assert [key[1] for key in fake.asked[-3:]] == ["exl3_layer_route_input", "exl3_layer_products",
+                                                       "ordered_publish_reduce_flags"]
+        assert [key[2] for key in fake.asked[-3:]] == [184, 128, 104]
+        route, products, reduce = launches
+        assert tuple(route.block) == (1024, 1, 1) and route.grid[0] == 1 + 8 * 9 * 2 * 32 // 32 and route.branch == 0
+        # a CTA an item: every job's gate and up items (two matrices x groups x runs), then its down items
+        assert tuple(products.grid) == (65 * (2 * (inner // 128) * runs + 32), 1, 1) and products.block[0] == 128
+        assert products.branch == reduce.branch == 0x100  # each is given its place while the one before it runs
+        record = R.Exl3LayerProducts.from_buffer_copy(bytes(products.argument[:128]))
+        assert (record.gate_up_runs, record.down_runs) == (runs, 1)
+        assert record.down_products_offset == description.route.moe.base.products_offset + 2 * 16 * 72 * inner * 4
+        publish = R.OrderedPublishReduce.from_buffer_copy(bytes(reduce.argument[:104]))
+        assert publish.pair_output_offset == record.down_products_offset  # run 0 of down's sums: the pair outputs
+    # the caller's cut; refusals leave the table untouched
+    description, _ = layer_description()
+    description.gate_up_runs, description.down_runs = 2, 2
+    launches = (R.KernelLaunch * R.EXL3_LAYER_LAUNCHES)()
+    assert lib.exl3_layer_prepare(C.byref(description), C.byref(fake.table), fake.card, launches) == 0
+    assert launches[1].grid[0] == 65 * (2 * 16 * 2 + 32 * 2)
+    untouched = bytes(launches)
+    for change in (dict(gate_up_runs=3), dict(gate_up_runs=64), dict(down_runs=32)):
+        bad, _ = layer_description()
+        for name, value in change.items():
+            setattr(bad, name, value)
+        assert lib.exl3_layer_prepare(C.byref(bad), C.byref(fake.table), fake.card, launches) == 1
+        assert bytes(launches) == untouched
+    bad, _ = layer_description()
+    bad.route.moe.counters_offset = bad.route.moe.base.products_offset  # overlaps the partial sums
+    assert lib.exl3_layer_prepare(C.byref(bad), C.byref(fake.table), fake.card, launches) == 1
+    assert bytes(launches) == untouched
