@@ -284,8 +284,10 @@ static uint32_t trunk_matrix_instance(const struct linear_matrix *matrix, enum w
 
 static result_status shared_expert_prepare(const struct linear_shared_expert_description *description,
 					   uint64_t arena_byte_count, const struct linear_kernels_record *kernels,
-					   enum weight_format_code format, const uint32_t *handles,
+					   enum weight_format_code format, const uint32_t *handles, uint32_t row_limit,
 					   struct kernel_launch *launches_out);
+
+#define SHARED_EXPERT_WIDE_ROWS 65535u
 
 result_status linear_shared_expert_prepare(const struct linear_shared_expert_description *description,
 					   uint64_t arena_byte_count, const struct linear_kernels_record *kernels,
@@ -294,7 +296,41 @@ result_status linear_shared_expert_prepare(const struct linear_shared_expert_des
 	if (kernels == NULL)
 		return STATUS_INVALID_ARGUMENT;
 	return shared_expert_prepare(description, arena_byte_count, kernels, WEIGHT_FORMAT_E4M3_SCALED,
-				     kernels->trunk_linear_quantized, launches_out);
+				     kernels->trunk_linear_quantized, LINEAR_MAXIMUM_ROWS, launches_out);
+}
+
+static result_status block128_handles(const struct backend_operations *backend, struct device_card *card,
+				      uint32_t handles[LINEAR_SLICE_INSTANCES])
+{
+	for (uint32_t instance = 0; instance < LINEAR_SLICE_INSTANCES; instance++) {
+		char name[48];
+		(void)snprintf(name, sizeof(name), "trunk_linear_block128_%u", slice_counts[instance]);
+		handles[instance] = BACKEND_NO_KERNEL;
+		const result_status status = backend->kernel_prepare(card, KERNEL_FILE_TRUNK_LINEAR, name,
+								     sizeof(struct trunk_linear_quantized_arguments),
+								     &handles[instance]);
+		if (status != STATUS_OK)
+			return status;
+	}
+	return STATUS_OK;
+}
+
+result_status linear_shared_expert_wide_prepare(const struct linear_shared_expert_description *description,
+						uint64_t arena_byte_count, const struct linear_kernels_record *kernels,
+						const struct backend_operations *backend, struct device_card *card,
+						struct kernel_launch *launches_out)
+{
+	if (description == NULL || kernels == NULL || backend == NULL || backend->kernel_prepare == NULL || card == NULL)
+		return STATUS_INVALID_ARGUMENT;
+	if (description->gate.weight_format != WEIGHT_FORMAT_E4M3_BLOCK128)
+		return shared_expert_prepare(description, arena_byte_count, kernels, WEIGHT_FORMAT_E4M3_SCALED,
+					     kernels->trunk_linear_quantized, SHARED_EXPERT_WIDE_ROWS, launches_out);
+	uint32_t handles[LINEAR_SLICE_INSTANCES];
+	const result_status status = block128_handles(backend, card, handles);
+	if (status != STATUS_OK)
+		return status;
+	return shared_expert_prepare(description, arena_byte_count, kernels, WEIGHT_FORMAT_E4M3_BLOCK128, handles,
+				     SHARED_EXPERT_WIDE_ROWS, launches_out);
 }
 
 result_status linear_shared_expert_block128_prepare(const struct linear_shared_expert_description *description,
@@ -306,27 +342,20 @@ result_status linear_shared_expert_block128_prepare(const struct linear_shared_e
 	if (kernels == NULL || backend == NULL || backend->kernel_prepare == NULL || card == NULL)
 		return STATUS_INVALID_ARGUMENT;
 	uint32_t handles[LINEAR_SLICE_INSTANCES];
-	for (uint32_t instance = 0; instance < LINEAR_SLICE_INSTANCES; instance++) {
-		char name[48];
-		(void)snprintf(name, sizeof(name), "trunk_linear_block128_%u", slice_counts[instance]);
-		handles[instance] = BACKEND_NO_KERNEL;
-		const result_status status = backend->kernel_prepare(card, KERNEL_FILE_TRUNK_LINEAR, name,
-								     sizeof(struct trunk_linear_quantized_arguments),
-								     &handles[instance]);
-		if (status != STATUS_OK)
-			return status;
-	}
+	const result_status status = block128_handles(backend, card, handles);
+	if (status != STATUS_OK)
+		return status;
 	return shared_expert_prepare(description, arena_byte_count, kernels, WEIGHT_FORMAT_E4M3_BLOCK128, handles,
-				     launches_out);
+				     LINEAR_MAXIMUM_ROWS, launches_out);
 }
 
 static result_status shared_expert_prepare(const struct linear_shared_expert_description *description,
 					   uint64_t arena_byte_count, const struct linear_kernels_record *kernels,
-					   enum weight_format_code format, const uint32_t *handles,
+					   enum weight_format_code format, const uint32_t *handles, uint32_t row_limit,
 					   struct kernel_launch *launches_out)
 {
 	if (description == NULL || kernels == NULL || launches_out == NULL || description->row_count == 0 ||
-	    description->row_count > LINEAR_MAXIMUM_ROWS || !isfinite(description->activation_limit) ||
+	    description->row_count > row_limit || !isfinite(description->activation_limit) ||
 	    description->activation_limit <= 0 || kernels->trunk_hidden == BACKEND_NO_KERNEL ||
 	    kernels->activation_quantize == BACKEND_NO_KERNEL)
 		return STATUS_INVALID_ARGUMENT;
@@ -393,8 +422,10 @@ static result_status shared_expert_prepare(const struct linear_shared_expert_des
 									 I,
 									 description->row_count };
 	struct kernel_launch launches[LINEAR_SHARED_EXPERT_LAUNCH_COUNT];
+	/* eight rows a block column of the two product launches */
+	const uint32_t row_groups = (description->row_count + LINEAR_MAXIMUM_ROWS - 1u) / LINEAR_MAXIMUM_ROWS;
 	prepare_launch_fill(&launches[LINEAR_SHARED_EXPERT_GATE_UP], handles[gate_instance],
-			    2u * I / LINEAR_OUTPUTS_PER_TILE, 1, 1, 32u * gate->slice_count, 0, &gate_up_arguments,
+			    2u * I / LINEAR_OUTPUTS_PER_TILE, row_groups, 1, 32u * gate->slice_count, 0, &gate_up_arguments,
 			    sizeof(gate_up_arguments));
 	prepare_launch_fill(&launches[LINEAR_SHARED_EXPERT_HIDDEN], kernels->trunk_hidden,
 			    (I + LINEAR_ELEMENT_THREADS - 1u) / LINEAR_ELEMENT_THREADS, description->row_count, 1,
@@ -403,7 +434,7 @@ static result_status shared_expert_prepare(const struct linear_shared_expert_des
 			    I / LINEAR_VALUES_PER_LOAD, description->row_count, 1, 32, 0, &quantize_arguments,
 			    sizeof(quantize_arguments));
 	prepare_launch_fill(&launches[LINEAR_SHARED_EXPERT_DOWN], handles[down_instance],
-			    O / LINEAR_OUTPUTS_PER_TILE, 1, 1, 32u * down->slice_count, 0, &down_arguments,
+			    O / LINEAR_OUTPUTS_PER_TILE, row_groups, 1, 32u * down->slice_count, 0, &down_arguments,
 			    sizeof(down_arguments));
 	memcpy(launches_out, launches, sizeof(launches));
 	return STATUS_OK;

@@ -48,6 +48,64 @@ result_status router_select_b200_prepare(const struct router_select_b200_argumen
 	return STATUS_OK;
 }
 
+result_status router_wide_prepare(const struct router_wide_arguments *arguments, uint64_t arena_byte_count,
+				  const struct backend_operations *backend, struct device_card *card,
+				  struct kernel_launch *launches_out)
+{
+	if (arguments == NULL || backend == NULL || backend->kernel_prepare == NULL || card == NULL || launches_out == NULL)
+		return STATUS_INVALID_ARGUMENT;
+	const struct exl3_prefill_record *const routing = &arguments->routing;
+	const uint64_t rows = routing->row_capacity;
+	if (arguments->reserved_zero != 0 || routing->expert_count == 0 ||
+	    routing->expert_count > ROUTER_B200_MAXIMUM_EXPERTS || routing->local_first != 0 ||
+	    routing->local_count != routing->expert_count || routing->shared_count != 0 || routing->picks == 0 ||
+	    routing->picks > ROUTER_B200_MAXIMUM_PICKS || routing->picks > routing->expert_count || rows == 0 ||
+	    rows > 65535u || routing->scoring > ROUTER_SCORING_SQRT_SOFTPLUS || !isfinite(routing->route_scale) ||
+	    routing->route_scale <= 0 || routing->workspace_offset % 1024u != 0 ||
+	    arguments->job_capacity < rows * routing->picks / LINEAR_MAXIMUM_ROWS + routing->expert_count)
+		return STATUS_INVALID_ARGUMENT;
+	const struct exl3_prefill_parts parts = exl3_prefill_parts_of(routing->row_capacity, routing->picks, 0,
+								      routing->expert_count, routing->input_size,
+								      routing->inner_size);
+	const struct checked_range ranges[8] = {
+		{ "bias", routing->bias_offset, routing->bias_offset != 0 ? (uint64_t)routing->expert_count * 4u : 0u },
+		{ "scores", routing->scores_offset, rows * routing->expert_count * 4u },
+		{ "expert table", routing->expert_table_offset, (uint64_t)routing->expert_count * 24u },
+		{ "picks", routing->picks_offset, rows * routing->picks * 4u },
+		{ "weights", routing->weights_offset, rows * routing->picks * 4u },
+		{ "workspace", routing->workspace_offset, parts.gate_up_operands },
+		{ "jobs", arguments->jobs_offset, (uint64_t)arguments->job_capacity * sizeof(struct expert_job_record) },
+		{ "step block", routing->step_offset, sizeof(struct step_block) }
+	};
+	if (!prepare_ranges_are_valid("router wide", ranges, 8, arena_byte_count))
+		return STATUS_INVALID_ARGUMENT;
+	const uint32_t row_warps = ROUTER_B200_THREADS / 32u;
+	const struct {
+		const char *file, *name;
+		const void *record;
+		uint32_t bytes, blocks, threads;
+	} shapes[ROUTER_WIDE_LAUNCHES] = {
+		{ EXL3_PREFILL_KERNEL_FILE, "exl3_prefill_picks", routing, sizeof(*routing),
+		  (routing->row_capacity + row_warps - 1u) / row_warps, ROUTER_B200_THREADS },
+		{ EXL3_PREFILL_KERNEL_FILE, "exl3_prefill_group", routing, sizeof(*routing), routing->expert_count, 256u },
+		{ KERNEL_FILE_ROUTER_B200, KERNEL_ROUTER_WIDE_JOBS, arguments, sizeof(*arguments), 1u, ROUTER_B200_THREADS }
+	};
+	struct kernel_launch launches[ROUTER_WIDE_LAUNCHES];
+	for (uint32_t index = 0; index < ROUTER_WIDE_LAUNCHES; index++) {
+		uint32_t kernel = BACKEND_NO_KERNEL;
+		const result_status status =
+			backend->kernel_prepare(card, shapes[index].file, shapes[index].name, shapes[index].bytes, &kernel);
+		if (status != STATUS_OK)
+			return status;
+		if (kernel == BACKEND_NO_KERNEL)
+			return STATUS_UNSUPPORTED;
+		prepare_launch_fill(&launches[index], kernel, shapes[index].blocks, 1, 1, shapes[index].threads, 0,
+				    shapes[index].record, shapes[index].bytes);
+	}
+	memcpy(launches_out, launches, sizeof(launches));
+	return STATUS_OK;
+}
+
 result_status step_input_select_prepare(const struct step_input_select_arguments *arguments, uint64_t arena_byte_count,
 					const struct backend_operations *backend, struct device_card *card,
 					struct kernel_launch *launch_out)

@@ -55,3 +55,75 @@ extern "C" __global__ void __launch_bounds__(ROUTER_B200_THREADS)
 	if (threadIdx.x == 0)
 		*cursor = *cursor + 1u;
 }
+
+/* ------------------------------------------------------------------ the job table of many rows */
+
+/* One block of ROUTER_B200_THREADS. The grouping launch has left, per expert, its rows' entries (pair, route weight)
+ * in ascending row order and their count. Thread e counts expert e's jobs of eight rows; a block-wide prefix sum gives
+ * every expert its first job; then a warp an expert (in turns) writes that expert's jobs, lane c the job's column c.
+ * The table's bytes are those router_select_b200 writes for the same choices. */
+extern "C" __global__ void __launch_bounds__(ROUTER_B200_THREADS)
+	router_wide_jobs(struct router_wide_arguments arguments, unsigned char *arena)
+{
+	__shared__ uint32_t first_job[ROUTER_B200_MAXIMUM_EXPERTS + 1u];
+	__shared__ uint32_t warp_total[ROUTER_B200_THREADS / WARP];
+	const struct exl3_prefill_record &routing = arguments.routing;
+	const struct exl3_prefill_parts parts = exl3_prefill_parts_of(routing.row_capacity, routing.picks, 0u,
+								      routing.expert_count, routing.input_size,
+								      routing.inner_size);
+	unsigned char *const workspace = arena + routing.workspace_offset;
+	const uint32_t *const counts = reinterpret_cast<const uint32_t *>(workspace + parts.counts);
+	const struct exl3_prefill_entry *const entries =
+		reinterpret_cast<const struct exl3_prefill_entry *>(workspace + parts.entries);
+	const uint64_t *const table = reinterpret_cast<const uint64_t *>(arena + routing.expert_table_offset);
+	struct expert_job_record *const jobs = reinterpret_cast<struct expert_job_record *>(arena + arguments.jobs_offset);
+	const uint32_t lane = threadIdx.x % WARP, warp = threadIdx.x / WARP, warps = blockDim.x / WARP;
+	const uint32_t experts = routing.expert_count;
+	/* jobs of expert `threadIdx.x`, and the block's exclusive prefix sum of them */
+	const uint32_t mine = threadIdx.x < experts ? (counts[threadIdx.x] + LINEAR_MAXIMUM_ROWS - 1u) / LINEAR_MAXIMUM_ROWS : 0u;
+	uint32_t before = mine;
+	for (uint32_t distance = 1; distance < WARP; distance <<= 1) {
+		const uint32_t other = __shfl_up_sync(0xFFFFFFFFu, before, distance);
+		if (lane >= distance)
+			before += other;
+	}
+	if (lane == WARP - 1u)
+		warp_total[warp] = before;
+	__syncthreads();
+	uint32_t earlier = 0;
+	for (uint32_t other = 0; other < warp; other++)
+		earlier += warp_total[other];
+	if (threadIdx.x < experts)
+		first_job[threadIdx.x] = earlier + before - mine;
+	if (threadIdx.x == blockDim.x - 1u)
+		first_job[ROUTER_B200_MAXIMUM_EXPERTS] = earlier + before; /* every expert's jobs together */
+	__syncthreads();
+	const uint32_t live_jobs = min(first_job[ROUTER_B200_MAXIMUM_EXPERTS], arguments.job_capacity);
+	/* every byte of the jobs behind the live ones is zero */
+	uint4 *const words = reinterpret_cast<uint4 *>(jobs + live_jobs);
+	const uint32_t spare = (arguments.job_capacity - live_jobs) * (uint32_t)(sizeof(struct expert_job_record) / 16u);
+	for (uint32_t index = threadIdx.x; index < spare; index += blockDim.x)
+		words[index] = make_uint4(0, 0, 0, 0);
+	for (uint32_t expert = warp; expert < experts; expert += warps) {
+		const uint32_t rows = counts[expert];
+		const struct exl3_prefill_entry *const of_expert = entries + (uint64_t)expert * routing.row_capacity;
+		for (uint32_t first = 0, job_index = first_job[expert]; first < rows && job_index < arguments.job_capacity;
+		     first += LINEAR_MAXIMUM_ROWS, job_index++) {
+			struct expert_job_record *const job = &jobs[job_index];
+			if (lane < LINEAR_MAXIMUM_ROWS) {
+				const bool held = first + lane < rows;
+				const struct exl3_prefill_entry entry =
+					held ? of_expert[first + lane] : exl3_prefill_entry{ 0u, 0.0f };
+				job->pair_index[lane] = entry.pair;
+				job->route_weight[lane] = entry.route_weight;
+			}
+			if (lane == 0) {
+				job->gate_offset = table[3u * expert];
+				job->up_offset = table[3u * expert + 1u];
+				job->down_offset = table[3u * expert + 2u];
+				job->expert = expert;
+				job->row_count = min(rows - first, LINEAR_MAXIMUM_ROWS);
+			}
+		}
+	}
+}

@@ -85,9 +85,12 @@ __device__ __forceinline__ void trunk_linear_quantized(const struct trunk_linear
 	const uint32_t outputs = arguments.output_size[second ? 1 : 0], inputs = arguments.input_size;
 	const unsigned char *const matrix = arena + arguments.weights_offset[second ? 1 : 0];
 	const uint32_t groups = inputs / LINEAR_VALUES_PER_BLOCK, loads = inputs / LINEAR_VALUES_PER_LOAD;
-	const uint32_t rows = arguments.row_count;
-	const uint32_t fed_row = group_lane < rows ? group_lane : 0u;
-	const uint32_t even_row = 2u * place < rows ? 2u * place : 0u, odd_row = 2u * place + 1u < rows ? 2u * place + 1u : 0u;
+	/* eight rows a block column (blockIdx.y; the reference's launches have one: at most eight rows) */
+	const uint32_t row_base = blockIdx.y * LINEAR_MAXIMUM_ROWS;
+	const uint32_t rows = min(arguments.row_count - row_base, LINEAR_MAXIMUM_ROWS);
+	const uint32_t fed_row = row_base + (group_lane < rows ? group_lane : 0u);
+	const uint32_t even_row = row_base + (2u * place < rows ? 2u * place : 0u);
+	const uint32_t odd_row = row_base + (2u * place + 1u < rows ? 2u * place + 1u : 0u);
 	const uint4 *const bytes = reinterpret_cast<const uint4 *>(matrix) + ((uint64_t)tile * groups) * WARP + lane;
 	const unsigned char *const scales = matrix + (uint64_t)outputs * inputs + (uint64_t)(tile / 2u) * groups;
 	const float *const scales128 =
@@ -161,7 +164,7 @@ __device__ __forceinline__ void trunk_linear_quantized(const struct trunk_linear
 #pragma unroll
 		for (uint32_t part = 0; part < S; part++)
 			sum = __fadd_rn(sum, parts[part][lane][c]);
-		output[(uint64_t)row * outputs + tile * LINEAR_OUTPUTS_PER_TILE + group_lane + (c >> 1) * 8u] =
+		output[(uint64_t)(row_base + row) * outputs + tile * LINEAR_OUTPUTS_PER_TILE + group_lane + (c >> 1) * 8u] =
 			(uint16_t)bfloat16_bits(sum);
 	}
 }

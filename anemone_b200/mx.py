@@ -7,6 +7,11 @@ and run per step through the C-ABI library. Launches of one step, all from liban
     -> ordered_row_sum_publish -> ordered_reduce_bf16
 (linear_routed_experts_prepare's four, linear_shared_expert_prepare's four). Tensor parallelism is by intermediate columns, as in the
 EXL3 decode layer; the ranks' FP32 rows are added in rank order and rounded once. Nothing here computes on the host.
+
+wide=True is the same layer for MANY rows (the profile's prefill): the router's launch gives way to the three of
+router_wide_prepare (the prefill's picks and grouping, then a job table of eight rows a job), the always-on expert to
+linear_shared_expert_wide_prepare (a block column per eight rows), and the reduction adds by owner runs. The expert
+launches are the same thin instances: every job streams its expert's matrices again (mostly from L2).
 """
 import ctypes as C
 
@@ -34,15 +39,15 @@ def shared_matrix_bytes(outputs, inputs, block128=False):
 
 
 class MxLayout:
-    def __init__(self, config, rank_count, rank, pool_entries=0, block128=False):
+    def __init__(self, config, rank_count, rank, pool_entries=0, block128=False, wide=False):
         assert config.shared in (0, 1)
-        self.block128 = block128
+        self.block128, self.wide = block128, wide
         self.pool_entries = pool_entries
         self.config = c = config
         self.inner_local = I = rank_columns(c.inner, rank_count, rank)[1]
         H, rows = c.hidden, c.row_capacity
         self.pairs = pairs = rows * c.picks
-        self.job_capacity = rows * c.picks
+        self.job_capacity = rows * c.picks // 8 + c.experts if wide else rows * c.picks
         layout = api.Layout()
         self.peer_table = layout.take(16 * 32)
         self.step = layout.take(256)
@@ -63,6 +68,9 @@ class MxLayout:
         self.weights = layout.take(rows * c.picks * 4)
         self.jobs = layout.take(self.job_capacity * 96)
         self.expert_table = layout.take(c.experts * 24)
+        # many rows: counts and entries of the grouping launch (the head of the prefill's workspace)
+        self.workspace_bytes = api.prefill_parts(rows, c.picks, 0, c.experts, H, I).gate_up_operands if wide else 0
+        self.workspace = layout.take(self.workspace_bytes, 1024) if wide else 0
         self.sizes = {"codes": rows * H, "exponents": rows * H // 32, "operands": rows * H * 2,
                       "hidden": pairs * I * 2, "hidden_codes": pairs * I, "hidden_exponents": pairs * I // 32,
                       "hidden_operands": pairs * I * 2, "pair_output": pairs * H * 2, "row_output": rows * H * 4}
@@ -85,12 +93,12 @@ class MxLayout:
 
 class MxLayer:
     def __init__(self, card, config, matrices, rank=0, rank_count=1, slices=(4, 4), shared_matrices=None,
-                 shared_slices=(2, 2), pool_entries=0, block128=False):
+                 shared_slices=(2, 2), pool_entries=0, block128=False, wide=False):
         """matrices: iterable over the routed experts of this rank's (gate, up, down) stored MXFP4 bytes;
         shared_matrices: the always-on expert's (gate, up, down) stored E4M3 bytes, where the configuration has one:
         WEIGHT_FORMAT_E4M3_SCALED, or with block128 WEIGHT_FORMAT_E4M3_BLOCK128 (one FP32 scale per 128 by 128)."""
         self.card, self.config = card, config
-        self.layout = L = MxLayout(config, rank_count, rank, pool_entries, block128)
+        self.layout = L = MxLayout(config, rank_count, rank, pool_entries, block128, wide)
         assert card.arena_bytes >= L.arena_bytes
         self.rank, self.rank_count = rank, rank_count
         self.weight_bytes = 0
@@ -120,8 +128,24 @@ class MxLayer:
                                                    C.POINTER(api.BackendOperations), C.c_void_p,
                                                    C.POINTER(R.KernelLaunch)]
         router_launch = R.KernelLaunch()
-        api.check(lib.router_select_b200_prepare(C.byref(router), card.arena_bytes, card.ops_pointer, card.handle,
-                                                 C.byref(router_launch)), "router_select_b200_prepare")
+        if wide:
+            routing = R.Exl3Prefill()
+            routing.scores_offset, routing.expert_table_offset = L.scores, L.expert_table
+            routing.picks_offset, routing.weights_offset, routing.workspace_offset = L.picks, L.weights, L.workspace
+            routing.step_offset, routing.input_size, routing.inner_size = L.step, H, I
+            routing.expert_count, routing.local_count, routing.picks = c.experts, c.experts, c.picks
+            routing.row_capacity, routing.scoring, routing.route_scale = c.row_capacity, c.scoring, c.route_scale
+            lib.router_wide_prepare.argtypes = [C.POINTER(R.RouterWide), C.c_uint64, C.POINTER(api.BackendOperations),
+                                                C.c_void_p, C.POINTER(R.KernelLaunch)]
+            router_launches = (R.KernelLaunch * R.ROUTER_WIDE_LAUNCHES)()
+            api.check(lib.router_wide_prepare(C.byref(R.RouterWide(routing, L.jobs, L.job_capacity, 0)),
+                                              card.arena_bytes, card.ops_pointer, card.handle, router_launches),
+                      "router_wide_prepare")
+            router_launches = list(router_launches)
+        else:
+            api.check(lib.router_select_b200_prepare(C.byref(router), card.arena_bytes, card.ops_pointer, card.handle,
+                                                     C.byref(router_launch)), "router_select_b200_prepare")
+            router_launches = [router_launch]
         kernels = R.LinearKernels()
         lib.linear_kernels_prepare.argtypes = [C.POINTER(api.BackendOperations), C.c_void_p, C.c_uint32,
                                                C.POINTER(R.LinearKernels)]
@@ -172,8 +196,13 @@ class MxLayer:
                                                                   C.POINTER(R.LinearKernels),
                                                                   C.POINTER(api.BackendOperations), C.c_void_p,
                                                                   C.POINTER(R.KernelLaunch)]
+            lib.linear_shared_expert_wide_prepare.argtypes = lib.linear_shared_expert_block128_prepare.argtypes
             four = (R.KernelLaunch * 4)()
-            if L.block128:
+            if wide:
+                api.check(lib.linear_shared_expert_wide_prepare(C.byref(shared), card.arena_bytes, C.byref(kernels),
+                                                                card.ops_pointer, card.handle, four),
+                          "linear_shared_expert_wide_prepare")
+            elif L.block128:
                 api.check(lib.linear_shared_expert_block128_prepare(C.byref(shared), card.arena_bytes, C.byref(kernels),
                                                                     card.ops_pointer, card.handle, four),
                           "linear_shared_expert_block128_prepare")
@@ -193,6 +222,7 @@ class MxLayer:
                                                        L.parity_stride, c.deadline_cycles, c.row_capacity * H,
                                                        rank_count, rank, 0)
         reduce.reduce.status_offset, reduce.reduce.width = L.status, H
+        reduce.reduce.mode = R.ORDERED_REDUCE_OWNER_RUNS if wide else R.ORDERED_REDUCE_EVERY_RANK
         reduce.pair_output_offset, reduce.arena_byte_count = L.at["row_output"], card.arena_bytes
         reduce.pairs_per_row, reduce.row_capacity = 1, c.row_capacity
         lib.ordered_reduce_bf16_prepare.argtypes = [C.POINTER(R.OrderedReduceBf16Description),
@@ -201,7 +231,7 @@ class MxLayer:
         reduce_launches = (R.KernelLaunch * 2)()
         api.check(lib.ordered_reduce_bf16_prepare(C.byref(reduce), card.ops_pointer, card.handle, reduce_launches),
                   "ordered_reduce_bf16_prepare")
-        self.launches = [router_launch, quantize_launch] + list(self.expert_launches) + shared_launches + \
+        self.launches = router_launches + [quantize_launch] + list(self.expert_launches) + shared_launches + \
             list(reduce_launches)
         self.graph = card.graph(self.launches)
         self.resident_graph = None

@@ -111,6 +111,14 @@ class Exl3Prefill(C.Structure):
                 ("route_scale", C.c_float), ("activation_limit", C.c_float), ("bias_offset", C.c_uint64)]
 
 
+class RouterWide(C.Structure):
+    _fields_ = [("routing", Exl3Prefill), ("jobs_offset", C.c_uint64), ("job_capacity", C.c_uint32),
+                ("reserved_zero", C.c_uint32)]
+
+
+ROUTER_WIDE_LAUNCHES = 3
+
+
 class Exl3PrefillTile(C.Structure):
     _fields_ = [("expert", C.c_uint32), ("first_entry", C.c_uint32), ("row_count", C.c_uint32),
                 ("reserved_zero", C.c_uint32)]

@@ -148,6 +148,16 @@ MUST_CHECK result_status linear_shared_expert_block128_prepare(const struct line
 							       const struct linear_kernels_record *kernels,
 							       const struct backend_operations *backend,
 							       struct device_card *card, struct kernel_launch *launches_out);
+
+/* B200 extension: the always-on expert for ANY number of rows (up to 65535), in either E4M3 format (the description's
+ * gate.weight_format decides): the same four launches with a block column per eight rows in the two product launches
+ * (grid[1]); everything else as the two entries above. For calls of many rows (the original-weights profile's
+ * prefill), whose rows the reference's thin launches would take eight at a time. */
+MUST_CHECK result_status linear_shared_expert_wide_prepare(const struct linear_shared_expert_description *description,
+							   uint64_t arena_byte_count,
+							   const struct linear_kernels_record *kernels,
+							   const struct backend_operations *backend,
+							   struct device_card *card, struct kernel_launch *launches_out);
 extern const struct weight_format_operations e4m3_block128_weight_operations;
 
 /* B200 extension (the reference joins the two in its FFN join, outside this path): one launch of

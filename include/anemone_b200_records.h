@@ -748,6 +748,22 @@ AB_INLINE struct exl3_prefill_parts exl3_prefill_parts_of(uint32_t row_capacity,
 	return parts;
 }
 
+/* B200 extension, kernel file "kernel_router_b200": the job table of MANY rows (up to the prefill's row capacity), for
+ * expert launches that take jobs of at most eight rows (the original-weights experts' thin instances). Three launches:
+ * the prefill's picks and grouping (exl3_prefill_picks, exl3_prefill_group with `routing`: every routed expert local,
+ * no always-on expert, a workspace of exl3_prefill_parts_of(...).gate_up_operands bytes: counts, tiles, entries), then
+ * router_wide_jobs (one block of ROUTER_B200_THREADS): expert e's rows, ascending, eight to a job, the experts'
+ * jobs in ascending expert order: the table router_select_b200 writes for a step of few rows. pair = row * picks +
+ * slot. Jobs from the live count on have a row count of zero. routing.expert_table_offset: uint64 [expert_count][3]. */
+#define KERNEL_ROUTER_WIDE_JOBS "router_wide_jobs"
+#define ROUTER_WIDE_LAUNCHES 3u
+struct router_wide_arguments {
+	struct exl3_prefill_record routing;
+	uint64_t jobs_offset; /* written: struct expert_job_record [job_capacity] */
+	uint32_t job_capacity; /* at least row_capacity * picks / 8 + expert_count */
+	uint32_t reserved_zero;
+};
+
 /* ------------------------------------------------------------------------------------------------------------
  * Original-weights experts: MXFP4 (E2M1 weights, one E8M0 scale per 32 inputs) by E4M3 block-quantized activations
  * (reference: include/anemone/linear_records.h:36-99, 222-299; include/anemone/weight_format_seam.h:23-46).
@@ -925,6 +941,7 @@ AB_RECORD_HAS(exl3_layer_publish_arguments, 72);
 AB_RECORD_HAS(exl3_prefill_tile, 16);
 AB_RECORD_HAS(exl3_prefill_entry, 8);
 AB_RECORD_HAS(exl3_prefill_record, 136);
+AB_RECORD_HAS(router_wide_arguments, 152);
 AB_RECORD_HAS(activation_quantize_arguments, 40);
 AB_RECORD_HAS(expert_gate_up_arguments, 64);
 AB_RECORD_HAS(expert_down_arguments, 56);

@@ -25,6 +25,14 @@ MUST_CHECK result_status router_select_b200_prepare(const struct router_select_b
 						    const struct backend_operations *backend, struct device_card *card,
 						    struct kernel_launch *launch_out);
 
+/* B200 extension: the job table of many rows (struct router_wide_arguments): ROUTER_WIDE_LAUNCHES launches. Checks
+ * the counts against the kernels' limits, routing.local_first == 0, local_count == expert_count, shared_count == 0,
+ * job_capacity >= row_capacity * picks / 8 + expert_count, and the ranges (scores, bias, expert table, picks, weights,
+ * the workspace up to its operand blocks, jobs, step block): inside the arena, aligned, disjoint. */
+MUST_CHECK result_status router_wide_prepare(const struct router_wide_arguments *arguments, uint64_t arena_byte_count,
+					     const struct backend_operations *backend, struct device_card *card,
+					     struct kernel_launch *launches_out);
+
 /* No reference counterpart (its step driver uploads every step block from the host). Checks the pool, the destination
  * and the cursor ranges (16-byte aligned, inside the arena, disjoint), pool_count >= 1, byte_count a positive multiple
  * of 16 not above pool_stride. One launch: ("kernel_router_b200", "step_input_select"), one block. */

@@ -357,3 +357,92 @@ def test_shared_expert_matches_oracle(api, oracle, rows, slices, block128):
         assert (received[at[name] + size:at[name] + size + 64] == 0xC3).all(), name
     for name, data in stored.items():
         assert np.array_equal(received[where[name]:where[name] + data.size], data)
+
+
+@pytest.mark.parametrize("block128", [False, True])
+def test_wide_layer_matches_oracle(api, oracle, block128):
+    """The original-weights layer for MANY rows (MxLayer(wide=True): the prefill's picks and grouping, a job table of
+    eight rows a job, the thin expert launches, the always-on expert a block column per eight rows, owner-run
+    reduction): the job table against the oracle's picks grouped by the same rule, bit for bit; then the oracle's
+    experts and always-on expert on the card's own quantized rows."""
+    from anemone_b200.moe import MoeConfig
+    from anemone_b200.mx import MxLayer, MxLayout
+    from oracle import moe_reference
+    rows = 203
+    config = MoeConfig(hidden=512, inner=384 if block128 else 256, experts=12, shared=1, picks=3, row_capacity=256,
+                       activation_limit=7.0)
+    rng = np.random.default_rng(123)
+    H, I = config.hidden, config.inner
+    matrices = [(mx_matrix(oracle, rng, I, H), mx_matrix(oracle, rng, I, H), mx_matrix(oracle, rng, H, I))
+                for _ in range(config.experts)]
+    draw = synthetic.e4m3_block128_matrix if block128 else synthetic.e4m3_matrix
+    always = (draw(rng, I, H), draw(rng, I, H), draw(rng, H, I))
+    tokens = synthetic.tokens(rng, rows, H)
+    scores = rng.normal(0, 1, size=(rows, config.experts)).astype(np.float32)
+    scores[:, 1] += 1.0  # one expert with many jobs
+    L = MxLayout(config, 1, 0, block128=block128, wide=True)
+    card = api.Card(0, L.arena_bytes)
+    try:
+        layer = MxLayer(card, config, matrices, slices=(2, 2), shared_matrices=always, block128=block128, wide=True)
+        layer.connect_local([layer])
+        for _ in range(2):  # both parity slots
+            result = layer.step(tokens, scores)
+        received = card.download(0, L.arena_bytes)
+    finally:
+        card.close()
+    experts, weights = moe_reference.route(oracle, config, scores)
+    picks = received[L.picks:L.picks + rows * config.picks * 4].view(np.uint32).reshape(rows, config.picks)
+    assert np.array_equal(picks, experts)
+    # the job table: expert e's rows ascending, eight to a job, experts ascending; everything else zero
+    table = np.frombuffer(received[L.expert_table:L.expert_table + config.experts * 24].tobytes(), dtype=np.uint64)
+    want = (R.ExpertJob * L.job_capacity)()
+    job = 0
+    for expert in range(config.experts):
+        held = [(row, slot) for row in range(rows) for slot in range(config.picks) if experts[row, slot] == expert]
+        for first in range(0, len(held), 8):
+            record = want[job]
+            record.gate_offset, record.up_offset, record.down_offset = (int(x) for x in table[3 * expert:3 * expert + 3])
+            record.expert, record.row_count = expert, min(8, len(held) - first)
+            for column, (row, slot) in enumerate(held[first:first + 8]):
+                record.pair_index[column] = row * config.picks + slot
+                record.route_weight[column] = float(weights[row, slot])
+            job += 1
+    assert job > config.experts and bytes(received[L.jobs:L.jobs + L.job_capacity * 96]) == bytes(want)
+    # the routed experts: the oracle on the card's own job table and quantized rows
+    expected = received.copy()
+    at, pairs = L.at, L.pairs
+    gate_up = R.ExpertGateUp(L.jobs, at["codes"], at["exponents"], at["operands"], at["hidden"], I, H, pairs,
+                             config.picks, 7.0, 0)
+    down = R.ExpertDown(L.jobs, at["hidden_codes"], at["hidden_exponents"], at["hidden_operands"], at["pair_output"],
+                        H, I, pairs, 0)
+    oracle.orc_mx_experts(C.byref(gate_up), C.byref(down), L.job_capacity, 2, 2, at["hidden_codes"],
+                          at["hidden_exponents"], at["hidden_operands"], ptr(expected, u8p))
+    live = rows * config.picks
+    out_got = synthetic.from_bfloat16(received[at["pair_output"]:at["pair_output"] + live * H * 2].view(np.uint16))
+    out_want = synthetic.from_bfloat16(expected[at["pair_output"]:at["pair_output"] + live * H * 2].view(np.uint16))
+    assert np.isfinite(out_got).all() and np.abs(out_want).max() > 0
+    assert np.abs(out_got - out_want).max() <= max(2e-2, 2.0 ** -6 * np.abs(out_want).max())
+    # the always-on expert on all rows: the oracle on the same quantized rows
+    S = L.shared_at
+    trunk_gate_up = R.TrunkLinearQuantized((C.c_uint64 * 2)(L.shared_matrices[0], L.shared_matrices[1]),
+                                           (C.c_uint64 * 2)(S["gate_output"], S["up_output"]), at["codes"],
+                                           at["exponents"], at["operands"], (C.c_uint32 * 2)(I, I), H, rows)
+    hidden = R.TrunkHidden(S["gate_output"], S["up_output"], S["hidden"], I, 7.0)
+    requantize = R.ActivationQuantize(S["hidden"], S["hidden_codes"], S["hidden_exponents"], S["hidden_operands"], I, 0)
+    trunk_down = R.TrunkLinearQuantized((C.c_uint64 * 2)(L.shared_matrices[2], 0), (C.c_uint64 * 2)(S["output"], 0),
+                                        S["hidden_codes"], S["hidden_exponents"], S["hidden_operands"],
+                                        (C.c_uint32 * 2)(H, 0), I, rows)
+    (oracle.orc_shared_expert_block128 if block128 else oracle.orc_shared_expert)(
+        C.byref(trunk_gate_up), C.byref(hidden), C.byref(requantize), C.byref(trunk_down), 2, 2, ptr(expected, u8p))
+    joined = synthetic.from_bfloat16(received[S["output"]:S["output"] + rows * H * 2].view(np.uint16)).reshape(rows, H)
+    joined_want = synthetic.from_bfloat16(expected[S["output"]:S["output"] + rows * H * 2].view(np.uint16)).reshape(rows, H)
+    assert np.abs(joined_want).max() > 0
+    assert np.abs(joined - joined_want).max() <= max(2e-2, 2.0 ** -6 * np.abs(joined_want).max())
+    # row sums, the join and the reduction are bit-exact given what the card wrote
+    resummed = np.zeros((rows, H), dtype=np.float32)
+    for slot in range(config.picks):
+        resummed = (resummed + out_got.reshape(rows, config.picks, H)[:, slot, :]).astype(np.float32)
+    resummed = (resummed + joined).astype(np.float32)
+    row_output = received[at["row_output"]:at["row_output"] + rows * H * 4].view(np.float32).reshape(rows, H)
+    assert np.array_equal(resummed.view(np.uint32), row_output.view(np.uint32))
+    assert np.array_equal(result, synthetic.to_bfloat16(np.float32(0.0) + row_output))
