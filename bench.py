@@ -24,6 +24,7 @@ Further objects of the same line, each with its own value, e2e and roofline wher
   prefill            cfg4: the same layer for M = 4096 rows, Zipf(1.1) routing, experts sharded over the ranks,
                      tensor-core (tcgen05) grouped products, ordered reduction with owner runs;
   original_weights   cfg5 decode: MXFP4 routed experts and the E4M3 always-on expert, E4M3 block-quantized activations;
+  original_weights_prefill  cfg5 prefill: the same layer for M = 2048 rows (thin product instances, jobs of eight rows);
   reduction          (N > 1) cfg2: the fixed-order reduction alone, FP32 [M][4096] a rank, M in {1, 8, 64}, in this
                      library's four forms, microseconds a call and NVLink bytes a second;
   reference_kernels  (N = 1) the reference's own EXL3 kernels, recompiled for sm_100a from its sources into oracle/_ref,
@@ -72,6 +73,8 @@ def parse():
     parser.add_argument("--cut", default="0,0",
                         help="runs of K of the decode products (gate/up,down); 0: the library's measured default")
     parser.add_argument("--no-original-weights", action="store_true", help="skip the MXFP4 part")
+    parser.add_argument("--original-prefill-rows", type=int, default=2048,
+                        help="rows of the original-weights prefill (cfg5); 0 skips it")
     parser.add_argument("--no-reduction", action="store_true",
                         help="skip the reduction-alone measurement of runs on two or more GPUs")
     parser.add_argument("--no-reference-kernels", action="store_true",
@@ -644,6 +647,83 @@ def run_original_weights(args, api, base, rank, world, local_rank, dist, barrier
                              "from a pool on the card by a select launch"}}
 
 
+def run_original_weights_prefill(args, api, base, rank, world, local_rank, dist, barrier, maximum):
+    """cfg5 prefill: the same original-weights layer for M = 2048 rows, tensor parallel by intermediate columns. The
+    products are the thin instances (jobs of at most eight rows: every job streams its expert's matrices again, mostly
+    from L2), not yet a tensor-core grouped GEMM: the number says where that stands."""
+    from anemone_b200 import synthetic
+    from anemone_b200.moe import MoeConfig
+    from anemone_b200.mx import MxLayer, MxLayout
+    rows, steps, warmup = args.original_prefill_rows, 3, 2
+    config = MoeConfig(hidden=base.hidden, inner=base.inner, experts=base.experts, shared=1, picks=base.picks,
+                       row_capacity=rows, activation_limit=7.0)
+    layout = MxLayout(config, world, rank, block128=True, wide=True)
+    H, I = config.hidden, layout.inner_local
+    card = api.Card(local_rank, layout.arena_bytes)
+
+    def draw(expert):
+        rng = np.random.default_rng([SEED, 2000 + expert, rank])
+        return (synthetic.mx_matrix(rng, I, H), synthetic.mx_matrix(rng, I, H), synthetic.mx_matrix(rng, H, I))
+    always_rng = np.random.default_rng([SEED, 2999, rank])
+    always = (synthetic.e4m3_block128_matrix(always_rng, I, H), synthetic.e4m3_block128_matrix(always_rng, I, H),
+              synthetic.e4m3_block128_matrix(always_rng, H, I))
+    layer = MxLayer(card, config, (draw(expert) for expert in range(config.experts)), rank=rank, rank_count=world,
+                    slices=(2, 2), shared_matrices=always, block128=True, wide=True)
+    if dist is None:
+        layer.connect_local([layer])
+    else:
+        handles = [None] * world
+        dist.all_gather_object(handles, card.ipc_export())
+        layer.connect_handles(handles)
+    card.wait()
+    barrier()
+    inputs = [prefill_inputs(config, rows, 50 + index) for index in range(2)]
+    # ---- e2e: the public call on host arrays (inputs up, graph, result down, wait) ----
+    for index in range(warmup):
+        layer.step(*inputs[index % 2])
+    barrier()
+    wall_begin = time.perf_counter()
+    for index in range(steps):
+        layer.step(*inputs[index % 2])
+    e2e_ms = maximum(1000.0 * (time.perf_counter() - wall_begin)) / steps
+    barrier()
+    # ---- value: the inputs of the last call wait in the arena; a step's 16-byte block goes up, then the graph is timed
+    device_us = 0.0
+    launches_before = card.launch_count()
+    for _ in range(steps):
+        layer.sequence += 1
+        card.upload(layout.step, np.frombuffer(bytes(R_step(layer.sequence, rows)), dtype=np.uint8))
+        barrier()
+        card.measure_begin()
+        card.graph_run(layer.graph)
+        card.measure_end()
+        device_us += maximum(card.measure_elapsed_us())
+        card.wait()
+    launches = (card.launch_count() - launches_before) // steps
+    layer.check_status()
+    expired = card.expired_bits()
+    barrier()
+    card.close()
+    if expired:
+        raise RuntimeError("a kernel of the original-weights prefill gave up a bounded wait (bits %d)" % expired)
+    device_ms = device_us / 1000.0 / steps
+    return {"value": rows * 1000.0 / device_ms, "unit": "tok/s", "ms_per_step": device_ms, "rows": rows,
+            "steps": steps, "warmup": warmup, "gpu_launches_per_step": int(launches),
+            "e2e": {"value": rows * 1000.0 / e2e_ms, "unit": "tok/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": layout.step_input_bytes, "d2h_bytes_per_step": rows * H * 2},
+            "dtype": "e2m1 x e4m3 -> f32", "jobs": layout.job_capacity,
+            "config": {"workload": "cfg5 original-weights MoE layer prefill: M=%d, %d routed MXFP4 experts, top-%d, 1 "
+                                   "always-on expert E4M3 with one FP32 scale per 128x128 weights, hidden %d, "
+                                   "intermediate %d; thin product instances (jobs of at most eight rows)" %
+                                   (rows, config.experts, config.picks, H, config.inner),
+                       "parallelism": "tp%d by intermediate columns, ordered FP32->bf16 reduce (owner runs)" % world}}
+
+
+def R_step(sequence, rows):
+    from anemone_b200 import records as R
+    return R.StepBlock(sequence, rows, 0)
+
+
 def run_reduction(args, api, hidden, rank, world, local_rank, dist, barrier, maximum):
     """cfg2: the fixed-order reduction ALONE between the ranks: FP32 [M][hidden] a rank, added in rank order, rounded
     once to bfloat16, M in {1, 8, 64}. Four forms of this library: every rank stores its rows into every rank's inbox and adds
@@ -1004,6 +1084,10 @@ def main():
     original = None
     if not args.no_original_weights:
         original = run_original_weights(args, api, config, rank, world, local_rank, dist, barrier, maximum)
+    original_prefill = None
+    if not args.no_original_weights and args.original_prefill_rows:
+        original_prefill = run_original_weights_prefill(args, api, config, rank, world, local_rank, dist, barrier,
+                                                        maximum)
     reduction = None
     if world > 1 and not args.no_reduction:
         reduction = run_reduction(args, api, config.hidden, rank, world, local_rank, dist, barrier, maximum)
@@ -1014,6 +1098,8 @@ def main():
             line["prefill"] = prefill
         if original is not None:
             line["original_weights"] = original
+        if original_prefill is not None:
+            line["original_weights_prefill"] = original_prefill
         if reference_kernels is not None:
             line["reference_kernels"] = reference_kernels
         print(json.dumps(line))

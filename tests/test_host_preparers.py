@@ -389,3 +389,45 @@ def test_layer_prepare_three_launches():
     bad.route.moe.counters_offset = bad.route.moe.base.products_offset  # overlaps the partial sums
     assert lib.exl3_layer_prepare(C.byref(bad), C.byref(fake.table), fake.card, launches) == 1
     assert bytes(launches) == untouched
+
+
+def test_router_wide_prepare():
+    """The job table of many rows: three launches (the prefill's picks and grouping, then router_wide_jobs)."""
+    lib, fake = api.library(), FakeBackend()
+    lib.router_wide_prepare.argtypes = [C.POINTER(R.RouterWide), C.c_uint64, C.POINTER(api.BackendOperations),
+                                        C.c_void_p, C.POINTER(R.KernelLaunch)]
+    rows, experts, picks, hidden, inner = 2048, 256, 8, 4096, 256
+
+    def arguments(**changes):
+        layout = api.Layout(256)
+        routing = R.Exl3Prefill()
+        routing.scores_offset, routing.expert_table_offset = layout.take(rows * experts * 4), layout.take(experts * 24)
+        routing.picks_offset, routing.weights_offset = layout.take(rows * picks * 4), layout.take(rows * picks * 4)
+        parts = api.prefill_parts(rows, picks, 0, experts, hidden, inner)
+        routing.workspace_offset, routing.step_offset = layout.take(parts.gate_up_operands, 1024), layout.take(16)
+        routing.input_size, routing.inner_size, routing.expert_count, routing.local_count = hidden, inner, experts, experts
+        routing.picks, routing.row_capacity, routing.scoring, routing.route_scale = picks, rows, 0, 1.0
+        value = R.RouterWide(routing, layout.take((rows * picks // 8 + experts) * 96), rows * picks // 8 + experts, 0)
+        for name, change in changes.items():
+            if hasattr(value, name):
+                setattr(value, name, change)
+            else:
+                setattr(value.routing, name, change)
+        return value, layout.take(0, 4096) + 4096
+    value, arena = arguments()
+    launches = (R.KernelLaunch * R.ROUTER_WIDE_LAUNCHES)()
+    assert lib.router_wide_prepare(C.byref(value), arena, C.byref(fake.table), fake.card, launches) == 0
+    assert fake.asked == [("kernel_exl3_prefill", "exl3_prefill_picks", 136), ("kernel_exl3_prefill", "exl3_prefill_group", 136),
+                          ("kernel_router_b200", "router_wide_jobs", 152)]
+    assert [tuple(l.grid) for l in launches] == [(rows // 32, 1, 1), (experts, 1, 1), (1, 1, 1)]
+    assert [l.block[0] for l in launches] == [1024, 256, 1024]
+    assert bytes(launches[2].argument[:152]) == bytes(value) and bytes(launches[0].argument[:136]) == bytes(value.routing)
+    untouched = bytes(launches)
+    for change in (dict(job_capacity=rows * picks // 8 + experts - 1), dict(shared_count=1), dict(local_first=1),
+                   dict(local_count=experts - 1), dict(picks=17), dict(expert_count=513), dict(row_capacity=0),
+                   dict(route_scale=0.0), dict(scoring=2), dict(reserved_zero=1), dict(jobs_offset=8),
+                   dict(workspace_offset=256 + 512)):
+        bad, size = arguments(**change)
+        assert lib.router_wide_prepare(C.byref(bad), size, C.byref(fake.table), fake.card, launches) == 1, change
+        assert bytes(launches) == untouched
+    assert lib.router_wide_prepare(C.byref(value), arena - 8192, C.byref(fake.table), fake.card, launches) == 1
