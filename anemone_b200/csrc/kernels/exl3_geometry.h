@@ -41,8 +41,7 @@ AB_INLINE uint32_t exl3_moe_splits(uint32_t inputs, uint32_t outputs)
 	return splits;
 }
 
-/* ---- the decode step's four launches (kernel_exl3_layer) ---- */
-#define EXL3_LAYER_PRODUCT_CTAS_PER_SM 5u /* resident product CTAs of 128 threads at their register count */
+/* ---- the decode step's three launches (kernel_exl3_layer) ---- */
 #define EXL3_LAYER_DEFAULT_SMS 148u
 #define EXL3_LAYER_WORD_LIVE_JOBS 0u
 #define EXL3_LAYER_WORD_TICKET 1u /* the next item of the products' list; zero between steps */
@@ -67,14 +66,14 @@ AB_INLINE uint64_t exl3_layer_counter_begin(uint32_t job_count, uint32_t input_s
 
 /* bytes at counters_offset in the layer form: the per-(job, group) counters, then the layer's words, then a word a
  * job: how many groups of 128 inner channels of the job have their down operands in place (the router's launch
- * zeroes them, the gate/up launch counts, the down launch, which may begin before the gate/up launch ends, reads) */
+ * zeroes them, the gate and up items count, the down items, which run beside the last of those, read) */
 AB_INLINE uint64_t exl3_layer_counter_bytes(uint32_t job_count, uint32_t input_size, uint32_t inner_size)
 {
 	return (exl3_layer_counter_begin(job_count, input_size, inner_size) + EXL3_LAYER_COUNTER_WORDS + job_count) * 4u;
 }
 
-/* the FP32 partial sums of the layer form: gate/up's [2][runs][pairs][inner], then, in a range of their own (the down
- * launch may write while the gate/up launch still reads), down's [runs][pairs][input] */
+/* the FP32 partial sums of the layer form: gate/up's [2][runs][pairs][inner], then, in a range of their own (down
+ * items write while gate and up items still read), down's [runs][pairs][input] */
 AB_INLINE uint64_t exl3_layer_gate_up_product_bytes(uint32_t pair_count, uint32_t inner_size)
 {
 	return (uint64_t)EXL3_PROJECTIONS * EXL3_LAYER_MAXIMUM_RUNS * pair_count * inner_size * 4u;
