@@ -1086,8 +1086,11 @@ def main():
         original = run_original_weights(args, api, config, rank, world, local_rank, dist, barrier, maximum)
     original_prefill = None
     if not args.no_original_weights and args.original_prefill_rows:
-        original_prefill = run_original_weights_prefill(args, api, config, rank, world, local_rank, dist, barrier,
-                                                        maximum)
+        try:
+            original_prefill = run_original_weights_prefill(args, api, config, rank, world, local_rank, dist, barrier,
+                                                            maximum)
+        except Exception as error:  # a secondary object of the line: it must not take the line with it
+            original_prefill = {"error": "%s: %s" % (type(error).__name__, error)}
     reduction = None
     if world > 1 and not args.no_reduction:
         reduction = run_reduction(args, api, config.hidden, rank, world, local_rank, dist, barrier, maximum)
