@@ -446,3 +446,84 @@ def test_wide_layer_matches_oracle(api, oracle, block128):
     row_output = received[at["row_output"]:at["row_output"] + rows * H * 4].view(np.float32).reshape(rows, H)
     assert np.array_equal(resummed.view(np.uint32), row_output.view(np.uint32))
     assert np.array_equal(result, synthetic.to_bfloat16(np.float32(0.0) + row_output))
+
+
+def test_layer_at_the_configured_shapes(api, oracle):
+    """The original-weights layer at the configured shapes (256 MXFP4 routed experts, top-8, hidden 4096, intermediate
+    2048, the always-on expert E4M3 with 128 x 128 FP32 scales, 8 rows) against the oracle: the card's own picks, job
+    table and quantized rows, then the oracle's experts on an image that holds the matrices of the experts a job
+    names (the others are never read)."""
+    from anemone_b200.moe import MoeConfig
+    from anemone_b200.mx import MxLayer, MxLayout
+    from oracle import moe_reference
+    config = MoeConfig(hidden=4096, inner=2048, experts=256, shared=1, picks=8, row_capacity=8, activation_limit=7.0)
+    rng = np.random.default_rng(555)
+    H, I, rows = config.hidden, config.inner, 8
+    tokens = synthetic.tokens(rng, rows, H)
+    scores = rng.normal(0, 1, size=(rows, config.experts)).astype(np.float32)
+    experts, weights = moe_reference.route(oracle, config, scores)
+    active = set(experts.reshape(-1).tolist())
+    filler = (synthetic.mx_matrix(rng, I, H), synthetic.mx_matrix(rng, I, H), synthetic.mx_matrix(rng, H, I))
+    matrices = [(synthetic.mx_matrix(rng, I, H), synthetic.mx_matrix(rng, I, H), synthetic.mx_matrix(rng, H, I))
+                if expert in active else filler for expert in range(config.experts)]
+    always = (synthetic.e4m3_block128_matrix(rng, I, H), synthetic.e4m3_block128_matrix(rng, I, H),
+              synthetic.e4m3_block128_matrix(rng, H, I))
+    L = MxLayout(config, 1, 0, block128=True)
+    card = api.Card(0, L.arena_bytes)
+    at, S = L.at, L.shared_at
+    try:
+        layer = MxLayer(card, config, matrices, slices=(4, 4), shared_matrices=always, block128=True)
+        layer.connect_local([layer])
+        result = layer.step(tokens, scores)
+        expected = np.zeros(L.arena_bytes, dtype=np.uint8)  # pages are taken as they are written
+        for offset, size in [(L.picks, rows * config.picks * 4), (L.jobs, L.job_capacity * 96)] + \
+                [(at[name], L.sizes[name]) for name in L.sizes] + [(S[name], L.shared_sizes[name]) for name in S]:
+            expected[offset:offset + size] = card.download(offset, size)
+        received = {name: expected[at[name]:at[name] + L.sizes[name]].copy() for name in ("pair_output", "row_output")}
+        joined_bits = expected[S["output"]:S["output"] + rows * H * 2].copy()
+    finally:
+        card.close()
+    picks = expected[L.picks:L.picks + rows * config.picks * 4].view(np.uint32).reshape(rows, config.picks)
+    assert np.array_equal(picks, experts)
+    for expert in active:
+        for which in range(3):
+            data = matrices[expert][which]
+            expected[L.matrices[expert][which]:L.matrices[expert][which] + data.size] = data
+    for which in range(3):
+        expected[L.shared_matrices[which]:L.shared_matrices[which] + always[which].size] = always[which]
+    pairs = L.pairs
+    gate_up = R.ExpertGateUp(L.jobs, at["codes"], at["exponents"], at["operands"], at["hidden"], I, H, pairs,
+                             config.picks, 7.0, 0)
+    down = R.ExpertDown(L.jobs, at["hidden_codes"], at["hidden_exponents"], at["hidden_operands"], at["pair_output"],
+                        H, I, pairs, 0)
+    oracle.orc_mx_experts(C.byref(gate_up), C.byref(down), L.job_capacity, 4, 4, at["hidden_codes"],
+                          at["hidden_exponents"], at["hidden_operands"], ptr(expected, u8p))
+    out_got = synthetic.from_bfloat16(received["pair_output"].view(np.uint16))
+    out_want = synthetic.from_bfloat16(expected[at["pair_output"]:at["pair_output"] + pairs * H * 2].view(np.uint16))
+    assert np.isfinite(out_got).all() and np.abs(out_want).max() > 0
+    assert np.abs(out_got - out_want).max() <= max(2e-2, 2.0 ** -6 * np.abs(out_want).max())
+    cosine = float(out_got.astype(np.float64) @ out_want.astype(np.float64) /
+                   (np.linalg.norm(out_got) * np.linalg.norm(out_want)))
+    assert cosine >= 0.9999
+    # the always-on expert
+    trunk_gate_up = R.TrunkLinearQuantized((C.c_uint64 * 2)(L.shared_matrices[0], L.shared_matrices[1]),
+                                           (C.c_uint64 * 2)(S["gate_output"], S["up_output"]), at["codes"],
+                                           at["exponents"], at["operands"], (C.c_uint32 * 2)(I, I), H, rows)
+    hidden = R.TrunkHidden(S["gate_output"], S["up_output"], S["hidden"], I, 7.0)
+    requantize = R.ActivationQuantize(S["hidden"], S["hidden_codes"], S["hidden_exponents"], S["hidden_operands"], I, 0)
+    trunk_down = R.TrunkLinearQuantized((C.c_uint64 * 2)(L.shared_matrices[2], 0), (C.c_uint64 * 2)(S["output"], 0),
+                                        S["hidden_codes"], S["hidden_exponents"], S["hidden_operands"],
+                                        (C.c_uint32 * 2)(H, 0), I, rows)
+    oracle.orc_shared_expert_block128(C.byref(trunk_gate_up), C.byref(hidden), C.byref(requantize),
+                                      C.byref(trunk_down), 2, 2, ptr(expected, u8p))
+    joined = synthetic.from_bfloat16(joined_bits.view(np.uint16)).reshape(rows, H)
+    joined_want = synthetic.from_bfloat16(expected[S["output"]:S["output"] + rows * H * 2].view(np.uint16)).reshape(rows, H)
+    assert np.abs(joined - joined_want).max() <= max(2e-2, 2.0 ** -6 * np.abs(joined_want).max())
+    # row sums, the join and the reduction: bit for bit given what the card wrote
+    resummed = np.zeros((rows, H), dtype=np.float32)
+    for slot in range(config.picks):
+        resummed = (resummed + out_got.reshape(rows, config.picks, H)[:, slot, :]).astype(np.float32)
+    resummed = (resummed + joined).astype(np.float32)
+    row_output = received["row_output"].view(np.float32).reshape(rows, H)
+    assert np.array_equal(resummed.view(np.uint32), row_output.view(np.uint32))
+    assert np.array_equal(result, synthetic.to_bfloat16(np.float32(0.0) + row_output))

@@ -267,6 +267,13 @@ def test_prefill_full_size_properties(api):
         card.close()
     scale = max(float(np.abs(decode_rows).max()), 1.0)
     assert np.abs(first[:8] - decode_rows).max() <= 2e-3 * scale and cosine(first[:8], decode_rows) >= 0.99999
+    # (4) the CPU oracle on a sample of the call's rows (a row's result does not depend on the others, (1)): the FP32
+    # rows of the prefill launches at the configured shapes within the layer's tolerance
+    sample = np.array([0, 1, 2, 1000, 2047, 2048, 4000, 4095])
+    from oracle import binding
+    wanted = moe_reference.layer(binding.load_oracle(), small, widths, matrices, tokens[sample], scores[sample], 1)[1][0]
+    wanted = np.asarray(wanted, dtype=np.float32).reshape(len(sample), config.hidden)
+    assert np.abs(first[sample] - wanted).max() <= 2e-2 and cosine(first[sample], wanted) >= 0.9999
 
 
 def test_prefill_empty_and_full_calls(api, oracle):
