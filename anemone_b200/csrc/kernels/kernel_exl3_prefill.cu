@@ -5,9 +5,10 @@
  * model's shapes and to mma.sync; here a CTA
  *   - streams the row tile's FP16 operand blocks (pre-tiled in the tensor cores' no-swizzle K-major layout) into a ring
  *     of shared-memory stages by bulk asynchronous copies (one warp),
- *   - loads the trellis words of its outputs straight from global memory into registers one stage ahead, decodes them
- *     in registers into FP16 and stores them as the B operand block of the stage (sixteen warps; the decode's fragment
- *     order makes every store a contiguous 128 bytes of the block); two row tiles of one expert share one decode,
+ *   - streams the trellis words of its outputs into a second ring by bulk copies a whole turn of the ring ahead,
+ *     decodes them in registers into FP16 and stores them as the B operand block of the stage (sixteen warps in four
+ *     teams, a team a stage; the decode's fragment order makes every store a contiguous 128 bytes of the block); two
+ *     row tiles of one expert share one decode,
  *   - multiplies with tcgen05.mma (one thread), FP32 accumulators in tensor memory, the stage released by
  *     tcgen05.commit,
  *   - reads the accumulators back with tcgen05.ld and applies the chain's FP32 epilogue (exl3_passes.cuh: Hadamard,
