@@ -234,6 +234,51 @@ result_status linear_routed_experts_prepare(const struct linear_routed_experts_d
 	return STATUS_OK;
 }
 
+/* The routed experts for a job table of MANY rows: linear_routed_experts_prepare's four launches with the two product
+ * launches given to expert_gate_up_many and expert_down_many (a group of LINEAR_MANY_JOBS jobs and several tiles a
+ * block; the slice counts travel in the argument records, so every slice count the thin instances have is accepted). */
+result_status linear_routed_experts_wide_prepare(const struct linear_routed_experts_description *description,
+						 uint64_t arena_byte_count, const struct linear_kernels_record *kernels,
+						 const struct backend_operations *backend, struct device_card *card,
+						 struct kernel_launch *launches_out)
+{
+	if (backend == NULL || backend->kernel_prepare == NULL || card == NULL)
+		return STATUS_INVALID_ARGUMENT;
+	struct kernel_launch launches[LINEAR_ROUTED_EXPERTS_LAUNCH_COUNT];
+	result_status status = linear_routed_experts_prepare(description, arena_byte_count, kernels, launches);
+	if (status != STATUS_OK)
+		return status;
+	const uint32_t H = description->gate_up_shape.input_size, I = description->gate_up_shape.output_size;
+	/* whole blocks of four tiles of gate and up, of eight tiles of down */
+	if (I % (4u * LINEAR_OUTPUTS_PER_TILE) != 0 || H % (8u * LINEAR_OUTPUTS_PER_TILE) != 0)
+		return STATUS_INVALID_ARGUMENT;
+	uint32_t gate_up = BACKEND_NO_KERNEL, down = BACKEND_NO_KERNEL;
+	status = backend->kernel_prepare(card, KERNEL_FILE_EXPERT_LINEAR, KERNEL_EXPERT_GATE_UP_MANY,
+					 sizeof(struct expert_gate_up_many_arguments), &gate_up);
+	if (status == STATUS_OK)
+		status = backend->kernel_prepare(card, KERNEL_FILE_EXPERT_LINEAR, KERNEL_EXPERT_DOWN_MANY,
+						 sizeof(struct expert_down_many_arguments), &down);
+	if (status != STATUS_OK)
+		return status;
+	if (gate_up == BACKEND_NO_KERNEL || down == BACKEND_NO_KERNEL)
+		return STATUS_UNSUPPORTED;
+	struct expert_gate_up_many_arguments gate_up_arguments;
+	struct expert_down_many_arguments down_arguments;
+	memcpy(&gate_up_arguments.base, launches[LINEAR_ROUTED_EXPERTS_GATE_UP].argument, sizeof(gate_up_arguments.base));
+	memcpy(&down_arguments.base, launches[LINEAR_ROUTED_EXPERTS_DOWN].argument, sizeof(down_arguments.base));
+	gate_up_arguments.slice_count = description->gate_up_slice_count;
+	gate_up_arguments.job_count = description->job_count;
+	down_arguments.slice_count = description->down_slice_count;
+	down_arguments.job_count = description->job_count;
+	const uint32_t groups = (description->job_count + LINEAR_MANY_JOBS - 1u) / LINEAR_MANY_JOBS;
+	prepare_launch_fill(&launches[LINEAR_ROUTED_EXPERTS_GATE_UP], gate_up, I / (4u * LINEAR_OUTPUTS_PER_TILE), groups, 1,
+			    256, 0, &gate_up_arguments, sizeof(gate_up_arguments));
+	prepare_launch_fill(&launches[LINEAR_ROUTED_EXPERTS_DOWN], down, H / (8u * LINEAR_OUTPUTS_PER_TILE), groups, 1, 256,
+			    0, &down_arguments, sizeof(down_arguments));
+	memcpy(launches_out, launches, sizeof(launches));
+	return STATUS_OK;
+}
+
 static result_status e4m3_stored_byte_count(const struct matrix_shape_record *shape, uint64_t *byte_count_out)
 {
 	if (shape == NULL || byte_count_out == NULL || shape->reserved_must_be_zero != 0 || shape->bits_per_weight != 8 ||

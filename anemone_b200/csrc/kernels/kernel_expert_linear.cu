@@ -236,6 +236,264 @@ EXPERT_ENTRIES(4)
 EXPERT_ENTRIES(8)
 EXPERT_ENTRIES(16)
 
+/* ------------------------------------------------------------------ many rows: a group of jobs a block
+ *
+ * expert_gate_up_many / expert_down_many: the same products for a job table of many rows. A warp owns one tile of 16
+ * outputs for ALL of K and for up to LINEAR_MANY_JOBS consecutive jobs of one expert: it places a load's words once
+ * and multiplies them with every job's columns; a job's slices are walked one after the other (a slice one chain, the
+ * chains added from +0 in ascending order), so every value goes through the thin instances' operations in their order.
+ * The warps of a block take neighbouring tiles and the same jobs: the rows' operands come from L2 once a block. */
+
+/* The chains of R jobs over one slice of one tile. fed[r], exponents_even[r], exponents_odd[r]: as slice_chains'
+ * fed, exponents_even, exponents_odd, of job r. */
+template <uint32_t R>
+__device__ __forceinline__ void slice_chains_many(const unsigned char *matrix, uint32_t outputs, uint32_t inputs,
+						   uint32_t tile, uint32_t first_load, uint32_t last_load,
+						   const uint4 *const (&fed)[R], const unsigned char *const (&exponents_even)[R],
+						   const unsigned char *const (&exponents_odd)[R], float (&chains)[R][4])
+{
+	const uint32_t lane = threadIdx.x % WARP, group = lane / 4u;
+	const uint32_t loads = inputs / LINEAR_VALUES_PER_LOAD;
+	const uint4 *const words = reinterpret_cast<const uint4 *>(matrix) + ((uint64_t)tile * loads) * WARP + lane;
+	const uint32_t *const scales =
+		reinterpret_cast<const uint32_t *>(matrix + (uint64_t)outputs * inputs / 2u) + (uint64_t)tile * loads * 8u + group;
+#pragma unroll
+	for (uint32_t r = 0; r < R; r++)
+		chains[r][0] = chains[r][1] = chains[r][2] = chains[r][3] = 0.0f;
+	if (first_load >= last_load)
+		return;
+	uint4 ahead_words[EXPERT_AHEAD];
+	uint32_t ahead_scales[EXPERT_AHEAD];
+#pragma unroll
+	for (uint32_t slot = 0; slot < EXPERT_AHEAD; slot++)
+		if (first_load + slot < last_load) {
+			ahead_words[slot] = __ldcs(words + (uint64_t)(first_load + slot) * WARP);
+			ahead_scales[slot] = __ldcs(scales + (uint64_t)(first_load + slot) * 8u);
+		}
+	for (uint32_t base = first_load; base < last_load; base += EXPERT_AHEAD) {
+#pragma unroll
+		for (uint32_t slot = 0; slot < EXPERT_AHEAD; slot++) {
+			const uint32_t load = base + slot;
+			if (load >= last_load)
+				break;
+			const uint4 current = ahead_words[slot];
+			const uint32_t scale_word = ahead_scales[slot];
+			if (load + EXPERT_AHEAD < last_load) {
+				ahead_words[slot] = __ldcs(words + (uint64_t)(load + EXPERT_AHEAD) * WARP);
+				ahead_scales[slot] = __ldcs(scales + (uint64_t)(load + EXPERT_AHEAD) * 8u);
+			}
+			const uint32_t step_words[4] = { current.x, current.y, current.z, current.w };
+			uint32_t a[4][4];
+#pragma unroll
+			for (uint32_t step = 0; step < 4u; step++) {
+				a[step][0] = place_e2m1<0>(step_words[step]);
+				a[step][1] = place_e2m1<1>(step_words[step]);
+				a[step][2] = place_e2m1<2>(step_words[step]);
+				a[step][3] = place_e2m1<3>(step_words[step]);
+			}
+#pragma unroll
+			for (uint32_t r = 0; r < R; r++) {
+				const uint4 fed_low = __ldg(fed[r] + (uint64_t)load * 8u), fed_high = __ldg(fed[r] + (uint64_t)load * 8u + 1u);
+				const uint32_t fed_registers[8] = { fed_low.x, fed_low.y, fed_low.z, fed_low.w,
+								    fed_high.x, fed_high.y, fed_high.z, fed_high.w };
+				const uint32_t even = *reinterpret_cast<const uint16_t *>(exponents_even[r] + 2u * load);
+				const uint32_t odd = *reinterpret_cast<const uint16_t *>(exponents_odd[r] + 2u * load);
+#pragma unroll
+				for (uint32_t q = 0; q < 2u; q++) {
+					float sum[4] = { 0.0f, 0.0f, 0.0f, 0.0f };
+#pragma unroll
+					for (uint32_t half = 0; half < 2u; half++) {
+						const uint32_t step = 2u * q + half;
+						mma_f16(sum, a[step], fed_registers[2u * step], fed_registers[2u * step + 1u]);
+					}
+					const uint32_t low_row = (scale_word >> (16u * q)) & 0xFFu,
+						       high_row = (scale_word >> (16u * q + 8u)) & 0xFFu;
+					const uint32_t even_code = (even >> (8u * q)) & 0xFFu, odd_code = (odd >> (8u * q)) & 0xFFu;
+					chains[r][0] = __fmaf_rn(sum[0], block_scale(low_row, even_code), chains[r][0]);
+					chains[r][1] = __fmaf_rn(sum[1], block_scale(low_row, odd_code), chains[r][1]);
+					chains[r][2] = __fmaf_rn(sum[2], block_scale(high_row, even_code), chains[r][2]);
+					chains[r][3] = __fmaf_rn(sum[3], block_scale(high_row, odd_code), chains[r][3]);
+				}
+			}
+		}
+	}
+}
+
+/* the sums of R jobs for one tile of one matrix: every slice's chains, added from +0 in ascending order. vectors: the
+ * divisor that makes a pair index a vector of the operand arrays (pairs_per_row for gate/up, 1 for down) */
+template <uint32_t R>
+__device__ __forceinline__ void sums_many(const unsigned char *matrix, uint32_t outputs, uint32_t inputs, uint32_t tile,
+					   uint32_t slices, const struct expert_job_record *jobs, uint32_t vectors,
+					   const unsigned char *operands, const unsigned char *exponents, float (&totals)[R][4])
+{
+	const uint32_t lane = threadIdx.x % WARP, group = lane / 4u, place = lane % 4u;
+	const uint32_t loads = inputs / LINEAR_VALUES_PER_LOAD;
+	const uint4 *fed[R];
+	const unsigned char *even[R], *odd[R];
+#pragma unroll
+	for (uint32_t r = 0; r < R; r++) {
+		fed[r] = reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(operands) +
+							 (uint64_t)(column_pair(&jobs[r], group) / vectors) * inputs) +
+			 place * 2u;
+		even[r] = exponents + (uint64_t)(column_pair(&jobs[r], 2u * place) / vectors) * (inputs / 32u);
+		odd[r] = exponents + (uint64_t)(column_pair(&jobs[r], 2u * place + 1u) / vectors) * (inputs / 32u);
+		totals[r][0] = totals[r][1] = totals[r][2] = totals[r][3] = 0.0f;
+	}
+	for (uint32_t slice = 0; slice < slices; slice++) {
+		float chains[R][4];
+		slice_chains_many<R>(matrix, outputs, inputs, tile, loads * slice / slices, loads * (slice + 1u) / slices, fed,
+				     even, odd, chains);
+#pragma unroll
+		for (uint32_t r = 0; r < R; r++)
+#pragma unroll
+			for (uint32_t c = 0; c < 4; c++)
+				totals[r][c] = __fadd_rn(totals[r][c], chains[r][c]);
+	}
+}
+
+#define MANY_GATE_UP_TILES 4u /* tiles of 16 outputs of a block, of gate and of up */
+#define MANY_DOWN_TILES 8u
+
+template <uint32_t R>
+__device__ __forceinline__ void gate_up_many(const struct expert_gate_up_many_arguments &many, unsigned char *arena,
+					     const struct expert_job_record *jobs,
+					     float (&parts)[MANY_GATE_UP_TILES][LINEAR_MANY_JOBS][WARP][4])
+{
+	const struct expert_gate_up_arguments &arguments = many.base;
+	const uint32_t lane = threadIdx.x % WARP, warp = threadIdx.x / WARP, group = lane / 4u, place = lane % 4u;
+	const uint32_t which = warp / MANY_GATE_UP_TILES, mine = warp % MANY_GATE_UP_TILES;
+	const uint32_t tile = blockIdx.x * MANY_GATE_UP_TILES + mine;
+	float totals[R][4];
+	sums_many<R>(arena + (which == 0 ? jobs[0].gate_offset : jobs[0].up_offset), arguments.output_size,
+		     arguments.input_size, tile, many.slice_count, jobs, arguments.pairs_per_row,
+		     arena + arguments.operands_offset, arena + arguments.exponents_offset, totals);
+	__syncthreads(); /* the run before this one has read its parts */
+	if (which == 1u) {
+#pragma unroll
+		for (uint32_t r = 0; r < R; r++)
+#pragma unroll
+			for (uint32_t c = 0; c < 4; c++)
+				parts[mine][r][lane][c] = totals[r][c];
+	}
+	__syncthreads();
+	if (which != 0u)
+		return;
+	uint16_t *const hidden = reinterpret_cast<uint16_t *>(arena + arguments.hidden_offset);
+#pragma unroll
+	for (uint32_t r = 0; r < R; r++)
+#pragma unroll
+		for (uint32_t c = 0; c < 4; c++) {
+			const uint32_t column = 2u * place + (c & 1u);
+			if (column >= jobs[r].row_count)
+				continue;
+			/* gate and up are bfloat16 first, as the reference's linear returns them */
+			const float g = bfloat16_value(bfloat16_bits(totals[r][c])),
+				    u = bfloat16_value(bfloat16_bits(parts[mine][r][lane][c]));
+			const float limit = arguments.activation_limit;
+			const float bounded_gate = g > limit ? limit : g;
+			const float bounded_up = u > limit ? limit : (u < -limit ? -limit : u);
+			const float gated = __fdiv_rn(bounded_gate, __fadd_rn(1.0f, expf(-bounded_gate)));
+			const float value = __fmul_rn(__fmul_rn(gated, bounded_up), jobs[r].route_weight[column]);
+			hidden[(uint64_t)jobs[r].pair_index[column] * arguments.output_size + tile * LINEAR_OUTPUTS_PER_TILE + group +
+			       (c >> 1) * 8u] = (uint16_t)bfloat16_bits(value);
+		}
+}
+
+template <uint32_t R>
+__device__ __forceinline__ void down_many(const struct expert_down_many_arguments &many, unsigned char *arena,
+					  const struct expert_job_record *jobs)
+{
+	const struct expert_down_arguments &arguments = many.base;
+	const uint32_t lane = threadIdx.x % WARP, warp = threadIdx.x / WARP, group = lane / 4u, place = lane % 4u;
+	const uint32_t tile = blockIdx.x * MANY_DOWN_TILES + warp;
+	float totals[R][4];
+	sums_many<R>(arena + jobs[0].down_offset, arguments.output_size, arguments.input_size, tile, many.slice_count, jobs, 1u,
+		     arena + arguments.operands_offset, arena + arguments.exponents_offset, totals);
+	uint16_t *const output = reinterpret_cast<uint16_t *>(arena + arguments.output_offset);
+#pragma unroll
+	for (uint32_t r = 0; r < R; r++)
+#pragma unroll
+		for (uint32_t c = 0; c < 4; c++) {
+			const uint32_t column = 2u * place + (c & 1u);
+			if (column >= jobs[r].row_count)
+				continue;
+			output[(uint64_t)jobs[r].pair_index[column] * arguments.output_size + tile * LINEAR_OUTPUTS_PER_TILE + group +
+			       (c >> 1) * 8u] = (uint16_t)bfloat16_bits(totals[r][c]);
+		}
+}
+
+/* the jobs of the block's group from `first` that are live and of one expert (at most LINEAR_MANY_JOBS - first) */
+__device__ __forceinline__ uint32_t many_run(const struct expert_job_record *jobs, uint32_t first, uint32_t count)
+{
+	uint32_t run = 0;
+	while (first + run < count && jobs[first + run].row_count != 0 && jobs[first + run].expert == jobs[first].expert)
+		run++;
+	return run;
+}
+
+#if LINEAR_MANY_JOBS >= 3
+#define MANY_CASE_3(call) \
+	case 3:           \
+		call(3);  \
+		break;
+#else
+#define MANY_CASE_3(call)
+#endif
+#if LINEAR_MANY_JOBS >= 4
+#define MANY_CASE_4(call) \
+	case 4:           \
+		call(4);  \
+		break;
+#else
+#define MANY_CASE_4(call)
+#endif
+#define MANY_RUNS(call)                                                                  \
+	const uint32_t first_job = blockIdx.y * LINEAR_MANY_JOBS;                         \
+	const struct expert_job_record *const group_jobs =                                \
+		reinterpret_cast<const struct expert_job_record *>(arena + many.base.jobs_offset) + first_job; \
+	const uint32_t count = min(LINEAR_MANY_JOBS, many.job_count - first_job);         \
+	for (uint32_t first = 0; first < count;) {                                        \
+		const uint32_t run = many_run(group_jobs, first, count);                  \
+		const struct expert_job_record *const jobs = group_jobs + first;          \
+		switch (run) {                                                            \
+		case 0:                                                                   \
+			first++; /* an empty job */                                       \
+			break;                                                            \
+		case 1:                                                                   \
+			call(1);                                                          \
+			break;                                                            \
+		case 2:                                                                   \
+			call(2);                                                          \
+			break;                                                            \
+		MANY_CASE_3(call)                                                         \
+		MANY_CASE_4(call)                                                         \
+		default:                                                                  \
+			break;                                                            \
+		}                                                                         \
+		first += run;                                                             \
+	}
+
+extern "C" __global__ void __launch_bounds__(2u * MANY_GATE_UP_TILES * WARP, 2)
+	expert_gate_up_many(struct expert_gate_up_many_arguments many, unsigned char *arena)
+{
+	__shared__ float parts[MANY_GATE_UP_TILES][LINEAR_MANY_JOBS][WARP][4];
+	if (blockIdx.y * LINEAR_MANY_JOBS >= many.job_count)
+		return;
+#define MANY_CALL(R) gate_up_many<R>(many, arena, jobs, parts)
+	MANY_RUNS(MANY_CALL)
+#undef MANY_CALL
+}
+
+extern "C" __global__ void __launch_bounds__(MANY_DOWN_TILES * WARP, 2)
+	expert_down_many(struct expert_down_many_arguments many, unsigned char *arena)
+{
+	if (blockIdx.y * LINEAR_MANY_JOBS >= many.job_count)
+		return;
+#define MANY_CALL(R) down_many<R>(many, arena, jobs)
+	MANY_RUNS(MANY_CALL)
+#undef MANY_CALL
+}
+
 extern "C" __global__ void expert_row_sum_entry(struct expert_row_sum_arguments arguments, unsigned char *arena)
 {
 	const uint32_t channel = blockIdx.x * blockDim.x + threadIdx.x;

@@ -10,8 +10,9 @@ EXL3 decode layer; the ranks' FP32 rows are added in rank order and rounded once
 
 wide=True is the same layer for MANY rows (the profile's prefill): the router's launch gives way to the three of
 router_wide_prepare (the prefill's picks and grouping, then a job table of eight rows a job), the always-on expert to
-linear_shared_expert_wide_prepare (a block column per eight rows), and the reduction adds by owner runs. The expert
-launches are the same thin instances: every job streams its expert's matrices again (mostly from L2).
+linear_shared_expert_wide_prepare (a block column per eight rows), and the reduction adds by owner runs. The routed
+experts' products are linear_routed_experts_wide_prepare's (a group of jobs and several tiles a block, the thin
+instances' arithmetic; many=False keeps the thin instances, where every job streams its expert's matrices again).
 """
 import ctypes as C
 
@@ -93,7 +94,7 @@ class MxLayout:
 
 class MxLayer:
     def __init__(self, card, config, matrices, rank=0, rank_count=1, slices=(4, 4), shared_matrices=None,
-                 shared_slices=(2, 2), pool_entries=0, block128=False, wide=False):
+                 shared_slices=(2, 2), pool_entries=0, block128=False, wide=False, many=True):
         """matrices: iterable over the routed experts of this rank's (gate, up, down) stored MXFP4 bytes;
         shared_matrices: the always-on expert's (gate, up, down) stored E4M3 bytes, where the configuration has one:
         WEIGHT_FORMAT_E4M3_SCALED, or with block128 WEIGHT_FORMAT_E4M3_BLOCK128 (one FP32 scale per 128 by 128)."""
@@ -173,9 +174,18 @@ class MxLayer:
         description.gate_up_slice_count, description.down_slice_count = slices
         lib.linear_routed_experts_prepare.argtypes = [C.POINTER(R.LinearRoutedExpertsDescription), C.c_uint64,
                                                       C.POINTER(R.LinearKernels), C.POINTER(R.KernelLaunch)]
+        lib.linear_routed_experts_wide_prepare.argtypes = [C.POINTER(R.LinearRoutedExpertsDescription), C.c_uint64,
+                                                           C.POINTER(R.LinearKernels),
+                                                           C.POINTER(api.BackendOperations), C.c_void_p,
+                                                           C.POINTER(R.KernelLaunch)]
         self.expert_launches = (R.KernelLaunch * 4)()
-        api.check(lib.linear_routed_experts_prepare(C.byref(description), card.arena_bytes, C.byref(kernels),
-                                                    self.expert_launches), "linear_routed_experts_prepare")
+        if wide and many:
+            api.check(lib.linear_routed_experts_wide_prepare(C.byref(description), card.arena_bytes, C.byref(kernels),
+                                                             card.ops_pointer, card.handle, self.expert_launches),
+                      "linear_routed_experts_wide_prepare")
+        else:
+            api.check(lib.linear_routed_experts_prepare(C.byref(description), card.arena_bytes, C.byref(kernels),
+                                                        self.expert_launches), "linear_routed_experts_prepare")
         shared_launches = []
         if c.shared:
             shared = R.LinearSharedExpertDescription()

@@ -272,6 +272,17 @@ class ExpertDown(C.Structure):
                 ("input_size", C.c_uint32), ("pair_count", C.c_uint32), ("reserved_zero", C.c_uint32)]
 
 
+LINEAR_MANY_JOBS = 2
+
+
+class ExpertGateUpMany(C.Structure):
+    _fields_ = [("base", ExpertGateUp), ("slice_count", C.c_uint32), ("job_count", C.c_uint32)]
+
+
+class ExpertDownMany(C.Structure):
+    _fields_ = [("base", ExpertDown), ("slice_count", C.c_uint32), ("job_count", C.c_uint32)]
+
+
 class LinearRange(C.Structure):
     _fields_ = [("byte_offset", C.c_uint64), ("byte_count", C.c_uint64)]
 

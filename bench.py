@@ -24,7 +24,7 @@ Further objects of the same line, each with its own value, e2e and roofline wher
   prefill            cfg4: the same layer for M = 4096 rows, Zipf(1.1) routing, experts sharded over the ranks,
                      tensor-core (tcgen05) grouped products, ordered reduction with owner runs;
   original_weights   cfg5 decode: MXFP4 routed experts and the E4M3 always-on expert, E4M3 block-quantized activations;
-  original_weights_prefill  cfg5 prefill: the same layer for M = 2048 rows (thin product instances, jobs of eight rows);
+  original_weights_prefill  cfg5 prefill: the same layer for M = 2048 rows (group products: two jobs of eight rows a block);
   reduction          (N > 1) cfg2: the fixed-order reduction alone, FP32 [M][4096] a rank, M in {1, 8, 64}, in this
                      library's four forms, microseconds a call and NVLink bytes a second;
   reference_kernels  (N = 1) the reference's own EXL3 kernels, recompiled for sm_100a from its sources into oracle/_ref,
@@ -649,8 +649,8 @@ def run_original_weights(args, api, base, rank, world, local_rank, dist, barrier
 
 def run_original_weights_prefill(args, api, base, rank, world, local_rank, dist, barrier, maximum):
     """cfg5 prefill: the same original-weights layer for M = 2048 rows, tensor parallel by intermediate columns. The
-    products are the thin instances (jobs of at most eight rows: every job streams its expert's matrices again, mostly
-    from L2), not yet a tensor-core grouped GEMM: the number says where that stands."""
+    products are linear_routed_experts_wide_prepare's (a group of two jobs of eight rows and several tiles a block, the
+    thin instances' arithmetic bit for bit), not yet a tcgen05 grouped GEMM: the number says where that stands."""
     from anemone_b200 import synthetic
     from anemone_b200.moe import MoeConfig
     from anemone_b200.mx import MxLayer, MxLayout
@@ -714,7 +714,7 @@ def run_original_weights_prefill(args, api, base, rank, world, local_rank, dist,
             "dtype": "e2m1 x e4m3 -> f32", "jobs": layout.job_capacity,
             "config": {"workload": "cfg5 original-weights MoE layer prefill: M=%d, %d routed MXFP4 experts, top-%d, 1 "
                                    "always-on expert E4M3 with one FP32 scale per 128x128 weights, hidden %d, "
-                                   "intermediate %d; thin product instances (jobs of at most eight rows)" %
+                                   "intermediate %d; group products (two jobs of eight rows a block, mma.sync, the thin instances' bits)" %
                                    (rows, config.experts, config.picks, H, config.inner),
                        "parallelism": "tp%d by intermediate columns, ordered FP32->bf16 reduce (owner runs)" % world}}
 

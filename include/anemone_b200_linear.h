@@ -93,6 +93,17 @@ MUST_CHECK result_status linear_routed_experts_prepare(const struct linear_route
 						       const struct linear_kernels_record *kernels,
 						       struct kernel_launch *launches_out);
 
+/* B200 extension: the routed experts for a job table of MANY rows (the original-weights profile's prefill): the same
+ * description and the same four launches with the two product launches given to "expert_gate_up_many" and
+ * "expert_down_many" (struct expert_gate_up_many_arguments: a block a group of LINEAR_MANY_JOBS consecutive jobs and
+ * several tiles, the words of a tile placed once for the group's jobs of one expert), prepared here. The results are
+ * linear_routed_experts_prepare's bit for bit. gate_up_shape.output_size a multiple of 64, input_size of 128. */
+MUST_CHECK result_status linear_routed_experts_wide_prepare(const struct linear_routed_experts_description *description,
+							    uint64_t arena_byte_count,
+							    const struct linear_kernels_record *kernels,
+							    const struct backend_operations *backend,
+							    struct device_card *card, struct kernel_launch *launches_out);
+
 /* include/anemone/linear.h:200-208: a matrix where it lies in the arena and the slices its products are cut into.
  * wide_form: 0 (this library has the thin instances only). */
 struct linear_matrix {

@@ -894,6 +894,30 @@ struct expert_down_arguments {
 	uint32_t reserved_zero;
 };
 
+/* B200 extension, kernel file "kernel_expert_linear", entries "expert_gate_up_many" and "expert_down_many": the
+ * routed experts' products for MANY rows (the profile's prefill). A block takes LINEAR_MANY_JOBS consecutive jobs of
+ * the table and several tiles of 16 outputs: a warp decodes its tile's words once a load of 64 inputs and multiplies
+ * them with the columns of every job of the group that belongs to the same expert (a job table in expert order, as
+ * router_wide_jobs writes it, has up to 32 rows of one expert in a group), and the warps of a block read the same
+ * rows' operands: the bytes a product moves from L2 fall to a sixth of the thin instances'. Every value's arithmetic
+ * is the thin instances' (a slice is one chain of fma(p, 2^e, chain), the `slice_count` chains added from +0 in
+ * ascending order, one rounding), so the results are theirs bit for bit.
+ *   expert_gate_up_many  grid (output_size / 64, ceil(job_count / 4)), block 256: warps 0..3 four tiles of gate, 4..7 of up
+ *   expert_down_many     grid (output_size / 128, ceil(job_count / 4)), block 256: a warp a tile */
+#define LINEAR_MANY_JOBS 2u
+#define KERNEL_EXPERT_GATE_UP_MANY "expert_gate_up_many"
+#define KERNEL_EXPERT_DOWN_MANY "expert_down_many"
+struct expert_gate_up_many_arguments {
+	struct expert_gate_up_arguments base;
+	uint32_t slice_count; /* 1, 2, 4, 8 or 16 */
+	uint32_t job_count;
+};
+struct expert_down_many_arguments {
+	struct expert_down_arguments base;
+	uint32_t slice_count;
+	uint32_t job_count;
+};
+
 /* B200 extension, kernel file "kernel_router_b200", entry "step_input_select": the step driver's hand-over of one
  * step's inputs that already lie in device memory. A pool holds `pool_count` prepared step input areas of `byte_count`
  * bytes at `pool_stride` apart (each beginning with its struct step_block, sequences strictly increasing); the kernel
@@ -945,6 +969,8 @@ AB_RECORD_HAS(router_wide_arguments, 152);
 AB_RECORD_HAS(activation_quantize_arguments, 40);
 AB_RECORD_HAS(expert_gate_up_arguments, 64);
 AB_RECORD_HAS(expert_down_arguments, 56);
+AB_RECORD_HAS(expert_gate_up_many_arguments, 72);
+AB_RECORD_HAS(expert_down_many_arguments, 64);
 AB_RECORD_HAS(trunk_linear_quantized_arguments, 72);
 AB_RECORD_HAS(trunk_hidden_arguments, 32);
 AB_RECORD_HAS(trunk_rows_add_arguments, 24);

@@ -63,7 +63,8 @@ def test_record_sizes_match_the_headers():
               "exl3_layer_route_record": R.Exl3LayerRoute, "exl3_layer_publish_arguments": R.Exl3LayerPublish,
               "ordered_publish_reduce_arguments": R.OrderedPublishReduce,
               "exact_ring_arguments": R.ExactRing, "exl3_layer_products_record": R.Exl3LayerProducts,
-              "router_wide_arguments": R.RouterWide}
+              "router_wide_arguments": R.RouterWide, "expert_gate_up_many_arguments": R.ExpertGateUpMany,
+              "expert_down_many_arguments": R.ExpertDownMany}
     assert set(declared) == set(mirror)
     for name, record in mirror.items():
         assert C.sizeof(record) == int(declared[name]), name

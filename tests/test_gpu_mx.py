@@ -527,3 +527,45 @@ def test_layer_at_the_configured_shapes(api, oracle):
     row_output = received["row_output"].view(np.float32).reshape(rows, H)
     assert np.array_equal(resummed.view(np.uint32), row_output.view(np.uint32))
     assert np.array_equal(result, synthetic.to_bfloat16(np.float32(0.0) + row_output))
+
+
+@pytest.mark.parametrize("slices", [(1, 1), (2, 2), (4, 4)])
+def test_many_row_products_equal_the_thin_instances(api, oracle, slices):
+    """linear_routed_experts_wide_prepare (a group of jobs and several tiles a block) against the thin instances on the
+    same layer, rows and routing: hidden values and pair outputs bit for bit, for runs of one expert that fill a group,
+    runs that end inside one, and experts with a single job or none."""
+    from anemone_b200.moe import MoeConfig
+    from anemone_b200.mx import MxLayer, MxLayout
+    rows = 171
+    config = MoeConfig(hidden=512, inner=256, experts=12, shared=1, picks=3, row_capacity=256, activation_limit=7.0)
+    rng = np.random.default_rng(321)
+    H, I = config.hidden, config.inner
+    matrices = [(mx_matrix(oracle, rng, I, H), mx_matrix(oracle, rng, I, H), mx_matrix(oracle, rng, H, I))
+                for _ in range(config.experts)]
+    always = (synthetic.e4m3_matrix(rng, I, H), synthetic.e4m3_matrix(rng, I, H), synthetic.e4m3_matrix(rng, H, I))
+    tokens = synthetic.tokens(rng, rows, H)
+    scores = rng.normal(0, 1, size=(rows, config.experts)).astype(np.float32)
+    scores[:, 1] += 1.5  # one expert with many jobs
+    scores[:, 7] -= 30.0  # one with none
+    L = MxLayout(config, 1, 0, wide=True)
+    got = {}
+    for many in (False, True):
+        card = api.Card(0, L.arena_bytes)
+        try:
+            layer = MxLayer(card, config, matrices, slices=slices, shared_matrices=always, wide=True, many=many)
+            layer.connect_local([layer])
+            result = layer.step(tokens, scores)
+            received = card.download(0, L.arena_bytes)
+        finally:
+            card.close()
+        live = rows * config.picks
+        got[many] = (received[L.at["hidden"]:L.at["hidden"] + live * I * 2].copy(),
+                     received[L.at["pair_output"]:L.at["pair_output"] + live * H * 2].copy(), result.copy(),
+                     tuple(tuple(launch.grid) for launch in layer.expert_launches))
+    assert got[True][3] != got[False][3]  # other launches
+    assert got[True][3][0] == (I // 64, (L.job_capacity + R.LINEAR_MANY_JOBS - 1) // R.LINEAR_MANY_JOBS, 1)
+    assert got[True][3][2] == (H // 128, (L.job_capacity + R.LINEAR_MANY_JOBS - 1) // R.LINEAR_MANY_JOBS, 1)
+    assert np.any(got[False][1] != 0)
+    assert np.array_equal(got[True][0], got[False][0])
+    assert np.array_equal(got[True][1], got[False][1])
+    assert np.array_equal(got[True][2], got[False][2])

@@ -431,3 +431,55 @@ def test_router_wide_prepare():
         assert lib.router_wide_prepare(C.byref(bad), size, C.byref(fake.table), fake.card, launches) == 1, change
         assert bytes(launches) == untouched
     assert lib.router_wide_prepare(C.byref(value), arena - 8192, C.byref(fake.table), fake.card, launches) == 1
+
+
+def test_routed_experts_wide_prepare():
+    """The routed experts for a job table of many rows: the thin preparer's four launches with the two product
+    launches given to the group kernels (slice counts and the job count in their records), and its refusals."""
+    lib, fake = api.library(), FakeBackend()
+    lib.linear_kernels_prepare.argtypes = [C.POINTER(api.BackendOperations), C.c_void_p, C.c_uint32,
+                                           C.POINTER(R.LinearKernels)]
+    kernels = R.LinearKernels()
+    assert lib.linear_kernels_prepare(C.byref(fake.table), fake.card, 100, C.byref(kernels)) == 0
+    thin_prepare, wide_prepare = lib.linear_routed_experts_prepare, lib.linear_routed_experts_wide_prepare
+    thin_prepare.argtypes = [C.POINTER(R.LinearRoutedExpertsDescription), C.c_uint64, C.POINTER(R.LinearKernels),
+                             C.POINTER(R.KernelLaunch)]
+    wide_prepare.argtypes = [C.POINTER(R.LinearRoutedExpertsDescription), C.c_uint64, C.POINTER(R.LinearKernels),
+                             C.POINTER(api.BackendOperations), C.c_void_p, C.POINTER(R.KernelLaunch)]
+
+    def description(H=512, I=256, rows=64, picks=3, jobs=37, slices=(2, 4)):
+        layout, pairs = api.Layout(256), rows * picks
+        d = R.LinearRoutedExpertsDescription()
+        sizes = dict(jobs=jobs * 96, expert_weights=max(I * H, H * I) // 2 + max(I * H, H * I) // 32,
+                     codes=rows * H, exponents=rows * H // 32, operands=rows * H * 2, hidden=pairs * I * 2,
+                     hidden_codes=pairs * I, hidden_exponents=pairs * I // 32, hidden_operands=pairs * I * 2,
+                     pair_output=pairs * H * 2, row_output=rows * H * 4)
+        for name, size in sizes.items():
+            setattr(d, name, R.LinearRange(layout.take(size, 64), size))
+        d.gate_up_shape, d.down_shape = R.MatrixShape(I, H, 4, 0), R.MatrixShape(H, I, 4, 0)
+        d.weight_format, d.job_count, d.row_count, d.pairs_per_row = 3, jobs, rows, picks  # WEIGHT_FORMAT_E2M1_SCALED
+        d.gate_up_slice_count, d.down_slice_count = slices
+        d.activation_limit = 7.0
+        return d, layout.take(0, 4096) + 4096
+    d, arena = description()
+    thin, wide = (R.KernelLaunch * 4)(), (R.KernelLaunch * 4)()
+    assert thin_prepare(C.byref(d), arena, C.byref(kernels), thin) == 0
+    assert wide_prepare(C.byref(d), arena, C.byref(kernels), C.byref(fake.table), fake.card, wide) == 0
+    assert ("kernel_expert_linear", "expert_gate_up_many", 72) in fake.asked
+    assert ("kernel_expert_linear", "expert_down_many", 64) in fake.asked
+    groups = (37 + R.LINEAR_MANY_JOBS - 1) // R.LINEAR_MANY_JOBS
+    assert tuple(wide[0].grid) == (256 // 64, groups, 1) and tuple(wide[2].grid) == (512 // 128, groups, 1)
+    assert wide[0].block[0] == 256 and wide[2].block[0] == 256
+    gate_up = R.ExpertGateUpMany.from_buffer_copy(bytes(wide[0].argument[:72]))
+    down = R.ExpertDownMany.from_buffer_copy(bytes(wide[2].argument[:64]))
+    assert bytes(gate_up.base) == bytes(thin[0].argument[:64]) and (gate_up.slice_count, gate_up.job_count) == (2, 37)
+    assert bytes(down.base) == bytes(thin[2].argument[:56]) and (down.slice_count, down.job_count) == (4, 37)
+    assert bytes(wide[1]) == bytes(thin[1]) and bytes(wide[3]) == bytes(thin[3])  # quantization and row sum as they were
+    assert wide[0].kernel != thin[0].kernel and wide[2].kernel != thin[2].kernel
+    untouched = bytes(wide)
+    for change in (dict(I=224), dict(H=448), dict(slices=(3, 1)), dict(jobs=0)):
+        bad, size = description(**change)
+        assert wide_prepare(C.byref(bad), size, C.byref(kernels), C.byref(fake.table), fake.card, wide) == 1, change
+        assert bytes(wide) == untouched
+    assert wide_prepare(C.byref(d), arena, C.byref(kernels), None, fake.card, wide) == 1
+    assert wide_prepare(C.byref(d), arena - 8192, C.byref(kernels), C.byref(fake.table), fake.card, wide) == 1
