@@ -58,6 +58,37 @@ __device__ __forceinline__ float block_scale(uint32_t weight_code, uint32_t acti
 	return field < 1 ? 0.0f : __uint_as_float((uint32_t)(field > 254 ? 254 : field) << 23);
 }
 
+/* True if every byte of `word` is an E8M0 code from 53 to 179. Where the two codes of a block's scale both are,
+ * block_scale(w, a) is the product of the normal numbers 2^(w - 127) and 2^(a - 105) and is formed that way (two
+ * multiply-adds of the integer multiplier and one FP32 multiplication instead of the clamped sum on the ALU pipe, which
+ * bounds these kernels): field = w + a - 105 lies in 1 .. 253, nothing is clamped, the product is exact. */
+__device__ __forceinline__ bool codes_are_central(uint32_t word)
+{
+	const uint32_t even = (word & 0x00FF00FFu) + 0x004B004Bu, odd = ((word >> 8) & 0x00FF00FFu) + 0x004B004Bu;
+	return (((even ^ 0x00800080u) | (odd ^ 0x00800080u)) & 0x01800180u) == 0u;
+}
+
+/* the four scales of one block of 32 inputs: (low row, high row) x (even column, odd column). central: every code
+ * involved passed codes_are_central (a lane decides for itself: the products lie outside the branch) */
+__device__ __forceinline__ void block_scales(bool central, uint32_t low_row, uint32_t high_row, uint32_t even_code,
+					     uint32_t odd_code, float scales[4])
+{
+	if (central) {
+		const float low = __uint_as_float(low_row * 0x00800000u), high = __uint_as_float(high_row * 0x00800000u);
+		const float even = __uint_as_float(even_code * 0x00800000u + 0x0B000000u),
+			    odd = __uint_as_float(odd_code * 0x00800000u + 0x0B000000u); /* 2^(code - 127 + 22) */
+		scales[0] = __fmul_rn(low, even);
+		scales[1] = __fmul_rn(low, odd);
+		scales[2] = __fmul_rn(high, even);
+		scales[3] = __fmul_rn(high, odd);
+	} else {
+		scales[0] = block_scale(low_row, even_code);
+		scales[1] = block_scale(low_row, odd_code);
+		scales[2] = block_scale(high_row, even_code);
+		scales[3] = block_scale(high_row, odd_code);
+	}
+}
+
 /* One slice of one tile: the chains of this lane's four (output, column) results. matrix: the stored matrix of
  * `outputs` x `inputs`; operands / exponents: per column's vector (this lane feeds column lane / 4 and collects columns
  * 2 t, 2 t + 1). */
@@ -103,6 +134,7 @@ __device__ __forceinline__ void slice_chains(const unsigned char *matrix, uint32
 			const uint32_t step_words[4] = { current.x, current.y, current.z, current.w };
 			const uint32_t even = *reinterpret_cast<const uint16_t *>(exponents_even + 2u * load);
 			const uint32_t odd = *reinterpret_cast<const uint16_t *>(exponents_odd + 2u * load);
+			const bool central = codes_are_central(scale_word) && codes_are_central(even | odd << 16);
 #pragma unroll
 			for (uint32_t q = 0; q < 2u; q++) {
 				float sum[4] = { 0.0f, 0.0f, 0.0f, 0.0f };
@@ -113,13 +145,12 @@ __device__ __forceinline__ void slice_chains(const unsigned char *matrix, uint32
 								place_e2m1<3>(word) };
 					mma_f16(sum, a, fed_registers[2u * step], fed_registers[2u * step + 1u]);
 				}
-				const uint32_t low_row = (scale_word >> (16u * q)) & 0xFFu,
-					       high_row = (scale_word >> (16u * q + 8u)) & 0xFFu;
-				const uint32_t even_code = (even >> (8u * q)) & 0xFFu, odd_code = (odd >> (8u * q)) & 0xFFu;
-				chains[0] = __fmaf_rn(sum[0], block_scale(low_row, even_code), chains[0]);
-				chains[1] = __fmaf_rn(sum[1], block_scale(low_row, odd_code), chains[1]);
-				chains[2] = __fmaf_rn(sum[2], block_scale(high_row, even_code), chains[2]);
-				chains[3] = __fmaf_rn(sum[3], block_scale(high_row, odd_code), chains[3]);
+				float scales[4];
+				block_scales(central, (scale_word >> (16u * q)) & 0xFFu, (scale_word >> (16u * q + 8u)) & 0xFFu,
+					     (even >> (8u * q)) & 0xFFu, (odd >> (8u * q)) & 0xFFu, scales);
+#pragma unroll
+				for (uint32_t c = 0; c < 4; c++)
+					chains[c] = __fmaf_rn(sum[c], scales[c], chains[c]);
 			}
 		}
 	}
@@ -306,6 +337,8 @@ __device__ __forceinline__ void slice_chains_many(const unsigned char *matrix, u
 						const uint32_t step = 2u * q + half;
 						mma_f16(sum, a[step], fed_registers[2u * step], fed_registers[2u * step + 1u]);
 					}
+					/* the clamped sums here: with two jobs' chains live the branch of block_scales costs more than
+					 * it saves */
 					const uint32_t low_row = (scale_word >> (16u * q)) & 0xFFu,
 						       high_row = (scale_word >> (16u * q + 8u)) & 0xFFu;
 					const uint32_t even_code = (even >> (8u * q)) & 0xFFu, odd_code = (odd >> (8u * q)) & 0xFFu;

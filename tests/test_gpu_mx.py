@@ -21,10 +21,11 @@ def api():
     return module
 
 
-def mx_matrix(oracle, rng, outputs, inputs):
-    """Stored MXFP4 matrix of the original-weights profile: uniform E2M1 nibbles, E8M0 codes 127 + e, e in [-8, -4]."""
+def mx_matrix(oracle, rng, outputs, inputs, scale_codes=(119, 124)):
+    """Stored MXFP4 matrix of the original-weights profile: uniform E2M1 nibbles, E8M0 codes 127 + e, e in [-8, -4]
+    (or from the given half-open range)."""
     codes = rng.integers(0, 16, size=outputs * inputs, dtype=np.uint8)
-    scales = (127 + rng.integers(-8, -3, size=outputs * inputs // 32)).astype(np.uint8)
+    scales = rng.integers(scale_codes[0], scale_codes[1], size=outputs * inputs // 32).astype(np.uint8)
     stored = np.zeros(outputs * inputs // 2 + outputs * inputs // 32, dtype=np.uint8)
     oracle.orc_mx_weights_lay_out(ptr(codes, u8p), ptr(scales, u8p), outputs, inputs, ptr(stored, u8p))
     return stored
@@ -82,8 +83,12 @@ def test_activation_quantize_is_bit_exact(api, oracle):
         assert np.array_equal(operands[row], want_operands), row
 
 
-@pytest.mark.parametrize("slices", [(1, 1), (4, 4), (8, 2), (16, 8)])
-def test_routed_experts_match_oracle(api, oracle, slices):
+@pytest.mark.parametrize("slices,edge", [((1, 1), False), ((4, 4), False), ((8, 2), False), ((16, 8), False),
+                                         ((2, 2), True)])
+def test_routed_experts_match_oracle(api, oracle, slices, edge):
+    """edge: the block scales' codes straddle the window inside which the kernels form a scale as a product of two
+    powers of two (53 .. 179) and outside which they clamp the sum: weights' codes 50 .. 56, the rows' blocks scaled so
+    that their codes are about 176 .. 182, so that lanes of one warp go both ways and the scales stay near one."""
     rng = np.random.default_rng(32 + slices[0])
     H, I, experts, rows, picks = 1024, 512, 6, 11, 2
     pairs = rows * picks
@@ -92,7 +97,7 @@ def test_routed_experts_match_oracle(api, oracle, slices):
     matrices = []
     for expert in range(experts):
         for which, (outputs, inputs) in enumerate(((I, H), (I, H), (H, I))):
-            data = mx_matrix(oracle, rng, outputs, inputs)
+            data = mx_matrix(oracle, rng, outputs, inputs, (50, 57) if edge and which < 2 else (119, 124))
             table[expert, which] = layout.take(data.size, 64)
             matrices.append((int(table[expert, which]), data))
     weights_end = layout.cursor
@@ -113,6 +118,10 @@ def test_routed_experts_match_oracle(api, oracle, slices):
         image[offset:offset + data.size] = data
     image[at["jobs"]:at["jobs"] + sizes["jobs"]] = np.frombuffer(bytes(jobs), dtype=np.uint8)
     tokens = synthetic.tokens(rng, rows, H)
+    if edge:
+        blocks = synthetic.from_bfloat16(tokens).reshape(rows, H // 32, 32)
+        blocks = blocks * np.exp2(rng.integers(56, 63, size=(rows, H // 32, 1))).astype(np.float32)
+        tokens = synthetic.to_bfloat16(blocks.reshape(rows, H).astype(np.float32))
     image[at["values"]:at["values"] + sizes["values"]] = tokens.view(np.uint8).reshape(-1)
     description = R.LinearRoutedExpertsDescription()
     description.jobs = R.LinearRange(at["jobs"], sizes["jobs"])
@@ -145,6 +154,9 @@ def test_routed_experts_match_oracle(api, oracle, slices):
         received = card.download(0, arena_bytes)
     finally:
         card.close()
+    if edge:
+        seen = received[at["exponents"]:at["exponents"] + sizes["exponents"]]
+        assert (seen > 179).any() and (seen <= 179).any() and seen.min() >= 170
     # the oracle on the same image, from the card's own (bit-exact, checked above) quantized rows
     expected = image.copy()
     for name in ("codes", "exponents", "operands"):
