@@ -94,10 +94,12 @@ class MxLayout:
 
 class MxLayer:
     def __init__(self, card, config, matrices, rank=0, rank_count=1, slices=(4, 4), shared_matrices=None,
-                 shared_slices=(2, 2), pool_entries=0, block128=False, wide=False, many=True):
+                 shared_slices=(2, 2), pool_entries=0, block128=False, wide=False, many=True, side_run=True):
         """matrices: iterable over the routed experts of this rank's (gate, up, down) stored MXFP4 bytes;
         shared_matrices: the always-on expert's (gate, up, down) stored E4M3 bytes, where the configuration has one:
-        WEIGHT_FORMAT_E4M3_SCALED, or with block128 WEIGHT_FORMAT_E4M3_BLOCK128 (one FP32 scale per 128 by 128)."""
+        WEIGHT_FORMAT_E4M3_SCALED, or with block128 WEIGHT_FORMAT_E4M3_BLOCK128 (one FP32 scale per 128 by 128).
+        side_run: the always-on expert's launches as a side run of the step's graph, beside the routed experts' (the
+        same values either way: the two touch disjoint ranges until the launch that joins them)."""
         self.card, self.config = card, config
         self.layout = L = MxLayout(config, rank_count, rank, pool_entries, block128, wide)
         assert card.arena_bytes >= L.arena_bytes
@@ -241,8 +243,19 @@ class MxLayer:
         reduce_launches = (R.KernelLaunch * 2)()
         api.check(lib.ordered_reduce_bf16_prepare(C.byref(reduce), card.ops_pointer, card.handle, reduce_launches),
                   "ordered_reduce_bf16_prepare")
-        self.launches = router_launches + [quantize_launch] + list(self.expert_launches) + shared_launches + \
-            list(reduce_launches)
+        # the always-on expert reads the quantized rows alone: its four launches are a side run of the graph beside the
+        # routed experts' launches (a decode step's trunk launches are too small to fill the card by themselves);
+        # the join is the launch that adds its rows to the routed experts' sums
+        if shared_launches and side_run:
+            for launch in shared_launches[:4]:
+                launch.branch = R.LAUNCH_SIDE
+            self.expert_launches[0].branch = R.LAUNCH_RESUME
+            shared_launches[4].branch = R.LAUNCH_JOIN
+            self.launches = router_launches + [quantize_launch] + shared_launches[:4] + list(self.expert_launches) + \
+                shared_launches[4:] + list(reduce_launches)
+        else:
+            self.launches = router_launches + [quantize_launch] + list(self.expert_launches) + shared_launches + \
+                list(reduce_launches)
         self.graph = card.graph(self.launches)
         self.resident_graph = None
         if L.pool_entries:

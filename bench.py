@@ -614,7 +614,8 @@ def run_original_weights(args, api, base, rank, world, local_rank, dist, barrier
     roofline = None
     if rank == 0:
         peak, source = measured_peaks()
-        gate_up = (R.KernelLaunch * 1)(layer.launches[2])
+        gate_up = (R.KernelLaunch * 1)(R.KernelLaunch.from_buffer_copy(bytes(layer.expert_launches[0])))
+        gate_up[0].branch = 0  # alone: in the step's graph it resumes the main run beside the always-on expert's
         card.run(gate_up)
         card.wait()
         card.measure_begin()
