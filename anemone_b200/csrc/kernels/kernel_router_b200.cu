@@ -1,6 +1,7 @@
 /*
  * kernel_router_b200.cu: router select and job-table builder for up to 64 live rows (struct
- * router_select_b200_arguments). One block of 1024 threads, a row's picks depend on that row alone.
+ * router_select_b200_arguments). One block of 1024 threads, a row's picks depend on that row alone (a team of four
+ * warps a row for up to eight live rows, a warp a row beyond).
  * (The only atomic is an OR into a shared-memory bit mask, whose result does not depend on order.)
  * Conventions are the reference's router_select_entry (source/kernel_router.cuh:36-119, include/anemone/
  * router_records.h:7-30): keys order scores as the reference's top-k orders float32 (a not-a-number above every
@@ -21,20 +22,34 @@ extern "C" __global__ void __launch_bounds__(ROUTER_B200_THREADS)
 	__shared__ float weight[ROUTER_B200_MAXIMUM_ROWS][ROUTER_B200_MAXIMUM_PICKS];
 	__shared__ unsigned long long row_mask[ROUTER_B200_MAXIMUM_EXPERTS]; /* bit r: row r stands in the expert */
 	__shared__ uint32_t first_job[ROUTER_B200_MAXIMUM_EXPERTS];
+	__shared__ uint64_t candidates[ROUTER_B200_THREADS / WARP / ROUTER_TEAM_WARPS]
+				      [ROUTER_TEAM_WARPS * ROUTER_B200_MAXIMUM_PICKS];
 	const struct step_block step = *reinterpret_cast<const struct step_block *>(arena + arguments.step_offset);
 	const uint32_t live = min(step.row_count, arguments.row_capacity);
 	const uint32_t experts = arguments.expert_count, picks = arguments.picks, shared = arguments.shared_count;
 	const uint32_t lane = threadIdx.x % WARP, warp = threadIdx.x / WARP;
 	const float *const scores = reinterpret_cast<const float *>(arena + arguments.scores_offset);
 
-	/* one warp a row */
 	const float *const bias =
 		arguments.bias_offset != 0 ? reinterpret_cast<const float *>(arena + arguments.bias_offset) : nullptr;
-	for (uint32_t row = warp; row < live; row += blockDim.x / WARP)
-		router_row(scores + (uint64_t)row * experts, bias, experts, picks, arguments.scoring, arguments.route_scale,
-			   lane, chosen[row], weight[row],
-			   reinterpret_cast<uint32_t *>(arena + arguments.picks_offset) + (uint64_t)row * picks,
-			   reinterpret_cast<float *>(arena + arguments.weights_offset) + (uint64_t)row * picks);
+	uint32_t *const picks_out = reinterpret_cast<uint32_t *>(arena + arguments.picks_offset);
+	float *const weights_out = reinterpret_cast<float *>(arena + arguments.weights_offset);
+	const uint32_t team = warp / ROUTER_TEAM_WARPS, teams = blockDim.x / WARP / ROUTER_TEAM_WARPS;
+	if (live <= teams) {
+		/* a team of four warps a row (the same picks and weights): the launch lasts as long as one row's chain of
+		 * dependent instructions, which a team shortens */
+		if (team < live)
+			router_row_team(scores + (uint64_t)team * experts, bias, experts, picks, arguments.scoring,
+					arguments.route_scale, lane, warp % ROUTER_TEAM_WARPS, 1u + team, candidates[team],
+					chosen[team], weight[team], picks_out + (uint64_t)team * picks,
+					weights_out + (uint64_t)team * picks);
+	} else {
+		/* one warp a row */
+		for (uint32_t row = warp; row < live; row += blockDim.x / WARP)
+			router_row(scores + (uint64_t)row * experts, bias, experts, picks, arguments.scoring,
+				   arguments.route_scale, lane, chosen[row], weight[row], picks_out + (uint64_t)row * picks,
+				   weights_out + (uint64_t)row * picks);
+	}
 	__syncthreads();
 	router_job_table(live, experts, picks, shared, arguments.job_capacity, chosen, weight, row_mask, first_job,
 			 reinterpret_cast<struct expert_job_record *>(arena + arguments.jobs_offset),
