@@ -90,6 +90,10 @@ def library():
         lib.backend_b200_fill.argtypes = [_card, C.c_uint64, C.c_ubyte, C.c_uint64]
         lib.backend_b200_step_run.argtypes = [_card, C.c_uint32, C.c_uint64, C.c_void_p, C.c_uint64, C.c_uint64,
                                               C.c_void_p, C.c_uint64]
+        lib.backend_b200_step_capture.argtypes = [_card, C.POINTER(R.KernelLaunch), C.c_uint32, C.c_uint64, C.c_void_p,
+                                                  C.c_uint64, C.c_uint64, C.c_void_p, C.c_uint64,
+                                                  C.POINTER(C.c_uint32)]
+        lib.backend_b200_graph_run_wait.argtypes = [_card, C.c_uint32]
         lib.backend_b200_ipc_export.argtypes = [_card, C.c_char_p]
         lib.backend_b200_ipc_connect.argtypes = [_card, C.c_char_p, C.c_uint64, C.c_uint64]
         lib.exl3_reconstruct_prepare.argtypes = [C.POINTER(R.Exl3Reconstruct), C.c_uint64, C.c_uint32,
@@ -266,6 +270,25 @@ class Card:
                                               output_offset,
                                               C.c_void_p(self.staging.value + output_staging_offset), output_bytes),
               "step_run")
+
+    def step_capture(self, launches, input_offset, input_staging_offset, input_bytes, output_offset,
+                     output_staging_offset, output_bytes):
+        """The copy in, a chain of launches and the copy out as ONE graph (backend_b200_step_capture); None if the
+        table is not a plain chain. Run it with graph_run_wait."""
+        table = launches if isinstance(launches, C.Array) else (R.KernelLaunch * len(launches))(*launches)
+        graph = C.c_uint32()
+        status = library().backend_b200_step_capture(self.handle, table, len(table), input_offset,
+                                                     C.c_void_p(self.staging.value + input_staging_offset), input_bytes,
+                                                     output_offset,
+                                                     C.c_void_p(self.staging.value + output_staging_offset),
+                                                     output_bytes, C.byref(graph))
+        if status == R.STATUS_UNSUPPORTED:
+            return None
+        check(status, "step_capture")
+        return graph.value
+
+    def graph_run_wait(self, graph):
+        check(library().backend_b200_graph_run_wait(self.handle, graph), "graph_run_wait")
 
     def measure_begin(self):
         check(self.ops.measure_begin(self.handle), "measure_begin")

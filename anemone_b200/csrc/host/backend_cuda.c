@@ -1342,6 +1342,81 @@ done:
 	CARD_LEAVE(card);
 }
 
+result_status backend_b200_step_capture(struct device_card *card, const struct kernel_launch *launches,
+					uint32_t launch_count, uint64_t input_arena_offset, const void *page_locked_input,
+					uint64_t input_byte_count, uint64_t output_arena_offset, void *page_locked_output,
+					uint64_t output_byte_count, uint32_t *graph_out)
+{
+	if (card == NULL || graph_out == NULL ||
+	    (input_byte_count != 0 &&
+	     (page_locked_input == NULL || !range_inside(input_arena_offset, input_byte_count, card->arena_byte_count) ||
+	      !inside_one_staging_block(page_locked_input, input_byte_count))) ||
+	    (output_byte_count != 0 &&
+	     (page_locked_output == NULL || !range_inside(output_arena_offset, output_byte_count, card->arena_byte_count) ||
+	      !inside_one_staging_block(page_locked_output, output_byte_count))))
+		return STATUS_INVALID_ARGUMENT;
+	CARD_ENTER(card);
+	CUgraph graph = NULL;
+	status = card->failed ? STATUS_DEVICE_ERROR : table_check(card, launches, launch_count);
+	if (status != STATUS_OK)
+		goto done;
+	if (!table_is_a_plain_chain(launches, launch_count)) {
+		status = STATUS_UNSUPPORTED; /* side runs and copy launches: graph_capture and backend_b200_step_run */
+		goto done;
+	}
+	if (card->graph_count == BACKEND_MAXIMUM_GRAPHS) {
+		status = STATUS_BUSY_VALUE;
+		goto done;
+	}
+	DRIVER(card, cuStreamBeginCapture(card->stream, CU_STREAM_CAPTURE_MODE_THREAD_LOCAL));
+	{
+		CUresult copied = CUDA_SUCCESS;
+		if (input_byte_count != 0)
+			copied = cu->cuMemcpyHtoDAsync(card->arena + input_arena_offset, page_locked_input, input_byte_count,
+						       card->stream);
+		status = copied == CUDA_SUCCESS ? launches_queue(cu, card, launches, launch_count) :
+						  driver_failure(card, "capturing the copy in", copied);
+		if (status == STATUS_OK && output_byte_count != 0) {
+			copied = cu->cuMemcpyDtoHAsync(page_locked_output, card->arena + output_arena_offset, output_byte_count,
+						       card->stream);
+			if (copied != CUDA_SUCCESS)
+				status = driver_failure(card, "capturing the copy out", copied);
+		}
+		const CUresult ended = cu->cuStreamEndCapture(card->stream, &graph);
+		if (status == STATUS_OK && ended != CUDA_SUCCESS)
+			status = driver_failure(card, "ending the capture", ended);
+	}
+	if (status != STATUS_OK)
+		goto done;
+	DRIVER(card, cuGraphInstantiateWithFlags(&card->graphs[card->graph_count], graph, 0));
+	card->graph_kernel_nodes[card->graph_count] = kernel_launches_of(launches, launch_count);
+	*graph_out = card->graph_count++;
+done:
+	if (graph != NULL)
+		(void)cu->cuGraphDestroy(graph);
+	CARD_LEAVE(card);
+}
+
+result_status backend_b200_graph_run_wait(struct device_card *card, uint32_t graph)
+{
+	if (card == NULL)
+		return STATUS_INVALID_ARGUMENT;
+	CARD_ENTER(card);
+	if (card->failed) {
+		status = STATUS_DEVICE_ERROR;
+		goto done;
+	}
+	if (graph >= card->graph_count) {
+		status = STATUS_INVALID_ARGUMENT;
+		goto done;
+	}
+	DRIVER(card, cuGraphLaunch(card->graphs[graph], card->stream));
+	card->launches_queued += card->graph_kernel_nodes[graph];
+	DRIVER(card, cuStreamSynchronize(card->stream));
+done:
+	CARD_LEAVE(card);
+}
+
 uint64_t backend_b200_launch_count(const struct device_card *card)
 {
 	return card != NULL ? card->launches_queued : 0;

@@ -210,6 +210,7 @@ class MoeLayer:
     def _prepare(self):
         c, L, card, lib = self.config, self.layout, self.card, api.library()
         # which launches stand before the gate/up products, and which launch they are (for callers that time them)
+        self.step_graph = None  # step(): the copies and the launches as one graph, captured at its first call
         self.gate_up_index = 1 if L.reduce_form == "fused" else 2
         self.gate_up_kernel = "exl3_layer_products" if L.reduce_form == "fused" else "exl3_moe_gate_up"
         # the launch at gate_up_index holds the down products too (callers that count a launch's bytes ask)
@@ -324,8 +325,16 @@ class MoeLayer:
         result_at = api.align(L.step_input_bytes, 4096)
         nbytes = rows * self.config.hidden * 2
         self.stage_step(0, self.sequence, tokens, scores)
-        # one library call: inputs in, the graph, status block and result out, wait
-        card.step_run(self.graph, L.step, 0, L.step_input_bytes, L.status, result_at, 16 + nbytes)
+        # one library call: inputs in, the graph, status block and result out, wait. The copies are nodes of the
+        # step's own graph where its table is a plain chain (one graph launch a step)
+        if self.step_graph is None:
+            captured = card.step_capture(self.launches, L.step, 0, L.step_input_bytes, L.status, result_at,
+                                         16 + self.config.row_capacity * self.config.hidden * 2)
+            self.step_graph = -1 if captured is None else captured
+        if self.step_graph >= 0:
+            card.graph_run_wait(self.step_graph)
+        else:
+            card.step_run(self.graph, L.step, 0, L.step_input_bytes, L.status, result_at, 16 + nbytes)
         if L.reduce_form == "push":
             self.check_status()
         else:

@@ -239,6 +239,18 @@ MUST_CHECK result_status backend_b200_step_run(struct device_card *card, uint32_
 					       uint64_t input_arena_offset, const void *page_locked_input,
 					       uint64_t input_byte_count, uint64_t output_arena_offset,
 					       void *page_locked_output, uint64_t output_byte_count);
+/* The same step as ONE graph: the copy in, the chain of launches and the copy out are captured together (memcpy nodes
+ * at fixed page-locked addresses, read and written when the graph runs), so that a step is a single graph launch and a
+ * wait: backend_b200_graph_run_wait. For tables of LAUNCH_CHAIN kernel launches (STATUS_UNSUPPORTED otherwise: such a
+ * table goes through graph_capture and backend_b200_step_run). The caller writes its inputs to the same page-locked
+ * range before every run and reads the output range after the wait. */
+MUST_CHECK result_status backend_b200_step_capture(struct device_card *card, const struct kernel_launch *launches,
+						   uint32_t launch_count, uint64_t input_arena_offset,
+						   const void *page_locked_input, uint64_t input_byte_count,
+						   uint64_t output_arena_offset, void *page_locked_output,
+						   uint64_t output_byte_count, uint32_t *graph_out);
+/* graph_run of the table, then the driver's stream wait: returns when the graph has run (any captured graph). */
+MUST_CHECK result_status backend_b200_graph_run_wait(struct device_card *card, uint32_t graph);
 /* Kernel launches this card has queued since it was opened, graph launches counted by their kernel nodes. */
 /* The dependencies graph_capture gives every launch of a table (order_out[launch_count]), from the branches alone: no
  * card is needed. STATUS_INVALID_ARGUMENT for a NULL, an empty table, a branch that is none of LAUNCH_* or a table

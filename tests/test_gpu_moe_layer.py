@@ -302,3 +302,29 @@ def test_fused_step_reports_a_wait_that_runs_out(api, oracle):
             layer.step(tokens, scores)
     finally:
         card.close()
+
+
+@pytest.mark.parametrize("form", ["fused", "pull"])
+def test_step_as_one_graph_equals_the_three_calls(api, oracle, form):
+    """MoeLayer.step's own graph (the copy in, the chain and the copy out captured together,
+    backend_b200_step_capture + backend_b200_graph_run_wait) against backend_b200_step_run on the same steps: the
+    same bits, for fewer live rows than the capacity too; a table with a side run is refused as unsupported."""
+    config = MoeConfig(hidden=512, inner=256, experts=32, shared=1, picks=4, row_capacity=8)
+    widths, matrices, tokens, scores = make_layer_inputs(77, config, 8)
+    layout = MoeLayout(config, widths, 1, 0, reduce_form=form)
+    card = api.Card(0, layout.arena_bytes)
+    try:
+        layer = MoeLayer(card, config, widths, matrices, reduce_form=form)
+        layer.connect_local([layer])
+        results = {}
+        for one_graph in (True, False):
+            layer.step_graph = None if one_graph else -1
+            results[one_graph] = [layer.step(tokens[:rows], scores[:rows]).copy() for rows in (8, 3, 8, 5)]
+            assert (layer.step_graph >= 0) == one_graph
+        for a, b in zip(results[True], results[False]):
+            assert a.shape == b.shape and np.array_equal(a, b) and np.any(a != 0)
+        side = [R.KernelLaunch.from_buffer_copy(bytes(layer.launches[index])) for index in (0, 1, 1, 2)]
+        side[1].branch, side[2].branch, side[3].branch = R.LAUNCH_SIDE, R.LAUNCH_RESUME, R.LAUNCH_JOIN
+        assert card.step_capture(side, layout.step, 0, layout.step_input_bytes, layout.status, 1 << 20, 16) is None
+    finally:
+        card.close()
