@@ -233,6 +233,70 @@ result_status ordered_collective_prepare(const struct ordered_collective_descrip
 	return STATUS_OK;
 }
 
+/* One launch: ordered_publish_reduce_flags_bf16 (row sums of bfloat16 pair outputs, the optional bfloat16 addend, READY
+ * and the reduction, with flags that arrive in the reader's own memory: the slot layout of the EXL3 layer's step). */
+result_status ordered_publish_reduce_bf16_prepare(const struct ordered_reduce_bf16_description *description,
+						  uint64_t addend_offset, uint64_t row_output_offset,
+						  const struct backend_operations *backend, struct device_card *card,
+						  struct kernel_launch *launch_out)
+{
+	if (description == NULL || backend == NULL || backend->kernel_prepare == NULL || card == NULL || launch_out == NULL)
+		return STATUS_INVALID_ARGUMENT;
+	const struct ordered_reduce_bf16_arguments *const reduce = &description->reduce;
+	const struct ordered_collective_arguments *const collective = &reduce->collective;
+	const uint64_t capacity = description->arena_byte_count;
+	if (reduce->mode != ORDERED_REDUCE_EVERY_RANK || reduce->width == 0 || reduce->width % 4u != 0 ||
+	    description->row_capacity == 0 || description->row_capacity > ORDERED_COLLECTIVE_MAXIMUM_ELEMENTS / 4u ||
+	    description->pairs_per_row == 0 ||
+	    (uint64_t)description->row_capacity * reduce->width != collective->element_count ||
+	    collective->element_count > ORDERED_COLLECTIVE_MAXIMUM_ELEMENTS || collective->rank_count == 0 ||
+	    collective->rank_count > ORDERED_COLLECTIVE_MAXIMUM_RANKS || collective->rank >= collective->rank_count ||
+	    collective->reserved_zero != 0 || collective->scratch_offset != 0 || collective->deadline_cycles == 0 ||
+	    collective->input_offset < EXL3_LAYER_SIGNAL_BYTES || collective->input_offset % 16u != 0 ||
+	    collective->parity_stride % ORDERED_COLLECTIVE_LINE_BYTES != 0 ||
+	    collective->region_offset % ORDERED_COLLECTIVE_LINE_BYTES != 0 ||
+	    collective->parity_stride < collective->input_offset + (uint64_t)collective->element_count * VALUE_BYTES ||
+	    collective->peer_table_offset % ADDRESS_BYTES != 0 || collective->step_offset % ADDRESS_BYTES != 0 ||
+	    addend_offset % 16u != 0 || row_output_offset % 16u != 0 || description->pair_output_offset % 16u != 0)
+		return STATUS_INVALID_ARGUMENT;
+	const uint64_t elements = collective->element_count;
+	const struct checked_range ranges[8] = {
+		{ "result", collective->output_offset, elements * 2u },
+		{ "status", reduce->status_offset, ORDERED_B200_STATUS_BYTES },
+		{ "pair outputs", description->pair_output_offset, elements * 2u * description->pairs_per_row },
+		{ "region", collective->region_offset, collective->parity_stride * ORDERED_COLLECTIVE_SLOTS },
+		{ "peer table", collective->peer_table_offset,
+		  (uint64_t)collective->rank_count * sizeof(struct ordered_collective_peer) },
+		{ "step block", collective->step_offset, STEP_BLOCK_BYTES },
+		{ "addend", addend_offset, addend_offset != 0 ? elements * 2u : 0u },
+		{ "row output", row_output_offset, row_output_offset != 0 ? elements * 4u : 0u }
+	};
+	if (!prepare_ranges_are_valid("ordered publish and reduce", ranges, 8, capacity))
+		return STATUS_INVALID_ARGUMENT;
+	uint32_t kernel = BACKEND_NO_KERNEL;
+	const result_status status = backend->kernel_prepare(card, KERNEL_FILE_ORDERED_B200,
+							     KERNEL_ORDERED_PUBLISH_REDUCE_FLAGS_BF16,
+							     sizeof(struct ordered_publish_reduce_bf16_arguments), &kernel);
+	if (status != STATUS_OK)
+		return status;
+	if (kernel == BACKEND_NO_KERNEL)
+		return STATUS_UNSUPPORTED;
+	const struct ordered_publish_reduce_bf16_arguments arguments = {
+		.base = { .collective = *collective,
+			  .status_offset = reduce->status_offset,
+			  .pair_output_offset = description->pair_output_offset,
+			  .width = reduce->width,
+			  .pairs_per_row = description->pairs_per_row },
+		.addend_offset = addend_offset,
+		.row_output_offset = row_output_offset
+	};
+	uint32_t blocks = ((uint32_t)(elements / 4u) + ORDERED_COLLECTIVE_THREADS - 1u) / ORDERED_COLLECTIVE_THREADS;
+	if (blocks > ORDERED_B200_MAXIMUM_BLOCKS) /* the blocks wait for a word their own grid's last block stores */
+		blocks = ORDERED_B200_MAXIMUM_BLOCKS;
+	prepare_launch_fill(launch_out, kernel, blocks, 1, 1, ORDERED_COLLECTIVE_THREADS, 0, &arguments, sizeof(arguments));
+	return STATUS_OK;
+}
+
 result_status ordered_reduce_bf16_prepare(const struct ordered_reduce_bf16_description *description,
 					  const struct backend_operations *backend, struct device_card *card,
 					  struct kernel_launch *launches_out)

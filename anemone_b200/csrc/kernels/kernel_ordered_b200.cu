@@ -201,8 +201,10 @@ extern "C" __global__ void __launch_bounds__(ORDERED_COLLECTIVE_THREADS)
  * The blocks wait for a word their own grid's last block stores: the grid is at most ORDERED_B200_MAXIMUM_BLOCKS blocks
  * of 256 threads, which a card always holds at once. Every wait is bounded; one that runs out sets the status block
  * and, before READY, leaves READY unpublished (the peers' own waits then say so). */
-extern "C" __global__ void __launch_bounds__(ORDERED_COLLECTIVE_THREADS)
-	ordered_publish_reduce_flags(struct ordered_publish_reduce_arguments arguments, unsigned char *arena)
+template <bool BF16_PAIRS>
+__device__ __forceinline__ void publish_reduce_flags(const struct ordered_publish_reduce_arguments &arguments,
+						     uint64_t addend_offset, uint64_t row_output_offset,
+						     unsigned char *arena)
 {
 	__shared__ uint32_t verdict, last;
 	const struct ordered_collective_arguments &collective = arguments.collective;
@@ -242,17 +244,41 @@ extern "C" __global__ void __launch_bounds__(ORDERED_COLLECTIVE_THREADS)
 	}
 	__syncthreads();
 	if (verdict != 0u) {
-		const float4 *const pairs = reinterpret_cast<const float4 *>(arena + arguments.pair_output_offset);
 		float4 *const rows = reinterpret_cast<float4 *>(mine + collective.input_offset);
 		for (uint32_t vector = blockIdx.x * blockDim.x + threadIdx.x; vector < vectors; vector += gridDim.x * blockDim.x) {
 			const uint32_t row = vector / row_vectors, column = vector % row_vectors;
 			float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-			for (uint32_t slot = 0; slot < arguments.pairs_per_row; slot++) {
-				const float4 value = __ldcg(pairs + ((uint64_t)row * arguments.pairs_per_row + slot) * row_vectors + column);
-				sum.x = __fadd_rn(sum.x, value.x);
-				sum.y = __fadd_rn(sum.y, value.y);
-				sum.z = __fadd_rn(sum.z, value.z);
-				sum.w = __fadd_rn(sum.w, value.w);
+			if (BF16_PAIRS) {
+				const uint2 *const pairs = reinterpret_cast<const uint2 *>(arena + arguments.pair_output_offset);
+				for (uint32_t slot = 0; slot < arguments.pairs_per_row; slot++) {
+					const uint2 value = __ldcg(pairs + ((uint64_t)row * arguments.pairs_per_row + slot) * row_vectors + column);
+					sum.x = __fadd_rn(sum.x, __uint_as_float(value.x << 16));
+					sum.y = __fadd_rn(sum.y, __uint_as_float(value.x & 0xFFFF0000u));
+					sum.z = __fadd_rn(sum.z, __uint_as_float(value.y << 16));
+					sum.w = __fadd_rn(sum.w, __uint_as_float(value.y & 0xFFFF0000u));
+				}
+				if (addend_offset != 0) {
+					const uint2 value = __ldcg(reinterpret_cast<const uint2 *>(arena + addend_offset) + vector);
+					sum.x = __fadd_rn(sum.x, __uint_as_float(value.x << 16));
+					sum.y = __fadd_rn(sum.y, __uint_as_float(value.x & 0xFFFF0000u));
+					sum.z = __fadd_rn(sum.z, __uint_as_float(value.y << 16));
+					sum.w = __fadd_rn(sum.w, __uint_as_float(value.y & 0xFFFF0000u));
+				}
+				if (row_output_offset != 0)
+					reinterpret_cast<float4 *>(arena + row_output_offset)[vector] = sum;
+				/* as the publish launch of one "pair" a row enters it: onto +0 */
+				sum = make_float4(__fadd_rn(0.0f, sum.x), __fadd_rn(0.0f, sum.y), __fadd_rn(0.0f, sum.z),
+						  __fadd_rn(0.0f, sum.w));
+			} else {
+				const float4 *const pairs = reinterpret_cast<const float4 *>(arena + arguments.pair_output_offset);
+				for (uint32_t slot = 0; slot < arguments.pairs_per_row; slot++) {
+					const float4 value =
+						__ldcg(pairs + ((uint64_t)row * arguments.pairs_per_row + slot) * row_vectors + column);
+					sum.x = __fadd_rn(sum.x, value.x);
+					sum.y = __fadd_rn(sum.y, value.y);
+					sum.z = __fadd_rn(sum.z, value.z);
+					sum.w = __fadd_rn(sum.w, value.w);
+				}
 			}
 			rows[vector] = sum;
 		}
@@ -334,6 +360,18 @@ extern "C" __global__ void __launch_bounds__(ORDERED_COLLECTIVE_THREADS)
 		signal_store(ordered_slot(collective, arena, threadIdx.x, sequence) +
 				     (EXL3_LAYER_DONE_LINE + collective.rank) * ORDERED_COLLECTIVE_LINE_BYTES,
 			     sequence);
+}
+
+extern "C" __global__ void __launch_bounds__(ORDERED_COLLECTIVE_THREADS)
+	ordered_publish_reduce_flags(struct ordered_publish_reduce_arguments arguments, unsigned char *arena)
+{
+	publish_reduce_flags<false>(arguments, 0, 0, arena);
+}
+
+extern "C" __global__ void __launch_bounds__(ORDERED_COLLECTIVE_THREADS)
+	ordered_publish_reduce_flags_bf16(struct ordered_publish_reduce_bf16_arguments arguments, unsigned char *arena)
+{
+	publish_reduce_flags<true>(arguments.base, arguments.addend_offset, arguments.row_output_offset, arena);
 }
 
 extern "C" __global__ void __launch_bounds__(ORDERED_COLLECTIVE_THREADS)

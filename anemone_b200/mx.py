@@ -62,8 +62,11 @@ class MxLayout:
         self.pool_stride = api.align(self.step_input_bytes, 256)
         self.cursor = layout.take(16)
         self.pool = layout.take(self.pool_stride * pool_entries) if pool_entries else 0
-        self.slot_input = SIGNAL_BYTES
-        self.parity_stride = api.align(SIGNAL_BYTES + rows * H * 4, LINE)
+        # a decode step's reduction is one launch whose flags arrive in the reader's own memory (the slot layout of the
+        # EXL3 layer's step); many rows (owner runs) and steps beyond that launch's size keep the two-launch form
+        self.flags = not wide and rows * H <= R.ORDERED_COLLECTIVE_MAXIMUM_ELEMENTS
+        self.slot_input = R.EXL3_LAYER_SIGNAL_BYTES if self.flags else SIGNAL_BYTES
+        self.parity_stride = api.align(self.slot_input + rows * H * 4, LINE)
         self.region = layout.take(2 * self.parity_stride, LINE)
         self.picks = layout.take(rows * c.picks * 4)
         self.weights = layout.take(rows * c.picks * 4)
@@ -240,22 +243,36 @@ class MxLayer:
         lib.ordered_reduce_bf16_prepare.argtypes = [C.POINTER(R.OrderedReduceBf16Description),
                                                     C.POINTER(api.BackendOperations), C.c_void_p,
                                                     C.POINTER(R.KernelLaunch)]
-        reduce_launches = (R.KernelLaunch * 2)()
-        api.check(lib.ordered_reduce_bf16_prepare(C.byref(reduce), card.ops_pointer, card.handle, reduce_launches),
-                  "ordered_reduce_bf16_prepare")
+        lib.ordered_publish_reduce_bf16_prepare.argtypes = [C.POINTER(R.OrderedReduceBf16Description), C.c_uint64,
+                                                            C.c_uint64, C.POINTER(api.BackendOperations), C.c_void_p,
+                                                            C.POINTER(R.KernelLaunch)]
+        if L.flags:
+            # row sums of the pair outputs, the always-on expert's rows, READY and the ranks' sum in one launch: it
+            # stands for expert_row_sum_entry, trunk_rows_add_entry and the reduction's two
+            reduce.pair_output_offset, reduce.pairs_per_row = L.at["pair_output"], c.picks
+            reduce_launches = (R.KernelLaunch * 1)()
+            api.check(lib.ordered_publish_reduce_bf16_prepare(
+                C.byref(reduce), L.shared_at["output"] if c.shared else 0, L.at["row_output"], card.ops_pointer,
+                card.handle, reduce_launches), "ordered_publish_reduce_bf16_prepare")
+            self.step_launches = list(self.expert_launches)[:3]
+            shared_launches = shared_launches[:4]
+        else:
+            reduce_launches = (R.KernelLaunch * 2)()
+            api.check(lib.ordered_reduce_bf16_prepare(C.byref(reduce), card.ops_pointer, card.handle, reduce_launches),
+                      "ordered_reduce_bf16_prepare")
+            self.step_launches = list(self.expert_launches)
         # the always-on expert reads the quantized rows alone: its four launches are a side run of the graph beside the
         # routed experts' launches (a decode step's trunk launches are too small to fill the card by themselves);
         # the join is the launch that adds its rows to the routed experts' sums
+        behind = shared_launches[4:] + list(reduce_launches)  # the launch that joins the two runs first
         if shared_launches and side_run:
             for launch in shared_launches[:4]:
                 launch.branch = R.LAUNCH_SIDE
             self.expert_launches[0].branch = R.LAUNCH_RESUME
-            shared_launches[4].branch = R.LAUNCH_JOIN
-            self.launches = router_launches + [quantize_launch] + shared_launches[:4] + list(self.expert_launches) + \
-                shared_launches[4:] + list(reduce_launches)
+            behind[0].branch = R.LAUNCH_JOIN
+            self.launches = router_launches + [quantize_launch] + shared_launches[:4] + self.step_launches + behind
         else:
-            self.launches = router_launches + [quantize_launch] + list(self.expert_launches) + shared_launches + \
-                list(reduce_launches)
+            self.launches = router_launches + [quantize_launch] + self.step_launches + shared_launches[:4] + behind
         self.graph = card.graph(self.launches)
         self.resident_graph = None
         if L.pool_entries:

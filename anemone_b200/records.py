@@ -70,6 +70,7 @@ class Exl3LayerDescription(C.Structure):
 
 
 EXL3_LAYER_SIGNAL_BYTES = 33 * 128
+ORDERED_COLLECTIVE_MAXIMUM_ELEMENTS = 262144
 EXL3_LAYER_LAUNCHES = 3
 EXL3_LAYER_READY_LINE, EXL3_LAYER_DONE_LINE, EXL3_LAYER_LOCAL_LINE = 0, 16, 32
 
@@ -161,6 +162,10 @@ class OrderedReduceBf16(C.Structure):
 class OrderedPublishReduce(C.Structure):
     _fields_ = [("collective", OrderedCollective), ("status_offset", C.c_uint64), ("pair_output_offset", C.c_uint64),
                 ("width", C.c_uint32), ("pairs_per_row", C.c_uint32)]
+
+
+class OrderedPublishReduceBf16(C.Structure):
+    _fields_ = [("base", OrderedPublishReduce), ("addend_offset", C.c_uint64), ("row_output_offset", C.c_uint64)]
 
 
 class OrderedRowSumPublish(C.Structure):

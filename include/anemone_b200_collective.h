@@ -107,6 +107,17 @@ struct ordered_reduce_bf16_description {
 MUST_CHECK result_status ordered_reduce_bf16_prepare(const struct ordered_reduce_bf16_description *description,
 						     const struct backend_operations *backend,
 						     struct device_card *card, struct kernel_launch *launches_out);
+/* B200 extension: the same reduction for pair outputs that are bfloat16, in ONE launch
+ * ("ordered_publish_reduce_flags_bf16", struct ordered_publish_reduce_bf16_arguments): row sums, the optional
+ * bfloat16 addend row (0: none), the optional FP32 copy of the rank's own rows (0: none), READY and the rank-ordered
+ * sum with one rounding, with flags that arrive in the reader's own memory. The description is
+ * ordered_reduce_bf16_prepare's with pair outputs of 2 bytes an element; mode ORDERED_REDUCE_EVERY_RANK; the slot
+ * layout is the EXL3 layer step's (input_offset at least EXL3_LAYER_SIGNAL_BYTES), at most
+ * ORDERED_COLLECTIVE_MAXIMUM_ELEMENTS elements. */
+MUST_CHECK result_status ordered_publish_reduce_bf16_prepare(const struct ordered_reduce_bf16_description *description,
+							     uint64_t addend_offset, uint64_t row_output_offset,
+							     const struct backend_operations *backend,
+							     struct device_card *card, struct kernel_launch *launch_out);
 
 /* ---- one-shot push all-reduce (include/anemone/ordered_push.h:37-59) ---- */
 

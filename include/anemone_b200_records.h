@@ -399,6 +399,19 @@ struct ordered_publish_reduce_arguments {
 	uint32_t pairs_per_row;
 };
 
+/* B200 extension, entry "ordered_publish_reduce_flags_bf16": the same launch for pair outputs that are BFLOAT16
+ * (the original-weights experts' expert_down outputs): a row's pairs added from +0 in ascending slot order as FP32,
+ * then, where addend_offset is not 0, one FP32 addition of the bfloat16 row at addend_offset ([rows][width]: the
+ * always-on expert's output); the sum is stored at row_output_offset where that is not 0 (FP32 [rows][width], for
+ * readers of the rank's own rows) and enters the slot through one more addition onto +0: the operations of
+ * expert_row_sum_entry, trunk_rows_add_entry and ordered_row_sum_publish with one "pair" a row, in their order. */
+#define KERNEL_ORDERED_PUBLISH_REDUCE_FLAGS_BF16 "ordered_publish_reduce_flags_bf16"
+struct ordered_publish_reduce_bf16_arguments {
+	struct ordered_publish_reduce_arguments base; /* pair_output_offset: bfloat16 [rows * pairs_per_row][width] */
+	uint64_t addend_offset;
+	uint64_t row_output_offset;
+};
+
 /* B200 extension: the row sum of a rank written straight into its collective input slot of this step's parity
  * (FP32 [rows][width] at collective.input_offset of the slot), so that no copy stands between the experts and the
  * reduction. Rows at or beyond step.row_count are not written. grid (width / 512 rounded up, up to
@@ -952,6 +965,7 @@ AB_RECORD_HAS(ordered_collective_arguments, 80);
 AB_RECORD_HAS(ordered_reduce_bf16_arguments, 96);
 AB_RECORD_HAS(ordered_row_sum_publish_arguments, 104);
 AB_RECORD_HAS(ordered_publish_reduce_arguments, 104);
+AB_RECORD_HAS(ordered_publish_reduce_bf16_arguments, 120);
 AB_RECORD_HAS(ordered_push_arguments, 96);
 AB_RECORD_HAS(tp_exchange_arguments, 112);
 AB_RECORD_HAS(ordered_rows_push_arguments, 112);

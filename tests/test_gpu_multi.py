@@ -348,3 +348,77 @@ def test_copy_launches_to_peers_at_once(api):
         finally:
             for card in cards:
                 card.close()
+
+
+@pytest.mark.parametrize("shared", [1, 0])
+def test_original_weights_layer_tensor_parallel(api, oracle, shared):
+    """The original-weights decode layer on R cards (every rank its own column slice of the MXFP4 experts and of the
+    always-on expert): its reduction is one launch a rank (row sums of the bfloat16 pair outputs, the always-on
+    expert's rows, READY and the rank-ordered sum, flags in the reader's memory). Every rank ends with the same bits;
+    they are the oracle's rank-ordered sum of the FP32 rows the ranks published; a rank's published rows are its pair
+    outputs added in slot order, its always-on rows, and one addition onto +0, bit for bit."""
+    from anemone_b200.mx import MxLayer, MxLayout
+    from tests.test_gpu_mx import mx_matrix
+    for ranks in world_sizes(api):
+        config = MoeConfig(hidden=512, inner=128 * ranks, experts=12, shared=shared, picks=3, row_capacity=8,
+                           activation_limit=7.0)
+        rng = np.random.default_rng(700 + ranks)
+        H = config.hidden
+        cards, layers = [], []
+        try:
+            for rank in range(ranks):
+                L = MxLayout(config, ranks, rank)
+                assert L.flags
+                I = L.inner_local
+                card = api.Card(rank, L.arena_bytes)
+                cards.append(card)
+                matrices = [(mx_matrix(oracle, rng, I, H), mx_matrix(oracle, rng, I, H), mx_matrix(oracle, rng, H, I))
+                            for _ in range(config.experts)]
+                always = (synthetic.e4m3_matrix(rng, I, H), synthetic.e4m3_matrix(rng, I, H),
+                          synthetic.e4m3_matrix(rng, H, I)) if shared else None
+                layers.append(MxLayer(card, config, matrices, rank=rank, rank_count=ranks, slices=(2, 2),
+                                      shared_matrices=always))
+            for layer in layers:
+                layer.connect_local(layers)
+            for card in cards:
+                card.wait()
+            for step in range(4):
+                rows = [8, 3, 8, 1][step]
+                tokens = synthetic.tokens(rng, rows, H)
+                scores = rng.normal(0, 1, size=(rows, config.experts)).astype(np.float32)
+                result_at = api.align(layers[0].layout.step_input_bytes, 4096)
+                tickets = []
+                for layer in layers:  # queue every rank before waiting for any
+                    layer.sequence += 1
+                    layer.stage_step(0, layer.sequence, tokens, scores)
+                    tickets.append(layer.submit(0, result_at, rows))
+                outputs, published = [], []
+                for layer, ticket in zip(layers, tickets):
+                    layer.card.transfer_wait(ticket)
+                    layer.check_status()
+                    outputs.append(layer.card.staging_view[result_at:result_at + rows * H * 2].view(np.uint16).copy())
+                for rank in range(1, ranks):
+                    assert np.array_equal(outputs[rank], outputs[0])
+                for layer in layers:
+                    L = layer.layout
+                    slot = L.region + (layer.sequence & 1) * L.parity_stride + L.slot_input
+                    mine = layer.card.download(slot, rows * H * 4, np.float32)
+                    published.append(mine)
+                    pairs = synthetic.from_bfloat16(layer.card.download(L.at["pair_output"], rows * config.picks * H * 2,
+                                                                       np.uint16)).reshape(rows, config.picks, H)
+                    resummed = np.zeros((rows, H), dtype=np.float32)
+                    for slot_index in range(config.picks):
+                        resummed = (resummed + pairs[:, slot_index, :]).astype(np.float32)
+                    if shared:
+                        resummed = (resummed + synthetic.from_bfloat16(layer.card.download(
+                            L.shared_at["output"], rows * H * 2, np.uint16)).reshape(rows, H)).astype(np.float32)
+                    row_output = layer.card.download(L.at["row_output"], rows * H * 4, np.float32).reshape(rows, H)
+                    assert np.array_equal(resummed.view(np.uint32), row_output.view(np.uint32))
+                    assert np.array_equal((np.float32(0.0) + resummed).view(np.uint32).reshape(-1), mine.view(np.uint32))
+                    assert np.any(mine != 0)
+                want = np.zeros(rows * H, dtype=np.uint16)
+                oracle.orc_ordered_reduce_bf16(pointer_array(published), ranks, want.size, ptr(want, u16p))
+                assert np.array_equal(outputs[0], want)
+        finally:
+            for card in cards:
+                card.close()
