@@ -48,6 +48,44 @@ result_status router_select_b200_prepare(const struct router_select_b200_argumen
 	return STATUS_OK;
 }
 
+/* router_select_b200 and the quantizer of the step's rows in one launch: both records as their own preparers accept
+ * them (the quantizer's as linear_quantize_prepare writes it, handed over with that launch). */
+result_status router_select_quantize_prepare(const struct router_select_b200_arguments *router,
+					     const struct kernel_launch *quantize_launch, uint64_t arena_byte_count,
+					     const struct backend_operations *backend, struct device_card *card,
+					     struct kernel_launch *launch_out)
+{
+	struct kernel_launch checked;
+	if (quantize_launch == NULL || quantize_launch->argument_byte_count != sizeof(struct activation_quantize_arguments) ||
+	    quantize_launch->block[0] != 32u || quantize_launch->grid[0] == 0 || quantize_launch->grid[1] == 0)
+		return STATUS_INVALID_ARGUMENT;
+	const result_status valid = router_select_b200_prepare(router, arena_byte_count, backend, card, &checked);
+	if (valid != STATUS_OK)
+		return valid;
+	struct router_select_quantize_arguments arguments = { .router = *router,
+							       .vector_count = quantize_launch->grid[1],
+							       .reserved_zero = 0 };
+	memcpy(&arguments.quantize, quantize_launch->argument, sizeof(arguments.quantize));
+	if (arguments.quantize.width == 0 || arguments.quantize.width % 64u != 0 ||
+	    arguments.quantize.width / 64u != quantize_launch->grid[0] || arguments.quantize.reserved_zero != 0)
+		return STATUS_INVALID_ARGUMENT;
+	uint32_t kernel = BACKEND_NO_KERNEL;
+	const result_status status = backend->kernel_prepare(card, KERNEL_FILE_ROUTER_B200, KERNEL_ROUTER_SELECT_QUANTIZE,
+							     sizeof(arguments), &kernel);
+	if (status != STATUS_OK)
+		return status;
+	if (kernel == BACKEND_NO_KERNEL)
+		return STATUS_UNSUPPORTED;
+	const uint64_t tasks = (uint64_t)arguments.vector_count * (arguments.quantize.width / 64u);
+	const uint64_t warps = ROUTER_B200_THREADS / 32u;
+	uint64_t blocks = (tasks + warps - 1u) / warps;
+	if (blocks > 1024u)
+		blocks = 1024u; /* the warps walk the rest */
+	prepare_launch_fill(launch_out, kernel, 1u + (uint32_t)blocks, 1, 1, ROUTER_B200_THREADS, 0, &arguments,
+			    sizeof(arguments));
+	return STATUS_OK;
+}
+
 result_status router_wide_prepare(const struct router_wide_arguments *arguments, uint64_t arena_byte_count,
 				  const struct backend_operations *backend, struct device_card *card,
 				  struct kernel_launch *launches_out)

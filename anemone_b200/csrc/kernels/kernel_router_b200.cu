@@ -13,10 +13,12 @@
  * (router_device.cuh), so that the choice can be restated bit for bit on a host; always-on shared experts get jobs
  * behind the routed ones.
  */
+#include "activation_quantize_device.cuh"
 #include "router_device.cuh"
 
-extern "C" __global__ void __launch_bounds__(ROUTER_B200_THREADS)
-	router_select_b200(struct router_select_b200_arguments arguments, unsigned char *arena)
+/* router_select_b200's one block */
+__device__ __forceinline__ void router_select_block(const struct router_select_b200_arguments &arguments,
+						    unsigned char *arena)
 {
 	__shared__ uint32_t chosen[ROUTER_B200_MAXIMUM_ROWS][ROUTER_B200_MAXIMUM_PICKS]; /* by slot */
 	__shared__ float weight[ROUTER_B200_MAXIMUM_ROWS][ROUTER_B200_MAXIMUM_PICKS];
@@ -54,6 +56,27 @@ extern "C" __global__ void __launch_bounds__(ROUTER_B200_THREADS)
 	router_job_table(live, experts, picks, shared, arguments.job_capacity, chosen, weight, row_mask, first_job,
 			 reinterpret_cast<struct expert_job_record *>(arena + arguments.jobs_offset),
 			 reinterpret_cast<const uint64_t *>(arena + arguments.expert_table_offset), nullptr);
+}
+
+extern "C" __global__ void __launch_bounds__(ROUTER_B200_THREADS)
+	router_select_b200(struct router_select_b200_arguments arguments, unsigned char *arena)
+{
+	router_select_block(arguments, arena);
+}
+
+/* grid (1 + quantizer blocks) x ROUTER_B200_THREADS: block 0 is the router's block, the warps of the others take the
+ * quantizer's loads of 64 values, row after row */
+extern "C" __global__ void __launch_bounds__(ROUTER_B200_THREADS)
+	router_select_quantize(struct router_select_quantize_arguments arguments, unsigned char *arena)
+{
+	if (blockIdx.x == 0) {
+		router_select_block(arguments.router, arena);
+		return;
+	}
+	const uint32_t warps = blockDim.x / WARP, loads = arguments.quantize.width / 64u;
+	const uint32_t tasks = arguments.vector_count * loads;
+	for (uint32_t task = (blockIdx.x - 1u) * warps + threadIdx.x / WARP; task < tasks; task += (gridDim.x - 1u) * warps)
+		activation_quantize_load(arguments.quantize, arena, task / loads, task % loads, threadIdx.x % WARP);
 }
 
 /* One block: copy the pool entry the cursor names into the step input area, then advance the cursor. */

@@ -167,6 +167,18 @@ class MxLayer:
         quantize_launch = R.KernelLaunch()
         api.check(lib.linear_quantize_prepare(C.byref(quantize), card.arena_bytes, C.byref(kernels),
                                               C.byref(quantize_launch)), "linear_quantize_prepare")
+        head = router_launches + [quantize_launch]
+        if not wide:
+            # a decode step begins with the router and the rows' quantization, neither of which reads the other's
+            # output: one launch (block 0 routes, the others quantize)
+            lib.router_select_quantize_prepare.argtypes = [C.POINTER(R.RouterSelectB200), C.POINTER(R.KernelLaunch),
+                                                           C.c_uint64, C.POINTER(api.BackendOperations), C.c_void_p,
+                                                           C.POINTER(R.KernelLaunch)]
+            first = R.KernelLaunch()
+            api.check(lib.router_select_quantize_prepare(C.byref(router), C.byref(quantize_launch), card.arena_bytes,
+                                                         card.ops_pointer, card.handle, C.byref(first)),
+                      "router_select_quantize_prepare")
+            head = [first]
         description = R.LinearRoutedExpertsDescription()
         description.jobs = R.LinearRange(L.jobs, L.job_capacity * 96)
         description.expert_weights = R.LinearRange(L.weights_begin, L.weights_end - L.weights_begin)
@@ -270,9 +282,9 @@ class MxLayer:
                 launch.branch = R.LAUNCH_SIDE
             self.expert_launches[0].branch = R.LAUNCH_RESUME
             behind[0].branch = R.LAUNCH_JOIN
-            self.launches = router_launches + [quantize_launch] + shared_launches[:4] + self.step_launches + behind
+            self.launches = head + shared_launches[:4] + self.step_launches + behind
         else:
-            self.launches = router_launches + [quantize_launch] + self.step_launches + shared_launches[:4] + behind
+            self.launches = head + self.step_launches + shared_launches[:4] + behind
         self.graph = card.graph(self.launches)
         self.resident_graph = None
         if L.pool_entries:

@@ -264,6 +264,11 @@ class ActivationQuantize(C.Structure):
                 ("operands_offset", C.c_uint64), ("width", C.c_uint32), ("reserved_zero", C.c_uint32)]
 
 
+class RouterSelectQuantize(C.Structure):
+    _fields_ = [("router", RouterSelectB200), ("quantize", ActivationQuantize), ("vector_count", C.c_uint32),
+                ("reserved_zero", C.c_uint32)]
+
+
 class ExpertGateUp(C.Structure):
     _fields_ = [("jobs_offset", C.c_uint64), ("codes_offset", C.c_uint64), ("exponents_offset", C.c_uint64),
                 ("operands_offset", C.c_uint64), ("hidden_offset", C.c_uint64), ("output_size", C.c_uint32),

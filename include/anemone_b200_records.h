@@ -879,6 +879,20 @@ struct activation_quantize_arguments {
 	uint32_t reserved_zero;
 };
 
+/* B200 extension, kernel file "kernel_router_b200", entry "router_select_quantize": router_select_b200 and the
+ * activation quantizer of the step's rows in ONE launch (neither reads what the other writes: a decode step of the
+ * original-weights layer begins with both). Block 0 is router_select_b200's block; every warp of the blocks behind it
+ * takes loads of 64 values of the rows (activation_quantize_entry's task). grid (1 + ceil(vector_count * width / 64 /
+ * 32)), block ROUTER_B200_THREADS. */
+#define KERNEL_ROUTER_SELECT_QUANTIZE "router_select_quantize"
+struct router_select_quantize_arguments {
+	struct router_select_b200_arguments router;
+	struct activation_quantize_arguments quantize;
+	uint32_t vector_count; /* rows the quantizer takes: the capacity, as the separate launch */
+	uint32_t reserved_zero;
+};
+
+
 /* expert_gate_up_<S>: grid (output_size / 16, jobs), block 64 S; writes hidden bfloat16 [pair][output_size] */
 struct expert_gate_up_arguments {
 	uint64_t jobs_offset;
@@ -980,6 +994,7 @@ AB_RECORD_HAS(exl3_prefill_tile, 16);
 AB_RECORD_HAS(exl3_prefill_entry, 8);
 AB_RECORD_HAS(exl3_prefill_record, 136);
 AB_RECORD_HAS(router_wide_arguments, 152);
+AB_RECORD_HAS(router_select_quantize_arguments, 136);
 AB_RECORD_HAS(activation_quantize_arguments, 40);
 AB_RECORD_HAS(expert_gate_up_arguments, 64);
 AB_RECORD_HAS(expert_down_arguments, 56);

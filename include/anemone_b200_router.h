@@ -25,6 +25,16 @@ MUST_CHECK result_status router_select_b200_prepare(const struct router_select_b
 						    const struct backend_operations *backend, struct device_card *card,
 						    struct kernel_launch *launch_out);
 
+/* B200 extension: router_select_b200 and the activation quantizer of the step's rows in ONE launch
+ * ("router_select_quantize", struct router_select_quantize_arguments): the first launch of an original-weights decode
+ * step. router: as router_select_b200_prepare takes it; quantize_launch: the launch linear_quantize_prepare wrote for
+ * the rows (its record and row count are taken over). The results are the two launches'. */
+MUST_CHECK result_status router_select_quantize_prepare(const struct router_select_b200_arguments *router,
+							const struct kernel_launch *quantize_launch,
+							uint64_t arena_byte_count,
+							const struct backend_operations *backend, struct device_card *card,
+							struct kernel_launch *launch_out);
+
 /* B200 extension: the job table of many rows (struct router_wide_arguments): ROUTER_WIDE_LAUNCHES launches. Checks
  * the counts against the kernels' limits, routing.local_first == 0, local_count == expert_count, shared_count == 0,
  * job_capacity >= row_capacity * picks / 8 + expert_count, and the ranges (scores, bias, expert table, picks, weights,

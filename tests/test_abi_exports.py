@@ -65,7 +65,8 @@ def test_record_sizes_match_the_headers():
               "exact_ring_arguments": R.ExactRing, "exl3_layer_products_record": R.Exl3LayerProducts,
               "router_wide_arguments": R.RouterWide, "expert_gate_up_many_arguments": R.ExpertGateUpMany,
               "expert_down_many_arguments": R.ExpertDownMany,
-              "ordered_publish_reduce_bf16_arguments": R.OrderedPublishReduceBf16}
+              "ordered_publish_reduce_bf16_arguments": R.OrderedPublishReduceBf16,
+              "router_select_quantize_arguments": R.RouterSelectQuantize}
     assert set(declared) == set(mirror)
     for name, record in mirror.items():
         assert C.sizeof(record) == int(declared[name]), name

@@ -483,3 +483,50 @@ def test_routed_experts_wide_prepare():
         assert bytes(wide) == untouched
     assert wide_prepare(C.byref(d), arena, C.byref(kernels), None, fake.card, wide) == 1
     assert wide_prepare(C.byref(d), arena - 8192, C.byref(kernels), C.byref(fake.table), fake.card, wide) == 1
+
+
+def test_router_select_quantize_prepare():
+    """The router and the rows' quantizer as one launch: both records taken over as their own preparers accept them."""
+    lib, fake = api.library(), FakeBackend()
+    lib.linear_kernels_prepare.argtypes = [C.POINTER(api.BackendOperations), C.c_void_p, C.c_uint32,
+                                           C.POINTER(R.LinearKernels)]
+    kernels = R.LinearKernels()
+    assert lib.linear_kernels_prepare(C.byref(fake.table), fake.card, 100, C.byref(kernels)) == 0
+    lib.linear_quantize_prepare.argtypes = [C.POINTER(R.LinearQuantizeDescription), C.c_uint64,
+                                            C.POINTER(R.LinearKernels), C.POINTER(R.KernelLaunch)]
+    lib.router_select_quantize_prepare.argtypes = [C.POINTER(R.RouterSelectB200), C.POINTER(R.KernelLaunch), C.c_uint64,
+                                                   C.POINTER(api.BackendOperations), C.c_void_p,
+                                                   C.POINTER(R.KernelLaunch)]
+    rows, experts, picks, H = 8, 64, 4, 1024
+    layout = api.Layout(256)
+    scores, table = layout.take(rows * experts * 4), layout.take(experts * 24)
+    picked, weights, jobs = layout.take(rows * picks * 4), layout.take(rows * picks * 4), layout.take(rows * picks * 96)
+    step, values = layout.take(16), layout.take(rows * H * 2)
+    codes, exponents, operands = layout.take(rows * H), layout.take(rows * H // 32), layout.take(rows * H * 2)
+    arena = layout.take(0, 4096) + 4096
+    router = R.RouterSelectB200(scores, table, picked, weights, jobs, step, experts, 0, picks, rows, rows * picks, 0,
+                                1.0, 0)
+    quantize = R.LinearQuantizeDescription(R.LinearRange(values, rows * H * 2), R.LinearRange(codes, rows * H),
+                                           R.LinearRange(exponents, rows * H // 32),
+                                           R.LinearRange(operands, rows * H * 2), H, rows)
+    quantize_launch, launch = R.KernelLaunch(), R.KernelLaunch()
+    assert lib.linear_quantize_prepare(C.byref(quantize), arena, C.byref(kernels), C.byref(quantize_launch)) == 0
+    assert lib.router_select_quantize_prepare(C.byref(router), C.byref(quantize_launch), arena, C.byref(fake.table),
+                                              fake.card, C.byref(launch)) == 0
+    assert ("kernel_router_b200", "router_select_quantize", 136) in fake.asked
+    assert tuple(launch.grid) == (1 + (rows * H // 64 + 31) // 32, 1, 1) and launch.block[0] == 1024
+    record = R.RouterSelectQuantize.from_buffer_copy(bytes(launch.argument[:136]))
+    assert bytes(record.router) == bytes(router) and bytes(record.quantize) == bytes(quantize_launch.argument[:40])
+    assert record.vector_count == rows and record.reserved_zero == 0
+    untouched = bytes(launch)
+    bad = R.RouterSelectB200.from_buffer_copy(bytes(router))
+    bad.picks = 17
+    assert lib.router_select_quantize_prepare(C.byref(bad), C.byref(quantize_launch), arena, C.byref(fake.table),
+                                              fake.card, C.byref(launch)) == 1
+    other = R.KernelLaunch.from_buffer_copy(bytes(quantize_launch))
+    other.block[0] = 64
+    assert lib.router_select_quantize_prepare(C.byref(router), C.byref(other), arena, C.byref(fake.table), fake.card,
+                                              C.byref(launch)) == 1
+    assert lib.router_select_quantize_prepare(C.byref(router), None, arena, C.byref(fake.table), fake.card,
+                                              C.byref(launch)) == 1
+    assert bytes(launch) == untouched
