@@ -530,3 +530,51 @@ def test_router_select_quantize_prepare():
     assert lib.router_select_quantize_prepare(C.byref(router), None, arena, C.byref(fake.table), fake.card,
                                               C.byref(launch)) == 1
     assert bytes(launch) == untouched
+
+
+def test_publish_reduce_bf16_prepare():
+    """The original-weights decode step's reduction as one launch: its record, its grid and its refusals; the step
+    entries of the card interface refuse a card that is not there."""
+    lib, fake = api.library(), FakeBackend()
+    from anemone_b200.moe import MoeConfig
+    from anemone_b200.mx import MxLayout
+    config = MoeConfig(hidden=512, inner=256, experts=12, shared=1, picks=3, row_capacity=8, activation_limit=7.0)
+    L = MxLayout(config, 2, 1)
+    assert L.flags and L.slot_input == R.EXL3_LAYER_SIGNAL_BYTES
+    prepare = lib.ordered_publish_reduce_bf16_prepare
+    prepare.argtypes = [C.POINTER(R.OrderedReduceBf16Description), C.c_uint64, C.c_uint64,
+                        C.POINTER(api.BackendOperations), C.c_void_p, C.POINTER(R.KernelLaunch)]
+    description = R.OrderedReduceBf16Description()
+    description.reduce.collective = R.OrderedCollective(L.peer_table, L.region, L.slot_input, L.result, 0, L.step,
+                                                        L.parity_stride, 1000, 8 * 512, 2, 1, 0)
+    description.reduce.status_offset, description.reduce.width = L.status, 512
+    description.pair_output_offset, description.arena_byte_count = L.at["pair_output"], L.arena_bytes
+    description.pairs_per_row, description.row_capacity = 3, 8
+    launch = R.KernelLaunch()
+    addend, rows_at = L.shared_at["output"], L.at["row_output"]
+    assert prepare(C.byref(description), addend, rows_at, C.byref(fake.table), fake.card, C.byref(launch)) == 0
+    assert fake.asked[-1] == ("kernel_ordered_b200", "ordered_publish_reduce_flags_bf16", 120)
+    assert tuple(launch.grid) == (4, 1, 1) and launch.block[0] == 256 and launch.argument_byte_count == 120
+    record = R.OrderedPublishReduceBf16.from_buffer_copy(bytes(launch.argument[:120]))
+    assert bytes(record.base.collective) == bytes(description.reduce.collective)
+    assert (record.base.status_offset, record.base.pair_output_offset, record.base.width, record.base.pairs_per_row,
+            record.addend_offset, record.row_output_offset) == (L.status, L.at["pair_output"], 512, 3, addend, rows_at)
+    assert prepare(C.byref(description), 0, 0, C.byref(fake.table), fake.card, C.byref(launch)) == 0  # neither
+    untouched = bytes(launch)
+    for path, value in (("rank", 2), ("rank_count", 17), ("deadline_cycles", 0), ("region_offset", L.region + 64),
+                        ("input_offset", R.EXL3_LAYER_SIGNAL_BYTES - 128), ("parity_stride", L.parity_stride - 128),
+                        ("scratch_offset", 16)):
+        broken = R.OrderedReduceBf16Description.from_buffer_copy(bytes(description))
+        setattr(broken.reduce.collective, path, value)
+        assert prepare(C.byref(broken), addend, rows_at, C.byref(fake.table), fake.card, C.byref(launch)) == 1, path
+    for change in (dict(width=510), dict(mode=R.ORDERED_REDUCE_OWNER_RUNS)):
+        broken = R.OrderedReduceBf16Description.from_buffer_copy(bytes(description))
+        for name, value in change.items():
+            setattr(broken.reduce, name, value)
+        assert prepare(C.byref(broken), addend, rows_at, C.byref(fake.table), fake.card, C.byref(launch)) == 1, change
+    assert prepare(C.byref(description), addend + 8, rows_at, C.byref(fake.table), fake.card, C.byref(launch)) == 1
+    assert prepare(C.byref(description), addend, L.region, C.byref(fake.table), fake.card, C.byref(launch)) == 1
+    assert bytes(launch) == untouched
+    graph = C.c_uint32(7)
+    assert lib.backend_b200_step_capture(None, launch, 1, 0, None, 0, 0, None, 0, C.byref(graph)) == 1
+    assert lib.backend_b200_graph_run_wait(None, 0) == 1 and graph.value == 7
